@@ -1,0 +1,97 @@
+/*
+ * pssa_b200 — C ABI of the B200-native PSSA inference forward path.
+ *
+ * This is the drop-in boundary: the entry points below are what a `GpuDispatch::B200` /
+ * `Device::B200` arm of the reference crate (src/backend.rs:1012-1029) binds over FFI.
+ * Plain pointers and sizes only. All matrices are row-major f32 unless stated otherwise.
+ *
+ * Conventions
+ *  - Every function returns a `pssa_b200_status`. On failure the message is available from
+ *    `pssa_b200_last_error(ctx)`; caller-owned outputs are left untouched when validation
+ *    fails (reference behaviour: src/backend.rs:684-686, tests/backend.rs:66-82).
+ *  - Shape validation happens before any allocation or launch and uses the reference's
+ *    wording "refusing launch" (src/cuda/stage_bounds.rs:5-65).
+ *  - `*_dev` functions take DEVICE pointers, enqueue on the context's stream and return
+ *    without synchronising. Functions without the suffix take HOST pointers, stage them
+ *    through the context's device arena and return after the result is back on the host,
+ *    which is the contract of the reference's `GpuDispatch` methods (src/cuda.rs:517-585).
+ *  - There is no CPU fallback anywhere behind this header: without a CUDA device every
+ *    compute entry point fails with PSSA_B200_ERR_CUDA.
+ *  - A context is single-threaded, like a reference model (`&mut self` on every call).
+ */
+#ifndef PSSA_B200_H
+#define PSSA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum pssa_b200_status {
+    PSSA_B200_OK = 0,
+    PSSA_B200_ERR_INVALID_ARGUMENT = 1, /* null pointer, bad enum, bad handle */
+    PSSA_B200_ERR_SHAPE = 2,            /* dimension / length check failed; nothing launched */
+    PSSA_B200_ERR_CUDA = 3,             /* recoverable CUDA error (no device, allocation, ...) */
+    PSSA_B200_ERR_FATAL_CUDA = 4,       /* context lost: src/cuda.rs:592-602 classes */
+    PSSA_B200_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up */
+    PSSA_B200_ERR_UNSUPPORTED = 6,      /* option the device path refuses (src/pssa.rs:2080-2243) */
+    PSSA_B200_ERR_TOKEN = 7,            /* token id outside the vocabulary */
+    PSSA_B200_ERR_CANCELLED = 8         /* the caller's cancellation callback fired */
+} pssa_b200_status;
+
+typedef struct pssa_b200_ctx pssa_b200_ctx;     /* one device, one stream, one scratch arena */
+typedef struct pssa_b200_model pssa_b200_model; /* device-resident weights, banks and carries */
+
+/* ------------------------------------------------------------------ context */
+
+/* Replaces `CudaContext::init` (src/cuda.rs:168-196); `device` is a CUDA ordinal. */
+int32_t pssa_b200_ctx_create(int32_t device, pssa_b200_ctx** out);
+void pssa_b200_ctx_destroy(pssa_b200_ctx* ctx);
+/* Message of the last failure on `ctx` (or of the last failed create when ctx is NULL). */
+const char* pssa_b200_last_error(const pssa_b200_ctx* ctx);
+/* Use an existing cudaStream_t (e.g. the caller framework's current stream); NULL = own stream. */
+int32_t pssa_b200_ctx_set_stream(pssa_b200_ctx* ctx, void* cuda_stream);
+int32_t pssa_b200_ctx_synchronize(pssa_b200_ctx* ctx);
+/* Replaces `backend_label` (src/backend.rs:1439-1446): "b200 (<device name>)". */
+const char* pssa_b200_backend_label(const pssa_b200_ctx* ctx);
+/* Number of kernels of this library launched on `ctx` since creation. */
+uint64_t pssa_b200_launch_count(const pssa_b200_ctx* ctx);
+/* Pre-size the context's scratch arena (bytes) so later calls do not allocate. */
+int32_t pssa_b200_ctx_reserve(pssa_b200_ctx* ctx, size_t bytes);
+
+/* Force the number of time chunks of the scan (0 = automatic). A test hook: with more than one
+ * chunk the scan runs its reduce / carry / apply passes even on shapes that would not need them. */
+int32_t pssa_b200_ctx_set_scan_chunks(pssa_b200_ctx* ctx, uint32_t chunks);
+
+/* ------------------------------------------------------------------ scan operator */
+
+/*
+ * In-place EXCLUSIVE prefix of diagonal affine maps over time, `lanes` independent problems.
+ * scan_a/scan_b: [lanes, len, stride]; on return row t holds the composition of rows < t
+ * (row 0 = identity). Replaces `affine_scan_in_place` (src/gpu_batch.rs:98-164) and the
+ * `affine_scan` launch (src/cuda/stages.rs:212-259, shape rule src/cuda/stage_bounds.rs:45-65).
+ * No power-of-two padding is needed.
+ */
+int32_t pssa_b200_affine_scan_dev(pssa_b200_ctx* ctx, float* scan_a, float* scan_b, size_t lanes,
+                                  size_t len, size_t stride);
+int32_t pssa_b200_affine_scan(pssa_b200_ctx* ctx, float* scan_a, float* scan_b, size_t lanes,
+                              size_t len, size_t stride);
+
+/*
+ * All prefix states of h_t = a_t * h_{t-1} + b_t (multiply, then add, each rounded: the order
+ * of src/gpu_batch.rs:543-575). a, b, h: [lanes, len, stride]; h0 and h_last: [lanes, stride],
+ * either may be NULL (zero carry in / carry out not wanted). h may alias b. This is the scan
+ * operator "alone": 12 bytes of HBM traffic per element.
+ */
+int32_t pssa_b200_scan_states_dev(pssa_b200_ctx* ctx, const float* a, const float* b,
+                                  const float* h0, float* h, float* h_last, size_t lanes,
+                                  size_t len, size_t stride);
+int32_t pssa_b200_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0,
+                              float* h, float* h_last, size_t lanes, size_t len, size_t stride);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PSSA_B200_H */

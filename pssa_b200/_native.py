@@ -1,0 +1,58 @@
+"""ctypes binding of include/pssa_b200.h. Fails loudly when the CUDA library is missing: there is
+no CPU fallback behind this package."""
+import ctypes as C
+import pathlib
+
+PKG = pathlib.Path(__file__).resolve().parent
+LIB_PATH = PKG / "libpssa_b200.so"
+
+OK, ERR_INVALID_ARGUMENT, ERR_SHAPE, ERR_CUDA, ERR_FATAL_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_TOKEN, \
+    ERR_CANCELLED = range(9)
+
+_fp = C.POINTER(C.c_float)
+_vp = C.c_void_p
+_sz = C.c_size_t
+
+# name -> (restype, argtypes); every symbol include/pssa_b200.h declares
+SIGNATURES = {
+    "pssa_b200_ctx_create": (C.c_int32, [C.c_int32, C.POINTER(_vp)]),
+    "pssa_b200_ctx_destroy": (None, [_vp]),
+    "pssa_b200_last_error": (C.c_char_p, [_vp]),
+    "pssa_b200_ctx_set_stream": (C.c_int32, [_vp, _vp]),
+    "pssa_b200_ctx_synchronize": (C.c_int32, [_vp]),
+    "pssa_b200_backend_label": (C.c_char_p, [_vp]),
+    "pssa_b200_launch_count": (C.c_uint64, [_vp]),
+    "pssa_b200_ctx_reserve": (C.c_int32, [_vp, _sz]),
+    "pssa_b200_ctx_set_scan_chunks": (C.c_int32, [_vp, C.c_uint32]),
+    "pssa_b200_affine_scan_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz]),
+    "pssa_b200_affine_scan": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz]),
+    "pssa_b200_scan_states_dev": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "pssa_b200_scan_states": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Load libpssa_b200.so (built in-tree by pssa_b200.build). Raises if it is absent."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m pssa_b200.build` (needs nvcc). "
+                "The B200 path has no CPU fallback.")
+        L = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+class B200Error(RuntimeError):
+    """A non-zero status from the C ABI; `.status` holds the code, the text is the library's message."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status

@@ -1,0 +1,38 @@
+// Driver-free shape validation run before any allocation or launch.
+// Same role and wording as the reference's src/cuda/stage_bounds.rs:5-65 ("refusing launch"),
+// with this library's limits: element counts are indexed with 64-bit offsets on the device, so the
+// only caps are size_t products and a byte size that fits isize.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+#include "context.hpp"
+
+namespace pssa {
+
+inline bool checked_mul(size_t a, size_t b, size_t* out) {
+    if (a != 0 && b > SIZE_MAX / a) return false;
+    *out = a * b;
+    return true;
+}
+
+// product of dims as an f32 element count whose byte size fits isize (stage_bounds.rs:5-30)
+inline int32_t f32_elems(pssa_b200_ctx* ctx, const char* what, std::initializer_list<size_t> dims, size_t* out) {
+    size_t n = 1;
+    for (size_t d : dims)
+        if (!checked_mul(n, d, &n))
+            return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 %s: size overflow; refusing launch", what);
+    if (n > (size_t)INTPTR_MAX / 4)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 %s: f32 allocation byte size overflow; refusing launch", what);
+    *out = n;
+    return PSSA_B200_OK;
+}
+
+// stage_bounds.rs:45-65
+inline int32_t scan_shape(pssa_b200_ctx* ctx, size_t lanes, size_t len, size_t stride, size_t* elems) {
+    if (lanes == 0 || len == 0 || stride == 0)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 affine scan dimensions must be positive; refusing launch");
+    return f32_elems(ctx, "affine scan elements", {lanes, len, stride}, elems);
+}
+
+}  // namespace pssa

@@ -1,0 +1,85 @@
+// Per-device context shared by every entry point: stream, scratch arena, error text.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/pssa_b200.h"
+
+struct pssa_b200_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    // scratch arena: one growing device allocation, carved per call (no per-call cudaMalloc once warm)
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    size_t arena_used = 0;
+    // pinned staging for the host-pointer entry points
+    std::string error;
+    std::string label;
+    uint64_t launches = 0;
+    int sm_count = 148;
+    // device status word for bounded waits (0 = ok)
+    int* status_dev = nullptr;
+    int scan_chunks = 0;  // 0 = choose automatically; tests force the multi-chunk passes with it
+};
+
+namespace pssa {
+
+extern thread_local std::string g_create_error;
+
+inline int32_t fail(pssa_b200_ctx* ctx, int32_t code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx)
+        ctx->error = buf;
+    else
+        g_create_error = buf;
+    return code;
+}
+
+// Fatal classes follow src/cuda.rs:592-602: once seen the context is unusable.
+inline bool cuda_error_is_fatal(cudaError_t e) {
+    return e == cudaErrorIllegalAddress || e == cudaErrorContextIsDestroyed || e == cudaErrorDevicesUnavailable ||
+           e == cudaErrorLaunchTimeout || e == cudaErrorIllegalInstruction || e == cudaErrorMisalignedAddress ||
+           e == cudaErrorHardwareStackError || e == cudaErrorLaunchFailure;
+}
+
+inline int32_t cuda_fail(pssa_b200_ctx* ctx, cudaError_t e, const char* what) {
+    return fail(ctx, cuda_error_is_fatal(e) ? PSSA_B200_ERR_FATAL_CUDA : PSSA_B200_ERR_CUDA, "CUDA %s: %s (%s)", what,
+                cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+#define PSSA_CUDA(ctx, call)                                      \
+    do {                                                          \
+        cudaError_t e__ = (call);                                 \
+        if (e__ != cudaSuccess) return pssa::cuda_fail(ctx, e__, #call); \
+    } while (0)
+
+// Arena: reset at the start of an entry point, then bump-allocate 256-byte aligned blocks.
+int32_t arena_reserve(pssa_b200_ctx* ctx, size_t bytes);
+inline void arena_reset(pssa_b200_ctx* ctx) { ctx->arena_used = 0; }
+// Call after the total need is known (arena_reserve) so pointers stay valid.
+inline void* arena_take(pssa_b200_ctx* ctx, size_t bytes) {
+    size_t off = (ctx->arena_used + 255) & ~size_t(255);
+    if (off + bytes > ctx->arena_bytes) return nullptr;
+    ctx->arena_used = off + bytes;
+    return ctx->arena + off;
+}
+inline size_t arena_round(size_t bytes) { return (bytes + 255) & ~size_t(255); }
+
+// Launch bookkeeping: every kernel launch of this library goes through here.
+inline int32_t after_launch(pssa_b200_ctx* ctx, const char* kernel) {
+    ctx->launches += 1;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(ctx, e, kernel);
+    return PSSA_B200_OK;
+}
+
+}  // namespace pssa

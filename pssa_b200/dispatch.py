@@ -1,0 +1,128 @@
+"""Host-side mirror of the reference's device seam (`Device` / `GpuDispatch`, src/backend.rs:1012-1482).
+
+Method names, argument meaning and error behaviour follow the reference; every method is a thin call
+into the C ABI. numpy arrays are host buffers (the reference's `&[f32]` slices); the `*_dev` methods
+take device pointers (ints) or objects with `.data_ptr()` (torch tensors) and only enqueue work.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import _native as N
+
+
+def _ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return C.c_void_p(x)
+    if isinstance(x, np.ndarray):
+        return C.c_void_p(x.ctypes.data)
+    if hasattr(x, "data_ptr"):
+        return C.c_void_p(x.data_ptr())
+    raise TypeError(f"cannot take a pointer of {type(x)}")
+
+
+def _host(a, name, shape=None):
+    if not isinstance(a, np.ndarray) or a.dtype != np.float32 or not a.flags["C_CONTIGUOUS"]:
+        raise TypeError(f"{name} must be a C-contiguous float32 numpy array")
+    if shape is not None and tuple(a.shape) != tuple(shape):
+        raise ValueError(f"{name} has shape {a.shape}, expected {shape}")
+    return a
+
+
+class B200Dispatch:
+    """One context on one B200 (`GpuDispatch::B200`)."""
+
+    def __init__(self, device: int = 0, stream=None):
+        self._lib = N.lib()
+        h = C.c_void_p()
+        rc = self._lib.pssa_b200_ctx_create(device, C.byref(h))
+        if rc != N.OK:
+            raise N.B200Error(rc, self._lib.pssa_b200_last_error(None).decode())
+        self._h = h
+        self.device = device
+        if stream is not None:
+            self.set_stream(stream)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.pssa_b200_ctx_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != N.OK:
+            raise N.B200Error(rc, self._lib.pssa_b200_last_error(self._h).decode())
+
+    # ---- context
+    def set_stream(self, stream):
+        """`stream`: a cudaStream_t as int, or a torch.cuda.Stream."""
+        raw = getattr(stream, "cuda_stream", stream)
+        self._check(self._lib.pssa_b200_ctx_set_stream(self._h, C.c_void_p(raw)))
+
+    def synchronize(self):
+        self._check(self._lib.pssa_b200_ctx_synchronize(self._h))
+
+    def backend_label(self) -> str:  # src/backend.rs:1439-1446
+        return self._lib.pssa_b200_backend_label(self._h).decode()
+
+    def launch_count(self) -> int:
+        return int(self._lib.pssa_b200_launch_count(self._h))
+
+    def reserve(self, nbytes: int):
+        self._check(self._lib.pssa_b200_ctx_reserve(self._h, nbytes))
+
+    def set_scan_chunks(self, chunks: int):
+        self._check(self._lib.pssa_b200_ctx_set_scan_chunks(self._h, chunks))
+
+    # ---- scan operator
+    def affine_scan_in_place(self, scan_a: np.ndarray, scan_b: np.ndarray, length: int, stride: int, lanes: int = 1):
+        """Exclusive prefix of affine maps, in place (src/gpu_batch.rs:98-164). Host arrays."""
+        _host(scan_a, "scan_a")
+        _host(scan_b, "scan_b")
+        if scan_a.size != lanes * length * stride or scan_b.size != lanes * length * stride:
+            raise N.B200Error(N.ERR_SHAPE, "B200 affine scan: buffers must hold lanes*len*stride elements; refusing launch")
+        self._check(self._lib.pssa_b200_affine_scan(self._h, _ptr(scan_a), _ptr(scan_b), lanes, length, stride))
+
+    def affine_scan_dev(self, scan_a, scan_b, lanes: int, length: int, stride: int):
+        self._check(self._lib.pssa_b200_affine_scan_dev(self._h, _ptr(scan_a), _ptr(scan_b), lanes, length, stride))
+
+    def scan_states(self, a: np.ndarray, b: np.ndarray, h0=None, want_last=False):
+        """All states of h_t = a_t*h_{t-1} + b_t for host arrays [lanes, len, stride]."""
+        _host(a, "a")
+        _host(b, "b", a.shape)
+        lanes, length, stride = a.shape
+        if h0 is not None:
+            _host(h0, "h0", (lanes, stride))
+        h = np.empty_like(a)
+        last = np.empty((lanes, stride), np.float32) if want_last else None
+        self._check(self._lib.pssa_b200_scan_states(self._h, _ptr(a), _ptr(b), _ptr(h0), _ptr(h), _ptr(last), lanes,
+                                                    length, stride))
+        return (h, last) if want_last else h
+
+    def scan_states_dev(self, a, b, h0, h, h_last, lanes: int, length: int, stride: int):
+        self._check(self._lib.pssa_b200_scan_states_dev(self._h, _ptr(a), _ptr(b), _ptr(h0), _ptr(h), _ptr(h_last),
+                                                        lanes, length, stride))
+
+
+class Device:
+    """`Device` of src/backend.rs:1012-1018 reduced to the arm this package adds."""
+
+    def __init__(self, dispatch: B200Dispatch):
+        self._dispatch = dispatch
+
+    @classmethod
+    def try_gpu(cls, device: int = 0) -> "Device":  # src/backend.rs:1467-1481
+        return cls(B200Dispatch(device))
+
+    def is_gpu(self) -> bool:
+        return True
+
+    def gpu(self) -> B200Dispatch:
+        return self._dispatch
