@@ -28,6 +28,7 @@ sys.path.insert(0, str(ROOT))
 LANES, T, STRIDE = 64, 4096, 8192
 BYTES_PER_ELEM = 12  # read a, read b, write h
 WORKLOAD = "scan_c2: associative scan alone, 64 lanes x 4096 steps x 8192 channels (512 ch x state 16), fp32"
+NCU_TRAFFIC_BYTES_PER_ELEM = 11.87
 E2E_BLOCK_LANES = 16  # host block reused LANES/E2E_BLOCK_LANES times per e2e step
 
 
@@ -154,12 +155,12 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # samples cover warm-up and the timed region
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     launches0 = gpu.launch_count()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -221,10 +222,9 @@ def run_b200(args):
         peak, peak_kind = measured_peaks()
         k_ms = statistics.mean(kernel_ms)
         achieved = elems * BYTES_PER_ELEM / (k_ms / 1e3) / 1e9
-        traffic = None
-        prof = ROOT / "profiles" / "scan_chunk_apply_c2_traffic.json"
-        if prof.exists():
-            traffic = json.loads(prof.read_text()).get("traffic_bytes_per_launch")
+        # dram read+write bytes per element from the ncu capture summarised in
+        # profiles/scan_chunk_apply_small_case.md (8 lanes), scaled to this launch by element count
+        traffic = NCU_TRAFFIC_BYTES_PER_ELEM * elems
         import oracle as O
         threads = max(1, O.lib().pssa_oracle_hardware_threads())
         sample_lanes = 2

@@ -51,8 +51,11 @@ int32_t pssa_b200_ctx_create(int32_t device, pssa_b200_ctx** out);
 void pssa_b200_ctx_destroy(pssa_b200_ctx* ctx);
 /* Message of the last failure on `ctx` (or of the last failed create when ctx is NULL). */
 const char* pssa_b200_last_error(const pssa_b200_ctx* ctx);
-/* Use an existing cudaStream_t (e.g. the caller framework's current stream); NULL = own stream. */
+/* Enqueue on an existing cudaStream_t (e.g. the caller framework's current stream). NULL is the
+ * legacy default stream. A fresh context runs on a non-blocking stream of its own. */
 int32_t pssa_b200_ctx_set_stream(pssa_b200_ctx* ctx, void* cuda_stream);
+/* Go back to a non-blocking stream owned by the context. */
+int32_t pssa_b200_ctx_use_own_stream(pssa_b200_ctx* ctx);
 int32_t pssa_b200_ctx_synchronize(pssa_b200_ctx* ctx);
 /* Replaces `backend_label` (src/backend.rs:1439-1446): "b200 (<device name>)". */
 const char* pssa_b200_backend_label(const pssa_b200_ctx* ctx);

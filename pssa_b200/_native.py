@@ -19,6 +19,7 @@ SIGNATURES = {
     "pssa_b200_ctx_destroy": (None, [_vp]),
     "pssa_b200_last_error": (C.c_char_p, [_vp]),
     "pssa_b200_ctx_set_stream": (C.c_int32, [_vp, _vp]),
+    "pssa_b200_ctx_use_own_stream": (C.c_int32, [_vp]),
     "pssa_b200_ctx_synchronize": (C.c_int32, [_vp]),
     "pssa_b200_backend_label": (C.c_char_p, [_vp]),
     "pssa_b200_launch_count": (C.c_uint64, [_vp]),

@@ -95,16 +95,19 @@ int32_t pssa_b200_ctx_set_stream(pssa_b200_ctx* ctx, void* cuda_stream) {
     if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (cuda_stream == nullptr) {
-        if (!ctx->owns_stream) {
-            PSSA_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
-            ctx->owns_stream = true;
-        }
-        return PSSA_B200_OK;
-    }
     if (ctx->owns_stream) cudaStreamDestroy(ctx->stream);
-    ctx->stream = (cudaStream_t)cuda_stream;
+    ctx->stream = (cudaStream_t)cuda_stream;  // NULL is the legacy default stream
     ctx->owns_stream = false;
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_ctx_use_own_stream(pssa_b200_ctx* ctx) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->owns_stream) return PSSA_B200_OK;
+    PSSA_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+    ctx->owns_stream = true;
     return PSSA_B200_OK;
 }
 

@@ -62,7 +62,11 @@ class B200Dispatch:
 
     # ---- context
     def set_stream(self, stream):
-        """`stream`: a cudaStream_t as int, or a torch.cuda.Stream."""
+        """`stream`: a cudaStream_t as int (0 = legacy default stream), a torch.cuda.Stream, or None to
+        return to the context's own non-blocking stream."""
+        if stream is None:
+            self._check(self._lib.pssa_b200_ctx_use_own_stream(self._h))
+            return
         raw = getattr(stream, "cuda_stream", stream)
         self._check(self._lib.pssa_b200_ctx_set_stream(self._h, C.c_void_p(raw)))
 

@@ -213,3 +213,23 @@ def test_stacked_prefill_equals_token_loop_bitwise():
         assert rc == 1 and done == n
         assert np.array_equal(last.view(np.uint32), row.view(np.uint32))
         assert np.array_equal(m.state().view(np.uint32), b.state().view(np.uint32))
+
+
+def test_reference_cpu_scans_differ_elementwise_at_cancellations():
+    """The reference's two CPU forms of the SSM stage (ordered and Blelloch) agree to its own absolute
+    2e-5 (tests/associative_scan.rs:10) but not to 1e-5 elementwise-relative: states that are
+    near-cancellations of O(1) terms carry an absolute roundoff of ~1e-7. This is why reassociated
+    GPU paths are held to a per-channel-scale bound (tests/parity.py)."""
+    from parity import chan_err, rel_err
+    rng = np.random.default_rng(7)
+    T, d, s = 1024, 8, 4
+    delta = rng.uniform(0.001, 0.1, (T, d)).astype(np.float32)
+    bp = rng.normal(size=(T, s)).astype(np.float32)
+    cp = rng.normal(size=(T, s)).astype(np.float32)
+    x = rng.normal(size=(T, d)).astype(np.float32)
+    rates = -rng.uniform(0.01, 1.0, d * s).astype(np.float32)
+    st0, y0, _, _ = O.ssm_forward(delta, bp, cp, x, rates, np.zeros(d * s, np.float32), mode=0)
+    st1, y1, _, _ = O.ssm_forward(delta, bp, cp, x, rates, np.zeros(d * s, np.float32), mode=1)
+    assert np.max(np.abs(st0 - st1)) < 2e-5
+    assert rel_err(st0[1:], st1[1:]) > 1e-5
+    assert chan_err(st1[1:], st0[1:], 0) < 1e-5
