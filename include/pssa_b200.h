@@ -94,6 +94,42 @@ int32_t pssa_b200_scan_states_dev(pssa_b200_ctx* ctx, const float* a, const floa
 int32_t pssa_b200_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0,
                               float* h, float* h_last, size_t lanes, size_t len, size_t stride);
 
+/* ------------------------------------------------------------------ fused SSM stage */
+
+/* Arithmetic mode of the SSM stage. Default (0): ex2.approx on delta*(A*log2 e) -- the recipe of the
+ * reference's own GPU kernel (src/cuda/stages.ptx:21-22) -- with fused multiply-adds. EXACT: expf and
+ * separately rounded multiply/add in the order of the CPU reference (src/pssa.rs:1131-1144). */
+#define PSSA_B200_SSM_EXACT 1u
+
+/*
+ * Discretise + scan + read out for `lanes` independent sequences packed in one row space:
+ *   a = exp(delta_i*rates_ij), b = delta_i*B_j, h_ij <- a*h_ij + b*x_i, y_i = sum_j h_ij*C_j.
+ * Replaces ssm_prepare + affine_scan + ssm_materialize (src/cuda/stages.rs:260-356), the lane-batched
+ * packed_scan / packed_materialize (src/cuda/packed.rs:384-428) and `ssm_forward_resident`
+ * (src/backend.rs:1190-1212): the state stays on the device in `carry`.
+ * DEVICE pointers: delta, x_norm, y [rows, d_m]; b_proj, c_proj [rows, d_s]; rates [d_m, d_s];
+ * carry [lanes, d_m*d_s] read and updated in place (NULL: zero carry in, carry out dropped);
+ * optional tape outputs states / bar_a / bar_b [rows, d_m*d_s] (state after each token; NULL = skip).
+ * HOST pointers: offsets / lengths [lanes] (u32, first row and row count of each lane; both NULL means
+ * one lane covering all rows). Lanes must not overlap and must lie inside [0, rows).
+ */
+int32_t pssa_b200_ssm_forward_dev(pssa_b200_ctx* ctx, const float* delta, const float* b_proj,
+                                  const float* c_proj, const float* x_norm, const float* rates,
+                                  float* carry, float* y, float* states, float* bar_a, float* bar_b,
+                                  const uint32_t* offsets, const uint32_t* lengths, size_t lanes,
+                                  size_t rows, size_t d_m, size_t d_s, uint32_t flags);
+
+/*
+ * Host-pointer form with the argument list of `GpuDispatch::ssm_forward` (src/backend.rs:1215-1244)
+ * minus the two backward-only inputs (delta_raw, rate_deriv): one lane of seq_len tokens, `initial`
+ * [d_m*d_s], states [(seq_len+1)*d_m*d_s] with row 0 = initial, bar_a / bar_b [seq_len*d_m*d_s],
+ * y_ssm [seq_len*d_m]. bar_a, bar_b and states may be NULL.
+ */
+int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const float* b_proj,
+                              const float* x_norm, const float* rates, const float* c_proj,
+                              const float* initial, size_t seq_len, size_t d_m, size_t d_s,
+                              float* bar_a, float* bar_b, float* states, float* y_ssm, uint32_t flags);
+
 #ifdef __cplusplus
 }
 #endif

@@ -210,4 +210,99 @@ int32_t pssa_b200_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b
     return PSSA_B200_OK;
 }
 
+// ------------------------------------------------------------------ fused SSM stage
+
+static bool ptr_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int32_t pssa_b200_ssm_forward_dev(pssa_b200_ctx* ctx, const float* delta, const float* b_proj, const float* c_proj,
+                                  const float* x_norm, const float* rates, float* carry, float* y, float* states,
+                                  float* bar_a, float* bar_b, const uint32_t* offsets, const uint32_t* lengths,
+                                  size_t lanes, size_t rows, size_t d_m, size_t d_s, uint32_t flags) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    SsmShape shape;
+    int32_t rc = ssm_shape(ctx, rows, d_m, d_s, &shape);
+    if (rc != PSSA_B200_OK) return rc;
+    if (lanes == 0 || lanes > 0x7fffffff)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM lane count %zu must be in 1..2^31-1; refusing launch", lanes);
+    if (!delta || !b_proj || !c_proj || !x_norm || !rates || !y)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 SSM forward: null buffer");
+    if ((offsets == nullptr) != (lengths == nullptr))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 SSM forward: offsets and lengths must both be given");
+    if (!offsets && lanes != 1)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM forward: %zu lanes need offsets and lengths; refusing launch", lanes);
+    if (flags & ~PSSA_B200_SSM_EXACT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 SSM forward: unknown flags");
+    if (offsets) {
+        for (size_t l = 0; l < lanes; ++l)
+            if ((size_t)offsets[l] + lengths[l] > rows)
+                return fail(ctx, PSSA_B200_ERR_SHAPE,
+                            "B200 SSM forward: lane %zu covers rows [%u, %u) outside %zu rows; refusing launch", l,
+                            offsets[l], offsets[l] + lengths[l], rows);
+    }
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    SsmParams p{};
+    p.delta = delta, p.x_norm = x_norm, p.b_proj = b_proj, p.c_proj = c_proj, p.rates = rates;
+    p.carry = carry, p.y = y, p.states = states, p.bar_a = bar_a, p.bar_b = bar_b;
+    p.rows = rows, p.d = (int)d_m, p.s = (int)d_s, p.lanes = (int)lanes;
+    p.aligned = d_m % 4 == 0 && d_s % 4 == 0 && ptr_aligned16(delta) && ptr_aligned16(x_norm) &&
+                ptr_aligned16(b_proj) && ptr_aligned16(c_proj);
+    if (offsets) {
+        arena_reset(ctx);
+        if ((rc = arena_reserve(ctx, arena_round(lanes * 4) * 2)) != PSSA_B200_OK) return rc;
+        uint32_t* d_off = (uint32_t*)arena_take(ctx, lanes * 4);
+        uint32_t* d_len = (uint32_t*)arena_take(ctx, lanes * 4);
+        PSSA_CUDA(ctx, cudaMemcpyAsync(d_off, offsets, lanes * 4, cudaMemcpyHostToDevice, ctx->stream));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(d_len, lengths, lanes * 4, cudaMemcpyHostToDevice, ctx->stream));
+        p.offsets = d_off, p.lengths = d_len;
+    }
+    return launch_ssm_fused(ctx, p, (flags & PSSA_B200_SSM_EXACT) != 0);
+}
+
+int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const float* b_proj, const float* x_norm,
+                              const float* rates, const float* c_proj, const float* initial, size_t seq_len,
+                              size_t d_m, size_t d_s, float* bar_a, float* bar_b, float* states, float* y_ssm,
+                              uint32_t flags) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    SsmShape sh;
+    int32_t rc = ssm_shape(ctx, seq_len, d_m, d_s, &sh);
+    if (rc != PSSA_B200_OK) return rc;
+    if (!delta || !b_proj || !c_proj || !x_norm || !rates || !initial || !y_ssm)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 SSM forward: null buffer");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    DeviceBuf d_delta, d_b, d_c, d_x, d_rates, d_carry, d_y, d_states, d_ba, d_bb;
+    size_t tape = seq_len * sh.stride * 4;
+    PSSA_CUDA(ctx, d_delta.alloc(sh.token_m * 4));
+    PSSA_CUDA(ctx, d_x.alloc(sh.token_m * 4));
+    PSSA_CUDA(ctx, d_y.alloc(sh.token_m * 4));
+    PSSA_CUDA(ctx, d_b.alloc(sh.token_s * 4));
+    PSSA_CUDA(ctx, d_c.alloc(sh.token_s * 4));
+    PSSA_CUDA(ctx, d_rates.alloc(sh.stride * 4));
+    PSSA_CUDA(ctx, d_carry.alloc(sh.stride * 4));
+    if (states) PSSA_CUDA(ctx, d_states.alloc(tape));
+    if (bar_a) PSSA_CUDA(ctx, d_ba.alloc(tape));
+    if (bar_b) PSSA_CUDA(ctx, d_bb.alloc(tape));
+    cudaStream_t st = ctx->stream;
+    PSSA_CUDA(ctx, cudaMemcpyAsync(d_delta.p, delta, sh.token_m * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(d_x.p, x_norm, sh.token_m * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(d_b.p, b_proj, sh.token_s * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(d_c.p, c_proj, sh.token_s * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(d_rates.p, rates, sh.stride * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(d_carry.p, initial, sh.stride * 4, cudaMemcpyHostToDevice, st));
+    rc = pssa_b200_ssm_forward_dev(ctx, d_delta.f(), d_b.f(), d_c.f(), d_x.f(), d_rates.f(), d_carry.f(), d_y.f(),
+                                   states ? d_states.f() : nullptr, bar_a ? d_ba.f() : nullptr,
+                                   bar_b ? d_bb.f() : nullptr, nullptr, nullptr, 1, seq_len, d_m, d_s, flags);
+    if (rc != PSSA_B200_OK) {
+        cudaStreamSynchronize(st);
+        return rc;
+    }
+    PSSA_CUDA(ctx, cudaMemcpyAsync(y_ssm, d_y.p, sh.token_m * 4, cudaMemcpyDeviceToHost, st));
+    if (states) {
+        memcpy(states, initial, sh.stride * 4);
+        PSSA_CUDA(ctx, cudaMemcpyAsync(states + sh.stride, d_states.p, tape, cudaMemcpyDeviceToHost, st));
+    }
+    if (bar_a) PSSA_CUDA(ctx, cudaMemcpyAsync(bar_a, d_ba.p, tape, cudaMemcpyDeviceToHost, st));
+    if (bar_b) PSSA_CUDA(ctx, cudaMemcpyAsync(bar_b, d_bb.p, tape, cudaMemcpyDeviceToHost, st));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+    return PSSA_B200_OK;
+}
+
 }  // extern "C"

@@ -35,4 +35,21 @@ inline int32_t scan_shape(pssa_b200_ctx* ctx, size_t lanes, size_t len, size_t s
     return f32_elems(ctx, "affine scan elements", {lanes, len, stride}, elems);
 }
 
+// stage_bounds.rs:67-105 (SsmShape::new)
+struct SsmShape {
+    size_t stride, token_m, token_s, token_state;
+};
+inline int32_t ssm_shape(pssa_b200_ctx* ctx, size_t rows, size_t dm, size_t ds, SsmShape* out) {
+    if (rows == 0 || dm == 0 || ds == 0)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM dimensions must be positive; refusing launch");
+    if (dm > 0x7fffffff || ds > 0x7fffffff)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM widths must fit i32; refusing launch");
+    int32_t rc;
+    if ((rc = f32_elems(ctx, "SSM stride", {dm, ds}, &out->stride))) return rc;
+    if ((rc = f32_elems(ctx, "SSM latent tape", {rows, dm}, &out->token_m))) return rc;
+    if ((rc = f32_elems(ctx, "SSM projection tape", {rows, ds}, &out->token_s))) return rc;
+    if ((rc = f32_elems(ctx, "SSM state maps", {rows + 1, out->stride}, &out->token_state))) return rc;
+    return PSSA_B200_OK;
+}
+
 }  // namespace pssa

@@ -13,4 +13,24 @@ int32_t launch_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b, c
 int32_t launch_scan_maps(pssa_b200_ctx* ctx, float* scan_a, float* scan_b, size_t lanes, size_t len, size_t stride,
                          int forced_chunks);
 
+// ssm_fused.cu
+struct SsmParams {
+    const float* delta;    // [rows, d]  softplus already applied
+    const float* x_norm;   // [rows, d]
+    const float* b_proj;   // [rows, s]
+    const float* c_proj;   // [rows, s]
+    const float* rates;    // [d, s]     A = -softplus(raw)
+    float* carry;          // [lanes, d*s] in/out, may be null (zero carry in, carry out dropped)
+    float* y;              // [rows, d]
+    float* states;         // optional [rows, d*s]: state after each token
+    float* bar_a;          // optional [rows, d*s]
+    float* bar_b;          // optional [rows, d*s]
+    const uint32_t* offsets;  // per lane first row, null = one lane starting at row 0
+    const uint32_t* lengths;  // per lane row count, null = rows
+    size_t rows;
+    int d, s, lanes;
+    int aligned;           // 16-byte vector staging allowed
+};
+int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact);
+
 }  // namespace pssa

@@ -1,0 +1,271 @@
+// Fused selective-SSM stage: discretise, scan and read out in one pass, state in registers.
+//
+//   a = exp(delta_i * A_ij);  b = delta_i * B_j;  h_ij <- a*h_ij + b*x_i;  y_i = sum_j h_ij * C_j
+//
+// Replaces the reference's three kernels ssm_prepare / affine_scan / ssm_materialize
+// (src/cuda/stages.ptx:8-65, launched from src/cuda/stages.rs:260-356), which write three
+// [T, d*s] arrays to HBM and read them back twice, and the CPU stage src/gpu_batch.rs:543-680.
+// Here the only HBM traffic is the inputs (delta, x, B, C: (2d + 2s) floats per token), y, and the
+// carry once per lane; the per-token maps never leave registers. The kernel is therefore bound by
+// the exp throughput (d*s per token), not by HBM.
+//
+// Work split: one CTA = one lane (independent sequence) x CH consecutive channels i; a channel's
+// s states are spread over G threads of one warp holding ST states each (G*ST >= s). Inside a warp
+// the 32/G threads that own the same state group sit in adjacent lanes, so the B_j / C_j vectors a
+// thread needs are one shared-memory address per quarter warp (a broadcast, no bank conflicts; the
+// groups are padded apart by 4 floats), and y is completed by a shuffle tree over the G groups.
+// Time is walked serially by every thread; token tiles (delta, x, B, C rows) are staged through a
+// cp.async ring in shared memory so the global-load latency is hidden behind the previous tile's exps.
+//
+// Two arithmetic modes:
+//   FAST  ex2.approx on delta*(A*log2 e) (the reference's own GPU recipe, stages.ptx:21-22),
+//         FMA contraction, y summed per thread then by a shuffle tree over the G threads.
+//   EXACT expf, separately rounded multiply/add in the reference's order (src/pssa.rs:1131-1144);
+//         with G == 1 the sum over j is the reference's sequential sum.
+#include <cuda_runtime.h>
+
+#include "bounds.hpp"
+#include "context.hpp"
+#include "kernels.hpp"
+
+namespace pssa {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kTileTokens = 8;
+constexpr int kStages = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int ST, int G, bool EXACT, bool TAPE>
+__global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
+    constexpr int CH = kThreads / G;  // channels per CTA
+    constexpr int LPG = 32 / G;       // lanes of a warp that share one state group
+    constexpr int SG = ST + 4;        // shared-memory pitch of a state group (bank spreading)
+    constexpr int SP = SG * G;        // floats per token row of B / C in shared memory
+    extern __shared__ __align__(16) float smem[];
+    float* sm_delta = smem;                                   // [kStages][kTileTokens][CH]
+    float* sm_x = sm_delta + kStages * kTileTokens * CH;      // [kStages][kTileTokens][CH]
+    float* sm_b = sm_x + kStages * kTileTokens * CH;          // [kStages][kTileTokens][SP]
+    float* sm_c = sm_b + kStages * kTileTokens * SP;          // [kStages][kTileTokens][SP]
+
+    const int tid = threadIdx.x;
+    const int lane_id = tid & 31;
+    const int g = lane_id / LPG;
+    const int c = (tid >> 5) * LPG + lane_id % LPG;
+    const int ncb = (p.d + CH - 1) / CH;
+    const int lane = blockIdx.x / ncb;
+    const int i0 = (blockIdx.x % ncb) * CH;
+    const int i = i0 + c;
+    const bool valid = i < p.d;
+    const size_t row0 = p.offsets ? p.offsets[lane] : 0;
+    const int len = p.lengths ? (int)p.lengths[lane] : (int)p.rows;
+    const int d = p.d, s = p.s;
+    const size_t ds = (size_t)d * s;
+    const int j0 = g * ST;
+
+    float A[ST], h[ST];
+#pragma unroll
+    for (int jj = 0; jj < ST; ++jj) {
+        bool ok = valid && (j0 + jj) < s;
+        float rate = ok ? __ldg(p.rates + (size_t)i * s + j0 + jj) : 0.0f;
+        A[jj] = EXACT ? rate : rate * 1.4426950408889634f;
+        h[jj] = (ok && p.carry) ? p.carry[lane * ds + (size_t)i * s + j0 + jj] : 0.0f;
+    }
+
+    const int ntiles = (len + kTileTokens - 1) / kTileTokens;
+
+    auto load_tile = [&](int k) {
+        if (k < ntiles) {
+            const int st = k % kStages;
+            const int t0 = k * kTileTokens;
+            const int nt = min(kTileTokens, len - t0);
+            float* dd = sm_delta + st * kTileTokens * CH;
+            float* dx = sm_x + st * kTileTokens * CH;
+            float* db = sm_b + st * kTileTokens * SP;
+            float* dc = sm_c + st * kTileTokens * SP;
+            if (p.aligned) {
+                constexpr int CQ = CH / 4 > 0 ? CH / 4 : 1;
+                for (int idx = tid; idx < nt * CQ; idx += kThreads) {
+                    int tt = idx / CQ, q = idx % CQ;
+                    int col = i0 + q * 4;
+                    size_t gro = (row0 + t0 + tt) * (size_t)d + col;
+                    if (CH >= 4 && col < d) {
+                        cp_async16(dd + tt * CH + q * 4, p.delta + gro);
+                        cp_async16(dx + tt * CH + q * 4, p.x_norm + gro);
+                    } else if (CH >= 4) {
+                        *reinterpret_cast<float4*>(dd + tt * CH + q * 4) = make_float4(0, 0, 0, 0);
+                        *reinterpret_cast<float4*>(dx + tt * CH + q * 4) = make_float4(0, 0, 0, 0);
+                    }
+                }
+                constexpr int SQ = ST * G / 4;
+                for (int idx = tid; idx < nt * SQ; idx += kThreads) {
+                    int tt = idx / SQ, q = idx % SQ;
+                    int j = q * 4;
+                    int dst = tt * SP + (j / ST) * SG + j % ST;
+                    size_t gro = (row0 + t0 + tt) * (size_t)s + j;
+                    if (j < s) {
+                        cp_async16(db + dst, p.b_proj + gro);
+                        cp_async16(dc + dst, p.c_proj + gro);
+                    } else {
+                        *reinterpret_cast<float4*>(db + dst) = make_float4(0, 0, 0, 0);
+                        *reinterpret_cast<float4*>(dc + dst) = make_float4(0, 0, 0, 0);
+                    }
+                }
+            } else {
+                for (int idx = tid; idx < nt * CH; idx += kThreads) {
+                    int tt = idx / CH, q = idx % CH;
+                    int col = i0 + q;
+                    size_t gro = (row0 + t0 + tt) * (size_t)d + col;
+                    dd[tt * CH + q] = col < d ? __ldg(p.delta + gro) : 0.0f;
+                    dx[tt * CH + q] = col < d ? __ldg(p.x_norm + gro) : 0.0f;
+                }
+                for (int idx = tid; idx < nt * ST * G; idx += kThreads) {
+                    int tt = idx / (ST * G), j = idx % (ST * G);
+                    int dst = tt * SP + (j / ST) * SG + j % ST;
+                    size_t gro = (row0 + t0 + tt) * (size_t)s + j;
+                    db[dst] = j < s ? __ldg(p.b_proj + gro) : 0.0f;
+                    dc[dst] = j < s ? __ldg(p.c_proj + gro) : 0.0f;
+                }
+            }
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int k = 0; k < kStages - 1; ++k) load_tile(k);
+
+    for (int k = 0; k < ntiles; ++k) {
+        load_tile(k + kStages - 1);
+        cp_async_wait<kStages - 1>();
+        __syncthreads();
+        const int st = k % kStages;
+        const int t0 = k * kTileTokens;
+        const int nt = min(kTileTokens, len - t0);
+        const float* dd = sm_delta + st * kTileTokens * CH;
+        const float* dx = sm_x + st * kTileTokens * CH;
+        const float* db = sm_b + st * kTileTokens * SP + g * SG;
+        const float* dc = sm_c + st * kTileTokens * SP + g * SG;
+        for (int tt = 0; tt < nt; ++tt) {
+            const float dl = dd[tt * CH + c];
+            const float xv = dx[tt * CH + c];
+            const size_t row = row0 + t0 + tt;
+            static_assert(ST % 4 == 0, "states per thread are loaded as float4");
+            float bj[ST], cj[ST];
+#pragma unroll
+            for (int q = 0; q < ST / 4; ++q) {
+                float4 vb = *reinterpret_cast<const float4*>(db + tt * SP + q * 4);
+                float4 vc = *reinterpret_cast<const float4*>(dc + tt * SP + q * 4);
+                bj[q * 4] = vb.x, bj[q * 4 + 1] = vb.y, bj[q * 4 + 2] = vb.z, bj[q * 4 + 3] = vb.w;
+                cj[q * 4] = vc.x, cj[q * 4 + 1] = vc.y, cj[q * 4 + 2] = vc.z, cj[q * 4 + 3] = vc.w;
+            }
+            float yp = 0.0f;
+            float av[TAPE ? ST : 1], bv[TAPE ? ST : 1];
+            if (EXACT) {
+#pragma unroll
+                for (int jj = 0; jj < ST; ++jj) {
+                    float a = expf(__fmul_rn(dl, A[jj]));
+                    float bb = __fmul_rn(dl, bj[jj]);
+                    h[jj] = __fadd_rn(__fmul_rn(a, h[jj]), __fmul_rn(bb, xv));
+                    yp = __fadd_rn(yp, __fmul_rn(h[jj], cj[jj]));
+                    if (TAPE) av[jj] = a, bv[jj] = bb;
+                }
+            } else {
+                const float w = dl * xv;
+#pragma unroll
+                for (int jj = 0; jj < ST; ++jj) {
+                    float a = ex2_approx(dl * A[jj]);
+                    h[jj] = fmaf(a, h[jj], w * bj[jj]);
+                    yp = fmaf(h[jj], cj[jj], yp);
+                    if (TAPE) av[jj] = a, bv[jj] = dl * bj[jj];
+                }
+            }
+#pragma unroll
+            for (int m = LPG; m < 32; m <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, m);
+            if (g == 0 && valid) p.y[row * d + i] = yp;
+            if (TAPE) {
+#pragma unroll
+                for (int jj = 0; jj < ST; ++jj) {
+                    if (valid && j0 + jj < s) {
+                        size_t o = row * ds + (size_t)i * s + j0 + jj;
+                        if (p.states) p.states[o] = h[jj];
+                        if (p.bar_a) p.bar_a[o] = av[jj];
+                        if (p.bar_b) p.bar_b[o] = bv[jj];
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    if (p.carry) {
+#pragma unroll
+        for (int jj = 0; jj < ST; ++jj)
+            if (valid && j0 + jj < s) p.carry[lane * ds + (size_t)i * s + j0 + jj] = h[jj];
+    }
+}
+
+template <int ST, int G, bool EXACT, bool TAPE>
+int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
+    constexpr int CH = kThreads / G;
+    constexpr int SP = (ST + 4) * G;
+    size_t smem = (size_t)kStages * kTileTokens * (2 * CH + 2 * SP) * sizeof(float);
+    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE>;
+    static bool attr_set = false;  // per instantiation; contexts share the device function
+    if (smem > 48 * 1024 && !attr_set) {
+        PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    int ncb = (p.d + CH - 1) / CH;
+    size_t blocks = (size_t)ncb * p.lanes;
+    if (blocks > 0x7fffffffull)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM grid (%zu, 1) exceeds grid limits; refusing launch", blocks);
+    kern<<<(unsigned)blocks, kThreads, smem, ctx->stream>>>(p);
+    return after_launch(ctx, "ssm_fused_kernel");
+}
+
+// The tape outputs (states, bar_a, bar_b: the reference's training tape) cost d*s floats per token
+// each; inference never asks for them, so they live in a separate instantiation.
+template <int ST, int G, bool EXACT>
+int32_t launch_one(pssa_b200_ctx* ctx, const SsmParams& p) {
+    if (p.states || p.bar_a || p.bar_b) return launch_cfg<ST, G, EXACT, true>(ctx, p);
+    return launch_cfg<ST, G, EXACT, false>(ctx, p);
+}
+
+}  // namespace
+
+int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact) {
+    const int s = p.s;
+    if (exact) {
+        if (s <= 4) return launch_one<4, 1, true>(ctx, p);
+        if (s <= 16) return launch_one<16, 1, true>(ctx, p);
+        if (s <= 64) return launch_one<64, 1, true>(ctx, p);
+        if (s <= 128) return launch_one<16, 8, true>(ctx, p);
+        if (s <= 512) return launch_one<16, 32, true>(ctx, p);
+    } else {
+        if (s <= 4) return launch_one<4, 1, false>(ctx, p);
+        if (s <= 8) return launch_one<4, 2, false>(ctx, p);
+        if (s <= 16) return launch_one<4, 4, false>(ctx, p);
+        if (s <= 32) return launch_one<16, 2, false>(ctx, p);
+        if (s <= 64) return launch_one<16, 4, false>(ctx, p);
+        if (s <= 128) return launch_one<16, 8, false>(ctx, p);
+        if (s <= 256) return launch_one<16, 16, false>(ctx, p);
+        if (s <= 512) return launch_one<16, 32, false>(ctx, p);
+    }
+    return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 SSM: state width %d exceeds 512; refusing launch", s);
+}
+
+}  // namespace pssa

@@ -115,6 +115,42 @@ class B200Dispatch:
                                                         lanes, length, stride))
 
 
+    # ---- fused SSM stage
+    def ssm_forward(self, delta, b_proj, x_norm, rates, c_proj, initial, seq_len, d_m, d_s, bar_a=None, bar_b=None,
+                    states=None, y_ssm=None, exact=False):
+        """`GpuDispatch::ssm_forward` (src/backend.rs:1215-1244) on host arrays; outputs are written in place.
+        Lengths are checked like the reference's "CUDA SSM forward shape mismatch" (src/cuda/stages.rs:281-290)."""
+        stride = d_m * d_s
+        want = [("delta", delta, seq_len * d_m), ("b_proj", b_proj, seq_len * d_s), ("x_norm", x_norm, seq_len * d_m),
+                ("rates", rates, stride), ("c_proj", c_proj, seq_len * d_s), ("initial", initial, stride),
+                ("y_ssm", y_ssm, seq_len * d_m)]
+        for name, arr, n in want:
+            _host(arr, name)
+            if arr.size != n:
+                raise N.B200Error(N.ERR_SHAPE, f"B200 SSM forward shape mismatch: {name} has {arr.size} elements, "
+                                               f"expected {n}; refusing launch")
+        for name, arr, n in (("bar_a", bar_a, seq_len * stride), ("bar_b", bar_b, seq_len * stride),
+                             ("states", states, (seq_len + 1) * stride)):
+            if arr is not None and (_host(arr, name).size != n):
+                raise N.B200Error(N.ERR_SHAPE, f"B200 SSM forward shape mismatch: {name}; refusing launch")
+        self._check(self._lib.pssa_b200_ssm_forward(self._h, _ptr(delta), _ptr(b_proj), _ptr(x_norm), _ptr(rates),
+                                                    _ptr(c_proj), _ptr(initial), seq_len, d_m, d_s, _ptr(bar_a),
+                                                    _ptr(bar_b), _ptr(states), _ptr(y_ssm), N.SSM_EXACT if exact else 0))
+
+    def ssm_forward_dev(self, delta, b_proj, c_proj, x_norm, rates, carry, y, offsets, lengths, rows, d_m, d_s,
+                        states=None, bar_a=None, bar_b=None, exact=False):
+        """Lane-batched, device-resident form: `offsets` / `lengths` are host uint32 arrays (or None for one lane)."""
+        lanes = 1
+        if offsets is not None:
+            offsets = np.ascontiguousarray(offsets, np.uint32)
+            lengths = np.ascontiguousarray(lengths, np.uint32)
+            lanes = len(offsets)
+        self._check(self._lib.pssa_b200_ssm_forward_dev(
+            self._h, _ptr(delta), _ptr(b_proj), _ptr(c_proj), _ptr(x_norm), _ptr(rates), _ptr(carry), _ptr(y),
+            _ptr(states), _ptr(bar_a), _ptr(bar_b), _ptr(offsets), _ptr(lengths), lanes, rows, d_m, d_s,
+            N.SSM_EXACT if exact else 0))
+
+
 class Device:
     """`Device` of src/backend.rs:1012-1018 reduced to the arm this package adds."""
 
