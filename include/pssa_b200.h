@@ -130,6 +130,36 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
                               const float* initial, size_t seq_len, size_t d_m, size_t d_s,
                               float* bar_a, float* bar_b, float* states, float* y_ssm, uint32_t flags);
 
+/* ------------------------------------------------------------------ episodic memory read */
+
+/* Keep the reference's sequential f32 summation order for the softmax sum and the value read
+ * (src/memory.rs:409-425) instead of tree sums and fused multiply-adds. */
+#define PSSA_B200_MEM_EXACT 1u
+
+/*
+ * Poincare-ball memory read for `rows` queries against one immutable bank. Replaces
+ * `diffeomorphic_project` + `retrieve_soft_into` (src/memory.rs:198-211, 344-426), the row loop
+ * `retrieve_memory_rows` (src/gpu_batch.rs:700-741) and the reference GPU's memory_forward kernel +
+ * cuBLAS value read (src/cuda/stages.rs:563-614).
+ *   q [rows, d_key]: Euclidean queries when q_is_euclidean != 0 (projected with q/(1+|q|), f64), else
+ *   points already inside the ball. keys [capacity, d_key], norm_sq [capacity], values [capacity, d_val];
+ *   only the first `count` slots are read. score = -distance, weights = softmax(score / tau) over all
+ *   occupied slots, or over the exact `top_k` nearest (ties to the lower slot) when 0 < top_k < count.
+ * Outputs: q_pnc [rows, d_key] (NULL to skip), q_norm [rows] (NULL to skip), weights [rows, capacity]
+ * (zero outside the occupied / selected slots; NULL: scratch from the context arena), m_val [rows, d_val],
+ * min_dist [rows] (NULL to skip). count == 0 gives zero weights and values (src/memory.rs:363-367).
+ */
+int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean,
+                                  const float* keys, const float* norm_sq, const float* values,
+                                  size_t rows, size_t d_key, size_t d_val, size_t capacity, size_t count,
+                                  float tau, size_t top_k, float* q_pnc, float* q_norm, float* weights,
+                                  float* m_val, float* min_dist, uint32_t flags);
+int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean,
+                              const float* keys, const float* norm_sq, const float* values, size_t rows,
+                              size_t d_key, size_t d_val, size_t capacity, size_t count, float tau,
+                              size_t top_k, float* q_pnc, float* q_norm, float* weights, float* m_val,
+                              float* min_dist, uint32_t flags);
+
 #ifdef __cplusplus
 }
 #endif

@@ -305,4 +305,72 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
     return PSSA_B200_OK;
 }
 
+// ------------------------------------------------------------------ episodic memory read
+
+int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys,
+                                  const float* norm_sq, const float* values, size_t rows, size_t d_key, size_t d_val,
+                                  size_t capacity, size_t count, float tau, size_t top_k, float* q_pnc, float* q_norm,
+                                  float* weights, float* m_val, float* min_dist, uint32_t flags) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    int32_t rc = memory_shape(ctx, rows, d_key, d_val, capacity, count, tau);
+    if (rc != PSSA_B200_OK) return rc;
+    if (!q || !keys || !norm_sq || !values || !m_val)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
+    if (flags & ~PSSA_B200_MEM_EXACT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!weights) {
+        arena_reset(ctx);
+        if ((rc = arena_reserve(ctx, arena_round(rows * capacity * 4))) != PSSA_B200_OK) return rc;
+        weights = (float*)arena_take(ctx, rows * capacity * 4);
+    }
+    RetrieveParams p{};
+    p.q = q, p.q_is_euclidean = q_is_euclidean, p.q_pnc = q_pnc, p.q_norm = q_norm;
+    p.keys = keys, p.norm_sq = norm_sq, p.values = values;
+    p.weights = weights, p.m_val = m_val, p.min_dist = min_dist;
+    p.rows = rows, p.dk = (int)d_key, p.dv = (int)d_val, p.cap = (int)capacity, p.count = (int)count;
+    p.top_k = (int)(top_k > capacity ? capacity : top_k), p.tau = tau;
+    return launch_memory_read(ctx, p, (flags & PSSA_B200_MEM_EXACT) != 0);
+}
+
+int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys,
+                              const float* norm_sq, const float* values, size_t rows, size_t d_key, size_t d_val,
+                              size_t capacity, size_t count, float tau, size_t top_k, float* q_pnc, float* q_norm,
+                              float* weights, float* m_val, float* min_dist, uint32_t flags) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    int32_t rc = memory_shape(ctx, rows, d_key, d_val, capacity, count, tau);
+    if (rc != PSSA_B200_OK) return rc;
+    if (!q || !keys || !norm_sq || !values || !m_val)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    DeviceBuf dq, dkeys, dns, dvals, dpnc, dqn, dw, dm, dmin;
+    cudaStream_t st = ctx->stream;
+    PSSA_CUDA(ctx, dq.alloc(rows * d_key * 4));
+    PSSA_CUDA(ctx, dkeys.alloc(capacity * d_key * 4));
+    PSSA_CUDA(ctx, dns.alloc(capacity * 4));
+    PSSA_CUDA(ctx, dvals.alloc(capacity * d_val * 4));
+    PSSA_CUDA(ctx, dpnc.alloc(rows * d_key * 4));
+    PSSA_CUDA(ctx, dqn.alloc(rows * 4));
+    PSSA_CUDA(ctx, dw.alloc(rows * capacity * 4));
+    PSSA_CUDA(ctx, dm.alloc(rows * d_val * 4));
+    PSSA_CUDA(ctx, dmin.alloc(rows * 4));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(dq.p, q, rows * d_key * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(dkeys.p, keys, capacity * d_key * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(dns.p, norm_sq, capacity * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(dvals.p, values, capacity * d_val * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemsetAsync(dw.p, 0, rows * capacity * 4, st));
+    rc = pssa_b200_memory_read_dev(ctx, dq.f(), q_is_euclidean, dkeys.f(), dns.f(), dvals.f(), rows, d_key, d_val,
+                                   capacity, count, tau, top_k, dpnc.f(), dqn.f(), dw.f(), dm.f(), dmin.f(), flags);
+    if (rc != PSSA_B200_OK) {
+        cudaStreamSynchronize(st);
+        return rc;
+    }
+    if (q_pnc) PSSA_CUDA(ctx, cudaMemcpyAsync(q_pnc, dpnc.p, rows * d_key * 4, cudaMemcpyDeviceToHost, st));
+    if (q_norm) PSSA_CUDA(ctx, cudaMemcpyAsync(q_norm, dqn.p, rows * 4, cudaMemcpyDeviceToHost, st));
+    if (weights) PSSA_CUDA(ctx, cudaMemcpyAsync(weights, dw.p, rows * capacity * 4, cudaMemcpyDeviceToHost, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(m_val, dm.p, rows * d_val * 4, cudaMemcpyDeviceToHost, st));
+    if (min_dist) PSSA_CUDA(ctx, cudaMemcpyAsync(min_dist, dmin.p, rows * 4, cudaMemcpyDeviceToHost, st));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+    return PSSA_B200_OK;
+}
+
 }  // extern "C"

@@ -52,4 +52,21 @@ inline int32_t ssm_shape(pssa_b200_ctx* ctx, size_t rows, size_t dm, size_t ds, 
     return PSSA_B200_OK;
 }
 
+// stage_bounds.rs:107-152 (MemoryShape::new), for the read alone
+inline int32_t memory_shape(pssa_b200_ctx* ctx, size_t rows, size_t dk, size_t dv, size_t cap, size_t count, float tau) {
+    if (rows == 0 || cap == 0 || dk == 0 || dv == 0 || dk > 0x7fffffff || dv > 0x7fffffff || cap > 0x7fffffff)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 memory dimensions must be positive and widths fit i32; refusing launch");
+    if (count > cap || !(tau > 0.0f) || !(tau <= 3.4028234e38f))
+        return fail(ctx, PSSA_B200_ERR_SHAPE,
+                    "B200 memory invalid count/capacity (%zu/%zu) or temperature (%g); refusing launch", count, cap, (double)tau);
+    size_t n;
+    int32_t rc;
+    if ((rc = f32_elems(ctx, "memory query", {rows, dk}, &n))) return rc;
+    if ((rc = f32_elems(ctx, "memory value", {rows, dv}, &n))) return rc;
+    if ((rc = f32_elems(ctx, "memory weights", {rows, cap}, &n))) return rc;
+    if ((rc = f32_elems(ctx, "memory keys", {cap, dk}, &n))) return rc;
+    if ((rc = f32_elems(ctx, "memory bank values", {cap, dv}, &n))) return rc;
+    return PSSA_B200_OK;
+}
+
 }  // namespace pssa

@@ -33,4 +33,22 @@ struct SsmParams {
 };
 int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact);
 
+// retrieve_poincare.cu
+struct RetrieveParams {
+    const float* q;        // [rows, dk] Euclidean queries (projected here) or points already in the ball
+    int q_is_euclidean;
+    float* q_pnc;          // [rows, dk] projected queries, may be null
+    float* q_norm;         // [rows] Euclidean norm of q, may be null
+    const float* keys;     // [cap, dk]
+    const float* norm_sq;  // [cap]
+    const float* values;   // [cap, dv]
+    float* weights;        // [rows, cap] distances in flight, weights on return
+    float* m_val;          // [rows, dv]
+    float* min_dist;       // [rows], may be null
+    size_t rows;
+    int dk, dv, cap, count, top_k;
+    float tau;
+};
+int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
+
 }  // namespace pssa

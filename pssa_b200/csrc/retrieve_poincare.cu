@@ -1,0 +1,377 @@
+// Poincare-ball episodic memory read: project queries into the ball, hyperbolic distance to every
+// occupied slot, softmax (all slots or exact top-k) and the weighted value read.
+//
+// Replaces `retrieve_soft_into` / `diffeomorphic_project` / `poincare_distance`
+// (src/memory.rs:198-211, 245-262, 344-426), the per-token loop `retrieve_memory_rows`
+// (src/gpu_batch.rs:700-741) and the reference's GPU kernel `memory_forward` (one thread per token,
+// src/cuda/stages.ptx:358-446) with its cuBLAS value read (src/cuda/stages.rs:583-614).
+//
+// Three launches:
+//   A  poincare_distance_kernel: 64 queries x 64 slots per CTA pass, 4x4 (query, slot) pairs per
+//      thread, squared differences accumulated in f64 exactly like the reference (projection and
+//      distance are f64 there, rounded to f32); distances go to the [rows, cap] weights buffer.
+//   B  softmax_topk_kernel: one warp per query: min, exp((min-d)/tau), normalise; or exact top-k by
+//      (distance bits, slot) with the value read fused (k rows of the bank).
+//   C  value_mix_kernel: m = W[rows, count] x V[count, dv] for the all-slots read, fp32, slots
+//      accumulated in ascending order like the reference.
+// B and C keep the reference's sequential f32 summation order when `exact` is set.
+#include <cuda_runtime.h>
+
+#include <cfloat>
+
+#include "bounds.hpp"
+#include "context.hpp"
+#include "kernels.hpp"
+
+namespace pssa {
+namespace {
+
+constexpr int QT = 64;   // queries per CTA in kernel A
+constexpr int STL = 64;  // slots per pass
+constexpr int KC = 32;   // key dimensions per shared-memory chunk
+
+// ------------------------------------------------------------------ A: projection + distances
+__global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kpad = (p.dk + KC - 1) / KC * KC;
+    double* Ps = reinterpret_cast<double*>(smem_raw);  // [kpad][QT]
+    double* Ks = Ps + (size_t)kpad * QT;               // [KC][STL]
+    float* qsq = reinterpret_cast<float*>(Ks + KC * STL);  // [QT]
+
+    const int tid = threadIdx.x;
+    const size_t q0 = (size_t)blockIdx.x * QT;
+    const int dk = p.dk;
+
+    // zero the padded rows of P
+    for (int idx = tid; idx < (kpad - dk) * QT; idx += 256) Ps[(size_t)dk * QT + idx] = 0.0;
+
+    if (tid < QT) {
+        const size_t q = q0 + tid;
+        if (q < p.rows) {
+            const float* src = p.q + q * dk;
+            float* dst = p.q_pnc ? p.q_pnc + q * dk : nullptr;
+            float qs;
+            if (p.q_is_euclidean) {
+                // memory.rs:198-211: r = sqrt(sum q^2) in f64, sequential; p = q * min(r/(1+r), R)/r
+                double r2 = 0.0;
+                for (int i = 0; i < dk; ++i) {
+                    double v = (double)src[i];
+                    r2 = __dadd_rn(r2, __dmul_rn(v, v));
+                }
+                double r = sqrt(r2);
+                const double max_radius = 1.0 - 8.0 * (double)FLT_EPSILON;
+                double scale = (r == 0.0) ? 1.0 : fmin(r / (1.0 + r), max_radius) / r;
+                double n2 = 0.0;
+                for (int i = 0; i < dk; ++i) {
+                    float pv = (float)__dmul_rn((double)src[i], scale);
+                    if (dst) dst[i] = pv;
+                    double pd = (double)pv;
+                    Ps[(size_t)i * QT + tid] = pd;
+                    n2 = __dadd_rn(n2, __dmul_rn(pd, pd));
+                }
+                if (p.q_norm) p.q_norm[q] = (float)fmin(r, (double)FLT_MAX);
+                qs = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;  // memory.rs:181-188
+            } else {
+                double n2 = 0.0;
+                for (int i = 0; i < dk; ++i) {
+                    float pv = src[i];
+                    if (dst && dst != src) dst[i] = pv;
+                    double pd = (double)pv;
+                    Ps[(size_t)i * QT + tid] = pd;
+                    n2 = __dadd_rn(n2, __dmul_rn(pd, pd));
+                }
+                qs = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;
+            }
+            qsq[tid] = qs;
+        } else {
+            for (int i = 0; i < dk; ++i) Ps[(size_t)i * QT + tid] = 0.0;
+            qsq[tid] = 0.0f;
+        }
+    }
+    __syncthreads();
+
+    const int ts = tid & 15, tq = tid >> 4;  // 16 slot threads x 16 query threads
+    const int count = p.count;
+    for (int s0 = 0; s0 < count; s0 += STL) {
+        double acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0.0;
+        for (int i0 = 0; i0 < kpad; i0 += KC) {
+            __syncthreads();  // previous chunk fully consumed
+            for (int idx = tid; idx < STL * KC; idx += 256) {
+                int sl = idx / KC, ii = idx % KC;
+                int slot = s0 + sl, i = i0 + ii;
+                float v = (slot < count && i < dk) ? __ldg(p.keys + (size_t)slot * dk + i) : 0.0f;
+                Ks[ii * STL + sl] = (double)v;
+            }
+            __syncthreads();
+#pragma unroll 4
+            for (int ii = 0; ii < KC; ++ii) {
+                const double2* pp = reinterpret_cast<const double2*>(Ps + (size_t)(i0 + ii) * QT + tq * 4);
+                const double2* kp = reinterpret_cast<const double2*>(Ks + ii * STL + ts * 4);
+                double2 p01 = pp[0], p23 = pp[1], k01 = kp[0], k23 = kp[1];
+                double pv[4] = {p01.x, p01.y, p23.x, p23.y};
+                double kv[4] = {k01.x, k01.y, k23.x, k23.y};
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        double df = pv[a] - kv[b];
+                        acc[a][b] = fma(df, df, acc[a][b]);
+                    }
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const size_t q = q0 + tq * 4 + a;
+            if (q >= p.rows) continue;
+            const double one_minus_q = 1.0 - (double)qsq[tq * 4 + a];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                int slot = s0 + ts * 4 + b;
+                if (slot < count) {
+                    // memory.rs:245-262: 2*asinh(sqrt(sq/denom)); 2*asinh(z) = log1p(2u + 2*sqrt(u*u + u)), u = z^2
+                    double denom = one_minus_q * (1.0 - (double)__ldg(p.norm_sq + slot));
+                    double u = acc[a][b] / denom;
+                    double dist = log1p(2.0 * u + 2.0 * sqrt(fma(u, u, u)));
+                    p.weights[q * p.cap + slot] = (float)dist;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ B: softmax / top-k (+ fused value read)
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    return v;
+}
+__device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        unsigned long long o = __shfl_xor_sync(0xffffffffu, v, m);
+        v = o < v ? o : v;
+    }
+    return v;
+}
+
+template <bool EXACT>
+__device__ __forceinline__ float weight_of(float min_dist, float d, float tau) {
+    // memory.rs:396-398 / 411-414: exp((min - d) / tau), subtraction before division
+    float x = __fdiv_rn(__fsub_rn(min_dist, d), tau);
+    return expf(x);
+}
+
+// One warp per query. Distances are read from `weights` and replaced by the weights.
+template <bool EXACT>
+__global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
+    extern __shared__ float sm[];  // [8 warps][cap] distances / weights
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t q = (size_t)blockIdx.x * 8 + warp;
+    if (q >= p.rows) return;
+    const int cap = p.cap, count = p.count, dv = p.dv;
+    float* row = p.weights + q * cap;
+    float* w = sm + (size_t)warp * cap;
+    if (count == 0) {  // memory.rs:363-367
+        for (int i = lane; i < cap; i += 32) row[i] = 0.0f;
+        for (int j = lane; j < dv; j += 32) p.m_val[q * dv + j] = 0.0f;
+        if (p.min_dist) p.min_dist[q] = 0.0f;
+        return;
+    }
+    float mn = FLT_MAX;
+    for (int i = lane; i < count; i += 32) {
+        float d = row[i];
+        w[i] = d;
+        mn = fminf(mn, d);
+    }
+    mn = warp_min(mn);
+    if (p.min_dist && lane == 0) p.min_dist[q] = mn;
+    __syncwarp();
+    const float tau = p.tau;
+    const int k = p.top_k;
+    if (k != 0 && k < count) {
+        // memory.rs:380-408: keep the k smallest (distance bits, slot); weights over those only, slot order
+        // selected slots are marked by setting the sign bit of their distance in shared memory
+        for (int r = 0; r < k; ++r) {
+            unsigned long long local = ~0ull;
+            for (int i = lane; i < count; i += 32) {
+                unsigned bits = __float_as_uint(w[i]);
+                if (bits & 0x80000000u) continue;  // already selected (distances are >= +0)
+                unsigned long long key = ((unsigned long long)bits << 32) | (unsigned)i;
+                local = key < local ? key : local;
+            }
+            unsigned long long key = warp_min_u64(local);
+            int idx = (int)(key & 0xffffffffu);
+            if (lane == 0) w[idx] = __uint_as_float(__float_as_uint(w[idx]) | 0x80000000u);
+            __syncwarp();
+        }
+        // sum in ascending slot order (selected.sort_unstable_by_key(idx); iter().sum()), memory.rs:391-398
+        float sum = 0.0f;
+        if (lane == 0) {
+            for (int i = 0; i < count; ++i) {
+                unsigned bits = __float_as_uint(w[i]);
+                if (bits & 0x80000000u) sum = __fadd_rn(sum, weight_of<EXACT>(mn, __uint_as_float(bits & 0x7fffffffu), tau));
+            }
+        }
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+        // weights: zero everywhere except the selected slots (out_weights.fill(0.0))
+        for (int i = lane; i < cap; i += 32) {
+            float out = 0.0f;
+            if (i < count) {
+                unsigned bits = __float_as_uint(w[i]);
+                if (bits & 0x80000000u)
+                    out = __fdiv_rn(weight_of<EXACT>(mn, __uint_as_float(bits & 0x7fffffffu), tau), sum);
+                w[i] = (bits & 0x80000000u) ? out : -1.0f;  // -1 marks "not selected" for the read below
+            }
+            row[i] = out;
+        }
+        __syncwarp();
+        // fused value read: each lane owns columns j = lane, lane+32, ...; slots in ascending order
+        for (int j0 = lane; j0 < dv; j0 += 32 * 4) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int i = 0; i < count; ++i) {
+                float wi = w[i];
+                if (wi < 0.0f) continue;
+                const float* v = p.values + (size_t)i * dv;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    int j = j0 + e * 32;
+                    if (j < dv) acc[e] = __fadd_rn(acc[e], __fmul_rn(wi, __ldg(v + j)));
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int j = j0 + e * 32;
+                if (j < dv) p.m_val[q * dv + j] = acc[e];
+            }
+        }
+        return;
+    }
+    // all-slots read: w = exp((min - d)/tau); sum in slot order; w /= sum   (memory.rs:409-420)
+    for (int i = lane; i < count; i += 32) w[i] = weight_of<EXACT>(mn, w[i], tau);
+    __syncwarp();
+    float sum = 0.0f;
+    if (EXACT) {
+        if (lane == 0)
+            for (int i = 0; i < count; ++i) sum = __fadd_rn(sum, w[i]);
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+    } else {
+        for (int i = lane; i < count; i += 32) sum += w[i];
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+    }
+    for (int i = lane; i < cap; i += 32) row[i] = i < count ? __fdiv_rn(w[i], sum) : 0.0f;
+}
+
+// ------------------------------------------------------------------ C: dense value read m = W x V
+// 64 queries x 64 columns per CTA, 4x4 per thread, slots walked in ascending order.
+template <bool EXACT>
+__global__ void __launch_bounds__(256) value_mix_kernel(RetrieveParams p) {
+    __shared__ __align__(16) float Ws[32][QT + 4];  // [slot][query]
+    __shared__ __align__(16) float Vs[32][64 + 4];  // [slot][column]
+    const int tid = threadIdx.x;
+    const int tc = tid & 15, tq = tid >> 4;
+    const size_t q0 = (size_t)blockIdx.x * QT;
+    const int c0 = blockIdx.y * 64;
+    const int cap = p.cap, count = p.count, dv = p.dv;
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) acc[a][b] = 0.0f;
+    for (int s0 = 0; s0 < count; s0 += 32) {
+        __syncthreads();
+        for (int idx = tid; idx < 32 * QT; idx += 256) {
+            int qq = idx / 32, sl = idx % 32;  // consecutive threads read consecutive slots of one query row
+            size_t q = q0 + qq;
+            int slot = s0 + sl;
+            Ws[sl][qq] = (q < p.rows && slot < count) ? p.weights[q * cap + slot] : 0.0f;
+        }
+        for (int idx = tid; idx < 32 * 64; idx += 256) {
+            int sl = idx / 64, cc = idx % 64;
+            int slot = s0 + sl, col = c0 + cc;
+            Vs[sl][cc] = (slot < count && col < dv) ? __ldg(p.values + (size_t)slot * dv + col) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int sl = 0; sl < 32; ++sl) {
+            float4 wv = *reinterpret_cast<const float4*>(&Ws[sl][tq * 4]);
+            float4 vv = *reinterpret_cast<const float4*>(&Vs[sl][tc * 4]);
+            float wa[4] = {wv.x, wv.y, wv.z, wv.w};
+            float va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (EXACT)
+                        acc[a][b] = __fadd_rn(acc[a][b], __fmul_rn(wa[a], va[b]));
+                    else
+                        acc[a][b] = fmaf(wa[a], va[b], acc[a][b]);
+                }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        size_t q = q0 + tq * 4 + a;
+        if (q >= p.rows) continue;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            int col = c0 + tc * 4 + b;
+            if (col < dv) p.m_val[q * dv + col] = acc[a][b];
+        }
+    }
+}
+
+}  // namespace
+
+int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact) {
+    const int kpad = (p.dk + KC - 1) / KC * KC;
+    size_t smem_a = ((size_t)kpad * QT + KC * STL) * sizeof(double) + QT * sizeof(float);
+    if (smem_a > 200 * 1024)
+        return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 memory read: key width %d needs %zu bytes of shared memory; refusing launch",
+                    p.dk, smem_a);
+    size_t smem_b = (size_t)8 * p.cap * sizeof(float);
+    if (smem_b > 200 * 1024)
+        return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 memory read: capacity %d exceeds the %d slots one CTA can hold; refusing launch",
+                    p.cap, 200 * 1024 / 32);
+    size_t qblocks = (p.rows + QT - 1) / QT;
+    if (qblocks > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 memory read grid exceeds grid limits; refusing launch");
+    int32_t rc;
+    // with an empty bank the launch still publishes the projection (gpu_batch.rs:682-698 projects first)
+    static bool attr_a = false;
+    if (smem_a > 48 * 1024 && !attr_a) {
+        PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_a = true;
+    }
+    poincare_distance_kernel<<<(unsigned)qblocks, 256, smem_a, ctx->stream>>>(p);
+    if ((rc = after_launch(ctx, "poincare_distance_kernel")) != PSSA_B200_OK) return rc;
+    size_t wblocks = (p.rows + 7) / 8;
+    static bool attr_b[2] = {false, false};
+    if (smem_b > 48 * 1024 && !attr_b[exact]) {
+        if (exact)
+            PSSA_CUDA(ctx, cudaFuncSetAttribute(softmax_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        else
+            PSSA_CUDA(ctx, cudaFuncSetAttribute(softmax_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr_b[exact] = true;
+    }
+    if (exact)
+        softmax_topk_kernel<true><<<(unsigned)wblocks, 256, smem_b, ctx->stream>>>(p);
+    else
+        softmax_topk_kernel<false><<<(unsigned)wblocks, 256, smem_b, ctx->stream>>>(p);
+    if ((rc = after_launch(ctx, "softmax_topk_kernel")) != PSSA_B200_OK) return rc;
+    bool topk = p.top_k != 0 && p.top_k < p.count;
+    if (p.count > 0 && !topk) {
+        dim3 grid((unsigned)qblocks, (unsigned)((p.dv + 63) / 64));
+        if (exact)
+            value_mix_kernel<true><<<grid, 256, 0, ctx->stream>>>(p);
+        else
+            value_mix_kernel<false><<<grid, 256, 0, ctx->stream>>>(p);
+        if ((rc = after_launch(ctx, "value_mix_kernel")) != PSSA_B200_OK) return rc;
+    }
+    return PSSA_B200_OK;
+}
+
+}  // namespace pssa

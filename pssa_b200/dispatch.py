@@ -151,6 +151,38 @@ class B200Dispatch:
             N.SSM_EXACT if exact else 0))
 
 
+    # ---- episodic memory read
+    def memory_read(self, q, keys, norm_sq, values, count, tau, top_k=0, q_is_euclidean=True, exact=False):
+        """Bank read on host arrays: returns (q_pnc, q_norm, weights, m_val, min_dist). Mirrors
+        `retrieve_memory_rows` (src/gpu_batch.rs:700-741): project, distances, softmax / top-k, value read."""
+        _host(q, "q")
+        _host(keys, "keys")
+        _host(values, "values")
+        _host(norm_sq, "norm_sq")
+        rows, dk = q.shape
+        cap, dk2 = keys.shape
+        dv = values.shape[1]
+        if dk2 != dk or values.shape[0] != cap or norm_sq.size != cap:
+            raise N.B200Error(N.ERR_SHAPE, "B200 memory read shape mismatch; refusing launch")
+        q_pnc = np.empty((rows, dk), np.float32)
+        q_norm = np.empty(rows, np.float32)
+        weights = np.empty((rows, cap), np.float32)
+        m_val = np.empty((rows, dv), np.float32)
+        md = np.empty(rows, np.float32)
+        self._check(self._lib.pssa_b200_memory_read(
+            self._h, _ptr(q), 1 if q_is_euclidean else 0, _ptr(keys), _ptr(norm_sq), _ptr(values), rows, dk, dv, cap,
+            count, tau, top_k or 0, _ptr(q_pnc), _ptr(q_norm), _ptr(weights), _ptr(m_val), _ptr(md),
+            N.MEM_EXACT if exact else 0))
+        return q_pnc, q_norm, weights, m_val, md
+
+    def memory_read_dev(self, q, keys, norm_sq, values, rows, dk, dv, cap, count, tau, m_val, top_k=0, q_pnc=None,
+                        q_norm=None, weights=None, min_dist=None, q_is_euclidean=True, exact=False):
+        self._check(self._lib.pssa_b200_memory_read_dev(
+            self._h, _ptr(q), 1 if q_is_euclidean else 0, _ptr(keys), _ptr(norm_sq), _ptr(values), rows, dk, dv, cap,
+            count, tau, top_k or 0, _ptr(q_pnc), _ptr(q_norm), _ptr(weights), _ptr(m_val), _ptr(min_dist),
+            N.MEM_EXACT if exact else 0))
+
+
 class Device:
     """`Device` of src/backend.rs:1012-1018 reduced to the arm this package adds."""
 
