@@ -64,6 +64,10 @@ uint64_t pssa_b200_launch_count(const pssa_b200_ctx* ctx);
 /* Pre-size the context's scratch arena (bytes) so later calls do not allocate. */
 int32_t pssa_b200_ctx_reserve(pssa_b200_ctx* ctx, size_t bytes);
 
+/* Device-side waits (mbarrier phases of the tensor-core pipeline) are bounded; when one expires the kernel
+ * records it and returns. This reads and clears that record: PSSA_B200_OK or PSSA_B200_ERR_TIMEOUT. */
+int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx);
+
 /* Force the number of time chunks of the scan (0 = automatic). A test hook: with more than one
  * chunk the scan runs its reduce / carry / apply passes even on shapes that would not need them. */
 int32_t pssa_b200_ctx_set_scan_chunks(pssa_b200_ctx* ctx, uint32_t chunks);
@@ -159,6 +163,123 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
                               size_t d_key, size_t d_val, size_t capacity, size_t count, float tau,
                               size_t top_k, float* q_pnc, float* q_norm, float* weights, float* m_val,
                               float* min_dist, uint32_t flags);
+
+/* ------------------------------------------------------------------ dense product */
+
+/* Epilogue applied to every output of pssa_b200_gemm_xwt (the reference's elementwise kernels
+ * softplus_in_place / sigmoid_in_place / add_in_place, src/cuda/stages.ptx:541-607, folded in). */
+typedef enum pssa_b200_epilogue {
+    PSSA_B200_EPI_NONE = 0,
+    PSSA_B200_EPI_SOFTPLUS = 1,
+    PSSA_B200_EPI_SIGMOID = 2,
+    PSSA_B200_EPI_SILU = 3,
+    PSSA_B200_EPI_SCALE = 4,  /* out = acc * alpha */
+    PSSA_B200_EPI_ADD_OUT = 5 /* out = out + acc */
+} pssa_b200_epilogue;
+
+/* Arithmetic of the dense products and of the whole model path. */
+typedef enum pssa_b200_precision {
+    PSSA_B200_PRECISION_BF16 = 0, /* bf16 operands on the tensor cores, fp32 accumulate; fp32 scan and retrieval */
+    PSSA_B200_PRECISION_FP32_EXACT = 1 /* fp32 everywhere with the CPU reference's reduction order */
+} pssa_b200_precision;
+
+/*
+ * Y[batch*M, N] = epilogue(X[batch*M, K] * W[N, K]^T): `dispatch_gemm_into` (src/backend.rs:1087-1110,
+ * layout contract 41-48: the batch is folded into rows). HOST pointers, fp32. With
+ * PSSA_B200_PRECISION_FP32_EXACT every output is the reference's `dot_slice` (src/linalg.rs:184-298) bit for
+ * bit; with PSSA_B200_PRECISION_BF16 operands are rounded to bf16 and multiplied on the tensor cores.
+ * `out` must hold batch*M*N floats; it is read only by PSSA_B200_EPI_ADD_OUT.
+ */
+int32_t pssa_b200_gemm_xwt(pssa_b200_ctx* ctx, const float* x, const float* w, size_t m, size_t n, size_t k,
+                           size_t batch, float* out, int32_t epilogue, float alpha, int32_t precision);
+/* Same on DEVICE pointers; `ldo` is the row pitch of out in floats (>= n). */
+int32_t pssa_b200_gemm_xwt_dev(pssa_b200_ctx* ctx, const float* x, const float* w, size_t rows, size_t n, size_t k,
+                               float* out, size_t ldo, int32_t epilogue, float alpha, int32_t precision);
+
+/* ------------------------------------------------------------------ model */
+
+/* `PSSAConfigV2` (src/pssa.rs:253-331) reduced to what the forward path reads. */
+typedef struct pssa_b200_config {
+    uint64_t depth, d_vocab, d_latent, d_state, d_mem_key, mem_capacity;
+    float tau_mem;
+    uint32_t reserved;
+} pssa_b200_config;
+
+/* Parameter / state identifiers for set_tensor and get_tensor (row-major fp32, reference shapes:
+ * src/pssa.rs:506-620). EMBED, UNEMBED and RESIDUAL_SCALES are model-level (layer ignored). */
+typedef enum pssa_b200_tensor {
+    PSSA_B200_T_EMBED = 0,       /* [V, d] */
+    PSSA_B200_T_UNEMBED = 1,     /* [V, d] */
+    PSSA_B200_T_NORM_GAMMA = 2,  /* [d] */
+    PSSA_B200_T_NORM_BETA = 3,   /* [d] */
+    PSSA_B200_T_A_MAT = 4,       /* [d, s] raw; A = -softplus(raw) */
+    PSSA_B200_T_W_DELTA = 5,     /* [d, d] */
+    PSSA_B200_T_W_B = 6,         /* [s, d] */
+    PSSA_B200_T_W_C = 7,         /* [s, d] */
+    PSSA_B200_T_W_QX = 8,        /* [k, d] */
+    PSSA_B200_T_W_QH = 9,        /* [k, d] */
+    PSSA_B200_T_W_GATE = 10,     /* [d, d] */
+    PSSA_B200_T_W_PROJ = 11,     /* [d, d] */
+    PSSA_B200_T_MLP_W1 = 12,     /* [2d, d] */
+    PSSA_B200_T_MLP_W2 = 13,     /* [d, 2d] */
+    PSSA_B200_T_AD_DOWN = 14,    /* [16, d] */
+    PSSA_B200_T_AD_UP = 15,      /* [d, 16] fast */
+    PSSA_B200_T_AD_CONS = 16,    /* [d, 16] consolidated */
+    PSSA_B200_T_RESIDUAL_SCALES = 22 /* [depth-1] */
+} pssa_b200_tensor;
+
+/* Allocates device storage for a model of `cfg` and `max_streams` independent recurrent carries
+ * (`PSSALayerV2::new`, src/pssa.rs:2019-2072, without the random init: weights are uploaded). */
+int32_t pssa_b200_model_create(pssa_b200_ctx* ctx, const pssa_b200_config* cfg, uint32_t max_streams,
+                               pssa_b200_model** out);
+void pssa_b200_model_destroy(pssa_b200_model* model);
+/* Upload one parameter (host fp32). Replaces the reference backends' host-pointer-keyed weight cache and
+ * its invalidation calls (src/cuda.rs:198-252, src/backend.rs:1113-1133): the caller re-uploads what changed. */
+int32_t pssa_b200_model_set_tensor(pssa_b200_model* model, int32_t layer, int32_t tensor, const float* data, size_t len);
+/* Upload one block's bank (src/memory.rs:4-33): keys [cap,k], norm_sq [cap], values [cap,d], count,
+ * write_head, confidence [cap], last_seen_step [cap]. Checks the invariants of src/checkpoint.rs:1060-1066. */
+int32_t pssa_b200_model_set_bank(pssa_b200_model* model, int32_t layer, const float* keys, const float* norm_sq,
+                                 const float* values, uint64_t count, uint64_t write_head, const float* confidence,
+                                 const uint64_t* last_seen_step);
+/* `set_memory_top_k` (src/pssa.rs:2215-2229): 0 restores the all-slots read. The reference refuses this on a
+ * GPU device; here it is the one runtime option the device path adds. */
+int32_t pssa_b200_model_set_top_k(pssa_b200_model* model, size_t top_k);
+int32_t pssa_b200_model_set_precision(pssa_b200_model* model, int32_t precision);
+/* Runtime options the reference refuses on any GPU device (src/pssa.rs:2080-2105, 2232-2243): always
+ * PSSA_B200_ERR_UNSUPPORTED with the reference's message. option: 0 local_conv, 1 ssm_skip, 2 hybrid_read,
+ * 3 grow_memory, 4 loops > 1. */
+int32_t pssa_b200_model_set_option(pssa_b200_model* model, int32_t option, int32_t value);
+
+/* `reset_recurrent_state` (src/pssa.rs:2245-2250) for one stream. */
+int32_t pssa_b200_model_reset_state(pssa_b200_model* model, uint32_t stream);
+/* `copy_recurrent_state_to / from` (src/pssa.rs:2263-2310): [block][d*s] fp32, len = depth*d*s. */
+int32_t pssa_b200_model_get_state(pssa_b200_model* model, uint32_t stream, float* out, size_t len);
+int32_t pssa_b200_model_set_state(pssa_b200_model* model, uint32_t stream, const float* data, size_t len);
+
+/*
+ * `prefill_inference` (src/pssa.rs:2399-2442) on one stream: advances the carry over `n` tokens and, when
+ * logits is not NULL, writes the last token's logits [V]. Empty input is an error; an id >= V stops after
+ * the valid prefix (PSSA_B200_ERR_TOKEN, *processed = prefix length, logits untouched). `cancelled` (may be
+ * NULL) is polled before every pass of at most max_rows tokens; a non-zero return stops with
+ * PSSA_B200_ERR_CANCELLED, the carry holding the passes already done.
+ */
+int32_t pssa_b200_model_prefill(pssa_b200_model* model, uint32_t stream, const uint64_t* ids, size_t n, float* logits,
+                                size_t* processed, int32_t (*cancelled)(void*), void* cancel_arg);
+/*
+ * Independent sequences packed in one id array (`SequenceBatch::forward`, src/sequence_batch.rs:233-384, with
+ * a per-lane carry): lane l = ids[offsets[l] .. offsets[l]+lengths[l]) continuing stream streams[l]. All lanes
+ * are validated before any work. logits (NULL to skip) receives [n_lanes, V]: each lane's last-token logits
+ * (rows of zero-length lanes are left untouched). greedy (NULL to skip) receives each lane's greedy next
+ * token (src/inference.rs:123-127).
+ */
+int32_t pssa_b200_model_prefill_batch(pssa_b200_model* model, const uint64_t* ids, const uint32_t* offsets,
+                                      const uint32_t* lengths, const uint32_t* streams, size_t n_lanes, float* logits,
+                                      uint64_t* greedy);
+/* `forward_inference` (src/pssa.rs:2387-2391) for n streams at once: one token each. */
+int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* streams, const uint64_t* ids, size_t n,
+                                    float* logits, uint64_t* greedy);
+/* Upper bound on token rows processed per pass (activation workspace = about 40 KB per row at d 768). */
+int32_t pssa_b200_model_set_max_rows(pssa_b200_model* model, size_t max_rows);
 
 #ifdef __cplusplus
 }

@@ -5,5 +5,6 @@ happens in libpssa_b200.so (hand-written sm_100a CUDA), reached through the C AB
 """
 from ._native import B200Error, LIB_PATH, lib  # noqa: F401
 from .dispatch import B200Dispatch, Device  # noqa: F401
+from .model import PSSAModel  # noqa: F401
 
-__all__ = ["B200Dispatch", "B200Error", "Device", "LIB_PATH", "lib"]
+__all__ = ["B200Dispatch", "B200Error", "Device", "LIB_PATH", "PSSAModel", "lib"]

@@ -35,9 +35,35 @@ SIGNATURES = {
                                               _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "pssa_b200_memory_read": (C.c_int32, [_vp, _vp, C.c_int32, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _sz,
                                           _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
+    "pssa_b200_ctx_poll_status": (C.c_int32, [_vp]),
+    "pssa_b200_gemm_xwt": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, C.c_int32, C.c_float, C.c_int32]),
+    "pssa_b200_gemm_xwt_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _sz, C.c_int32, C.c_float, C.c_int32]),
+    "pssa_b200_model_create": (C.c_int32, [_vp, _vp, C.c_uint32, C.POINTER(_vp)]),
+    "pssa_b200_model_destroy": (None, [_vp]),
+    "pssa_b200_model_set_tensor": (C.c_int32, [_vp, C.c_int32, C.c_int32, _vp, _sz]),
+    "pssa_b200_model_set_bank": (C.c_int32, [_vp, C.c_int32, _vp, _vp, _vp, C.c_uint64, C.c_uint64, _vp, _vp]),
+    "pssa_b200_model_set_top_k": (C.c_int32, [_vp, _sz]),
+    "pssa_b200_model_set_precision": (C.c_int32, [_vp, C.c_int32]),
+    "pssa_b200_model_set_option": (C.c_int32, [_vp, C.c_int32, C.c_int32]),
+    "pssa_b200_model_set_max_rows": (C.c_int32, [_vp, _sz]),
+    "pssa_b200_model_reset_state": (C.c_int32, [_vp, C.c_uint32]),
+    "pssa_b200_model_get_state": (C.c_int32, [_vp, C.c_uint32, _vp, _sz]),
+    "pssa_b200_model_set_state": (C.c_int32, [_vp, C.c_uint32, _vp, _sz]),
+    "pssa_b200_model_prefill": (C.c_int32, [_vp, C.c_uint32, _vp, _sz, _vp, C.POINTER(_sz), _vp, _vp]),
+    "pssa_b200_model_prefill_batch": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "pssa_b200_model_decode_step": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, _vp]),
 }
 SSM_EXACT = 1
 MEM_EXACT = 1
+EPI_NONE, EPI_SOFTPLUS, EPI_SIGMOID, EPI_SILU, EPI_SCALE, EPI_ADD_OUT = range(6)
+PRECISION_BF16, PRECISION_FP32_EXACT = 0, 1
+CANCEL_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)
+
+
+class Config(C.Structure):
+    """`pssa_b200_config`"""
+    _fields_ = [("depth", C.c_uint64), ("d_vocab", C.c_uint64), ("d_latent", C.c_uint64), ("d_state", C.c_uint64),
+                ("d_mem_key", C.c_uint64), ("mem_capacity", C.c_uint64), ("tau_mem", C.c_float), ("reserved", C.c_uint32)]
 
 _lib = None
 

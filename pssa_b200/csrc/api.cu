@@ -212,7 +212,6 @@ int32_t pssa_b200_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b
 
 // ------------------------------------------------------------------ fused SSM stage
 
-static bool ptr_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int32_t pssa_b200_ssm_forward_dev(pssa_b200_ctx* ctx, const float* delta, const float* b_proj, const float* c_proj,
                                   const float* x_norm, const float* rates, float* carry, float* y, float* states,
@@ -243,8 +242,7 @@ int32_t pssa_b200_ssm_forward_dev(pssa_b200_ctx* ctx, const float* delta, const 
     p.delta = delta, p.x_norm = x_norm, p.b_proj = b_proj, p.c_proj = c_proj, p.rates = rates;
     p.carry = carry, p.y = y, p.states = states, p.bar_a = bar_a, p.bar_b = bar_b;
     p.rows = rows, p.d = (int)d_m, p.s = (int)d_s, p.lanes = (int)lanes;
-    p.aligned = d_m % 4 == 0 && d_s % 4 == 0 && ptr_aligned16(delta) && ptr_aligned16(x_norm) &&
-                ptr_aligned16(b_proj) && ptr_aligned16(c_proj);
+    p.aligned = ssm_vector_ok(p);
     if (offsets) {
         arena_reset(ctx);
         if ((rc = arena_reserve(ctx, arena_round(lanes * 4) * 2)) != PSSA_B200_OK) return rc;
@@ -370,6 +368,88 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
     PSSA_CUDA(ctx, cudaMemcpyAsync(m_val, dm.p, rows * d_val * 4, cudaMemcpyDeviceToHost, st));
     if (min_dist) PSSA_CUDA(ctx, cudaMemcpyAsync(min_dist, dmin.p, rows * 4, cudaMemcpyDeviceToHost, st));
     PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+    return PSSA_B200_OK;
+}
+
+// ------------------------------------------------------------------ dense product
+
+// backend.rs:11-38 (checked_gemm_sizes)
+static int32_t gemm_sizes(pssa_b200_ctx* ctx, size_t rows, size_t n, size_t k, size_t ldo, int32_t epi, int32_t precision) {
+    if (rows == 0 || n == 0 || k == 0) return fail(ctx, PSSA_B200_ERR_SHAPE, "GEMM dimensions must be positive");
+    size_t e;
+    int32_t rc;
+    if ((rc = f32_elems(ctx, "GEMM input", {rows, k}, &e))) return rc;
+    if ((rc = f32_elems(ctx, "GEMM weights", {n, k}, &e))) return rc;
+    if ((rc = f32_elems(ctx, "GEMM output", {rows, ldo}, &e))) return rc;
+    if (ldo < n) return fail(ctx, PSSA_B200_ERR_SHAPE, "GEMM output pitch %zu is smaller than N %zu", ldo, n);
+    if (epi < PSSA_B200_EPI_NONE || epi > PSSA_B200_EPI_ADD_OUT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "unknown GEMM epilogue %d", epi);
+    if (precision != PSSA_B200_PRECISION_BF16 && precision != PSSA_B200_PRECISION_FP32_EXACT)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "unknown GEMM precision %d", precision);
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_gemm_xwt_dev(pssa_b200_ctx* ctx, const float* x, const float* w, size_t rows, size_t n, size_t k, float* out,
+                               size_t ldo, int32_t epilogue, float alpha, int32_t precision) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    int32_t rc = gemm_sizes(ctx, rows, n, k, ldo, epilogue, precision);
+    if (rc) return rc;
+    if (!x || !w || !out) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "GEMM: null buffer");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (precision == PSSA_B200_PRECISION_FP32_EXACT) return launch_gemm_exact(ctx, x, w, out, rows, n, k, ldo, epilogue, alpha);
+    // operands are rounded to bf16 in scratch from the arena
+    arena_reset(ctx);
+    if ((rc = arena_reserve(ctx, arena_round(rows * k * 2) + arena_round(n * k * 2)))) return rc;
+    void* x16 = arena_take(ctx, rows * k * 2);
+    void* w16 = arena_take(ctx, n * k * 2);
+    if ((rc = launch_to_bf16(ctx, x, x16, rows * k))) return rc;
+    if ((rc = launch_to_bf16(ctx, w, w16, n * k))) return rc;
+    return launch_gemm_bf16(ctx, x16, w16, out, nullptr, rows, n, k, ldo, epilogue, alpha);
+}
+
+int32_t pssa_b200_gemm_xwt(pssa_b200_ctx* ctx, const float* x, const float* w, size_t m, size_t n, size_t k, size_t batch,
+                           float* out, int32_t epilogue, float alpha, int32_t precision) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    size_t rows;
+    // backend.rs:41-48: the batch shares W and is folded into rows
+    if (m == 0 || batch == 0 || !checked_mul(m, batch, &rows)) return fail(ctx, PSSA_B200_ERR_SHAPE, "GEMM row count must be positive and fit usize");
+    int32_t rc = gemm_sizes(ctx, rows, n, k, n, epilogue, precision);
+    if (rc) return rc;
+    if (!x || !w || !out) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "GEMM: null buffer");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    DeviceBuf dx, dw, dout;
+    cudaStream_t st = ctx->stream;
+    PSSA_CUDA(ctx, dx.alloc(rows * k * 4));
+    PSSA_CUDA(ctx, dw.alloc(n * k * 4));
+    PSSA_CUDA(ctx, dout.alloc(rows * n * 4));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(dx.p, x, rows * k * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(dw.p, w, n * k * 4, cudaMemcpyHostToDevice, st));
+    if (epilogue == PSSA_B200_EPI_ADD_OUT) PSSA_CUDA(ctx, cudaMemcpyAsync(dout.p, out, rows * n * 4, cudaMemcpyHostToDevice, st));
+    rc = pssa_b200_gemm_xwt_dev(ctx, dx.f(), dw.f(), rows, n, k, dout.f(), n, epilogue, alpha, precision);
+    if (rc == PSSA_B200_OK) {
+        int status = 0;
+        PSSA_CUDA(ctx, cudaMemcpyAsync(&status, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, st));
+        PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+        if (status != 0) {
+            cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), st);
+            return fail(ctx, status, "B200 GEMM: a bounded device-side wait expired");
+        }
+        PSSA_CUDA(ctx, cudaMemcpyAsync(out, dout.p, rows * n * 4, cudaMemcpyDeviceToHost, st));
+    }
+    PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+    return rc;
+}
+
+/* Reads and clears the device status word written by bounded waits (0 = none expired). */
+int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    int status = 0;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(&status, ctx->status_dev, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (status != 0) {
+        PSSA_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
+        return fail(ctx, status, "a bounded device-side wait expired (status %d)", status);
+    }
     return PSSA_B200_OK;
 }
 

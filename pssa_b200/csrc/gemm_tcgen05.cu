@@ -1,0 +1,368 @@
+// bf16 tensor-core product for the projections: OUT[M, N] = epilogue(A[M, K] * B[N, K]^T), fp32 accumulate.
+//
+// Replaces the reference's cuBLAS SGEMM calls for W_delta, W_B, W_C, W_qx, W_qh, W_gate, W_proj, adapter
+// down, MLP W1/W2 and the vocabulary head (src/cuda.rs:287-320, src/cuda/stages.rs:183-208) and the
+// elementwise kernels that follow them (softplus / sigmoid / sigmoid_mul / add, src/cuda/stages.ptx:541-607),
+// which become the epilogue.
+//
+// Blackwell data path, one 128 x BN output tile per CTA:
+//   warp 0   producer: TMA (cp.async.bulk.tensor.2d) loads of 128x64 / BNx64 bf16 boxes, 128-byte swizzle,
+//            into a 4-stage shared-memory ring; completion on per-stage "full" mbarriers.
+//   warp 1   issuer: one thread issues tcgen05.mma (cta_group::1, kind::f16, M 128, N BN, K 16) from shared-
+//            memory descriptors into a TMEM accumulator of BN fp32 columns; tcgen05.commit releases each
+//            ring stage ("empty" mbarrier) and finally signals "accumulator ready".
+//   warps 2-5 epilogue: tcgen05.ld (32 lanes x 32 columns per warp) -> activation -> global stores (fp32
+//            and/or bf16).
+// Both operands are K-major (row-major [rows, K]), so X * W^T needs no transpose anywhere.
+// Every mbarrier wait is bounded: on expiry the kernel records PSSA_B200_ERR_TIMEOUT in the context's
+// status word, stops issuing work, and still frees its TMEM.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "bounds.hpp"
+#include "context.hpp"
+#include "device_math.cuh"
+#include "kernels.hpp"
+
+namespace pssa {
+namespace {
+
+constexpr int BM = 128;      // rows per tile = UMMA M
+constexpr int BK = 64;       // bf16 per stage row = 128 bytes = one swizzle atom
+constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit operands
+constexpr int STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned kSpinLimit = 1u << 24;
+
+struct GemmEpilogue {
+    float* out;            // fp32 [M, ldo] or null
+    __nv_bfloat16* out16;  // bf16 [M, ld16] or null
+    size_t ldo, ld16;
+    int M, N, K;
+    int epi;               // Epilogue, or -1 for the column-range table below
+    float alpha;
+    int c1, c2, c3;        // table: [0,c1) softplus, [c1,c2) none, [c2,c3) sigmoid, [c3,N) silu
+    int* status;
+};
+
+// ---- PTX wrappers -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// bounded wait: false when the phase did not complete within the spin budget
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t addr = smem_u32(bar);
+    for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread
+__device__ __forceinline__ void tcgen05_ld_32x32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);  // start address, 16-byte units
+    desc |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+    desc |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset: 8 rows x 128 bytes
+    desc |= (uint64_t)1 << 46;                       // descriptor version for tcgen05
+    desc |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return desc;
+}
+
+// kind::f16 instruction descriptor: D fp32, A and B bf16, both K-major, shape M x N
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ float fast_epilogue(const GemmEpilogue& e, float acc, int col, float prev) {
+    int epi = e.epi;
+    if (epi < 0) epi = col < e.c1 ? EPI_SOFTPLUS : col < e.c2 ? EPI_NONE : col < e.c3 ? EPI_SIGMOID : EPI_SILU;
+    switch (epi) {
+        case EPI_SOFTPLUS: return acc > 20.0f ? acc : log1pf(__expf(acc));
+        case EPI_SIGMOID: return 1.0f / (1.0f + __expf(-acc));
+        case EPI_SILU: return acc / (1.0f + __expf(-acc));
+        case EPI_SCALE: return acc * e.alpha;
+        case EPI_ADD_OUT: return prev + acc;
+        default: return acc;
+    }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                         const __grid_constant__ CUtensorMap map_b,
+                                                                         GemmEpilogue e) {
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // 1024-byte alignment is required by the 128-byte swizzle
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char* smem_a = smem;
+    unsigned char* smem_b = smem + STAGES * A_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_b + STAGES * B_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_bar = empty_bar + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int num_kb = (e.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM allocation is a warp-wide operation; BN fp32 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t round = kb / STAGES;
+                if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+                    atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+                    break;
+                }
+                mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], kb * BK, m0);
+                tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kb * BK, n0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) {
+                    atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint64_t da = umma_desc_sw128(smem_u32(smem_a + s * A_BYTES));
+                const uint64_t db = umma_desc_sw128(smem_u32(smem_b + s * B_BYTES));
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // advance 32 bytes (16 bf16) inside the swizzle atom: +2 in 16-byte units
+                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+            }
+            tcgen05_commit(acc_bar);  // accumulator complete (or abandoned)
+        }
+    } else {
+        // epilogue warps 2..5 own TMEM lane quadrants (warp % 4)
+        const int quad = warp & 3;
+        const bool ready = mbar_wait(acc_bar, 0);
+        tcgen05_fence_after();
+        const int row = m0 + quad * 32 + lane;
+        if (ready && *(volatile int*)e.status == 0) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= e.N) break;  // warp-uniform
+                float v[32];
+                tcgen05_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                if (row < e.M) {
+                    const int col0 = n0 + c0;
+                    float* orow = e.out ? e.out + (size_t)row * e.ldo + col0 : nullptr;
+                    __nv_bfloat16* brow = e.out16 ? e.out16 + (size_t)row * e.ld16 + col0 : nullptr;
+                    const bool full_chunk = col0 + 32 <= e.N;
+                    const bool vec_ok = full_chunk && orow && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float prev = (e.epi == EPI_ADD_OUT && orow && col0 + j < e.N) ? orow[j] : 0.0f;
+                        v[j] = fast_epilogue(e, v[j], col0 + j, prev);
+                    }
+                    if (vec_ok) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else if (orow) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < e.N) orow[j] = v[j];
+                    }
+                    if (brow) {
+                        if (full_chunk && ((reinterpret_cast<uintptr_t>(brow) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                uint4 pk;
+                                pk.x = *reinterpret_cast<uint32_t*>(&p0), pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                                pk.z = *reinterpret_cast<uint32_t*>(&p2), pk.w = *reinterpret_cast<uint32_t*>(&p3);
+                                *reinterpret_cast<uint4*>(brow + j) = pk;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < e.N) brow[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                }
+            }
+        } else if (!ready && lane == 0) {
+            atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn(pssa_b200_ctx* ctx) {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+        fail(ctx, PSSA_B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+        return nullptr;
+    }
+    fn = (EncodeTiledFn)p;
+    return fn;
+}
+
+// bf16 row-major [rows, k] tensor, box = 64 columns (128 bytes) x box_rows rows, 128-byte swizzle
+int32_t make_map(pssa_b200_ctx* ctx, CUtensorMap* map, const void* base, size_t rows, size_t k, int box_rows) {
+    EncodeTiledFn fn = encode_fn(ctx);
+    if (!fn) return PSSA_B200_ERR_CUDA;
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, PSSA_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (rows %zu, k %zu)", (int)r, rows, k);
+    return PSSA_B200_OK;
+}
+
+template <int BN>
+int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const GemmEpilogue& e) {
+    CUtensorMap map_a, map_b;
+    int32_t rc;
+    if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
+    if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
+    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
+    auto kern = gemm_bf16_tcgen05_kernel<BN>;
+    static bool attr = false;
+    if (!attr) {
+        PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr = true;
+    }
+    dim3 grid((unsigned)((e.M + BM - 1) / BM), (unsigned)((e.N + BN - 1) / BN));
+    kern<<<grid, GEMM_THREADS, smem, ctx->stream>>>(map_a, map_b, e);
+    return after_launch(ctx, "gemm_bf16_tcgen05_kernel");
+}
+
+int32_t check_shape(pssa_b200_ctx* ctx, const void* a, const void* b, size_t M, size_t N, size_t K) {
+    if (M == 0 || N == 0 || K == 0) return fail(ctx, PSSA_B200_ERR_SHAPE, "GEMM dimensions must be positive");
+    if (M > 0x7fffffff || N > 0x7fffffff || K > 0x7fffffff)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 GEMM dimensions must fit i32; refusing launch");
+    if (K % 8 != 0 || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15))
+        return fail(ctx, PSSA_B200_ERR_UNSUPPORTED,
+                    "B200 bf16 GEMM needs K %% 8 == 0 and 16-byte aligned operands (TMA row pitch); K = %zu; use the fp32 path", K);
+    if ((M + BM - 1) / BM > 0x7fffffff || (N + 63) / 64 > 65535)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 GEMM grid exceeds grid limits; refusing launch");
+    return PSSA_B200_OK;
+}
+
+int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue& e) {
+    e.status = ctx->status_dev;
+    // narrow outputs (state / key / rank projections) use the 64-column tile so fewer tensor-core columns idle
+    if (e.N <= 64) return launch_tile<64>(ctx, a, b, e);
+    return launch_tile<128>(ctx, a, b, e);
+}
+
+}  // namespace
+
+int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
+                         size_t K, size_t ldo, int epi, float alpha) {
+    int32_t rc = check_shape(ctx, x16, w16, M, N, K);
+    if (rc) return rc;
+    GemmEpilogue e{};
+    e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
+    e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = epi, e.alpha = alpha;
+    return dispatch(ctx, x16, w16, e);
+}
+
+int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
+                             size_t ldo, int c1, int c2, int c3) {
+    int32_t rc = check_shape(ctx, x16, w16, M, N, K);
+    if (rc) return rc;
+    GemmEpilogue e{};
+    e.out = out, e.out16 = nullptr, e.ldo = ldo, e.ld16 = 0;
+    e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = -1, e.alpha = 1.0f, e.c1 = c1, e.c2 = c2, e.c3 = c3;
+    return dispatch(ctx, x16, w16, e);
+}
+
+}  // namespace pssa

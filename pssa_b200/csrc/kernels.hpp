@@ -30,8 +30,20 @@ struct SsmParams {
     size_t rows;
     int d, s, lanes;
     int aligned;           // 16-byte vector staging allowed
+    // row pitches in floats (0 = dense: d for delta, s for b_proj / c_proj)
+    size_t ld_delta, ld_bc;
+    // carry of lane l lives at carry + slot(l) * carry_stride, slot(l) = lane_slots ? lane_slots[l] : l
+    const uint32_t* lane_slots;
+    size_t carry_stride;   // 0 = d*s
 };
 int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact);
+// 16-byte staging needs 16-byte aligned bases and row pitches / widths that are multiples of 4 floats
+inline bool ssm_vector_ok(const SsmParams& p) {
+    auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    size_t ldd = p.ld_delta ? p.ld_delta : (size_t)p.d, ldbc = p.ld_bc ? p.ld_bc : (size_t)p.s;
+    return p.d % 4 == 0 && p.s % 4 == 0 && ldd % 4 == 0 && ldbc % 4 == 0 && al(p.delta) && al(p.x_norm) && al(p.b_proj) &&
+           al(p.c_proj);
+}
 
 // retrieve_poincare.cu
 struct RetrieveParams {
@@ -42,6 +54,7 @@ struct RetrieveParams {
     const float* keys;     // [cap, dk]
     const float* norm_sq;  // [cap]
     const float* values;   // [cap, dv]
+    size_t ldq;            // row pitch of q in floats (0 = dk)
     float* weights;        // [rows, cap] distances in flight, weights on return
     float* m_val;          // [rows, dv]
     float* min_dist;       // [rows], may be null
@@ -50,5 +63,27 @@ struct RetrieveParams {
     float tau;
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
+
+// gemm_exact.cu: out[M, ldo] (first N columns) = epilogue(X[M,K] * W[N,K]^T), fp32, dot_slice order
+int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, float* out, size_t M, size_t N, size_t K,
+                          size_t ldo, int epi, float alpha);
+
+// gemm_tcgen05.cu: bf16 operands [rows, K] row-major, fp32 accumulate in TMEM; out fp32 [M, ldo] and/or bf16 [M, N]
+int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
+                         size_t K, size_t ldo, int epi, float alpha);
+// concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU
+int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
+                             size_t ldo, int c1, int c2, int c3);
+
+// elementwise.cu
+int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t* ids, const float* feats, const float* gamma,
+                          const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact);
+int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
+                            size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
+                            float ssm_scale);
+int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale);
+int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d);
+int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n);
+int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v);
 
 }  // namespace pssa

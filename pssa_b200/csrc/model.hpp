@@ -1,0 +1,70 @@
+// Device-resident PSSA model: weights, banks, per-stream recurrent carries and the activation workspace.
+// Mirrors the persistent part of `PSSALayerV2` / `PSSAContinuousBlockV2` (src/pssa.rs:506-620, 1931-1966).
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "context.hpp"
+
+namespace pssa {
+
+// index = pssa_b200_tensor value (include/pssa_b200.h)
+enum TensorId : int {
+    T_EMBED = 0, T_UNEMBED = 1, T_NORM_GAMMA = 2, T_NORM_BETA = 3, T_A_MAT = 4, T_W_DELTA = 5, T_W_B = 6, T_W_C = 7,
+    T_W_QX = 8, T_W_QH = 9, T_W_GATE = 10, T_W_PROJ = 11, T_MLP_W1 = 12, T_MLP_W2 = 13, T_AD_DOWN = 14, T_AD_UP = 15,
+    T_AD_CONS = 16, T_H_PERSISTENT = 17, T_BANK_KEYS = 18, T_BANK_VALUES = 19, T_BANK_NORM_SQ = 20,
+    T_BANK_CONFIDENCE = 21, T_RESIDUAL_SCALES = 22, T_COUNT = 23,
+};
+
+struct DeviceBlock {
+    float* w[T_COUNT] = {};  // fp32 masters (only block-level ids are used)
+    float* rates = nullptr;  // A = -softplus(raw)               [d, s]
+    float* u_eff = nullptr;  // adapter up: fast + consolidated   [d, rank]
+    std::vector<float> host_up, host_cons;
+    // bank metadata kept on the host (src/memory.rs:4-33)
+    uint64_t count = 0, write_head = 0;
+    std::vector<float> confidence;
+    std::vector<uint64_t> last_seen;
+    // bf16 copies for the tensor-core path
+    void* wcat_bf16 = nullptr;  // [ncat, d] rows: W_delta | W_B | W_C | W_qx | W_gate | adapter down
+    void* wqh_bf16 = nullptr;
+    void* wproj_bf16 = nullptr;
+    void* w1_bf16 = nullptr;
+    void* w2_bf16 = nullptr;
+    bool bf16_dirty = true;
+};
+
+struct Workspace {
+    size_t rows = 0, lanes = 0;
+    uint32_t *ids = nullptr, *lane_off = nullptr, *lane_len = nullptr, *lane_slot = nullptr, *last_rows = nullptr,
+             *greedy = nullptr;
+    float *feat_a = nullptr, *feat_b = nullptr, *x_norm = nullptr, *proj = nullptr, *y = nullptr, *weights = nullptr,
+          *m_val = nullptr, *m_proj = nullptr, *z = nullptr, *mlp_act = nullptr, *last_feat = nullptr, *logits = nullptr;
+    void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr;
+    char* base = nullptr;
+    size_t bytes = 0;
+};
+
+}  // namespace pssa
+
+struct pssa_b200_model {
+    pssa_b200_ctx* ctx = nullptr;
+    pssa_b200_config cfg{};
+    size_t d = 0, s = 0, k = 0, cap = 0, v = 0, depth = 0, rank = 16;
+    size_t ncat = 0;  // d + s + s + k + d + rank
+    size_t off_delta = 0, off_b = 0, off_c = 0, off_q = 0, off_gate = 0, off_act = 0;
+    uint32_t max_streams = 1;
+    uint32_t precision = 0;  // PSSA_B200_PRECISION_*
+    size_t top_k = 0;
+    size_t max_rows = 65536;
+    float* embed = nullptr;
+    float* unembed = nullptr;
+    void* unembed_bf16 = nullptr;
+    bool unembed_dirty = true;
+    std::vector<pssa::DeviceBlock> blocks;
+    std::vector<float> residual_scales;
+    float* state = nullptr;  // [max_streams][depth][d*s]
+    pssa::Workspace ws;
+    std::vector<bool> tensor_set;  // [depth * T_COUNT + id] upload bookkeeping
+};

@@ -1,0 +1,319 @@
+// Batched forward over packed lanes: the reference's staged block schedule on device-resident buffers.
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "bounds.hpp"
+#include "context.hpp"
+#include "device_math.cuh"
+#include "kernels.hpp"
+#include "model.hpp"
+
+using namespace pssa;
+
+namespace {
+
+struct Carver {
+    size_t off = 0;
+    size_t take(size_t bytes) {
+        size_t o = (off + 255) & ~size_t(255);
+        off = o + bytes;
+        return o;
+    }
+};
+
+// one allocation carved into the per-row activation buffers; grows when a larger pass is requested
+int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
+    Workspace& ws = m->ws;
+    if (ws.base && rows <= ws.rows && lanes <= ws.lanes) return PSSA_B200_OK;
+    pssa_b200_ctx* ctx = m->ctx;
+    rows = std::max(rows, ws.rows);
+    lanes = std::max(lanes, ws.lanes);
+    const size_t d = m->d, f = sizeof(float);
+    Carver c;
+    size_t o_ids = c.take(rows * 4), o_off = c.take(lanes * 4), o_len = c.take(lanes * 4), o_slot = c.take(lanes * 4),
+           o_last = c.take(lanes * 4), o_greedy = c.take(lanes * 4);
+    size_t o_fa = c.take(rows * d * f), o_fb = c.take(rows * d * f), o_xn = c.take(rows * d * f),
+           o_proj = c.take(rows * m->ncat * f), o_y = c.take(rows * d * f), o_w = c.take(rows * m->cap * f),
+           o_mv = c.take(rows * d * f), o_mp = c.take(rows * d * f), o_z = c.take(rows * d * f),
+           o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
+    size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * d * 2),
+           o_ab = c.take(rows * 2 * d * 2);
+    size_t total = c.take(0);
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ws.base) cudaFree(ws.base);
+    ws = Workspace();
+    cudaError_t e = cudaMalloc((void**)&ws.base, total);
+    if (e != cudaSuccess) {
+        ws = Workspace();
+        return cuda_fail(ctx, e, "activation workspace allocation");
+    }
+    ws.bytes = total, ws.rows = rows, ws.lanes = lanes;
+    char* b = ws.base;
+    ws.ids = (uint32_t*)(b + o_ids), ws.lane_off = (uint32_t*)(b + o_off), ws.lane_len = (uint32_t*)(b + o_len);
+    ws.lane_slot = (uint32_t*)(b + o_slot), ws.last_rows = (uint32_t*)(b + o_last), ws.greedy = (uint32_t*)(b + o_greedy);
+    ws.feat_a = (float*)(b + o_fa), ws.feat_b = (float*)(b + o_fb), ws.x_norm = (float*)(b + o_xn);
+    ws.proj = (float*)(b + o_proj), ws.y = (float*)(b + o_y), ws.weights = (float*)(b + o_w), ws.m_val = (float*)(b + o_mv);
+    ws.m_proj = (float*)(b + o_mp), ws.z = (float*)(b + o_z), ws.mlp_act = (float*)(b + o_act);
+    ws.last_feat = (float*)(b + o_lf), ws.logits = (float*)(b + o_lg);
+    ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab;
+    return PSSA_B200_OK;
+}
+
+// refresh the bf16 weight copies the tensor-core path reads (concatenated x-side projections)
+int32_t refresh_bf16(pssa_b200_model* m) {
+    pssa_b200_ctx* ctx = m->ctx;
+    const size_t d = m->d;
+    int32_t rc;
+    for (auto& b : m->blocks) {
+        if (!b.bf16_dirty) continue;
+        char* cat = (char*)b.wcat_bf16;
+        struct Part { int id; size_t row_off, rows; };
+        Part parts[] = {{T_W_DELTA, m->off_delta, d}, {T_W_B, m->off_b, m->s},       {T_W_C, m->off_c, m->s},
+                        {T_W_QX, m->off_q, m->k},     {T_W_GATE, m->off_gate, d},    {T_AD_DOWN, m->off_act, m->rank}};
+        for (auto& p : parts)
+            if ((rc = launch_to_bf16(ctx, b.w[p.id], cat + p.row_off * d * 2, p.rows * d))) return rc;
+        if ((rc = launch_to_bf16(ctx, b.w[T_W_QH], b.wqh_bf16, m->k * d))) return rc;
+        if ((rc = launch_to_bf16(ctx, b.w[T_W_PROJ], b.wproj_bf16, d * d))) return rc;
+        if ((rc = launch_to_bf16(ctx, b.w[T_MLP_W1], b.w1_bf16, 2 * d * d))) return rc;
+        if ((rc = launch_to_bf16(ctx, b.w[T_MLP_W2], b.w2_bf16, 2 * d * d))) return rc;
+        b.bf16_dirty = false;
+    }
+    if (m->unembed_dirty) {
+        if ((rc = launch_to_bf16(ctx, m->unembed, m->unembed_bf16, m->v * d))) return rc;
+        m->unembed_dirty = false;
+    }
+    return PSSA_B200_OK;
+}
+
+// out[rows, ldo](first n cols) = epilogue(X * W^T): exact fp32 or bf16 tensor cores
+int32_t dense(pssa_b200_model* m, const float* x32, const void* x16, const float* w32, const void* w16, float* out, size_t rows,
+              size_t n, size_t k, size_t ldo, int epi, float alpha, void* out_bf16 = nullptr) {
+    if (m->precision == PSSA_B200_PRECISION_FP32_EXACT) return launch_gemm_exact(m->ctx, x32, w32, out, rows, n, k, ldo, epi, alpha);
+    return launch_gemm_bf16(m->ctx, x16, w16, out, out_bf16, rows, n, k, ldo, epi, alpha);
+}
+
+// One pass: `rows` packed token rows of `lanes` lanes already described in the workspace (ids, lane_off, lane_len,
+// lane_slot, last_rows). Leaves the final features of every row in ws.feat_a or feat_b (returned).
+int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32_t* h_off, const uint32_t* h_len, float** feats_out) {
+    pssa_b200_ctx* ctx = m->ctx;
+    Workspace& ws = m->ws;
+    const bool exact = m->precision == PSSA_B200_PRECISION_FP32_EXACT;
+    const int d = (int)m->d, s = (int)m->s, k = (int)m->k;
+    const size_t nc = m->ncat, ds = m->d * m->s;
+    const float ssm_scale = 1.0f / std::sqrt((float)s);
+    int32_t rc;
+    if (!exact && (rc = refresh_bf16(m))) return rc;
+    float* feat_in = nullptr;
+    float* feat_out = ws.feat_a;
+    (void)h_off;
+    (void)h_len;
+    for (size_t l = 0; l < m->depth; ++l) {
+        DeviceBlock& b = m->blocks[l];
+        // stage 1: gather + RMSNorm (src/gpu_batch.rs:445-472)
+        if ((rc = launch_embed_norm(ctx, m->embed, l == 0 ? ws.ids : nullptr, feat_in, b.w[T_NORM_GAMMA], b.w[T_NORM_BETA],
+                                    ws.x_norm, exact ? nullptr : ws.x_bf16, rows, d, exact)))
+            return rc;
+        // stage 2: x-side projections (src/gpu_batch.rs:477-536 plus the query/gate/adapter rows that read x_norm)
+        if (exact) {
+            struct P { int id; size_t off, n; int epi; };
+            P ps[] = {{T_W_DELTA, m->off_delta, m->d, EPI_SOFTPLUS}, {T_W_B, m->off_b, m->s, EPI_NONE},
+                      {T_W_C, m->off_c, m->s, EPI_NONE},            {T_W_QX, m->off_q, m->k, EPI_NONE},
+                      {T_W_GATE, m->off_gate, m->d, EPI_SIGMOID},   {T_AD_DOWN, m->off_act, m->rank, EPI_SILU}};
+            for (auto& p : ps)
+                if ((rc = launch_gemm_exact(ctx, ws.x_norm, b.w[p.id], ws.proj + p.off, rows, p.n, m->d, nc, p.epi, 1.0f))) return rc;
+        } else {
+            if ((rc = launch_gemm_bf16_cat(ctx, ws.x_bf16, b.wcat_bf16, ws.proj, rows, nc, m->d, nc, (int)m->off_b, (int)m->off_gate,
+                                           (int)m->off_act)))
+                return rc;
+        }
+        // stage 3: SSM with the lane carries of this block (src/gpu_batch.rs:582-619)
+        SsmParams sp{};
+        sp.delta = ws.proj + m->off_delta, sp.x_norm = ws.x_norm, sp.b_proj = ws.proj + m->off_b, sp.c_proj = ws.proj + m->off_c;
+        sp.rates = b.rates, sp.carry = m->state + l * ds, sp.y = ws.y;
+        sp.offsets = ws.lane_off, sp.lengths = ws.lane_len, sp.rows = rows, sp.d = d, sp.s = s, sp.lanes = (int)lanes;
+        sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = m->depth * ds;
+        sp.aligned = ssm_vector_ok(sp);
+        if ((rc = launch_ssm_fused(ctx, sp, exact))) return rc;
+        // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
+        if (!exact && (rc = launch_to_bf16(ctx, ws.y, ws.y_bf16, rows * (size_t)d))) return rc;
+        if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
+        RetrieveParams rp{};
+        rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = nullptr, rp.q_norm = nullptr;
+        rp.keys = b.w[T_BANK_KEYS], rp.norm_sq = b.w[T_BANK_NORM_SQ], rp.values = b.w[T_BANK_VALUES];
+        rp.weights = ws.weights, rp.m_val = ws.m_val, rp.min_dist = nullptr;
+        rp.rows = rows, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
+        rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
+        if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
+        if (!exact && (rc = launch_to_bf16(ctx, ws.m_val, ws.m_bf16, rows * (size_t)d))) return rc;
+        if ((rc = dense(m, ws.m_val, ws.m_bf16, b.w[T_W_PROJ], b.wproj_bf16, ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
+        // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
+        if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z,
+                                      exact ? nullptr : ws.z_bf16, rows, d, (int)m->rank, ssm_scale)))
+            return rc;
+        if ((rc = dense(m, ws.z, ws.z_bf16, b.w[T_MLP_W1], b.w1_bf16, ws.mlp_act, rows, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f,
+                        exact ? nullptr : ws.act_bf16)))
+            return rc;
+        if ((rc = dense(m, ws.mlp_act, ws.act_bf16, b.w[T_MLP_W2], b.w2_bf16, ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
+        // depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
+        if ((rc = launch_residual(ctx, l == 0 ? nullptr : feat_in, ws.z, feat_out, rows * (size_t)d,
+                                  l == 0 ? 1.0f : m->residual_scales[l - 1])))
+            return rc;
+        feat_in = feat_out;
+        feat_out = (feat_out == ws.feat_a) ? ws.feat_b : ws.feat_a;
+    }
+    *feats_out = feat_in;
+    return PSSA_B200_OK;
+}
+
+// head for the last row of every non-empty lane (src/pssa.rs:2379-2385, 2438-2440)
+int32_t head_rows(pssa_b200_model* m, const float* feats, size_t n_heads, bool want_greedy) {
+    pssa_b200_ctx* ctx = m->ctx;
+    Workspace& ws = m->ws;
+    int32_t rc;
+    if ((rc = launch_gather_rows(ctx, feats, ws.last_rows, ws.last_feat, n_heads, (int)m->d))) return rc;
+    const float scale = 1.0f / std::sqrt((float)m->d);
+    if (m->precision == PSSA_B200_PRECISION_FP32_EXACT) {
+        if ((rc = launch_gemm_exact(ctx, ws.last_feat, m->unembed, ws.logits, n_heads, m->v, m->d, m->v, EPI_SCALE, scale))) return rc;
+    } else {
+        // the head input is a handful of rows: convert in place of the z staging buffer
+        if ((rc = launch_to_bf16(ctx, ws.last_feat, ws.z_bf16, n_heads * m->d))) return rc;
+        if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, m->unembed_bf16, ws.logits, nullptr, n_heads, m->v, m->d, m->v, EPI_SCALE, scale))) return rc;
+    }
+    if (want_greedy && (rc = launch_greedy(ctx, ws.logits, ws.greedy, n_heads, (int)m->v))) return rc;
+    return PSSA_B200_OK;
+}
+
+// Shared driver: lanes described on the host; processes them in passes of at most max_rows rows.
+int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offsets, const uint32_t* lengths, const uint32_t* streams,
+                  size_t n_lanes, float* logits, uint64_t* greedy, int32_t (*cancelled)(void*), void* cancel_arg, size_t* processed) {
+    pssa_b200_ctx* ctx = m->ctx;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    uint32_t max_len = 0;
+    size_t total = 0;
+    for (size_t l = 0; l < n_lanes; ++l) {
+        max_len = std::max(max_len, lengths[l]);
+        total += lengths[l];
+    }
+    if (processed) *processed = 0;
+    if (total == 0) return PSSA_B200_OK;
+    // window of tokens per lane per pass
+    size_t window = std::max<size_t>(1, m->max_rows / n_lanes);
+    if (window > max_len) window = max_len;
+    std::vector<uint32_t> h_ids, h_off(n_lanes), h_len(n_lanes), h_slot(n_lanes), h_last;
+    int32_t rc;
+    for (size_t t0 = 0; t0 < max_len; t0 += window) {
+        if (cancelled && cancelled(cancel_arg)) return fail(ctx, PSSA_B200_ERR_CANCELLED, "prefill cancelled after %zu tokens", t0);
+        h_ids.clear();
+        size_t rows = 0;
+        for (size_t l = 0; l < n_lanes; ++l) {
+            uint32_t len = lengths[l] > t0 ? (uint32_t)std::min<size_t>(window, lengths[l] - t0) : 0;
+            h_off[l] = (uint32_t)rows, h_len[l] = len, h_slot[l] = streams ? streams[l] : (uint32_t)l;
+            for (uint32_t t = 0; t < len; ++t) h_ids.push_back((uint32_t)ids[offsets[l] + t0 + t]);
+            rows += len;
+        }
+        const bool final_pass = t0 + window >= max_len;
+        // heads: a lane's last token is in this pass iff its length ends inside the window
+        h_last.clear();
+        std::vector<size_t> head_lane;
+        if (logits || greedy)
+            for (size_t l = 0; l < n_lanes; ++l)
+                if (lengths[l] > t0 && lengths[l] <= t0 + window) {
+                    h_last.push_back(h_off[l] + h_len[l] - 1);
+                    head_lane.push_back(l);
+                }
+        if ((rc = ensure_workspace(m, rows, n_lanes))) return rc;
+        Workspace& ws = m->ws;
+        cudaStream_t st = ctx->stream;
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.ids, h_ids.data(), rows * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, h_off.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_len, h_len.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, h_slot.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+        if (!h_last.empty()) PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
+        float* feats = nullptr;
+        if ((rc = forward_rows(m, rows, n_lanes, h_off.data(), h_len.data(), &feats))) return rc;
+        if (!h_last.empty()) {
+            if ((rc = head_rows(m, feats, h_last.size(), greedy != nullptr))) return rc;
+            std::vector<uint32_t> g(h_last.size());
+            if (greedy) PSSA_CUDA(ctx, cudaMemcpyAsync(g.data(), ws.greedy, g.size() * 4, cudaMemcpyDeviceToHost, st));
+            if (logits) {
+                // contiguous runs of lanes are copied in one transfer
+                size_t i = 0;
+                while (i < head_lane.size()) {
+                    size_t j = i;
+                    while (j + 1 < head_lane.size() && head_lane[j + 1] == head_lane[j] + 1) ++j;
+                    PSSA_CUDA(ctx, cudaMemcpyAsync(logits + head_lane[i] * m->v, ws.logits + i * m->v, (j - i + 1) * m->v * 4,
+                                                   cudaMemcpyDeviceToHost, st));
+                    i = j + 1;
+                }
+            }
+            PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+            if (greedy)
+                for (size_t i = 0; i < head_lane.size(); ++i) {
+                    if (g[i] == 0xffffffffu) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "model emitted non-finite logits");
+                    greedy[head_lane[i]] = g[i];
+                }
+        } else if (final_pass || cancelled) {
+            PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+        }
+        if (processed) *processed = std::min<size_t>(max_len, t0 + window);
+    }
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PSSA_B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t pssa_b200_model_prefill_batch(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offsets, const uint32_t* lengths,
+                                      const uint32_t* streams, size_t n_lanes, float* logits, uint64_t* greedy) {
+    if (!m || !ids || !offsets || !lengths) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "prefill_batch: null argument");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (n_lanes == 0 || n_lanes > 0x7fffffff) return fail(ctx, PSSA_B200_ERR_SHAPE, "prefill_batch: lane count must be in 1..2^31-1");
+    // validate every lane before any work (src/sequence_batch.rs:250-273)
+    std::vector<bool> seen(m->max_streams, false);
+    for (size_t l = 0; l < n_lanes; ++l) {
+        uint32_t slot = streams ? streams[l] : (uint32_t)l;
+        if (slot >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "lane %zu uses stream %u outside %u streams", l, slot, m->max_streams);
+        if (seen[slot]) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u appears in more than one lane", slot);
+        seen[slot] = true;
+        for (uint32_t t = 0; t < lengths[l]; ++t) {
+            uint64_t id = ids[(size_t)offsets[l] + t];
+            if (id >= m->v) return fail(ctx, PSSA_B200_ERR_TOKEN, "prompt ID %llu outside model vocabulary", (unsigned long long)id);
+        }
+    }
+    return run_lanes(m, ids, offsets, lengths, streams, n_lanes, logits, greedy, nullptr, nullptr, nullptr);
+}
+
+int32_t pssa_b200_model_prefill(pssa_b200_model* m, uint32_t stream, const uint64_t* ids, size_t n, float* logits, size_t* processed,
+                                int32_t (*cancelled)(void*), void* cancel_arg) {
+    if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (processed) *processed = 0;
+    if (n == 0 || !ids) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "prefill requires at least one token");  // src/pssa.rs:2405-2407
+    if (stream >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u outside %u streams", stream, m->max_streams);
+    if (n > 0xffffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "prefill: %zu tokens exceed the u32 row index", n);
+    size_t valid = 0;
+    while (valid < n && ids[valid] < m->v) ++valid;
+    uint32_t off = 0, len = (uint32_t)valid;
+    int32_t rc = PSSA_B200_OK;
+    size_t done = 0;
+    if (valid > 0) rc = run_lanes(m, ids, &off, &len, &stream, 1, valid == n ? logits : nullptr, nullptr, cancelled, cancel_arg, &done);
+    if (processed) *processed = done;
+    if (rc != PSSA_B200_OK) return rc;
+    if (valid < n)  // the valid prefix has advanced the carry; logits untouched (src/pssa.rs:2414-2416)
+        return fail(ctx, PSSA_B200_ERR_TOKEN, "prompt ID %llu outside model vocabulary", (unsigned long long)ids[valid]);
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_model_decode_step(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n, float* logits,
+                                    uint64_t* greedy) {
+    if (!m || !ids) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "decode_step: null argument");
+    if (n == 0 || n > 0x7fffffff) return fail(m->ctx, PSSA_B200_ERR_SHAPE, "decode_step: stream count must be in 1..2^31-1");
+    std::vector<uint32_t> off(n), len(n, 1);
+    for (size_t i = 0; i < n; ++i) off[i] = (uint32_t)i;
+    return pssa_b200_model_prefill_batch(m, ids, off.data(), len.data(), streams, n, logits, greedy);
+}
+
+}  // extern "C"

@@ -48,7 +48,7 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
     if (tid < QT) {
         const size_t q = q0 + tid;
         if (q < p.rows) {
-            const float* src = p.q + q * dk;
+            const float* src = p.q + q * (p.ldq ? p.ldq : (size_t)dk);
             float* dst = p.q_pnc ? p.q_pnc + q * dk : nullptr;
             float qs;
             if (p.q_is_euclidean) {
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
                 double n2 = 0.0;
                 for (int i = 0; i < dk; ++i) {
                     float pv = src[i];
-                    if (dst && dst != src) dst[i] = pv;
+                    if (dst) dst[i] = pv;
                     double pd = (double)pv;
                     Ps[(size_t)i * QT + tid] = pd;
                     n2 = __dadd_rn(n2, __dmul_rn(pd, pd));

@@ -76,6 +76,10 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
     const int d = p.d, s = p.s;
     const size_t ds = (size_t)d * s;
     const int j0 = g * ST;
+    const size_t ldd = p.ld_delta ? p.ld_delta : (size_t)d;
+    const size_t ldbc = p.ld_bc ? p.ld_bc : (size_t)s;
+    float* carry = p.carry ? p.carry + (size_t)(p.lane_slots ? p.lane_slots[lane] : lane) * (p.carry_stride ? p.carry_stride : ds)
+                           : nullptr;
 
     float A[ST], h[ST];
 #pragma unroll
@@ -83,7 +87,7 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
         bool ok = valid && (j0 + jj) < s;
         float rate = ok ? __ldg(p.rates + (size_t)i * s + j0 + jj) : 0.0f;
         A[jj] = EXACT ? rate : rate * 1.4426950408889634f;
-        h[jj] = (ok && p.carry) ? p.carry[lane * ds + (size_t)i * s + j0 + jj] : 0.0f;
+        h[jj] = (ok && carry) ? carry[(size_t)i * s + j0 + jj] : 0.0f;
     }
 
     const int ntiles = (len + kTileTokens - 1) / kTileTokens;
@@ -104,7 +108,7 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
                     int col = i0 + q * 4;
                     size_t gro = (row0 + t0 + tt) * (size_t)d + col;
                     if (CH >= 4 && col < d) {
-                        cp_async16(dd + tt * CH + q * 4, p.delta + gro);
+                        cp_async16(dd + tt * CH + q * 4, p.delta + (row0 + t0 + tt) * ldd + col);
                         cp_async16(dx + tt * CH + q * 4, p.x_norm + gro);
                     } else if (CH >= 4) {
                         *reinterpret_cast<float4*>(dd + tt * CH + q * 4) = make_float4(0, 0, 0, 0);
@@ -116,7 +120,7 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
                     int tt = idx / SQ, q = idx % SQ;
                     int j = q * 4;
                     int dst = tt * SP + (j / ST) * SG + j % ST;
-                    size_t gro = (row0 + t0 + tt) * (size_t)s + j;
+                    size_t gro = (row0 + t0 + tt) * ldbc + j;
                     if (j < s) {
                         cp_async16(db + dst, p.b_proj + gro);
                         cp_async16(dc + dst, p.c_proj + gro);
@@ -130,13 +134,13 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
                     int tt = idx / CH, q = idx % CH;
                     int col = i0 + q;
                     size_t gro = (row0 + t0 + tt) * (size_t)d + col;
-                    dd[tt * CH + q] = col < d ? __ldg(p.delta + gro) : 0.0f;
+                    dd[tt * CH + q] = col < d ? __ldg(p.delta + (row0 + t0 + tt) * ldd + col) : 0.0f;
                     dx[tt * CH + q] = col < d ? __ldg(p.x_norm + gro) : 0.0f;
                 }
                 for (int idx = tid; idx < nt * ST * G; idx += kThreads) {
                     int tt = idx / (ST * G), j = idx % (ST * G);
                     int dst = tt * SP + (j / ST) * SG + j % ST;
-                    size_t gro = (row0 + t0 + tt) * (size_t)s + j;
+                    size_t gro = (row0 + t0 + tt) * ldbc + j;
                     db[dst] = j < s ? __ldg(p.b_proj + gro) : 0.0f;
                     dc[dst] = j < s ? __ldg(p.c_proj + gro) : 0.0f;
                 }
@@ -211,10 +215,10 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
         __syncthreads();
     }
     cp_async_wait<0>();
-    if (p.carry) {
+    if (carry && len > 0) {
 #pragma unroll
         for (int jj = 0; jj < ST; ++jj)
-            if (valid && j0 + jj < s) p.carry[lane * ds + (size_t)i * s + j0 + jj] = h[jj];
+            if (valid && j0 + jj < s) carry[(size_t)i * s + j0 + jj] = h[jj];
     }
 }
 

@@ -183,6 +183,35 @@ class B200Dispatch:
             N.MEM_EXACT if exact else 0))
 
 
+    # ---- dense product
+    def dispatch_gemm_into(self, x, w, m, n, k, batch, out, epilogue=N.EPI_NONE, alpha=1.0, precision=N.PRECISION_FP32_EXACT):
+        """`GpuDispatch::dispatch_gemm_into` (src/backend.rs:1087-1110): Y[batch,M,N] = X[batch,M,K] * W[N,K]^T on host
+        arrays. Lengths are validated before anything runs and `out` is left untouched on failure
+        (src/backend.rs:11-38, tests/backend.rs:66-82)."""
+        if 0 in (m, n, k, batch):
+            raise N.B200Error(N.ERR_SHAPE, "GEMM dimensions must be positive")
+        for name, arr in (("x", x), ("w", w), ("out", out)):
+            _host(arr, name)
+        if x.size != batch * m * k or w.size != n * k:
+            raise N.B200Error(N.ERR_SHAPE, f"GEMM operand lengths must be {batch * m * k} and {n * k}, got {x.size} and {w.size}")
+        if out.size != batch * m * n:
+            raise N.B200Error(N.ERR_SHAPE, "GEMM output length mismatch")
+        self._check(self._lib.pssa_b200_gemm_xwt(self._h, _ptr(x), _ptr(w), m, n, k, batch, _ptr(out), epilogue, alpha,
+                                                 precision))
+
+    def dispatch_gemm(self, x, w, m, n, k, batch, **kw):  # src/backend.rs:1031-1046
+        out = np.empty(batch * m * n, np.float32)
+        self.dispatch_gemm_into(x, w, m, n, k, batch, out, **kw)
+        return out
+
+    def gemm_xwt_dev(self, x, w, rows, n, k, out, ldo=None, epilogue=N.EPI_NONE, alpha=1.0, precision=N.PRECISION_BF16):
+        self._check(self._lib.pssa_b200_gemm_xwt_dev(self._h, _ptr(x), _ptr(w), rows, n, k, _ptr(out), ldo or n, epilogue,
+                                                     alpha, precision))
+
+    def poll_status(self):
+        self._check(self._lib.pssa_b200_ctx_poll_status(self._h))
+
+
 class Device:
     """`Device` of src/backend.rs:1012-1018 reduced to the arm this package adds."""
 

@@ -1,0 +1,162 @@
+"""Host-side mirror of the reference's model-level inference API (`PSSALayerV2`, src/pssa.rs:2245-2442) on top of
+the C ABI's device-resident model. Weights, banks and carries live on the GPU; token ids go in, logits come out."""
+import ctypes as C
+
+import numpy as np
+
+from . import _native as N
+from .dispatch import B200Dispatch, _ptr
+
+# tensor ids of include/pssa_b200.h
+EMBED, UNEMBED, NORM_GAMMA, NORM_BETA, A_MAT, W_DELTA, W_B, W_C, W_QX, W_QH, W_GATE, W_PROJ, MLP_W1, MLP_W2, AD_DOWN, \
+    AD_UP, AD_CONS = range(17)
+RESIDUAL_SCALES = 22
+BLOCK_TENSORS = (NORM_GAMMA, NORM_BETA, A_MAT, W_DELTA, W_B, W_C, W_QX, W_QH, W_GATE, W_PROJ, MLP_W1, MLP_W2, AD_DOWN,
+                 AD_UP, AD_CONS)
+
+
+class PSSAModel:
+    """One model on one B200. `streams` independent recurrent carries (lanes) share the weights and banks."""
+
+    def __init__(self, gpu: B200Dispatch, depth, d_vocab, d_latent, d_state, d_mem_key, mem_capacity, tau_mem=0.1,
+                 streams=1, precision=N.PRECISION_BF16):
+        self.gpu = gpu
+        self._lib = gpu._lib
+        self.depth, self.d_vocab, self.d_latent, self.d_state = depth, d_vocab, d_latent, d_state
+        self.d_mem_key, self.mem_capacity, self.tau_mem, self.streams = d_mem_key, mem_capacity, tau_mem, streams
+        cfg = N.Config(depth, d_vocab, d_latent, d_state, d_mem_key, mem_capacity, tau_mem, 0)
+        h = C.c_void_p()
+        gpu._check(self._lib.pssa_b200_model_create(gpu._h, C.byref(cfg), streams, C.byref(h)))
+        self._h = h
+        self.set_precision(precision)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.pssa_b200_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- upload
+    def set_tensor(self, layer: int, tensor: int, data):
+        a = np.ascontiguousarray(data, np.float32).ravel()
+        self.gpu._check(self._lib.pssa_b200_model_set_tensor(self._h, layer, tensor, _ptr(a), a.size))
+
+    def set_bank(self, layer, keys, norm_sq, values, count, write_head=0, confidence=None, last_seen_step=None):
+        keys = np.ascontiguousarray(keys, np.float32)
+        norm_sq = np.ascontiguousarray(norm_sq, np.float32)
+        values = np.ascontiguousarray(values, np.float32)
+        if keys.size != self.mem_capacity * self.d_mem_key or values.size != self.mem_capacity * self.d_latent or \
+                norm_sq.size != self.mem_capacity:
+            raise N.B200Error(N.ERR_SHAPE, "memory bank arrays do not match the configured capacity and widths")
+        conf = None if confidence is None else np.ascontiguousarray(confidence, np.float32)
+        seen = None if last_seen_step is None else np.ascontiguousarray(last_seen_step, np.uint64)
+        self.gpu._check(self._lib.pssa_b200_model_set_bank(self._h, layer, _ptr(keys), _ptr(norm_sq), _ptr(values), count,
+                                                           write_head, _ptr(conf), _ptr(seen)))
+
+    # ---- runtime options (src/pssa.rs:2080-2243)
+    def set_memory_top_k(self, top_k):
+        if top_k == 0:
+            raise N.B200Error(N.ERR_INVALID_ARGUMENT, "memory top-k must be positive")
+        self.gpu._check(self._lib.pssa_b200_model_set_top_k(self._h, top_k or 0))
+
+    def set_precision(self, precision):
+        self.gpu._check(self._lib.pssa_b200_model_set_precision(self._h, precision))
+
+    def set_local_conv(self, enabled):
+        self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 0, int(enabled)))
+
+    def set_ssm_skip(self, enabled):
+        self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 1, int(enabled)))
+
+    def set_hybrid_read(self, enabled, lam=1.0):
+        if not (np.isfinite(lam) and 0.0 < lam <= 1.0):
+            raise N.B200Error(N.ERR_INVALID_ARGUMENT, "hybrid decay lam must be in (0.0, 1.0]")
+        self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 2, int(enabled)))
+
+    def grow_memory(self, capacity):
+        self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 3, int(capacity)))
+
+    def set_loops(self, loops):
+        if not 1 <= loops <= 32:
+            raise N.B200Error(N.ERR_INVALID_ARGUMENT, "--loops must be between 1 and 32; use --loops 1 for the original model")
+        self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 4, int(loops)))
+
+    def set_max_rows(self, rows):
+        self.gpu._check(self._lib.pssa_b200_model_set_max_rows(self._h, rows))
+
+    # ---- recurrent state (src/pssa.rs:2245-2310)
+    def recurrent_state_len(self):
+        return self.depth * self.d_latent * self.d_state
+
+    def reset_recurrent_state(self, stream=None):
+        for s in (range(self.streams) if stream is None else [stream]):
+            self.gpu._check(self._lib.pssa_b200_model_reset_state(self._h, s))
+
+    def copy_recurrent_state_to(self, stream=0):
+        out = np.empty(self.recurrent_state_len(), np.float32)
+        self.gpu._check(self._lib.pssa_b200_model_get_state(self._h, stream, _ptr(out), out.size))
+        return out
+
+    def copy_recurrent_state_from(self, state, stream=0):
+        a = np.ascontiguousarray(state, np.float32)
+        self.gpu._check(self._lib.pssa_b200_model_set_state(self._h, stream, _ptr(a), a.size))
+
+    # ---- forward
+    def forward_inference(self, x_id: int, stream=0):
+        """`forward_inference` (src/pssa.rs:2387-2391): one token, returns logits [V]. A bad id raises, as the
+        reference panics (src/pssa.rs:2317)."""
+        return self.decode_step([x_id], [stream])[0]
+
+    def prefill_inference(self, token_ids, want_logits=True, cancelled=None, stream=0):
+        """`prefill_inference` (src/pssa.rs:2399-2442). Returns (completed, logits or None). Raises B200Error for an
+        empty prompt or an id outside the vocabulary (after the valid prefix has advanced the carry)."""
+        ids = np.ascontiguousarray(token_ids, np.uint64)
+        logits = np.empty(self.d_vocab, np.float32) if want_logits else None
+        done = C.c_size_t()
+        cb = N.CANCEL_FN(lambda _arg: 1 if cancelled() else 0) if cancelled else None
+        rc = self._lib.pssa_b200_model_prefill(self._h, stream, _ptr(ids) if ids.size else None, ids.size, _ptr(logits),
+                                               C.byref(done), cb, None)
+        self.processed = int(done.value)
+        if rc == N.ERR_CANCELLED:
+            return False, None
+        self.gpu._check(rc)
+        return True, logits
+
+    def prefill_batch(self, lanes, streams=None, want_logits=True, want_greedy=False):
+        """Independent sequences (`SequenceBatch::forward`, src/sequence_batch.rs:233-384): `lanes` is a list of id
+        sequences; lane l continues stream streams[l] (default l). Returns (logits [n, V] or None, greedy ids or None)."""
+        lengths = np.array([len(x) for x in lanes], np.uint32)
+        offsets = np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.uint32)
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(x, np.uint64) for x in lanes]) if lengths.sum() else
+                                   np.zeros(1, np.uint64), np.uint64)
+        st = None if streams is None else np.ascontiguousarray(streams, np.uint32)
+        logits = np.zeros((len(lanes), self.d_vocab), np.float32) if want_logits else None
+        greedy = np.zeros(len(lanes), np.uint64) if want_greedy else None
+        self.gpu._check(self._lib.pssa_b200_model_prefill_batch(self._h, _ptr(ids), _ptr(offsets), _ptr(lengths), _ptr(st),
+                                                                len(lanes), _ptr(logits), _ptr(greedy)))
+        return logits, greedy
+
+    def decode_step(self, ids, streams=None, want_logits=True, want_greedy=False):
+        ids = np.ascontiguousarray(ids, np.uint64)
+        st = None if streams is None else np.ascontiguousarray(streams, np.uint32)
+        logits = np.empty((ids.size, self.d_vocab), np.float32) if want_logits else None
+        greedy = np.empty(ids.size, np.uint64) if want_greedy else None
+        self.gpu._check(self._lib.pssa_b200_model_decode_step(self._h, _ptr(st), _ptr(ids), ids.size, _ptr(logits),
+                                                              _ptr(greedy)))
+        if want_logits and want_greedy:
+            return logits, greedy
+        return logits if want_logits else greedy
+
+    def generate_greedy(self, prompt_ids, n_new, stream=0):
+        """Prefill + greedy decode (src/inference.rs:348-418 at temperature 0): returns the generated ids."""
+        _, g = self.prefill_batch([prompt_ids], [stream], want_logits=False, want_greedy=True)
+        out = [int(g[0])]
+        for _ in range(n_new - 1):
+            g = self.decode_step([out[-1]], [stream], want_logits=False, want_greedy=True)
+            out.append(int(g[0]))
+        return np.array(out, np.uint64)

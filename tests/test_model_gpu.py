@@ -1,0 +1,158 @@
+"""End-to-end parity of prefill and decode with the CPU oracle, through the C ABI's device-resident model."""
+import numpy as np
+import pytest
+
+import oracle as O
+from helpers import fill_synthetic, upload
+from parity import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    import pssa_b200
+    d = pssa_b200.B200Dispatch(0)
+    yield d
+    d.close()
+
+
+def make_pair(gpu, depth, v, d, s, k, cap, seed, streams=1, bank_fill=1.0, precision=1, tau=0.1):
+    import pssa_b200
+    om = O.Model.new(depth, v, d, s, k, cap, tau_mem=tau, seed=seed)
+    fill_synthetic(om, seed, bank_fill)
+    gm = pssa_b200.PSSAModel(gpu, depth, v, d, s, k, cap, tau_mem=tau, streams=streams, precision=precision)
+    upload(om, gm)
+    return om, gm
+
+
+def test_golden_fixture_logits_through_the_gpu_model(gpu, golden_dir):
+    """The reference's own golden rows (tests/depth_one_parity.rs, AVX2 set words [1,22)) on the GPU path in fp32."""
+    import pssa_b200
+    om = O.Model.load((golden_dir / "depth_one_main85d9d33_initial.pssa").read_bytes())
+    obs = np.frombuffer((golden_dir / "depth_one_main014f617_avx2_observed.bin").read_bytes(), np.uint32)[1:22]
+    want = obs.view(np.float32).reshape(3, 7)
+    gm = pssa_b200.PSSAModel(gpu, 1, 7, 4, 2, 2, 3, tau_mem=om.tau_mem, precision=1)
+    upload(om, gm)
+    rows = [gm.forward_inference(t) for t in (1, 2, 1)]
+    assert rel_err(np.stack(rows), want) <= 1e-5
+
+
+@pytest.mark.parametrize("depth,v,d,s,k,cap,n", [(1, 50, 16, 4, 4, 8, 5), (2, 97, 32, 16, 8, 16, 40), (1, 300, 192, 64, 64, 64, 70),
+                                                 (3, 64, 40, 8, 12, 10, 33), (4, 128, 64, 64, 32, 32, 17)])
+def test_fp32_prefill_and_token_loop_match_the_oracle(gpu, depth, v, d, s, k, cap, n):
+    om, gm = make_pair(gpu, depth, v, d, s, k, cap, seed=depth * 100 + d)
+    ids = (np.arange(n) * 7 + 3) % v
+    ok, logits = gm.prefill_inference(ids)
+    rc, done, ref = om.prefill_inference(ids)
+    assert ok and rc == 1 and gm.processed == n
+    assert rel_err(logits, ref) <= 1e-5, "last-token logits"
+    st = gm.copy_recurrent_state_to()
+    assert np.max(np.abs(st - om.state())) <= 1e-5 * max(1.0, np.abs(om.state()).max())
+    # decode continues from the prefilled carry; greedy tokens agree
+    tok = int(np.argmax(ref[1:]) + 1)
+    for _ in range(6):
+        lg, gr = gm.decode_step([tok], [0], want_greedy=True)
+        ref = om.forward_inference(tok)
+        assert rel_err(lg[0], ref) <= 2e-5
+        nxt = int(O.lib().pssa_oracle_greedy(O.fptr(ref), v))
+        assert int(gr[0]) == nxt
+        tok = nxt
+
+
+def test_prefill_equals_token_loop_on_the_gpu(gpu):
+    # src/inference.rs:1069-1113: prefill == decode loop, with a non-reset carry
+    om, gm = make_pair(gpu, 2, 61, 32, 8, 8, 12, seed=9, streams=2)
+    ids = (np.arange(67) * 5 + 1) % 61
+    gm.copy_recurrent_state_from(om.state(), 1)
+    _, a = gm.prefill_inference(ids, stream=0)
+    for t in ids:
+        b = gm.forward_inference(int(t), stream=1)
+    assert rel_err(a, b) <= 1e-6
+    assert np.max(np.abs(gm.copy_recurrent_state_to(0) - gm.copy_recurrent_state_to(1))) <= 1e-6
+
+
+def test_independent_lanes_ragged_with_partial_bank_and_top_k(gpu):
+    om, gm = make_pair(gpu, 2, 80, 48, 16, 16, 20, seed=4, streams=4, bank_fill=0.6)
+    lanes = [list((np.arange(n) * 3 + j) % 80) for j, n in enumerate([9, 0, 31, 1])]
+    for top_k in (None, 3):
+        if top_k:
+            gm.set_memory_top_k(top_k)
+            for l in range(2):
+                c, h, _ = om.bank_meta(l)
+                om.set_bank_meta(l, c, h, top_k)
+        gm.reset_recurrent_state()
+        logits, greedy = gm.prefill_batch(lanes, want_greedy=True)
+        for j, lane in enumerate(lanes):
+            if not lane:
+                assert not logits[j].any()
+                continue
+            ref_m = om.clone()
+            ref_m.reset_recurrent_state()
+            _, _, ref = ref_m.prefill_inference(lane)
+            assert rel_err(logits[j], ref) <= 2e-5, (top_k, j)
+            assert int(greedy[j]) == int(O.lib().pssa_oracle_greedy(O.fptr(ref), 80))
+            assert np.max(np.abs(gm.copy_recurrent_state_to(j) - ref_m.state())) <= 1e-5
+
+
+def test_passes_split_long_prompts_without_changing_results(gpu):
+    om, gm = make_pair(gpu, 2, 40, 24, 8, 8, 8, seed=2, streams=2)
+    ids = (np.arange(100) * 11) % 40
+    _, a = gm.prefill_inference(ids, stream=0)
+    gm.set_max_rows(16)
+    _, b = gm.prefill_inference(ids, stream=1)
+    gm.set_max_rows(65536)
+    assert np.array_equal(a, b)
+    assert np.array_equal(gm.copy_recurrent_state_to(0), gm.copy_recurrent_state_to(1))
+
+
+def test_error_semantics_follow_the_reference(gpu):
+    import pssa_b200
+    om, gm = make_pair(gpu, 1, 30, 16, 4, 4, 4, seed=3)
+    with pytest.raises(pssa_b200.B200Error, match="at least one token"):  # src/pssa.rs:2405-2407
+        gm.prefill_inference([])
+    before = gm.copy_recurrent_state_to()
+    with pytest.raises(pssa_b200.B200Error, match="prompt ID 99 outside model vocabulary") as e:
+        gm.prefill_inference([3, 4, 99, 5])
+    assert e.value.status == 7 and gm.processed == 2
+    ref = om.clone()
+    ref.prefill_inference([3, 4], want_logits=False)
+    assert np.max(np.abs(gm.copy_recurrent_state_to() - ref.state())) <= 1e-6 and not np.array_equal(before, ref.state())
+    calls = []
+    gm.set_max_rows(4)
+    done, lg = gm.prefill_inference(np.arange(12) % 30, cancelled=lambda: len(calls) >= 2 or calls.append(1))
+    gm.set_max_rows(65536)
+    assert done is False and lg is None and gm.processed == 8  # two passes of 4 ran before the third poll cancelled
+    for fn, msg in ((lambda: gm.set_local_conv(True), "local mixing experiments require CPU"),
+                    (lambda: gm.set_hybrid_read(True, 0.5), "hybrid read currently requires the CPU backend"),
+                    (lambda: gm.grow_memory(64), "grow memory on the CPU checkpoint"),
+                    (lambda: gm.set_memory_top_k(0), "memory top-k must be positive")):
+        with pytest.raises(pssa_b200.B200Error, match=msg):
+            fn()
+    with pytest.raises(pssa_b200.B200Error, match="outside model vocabulary"):
+        gm.forward_inference(30)
+
+
+def test_bf16_path_logits_within_tolerance_and_greedy_tokens(gpu):
+    """bf16 projections, fp32 scan and retrieval: logits within 2e-2 max-abs of the fp32 CPU reference; greedy
+    tokens identical wherever the reference's top-1/top-2 gap exceeds twice the observed error."""
+    om, gm = make_pair(gpu, 2, 512, 192, 64, 64, 64, seed=21, precision=0)
+    ids = (np.arange(96) * 37 + 5) % 512
+    ok, logits = gm.prefill_inference(ids)
+    _, _, ref = om.prefill_inference(ids)
+    err = float(np.max(np.abs(logits - ref)))
+    assert err <= 2e-2, err
+    tok = int(O.lib().pssa_oracle_greedy(O.fptr(ref), 512))
+    agree = total = 0
+    for _ in range(24):
+        lg, gr = gm.decode_step([tok], [0], want_greedy=True)
+        ref = om.forward_inference(tok)
+        e = float(np.max(np.abs(lg[0] - ref)))
+        assert e <= 2e-2
+        order = np.sort(ref[1:])
+        nxt = int(O.lib().pssa_oracle_greedy(O.fptr(ref), 512))
+        if order[-1] - order[-2] > 2 * e:
+            total += 1
+            agree += int(gr[0]) == nxt
+        tok = nxt
+    assert agree == total
