@@ -41,3 +41,11 @@ def worst(x, y):
     e = rel_elems(x, y)
     idx = np.unravel_index(int(np.argmax(e)), e.shape)
     return float(e[idx]), tuple(int(i) for i in idx)
+
+
+def scale_err(x, y) -> float:
+    """max |x-y| / max |y|: the bar for vectors whose entries are dot products (logits, features): an entry that
+    happens to cancel to ~0 carries the absolute roundoff of its terms, so it is measured against the vector."""
+    x = np.asarray(x, np.float64)
+    y = np.asarray(y, np.float64)
+    return float(np.max(np.abs(x - y)) / max(1e-30, np.max(np.abs(y)))) if x.size else 0.0

@@ -4,7 +4,7 @@ import pytest
 
 import oracle as O
 from helpers import fill_synthetic, upload
-from parity import rel_err
+from parity import rel_err, scale_err
 
 pytestmark = pytest.mark.gpu
 
@@ -35,7 +35,7 @@ def test_golden_fixture_logits_through_the_gpu_model(gpu, golden_dir):
     gm = pssa_b200.PSSAModel(gpu, 1, 7, 4, 2, 2, 3, tau_mem=om.tau_mem, precision=1)
     upload(om, gm)
     rows = [gm.forward_inference(t) for t in (1, 2, 1)]
-    assert rel_err(np.stack(rows), want) <= 1e-5
+    assert scale_err(np.stack(rows), want) <= 1e-5 and rel_err(np.stack(rows), want) <= 1e-4
 
 
 @pytest.mark.parametrize("depth,v,d,s,k,cap,n", [(1, 50, 16, 4, 4, 8, 5), (2, 97, 32, 16, 8, 16, 40), (1, 300, 192, 64, 64, 64, 70),
@@ -46,7 +46,7 @@ def test_fp32_prefill_and_token_loop_match_the_oracle(gpu, depth, v, d, s, k, ca
     ok, logits = gm.prefill_inference(ids)
     rc, done, ref = om.prefill_inference(ids)
     assert ok and rc == 1 and gm.processed == n
-    assert rel_err(logits, ref) <= 1e-5, "last-token logits"
+    assert scale_err(logits, ref) <= 1e-5, "last-token logits"
     st = gm.copy_recurrent_state_to()
     assert np.max(np.abs(st - om.state())) <= 1e-5 * max(1.0, np.abs(om.state()).max())
     # decode continues from the prefilled carry; greedy tokens agree
@@ -54,7 +54,7 @@ def test_fp32_prefill_and_token_loop_match_the_oracle(gpu, depth, v, d, s, k, ca
     for _ in range(6):
         lg, gr = gm.decode_step([tok], [0], want_greedy=True)
         ref = om.forward_inference(tok)
-        assert rel_err(lg[0], ref) <= 2e-5
+        assert scale_err(lg[0], ref) <= 1e-5
         nxt = int(O.lib().pssa_oracle_greedy(O.fptr(ref), v))
         assert int(gr[0]) == nxt
         tok = nxt
@@ -68,7 +68,7 @@ def test_prefill_equals_token_loop_on_the_gpu(gpu):
     _, a = gm.prefill_inference(ids, stream=0)
     for t in ids:
         b = gm.forward_inference(int(t), stream=1)
-    assert rel_err(a, b) <= 1e-6
+    assert scale_err(a, b) <= 1e-6
     assert np.max(np.abs(gm.copy_recurrent_state_to(0) - gm.copy_recurrent_state_to(1))) <= 1e-6
 
 
@@ -90,7 +90,7 @@ def test_independent_lanes_ragged_with_partial_bank_and_top_k(gpu):
             ref_m = om.clone()
             ref_m.reset_recurrent_state()
             _, _, ref = ref_m.prefill_inference(lane)
-            assert rel_err(logits[j], ref) <= 2e-5, (top_k, j)
+            assert scale_err(logits[j], ref) <= 1e-5, (top_k, j)
             assert int(greedy[j]) == int(O.lib().pssa_oracle_greedy(O.fptr(ref), 80))
             assert np.max(np.abs(gm.copy_recurrent_state_to(j) - ref_m.state())) <= 1e-5
 
