@@ -98,6 +98,27 @@ int32_t pssa_b200_scan_states_dev(pssa_b200_ctx* ctx, const float* a, const floa
 int32_t pssa_b200_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0,
                               float* h, float* h_last, size_t lanes, size_t len, size_t stride);
 
+/*
+ * Allocation-free form of pssa_b200_scan_states_dev. It has no counterpart in the reference.
+ *
+ * Who needs it: a host process that must not see this library allocate device memory once it is running --
+ * for example a serving process whose own allocator took the whole GPU at start-up, or a loop that cannot
+ * afford the device-wide synchronisation that cudaMalloc / cudaFree imply. The scan splits time into `chunks`
+ * (>= 1) pieces; the per-chunk maps and carries, which the other entry point keeps in the context's growable
+ * arena, live here in a fixed 12 MiB array compiled into the library (held by every GPU that loads the
+ * library, until the process exits). Limit: lanes * chunks * stride <= 1,048,576 when chunks > 1; a larger
+ * request fails with PSSA_B200_ERR_SHAPE and launches nothing. The call never calls cudaMalloc, cudaFree or
+ * any allocating routine; inputs and outputs are the caller's (DEVICE pointers, as for the _dev form).
+ *
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device);
+ * make that first call outside any stream capture. All calls on a device share the one array: a call only
+ * reads scratch it has itself written, so nothing needs clearing between calls, but two calls whose kernels
+ * overlap on the GPU (different streams or contexts of one process) race on it -- serialise them.
+ */
+int32_t pssa_b200_scan_states_noalloc_dev(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0,
+                                          float* h, float* h_last, size_t lanes, size_t len, size_t stride,
+                                          uint32_t chunks);
+
 /* ------------------------------------------------------------------ fused SSM stage */
 
 /* Arithmetic mode of the SSM stage. Default (0): ex2.approx on delta*(A*log2 e) -- the recipe of the

@@ -29,6 +29,7 @@ SIGNATURES = {
     "pssa_b200_affine_scan": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz]),
     "pssa_b200_scan_states_dev": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
     "pssa_b200_scan_states": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz]),
+    "pssa_b200_scan_states_noalloc_dev": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, C.c_uint32]),
     "pssa_b200_ssm_forward_dev": (C.c_int32, [_vp] * 11 + [_vp, _vp, _sz, _sz, _sz, _sz, C.c_uint32]),
     "pssa_b200_ssm_forward": (C.c_int32, [_vp] * 7 + [_sz, _sz, _sz] + [_vp] * 4 + [C.c_uint32]),
     "pssa_b200_memory_read_dev": (C.c_int32, [_vp, _vp, C.c_int32, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _sz,

@@ -210,6 +210,18 @@ int32_t pssa_b200_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_scan_states_noalloc_dev(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0, float* h,
+                                          float* h_last, size_t lanes, size_t len, size_t stride, uint32_t chunks) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    size_t elems;
+    int32_t rc = scan_shape(ctx, lanes, len, stride, &elems);
+    if (rc != PSSA_B200_OK) return rc;
+    if (!a || !b || !h) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 scan states: null buffer");
+    if (chunks == 0) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 static scan: chunks must be at least 1");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    return launch_scan_states_static(ctx, a, b, h0, h, h_last, lanes, len, stride, chunks);
+}
+
 // ------------------------------------------------------------------ fused SSM stage
 
 

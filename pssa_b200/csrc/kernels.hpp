@@ -13,6 +13,10 @@ int32_t launch_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b, c
 int32_t launch_scan_maps(pssa_b200_ctx* ctx, float* scan_a, float* scan_b, size_t lanes, size_t len, size_t stride,
                          int forced_chunks);
 
+// allocation-free variant of launch_scan_states: chunk scratch in a fixed __device__ array (scan_affine.cu)
+int32_t launch_scan_states_static(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0, float* h, float* h_last,
+                                  size_t lanes, size_t len, size_t stride, unsigned chunks);
+
 // ssm_fused.cu
 struct SsmParams {
     const float* delta;    // [rows, d]  softplus already applied

@@ -290,6 +290,89 @@ int32_t launch_scan_states(pssa_b200_ctx* ctx, const float* a, const float* b, c
     return run_scan<1, false>(ctx, a, b, h0, nullptr, h, h_last, lanes, len, stride, forced_chunks);
 }
 
+// ------------------------------------------------------------------ allocation-free variant
+//
+// Some hosts cannot let this library allocate device memory while they run: an inference server that
+// has handed the whole GPU to its own pool at start-up, or a latency-critical loop in which the
+// device-wide synchronisation hidden inside cudaMalloc / cudaFree is not acceptable. For them the
+// chunk maps and carries of the multi-chunk scan live in the fixed array below instead of the
+// context's growable arena. It is part of the module image, so every GPU that loads this library
+// holds these 12 MiB until the process exits.
+constexpr size_t kStaticScanFloats = size_t(3) << 20;  // 3 arrays (chunk A, chunk B, carry) x 2^20 floats
+static __device__ __align__(256) float g_scan_static_scratch[kStaticScanFloats];
+
+// In host code `g_scan_static_scratch` is only a handle for the runtime, not a device address; the address
+// a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+static float* static_scratch_for_current_device(pssa_b200_ctx* ctx, int32_t* rc) {
+    constexpr int kMaxDevices = 64;
+    static float* cached[kMaxDevices] = {};
+    *rc = PSSA_B200_OK;
+    if (ctx->device < 0 || ctx->device >= kMaxDevices) {
+        *rc = fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "static scan scratch: device ordinal %d is outside 0..%d", ctx->device, kMaxDevices - 1);
+        return nullptr;
+    }
+    if (cached[ctx->device] == nullptr) {
+        float* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_scan_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            *rc = cuda_fail(ctx, e, "cudaGetSymbolAddress(g_scan_static_scratch)");
+            return nullptr;
+        }
+        cached[ctx->device] = ptr;
+    }
+    return cached[ctx->device];
+}
+
+template <int V>
+static int32_t run_scan_states_static(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0, float* h, float* last,
+                                      size_t lanes, size_t len, size_t stride, unsigned chunks) {
+    ScanGeom g;
+    g.len = len;
+    g.stride = stride;
+    g.cvecs = (unsigned)(stride / V);
+    g.n_chunks = chunks > len ? (unsigned)len : chunks;
+    g.chunk_len = (unsigned)((len + g.n_chunks - 1) / g.n_chunks);
+    g.n_chunks = (unsigned)((len + g.chunk_len - 1) / g.chunk_len);
+    g.total = lanes * g.n_chunks * g.cvecs;
+    const int threads = 128;
+    size_t blocks = (g.total + threads - 1) / threads;
+    if (blocks > 0x7fffffffull)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 affine scan grid (%zu, 1) exceeds grid limits; refusing launch", blocks);
+    const float* carry = h0;
+    if (g.n_chunks > 1) {
+        size_t per = lanes * g.n_chunks * stride;  // floats in each of the three scratch arrays
+        if (per > kStaticScanFloats / 3)
+            return fail(ctx, PSSA_B200_ERR_SHAPE,
+                        "B200 static scan: lanes*chunks*stride = %zu floats exceeds the fixed scratch of %zu floats per array; "
+                        "use fewer chunks or the arena-backed entry point; refusing launch",
+                        per, kStaticScanFloats / 3);
+        int32_t rc;
+        float* base = static_scratch_for_current_device(ctx, &rc);
+        if (!base) return rc;
+        // every element of the three arrays that pass 2 and 3 read is written by pass 1 / 2 of this same call,
+        // so nothing left behind by an earlier call is ever observed and no clearing is needed
+        float* agg_a = base;
+        float* agg_b = base + kStaticScanFloats / 3;
+        float* c_b = base + 2 * (kStaticScanFloats / 3);
+        scan_chunk_reduce<V, 4><<<(unsigned)blocks, threads, 0, ctx->stream>>>(a, b, agg_a, agg_b, g);
+        if ((rc = after_launch(ctx, "scan_chunk_reduce")) != PSSA_B200_OK) return rc;
+        size_t cblocks = (lanes * g.cvecs + threads - 1) / threads;
+        scan_chunk_carry<V, false><<<(unsigned)cblocks, threads, 0, ctx->stream>>>(agg_a, agg_b, h0, nullptr, c_b, g, lanes);
+        if ((rc = after_launch(ctx, "scan_chunk_carry")) != PSSA_B200_OK) return rc;
+        carry = c_b;
+    }
+    scan_chunk_apply<V, 4, false><<<(unsigned)blocks, threads, 0, ctx->stream>>>(a, b, nullptr, carry, nullptr, h, last, g);
+    return after_launch(ctx, "scan_chunk_apply");
+}
+
+int32_t launch_scan_states_static(pssa_b200_ctx* ctx, const float* a, const float* b, const float* h0, float* h, float* h_last,
+                                  size_t lanes, size_t len, size_t stride, unsigned chunks) {
+    bool vec = stride % 4 == 0 && aligned16(a) && aligned16(b) && aligned16(h) && (!h0 || aligned16(h0)) &&
+               (!h_last || aligned16(h_last));
+    if (vec) return run_scan_states_static<4>(ctx, a, b, h0, h, h_last, lanes, len, stride, chunks);
+    return run_scan_states_static<1>(ctx, a, b, h0, h, h_last, lanes, len, stride, chunks);
+}
+
 int32_t launch_scan_maps(pssa_b200_ctx* ctx, float* scan_a, float* scan_b, size_t lanes, size_t len, size_t stride,
                          int forced_chunks) {
     bool vec = stride % 4 == 0 && aligned16(scan_a) && aligned16(scan_b);

@@ -115,6 +115,13 @@ class B200Dispatch:
                                                         lanes, length, stride))
 
 
+    def scan_states_noalloc_dev(self, a, b, h0, h, h_last, lanes: int, length: int, stride: int, chunks: int):
+        """Same result as `scan_states_dev` without any device allocation: for hosts that own all GPU memory
+        themselves or cannot tolerate the synchronisation of cudaMalloc. Scratch is a fixed array inside the
+        library (lanes*chunks*stride <= 2**20 when chunks > 1); concurrent calls on one GPU must be serialised."""
+        self._check(self._lib.pssa_b200_scan_states_noalloc_dev(self._h, _ptr(a), _ptr(b), _ptr(h0), _ptr(h), _ptr(h_last),
+                                                                lanes, length, stride, chunks))
+
     # ---- fused SSM stage
     def ssm_forward(self, delta, b_proj, x_norm, rates, c_proj, initial, seq_len, d_m, d_s, bar_a=None, bar_b=None,
                     states=None, y_ssm=None, exact=False):
