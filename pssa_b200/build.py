@@ -37,7 +37,7 @@ def build(force: bool = False, verbose: bool = False) -> pathlib.Path:
     procs = []
     for src in sources():
         obj = objdir / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("PSSA_B200_NVCC_FLAGS", "").split(), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -52,18 +52,33 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const float* __restrict
 }
 
 // src/pssa.rs:1179-1196: ad = (U_fast + U_slow) * act (sum over r in order), z = y/sqrt(s) + g*mp + ad.
+// One thread per (row, channel); the 16 adapter activations of a row are the same address for a whole warp
+// (broadcast), the 16 up-projection weights of a channel are four float4 loads.
 __global__ void __launch_bounds__(256) combine_zraw_kernel(const float* __restrict__ y, const float* __restrict__ g,
                                                            size_t ldg, const float* __restrict__ m_proj,
                                                            const float* __restrict__ act, size_t ldact,
                                                            const float* __restrict__ u_eff, float* __restrict__ z_raw,
                                                            __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d, int rank,
-                                                           float ssm_scale) {
+                                                           float ssm_scale, int vec) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * (size_t)d) return;
     size_t row = idx / d;
     int i = (int)(idx % d);
     float ad = 0.0f;
-    for (int r = 0; r < rank; ++r) ad = __fadd_rn(ad, __fmul_rn(__ldg(u_eff + (size_t)i * rank + r), __ldg(act + row * ldact + r)));
+    const float* u = u_eff + (size_t)i * rank;
+    const float* a = act + row * ldact;
+    if (vec) {  // rank % 4 == 0 and 16-byte aligned rows
+        for (int r = 0; r < rank; r += 4) {
+            float4 uv = __ldg(reinterpret_cast<const float4*>(u + r));
+            float4 av = __ldg(reinterpret_cast<const float4*>(a + r));
+            ad = __fadd_rn(ad, __fmul_rn(uv.x, av.x));
+            ad = __fadd_rn(ad, __fmul_rn(uv.y, av.y));
+            ad = __fadd_rn(ad, __fmul_rn(uv.z, av.z));
+            ad = __fadd_rn(ad, __fmul_rn(uv.w, av.w));
+        }
+    } else {
+        for (int r = 0; r < rank; ++r) ad = __fadd_rn(ad, __fmul_rn(__ldg(u + r), __ldg(a + r)));
+    }
     float z = __fadd_rn(__fadd_rn(__fmul_rn(y[idx], ssm_scale), __fmul_rn(g[row * ldg + i], m_proj[idx])), ad);
     z_raw[idx] = z;
     if (z_bf16) z_bf16[idx] = __float2bfloat16_rn(z);
@@ -149,8 +164,9 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
                             float ssm_scale) {
+    int vec = rank % 4 == 0 && ldact % 4 == 0 && ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(u_eff)) & 15) == 0;
     combine_zraw_kernel<<<blocks_for(rows * (size_t)d, 256), 256, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw,
-                                                                                 (__nv_bfloat16*)z_bf16, rows, d, rank, ssm_scale);
+                                                                                 (__nv_bfloat16*)z_bf16, rows, d, rank, ssm_scale, vec);
     return after_launch(ctx, "combine_zraw_kernel");
 }
 

@@ -5,14 +5,15 @@
 // elementwise kernels that follow them (softplus / sigmoid / sigmoid_mul / add, src/cuda/stages.ptx:541-607),
 // which become the epilogue.
 //
-// Blackwell data path, one 128 x BN output tile per CTA:
+// Blackwell data path, one persistent CTA per SM walking 128 x BN output tiles (BN = 64, 128 or 256):
 //   warp 0   producer: TMA (cp.async.bulk.tensor.2d) loads of 128x64 / BNx64 bf16 boxes, 128-byte swizzle,
-//            into a 4-stage shared-memory ring; completion on per-stage "full" mbarriers.
+//            into a 3- or 4-stage shared-memory ring; completion on per-stage "full" mbarriers.
 //   warp 1   issuer: one thread issues tcgen05.mma (cta_group::1, kind::f16, M 128, N BN, K 16) from shared-
-//            memory descriptors into a TMEM accumulator of BN fp32 columns; tcgen05.commit releases each
-//            ring stage ("empty" mbarrier) and finally signals "accumulator ready".
-//   warps 2-5 epilogue: tcgen05.ld (32 lanes x 32 columns per warp) -> activation -> global stores (fp32
-//            and/or bf16).
+//            memory descriptors into one of two TMEM accumulators of BN fp32 columns; tcgen05.commit releases
+//            each ring stage ("empty" mbarrier) and finally signals "accumulator full".
+//   warps 2-9 epilogue: tcgen05.ld (32 lanes x 32 columns per warp) -> activation -> transpose in shared
+//            memory -> whole-line global stores (fp32 and/or bf16); the accumulator is handed back ("accumulator empty") as soon as it is in registers,
+//            so the next tile's MMAs overlap this tile's epilogue.
 // Both operands are K-major (row-major [rows, K]), so X * W^T needs no transpose anywhere.
 // Every mbarrier wait is bounded: on expiry the kernel records PSSA_B200_ERR_TIMEOUT in the context's
 // status word, stops issuing work, and still frees its TMEM.
@@ -31,9 +32,11 @@ namespace {
 constexpr int BM = 128;      // rows per tile = UMMA M
 constexpr int BK = 64;       // bf16 per stage row = 128 bytes = one swizzle atom
 constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit operands
-constexpr int STAGES = 4;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;  // two warps per TMEM lane quadrant, each draining half of the tile's columns
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 3 : 4; }
 constexpr unsigned kSpinLimit = 1u << 24;
+constexpr int STG_PITCH = 36;  // floats per staged row: 32 + 4 keeps float4 rows 16-byte aligned and bank-spread
 
 struct GemmEpilogue {
     float* out;            // fp32 [M, ldo] or null
@@ -137,11 +140,23 @@ __device__ __forceinline__ float fast_epilogue(const GemmEpilogue& e, float acc,
     }
 }
 
+__device__ __forceinline__ int col_kind(const GemmEpilogue& e, int col) {
+    return col < e.c1 ? EPI_SOFTPLUS : col < e.c2 ? EPI_NONE : col < e.c3 ? EPI_SIGMOID : EPI_SILU;
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent kernel: CTA c processes tiles c, c + gridDim.x, ... ; tile index -> (m, n) with n fastest, so the
+// CTAs running at the same time share A row blocks through L2 and A is read from HBM once. Two TMEM accumulators
+// let the epilogue of tile i run while the tensor cores work on tile i + 1.
 template <int BN>
-__global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
-                                                                         const __grid_constant__ CUtensorMap map_b,
-                                                                         GemmEpilogue e) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                            const __grid_constant__ CUtensorMap map_b,
+                                                                            GemmEpilogue e) {
+    constexpr int STAGES = stages_for(BN);
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr uint32_t TMEM_COLS = 2 * BN;  // 128, 256 or 512: a power of two >= 32
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -149,23 +164,32 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_tcgen05_kernel(const _
     unsigned char* smem_b = smem + STAGES * A_BYTES;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem_b + STAGES * B_BYTES);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+    uint64_t* acc_full = empty_bar + STAGES;   // [2] accumulator written by the tensor cores
+    uint64_t* acc_empty = acc_full + 2;        // [2] accumulator drained by the epilogue warps
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EPI_WARPS][32 rows][STG_PITCH]
+    const bool vec32 = e.out && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0);
+    const bool vec16 = e.out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out16) & 7) == 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int num_kb = (e.K + BK - 1) / BK;
+    const int n_tiles = (e.N + BN - 1) / BN;
+    const int m_tiles = (e.M + BM - 1) / BM;
+    const long long total_tiles = (long long)n_tiles * m_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(acc_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], EPI_WARPS);  // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM allocation is a warp-wide operation; BN fp32 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+    if (warp == 1) {  // TMEM allocation is a warp-wide operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tcgen05_fence_before();
@@ -175,100 +199,187 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_bf16_tcgen05_kernel(const _
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t round = kb / STAGES;
-                if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-                    atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
-                    break;
+            uint32_t it = 0;  // k-block counter across all tiles of this CTA
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (int)(tile / n_tiles) * BM, n0 = (int)(tile % n_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t round = it / STAGES;
+                    if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+                        atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                    tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], kb * BK, m0);
+                    tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kb * BK, n0);
                 }
-                mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
-                tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], kb * BK, m0);
-                tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kb * BK, n0);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            uint32_t it = 0, t = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) {
+            for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+                const uint32_t buf = t & 1, use = t >> 1;
+                if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) {
                     atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
                     ok = false;
                     break;
                 }
                 tcgen05_fence_after();
-                const uint64_t da = umma_desc_sw128(smem_u32(smem_a + s * A_BYTES));
-                const uint64_t db = umma_desc_sw128(smem_u32(smem_b + s * B_BYTES));
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+                        atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint64_t da = umma_desc_sw128(smem_u32(smem_a + s * A_BYTES));
+                    const uint64_t db = umma_desc_sw128(smem_u32(smem_b + s * B_BYTES));
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // advance 32 bytes (16 bf16) inside the swizzle atom: +2 in 16-byte units
-                    tcgen05_mma_bf16(tmem_base, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advance 32 bytes (16 bf16) inside the swizzle atom: +2 in 16-byte units
+                        tcgen05_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
                 }
-                tcgen05_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+                tcgen05_commit(&acc_full[buf]);  // accumulator complete (or abandoned)
             }
-            tcgen05_commit(acc_bar);  // accumulator complete (or abandoned)
         }
     } else {
-        // epilogue warps 2..5 own TMEM lane quadrants (warp % 4)
+        // epilogue warps 2..9: TMEM lane quadrant = warp % 4 (a hardware rule), column half = (warp - 2) / 4
         const int quad = warp & 3;
-        const bool ready = mbar_wait(acc_bar, 0);
-        tcgen05_fence_after();
-        const int row = m0 + quad * 32 + lane;
-        if (ready && *(volatile int*)e.status == 0) {
+        const int half = (warp - 2) >> 2;
+        constexpr int HALF_COLS = BN / 2;
+        float* stg = stage + (warp - 2) * (32 * STG_PITCH);
+        const int cq = (lane & 7) * 4;   // column quad this lane stores after the transpose
+        const int rsub = lane >> 3;      // row within each group of 4 rows
+        uint32_t t = 0;
+        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+            const int m0 = (int)(tile / n_tiles) * BM, n0 = (int)(tile % n_tiles) * BN + half * HALF_COLS;
+            const uint32_t buf = t & 1, use = t >> 1;
+            const bool ready = mbar_wait(&acc_full[buf], use & 1);
+            if (!ready) {
+                if (lane == 0) atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + buf * BN + half * HALF_COLS + ((uint32_t)(quad * 32) << 16);
+            const int rbase = m0 + quad * 32;
+            // whole 32-row band and all of this warp's columns inside the matrix: no per-element bounds checks
+            const bool interior = rbase + 32 <= e.M && n0 + HALF_COLS <= e.N;
+            bool released = false;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= e.N) break;  // warp-uniform
+            for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
+                const int col0 = n0 + c0;
                 float v[32];
-                tcgen05_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
-                if (row < e.M) {
-                    const int col0 = n0 + c0;
-                    float* orow = e.out ? e.out + (size_t)row * e.ldo + col0 : nullptr;
-                    __nv_bfloat16* brow = e.out16 ? e.out16 + (size_t)row * e.ld16 + col0 : nullptr;
-                    const bool full_chunk = col0 + 32 <= e.N;
-                    const bool vec_ok = full_chunk && orow && ((reinterpret_cast<uintptr_t>(orow) & 15) == 0);
+                if (col0 < e.N) tcgen05_ld_32x32(taddr + (uint32_t)c0, v);  // warp-uniform
+                if (!released && (c0 + 32 >= HALF_COLS || col0 + 32 >= e.N)) {
+                    // this warp's last chunk of the accumulator is in registers: hand its share of the buffer back
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    released = true;
+                }
+                if (col0 >= e.N) break;
+                // One activation kind per 32-column chunk keeps the element loop free of branches (a per-element
+                // switch made the instruction stream jump between kilobytes of unrolled code and stalled on
+                // instruction fetch). The column table's boundaries are multiples of 32 for every model shape;
+                // a chunk that straddles one is activated element by element after the transpose (kind == -1).
+                int kind = e.epi;
+                if (kind < 0) {
+                    const int first = col_kind(e, col0), last = col_kind(e, min(col0 + 31, e.N - 1));
+                    kind = first == last ? first : -1;
+                }
+                switch (kind) {
+                    case EPI_SOFTPLUS:
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        float prev = (e.epi == EPI_ADD_OUT && orow && col0 + j < e.N) ? orow[j] : 0.0f;
-                        v[j] = fast_epilogue(e, v[j], col0 + j, prev);
-                    }
-                    if (vec_ok) {
+                        for (int j = 0; j < 32; ++j) v[j] = v[j] > 20.0f ? v[j] : log1pf(__expf(v[j]));
+                        break;
+                    case EPI_SIGMOID:
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else if (orow) {
+                        for (int j = 0; j < 32; ++j) v[j] = __fdividef(1.0f, 1.0f + __expf(-v[j]));
+                        break;
+                    case EPI_SILU:
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < e.N) orow[j] = v[j];
-                    }
-                    if (brow) {
-                        if (full_chunk && ((reinterpret_cast<uintptr_t>(brow) & 15) == 0)) {
+                        for (int j = 0; j < 32; ++j) v[j] = __fdividef(v[j], 1.0f + __expf(-v[j]));
+                        break;
+                    case EPI_SCALE:
 #pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                                uint4 pk;
-                                pk.x = *reinterpret_cast<uint32_t*>(&p0), pk.y = *reinterpret_cast<uint32_t*>(&p1);
-                                pk.z = *reinterpret_cast<uint32_t*>(&p2), pk.w = *reinterpret_cast<uint32_t*>(&p3);
-                                *reinterpret_cast<uint4*>(brow + j) = pk;
+                        for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+                        break;
+                    default:
+                        break;  // EPI_NONE, EPI_ADD_OUT (added after the transpose)
+                }
+                // transpose through a warp-private shared-memory tile: global stores become whole 128-byte lines
+                // (8 lanes per output row) instead of 32 scattered 16-byte pieces per instruction
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(stg + lane * STG_PITCH + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                __syncwarp();
+                const int gcol = col0 + cq;
+                if (interior && kind != -1 && vec32 && (!e.out16 || vec16)) {
+                    float* gp = e.out ? e.out + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
+                    __nv_bfloat16* bp = e.out16 ? e.out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
+                    const float* sp = stg + rsub * STG_PITCH + cq;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float4 val = *reinterpret_cast<const float4*>(sp + i * 4 * STG_PITCH);
+                        if (gp) {
+                            float4* g4 = reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo);
+                            if (e.epi == EPI_ADD_OUT) {
+                                float4 pv = *g4;
+                                val.x += pv.x, val.y += pv.y, val.z += pv.z, val.w += pv.w;
                             }
-                        } else {
+                            *g4 = val;
+                        }
+                        if (bp) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(val.x, val.y), p1 = __floats2bfloat162_rn(val.z, val.w);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&p0), pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                            *reinterpret_cast<uint2*>(bp + (size_t)i * 4 * e.ld16) = pk;
+                        }
+                    }
+                } else {
+#pragma unroll 1
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = i * 4 + rsub;
+                        const int grow = rbase + r;
+                        if (grow >= e.M || gcol >= e.N) continue;
+                        float4 val = *reinterpret_cast<const float4*>(stg + r * STG_PITCH + cq);
+                        float o[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < e.N) brow[j] = __float2bfloat16_rn(v[j]);
+                        for (int q = 0; q < 4; ++q) {
+                            if (gcol + q >= e.N) continue;
+                            if (kind == -1) o[q] = fast_epilogue(e, o[q], gcol + q, 0.0f);
+                            if (e.out) {
+                                float* gp = e.out + (size_t)grow * e.ldo + gcol + q;
+                                if (e.epi == EPI_ADD_OUT) o[q] += *gp;
+                                *gp = o[q];
+                            }
+                            if (e.out16) e.out16[(size_t)grow * e.ld16 + gcol + q] = __float2bfloat16_rn(o[q]);
                         }
                     }
                 }
+                __syncwarp();
             }
-        } else if (!ready && lane == 0) {
-            atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
+            if (!released) {  // this warp's column half lies entirely outside the matrix
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
         }
     }
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -312,14 +423,16 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     int32_t rc;
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
-    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16;
+    constexpr int STAGES = stages_for(BN);
+    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EPI_WARPS * 32 * STG_PITCH * 4;
     auto kern = gemm_bf16_tcgen05_kernel<BN>;
     static bool attr = false;
     if (!attr) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr = true;
     }
-    dim3 grid((unsigned)((e.M + BM - 1) / BM), (unsigned)((e.N + BN - 1) / BN));
+    long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
+    unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
     kern<<<grid, GEMM_THREADS, smem, ctx->stream>>>(map_a, map_b, e);
     return after_launch(ctx, "gemm_bf16_tcgen05_kernel");
 }
@@ -338,9 +451,12 @@ int32_t check_shape(pssa_b200_ctx* ctx, const void* a, const void* b, size_t M, 
 
 int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue& e) {
     e.status = ctx->status_dev;
-    // narrow outputs (state / key / rank projections) use the 64-column tile so fewer tensor-core columns idle
-    if (e.N <= 64) return launch_tile<64>(ctx, a, b, e);
-    return launch_tile<128>(ctx, a, b, e);
+    // widest tile that still gives every SM work: 256 columns halve the shared-memory operand traffic per flop,
+    // narrow outputs (state / key projections) and short batches (decode) use smaller tiles to spread over SMs
+    const long long m_tiles = (e.M + BM - 1) / BM;
+    if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2) return launch_tile<64>(ctx, a, b, e);
+    if (e.N <= 128 || m_tiles * ((e.N + 255) / 256) < ctx->sm_count) return launch_tile<128>(ctx, a, b, e);
+    return launch_tile<256>(ctx, a, b, e);
 }
 
 }  // namespace

@@ -26,6 +26,7 @@ struct SsmParams {
     const float* rates;    // [d, s]     A = -softplus(raw)
     float* carry;          // [lanes, d*s] in/out, may be null (zero carry in, carry out dropped)
     float* y;              // [rows, d]
+    void* y_bf16;          // optional bf16 copy of y for the tensor-core query projection
     float* states;         // optional [rows, d*s]: state after each token
     float* bar_a;          // optional [rows, d*s]
     float* bar_b;          // optional [rows, d*s]
@@ -61,6 +62,7 @@ struct RetrieveParams {
     size_t ldq;            // row pitch of q in floats (0 = dk)
     float* weights;        // [rows, cap] distances in flight, weights on return
     float* m_val;          // [rows, dv]
+    void* m_bf16;          // optional bf16 copy of m_val for the tensor-core memory projection
     float* min_dist;       // [rows], may be null
     size_t rows;
     int dk, dv, cap, count, top_k;

@@ -130,29 +130,28 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // stage 3: SSM with the lane carries of this block (src/gpu_batch.rs:582-619)
         SsmParams sp{};
         sp.delta = ws.proj + m->off_delta, sp.x_norm = ws.x_norm, sp.b_proj = ws.proj + m->off_b, sp.c_proj = ws.proj + m->off_c;
-        sp.rates = b.rates, sp.carry = m->state + l * ds, sp.y = ws.y;
+        sp.rates = b.rates, sp.carry = m->state + l * ds, sp.y = ws.y, sp.y_bf16 = exact ? nullptr : ws.y_bf16;
         sp.offsets = ws.lane_off, sp.lengths = ws.lane_len, sp.rows = rows, sp.d = d, sp.s = s, sp.lanes = (int)lanes;
         sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = m->depth * ds;
         sp.aligned = ssm_vector_ok(sp);
         if ((rc = launch_ssm_fused(ctx, sp, exact))) return rc;
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
-        if (!exact && (rc = launch_to_bf16(ctx, ws.y, ws.y_bf16, rows * (size_t)d))) return rc;
         if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
         RetrieveParams rp{};
         rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = nullptr, rp.q_norm = nullptr;
         rp.keys = b.w[T_BANK_KEYS], rp.norm_sq = b.w[T_BANK_NORM_SQ], rp.values = b.w[T_BANK_VALUES];
-        rp.weights = ws.weights, rp.m_val = ws.m_val, rp.min_dist = nullptr;
+        rp.weights = ws.weights, rp.m_val = ws.m_val, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
         rp.rows = rows, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
-        if (!exact && (rc = launch_to_bf16(ctx, ws.m_val, ws.m_bf16, rows * (size_t)d))) return rc;
         if ((rc = dense(m, ws.m_val, ws.m_bf16, b.w[T_W_PROJ], b.wproj_bf16, ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
         if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z,
                                       exact ? nullptr : ws.z_bf16, rows, d, (int)m->rank, ssm_scale)))
             return rc;
-        if ((rc = dense(m, ws.z, ws.z_bf16, b.w[T_MLP_W1], b.w1_bf16, ws.mlp_act, rows, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f,
-                        exact ? nullptr : ws.act_bf16)))
+        // the tensor-core path needs the MLP activations only as the next GEMM's bf16 operand
+        if ((rc = dense(m, ws.z, ws.z_bf16, b.w[T_MLP_W1], b.w1_bf16, exact ? ws.mlp_act : nullptr, rows, 2 * m->d, m->d, 2 * m->d,
+                        EPI_SILU, 1.0f, exact ? nullptr : ws.act_bf16)))
             return rc;
         if ((rc = dense(m, ws.mlp_act, ws.act_bf16, b.w[T_MLP_W2], b.w2_bf16, ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
         // depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual

@@ -15,6 +15,7 @@
 //   C  value_mix_kernel: m = W[rows, count] x V[count, dv] for the all-slots read, fp32, slots
 //      accumulated in ascending order like the reference.
 // B and C keep the reference's sequential f32 summation order when `exact` is set.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cfloat>
@@ -177,7 +178,10 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
     float* w = sm + (size_t)warp * cap;
     if (count == 0) {  // memory.rs:363-367
         for (int i = lane; i < cap; i += 32) row[i] = 0.0f;
-        for (int j = lane; j < dv; j += 32) p.m_val[q * dv + j] = 0.0f;
+        for (int j = lane; j < dv; j += 32) {
+            p.m_val[q * dv + j] = 0.0f;
+            if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + j] = __float2bfloat16_rn(0.0f);
+        }
         if (p.min_dist) p.min_dist[q] = 0.0f;
         return;
     }
@@ -245,7 +249,10 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 int j = j0 + e * 32;
-                if (j < dv) p.m_val[q * dv + j] = acc[e];
+                if (j < dv) {
+                    p.m_val[q * dv + j] = acc[e];
+                    if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + j] = __float2bfloat16_rn(acc[e]);
+                }
             }
         }
         return;
@@ -320,7 +327,10 @@ __global__ void __launch_bounds__(256) value_mix_kernel(RetrieveParams p) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
             int col = c0 + tc * 4 + b;
-            if (col < dv) p.m_val[q * dv + col] = acc[a][b];
+            if (col < dv) {
+                p.m_val[q * dv + col] = acc[a][b];
+                if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + col] = __float2bfloat16_rn(acc[a][b]);
+            }
         }
     }
 }

@@ -22,6 +22,7 @@
 //         FMA contraction, y summed per thread then by a shuffle tree over the G threads.
 //   EXACT expf, separately rounded multiply/add in the reference's order (src/pssa.rs:1131-1144);
 //         with G == 1 the sum over j is the reference's sequential sum.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "bounds.hpp"
@@ -199,7 +200,10 @@ __global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
             }
 #pragma unroll
             for (int m = LPG; m < 32; m <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, m);
-            if (g == 0 && valid) p.y[row * d + i] = yp;
+            if (g == 0 && valid) {
+                p.y[row * d + i] = yp;
+                if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y_bf16)[row * d + i] = __float2bfloat16_rn(yp);
+            }
             if (TAPE) {
 #pragma unroll
                 for (int jj = 0; jj < ST; ++jj) {
