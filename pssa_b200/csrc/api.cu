@@ -328,15 +328,30 @@ int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_
         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
     if (flags & ~PSSA_B200_MEM_EXACT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    if (!weights) {
+    // scratch from the arena: the weight rows when the caller does not want them, and the bf16 pieces of the
+    // weights and of the transposed values for the tensor-core value read (all-slots mode, capacity % 64 == 0)
+    const bool exact = (flags & PSSA_B200_MEM_EXACT) != 0;
+    const bool topk = top_k != 0 && top_k < count;
+    const bool tc_read = !exact && !topk && count > 0 && capacity % 64 == 0;
+    size_t need = (weights ? 0 : arena_round(rows * capacity * 4)) +
+                  (tc_read ? arena_round(rows * 3 * capacity * 2) + arena_round(d_val * 3 * capacity * 2) : 0);
+    void* w_split = nullptr;
+    void* v_split = nullptr;
+    if (need) {
         arena_reset(ctx);
-        if ((rc = arena_reserve(ctx, arena_round(rows * capacity * 4))) != PSSA_B200_OK) return rc;
-        weights = (float*)arena_take(ctx, rows * capacity * 4);
+        if ((rc = arena_reserve(ctx, need)) != PSSA_B200_OK) return rc;
+        if (!weights) weights = (float*)arena_take(ctx, rows * capacity * 4);
+        if (tc_read) {
+            w_split = arena_take(ctx, rows * 3 * capacity * 2);
+            v_split = arena_take(ctx, d_val * 3 * capacity * 2);
+            if ((rc = launch_split_values(ctx, values, v_split, (int)capacity, (int)d_val)) != PSSA_B200_OK) return rc;
+        }
     }
     RetrieveParams p{};
     p.q = q, p.q_is_euclidean = q_is_euclidean, p.q_pnc = q_pnc, p.q_norm = q_norm;
     p.keys = keys, p.norm_sq = norm_sq, p.values = values;
     p.weights = weights, p.m_val = m_val, p.min_dist = min_dist;
+    p.w_split = w_split, p.v_split = v_split;
     p.rows = rows, p.dk = (int)d_key, p.dv = (int)d_val, p.cap = (int)capacity, p.count = (int)count;
     p.top_k = (int)(top_k > capacity ? capacity : top_k), p.tau = tau;
     return launch_memory_read(ctx, p, (flags & PSSA_B200_MEM_EXACT) != 0);

@@ -47,6 +47,11 @@ struct GemmEpilogue {
     float alpha;
     int c1, c2, c3;        // table: [0,c1) softplus, [c1,c2) none, [c2,c3) sigmoid, [c3,N) silu
     int* status;
+    // Split-precision product: A = [A_0 | A_1 | A_2] and B = [B_0 | B_1 | B_2] hold bf16 pieces of fp32 operands
+    // (x = x_0 + x_1 + x_2), each piece seg_kb k-blocks wide; the kernel accumulates the listed (A piece, B piece)
+    // products into one fp32 accumulator. n_pairs == 0: plain product over K.
+    int n_pairs, seg_kb;
+    unsigned char pair_a[6], pair_b[6];
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -172,7 +177,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     const bool vec16 = e.out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out16) & 7) == 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (e.K + BK - 1) / BK;
+    const int num_kb = e.n_pairs > 0 ? e.n_pairs * e.seg_kb : (e.K + BK - 1) / BK;
     const int n_tiles = (e.N + BN - 1) / BN;
     const int m_tiles = (e.M + BM - 1) / BM;
     const long long total_tiles = (long long)n_tiles * m_tiles;
@@ -212,8 +217,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         break;
                     }
                     mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
-                    tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], kb * BK, m0);
-                    tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kb * BK, n0);
+                    int ka = kb, kbb = kb;
+                    if (e.n_pairs > 0) {
+                        const int pair = kb / e.seg_kb, within = kb % e.seg_kb;
+                        ka = e.pair_a[pair] * e.seg_kb + within;
+                        kbb = e.pair_b[pair] * e.seg_kb + within;
+                    }
+                    tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], ka * BK, m0);
+                    tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kbb * BK, n0);
                 }
             }
         }
@@ -469,6 +480,22 @@ int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, f
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = epi, e.alpha = alpha;
     return dispatch(ctx, x16, w16, e);
+}
+
+// fp32-accurate product from three bf16 pieces per operand: a16 [M, 3*K], b16 [N, 3*K], K a multiple of 64.
+// The six products whose weight is above 2^-24 are accumulated: (0,0) (0,1) (1,0) (0,2) (1,1) (2,0).
+int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
+                                size_t N, size_t K, size_t ldo) {
+    if (K % BK != 0) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 split GEMM needs K %% 64 == 0; K = %zu", K);
+    int32_t rc = check_shape(ctx, a16, b16, M, N, 3 * K);
+    if (rc) return rc;
+    GemmEpilogue e{};
+    e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
+    e.M = (int)M, e.N = (int)N, e.K = (int)(3 * K), e.epi = EPI_NONE, e.alpha = 1.0f;
+    e.n_pairs = 6, e.seg_kb = (int)(K / BK);
+    const unsigned char pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
+    for (int i = 0; i < 6; ++i) e.pair_a[i] = pa[i], e.pair_b[i] = pb[i];
+    return dispatch(ctx, a16, b16, e);
 }
 
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,

@@ -64,11 +64,17 @@ struct RetrieveParams {
     float* m_val;          // [rows, dv]
     void* m_bf16;          // optional bf16 copy of m_val for the tensor-core memory projection
     float* min_dist;       // [rows], may be null
+    // tensor-core value read (all-slots mode, non-exact): the softmax kernel also writes each weight row as three
+    // bf16 pieces [rows, 3*cap]; v_split is the bank's values transposed and split the same way [dv, 3*cap]
+    void* w_split;
+    const void* v_split;
     size_t rows;
     int dk, dv, cap, count, top_k;
     float tau;
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
+// values [cap, dv] fp32 -> v_split [dv, 3*cap] bf16 (transpose + three-way split); once per bank upload
+int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv);
 
 // gemm_exact.cu: out[M, ldo] (first N columns) = epilogue(X[M,K] * W[N,K]^T), fp32, dot_slice order
 int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, float* out, size_t M, size_t N, size_t K,
@@ -77,6 +83,9 @@ int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, fl
 // gemm_tcgen05.cu: bf16 operands [rows, K] row-major, fp32 accumulate in TMEM; out fp32 [M, ldo] and/or bf16 [M, N]
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
                          size_t K, size_t ldo, int epi, float alpha);
+// fp32-accurate product of operands pre-split into three bf16 pieces: a16 [M, 3K], b16 [N, 3K] (six partial products)
+int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
+                                size_t N, size_t K, size_t ldo);
 // concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
                              size_t ldo, int c1, int c2, int c3);

@@ -103,6 +103,7 @@ int32_t pssa_b200_model_create(pssa_b200_ctx* ctx, const pssa_b200_config* cfg, 
         guard(dev_alloc(ctx, &b.wproj_bf16, m->d * m->d * 2, true));
         guard(dev_alloc(ctx, &b.w1_bf16, 2 * m->d * m->d * 2, true));
         guard(dev_alloc(ctx, &b.w2_bf16, 2 * m->d * m->d * 2, true));
+        guard(dev_alloc(ctx, &b.vsplit_bf16, m->d * 3 * m->cap * 2, true));
         b.host_up.assign(m->d * m->rank, 0.0f);
         b.host_cons.assign(m->d * m->rank, 0.0f);
         b.confidence.assign(m->cap, 1.0f);
@@ -140,6 +141,7 @@ void pssa_b200_model_destroy(pssa_b200_model* m) {
         cudaFree(b.wproj_bf16);
         cudaFree(b.w1_bf16);
         cudaFree(b.w2_bf16);
+        cudaFree(b.vsplit_bf16);
     }
     free_workspace(m->ws);
     delete m;
@@ -211,6 +213,7 @@ int32_t pssa_b200_model_set_bank(pssa_b200_model* m, int32_t layer, const float*
     PSSA_CUDA(ctx, cudaMemcpyAsync(b.w[T_BANK_VALUES], values, m->cap * m->d * 4, cudaMemcpyHostToDevice, st));
     b.count = count;
     b.write_head = write_head;
+    b.vsplit_dirty = true;
     if (confidence) b.confidence.assign(confidence, confidence + m->cap);
     if (last_seen_step) b.last_seen.assign(last_seen_step, last_seen_step + m->cap);
     PSSA_CUDA(ctx, cudaStreamSynchronize(st));

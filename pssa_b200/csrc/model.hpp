@@ -32,7 +32,9 @@ struct DeviceBlock {
     void* wproj_bf16 = nullptr;
     void* w1_bf16 = nullptr;
     void* w2_bf16 = nullptr;
+    void* vsplit_bf16 = nullptr;  // bank values transposed, three bf16 pieces [d, 3*cap] (tensor-core value read)
     bool bf16_dirty = true;
+    bool vsplit_dirty = true;
 };
 
 struct Workspace {
@@ -41,7 +43,7 @@ struct Workspace {
              *greedy = nullptr;
     float *feat_a = nullptr, *feat_b = nullptr, *x_norm = nullptr, *proj = nullptr, *y = nullptr, *weights = nullptr,
           *m_val = nullptr, *m_proj = nullptr, *z = nullptr, *mlp_act = nullptr, *last_feat = nullptr, *logits = nullptr;
-    void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr;
+    void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr;
     char* base = nullptr;
     size_t bytes = 0;
 };

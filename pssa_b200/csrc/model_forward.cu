@@ -38,7 +38,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_mv = c.take(rows * d * f), o_mp = c.take(rows * d * f), o_z = c.take(rows * d * f),
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
     size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * d * 2),
-           o_ab = c.take(rows * 2 * d * 2);
+           o_ab = c.take(rows * 2 * d * 2), o_wsp = c.take(rows * 3 * m->cap * 2);
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -56,7 +56,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     ws.proj = (float*)(b + o_proj), ws.y = (float*)(b + o_y), ws.weights = (float*)(b + o_w), ws.m_val = (float*)(b + o_mv);
     ws.m_proj = (float*)(b + o_mp), ws.z = (float*)(b + o_z), ws.mlp_act = (float*)(b + o_act);
     ws.last_feat = (float*)(b + o_lf), ws.logits = (float*)(b + o_lg);
-    ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab;
+    ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab, ws.w_split = b + o_wsp;
     return PSSA_B200_OK;
 }
 
@@ -78,6 +78,11 @@ int32_t refresh_bf16(pssa_b200_model* m) {
         if ((rc = launch_to_bf16(ctx, b.w[T_MLP_W1], b.w1_bf16, 2 * d * d))) return rc;
         if ((rc = launch_to_bf16(ctx, b.w[T_MLP_W2], b.w2_bf16, 2 * d * d))) return rc;
         b.bf16_dirty = false;
+    }
+    for (auto& b : m->blocks) {
+        if (!b.vsplit_dirty) continue;
+        if ((rc = launch_split_values(ctx, b.w[T_BANK_VALUES], b.vsplit_bf16, (int)m->cap, (int)d))) return rc;
+        b.vsplit_dirty = false;
     }
     if (m->unembed_dirty) {
         if ((rc = launch_to_bf16(ctx, m->unembed, m->unembed_bf16, m->v * d))) return rc;
@@ -143,6 +148,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         rp.weights = ws.weights, rp.m_val = ws.m_val, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
         rp.rows = rows, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
+        if (!exact && m->cap % 64 == 0) rp.w_split = ws.w_split, rp.v_split = b.vsplit_bf16;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
         if ((rc = dense(m, ws.m_val, ws.m_bf16, b.w[T_W_PROJ], b.wproj_bf16, ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)

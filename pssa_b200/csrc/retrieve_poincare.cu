@@ -144,6 +144,25 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
     }
 }
 
+// x = x0 + x1 + x2 with bf16 pieces: 24 bits of significand survive, so products of pieces reproduce fp32 products
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& a, __nv_bfloat16& b, __nv_bfloat16& c) {
+    a = __float2bfloat16_rn(x);
+    float r = x - __bfloat162float(a);
+    b = __float2bfloat16_rn(r);
+    c = __float2bfloat16_rn(r - __bfloat162float(b));
+}
+
+__global__ void __launch_bounds__(256) split_values_kernel(const float* __restrict__ values, __nv_bfloat16* __restrict__ out,
+                                                           int cap, int dv) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)cap * dv) return;
+    int slot = (int)(idx / dv), col = (int)(idx % dv);
+    __nv_bfloat16 a, b, c;
+    split3(values[idx], a, b, c);
+    __nv_bfloat16* row = out + (size_t)col * 3 * cap;
+    row[slot] = a, row[cap + slot] = b, row[2 * cap + slot] = c;
+}
+
 // ------------------------------------------------------------------ B: softmax / top-k (+ fused value read)
 __device__ __forceinline__ float warp_min(float v) {
 #pragma unroll
@@ -270,7 +289,16 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
 #pragma unroll
         for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
     }
-    for (int i = lane; i < cap; i += 32) row[i] = i < count ? __fdiv_rn(w[i], sum) : 0.0f;
+    __nv_bfloat16* ws = p.w_split ? reinterpret_cast<__nv_bfloat16*>(p.w_split) + q * 3 * (size_t)cap : nullptr;
+    for (int i = lane; i < cap; i += 32) {
+        float wn = i < count ? __fdiv_rn(w[i], sum) : 0.0f;
+        row[i] = wn;
+        if (ws) {
+            __nv_bfloat16 a, b, c;
+            split3(wn, a, b, c);
+            ws[i] = a, ws[cap + i] = b, ws[2 * cap + i] = c;
+        }
+    }
 }
 
 // ------------------------------------------------------------------ C: dense value read m = W x V
@@ -373,7 +401,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         softmax_topk_kernel<false><<<(unsigned)wblocks, 256, smem_b, ctx->stream>>>(p);
     if ((rc = after_launch(ctx, "softmax_topk_kernel")) != PSSA_B200_OK) return rc;
     bool topk = p.top_k != 0 && p.top_k < p.count;
-    if (p.count > 0 && !topk) {
+    if (p.count > 0 && !topk && p.w_split && p.v_split && !exact) {
+        // all-slots value read on the tensor cores: m = W x V as six bf16 partial products (fp32-accurate)
+        if ((rc = launch_gemm_bf16_split3(ctx, p.w_split, p.v_split, p.m_val, p.m_bf16, p.rows, p.dv, p.cap, p.dv))) return rc;
+    } else if (p.count > 0 && !topk) {
         dim3 grid((unsigned)qblocks, (unsigned)((p.dv + 63) / 64));
         if (exact)
             value_mix_kernel<true><<<grid, 256, 0, ctx->stream>>>(p);
@@ -382,6 +413,12 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         if ((rc = after_launch(ctx, "value_mix_kernel")) != PSSA_B200_OK) return rc;
     }
     return PSSA_B200_OK;
+}
+
+int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv) {
+    size_t n = (size_t)cap * dv;
+    split_values_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(values, (__nv_bfloat16*)v_split, cap, dv);
+    return after_launch(ctx, "split_values_kernel");
 }
 
 }  // namespace pssa
