@@ -20,6 +20,7 @@ enum Epilogue : int {
     EPI_SILU = 3,
     EPI_SCALE = 4,    // out = acc * alpha
     EPI_ADD_OUT = 5,  // out = out + acc   (second half of q = Wqx x + Wqh y; residual adds)
+    EPI_RESIDUAL = 6, // tensor-core path only: acc + add_in, then the depth residual (see gemm_tcgen05.cu)
 };
 
 __device__ __forceinline__ float apply_epilogue(int epi, float acc, float alpha, float prev) {

@@ -52,36 +52,55 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const float* __restrict
 }
 
 // src/pssa.rs:1179-1196: ad = (U_fast + U_slow) * act (sum over r in order), z = y/sqrt(s) + g*mp + ad.
-// One thread per (row, channel); the 16 adapter activations of a row are the same address for a whole warp
-// (broadcast), the 16 up-projection weights of a channel are four float4 loads.
+// One thread owns one channel for ROWS_PER_CTA consecutive rows: its 16 up-projection weights stay in registers,
+// the 16 adapter activations of a row are one address for the whole CTA (broadcast), and y / g / m_proj / z are
+// read and written as coalesced rows.
+constexpr int kCombineRows = 16;
+template <int RANK>
 __global__ void __launch_bounds__(256) combine_zraw_kernel(const float* __restrict__ y, const float* __restrict__ g,
                                                            size_t ldg, const float* __restrict__ m_proj,
                                                            const float* __restrict__ act, size_t ldact,
                                                            const float* __restrict__ u_eff, float* __restrict__ z_raw,
                                                            __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d, int rank,
-                                                           float ssm_scale, int vec) {
-    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= rows * (size_t)d) return;
-    size_t row = idx / d;
-    int i = (int)(idx % d);
-    float ad = 0.0f;
-    const float* u = u_eff + (size_t)i * rank;
-    const float* a = act + row * ldact;
-    if (vec) {  // rank % 4 == 0 and 16-byte aligned rows
-        for (int r = 0; r < rank; r += 4) {
-            float4 uv = __ldg(reinterpret_cast<const float4*>(u + r));
-            float4 av = __ldg(reinterpret_cast<const float4*>(a + r));
-            ad = __fadd_rn(ad, __fmul_rn(uv.x, av.x));
-            ad = __fadd_rn(ad, __fmul_rn(uv.y, av.y));
-            ad = __fadd_rn(ad, __fmul_rn(uv.z, av.z));
-            ad = __fadd_rn(ad, __fmul_rn(uv.w, av.w));
-        }
-    } else {
-        for (int r = 0; r < rank; ++r) ad = __fadd_rn(ad, __fmul_rn(__ldg(u + r), __ldg(a + r)));
+                                                           float ssm_scale) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t row0 = (size_t)blockIdx.y * kCombineRows;
+    if (i >= d) return;
+    float u[RANK > 0 ? RANK : 1];
+    if (RANK > 0) {
+#pragma unroll
+        for (int r = 0; r < RANK; ++r) u[r] = __ldg(u_eff + (size_t)i * RANK + r);
     }
-    float z = __fadd_rn(__fadd_rn(__fmul_rn(y[idx], ssm_scale), __fmul_rn(g[row * ldg + i], m_proj[idx])), ad);
-    z_raw[idx] = z;
-    if (z_bf16) z_bf16[idx] = __float2bfloat16_rn(z);
+    // rows in groups of four: all global loads of a group are issued before any arithmetic
+    for (int r0 = 0; r0 < kCombineRows; r0 += 4) {
+        float yv[4], gv[4], mv[4];
+        size_t rowv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            size_t row = row0 + r0 + q;
+            rowv[q] = row < rows ? row : rows - 1;  // clamped for the loads; stores are predicated
+            yv[q] = y[rowv[q] * d + i];
+            gv[q] = g[rowv[q] * ldg + i];
+            mv[q] = m_proj[rowv[q] * d + i];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float* a = act + rowv[q] * ldact;
+            float ad = 0.0f;
+            if (RANK > 0) {
+#pragma unroll
+                for (int r = 0; r < RANK; ++r) ad = __fadd_rn(ad, __fmul_rn(u[r], __ldg(a + r)));
+            } else {
+                for (int r = 0; r < rank; ++r) ad = __fadd_rn(ad, __fmul_rn(__ldg(u_eff + (size_t)i * rank + r), __ldg(a + r)));
+            }
+            float z = __fadd_rn(__fadd_rn(__fmul_rn(yv[q], ssm_scale), __fmul_rn(gv[q], mv[q])), ad);
+            if (row0 + r0 + q < rows) {
+                const size_t idx = rowv[q] * d + i;
+                z_raw[idx] = z;
+                if (z_bf16) z_bf16[idx] = __float2bfloat16_rn(z);
+            }
+        }
+    }
 }
 
 // src/pssa.rs:2332-2337: features += scale * block_out  (prev == nullptr: features = z, block 0)
@@ -164,9 +183,24 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
                             float ssm_scale) {
-    int vec = rank % 4 == 0 && ldact % 4 == 0 && ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(u_eff)) & 15) == 0;
-    combine_zraw_kernel<<<blocks_for(rows * (size_t)d, 256), 256, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw,
-                                                                                 (__nv_bfloat16*)z_bf16, rows, d, rank, ssm_scale, vec);
+    dim3 grid((unsigned)((d + 255) / 256), (unsigned)((rows + kCombineRows - 1) / kCombineRows));
+    if (grid.y > 65535) {
+        // very long passes: fall back to several launches of at most 65535 row groups
+        size_t step = (size_t)65535 * kCombineRows;
+        for (size_t r0 = 0; r0 < rows; r0 += step) {
+            size_t n = rows - r0 < step ? rows - r0 : step;
+            int32_t rc = launch_combine_zraw(ctx, y + r0 * d, g + r0 * ldg, ldg, m_proj + r0 * d, act + r0 * ldact, ldact, u_eff,
+                                             z_raw + r0 * d, z_bf16 ? (char*)z_bf16 + r0 * d * 2 : nullptr, n, d, rank, ssm_scale);
+            if (rc) return rc;
+        }
+        return PSSA_B200_OK;
+    }
+    if (rank == 16)
+        combine_zraw_kernel<16><<<grid, 256, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw, (__nv_bfloat16*)z_bf16,
+                                                             rows, d, rank, ssm_scale);
+    else
+        combine_zraw_kernel<0><<<grid, 256, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw, (__nv_bfloat16*)z_bf16,
+                                                            rows, d, rank, ssm_scale);
     return after_launch(ctx, "combine_zraw_kernel");
 }
 

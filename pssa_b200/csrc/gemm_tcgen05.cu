@@ -52,6 +52,11 @@ struct GemmEpilogue {
     // products into one fp32 accumulator. n_pairs == 0: plain product over K.
     int n_pairs, seg_kb;
     unsigned char pair_a[6], pair_b[6];
+    // EPI_RESIDUAL: out = res_in ? res_in + res_scale * (acc + add_in) : acc + add_in   (MLP residual + depth residual)
+    const float* add_in;
+    const float* res_in;
+    size_t ld_add, ld_res;
+    float res_scale;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -132,11 +137,20 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// softplus for the bf16 path (operands already carry 2^-9 relative rounding): x > 20 -> x; x < -4 -> the two-term
+// series e^x (1 - e^x / 2) (relative error < e^2x / 3 < 1.2e-4); otherwise log(1 + e^x) with the fast intrinsics
+__device__ __forceinline__ float fast_softplus(float x) {
+    float ex = __expf(x);
+    float mid = __logf(1.0f + ex);
+    float low = ex * fmaf(-0.5f, ex, 1.0f);
+    return x > 20.0f ? x : (x < -4.0f ? low : mid);
+}
+
 __device__ __forceinline__ float fast_epilogue(const GemmEpilogue& e, float acc, int col, float prev) {
     int epi = e.epi;
     if (epi < 0) epi = col < e.c1 ? EPI_SOFTPLUS : col < e.c2 ? EPI_NONE : col < e.c3 ? EPI_SIGMOID : EPI_SILU;
     switch (epi) {
-        case EPI_SOFTPLUS: return acc > 20.0f ? acc : log1pf(__expf(acc));
+        case EPI_SOFTPLUS: return fast_softplus(acc);
         case EPI_SIGMOID: return 1.0f / (1.0f + __expf(-acc));
         case EPI_SILU: return acc / (1.0f + __expf(-acc));
         case EPI_SCALE: return acc * e.alpha;
@@ -174,6 +188,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EPI_WARPS][32 rows][STG_PITCH]
     const bool vec32 = e.out && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0);
+    const bool vec_res = e.epi == EPI_RESIDUAL && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
+                         (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & 15) == 0)));
     const bool vec16 = e.out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out16) & 7) == 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -288,6 +304,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
 #pragma unroll 1
             for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
                 const int col0 = n0 + c0;
+                // EPI_RESIDUAL reads two more fp32 arrays with the output's access pattern: issue those loads first so
+                // they are in flight during the TMEM load and the transpose
+                float4 pre_add[8], pre_res[8];
+                const bool prefetch = e.epi == EPI_RESIDUAL && interior && vec_res;
+                if (prefetch) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const size_t ro = (size_t)(rbase + rsub + i * 4);
+                        pre_add[i] = *reinterpret_cast<const float4*>(e.add_in + ro * e.ld_add + col0 + cq);
+                        pre_res[i] = e.res_in ? *reinterpret_cast<const float4*>(e.res_in + ro * e.ld_res + col0 + cq)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
                 float v[32];
                 if (col0 < e.N) tcgen05_ld_32x32(taddr + (uint32_t)c0, v);  // warp-uniform
                 if (!released && (c0 + 32 >= HALF_COLS || col0 + 32 >= e.N)) {
@@ -310,7 +339,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 switch (kind) {
                     case EPI_SOFTPLUS:
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = v[j] > 20.0f ? v[j] : log1pf(__expf(v[j]));
+                        for (int j = 0; j < 32; ++j) v[j] = fast_softplus(v[j]);
                         break;
                     case EPI_SIGMOID:
 #pragma unroll
@@ -334,7 +363,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                     *reinterpret_cast<float4*>(stg + lane * STG_PITCH + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 __syncwarp();
                 const int gcol = col0 + cq;
-                if (interior && kind != -1 && vec32 && (!e.out16 || vec16)) {
+                if (interior && kind != -1 && (!e.out || vec32) && (!e.out16 || vec16) && (kind != EPI_RESIDUAL || vec_res)) {
                     float* gp = e.out ? e.out + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
                     __nv_bfloat16* bp = e.out16 ? e.out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
                     const float* sp = stg + rsub * STG_PITCH + cq;
@@ -346,6 +375,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                             if (e.epi == EPI_ADD_OUT) {
                                 float4 pv = *g4;
                                 val.x += pv.x, val.y += pv.y, val.z += pv.z, val.w += pv.w;
+                            } else if (e.epi == EPI_RESIDUAL) {
+                                const float4 av = pre_add[i];
+                                val.x += av.x, val.y += av.y, val.z += av.z, val.w += av.w;
+                                if (e.res_in) {
+                                    const float4 rv = pre_res[i];
+                                    val.x = fmaf(e.res_scale, val.x, rv.x), val.y = fmaf(e.res_scale, val.y, rv.y);
+                                    val.z = fmaf(e.res_scale, val.z, rv.z), val.w = fmaf(e.res_scale, val.w, rv.w);
+                                }
                             }
                             *g4 = val;
                         }
@@ -368,6 +405,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         for (int q = 0; q < 4; ++q) {
                             if (gcol + q >= e.N) continue;
                             if (kind == -1) o[q] = fast_epilogue(e, o[q], gcol + q, 0.0f);
+                            if (e.epi == EPI_RESIDUAL) {
+                                o[q] += e.add_in[(size_t)grow * e.ld_add + gcol + q];
+                                if (e.res_in) o[q] = fmaf(e.res_scale, o[q], e.res_in[(size_t)grow * e.ld_res + gcol + q]);
+                            }
                             if (e.out) {
                                 float* gp = e.out + (size_t)grow * e.ldo + gcol + q;
                                 if (e.epi == EPI_ADD_OUT) o[q] += *gp;
@@ -479,6 +520,18 @@ int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, f
     GemmEpilogue e{};
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = epi, e.alpha = alpha;
+    return dispatch(ctx, x16, w16, e);
+}
+
+// out = res_in ? res_in + res_scale * (X W^T + add_in) : X W^T + add_in   (all fp32 [M, N] dense)
+int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const float* add_in,
+                                  const float* res_in, float res_scale, size_t M, size_t N, size_t K) {
+    int32_t rc = check_shape(ctx, x16, w16, M, N, K);
+    if (rc) return rc;
+    GemmEpilogue e{};
+    e.out = out, e.out16 = nullptr, e.ldo = N, e.ld16 = 0;
+    e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = EPI_RESIDUAL, e.alpha = 1.0f;
+    e.add_in = add_in, e.res_in = res_in, e.ld_add = N, e.ld_res = N, e.res_scale = res_scale;
     return dispatch(ctx, x16, w16, e);
 }
 

@@ -83,6 +83,9 @@ int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, fl
 // gemm_tcgen05.cu: bf16 operands [rows, K] row-major, fp32 accumulate in TMEM; out fp32 [M, ldo] and/or bf16 [M, N]
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
                          size_t K, size_t ldo, int epi, float alpha);
+// MLP output with both residuals fused: out = res_in ? res_in + res_scale*(X W^T + add_in) : X W^T + add_in
+int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const float* add_in,
+                                  const float* res_in, float res_scale, size_t M, size_t N, size_t K);
 // fp32-accurate product of operands pre-split into three bf16 pieces: a16 [M, 3K], b16 [N, 3K] (six partial products)
 int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
                                 size_t N, size_t K, size_t ldo);

@@ -159,11 +159,16 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         if ((rc = dense(m, ws.z, ws.z_bf16, b.w[T_MLP_W1], b.w1_bf16, exact ? ws.mlp_act : nullptr, rows, 2 * m->d, m->d, 2 * m->d,
                         EPI_SILU, 1.0f, exact ? nullptr : ws.act_bf16)))
             return rc;
-        if ((rc = dense(m, ws.mlp_act, ws.act_bf16, b.w[T_MLP_W2], b.w2_bf16, ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
-        // depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
-        if ((rc = launch_residual(ctx, l == 0 ? nullptr : feat_in, ws.z, feat_out, rows * (size_t)d,
-                                  l == 0 ? 1.0f : m->residual_scales[l - 1])))
-            return rc;
+        // MLP down projection + residual, then depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
+        const float rscale = l == 0 ? 1.0f : m->residual_scales[l - 1];
+        if (exact) {
+            if ((rc = launch_gemm_exact(ctx, ws.mlp_act, b.w[T_MLP_W2], ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
+            if ((rc = launch_residual(ctx, l == 0 ? nullptr : feat_in, ws.z, feat_out, rows * (size_t)d, rscale))) return rc;
+        } else {
+            if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2_bf16, feat_out, ws.z, l == 0 ? nullptr : feat_in, rscale, rows,
+                                                m->d, 2 * m->d)))
+                return rc;
+        }
         feat_in = feat_out;
         feat_out = (feat_out == ws.feat_a) ? ws.feat_b : ws.feat_a;
     }
