@@ -185,6 +185,38 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
                               size_t top_k, float* q_pnc, float* q_norm, float* weights, float* m_val,
                               float* min_dist, uint32_t flags);
 
+/* ------------------------------------------------------------------ bank write and plastic fast weights */
+
+/*
+ * `n` ORDERED protected inserts into one bank, gate and copy fused in one kernel. Replaces
+ * `insert_protected_with_device` (src/memory.rs:315-342), `apply_refractory_overwrite` (src/defense.rs:45-67) and
+ * the ring insert (src/memory.rs:268-303) as called by `insert_training_memory_at` (src/pssa.rs:3705-3737).
+ * All DEVICE pointers: keys [cap,d_key], norm_sq [cap], values [cap,d_val], confidence [cap], last_seen_step [cap]
+ * (u64), meta = {count, write_head} (u64, updated), key_pnc [n,d_key] (points inside the ball), val [n,d_val],
+ * surprise [n], step [n] (u64). slots_out [n] (i64, NULL to skip): the slot written, or -1 when the slot defended
+ * itself. While count < capacity a write appends; afterwards the ring head is gated: gain = max((1-exp(-dt/60))^2,
+ * 0.005), damage = 0.08*surprise*gain; confidence > damage keeps the slot (confidence -= damage), otherwise the
+ * slot is overwritten, confidence = 1 and the head advances.
+ *
+ * winning_slots (NULL for the behaviour above) selects the retrieval benchmark's variant, which is NOT a reference
+ * code path: write i gates slot winning_slots[i] (the caller's nearest slot) instead of the ring head, and a
+ * successful write is the rank-1 update values[slot] += eta * (val - values[slot]); keys are left untouched.
+ */
+int32_t pssa_b200_bank_insert_protected_dev(pssa_b200_ctx* ctx, float* keys, float* norm_sq, float* values,
+                                            float* confidence, uint64_t* last_seen_step, uint64_t* meta,
+                                            size_t capacity, size_t d_key, size_t d_val, const float* key_pnc,
+                                            const float* val, const float* surprise, const uint64_t* step, size_t n,
+                                            int64_t* slots_out, const uint32_t* winning_slots, float eta);
+/*
+ * Hebbian rank-1 update of the adapter's fast weights, `dream_replay_value` (src/pssa.rs:1814-1832) after the
+ * block forward: rate = 0.02/(1+|value|), err = clamp(value - ad_out, -4, 4), up_fast[i,r] += rate*err_i*ad_act[r].
+ * DEVICE pointers: up_fast [d, rank], value [d], ad_out [d], ad_act [rank].
+ */
+int32_t pssa_b200_adapter_plastic_update_dev(pssa_b200_ctx* ctx, float* up_fast, const float* value,
+                                             const float* ad_out, const float* ad_act, size_t d, size_t rank);
+/* `PlasticAdapterV2::consolidate` (src/adapter.rs:65-72): slow += alpha*fast; fast *= (1-alpha). DEVICE pointers. */
+int32_t pssa_b200_adapter_consolidate_dev(pssa_b200_ctx* ctx, float* up_fast, float* up_slow, size_t n, float alpha);
+
 /* ------------------------------------------------------------------ dense product */
 
 /* Epilogue applied to every output of pssa_b200_gemm_xwt (the reference's elementwise kernels

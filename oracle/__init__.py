@@ -111,6 +111,8 @@ def lib() -> C.CDLL:
         L.pssa_oracle_rawbank_array.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_size_t)]
         L.pssa_oracle_rawbank_meta.argtypes = [C.c_void_p, _u64p, _u64p]
         L.pssa_oracle_rawbank_set_meta.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, _fp, _u64p]
+        L.pssa_oracle_rawbank_plastic_write.restype = C.c_long
+        L.pssa_oracle_rawbank_plastic_write.argtypes = [C.c_void_p, C.c_size_t, _fp, C.c_float, C.c_uint64, C.c_float]
         L.pssa_oracle_greedy.restype = C.c_long
         L.pssa_oracle_greedy.argtypes = [_fp, C.c_size_t]
         L.pssa_oracle_hardware_threads.restype = C.c_int
@@ -357,6 +359,11 @@ class RawBank:
     def insert_protected(self, key, val, surprise, step):
         r = lib().pssa_oracle_rawbank_insert_protected(self.h, fptr(np.asarray(key, np.float32)),
                                                        fptr(np.asarray(val, np.float32)), surprise, step)
+        return None if r < 0 else int(r)
+
+    def plastic_write(self, slot, val, surprise, step, eta):
+        """Winning-slot rank-1 write of the retrieval benchmark configuration (restatement only, not in the reference)."""
+        r = lib().pssa_oracle_rawbank_plastic_write(self.h, slot, fptr(np.asarray(val, np.float32)), surprise, step, eta)
         return None if r < 0 else int(r)
 
     def set_top_k(self, k):

@@ -386,6 +386,25 @@ void pssa_oracle_rawbank_set_meta(void* b, uint64_t count, uint64_t head, const 
     }
 }
 
+// BASELINE config 3's "winning-slot rank-1 write": NOT a reference code path (the reference overwrites the ring
+// head, src/memory.rs:315-342). Defined here so the GPU variant has a restatement to be compared with: the gate of
+// src/defense.rs:45-67 applied to `slot`; on a successful write values[slot] += eta * (val - values[slot]).
+long pssa_oracle_rawbank_plastic_write(void* b, size_t slot, const float* val, float surprise, uint64_t step, float eta) {
+    Bank* k = (Bank*)b;
+    uint64_t delta_t = step >= k->last_seen_step[slot] ? step - k->last_seen_step[slot] : 0;
+    float damage = 0.08f * surprise * refractory_gain(delta_t, 60.0f);
+    if (k->confidence[slot] > damage) {
+        k->confidence[slot] -= damage;
+        k->last_seen_step[slot] = step;
+        return -1;
+    }
+    k->confidence[slot] = 1.0f;
+    k->last_seen_step[slot] = step;
+    float* v = &k->values[slot * k->dim_val];
+    for (size_t i = 0; i < k->dim_val; ++i) v[i] = v[i] + eta * (val[i] - v[i]);
+    return (long)slot;
+}
+
 long pssa_oracle_greedy(const float* logits, size_t v) { return greedy_token(logits, v); }
 
 int pssa_oracle_hardware_threads() { return (int)std::thread::hardware_concurrency(); }

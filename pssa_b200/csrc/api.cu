@@ -398,6 +398,49 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
     return PSSA_B200_OK;
 }
 
+// ------------------------------------------------------------------ bank write and plastic fast weights
+
+int32_t pssa_b200_bank_insert_protected_dev(pssa_b200_ctx* ctx, float* keys, float* norm_sq, float* values, float* confidence,
+                                            uint64_t* last_seen_step, uint64_t* meta, size_t capacity, size_t d_key,
+                                            size_t d_val, const float* key_pnc, const float* val, const float* surprise,
+                                            const uint64_t* step, size_t n, int64_t* slots_out,
+                                            const uint32_t* winning_slots, float eta) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    if (capacity == 0 || d_key == 0 || d_val == 0 || capacity > 0x7fffffff || d_key > 0x7fffffff || d_val > 0x7fffffff)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "memory dimensions and capacity must be positive");  // src/memory.rs:36-39
+    if (!keys || !norm_sq || !values || !confidence || !last_seen_step || !meta || !key_pnc || !val || !surprise || !step)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 bank write: null buffer");
+    if (winning_slots && !(eta >= 0.0f && eta <= 1.0f))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 bank write: eta must be in [0, 1]");
+    if (n == 0) return PSSA_B200_OK;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    BankWriteParams p{};
+    p.keys = keys, p.norm_sq = norm_sq, p.values = values, p.confidence = confidence;
+    p.last_seen = (unsigned long long*)last_seen_step, p.meta = (unsigned long long*)meta;
+    p.cap = (int)capacity, p.dk = (int)d_key, p.dv = (int)d_val;
+    p.key_pnc = key_pnc, p.val = val, p.surprise = surprise, p.step = (const unsigned long long*)step, p.n = n;
+    p.slots_out = (long long*)slots_out, p.winning_slots = winning_slots, p.eta = eta;
+    return launch_bank_insert_protected(ctx, p);
+}
+
+int32_t pssa_b200_adapter_plastic_update_dev(pssa_b200_ctx* ctx, float* up_fast, const float* value, const float* ad_out,
+                                             const float* ad_act, size_t d, size_t rank) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    if (d == 0 || rank == 0 || d > 0x7fffffff / (rank ? rank : 1)) return fail(ctx, PSSA_B200_ERR_SHAPE, "adapter dimensions must be positive and fit i32");
+    if (!up_fast || !value || !ad_out || !ad_act) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 plastic update: null buffer");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    return launch_plastic_update(ctx, up_fast, value, ad_out, ad_act, (int)d, (int)rank);
+}
+
+int32_t pssa_b200_adapter_consolidate_dev(pssa_b200_ctx* ctx, float* up_fast, float* up_slow, size_t n, float alpha) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    if (!(alpha >= 0.0f && alpha <= 1.0f)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "consolidation alpha must be in [0, 1]");
+    if (!up_fast || !up_slow) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 consolidate: null buffer");
+    if (n == 0) return PSSA_B200_OK;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    return launch_consolidate(ctx, up_fast, up_slow, n, alpha);
+}
+
 // ------------------------------------------------------------------ dense product
 
 // backend.rs:11-38 (checked_gemm_sizes)

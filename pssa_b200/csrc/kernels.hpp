@@ -76,6 +76,29 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
 // values [cap, dv] fp32 -> v_split [dv, 3*cap] bf16 (transpose + three-way split); once per bank upload
 int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv);
 
+// plastic_write.cu
+struct BankWriteParams {
+    float* keys;                 // [cap, dk]
+    float* norm_sq;              // [cap]
+    float* values;               // [cap, dv]
+    float* confidence;           // [cap]
+    unsigned long long* last_seen;  // [cap]
+    unsigned long long* meta;    // {count, write_head}
+    int cap, dk, dv;
+    const float* key_pnc;        // [n, dk]
+    const float* val;            // [n, dv]
+    const float* surprise;       // [n]
+    const unsigned long long* step;  // [n]
+    size_t n;
+    long long* slots_out;        // [n] written slot or -1 (defended); may be null
+    const unsigned* winning_slots;  // null = reference behaviour (ring head); else the slot each write targets
+    float eta;                   // rank-1 step of the winning-slot mode
+};
+int32_t launch_bank_insert_protected(pssa_b200_ctx* ctx, const BankWriteParams& p);
+int32_t launch_plastic_update(pssa_b200_ctx* ctx, float* up_fast, const float* value, const float* ad_out, const float* ad_act,
+                              int d, int rank);
+int32_t launch_consolidate(pssa_b200_ctx* ctx, float* up_fast, float* up_slow, size_t n, float alpha);
+
 // gemm_exact.cu: out[M, ldo] (first N columns) = epilogue(X[M,K] * W[N,K]^T), fp32, dot_slice order
 int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, float* out, size_t M, size_t N, size_t K,
                           size_t ldo, int epi, float alpha);

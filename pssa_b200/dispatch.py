@@ -190,6 +190,21 @@ class B200Dispatch:
             N.MEM_EXACT if exact else 0))
 
 
+    # ---- bank write / plastic fast weights (device pointers)
+    def bank_insert_protected_dev(self, keys, norm_sq, values, confidence, last_seen_step, meta, capacity, d_key, d_val,
+                                  key_pnc, val, surprise, step, n, slots_out=None, winning_slots=None, eta=0.0):
+        """Ordered protected inserts (`insert_protected`, src/memory.rs:305-342); see include/pssa_b200.h."""
+        self._check(self._lib.pssa_b200_bank_insert_protected_dev(
+            self._h, _ptr(keys), _ptr(norm_sq), _ptr(values), _ptr(confidence), _ptr(last_seen_step), _ptr(meta), capacity,
+            d_key, d_val, _ptr(key_pnc), _ptr(val), _ptr(surprise), _ptr(step), n, _ptr(slots_out), _ptr(winning_slots), eta))
+
+    def adapter_plastic_update_dev(self, up_fast, value, ad_out, ad_act, d, rank):
+        self._check(self._lib.pssa_b200_adapter_plastic_update_dev(self._h, _ptr(up_fast), _ptr(value), _ptr(ad_out),
+                                                                   _ptr(ad_act), d, rank))
+
+    def adapter_consolidate_dev(self, up_fast, up_slow, n, alpha):
+        self._check(self._lib.pssa_b200_adapter_consolidate_dev(self._h, _ptr(up_fast), _ptr(up_slow), n, alpha))
+
     # ---- dense product
     def dispatch_gemm_into(self, x, w, m, n, k, batch, out, epilogue=N.EPI_NONE, alpha=1.0, precision=N.PRECISION_FP32_EXACT):
         """`GpuDispatch::dispatch_gemm_into` (src/backend.rs:1087-1110): Y[batch,M,N] = X[batch,M,K] * W[N,K]^T on host
