@@ -68,6 +68,17 @@ int32_t pssa_b200_ctx_reserve(pssa_b200_ctx* ctx, size_t bytes);
  * records it and returns. This reads and clears that record: PSSA_B200_OK or PSSA_B200_ERR_TIMEOUT. */
 int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx);
 
+/*
+ * Per-kernel device timing, the role of the reference's `StageTrace` spans (src/training_diagnostics.rs:74-125,
+ * enabled there by PSSA_CUDA_PROFILE=1) with CUDA events instead of wall clock. Between begin and end an event is
+ * recorded after every kernel this library launches on `ctx`; end synchronises and aggregates the time between
+ * consecutive events by kernel name. Rows are read back one at a time.
+ */
+int32_t pssa_b200_ctx_profile_begin(pssa_b200_ctx* ctx);
+int32_t pssa_b200_ctx_profile_end(pssa_b200_ctx* ctx, uint32_t* n_rows);
+int32_t pssa_b200_ctx_profile_row(pssa_b200_ctx* ctx, uint32_t index, const char** name, uint64_t* launches,
+                                  double* ms);
+
 /* Force the number of time chunks of the scan (0 = automatic). A test hook: with more than one
  * chunk the scan runs its reduce / carry / apply passes even on shapes that would not need them. */
 int32_t pssa_b200_ctx_set_scan_chunks(pssa_b200_ctx* ctx, uint32_t chunks);
@@ -328,6 +339,16 @@ int32_t pssa_b200_model_prefill(pssa_b200_model* model, uint32_t stream, const u
 int32_t pssa_b200_model_prefill_batch(pssa_b200_model* model, const uint64_t* ids, const uint32_t* offsets,
                                       const uint32_t* lengths, const uint32_t* streams, size_t n_lanes, float* logits,
                                       uint64_t* greedy);
+/*
+ * Device-resident form of prefill_batch for callers that already hold token ids on the GPU (and want the logits
+ * there): ids_dev [total rows] u32 DEVICE pointer, logits_dev [n_lanes, V] and greedy_dev [n_lanes] u32 DEVICE
+ * pointers (either may be NULL); offsets / lengths / streams are HOST arrays as above. Ids are NOT range checked
+ * (the caller vouches for ids < V); the whole batch must fit one pass (total rows <= max_rows). Work is only
+ * enqueued on the context's stream: nothing is synchronised.
+ */
+int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* model, const uint32_t* ids_dev, const uint32_t* offsets,
+                                          const uint32_t* lengths, const uint32_t* streams, size_t n_lanes,
+                                          float* logits_dev, uint32_t* greedy_dev);
 /* `forward_inference` (src/pssa.rs:2387-2391) for n streams at once: one token each. */
 int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* streams, const uint64_t* ids, size_t n,
                                     float* logits, uint64_t* greedy);

@@ -70,6 +70,8 @@ def lib() -> C.CDLL:
         L.pssa_oracle_chunk_forward.argtypes = [C.c_void_p, _u64p, _u64p, C.c_size_t, _fp]
         L.pssa_oracle_generate_greedy.restype = C.c_long
         L.pssa_oracle_generate_greedy.argtypes = [C.c_void_p, _u64p, C.c_size_t, C.c_size_t, _u64p, _fp]
+        L.pssa_oracle_prefill_lanes_timed.restype = C.c_double
+        L.pssa_oracle_prefill_lanes_timed.argtypes = [C.c_void_p, _u64p, C.c_size_t, C.c_size_t, C.c_int, _fp]
         L.pssa_oracle_consolidate.argtypes = [C.c_void_p, C.c_int, C.c_float]
         L.pssa_oracle_dream_replay.argtypes = [C.c_void_p, C.c_int, _fp]
         L.pssa_oracle_dot.restype = C.c_float
@@ -239,6 +241,14 @@ class Model:
         if rc < 0:
             raise RuntimeError("oracle generation failed")
         return out, float(gap.value)
+
+    def prefill_lanes_timed(self, ids, threads):
+        """Token-serial prefill of independent lanes ids [n, T] on `threads` host threads; returns (seconds, logits)."""
+        ids = np.ascontiguousarray(ids, np.uint64)
+        n, T = ids.shape
+        logits = np.empty((n, self.d_vocab), np.float32)
+        sec = lib().pssa_oracle_prefill_lanes_timed(self.h, u64ptr(ids), n, T, threads, fptr(logits))
+        return float(sec), logits
 
     def state(self) -> np.ndarray:
         """Recurrent carry in the reference's `[block][d*s]` order (pssa.rs:2263-2310)."""

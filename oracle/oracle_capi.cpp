@@ -226,6 +226,29 @@ long pssa_oracle_generate_greedy(void* h, const uint64_t* ids, size_t n, size_t 
     return (long)n_new;
 }
 
+// CPU baseline for batched prefill: `n_lanes` independent sequences of `T` tokens (ids [n_lanes, T]) through
+// token-serial prefill_inference, lanes spread over `threads` host threads. Every thread works on its own copy of
+// the model (the carry is per lane; the weights are duplicated), made before the clock starts. Returns seconds.
+double pssa_oracle_prefill_lanes_timed(void* h, const uint64_t* ids, size_t n_lanes, size_t T, int threads, float* last_logits) {
+    Model* base = (Model*)h;
+    size_t nt = std::max<size_t>(1, std::min<size_t>((size_t)threads, n_lanes));
+    std::vector<Model> copies(nt, *base);
+    size_t v = base->cfg.d_vocab;
+    auto t0 = std::chrono::steady_clock::now();
+    std::vector<std::thread> pool;
+    for (size_t w = 0; w < nt; ++w)
+        pool.emplace_back([&, w] {
+            std::vector<float> lg(v);
+            for (size_t l = w; l < n_lanes; l += nt) {
+                copies[w].reset_recurrent_state();
+                copies[w].prefill_inference(ids + l * T, T, lg.data(), nullptr);
+                if (last_logits) std::memcpy(last_logits + l * v, lg.data(), v * sizeof(float));
+            }
+        });
+    for (auto& t : pool) t.join();
+    return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+}
+
 void pssa_oracle_consolidate(void* h, int layer, float alpha) { ((Model*)h)->blocks[layer].consolidate(alpha); }
 void pssa_oracle_dream_replay(void* h, int layer, const float* value) {
     ((Model*)h)->blocks[layer].dream_replay_value(value);

@@ -55,6 +55,11 @@ SIGNATURES = {
     "pssa_b200_model_set_state": (C.c_int32, [_vp, C.c_uint32, _vp, _sz]),
     "pssa_b200_model_prefill": (C.c_int32, [_vp, C.c_uint32, _vp, _sz, _vp, C.POINTER(_sz), _vp, _vp]),
     "pssa_b200_model_prefill_batch": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "pssa_b200_model_prefill_batch_dev": (C.c_int32, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "pssa_b200_ctx_profile_begin": (C.c_int32, [_vp]),
+    "pssa_b200_ctx_profile_end": (C.c_int32, [_vp, C.POINTER(C.c_uint32)]),
+    "pssa_b200_ctx_profile_row": (C.c_int32, [_vp, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64),
+                                              C.POINTER(C.c_double)]),
     "pssa_b200_model_decode_step": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, _vp]),
 }
 SSM_EXACT = 1

@@ -28,6 +28,25 @@ int32_t arena_reserve(pssa_b200_ctx* ctx, size_t bytes) {
     return PSSA_B200_OK;
 }
 
+static cudaEvent_t prof_event(pssa_b200_ctx* ctx) {
+    cudaEvent_t e = nullptr;
+    if (!ctx->prof_pool.empty()) {
+        e = ctx->prof_pool.back();
+        ctx->prof_pool.pop_back();
+    } else if (cudaEventCreate(&e) != cudaSuccess) {
+        e = nullptr;
+    }
+    return e;
+}
+
+void profile_record(pssa_b200_ctx* ctx, const char* kernel) {
+    cudaEvent_t e = prof_event(ctx);
+    if (!e) return;
+    cudaEventRecord(e, ctx->stream);
+    ctx->prof_events.push_back(e);
+    ctx->prof_names.push_back(kernel);
+}
+
 // RAII device buffers for the host-pointer entry points (freed on every exit path)
 struct DeviceBuf {
     void* p = nullptr;
@@ -85,6 +104,8 @@ void pssa_b200_ctx_destroy(pssa_b200_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->arena) cudaFree(ctx->arena);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
+    for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -507,6 +528,54 @@ int32_t pssa_b200_gemm_xwt(pssa_b200_ctx* ctx, const float* x, const float* w, s
     }
     PSSA_CUDA(ctx, cudaStreamSynchronize(st));
     return rc;
+}
+
+int32_t pssa_b200_ctx_profile_begin(pssa_b200_ctx* ctx) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    for (cudaEvent_t e : ctx->prof_events) ctx->prof_pool.push_back(e);
+    ctx->prof_events.clear();
+    ctx->prof_names.clear();
+    cudaEvent_t e = prof_event(ctx);
+    if (!e) return fail(ctx, PSSA_B200_ERR_CUDA, "profile: cannot create an event");
+    PSSA_CUDA(ctx, cudaEventRecord(e, ctx->stream));
+    ctx->prof_events.push_back(e);
+    ctx->profiling = true;
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_ctx_profile_end(pssa_b200_ctx* ctx, uint32_t* n_rows) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    ctx->profiling = false;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ctx->prof_rows.clear();
+    for (size_t i = 0; i + 1 < ctx->prof_events.size(); ++i) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, ctx->prof_events[i], ctx->prof_events[i + 1]) != cudaSuccess) continue;
+        const char* name = ctx->prof_names[i];
+        bool found = false;
+        for (auto& r : ctx->prof_rows)
+            if (r.name == name) {
+                r.launches += 1, r.ms += ms, found = true;
+                break;
+            }
+        if (!found) ctx->prof_rows.push_back({name, 1, (double)ms});
+    }
+    for (cudaEvent_t e : ctx->prof_events) ctx->prof_pool.push_back(e);
+    ctx->prof_events.clear();
+    ctx->prof_names.clear();
+    if (n_rows) *n_rows = (uint32_t)ctx->prof_rows.size();
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_ctx_profile_row(pssa_b200_ctx* ctx, uint32_t index, const char** name, uint64_t* launches, double* ms) {
+    if (!ctx || !name || !launches || !ms) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "profile_row: null argument");
+    if (index >= ctx->prof_rows.size()) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "profile_row: index %u of %zu", index, ctx->prof_rows.size());
+    *name = ctx->prof_rows[index].name.c_str();
+    *launches = ctx->prof_rows[index].launches;
+    *ms = ctx->prof_rows[index].ms;
+    return PSSA_B200_OK;
 }
 
 /* Reads and clears the device status word written by bounded waits (0 = none expired). */

@@ -6,6 +6,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <vector>
 
 #include "../../include/pssa_b200.h"
 
@@ -25,6 +26,19 @@ struct pssa_b200_ctx {
     // device status word for bounded waits (0 = ok)
     int* status_dev = nullptr;
     int scan_chunks = 0;  // 0 = choose automatically; tests force the multi-chunk passes with it
+    // Stage profile (the role of the reference's StageTrace, src/training_diagnostics.rs:74-125, with device
+    // events instead of wall clock): while enabled, an event is recorded after every kernel launch; the time
+    // between consecutive events on the (serial) stream is attributed to the kernel launched in between.
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;      // prof_events[0] is the start mark
+    std::vector<const char*> prof_names;       // prof_names[i] ran between events i and i+1
+    std::vector<cudaEvent_t> prof_pool;        // recycled events
+    struct ProfRow {
+        std::string name;
+        uint64_t launches;
+        double ms;
+    };
+    std::vector<ProfRow> prof_rows;            // result of the last profile_end
 };
 
 namespace pssa {
@@ -75,8 +89,10 @@ inline void* arena_take(pssa_b200_ctx* ctx, size_t bytes) {
 inline size_t arena_round(size_t bytes) { return (bytes + 255) & ~size_t(255); }
 
 // Launch bookkeeping: every kernel launch of this library goes through here.
+void profile_record(pssa_b200_ctx* ctx, const char* kernel);  // api.cu
 inline int32_t after_launch(pssa_b200_ctx* ctx, const char* kernel) {
     ctx->launches += 1;
+    if (ctx->profiling) profile_record(ctx, kernel);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(ctx, e, kernel);
     return PSSA_B200_OK;

@@ -296,6 +296,60 @@ int32_t pssa_b200_model_prefill_batch(pssa_b200_model* m, const uint64_t* ids, c
     return run_lanes(m, ids, offsets, lengths, streams, n_lanes, logits, greedy, nullptr, nullptr, nullptr);
 }
 
+int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* ids_dev, const uint32_t* offsets, const uint32_t* lengths,
+                                          const uint32_t* streams, size_t n_lanes, float* logits_dev, uint32_t* greedy_dev) {
+    if (!m || !ids_dev || !offsets || !lengths) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "prefill_batch_dev: null argument");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (n_lanes == 0 || n_lanes > 0x7fffffff) return fail(ctx, PSSA_B200_ERR_SHAPE, "prefill_batch: lane count must be in 1..2^31-1");
+    std::vector<bool> seen(m->max_streams, false);
+    std::vector<uint32_t> h_off(n_lanes), h_len(n_lanes), h_slot(n_lanes), h_last;
+    std::vector<size_t> head_lane;
+    size_t rows = 0, span = 0;
+    for (size_t l = 0; l < n_lanes; ++l) {
+        uint32_t slot = streams ? streams[l] : (uint32_t)l;
+        if (slot >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "lane %zu uses stream %u outside %u streams", l, slot, m->max_streams);
+        if (seen[slot]) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u appears in more than one lane", slot);
+        seen[slot] = true;
+        h_off[l] = offsets[l], h_len[l] = lengths[l], h_slot[l] = slot;
+        rows += lengths[l];
+        span = std::max(span, (size_t)offsets[l] + lengths[l]);
+        if (lengths[l] > 0) {
+            h_last.push_back(offsets[l] + lengths[l] - 1);
+            head_lane.push_back(l);
+        }
+    }
+    if (rows == 0) return PSSA_B200_OK;
+    if (span > m->max_rows)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "prefill_batch_dev: %zu token rows exceed one pass of %zu rows (set_max_rows)", span, m->max_rows);
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t rc;
+    if ((rc = ensure_workspace(m, span, n_lanes))) return rc;
+    Workspace& ws = m->ws;
+    cudaStream_t st = ctx->stream;
+    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.ids, ids_dev, span * 4, cudaMemcpyDeviceToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, h_off.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_len, h_len.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, h_slot.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
+    float* feats = nullptr;
+    if ((rc = forward_rows(m, span, n_lanes, h_off.data(), h_len.data(), &feats))) return rc;
+    if (logits_dev || greedy_dev) {
+        if ((rc = head_rows(m, feats, h_last.size(), greedy_dev != nullptr))) return rc;
+        size_t i = 0;
+        while (i < head_lane.size()) {  // contiguous runs of non-empty lanes go out in one copy
+            size_t j = i;
+            while (j + 1 < head_lane.size() && head_lane[j + 1] == head_lane[j] + 1) ++j;
+            if (logits_dev)
+                PSSA_CUDA(ctx, cudaMemcpyAsync(logits_dev + head_lane[i] * m->v, ws.logits + i * m->v, (j - i + 1) * m->v * 4,
+                                               cudaMemcpyDeviceToDevice, st));
+            if (greedy_dev)
+                PSSA_CUDA(ctx, cudaMemcpyAsync(greedy_dev + head_lane[i], ws.greedy + i, (j - i + 1) * 4, cudaMemcpyDeviceToDevice, st));
+            i = j + 1;
+        }
+    }
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_model_prefill(pssa_b200_model* m, uint32_t stream, const uint64_t* ids, size_t n, float* logits, size_t* processed,
                                 int32_t (*cancelled)(void*), void* cancel_arg) {
     if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");

@@ -230,6 +230,21 @@ class B200Dispatch:
         self._check(self._lib.pssa_b200_gemm_xwt_dev(self._h, _ptr(x), _ptr(w), rows, n, k, _ptr(out), ldo or n, epilogue,
                                                      alpha, precision))
 
+    def profile_begin(self):
+        """Start per-kernel device timing (the reference's StageTrace spans, src/training_diagnostics.rs:74-125)."""
+        self._check(self._lib.pssa_b200_ctx_profile_begin(self._h))
+
+    def profile_end(self):
+        """Stop timing; returns {kernel name: (launches, total ms)}."""
+        n = C.c_uint32()
+        self._check(self._lib.pssa_b200_ctx_profile_end(self._h, C.byref(n)))
+        rows = {}
+        for i in range(n.value):
+            name, launches, ms = C.c_char_p(), C.c_uint64(), C.c_double()
+            self._check(self._lib.pssa_b200_ctx_profile_row(self._h, i, C.byref(name), C.byref(launches), C.byref(ms)))
+            rows[name.value.decode()] = (int(launches.value), float(ms.value))
+        return rows
+
     def poll_status(self):
         self._check(self._lib.pssa_b200_ctx_poll_status(self._h))
 

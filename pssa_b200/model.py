@@ -141,6 +141,15 @@ class PSSAModel:
                                                                 len(lanes), _ptr(logits), _ptr(greedy)))
         return logits, greedy
 
+    def prefill_batch_dev(self, ids_dev, offsets, lengths, streams=None, logits_dev=None, greedy_dev=None):
+        """Device-resident form: `ids_dev` (uint32), `logits_dev` [n, V] fp32 and `greedy_dev` [n] uint32 are device
+        buffers (torch tensors or raw pointers); offsets / lengths / streams are host arrays. Only enqueues work."""
+        offsets = np.ascontiguousarray(offsets, np.uint32)
+        lengths = np.ascontiguousarray(lengths, np.uint32)
+        st = None if streams is None else np.ascontiguousarray(streams, np.uint32)
+        self.gpu._check(self._lib.pssa_b200_model_prefill_batch_dev(self._h, _ptr(ids_dev), _ptr(offsets), _ptr(lengths),
+                                                                    _ptr(st), len(lengths), _ptr(logits_dev), _ptr(greedy_dev)))
+
     def decode_step(self, ids, streams=None, want_logits=True, want_greedy=False):
         ids = np.ascontiguousarray(ids, np.uint64)
         st = None if streams is None else np.ascontiguousarray(streams, np.uint32)
