@@ -33,8 +33,13 @@ namespace pssa {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kTileTokens = 8;
-constexpr int kStages = 4;
+// tokens per staged tile; the widest state split keeps 8 so three stages stay inside the shared memory of one SM
+template <int G>
+constexpr int kTileTokensFor = G >= 32 ? 8 : 16;
+// The 16-state fast configuration is capped at 64 registers so four CTAs (32 warps) share an SM: the kernel is bound by
+// dependent-issue latency, not by a pipe, and the extra warps are worth more than the 16 bytes of spill they cost.
+constexpr int kMinCtasFast = 4;
+constexpr int kStages = 3;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -52,8 +57,9 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 template <int ST, int G, bool EXACT, bool TAPE>
-__global__ void __launch_bounds__(kThreads) ssm_fused_kernel(SsmParams p) {
+__global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMinCtasFast : 1) ssm_fused_kernel(SsmParams p) {
     constexpr int CH = kThreads / G;  // channels per CTA
+    constexpr int kTileTokens = kTileTokensFor<G>;
     constexpr int LPG = 32 / G;       // lanes of a warp that share one state group
     constexpr int SG = ST + 4;        // shared-memory pitch of a state group (bank spreading)
     constexpr int SP = SG * G;        // floats per token row of B / C in shared memory
@@ -230,6 +236,7 @@ template <int ST, int G, bool EXACT, bool TAPE>
 int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
     constexpr int CH = kThreads / G;
     constexpr int SP = (ST + 4) * G;
+    constexpr int kTileTokens = kTileTokensFor<G>;
     size_t smem = (size_t)kStages * kTileTokens * (2 * CH + 2 * SP) * sizeof(float);
     auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE>;
     static bool attr_set = false;  // per instantiation; contexts share the device function

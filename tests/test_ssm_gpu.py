@@ -45,7 +45,7 @@ def test_single_lane_matches_ordered_recurrence(gpu, T, d, s, exact):
     assert np.array_equal(states[0], h0)
     assert np.array_equal(bar_b.view(np.uint32), ref_b.view(np.uint32))  # one rounded product in both modes
     assert rel_err(bar_a, ref_a) <= (2e-7 if exact else 6e-7)
-    tol = 5e-6 if exact else REL_TOL  # CUDA expf (<= 2 ulp) vs glibc expf: see DESIGN.md
+    tol = 5e-6 if exact else REL_TOL  # CUDA expf (<= 2 ulp) vs glibc expf, both within their documented error
     assert chan_err(states, ref_states, 0) <= tol
     assert chan_err(y, ref_y, 0) <= tol
     # without the tape outputs (the inference form) y is the same
