@@ -5,6 +5,7 @@ into the C ABI. numpy arrays are host buffers (the reference's `&[f32]` slices);
 take device pointers (ints) or objects with `.data_ptr()` (torch tensors) and only enqueue work.
 """
 import ctypes as C
+import weakref
 
 import numpy as np
 
@@ -45,7 +46,15 @@ class B200Dispatch:
         if stream is not None:
             self.set_stream(stream)
 
+    def _adopt(self, child):
+        """Objects that hold a pointer to this context (models) are closed before the context is."""
+        if not hasattr(self, "_children"):
+            self._children = weakref.WeakSet()
+        self._children.add(child)
+
     def close(self):
+        for child in list(getattr(self, "_children", ())):
+            child.close()
         if getattr(self, "_h", None):
             self._lib.pssa_b200_ctx_destroy(self._h)
             self._h = None

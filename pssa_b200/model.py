@@ -28,11 +28,13 @@ class PSSAModel:
         h = C.c_void_p()
         gpu._check(self._lib.pssa_b200_model_create(gpu._h, C.byref(cfg), streams, C.byref(h)))
         self._h = h
+        gpu._adopt(self)
         self.set_precision(precision)
 
     def close(self):
         if getattr(self, "_h", None):
-            self._lib.pssa_b200_model_destroy(self._h)
+            if getattr(self.gpu, "_h", None):  # a model never outlives its context
+                self._lib.pssa_b200_model_destroy(self._h)
             self._h = None
 
     def __del__(self):

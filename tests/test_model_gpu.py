@@ -156,3 +156,60 @@ def test_bf16_path_logits_within_tolerance_and_greedy_tokens(gpu):
             agree += int(gr[0]) == nxt
         tok = nxt
     assert agree == total
+
+
+def test_closing_the_context_first_closes_its_models():
+    """A model holds a pointer into its context; closing the context must retire the model rather than
+    leave it to free device memory through a dead context later."""
+    import pssa_b200
+    g = pssa_b200.B200Dispatch(0)
+    m = pssa_b200.PSSAModel(g, 1, 32, 16, 4, 4, 8)
+    g.close()
+    assert m._h is None
+    m.close()  # idempotent
+    del m
+
+
+def test_sharded_prefill_single_rank_matches_the_oracle(gpu):
+    """The lane-sharding front end on one rank (no process group): one logits row per prompt, empty prompts zero."""
+    from pssa_b200 import lanes as L
+    om, gm = make_pair(gpu, 2, 61, 24, 4, 8, 16, seed=5, streams=8)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(1, 61, n) for n in (9, 0, 4, 17, 1, 6, 6)]
+    gm.reset_recurrent_state()
+    got = L.sharded_prefill(gm, prompts, 1, 0)
+    assert got.shape == (7, 61) and not got[1].any()
+    for j, p in enumerate(prompts):
+        if len(p):
+            ref_m = om.clone()
+            ref_m.reset_recurrent_state()
+            _, _, ref = ref_m.prefill_inference(p)
+            assert scale_err(got[j], ref) <= 1e-5, j
+
+
+def test_device_resident_prefill_equals_the_host_entry_and_profile_rows_add_up(gpu):
+    """`prefill_batch_dev` (ids and logits stay in HBM, work only enqueued) returns the host entry's bits, and the
+    per-kernel profile counts every launch the context counted."""
+    import torch
+    om, gm = make_pair(gpu, 2, 80, 48, 16, 16, 20, seed=9, streams=3, precision=0)
+    lanes = [list((np.arange(n) * 5 + j) % 79 + 1) for j, n in enumerate([33, 7, 64])]
+    gm.reset_recurrent_state()
+    host_logits, host_greedy = gm.prefill_batch(lanes, want_greedy=True)
+    gm.reset_recurrent_state()
+    lengths = np.array([len(x) for x in lanes], np.uint32)
+    offsets = np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.uint32)
+    ids_dev = torch.tensor(np.concatenate(lanes).astype(np.int32), device="cuda", dtype=torch.int32)
+    logits_dev = torch.zeros(3, 80, device="cuda")
+    greedy_dev = torch.zeros(3, device="cuda", dtype=torch.int32)
+    gpu.set_stream(torch.cuda.current_stream())
+    n0 = gpu.launch_count()
+    gpu.profile_begin()
+    gm.prefill_batch_dev(ids_dev, offsets, lengths, None, logits_dev, greedy_dev)
+    torch.cuda.synchronize()
+    rows = gpu.profile_end()
+    launched = gpu.launch_count() - n0
+    gpu.set_stream(None)
+    assert np.array_equal(logits_dev.cpu().numpy().view(np.uint32), host_logits.view(np.uint32))
+    assert np.array_equal(greedy_dev.cpu().numpy().astype(np.uint64), host_greedy)
+    assert launched > 0 and sum(n for n, _ in rows.values()) == launched
+    assert all(ms >= 0 for _, ms in rows.values()) and any("ssm_fused" in k for k in rows)
