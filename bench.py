@@ -359,7 +359,7 @@ def run_b200(args):
                          "traffic": None, "peak_kind": f"of {peak_kind}"})
         cpu = None
         parity = None
-        if world == 1:
+        if world == 1 and not args.no_cpu:
             import oracle as O
             threads = max(1, O.lib().pssa_oracle_hardware_threads())
             om = oracle_model(tensors, banks)
@@ -398,13 +398,21 @@ def run_b200(args):
 
 
 def main():
+    global LANES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-extras", action="store_true", help="skip the operator-alone extras (N = 1)")
+    ap.add_argument("--lanes", type=int, default=LANES,
+                    help="sequences per GPU; anything but the default is a reduced case for profiler captures, not the benchmark")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and parity sample (profiler captures)")
     args = ap.parse_args()
+    if args.lanes != LANES:
+        global WORKLOAD
+        WORKLOAD = WORKLOAD.replace(f"{LANES} sequences", f"{args.lanes} sequences (REDUCED CASE, not the benchmark)")
+        LANES = args.lanes
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -42,12 +42,12 @@ struct SsmParams {
     size_t carry_stride;   // 0 = d*s
 };
 int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact);
-// 16-byte staging needs 16-byte aligned bases and row pitches / widths that are multiples of 4 floats
+// 16-byte staging and stores need 16-byte aligned bases and row pitches / widths that are multiples of 4 floats
 inline bool ssm_vector_ok(const SsmParams& p) {
     auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     size_t ldd = p.ld_delta ? p.ld_delta : (size_t)p.d, ldbc = p.ld_bc ? p.ld_bc : (size_t)p.s;
     return p.d % 4 == 0 && p.s % 4 == 0 && ldd % 4 == 0 && ldbc % 4 == 0 && al(p.delta) && al(p.x_norm) && al(p.b_proj) &&
-           al(p.c_proj);
+           al(p.c_proj) && al(p.y) && (reinterpret_cast<uintptr_t>(p.y_bf16) & 7) == 0;
 }
 
 // retrieve_poincare.cu

@@ -56,6 +56,28 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// Packed fp32 pairs (one instruction, two IEEE-rounded results): the kernel is bound by instruction issue, and the
+// per-state multiply / fma work is half the instruction stream.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 template <int ST, int G, bool EXACT, bool TAPE>
 __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMinCtasFast : 1) ssm_fused_kernel(SsmParams p) {
     constexpr int CH = kThreads / G;  // channels per CTA
@@ -160,17 +182,19 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
     for (int k = 0; k < kStages - 1; ++k) load_tile(k);
 
     for (int k = 0; k < ntiles; ++k) {
-        load_tile(k + kStages - 1);
-        cp_async_wait<kStages - 1>();
+        // tile k has landed once at most kStages-2 newer groups are in flight; the barrier also means every thread is
+        // done with tile k-1 (its stage is the one the prefetch below overwrites)
+        cp_async_wait<kStages - 2>();
         __syncthreads();
+        load_tile(k + kStages - 1);
         const int st = k % kStages;
         const int t0 = k * kTileTokens;
         const int nt = min(kTileTokens, len - t0);
-        const float* dd = sm_delta + st * kTileTokens * CH;
+        float* dd = sm_delta + st * kTileTokens * CH;
         const float* dx = sm_x + st * kTileTokens * CH;
         const float* db = sm_b + st * kTileTokens * SP + g * SG;
         const float* dc = sm_c + st * kTileTokens * SP + g * SG;
-        for (int tt = 0; tt < nt; ++tt) {
+        auto token = [&](int tt) {
             const float dl = dd[tt * CH + c];
             const float xv = dx[tt * CH + c];
             const size_t row = row0 + t0 + tt;
@@ -196,20 +220,25 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
                 }
             } else {
                 const float w = dl * xv;
+                const f32x2 dl2 = pack2(dl, dl), w2 = pack2(w, w);
+                f32x2 y2 = pack2(0.0f, 0.0f);
 #pragma unroll
-                for (int jj = 0; jj < ST; ++jj) {
-                    float a = ex2_approx(dl * A[jj]);
-                    h[jj] = fmaf(a, h[jj], w * bj[jj]);
-                    yp = fmaf(h[jj], cj[jj], yp);
-                    if (TAPE) av[jj] = a, bv[jj] = dl * bj[jj];
+                for (int jj = 0; jj < ST; jj += 2) {
+                    float e0, e1;
+                    unpack2(mul2(dl2, pack2(A[jj], A[jj + 1])), e0, e1);
+                    const float a0 = ex2_approx(e0), a1 = ex2_approx(e1);
+                    f32x2 h2 = fma2(pack2(a0, a1), pack2(h[jj], h[jj + 1]), mul2(w2, pack2(bj[jj], bj[jj + 1])));
+                    unpack2(h2, h[jj], h[jj + 1]);
+                    y2 = fma2(h2, pack2(cj[jj], cj[jj + 1]), y2);
+                    if (TAPE) av[jj] = a0, av[jj + 1] = a1, bv[jj] = dl * bj[jj], bv[jj + 1] = dl * bj[jj + 1];
                 }
+                float y_lo, y_hi;
+                unpack2(y2, y_lo, y_hi);
+                yp = y_lo + y_hi;
             }
 #pragma unroll
             for (int m = LPG; m < 32; m <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, m);
-            if (g == 0 && valid) {
-                p.y[row * d + i] = yp;
-                if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y_bf16)[row * d + i] = __float2bfloat16_rn(yp);
-            }
+            if (g == 0) dd[tt * CH + c] = yp;  // every reader of this delta slot sits in this warp and has read it
             if (TAPE) {
 #pragma unroll
                 for (int jj = 0; jj < ST; ++jj) {
@@ -221,8 +250,43 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
                     }
                 }
             }
+        };
+        if (nt == kTileTokens) {
+#pragma unroll 4
+            for (int tt = 0; tt < kTileTokens; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < nt; ++tt) token(tt);
         }
         __syncthreads();
+        // write the tile's y rows out together: 16-byte stores instead of one predicated scalar store per token
+        if (p.aligned) {
+            constexpr int CQ = CH / 4;
+            for (int idx = tid; idx < nt * CQ; idx += kThreads) {
+                const int tt = idx / CQ, q = idx % CQ;
+                const int col = i0 + q * 4;
+                if (col < d) {
+                    const float4 v = *reinterpret_cast<const float4*>(dd + tt * CH + q * 4);
+                    const size_t o = (row0 + t0 + tt) * (size_t)d + col;
+                    *reinterpret_cast<float4*>(p.y + o) = v;
+                    if (p.y_bf16) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<unsigned*>(&lo);
+                        pk.y = *reinterpret_cast<unsigned*>(&hi);
+                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.y_bf16) + o) = pk;
+                    }
+                }
+            }
+        } else {
+            for (int idx = tid; idx < nt * CH; idx += kThreads) {
+                const int tt = idx / CH, q = idx % CH;
+                if (i0 + q < d) {
+                    const size_t o = (row0 + t0 + tt) * (size_t)d + i0 + q;
+                    p.y[o] = dd[tt * CH + q];
+                    if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y_bf16)[o] = __float2bfloat16_rn(dd[tt * CH + q]);
+                }
+            }
+        }
     }
     cp_async_wait<0>();
     if (carry && len > 0) {
