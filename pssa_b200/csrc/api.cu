@@ -347,7 +347,7 @@ int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_
     if (rc != PSSA_B200_OK) return rc;
     if (!q || !keys || !norm_sq || !values || !m_val)
         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
-    if (flags & ~PSSA_B200_MEM_EXACT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
+    if (flags & ~(PSSA_B200_MEM_EXACT | PSSA_B200_MEM_F32_DISTANCE)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     // scratch from the arena: the weight rows when the caller does not want them, and the bf16 pieces of the
     // weights and of the transposed values for the tensor-core value read (all-slots mode, capacity % 64 == 0)
@@ -375,6 +375,7 @@ int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_
     p.w_split = w_split, p.v_split = v_split;
     p.rows = rows, p.dk = (int)d_key, p.dv = (int)d_val, p.cap = (int)capacity, p.count = (int)count;
     p.top_k = (int)(top_k > capacity ? capacity : top_k), p.tau = tau;
+    p.f32_distance = (flags & PSSA_B200_MEM_F32_DISTANCE) != 0;
     return launch_memory_read(ctx, p, (flags & PSSA_B200_MEM_EXACT) != 0);
 }
 

@@ -71,6 +71,7 @@ struct RetrieveParams {
     size_t rows;
     int dk, dv, cap, count, top_k;
     float tau;
+    int f32_distance;      // fast mode: squared differences accumulated in fp32 instead of f64 (ignored when exact)
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
 // values [cap, dv] fp32 -> v_split [dv, 3*cap] bf16 (transpose + three-way split); once per bank upload

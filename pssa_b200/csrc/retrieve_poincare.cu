@@ -144,6 +144,181 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
     }
 }
 
+// ------------------------------------------------------------------ A': fp32 distances (fast mode)
+// Same tiling as kernel A with the squared differences accumulated in fp32. Differences are formed first, as in the
+// reference, so near-coincident points lose nothing to cancellation: the squared distance carries a relative error of
+// about 1e-6 (64 roundings), the distance half of that. The projection is the f64 one (bit-identical q_pnc). Two key
+// dimensions travel together as one packed f32x2 register so a (query, slot, dimension pair) costs two instructions.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ float sum2(f32x2 v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
+}
+// 2*asinh(sqrt(u)) = log1p(z), z = 2u + 2*sqrt(u*u + u), with the hardware sqrt / log2 / reciprocal approximations:
+// log1p(z) = log(w) + (z - (w - 1))/w for w = fl(1 + z). lg2.approx is within 2^-22 absolute near one, 2^-22 relative
+// elsewhere, so the distance is good to about 2e-7 absolute near zero and 3e-7 relative beyond.
+__device__ __forceinline__ float fast_poincare_distance(float u) {
+    float r, lg, rc;
+    const float t = fmaf(u, u, u);
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+    const float z = 2.0f * u + 2.0f * r;
+    const float w = 1.0f + z;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(w));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(w));
+    return fmaf(lg, 0.69314718055994531f, (z - (w - 1.0f)) * rc);
+}
+
+// Shared memory: P as [dimension pair][query] float2 (a thread's four queries are one 32-byte read, broadcast over the
+// slot threads), key tiles row-major [slot][kpad + 4] in two buffers filled by cp.async one pass ahead. A thread owns
+// queries tq*4 + a and slots ts + 16*b: consecutive slot threads sit 68 floats apart, so their 16-byte key reads hit
+// disjoint banks and their distance stores are 64-byte runs.
+__global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int kpad = (p.dk + 3) / 4 * 4;
+    const int kpitch = kpad + 4;
+    float2* Pf = reinterpret_cast<float2*>(smem_raw);                 // [kpad/2][QT]
+    float* Ks = reinterpret_cast<float*>(Pf + (size_t)(kpad / 2) * QT);  // [2][STL][kpitch]
+    float* rq = Ks + 2 * (size_t)STL * kpitch;                        // [QT]     1 / (1 - |p|^2)
+    float* rk = rq + QT;                                              // [2][STL] 1 / (1 - |k|^2)
+
+    const int tid = threadIdx.x;
+    const size_t q0 = (size_t)blockIdx.x * QT;
+    const int dk = p.dk, count = p.count;
+    const bool vec_in = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(p.keys) & 15) == 0;
+
+    auto load_keys = [&](int pass) {
+        const int s0 = pass * STL;
+        if (s0 < count) {
+            float* dst = Ks + (size_t)(pass & 1) * STL * kpitch;
+            if (vec_in) {
+                const int c4n = dk >> 2;
+                for (int idx = tid; idx < STL * c4n; idx += 256) {
+                    const int sl = idx / c4n, c4 = idx % c4n;
+                    if (s0 + sl < count)
+                        cp_async16(dst + sl * kpitch + c4 * 4, p.keys + (size_t)(s0 + sl) * dk + c4 * 4);
+                    else
+                        *reinterpret_cast<float4*>(dst + sl * kpitch + c4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            } else {
+                for (int idx = tid; idx < STL * kpad; idx += 256) {
+                    const int sl = idx / kpad, i = idx % kpad;
+                    dst[sl * kpitch + i] = (s0 + sl < count && i < dk) ? __ldg(p.keys + (size_t)(s0 + sl) * dk + i) : 0.0f;
+                }
+            }
+            if (tid < STL)
+                rk[(pass & 1) * STL + tid] = s0 + tid < count ? (float)(1.0 / (1.0 - (double)__ldg(p.norm_sq + s0 + tid))) : 0.0f;
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    load_keys(0);
+
+    float* Pflat = reinterpret_cast<float*>(Pf);
+    for (int idx = tid; idx < (kpad - dk) * QT; idx += 256) {  // zero the padded dimensions
+        int i = dk + idx / QT, qq = idx % QT;
+        Pflat[((size_t)(i >> 1) * QT + qq) * 2 + (i & 1)] = 0.0f;
+    }
+    if (tid < QT) {
+        const size_t q = q0 + tid;
+        float qs = 0.0f;
+        if (q < p.rows) {
+            const float* src = p.q + q * (p.ldq ? p.ldq : (size_t)dk);
+            float* dst = p.q_pnc ? p.q_pnc + q * dk : nullptr;
+            double scale = 1.0;
+            if (p.q_is_euclidean) {  // memory.rs:198-211
+                double r2 = 0.0;
+                for (int i = 0; i < dk; ++i) {
+                    double v = (double)src[i];
+                    r2 = __dadd_rn(r2, __dmul_rn(v, v));
+                }
+                double r = sqrt(r2);
+                const double max_radius = 1.0 - 8.0 * (double)FLT_EPSILON;
+                scale = (r == 0.0) ? 1.0 : fmin(r / (1.0 + r), max_radius) / r;
+                if (p.q_norm) p.q_norm[q] = (float)fmin(r, (double)FLT_MAX);
+            }
+            double n2 = 0.0;
+            for (int i = 0; i < dk; ++i) {
+                float pv = p.q_is_euclidean ? (float)__dmul_rn((double)src[i], scale) : src[i];
+                if (dst) dst[i] = pv;
+                Pflat[((size_t)(i >> 1) * QT + tid) * 2 + (i & 1)] = pv;
+                n2 = __dadd_rn(n2, __dmul_rn((double)pv, (double)pv));
+            }
+            qs = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;  // memory.rs:181-188
+        } else {
+            for (int i = 0; i < dk; ++i) Pflat[((size_t)(i >> 1) * QT + tid) * 2 + (i & 1)] = 0.0f;
+        }
+        rq[tid] = (float)(1.0 / (1.0 - (double)qs));
+    }
+
+    const int ts = tid & 15, tq = tid >> 4;
+    const int npass = (count + STL - 1) / STL;
+    for (int pass = 0; pass < npass; ++pass) {
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();      // tile `pass` (and, first time round, P) visible; everyone is done with tile pass-1
+        load_keys(pass + 1);  // lands while this tile is consumed
+        const float* kt = Ks + (size_t)(pass & 1) * STL * kpitch;
+        f32x2 acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0ull;
+#pragma unroll 2
+        for (int i4 = 0; i4 < kpad / 4; ++i4) {
+            f32x2 kv[4][2], pv[4][2];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const ulonglong2 k = *reinterpret_cast<const ulonglong2*>(kt + (ts + 16 * b) * kpitch + i4 * 4);
+                kv[b][0] = k.x, kv[b][1] = k.y;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const ulonglong2* pp = reinterpret_cast<const ulonglong2*>(Pf + (size_t)(i4 * 2 + h) * QT + tq * 4);
+                const ulonglong2 p01 = pp[0], p23 = pp[1];
+                pv[0][h] = p01.x, pv[1][h] = p01.y, pv[2][h] = p23.x, pv[3][h] = p23.y;
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        const f32x2 df = sub2(pv[a][h], kv[b][h]);
+                        acc[a][b] = fma2(df, df, acc[a][b]);
+                    }
+        }
+        const int s0 = pass * STL;
+        const float* rkt = rk + (pass & 1) * STL;
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const size_t q = q0 + tq * 4 + a;
+            if (q >= p.rows) continue;
+            const float rqa = rq[tq * 4 + a];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int slot = s0 + ts + 16 * b;
+                // memory.rs:245-262 with u = sq / ((1-|p|^2)(1-|k|^2))
+                if (slot < count) p.weights[q * p.cap + slot] = fast_poincare_distance(sum2(acc[a][b]) * (rqa * rkt[ts + 16 * b]));
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::);
+}
+
 // x = x0 + x1 + x2 with bf16 pieces: 24 bits of significand survive, so products of pieces reproduce fp32 products
 __device__ __forceinline__ void split3(float x, __nv_bfloat16& a, __nv_bfloat16& b, __nv_bfloat16& c) {
     a = __float2bfloat16_rn(x);
@@ -384,8 +559,20 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_a = true;
     }
-    poincare_distance_kernel<<<(unsigned)qblocks, 256, smem_a, ctx->stream>>>(p);
-    if ((rc = after_launch(ctx, "poincare_distance_kernel")) != PSSA_B200_OK) return rc;
+    const int kpad4 = (p.dk + 3) / 4 * 4;
+    const size_t smem_f = (size_t)(kpad4 / 2) * QT * sizeof(float2) + ((size_t)2 * STL * (kpad4 + 4) + QT + 2 * STL) * sizeof(float);
+    if (p.f32_distance && !exact && smem_f <= 72 * 1024) {  // wider keys keep the f64 kernel
+        static bool attr_f = false;
+        if (smem_f > 48 * 1024 && !attr_f) {
+            PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            attr_f = true;
+        }
+        poincare_distance_f32_kernel<<<(unsigned)qblocks, 256, smem_f, ctx->stream>>>(p);
+        if ((rc = after_launch(ctx, "poincare_distance_f32_kernel")) != PSSA_B200_OK) return rc;
+    } else {
+        poincare_distance_kernel<<<(unsigned)qblocks, 256, smem_a, ctx->stream>>>(p);
+        if ((rc = after_launch(ctx, "poincare_distance_kernel")) != PSSA_B200_OK) return rc;
+    }
     size_t wblocks = (p.rows + 7) / 8;
     static bool attr_b[2] = {false, false};
     if (smem_b > 48 * 1024 && !attr_b[exact]) {

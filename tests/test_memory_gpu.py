@@ -45,6 +45,27 @@ def check(gpu, q, keys, norm_sq, values, count, tau, top_k, euclid, exact):
     assert np.max(np.abs(m - ref_m)) / scale <= (2e-6 if exact else REL_TOL)
 
 
+@pytest.mark.parametrize("rows,dk,dv,cap,count", [(1, 1, 1, 1, 1), (3, 2, 4, 3, 2), (65, 16, 64, 32, 32),
+                                                  (130, 33, 70, 100, 77), (64, 64, 192, 512, 512),
+                                                  (17, 128, 128, 512, 300)])
+def test_fp32_distance_mode_stays_within_its_stated_error(gpu, rows, dk, dv, cap, count):
+    """Fast mode (fp32 accumulation of the squared differences): the projection is still bit-exact, distances are
+    within 2e-6 relative, so weights exp(-d/tau) move by at most d*2e-6/tau of themselves."""
+    keys, norm_sq, values = make_bank(cap, dk, dv, rows + dk + cap)
+    rng = np.random.default_rng(rows * 7)
+    q = (rng.standard_normal((rows, dk)) * rng.uniform(0.05, 3.0, (rows, 1))).astype(np.float32)
+    q[0] = keys[0] / (1.0 - np.linalg.norm(keys[0]))  # projects back onto slot 0 up to rounding: distance near zero
+    tau = 0.1
+    ref_p, ref_m, ref_w, ref_md = O.memory_read(keys, norm_sq, values, count, q, tau, 0, True)
+    q_pnc, _, w, m, md = gpu.memory_read(q, keys, norm_sq, values, count, tau, 0, True, False, f32_distance=True)
+    assert np.array_equal(q_pnc.view(np.uint32), ref_p.view(np.uint32))
+    assert np.max(np.abs(md - ref_md)) <= 2e-6 * np.maximum(1.0, np.abs(ref_md).max()) + 1e-5
+    assert np.max(np.abs(w - ref_w)) <= 2e-4
+    scale = np.maximum(1e-6, np.abs(values[:count]).max())
+    assert np.max(np.abs(m - ref_m)) / scale <= 4e-4
+    assert abs(float(w[0].sum()) - 1.0) <= 1e-5
+
+
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("top_k", [0, 1, 2, 8])
 @pytest.mark.parametrize("rows,dk,dv,cap,count", [(1, 1, 1, 1, 1), (3, 2, 4, 3, 2), (65, 16, 64, 32, 32),
