@@ -103,6 +103,60 @@ __global__ void __launch_bounds__(256) combine_zraw_kernel(const float* __restri
     }
 }
 
+// Tensor-core mode of the same stage (fused multiply-adds allowed): a thread owns four consecutive channels and their
+// 4 x 16 effective adapter weights in registers, walks kFastRows rows, and moves y / gate / m_proj / z as 16-byte
+// vectors; the rows' adapter activations sit in shared memory and are read as broadcasts. About a third of the
+// instructions of the exact kernel, which leaves the stage bound by its 18 bytes per element of HBM traffic.
+constexpr int kFastRows = 32;
+__global__ void __launch_bounds__(256) combine_zraw_fast_kernel(const float* __restrict__ y, const float* __restrict__ g,
+                                                                size_t ldg, const float* __restrict__ m_proj,
+                                                                const float* __restrict__ act, size_t ldact,
+                                                                const float* __restrict__ u_eff, float* __restrict__ z_raw,
+                                                                __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d,
+                                                                float ssm_scale) {
+    __shared__ __align__(16) float s_act[kFastRows][16];
+    const size_t row0 = (size_t)blockIdx.y * kFastRows;
+    const int nrows = (int)min((size_t)kFastRows, rows - row0);
+    for (int idx = threadIdx.x; idx < nrows * 4; idx += blockDim.x) {
+        const int r = idx >> 2, q = idx & 3;
+        *reinterpret_cast<float4*>(&s_act[r][q * 4]) = *reinterpret_cast<const float4*>(act + (row0 + r) * ldact + q * 4);
+    }
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    float4 u[4][4];  // [channel][rank quad]
+    if (i < d) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) u[c][q] = __ldg(reinterpret_cast<const float4*>(u_eff + (size_t)(i + c) * 16) + q);
+    }
+    __syncthreads();
+    if (i >= d) return;
+#pragma unroll 2
+    for (int r = 0; r < nrows; ++r) {
+        const size_t row = row0 + r;
+        const float4 yv = *reinterpret_cast<const float4*>(y + row * d + i);
+        const float4 gv = *reinterpret_cast<const float4*>(g + row * ldg + i);
+        const float4 mv = *reinterpret_cast<const float4*>(m_proj + row * d + i);
+        float z[4] = {fmaf(gv.x, mv.x, yv.x * ssm_scale), fmaf(gv.y, mv.y, yv.y * ssm_scale), fmaf(gv.z, mv.z, yv.z * ssm_scale),
+                      fmaf(gv.w, mv.w, yv.w * ssm_scale)};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float4 a = *reinterpret_cast<const float4*>(&s_act[r][q * 4]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                z[c] = fmaf(u[c][q].x, a.x, fmaf(u[c][q].y, a.y, fmaf(u[c][q].z, a.z, fmaf(u[c][q].w, a.w, z[c]))));
+        }
+        *reinterpret_cast<float4*>(z_raw + row * d + i) = make_float4(z[0], z[1], z[2], z[3]);
+        if (z_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(z[0], z[1]), hi = __floats2bfloat162_rn(z[2], z[3]);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned*>(&lo);
+            pk.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(z_bf16 + row * d + i) = pk;
+        }
+    }
+}
+
 // src/pssa.rs:2332-2337: features += scale * block_out  (prev == nullptr: features = z, block 0)
 __global__ void __launch_bounds__(256) residual_kernel(const float* __restrict__ prev, const float* __restrict__ z,
                                                        float* __restrict__ out, size_t n, float scale) {
@@ -182,7 +236,16 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
 
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
-                            float ssm_scale) {
+                            float ssm_scale, bool fast) {
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (fast && rank == 16 && d % 4 == 0 && ldg % 4 == 0 && ldact % 4 == 0 && al16(y) && al16(g) && al16(m_proj) && al16(act) &&
+        al16(u_eff) && al16(z_raw) && (reinterpret_cast<uintptr_t>(z_bf16) & 7) == 0 && (rows + kFastRows - 1) / kFastRows <= 65535) {
+        const int threads = d / 4 >= 256 ? 256 : ((d / 4 + 31) / 32 * 32);
+        dim3 grid((unsigned)((d / 4 + threads - 1) / threads), (unsigned)((rows + kFastRows - 1) / kFastRows));
+        combine_zraw_fast_kernel<<<grid, threads, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw,
+                                                                    (__nv_bfloat16*)z_bf16, rows, d, ssm_scale);
+        return after_launch(ctx, "combine_zraw_fast_kernel");
+    }
     dim3 grid((unsigned)((d + 255) / 256), (unsigned)((rows + kCombineRows - 1) / kCombineRows));
     if (grid.y > 65535) {
         // very long passes: fall back to several launches of at most 65535 row groups
@@ -190,7 +253,7 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
         for (size_t r0 = 0; r0 < rows; r0 += step) {
             size_t n = rows - r0 < step ? rows - r0 : step;
             int32_t rc = launch_combine_zraw(ctx, y + r0 * d, g + r0 * ldg, ldg, m_proj + r0 * d, act + r0 * ldact, ldact, u_eff,
-                                             z_raw + r0 * d, z_bf16 ? (char*)z_bf16 + r0 * d * 2 : nullptr, n, d, rank, ssm_scale);
+                                             z_raw + r0 * d, z_bf16 ? (char*)z_bf16 + r0 * d * 2 : nullptr, n, d, rank, ssm_scale, fast);
             if (rc) return rc;
         }
         return PSSA_B200_OK;

@@ -536,16 +536,17 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
 }
 
 // fp32-accurate product from three bf16 pieces per operand: a16 [M, 3*K], b16 [N, 3*K], K a multiple of 64.
-// The six products whose weight is above 2^-24 are accumulated: (0,0) (0,1) (1,0) (0,2) (1,1) (2,0).
+// The six products whose weight is above 2^-24 are accumulated: (0,0) (0,1) (1,0) (0,2) (1,1) (2,0); `terms` == 3 keeps
+// the first three (weight above 2^-16), enough when only the bf16 copy of the result is used.
 int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
-                                size_t N, size_t K, size_t ldo) {
+                                size_t N, size_t K, size_t ldo, int terms) {
     if (K % BK != 0) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 split GEMM needs K %% 64 == 0; K = %zu", K);
     int32_t rc = check_shape(ctx, a16, b16, M, N, 3 * K);
     if (rc) return rc;
     GemmEpilogue e{};
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
     e.M = (int)M, e.N = (int)N, e.K = (int)(3 * K), e.epi = EPI_NONE, e.alpha = 1.0f;
-    e.n_pairs = 6, e.seg_kb = (int)(K / BK);
+    e.n_pairs = terms == 3 ? 3 : 6, e.seg_kb = (int)(K / BK);
     const unsigned char pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
     for (int i = 0; i < 6; ++i) e.pair_a[i] = pa[i], e.pair_b[i] = pb[i];
     return dispatch(ctx, a16, b16, e);

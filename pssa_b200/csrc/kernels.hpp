@@ -61,7 +61,7 @@ struct RetrieveParams {
     const float* values;   // [cap, dv]
     size_t ldq;            // row pitch of q in floats (0 = dk)
     float* weights;        // [rows, cap] distances in flight, weights on return
-    float* m_val;          // [rows, dv]
+    float* m_val;          // [rows, dv]; may be null when m_bf16 is the only result wanted
     void* m_bf16;          // optional bf16 copy of m_val for the tensor-core memory projection
     float* min_dist;       // [rows], may be null
     // tensor-core value read (all-slots mode, non-exact): the softmax kernel also writes each weight row as three
@@ -71,6 +71,7 @@ struct RetrieveParams {
     size_t rows;
     int dk, dv, cap, count, top_k;
     float tau;
+    int value_terms;       // tensor-core value read: 3 = leading partial products only (bf16-grade result), else all six
     int f32_distance;      // fast mode: squared differences accumulated in fp32 instead of f64 (ignored when exact)
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
@@ -112,7 +113,7 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
                                   const float* res_in, float res_scale, size_t M, size_t N, size_t K);
 // fp32-accurate product of operands pre-split into three bf16 pieces: a16 [M, 3K], b16 [N, 3K] (six partial products)
 int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
-                                size_t N, size_t K, size_t ldo);
+                                size_t N, size_t K, size_t ldo, int terms = 6);
 // concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
                              size_t ldo, int c1, int c2, int c3);
@@ -122,7 +123,7 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
                           const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact);
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
-                            float ssm_scale);
+                            float ssm_scale, bool fast = false);
 int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale);
 int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d);
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n);

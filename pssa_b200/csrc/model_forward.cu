@@ -145,7 +145,8 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         RetrieveParams rp{};
         rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = nullptr, rp.q_norm = nullptr;
         rp.keys = b.w[T_BANK_KEYS], rp.norm_sq = b.w[T_BANK_NORM_SQ], rp.values = b.w[T_BANK_VALUES];
-        rp.weights = ws.weights, rp.m_val = ws.m_val, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
+        rp.weights = ws.weights, rp.m_val = exact ? ws.m_val : nullptr, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
+        rp.value_terms = exact ? 6 : 3;  // the bf16 mode keeps only the bf16 copy of m (the W_proj operand)
         rp.rows = rows, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
         rp.f32_distance = !exact;  // the bf16 mode's queries carry bf16 rounding already; f64 distances buy nothing there
@@ -154,7 +155,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         if ((rc = dense(m, ws.m_val, ws.m_bf16, b.w[T_W_PROJ], b.wproj_bf16, ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
         if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z,
-                                      exact ? nullptr : ws.z_bf16, rows, d, (int)m->rank, ssm_scale)))
+                                      exact ? nullptr : ws.z_bf16, rows, d, (int)m->rank, ssm_scale, !exact)))
             return rc;
         // the tensor-core path needs the MLP activations only as the next GEMM's bf16 operand
         if ((rc = dense(m, ws.z, ws.z_bf16, b.w[T_MLP_W1], b.w1_bf16, exact ? ws.mlp_act : nullptr, rows, 2 * m->d, m->d, 2 * m->d,

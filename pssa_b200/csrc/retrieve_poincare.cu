@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
     if (count == 0) {  // memory.rs:363-367
         for (int i = lane; i < cap; i += 32) row[i] = 0.0f;
         for (int j = lane; j < dv; j += 32) {
-            p.m_val[q * dv + j] = 0.0f;
+            if (p.m_val) p.m_val[q * dv + j] = 0.0f;
             if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + j] = __float2bfloat16_rn(0.0f);
         }
         if (p.min_dist) p.min_dist[q] = 0.0f;
@@ -444,7 +444,7 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
             for (int e = 0; e < 4; ++e) {
                 int j = j0 + e * 32;
                 if (j < dv) {
-                    p.m_val[q * dv + j] = acc[e];
+                    if (p.m_val) p.m_val[q * dv + j] = acc[e];
                     if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + j] = __float2bfloat16_rn(acc[e]);
                 }
             }
@@ -531,7 +531,7 @@ __global__ void __launch_bounds__(256) value_mix_kernel(RetrieveParams p) {
         for (int b = 0; b < 4; ++b) {
             int col = c0 + tc * 4 + b;
             if (col < dv) {
-                p.m_val[q * dv + col] = acc[a][b];
+                if (p.m_val) p.m_val[q * dv + col] = acc[a][b];
                 if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + col] = __float2bfloat16_rn(acc[a][b]);
             }
         }
@@ -589,8 +589,11 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     if ((rc = after_launch(ctx, "softmax_topk_kernel")) != PSSA_B200_OK) return rc;
     bool topk = p.top_k != 0 && p.top_k < p.count;
     if (p.count > 0 && !topk && p.w_split && p.v_split && !exact) {
-        // all-slots value read on the tensor cores: m = W x V as six bf16 partial products (fp32-accurate)
-        if ((rc = launch_gemm_bf16_split3(ctx, p.w_split, p.v_split, p.m_val, p.m_bf16, p.rows, p.dv, p.cap, p.dv))) return rc;
+        // all-slots value read on the tensor cores: m = W x V as six bf16 partial products (fp32-accurate), or the
+        // leading three (error near 2^-16 of the row scale) when the caller only keeps a bf16 result
+        if ((rc = launch_gemm_bf16_split3(ctx, p.w_split, p.v_split, p.m_val, p.m_bf16, p.rows, p.dv, p.cap, p.dv,
+                                          p.value_terms == 3 ? 3 : 6)))
+            return rc;
     } else if (p.count > 0 && !topk) {
         dim3 grid((unsigned)qblocks, (unsigned)((p.dv + 63) / 64));
         if (exact)
