@@ -103,56 +103,59 @@ __global__ void __launch_bounds__(256) combine_zraw_kernel(const float* __restri
     }
 }
 
-// Tensor-core mode of the same stage (fused multiply-adds allowed): a thread owns four consecutive channels and their
-// 4 x 16 effective adapter weights in registers, walks kFastRows rows, and moves y / gate / m_proj / z as 16-byte
-// vectors; the rows' adapter activations sit in shared memory and are read as broadcasts. About a third of the
-// instructions of the exact kernel, which leaves the stage bound by its 18 bytes per element of HBM traffic.
+// Tensor-core mode of the same stage (fused multiply-adds allowed): a thread owns two consecutive channels and their
+// 2 x 16 effective adapter weights in registers and walks kFastRows rows four at a time, all loads of a group issued
+// before any arithmetic; the rows' adapter activations sit in shared memory and are read as broadcasts. A third of the
+// instructions of the exact kernel and enough loads in flight to leave the stage bound by its 18 bytes per element.
 constexpr int kFastRows = 32;
-__global__ void __launch_bounds__(256) combine_zraw_fast_kernel(const float* __restrict__ y, const float* __restrict__ g,
-                                                                size_t ldg, const float* __restrict__ m_proj,
-                                                                const float* __restrict__ act, size_t ldact,
-                                                                const float* __restrict__ u_eff, float* __restrict__ z_raw,
-                                                                __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d,
-                                                                float ssm_scale) {
+__global__ void __launch_bounds__(384, 2) combine_zraw_fast_kernel(const float* __restrict__ y, const float* __restrict__ g,
+                                                                   size_t ldg, const float* __restrict__ m_proj,
+                                                                   const float* __restrict__ act, size_t ldact,
+                                                                   const float* __restrict__ u_eff, float* __restrict__ z_raw,
+                                                                   __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d,
+                                                                   float ssm_scale) {
     __shared__ __align__(16) float s_act[kFastRows][16];
     const size_t row0 = (size_t)blockIdx.y * kFastRows;
     const int nrows = (int)min((size_t)kFastRows, rows - row0);
-    for (int idx = threadIdx.x; idx < nrows * 4; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < kFastRows * 4; idx += blockDim.x) {
         const int r = idx >> 2, q = idx & 3;
-        *reinterpret_cast<float4*>(&s_act[r][q * 4]) = *reinterpret_cast<const float4*>(act + (row0 + r) * ldact + q * 4);
+        const size_t row = min(row0 + r, rows - 1);
+        *reinterpret_cast<float4*>(&s_act[r][q * 4]) = *reinterpret_cast<const float4*>(act + row * ldact + q * 4);
     }
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    float4 u[4][4];  // [channel][rank quad]
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    float4 u[2][4];  // [channel][rank quad]
     if (i < d) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int q = 0; q < 4; ++q) u[c][q] = __ldg(reinterpret_cast<const float4*>(u_eff + (size_t)(i + c) * 16) + q);
     }
     __syncthreads();
     if (i >= d) return;
-#pragma unroll 2
-    for (int r = 0; r < nrows; ++r) {
-        const size_t row = row0 + r;
-        const float4 yv = *reinterpret_cast<const float4*>(y + row * d + i);
-        const float4 gv = *reinterpret_cast<const float4*>(g + row * ldg + i);
-        const float4 mv = *reinterpret_cast<const float4*>(m_proj + row * d + i);
-        float z[4] = {fmaf(gv.x, mv.x, yv.x * ssm_scale), fmaf(gv.y, mv.y, yv.y * ssm_scale), fmaf(gv.z, mv.z, yv.z * ssm_scale),
-                      fmaf(gv.w, mv.w, yv.w * ssm_scale)};
+    for (int r0 = 0; r0 < nrows; r0 += 4) {
+        float2 yv[4], gv[4], mv[4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const float4 a = *reinterpret_cast<const float4*>(&s_act[r][q * 4]);
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                z[c] = fmaf(u[c][q].x, a.x, fmaf(u[c][q].y, a.y, fmaf(u[c][q].z, a.z, fmaf(u[c][q].w, a.w, z[c]))));
+        for (int k = 0; k < 4; ++k) {
+            const size_t row = min(row0 + r0 + k, rows - 1);  // clamped for the loads; stores are predicated
+            yv[k] = *reinterpret_cast<const float2*>(y + row * d + i);
+            gv[k] = *reinterpret_cast<const float2*>(g + row * ldg + i);
+            mv[k] = *reinterpret_cast<const float2*>(m_proj + row * d + i);
         }
-        *reinterpret_cast<float4*>(z_raw + row * d + i) = make_float4(z[0], z[1], z[2], z[3]);
-        if (z_bf16) {
-            __nv_bfloat162 lo = __floats2bfloat162_rn(z[0], z[1]), hi = __floats2bfloat162_rn(z[2], z[3]);
-            uint2 pk;
-            pk.x = *reinterpret_cast<unsigned*>(&lo);
-            pk.y = *reinterpret_cast<unsigned*>(&hi);
-            *reinterpret_cast<uint2*>(z_bf16 + row * d + i) = pk;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float z[2] = {fmaf(gv[k].x, mv[k].x, yv[k].x * ssm_scale), fmaf(gv[k].y, mv[k].y, yv[k].y * ssm_scale)};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 a = *reinterpret_cast<const float4*>(&s_act[r0 + k][q * 4]);
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                    z[c] = fmaf(u[c][q].x, a.x, fmaf(u[c][q].y, a.y, fmaf(u[c][q].z, a.z, fmaf(u[c][q].w, a.w, z[c]))));
+            }
+            if (r0 + k < nrows) {
+                const size_t o = (row0 + r0 + k) * d + i;
+                *reinterpret_cast<float2*>(z_raw + o) = make_float2(z[0], z[1]);
+                if (z_bf16) *reinterpret_cast<__nv_bfloat162*>(z_bf16 + o) = __floats2bfloat162_rn(z[0], z[1]);
+            }
         }
     }
 }
@@ -240,8 +243,8 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (fast && rank == 16 && d % 4 == 0 && ldg % 4 == 0 && ldact % 4 == 0 && al16(y) && al16(g) && al16(m_proj) && al16(act) &&
         al16(u_eff) && al16(z_raw) && (reinterpret_cast<uintptr_t>(z_bf16) & 7) == 0 && (rows + kFastRows - 1) / kFastRows <= 65535) {
-        const int threads = d / 4 >= 256 ? 256 : ((d / 4 + 31) / 32 * 32);
-        dim3 grid((unsigned)((d / 4 + threads - 1) / threads), (unsigned)((rows + kFastRows - 1) / kFastRows));
+        const int threads = d / 2 >= 384 ? 384 : ((d / 2 + 31) / 32 * 32);
+        dim3 grid((unsigned)((d / 2 + threads - 1) / threads), (unsigned)((rows + kFastRows - 1) / kFastRows));
         combine_zraw_fast_kernel<<<grid, threads, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw,
                                                                     (__nv_bfloat16*)z_bf16, rows, d, ssm_scale);
         return after_launch(ctx, "combine_zraw_fast_kernel");
