@@ -38,6 +38,9 @@ WORKLOAD = ("prefill_c4: 12-block PSSA (d 768, state 64, key 64, 512 slots, voca
 CPU_SAMPLE_LANES, CPU_SAMPLE_T = 16, 16
 # dram bytes per scan element from profiles/scan_chunk_apply_small_case.md
 NCU_SCAN_TRAFFIC_BYTES_PER_ELEM = 11.87
+# dram bytes per token row of one ssm_fused_kernel launch, from profiles/ssm_fused_kernel_prefill_16_lanes.md
+# (read 225.5 MB + write 119.9 MB over 32768 rows); traffic grows in proportion to the rows
+NCU_SSM_TRAFFIC_BYTES_PER_ROW = (225.52e6 + 119.92e6) / 32768
 
 
 def measured_peaks():
@@ -173,10 +176,12 @@ def kernel_roofline(name, launches, ms, rows, peak_hbm, peak_tf):
     d, s, k, cap = CFG["d_latent"], CFG["d_state"], CFG["d_mem_key"], CFG["mem_capacity"]
     per = ms / launches / 1e3
     if "ssm_fused" in name:
-        byts = rows * (3 * d + 2 * s) * 4 + LANES * 2 * d * s * 4
+        # in: delta, x (4d each), B, C (4s each); out: y fp32 + bf16 (6d); carry in and out once per lane
+        byts = rows * ((2 * d + 2 * s) * 4 + 6 * d) + LANES * 2 * d * s * 4
         exps = rows * d * s
         return {"bound": "hbm", "achieved": byts / per / 1e9, "peak": peak_hbm, "unit": "GB/s",
-                "frac": byts / per / 1e9 / peak_hbm, "limiter": "exp (MUFU) throughput",
+                "frac": byts / per / 1e9 / peak_hbm, "traffic": NCU_SSM_TRAFFIC_BYTES_PER_ROW * rows,
+                "limiter": "exp (MUFU) throughput: d*s exponentials per token against 16 per SM per clock",
                 "limiter_achieved_gexp_s": exps / per / 1e9, "limiter_peak_gexp_s": 148 * 16 * 1.965,
                 "limiter_frac": exps / per / 1e9 / (148 * 16 * 1.965)}
     if "gemm_bf16" in name:
@@ -188,7 +193,8 @@ def kernel_roofline(name, launches, ms, rows, peak_hbm, peak_tf):
     if "poincare_distance" in name:
         byts = rows * (k * 4 + cap * 4)
         return {"bound": "hbm", "achieved": byts / per / 1e9, "peak": peak_hbm, "unit": "GB/s", "frac": byts / per / 1e9 / peak_hbm,
-                "limiter": "fp64 FMA + log1p/sqrt (distances are f64 like the reference)"}
+                "limiter": "FP32 FMA pipe (fast mode: packed fp32 squared differences, 2 ops per key dimension)"
+                if "f32" in name else "fp64 FMA + log1p/sqrt (distances are f64 like the reference)"}
     return None
 
 
@@ -355,8 +361,9 @@ def run_b200(args):
             kernels.append(row)
         top = kernels[0]
         roofline = dict(top.get("roofline") or {"bound": "hbm", "achieved": None, "peak": peak_hbm, "unit": "GB/s", "frac": None})
+        roofline.setdefault("traffic", None)
         roofline.update({"kernel": top["kernel"], "kernel_ms_per_step": top["ms_per_step"], "share_of_step": top["share"],
-                         "traffic": None, "peak_kind": f"of {peak_kind}"})
+                         "peak_kind": f"of {peak_kind}"})
         cpu = None
         parity = None
         if world == 1 and not args.no_cpu:
