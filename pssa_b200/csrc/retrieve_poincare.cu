@@ -202,10 +202,12 @@ __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveP
     const int dk = p.dk, count = p.count;
     const bool vec_in = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(p.keys) & 15) == 0;
 
-    auto load_keys = [&](int pass) {
+    // passes over the slots are dealt round-robin to the CTAs of a column (gridDim.y > 1 only when there are too few
+    // query tiles to fill the machine: decode steps); `buf` alternates per pass this CTA owns
+    auto load_keys = [&](int pass, int buf) {
         const int s0 = pass * STL;
         if (s0 < count) {
-            float* dst = Ks + (size_t)(pass & 1) * STL * kpitch;
+            float* dst = Ks + (size_t)buf * STL * kpitch;
             if (vec_in) {
                 const int c4n = dk >> 2;
                 for (int idx = tid; idx < STL * c4n; idx += 256) {
@@ -222,11 +224,11 @@ __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveP
                 }
             }
             if (tid < STL)
-                rk[(pass & 1) * STL + tid] = s0 + tid < count ? (float)(1.0 / (1.0 - (double)__ldg(p.norm_sq + s0 + tid))) : 0.0f;
+                rk[buf * STL + tid] = s0 + tid < count ? (float)(1.0 / (1.0 - (double)__ldg(p.norm_sq + s0 + tid))) : 0.0f;
         }
         asm volatile("cp.async.commit_group;\n" ::);
     };
-    load_keys(0);
+    load_keys(blockIdx.y, 0);
 
     float* Pflat = reinterpret_cast<float*>(Pf);
     for (int idx = tid; idx < (kpad - dk) * QT; idx += 256) {  // zero the padded dimensions
@@ -238,7 +240,7 @@ __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveP
         float qs = 0.0f;
         if (q < p.rows) {
             const float* src = p.q + q * (p.ldq ? p.ldq : (size_t)dk);
-            float* dst = p.q_pnc ? p.q_pnc + q * dk : nullptr;
+            float* dst = (p.q_pnc && blockIdx.y == 0) ? p.q_pnc + q * dk : nullptr;
             double scale = 1.0;
             if (p.q_is_euclidean) {  // memory.rs:198-211
                 double r2 = 0.0;
@@ -249,7 +251,7 @@ __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveP
                 double r = sqrt(r2);
                 const double max_radius = 1.0 - 8.0 * (double)FLT_EPSILON;
                 scale = (r == 0.0) ? 1.0 : fmin(r / (1.0 + r), max_radius) / r;
-                if (p.q_norm) p.q_norm[q] = (float)fmin(r, (double)FLT_MAX);
+                if (p.q_norm && blockIdx.y == 0) p.q_norm[q] = (float)fmin(r, (double)FLT_MAX);
             }
             double n2 = 0.0;
             for (int i = 0; i < dk; ++i) {
@@ -267,11 +269,11 @@ __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveP
 
     const int ts = tid & 15, tq = tid >> 4;
     const int npass = (count + STL - 1) / STL;
-    for (int pass = 0; pass < npass; ++pass) {
+    for (int pass = blockIdx.y, buf = 0; pass < npass; pass += gridDim.y, buf ^= 1) {
         asm volatile("cp.async.wait_group 0;\n" ::);
-        __syncthreads();      // tile `pass` (and, first time round, P) visible; everyone is done with tile pass-1
-        load_keys(pass + 1);  // lands while this tile is consumed
-        const float* kt = Ks + (size_t)(pass & 1) * STL * kpitch;
+        __syncthreads();      // this tile (and, first time round, P) visible; everyone is done with the previous tile
+        load_keys(pass + gridDim.y, buf ^ 1);  // lands while this tile is consumed
+        const float* kt = Ks + (size_t)buf * STL * kpitch;
         f32x2 acc[4][4];
 #pragma unroll
         for (int a = 0; a < 4; ++a)
@@ -302,7 +304,7 @@ __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveP
                     }
         }
         const int s0 = pass * STL;
-        const float* rkt = rk + (pass & 1) * STL;
+        const float* rkt = rk + buf * STL;
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
             const size_t q = q0 + tq * 4 + a;
@@ -567,7 +569,11 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
             PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             attr_f = true;
         }
-        poincare_distance_f32_kernel<<<(unsigned)qblocks, 256, smem_f, ctx->stream>>>(p);
+        // few query tiles (decode): spread the slot passes over up to 8 CTAs per tile
+        unsigned ysplit = 1;
+        const unsigned npass = (unsigned)((p.count + STL - 1) / STL);
+        while (qblocks * ysplit < 148 && ysplit < 8 && ysplit * 2 <= (npass ? npass : 1)) ysplit *= 2;
+        poincare_distance_f32_kernel<<<dim3((unsigned)qblocks, ysplit), 256, smem_f, ctx->stream>>>(p);
         if ((rc = after_launch(ctx, "poincare_distance_f32_kernel")) != PSSA_B200_OK) return rc;
     } else {
         poincare_distance_kernel<<<(unsigned)qblocks, 256, smem_a, ctx->stream>>>(p);

@@ -111,12 +111,31 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
                            : nullptr;
 
     float A[ST], h[ST];
+    // a thread's states are contiguous in `rates` and in the carry: 16-byte accesses when the layout allows (decode
+    // steps are one token long, so this load and the store at the end are most of their traffic)
+    const bool vec_state = p.aligned && (s & 3) == 0 && (reinterpret_cast<uintptr_t>(p.rates) & 15) == 0 &&
+                           (reinterpret_cast<uintptr_t>(carry) & 15) == 0;
+    if (vec_state) {
 #pragma unroll
-    for (int jj = 0; jj < ST; ++jj) {
-        bool ok = valid && (j0 + jj) < s;
-        float rate = ok ? __ldg(p.rates + (size_t)i * s + j0 + jj) : 0.0f;
-        A[jj] = EXACT ? rate : rate * 1.4426950408889634f;
-        h[jj] = (ok && carry) ? carry[(size_t)i * s + j0 + jj] : 0.0f;
+        for (int q = 0; q < ST / 4; ++q) {
+            const bool ok = valid && (j0 + q * 4) < s;
+            const float4 r4 = ok ? __ldg(reinterpret_cast<const float4*>(p.rates + (size_t)i * s + j0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 h4 = (ok && carry) ? *(reinterpret_cast<const float4*>(carry + (size_t)i * s + j0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+            A[q * 4] = r4.x, A[q * 4 + 1] = r4.y, A[q * 4 + 2] = r4.z, A[q * 4 + 3] = r4.w;
+            h[q * 4] = h4.x, h[q * 4 + 1] = h4.y, h[q * 4 + 2] = h4.z, h[q * 4 + 3] = h4.w;
+        }
+        if (!EXACT) {
+#pragma unroll
+            for (int jj = 0; jj < ST; ++jj) A[jj] *= 1.4426950408889634f;
+        }
+    } else {
+#pragma unroll
+        for (int jj = 0; jj < ST; ++jj) {
+            bool ok = valid && (j0 + jj) < s;
+            float rate = ok ? __ldg(p.rates + (size_t)i * s + j0 + jj) : 0.0f;
+            A[jj] = EXACT ? rate : rate * 1.4426950408889634f;
+            h[jj] = (ok && carry) ? carry[(size_t)i * s + j0 + jj] : 0.0f;
+        }
     }
 
     const int ntiles = (len + kTileTokens - 1) / kTileTokens;
@@ -290,9 +309,16 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
     }
     cp_async_wait<0>();
     if (carry && len > 0) {
+        if (vec_state) {
 #pragma unroll
-        for (int jj = 0; jj < ST; ++jj)
-            if (valid && j0 + jj < s) carry[(size_t)i * s + j0 + jj] = h[jj];
+            for (int q = 0; q < ST / 4; ++q)
+                if (valid && j0 + q * 4 < s)
+                    *(reinterpret_cast<float4*>(carry + (size_t)i * s + j0) + q) = make_float4(h[q * 4], h[q * 4 + 1], h[q * 4 + 2], h[q * 4 + 3]);
+        } else {
+#pragma unroll
+            for (int jj = 0; jj < ST; ++jj)
+                if (valid && j0 + jj < s) carry[(size_t)i * s + j0 + jj] = h[jj];
+        }
     }
 }
 
