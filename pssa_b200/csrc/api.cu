@@ -276,6 +276,8 @@ int32_t pssa_b200_ssm_forward_dev(pssa_b200_ctx* ctx, const float* delta, const 
     p.carry = carry, p.y = y, p.states = states, p.bar_a = bar_a, p.bar_b = bar_b;
     p.rows = rows, p.d = (int)d_m, p.s = (int)d_s, p.lanes = (int)lanes;
     p.aligned = ssm_vector_ok(p);
+    p.single_token = 1;  // decode-step shape: every lane at most one token
+    for (size_t l = 0; l < lanes; ++l) p.single_token = p.single_token && (lengths ? lengths[l] <= 1 : rows <= 1);
     if (offsets) {
         arena_reset(ctx);
         if ((rc = arena_reserve(ctx, arena_round(lanes * 4) * 2)) != PSSA_B200_OK) return rc;

@@ -113,11 +113,11 @@ __global__ void __launch_bounds__(384, 2) combine_zraw_fast_kernel(const float* 
                                                                    const float* __restrict__ act, size_t ldact,
                                                                    const float* __restrict__ u_eff, float* __restrict__ z_raw,
                                                                    __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d,
-                                                                   float ssm_scale) {
+                                                                   float ssm_scale, int rows_per_cta) {
     __shared__ __align__(16) float s_act[kFastRows][16];
-    const size_t row0 = (size_t)blockIdx.y * kFastRows;
-    const int nrows = (int)min((size_t)kFastRows, rows - row0);
-    for (int idx = threadIdx.x; idx < kFastRows * 4; idx += blockDim.x) {
+    const size_t row0 = (size_t)blockIdx.y * rows_per_cta;
+    const int nrows = (int)min((size_t)rows_per_cta, rows - row0);
+    for (int idx = threadIdx.x; idx < rows_per_cta * 4; idx += blockDim.x) {
         const int r = idx >> 2, q = idx & 3;
         const size_t row = min(row0 + r, rows - 1);
         *reinterpret_cast<float4*>(&s_act[r][q * 4]) = *reinterpret_cast<const float4*>(act + row * ldact + q * 4);
@@ -182,26 +182,34 @@ __global__ void __launch_bounds__(256) to_bf16_kernel(const float* __restrict__ 
 }
 
 // src/inference.rs:111-127: argmax over ids 1..V-1 under total_cmp, ties to the lowest id; a non-finite
-// logit anywhere in the row is an error (id = UINT32_MAX). One warp per row.
+// logit anywhere in the row is an error (id = UINT32_MAX). One CTA per row.
 __device__ __forceinline__ int total_order_key(float v) {
     int b = __float_as_int(v);
     return b < 0 ? (b ^ 0x7fffffff) : b;  // monotone signed key of f32::total_cmp
 }
 __global__ void __launch_bounds__(256) greedy_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, size_t rows,
                                                      int v) {
+    __shared__ long long s_best[8];
+    __shared__ int s_bad[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t row = (size_t)blockIdx.x * 8 + warp;
-    if (row >= rows) return;
+    const size_t row = blockIdx.x;
     const float* lg = logits + row * v;
     long long best = LLONG_MIN;  // (key << 32) | (UINT32_MAX - id): larger is better, lower id wins ties
     bool bad = false;
-    for (int i = lane; i < v; i += 32) {
-        float x = lg[i];
+    auto take = [&](float x, int i) {
         if (!isfinite(x)) bad = true;
         if (i >= 1) {
             long long k = ((long long)total_order_key(x) << 32) | (unsigned)(0xffffffffu - (unsigned)i);
             best = k > best ? k : best;
         }
+    };
+    if ((v & 3) == 0 && (reinterpret_cast<uintptr_t>(lg) & 15) == 0) {
+        for (int i = threadIdx.x * 4; i < v; i += 256 * 4) {
+            const float4 x = *reinterpret_cast<const float4*>(lg + i);
+            take(x.x, i), take(x.y, i + 1), take(x.z, i + 2), take(x.w, i + 3);
+        }
+    } else {
+        for (int i = threadIdx.x; i < v; i += 256) take(lg[i], i);
     }
 #pragma unroll
     for (int m = 16; m > 0; m >>= 1) {
@@ -209,7 +217,15 @@ __global__ void __launch_bounds__(256) greedy_kernel(const float* __restrict__ l
         best = o > best ? o : best;
         bad = bad || __shfl_xor_sync(0xffffffffu, (int)bad, m);
     }
-    if (lane == 0) out[row] = (bad || v < 2) ? 0xffffffffu : 0xffffffffu - (unsigned)(best & 0xffffffffll);
+    if (lane == 0) s_best[warp] = best, s_bad[warp] = bad;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w) {
+            best = s_best[w] > best ? s_best[w] : best;
+            bad = bad || s_bad[w];
+        }
+        out[row] = (bad || v < 2) ? 0xffffffffu : 0xffffffffu - (unsigned)(best & 0xffffffffll);
+    }
 }
 
 inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
@@ -244,9 +260,11 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
     if (fast && rank == 16 && d % 4 == 0 && ldg % 4 == 0 && ldact % 4 == 0 && al16(y) && al16(g) && al16(m_proj) && al16(act) &&
         al16(u_eff) && al16(z_raw) && (reinterpret_cast<uintptr_t>(z_bf16) & 7) == 0 && (rows + kFastRows - 1) / kFastRows <= 65535) {
         const int threads = d / 2 >= 384 ? 384 : ((d / 2 + 31) / 32 * 32);
-        dim3 grid((unsigned)((d / 2 + threads - 1) / threads), (unsigned)((rows + kFastRows - 1) / kFastRows));
+        // short batches (decode steps) take 4 rows per CTA so the launch still covers the machine
+        const int rpc = rows >= (size_t)kFastRows * 296 ? kFastRows : 4;
+        dim3 grid((unsigned)((d / 2 + threads - 1) / threads), (unsigned)((rows + rpc - 1) / rpc));
         combine_zraw_fast_kernel<<<grid, threads, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw,
-                                                                    (__nv_bfloat16*)z_bf16, rows, d, ssm_scale);
+                                                                    (__nv_bfloat16*)z_bf16, rows, d, ssm_scale, rpc);
         return after_launch(ctx, "combine_zraw_fast_kernel");
     }
     dim3 grid((unsigned)((d + 255) / 256), (unsigned)((rows + kCombineRows - 1) / kCombineRows));
@@ -286,7 +304,8 @@ int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n
 }
 
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v) {
-    greedy_kernel<<<blocks_for(rows, 8), 256, 0, ctx->stream>>>(logits, out, rows, v);
+    if (rows > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "greedy: %zu rows exceed grid limits; refusing launch", rows);
+    greedy_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(logits, out, rows, v);
     return after_launch(ctx, "greedy_kernel");
 }
 

@@ -40,6 +40,7 @@ struct SsmParams {
     // carry of lane l lives at carry + slot(l) * carry_stride, slot(l) = lane_slots ? lane_slots[l] : l
     const uint32_t* lane_slots;
     size_t carry_stride;   // 0 = d*s
+    int single_token;      // caller's promise that every lane is at most one token long (a decode step)
 };
 int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact);
 // 16-byte staging and stores need 16-byte aligned bases and row pitches / widths that are multiples of 4 floats

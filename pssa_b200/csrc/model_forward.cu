@@ -112,7 +112,8 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
     float* feat_in = nullptr;
     float* feat_out = ws.feat_a;
     (void)h_off;
-    (void)h_len;
+    bool single_token = true;  // a decode step: the SSM stage is then one pass over the carries
+    for (size_t l = 0; l < lanes; ++l) single_token = single_token && h_len[l] <= 1;
     for (size_t l = 0; l < m->depth; ++l) {
         DeviceBlock& b = m->blocks[l];
         // stage 1: gather + RMSNorm (src/gpu_batch.rs:445-472)
@@ -139,6 +140,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         sp.offsets = ws.lane_off, sp.lengths = ws.lane_len, sp.rows = rows, sp.d = d, sp.s = s, sp.lanes = (int)lanes;
         sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = m->depth * ds;
         sp.aligned = ssm_vector_ok(sp);
+        sp.single_token = single_token;
         if ((rc = launch_ssm_fused(ctx, sp, exact))) return rc;
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
         if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;

@@ -322,6 +322,64 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
     }
 }
 
+// Decode step: every lane advances by one token, so the launch is one pass over the carries (2 * d * s * 4 bytes per
+// lane in and out) and nothing else matters. A thread owns four consecutive states of one channel: rates, carry in and
+// carry out are 16-byte accesses that a warp makes over a contiguous 512 bytes; y is finished by a shuffle tree over the
+// TPC threads of the channel. Same arithmetic as the fast mode of the tiled kernel (ex2.approx, fused multiply-adds).
+template <int TPC>
+__global__ void __launch_bounds__(256) ssm_step_kernel(SsmParams p) {
+    constexpr int CPB = 256 / TPC;  // channels per CTA
+    const int tid = threadIdx.x;
+    const int q = tid % TPC, c = tid / TPC;
+    const int ncb = (p.d + CPB - 1) / CPB;
+    const int lane = blockIdx.x / ncb;
+    const int i = (blockIdx.x % ncb) * CPB + c;
+    const int len = p.lengths ? (int)p.lengths[lane] : (int)p.rows;
+    if (len <= 0) return;  // idle lane: carry and y untouched
+    const size_t row = p.offsets ? p.offsets[lane] : 0;
+    const int d = p.d, s = p.s;
+    const size_t ds = (size_t)d * s;
+    const size_t ldd = p.ld_delta ? p.ld_delta : (size_t)d;
+    const size_t ldbc = p.ld_bc ? p.ld_bc : (size_t)s;
+    float* carry = p.carry ? p.carry + (size_t)(p.lane_slots ? p.lane_slots[lane] : lane) * (p.carry_stride ? p.carry_stride : ds)
+                           : nullptr;
+    const bool live = i < d && q * 4 < s;
+    float yp = 0.0f;
+    if (live) {
+        const size_t so = (size_t)i * s + q * 4;
+        const float4 a4 = __ldg(reinterpret_cast<const float4*>(p.rates + so));
+        const float4 h4 = carry ? *reinterpret_cast<const float4*>(carry + so) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 b4 = __ldg(reinterpret_cast<const float4*>(p.b_proj + row * ldbc + q * 4));
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.c_proj + row * ldbc + q * 4));
+        const float dl = __ldg(p.delta + row * ldd + i);
+        const float w = dl * __ldg(p.x_norm + row * d + i);
+        const float k = dl * 1.4426950408889634f;
+        float4 h;
+        h.x = fmaf(ex2_approx(k * a4.x), h4.x, w * b4.x);
+        h.y = fmaf(ex2_approx(k * a4.y), h4.y, w * b4.y);
+        h.z = fmaf(ex2_approx(k * a4.z), h4.z, w * b4.z);
+        h.w = fmaf(ex2_approx(k * a4.w), h4.w, w * b4.w);
+        yp = fmaf(h.x, c4.x, fmaf(h.y, c4.y, fmaf(h.z, c4.z, h.w * c4.w)));
+        if (carry) *reinterpret_cast<float4*>(carry + so) = h;
+    }
+#pragma unroll
+    for (int m = 1; m < TPC; m <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, m);
+    if (q == 0 && i < d) {
+        p.y[row * d + i] = yp;
+        if (p.y_bf16) reinterpret_cast<__nv_bfloat16*>(p.y_bf16)[row * d + i] = __float2bfloat16_rn(yp);
+    }
+}
+
+template <int TPC>
+int32_t launch_step(pssa_b200_ctx* ctx, const SsmParams& p) {
+    constexpr int CPB = 256 / TPC;
+    size_t blocks = (size_t)((p.d + CPB - 1) / CPB) * p.lanes;
+    if (blocks > 0x7fffffffull)
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM grid (%zu, 1) exceeds grid limits; refusing launch", blocks);
+    ssm_step_kernel<TPC><<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+    return after_launch(ctx, "ssm_step_kernel");
+}
+
 template <int ST, int G, bool EXACT, bool TAPE>
 int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
     constexpr int CH = kThreads / G;
@@ -354,6 +412,14 @@ int32_t launch_one(pssa_b200_ctx* ctx, const SsmParams& p) {
 
 int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact) {
     const int s = p.s;
+    const bool tape = p.states || p.bar_a || p.bar_b;
+    if (p.single_token && !exact && !tape && p.aligned && s <= 128 && (reinterpret_cast<uintptr_t>(p.rates) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(p.carry) & 15) == 0 && ((p.carry_stride ? p.carry_stride : (size_t)p.d * s) & 3) == 0) {
+        if (s <= 16) return launch_step<4>(ctx, p);
+        if (s <= 32) return launch_step<8>(ctx, p);
+        if (s <= 64) return launch_step<16>(ctx, p);
+        return launch_step<32>(ctx, p);
+    }
     if (exact) {
         if (s <= 4) return launch_one<4, 1, true>(ctx, p);
         if (s <= 16) return launch_one<16, 1, true>(ctx, p);

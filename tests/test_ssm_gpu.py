@@ -81,6 +81,33 @@ def test_packed_ragged_lanes_with_an_idle_lane(gpu):
     gpu.set_stream(None)
 
 
+def test_decode_step_shape_one_token_per_lane_with_an_idle_lane(gpu):
+    """Every lane one token long (the decode step, which has its own kernel in the fast mode): y and the carries
+    match the oracle, the idle lane keeps its carry, and a second step continues from the first."""
+    import torch
+    for d, s in ((48, 16), (768, 64), (20, 8), (32, 128)):
+        lengths = np.array([1, 1, 0, 1, 1, 1], np.uint32)
+        offsets = np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.uint32)
+        rows = int(lengths.sum())
+        carry = np.random.default_rng(d).normal(size=(len(lengths), d * s)).astype(np.float32)
+        ref_carry = carry.copy()
+        c = torch.from_numpy(carry).cuda()
+        gpu.set_stream(torch.cuda.current_stream())
+        for step in range(2):
+            delta, bp, cp, x, rates, _ = inputs(rows, d, s, 100 + step)
+            ref_y = O.ssm_lanes(delta, bp, cp, x, rates, ref_carry, offsets, lengths)
+            t = {k: torch.from_numpy(v).cuda() for k, v in dict(delta=delta, bp=bp, cp=cp, x=x, rates=rates).items()}
+            y = torch.zeros(rows, d, device="cuda")
+            gpu.ssm_forward_dev(t["delta"], t["bp"], t["cp"], t["x"], t["rates"], c, y, offsets, lengths, rows, d, s)
+            torch.cuda.synchronize()
+            got_c = c.cpu().numpy()
+            assert np.array_equal(got_c[2], carry[2])  # idle lane untouched
+            assert chan_err(y.cpu().numpy(), ref_y, 0) <= REL_TOL
+            scale = np.maximum(1e-6, np.abs(ref_carry).max())
+            assert float(np.max(np.abs(got_c - ref_carry))) / scale <= REL_TOL
+        gpu.set_stream(None)
+
+
 def test_continuation_equals_one_pass_bitwise_at_model_size(gpu):
     """Size-independent property at the stacked model's shape (d 768, state 64): running a sequence in two
     calls with the carry handed over gives bit-identical y and carry to one call (src/pssa.rs:1245-1247)."""
