@@ -198,6 +198,36 @@ def kernel_roofline(name, launches, ms, rows, peak_hbm, peak_tf):
     return None
 
 
+def run_decode_extra(model, gpu, torch, peak_hbm):
+    """Batched greedy decode of 256 concurrent streams on the same 12-block model (the decode half of BASELINE's
+    long-context configuration): 16-token prompts, then timed steps of one token per stream through
+    pssa_b200_model_decode_step, greedy ids back on the host every step (they are the next step's input)."""
+    streams, warm, steps = 256, 4, 64
+    rng = np.random.default_rng(7)
+    model.reset_recurrent_state()
+    _, ids = model.prefill_batch([rng.integers(1, CFG["d_vocab"], 16) for _ in range(streams)], want_logits=False,
+                                 want_greedy=True)
+    for _ in range(warm):
+        ids = model.decode_step(ids, want_logits=False, want_greedy=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ids = model.decode_step(ids, want_logits=False, want_greedy=True)
+    torch.cuda.synchronize()
+    sec = (time.perf_counter() - t0) / steps
+    d, s = CFG["d_latent"], CFG["d_state"]
+    state_bytes = streams * CFG["depth"] * d * s * 4 * 2  # every carry read and written once per step
+    v, k = CFG["d_vocab"], CFG["d_mem_key"]
+    weight_elems = v * d + CFG["depth"] * (2 * d * d + 2 * s * d + 2 * k * d + d * d + 4 * d * d + 32 * d)  # head + blocks
+    weight_bytes = weight_elems * 2
+    return {"workload": "greedy decode, 256 streams x 1 token per step, 12-block model, ids to host every step",
+            "ms_per_step": sec * 1e3, "tokens_per_s": streams / sec, "steps": steps,
+            "roofline": {"bound": "hbm", "achieved": (state_bytes + weight_bytes) / sec / 1e9, "peak": peak_hbm, "unit": "GB/s",
+                         "frac": (state_bytes + weight_bytes) / sec / 1e9 / peak_hbm,
+                         "note": "algorithmic bytes = recurrent state in and out + bf16 weights once; the step is 136 "
+                                 "launches of which 73 are M = 256 GEMM tiles bound by their own latency"}}
+
+
 def run_extras(gpu, torch, peak_hbm):
     """Operator-alone workloads of BASELINE.json (N = 1 only)."""
     extra = {}
@@ -394,9 +424,11 @@ def run_b200(args):
         }
     del logits_dev
     if world == 1 and rank == 0 and not args.no_extras:
+        decode_extra = run_decode_extra(model, gpu, torch, measured_peaks()[0])
         model.close()
         torch.cuda.empty_cache()
         line["extra"] = run_extras(gpu, torch, measured_peaks()[0])
+        line["extra"]["decode_c5"] = decode_extra
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

@@ -356,6 +356,25 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* model, const uint32_t
 /* `forward_inference` (src/pssa.rs:2387-2391) for n streams at once: one token each. */
 int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* streams, const uint64_t* ids, size_t n,
                                     float* logits, uint64_t* greedy);
+
+/*
+ * Sequence-parallel prefill: one long sequence (or several) split in TIME over `world` processes, one per GPU, each
+ * holding contiguous time shard `rank` of every lane. Not a reference code path; it follows from the reference's scan
+ * monoid (`compose_affine`, src/gpu_batch.rs:75-86): per block a rank reduces its shard to one affine map per
+ * (channel, state) (the sum of delta and the shard's end state from a zero carry), the maps are all-gathered, every
+ * rank folds the lower ranks' maps into its carry-in and runs the fused SSM; everything else in a block is token-local.
+ * The library does not link a communication library: the caller supplies the all-gather.
+ *   exchange(arg, send, recv, bytes) must, in stream order on the context's stream, place rank k's `bytes` at
+ *   recv + k*bytes on every rank (an NCCL all-gather on that stream), and return 0.
+ *   send / recv: DEVICE buffers owned by the caller, max_lanes * (d + d*s) floats and world times that.
+ * While enabled (world > 1), pssa_b200_model_prefill_batch_dev treats its lanes as this rank's shards: lane l must be
+ * the same sequence on every rank (a rank may hold zero tokens of it), every rank gets the same final recurrent
+ * state, and the logits a rank returns are those of ITS last token of each lane (the caller keeps the last
+ * non-empty rank's). world <= 1 or exchange == NULL switches it off.
+ */
+typedef int32_t (*pssa_b200_exchange_fn)(void* arg, const void* send_dev, void* recv_dev, size_t bytes);
+int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev,
+                                   size_t max_lanes, pssa_b200_exchange_fn exchange, void* arg);
 /* Upper bound on token rows processed per pass (activation workspace = about 40 KB per row at d 768). */
 int32_t pssa_b200_model_set_max_rows(pssa_b200_model* model, size_t max_rows);
 

@@ -61,6 +61,7 @@ SIGNATURES = {
     "pssa_b200_ctx_profile_row": (C.c_int32, [_vp, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64),
                                               C.POINTER(C.c_double)]),
     "pssa_b200_model_decode_step": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, _vp]),
+    "pssa_b200_model_set_seqpar": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, _vp, _sz, _vp, _vp]),
 }
 SSM_EXACT = 1
 MEM_EXACT = 1
@@ -68,6 +69,7 @@ MEM_F32_DISTANCE = 2
 EPI_NONE, EPI_SOFTPLUS, EPI_SIGMOID, EPI_SILU, EPI_SCALE, EPI_ADD_OUT = range(6)
 PRECISION_BF16, PRECISION_FP32_EXACT = 0, 1
 CANCEL_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)
+EXCHANGE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t)
 
 
 class Config(C.Structure):

@@ -68,5 +68,16 @@ struct pssa_b200_model {
     std::vector<float> residual_scales;
     float* state = nullptr;  // [max_streams][depth][d*s]
     pssa::Workspace ws;
+    // sequence-parallel prefill (world > 1): this process holds time shard `rank` of every lane
+    struct SeqPar {
+        uint32_t rank = 0, world = 1;
+        float* send = nullptr;      // caller-owned device buffer, max_lanes records of (d + d*s) floats
+        float* recv = nullptr;      // caller-owned device buffer, world * max_lanes records
+        size_t max_lanes = 0;
+        pssa_b200_exchange_fn fn = nullptr;
+        void* arg = nullptr;
+        float* carry_in = nullptr;  // [max_lanes][d*s], owned
+        bool active = false;        // set for the duration of a sharded prefill call only (decode steps stay local)
+    } sp;
     std::vector<bool> tensor_set;  // [depth * T_COUNT + id] upload bookkeeping
 };

@@ -141,6 +141,26 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = m->depth * ds;
         sp.aligned = ssm_vector_ok(sp);
         sp.single_token = single_token;
+        if (m->sp.active) {
+            // sequence-parallel: this process holds one time shard of every lane. Reduce the shard to its affine map
+            // (zero carry in), all-gather the maps, fold the lower ranks' maps into the carry-in, then the real pass.
+            if (lanes > m->sp.max_lanes)
+                return fail(ctx, PSSA_B200_ERR_SHAPE, "sequence-parallel prefill: %zu lanes exceed the %zu the exchange buffers hold", lanes,
+                            m->sp.max_lanes);
+            const size_t rec = (size_t)d + ds;
+            PSSA_CUDA(ctx, cudaMemsetAsync(m->sp.send, 0, lanes * rec * sizeof(float), ctx->stream));
+            SsmParams ag = sp;
+            ag.carry = m->sp.send + d, ag.carry_stride = rec, ag.lane_slots = nullptr;
+            ag.sum_delta = m->sp.send, ag.sum_delta_stride = rec;
+            ag.y_bf16 = nullptr, ag.single_token = 0;  // y of this pass is scratch: the real pass below overwrites it
+            if ((rc = launch_ssm_fused(ctx, ag, exact))) return rc;
+            if (m->sp.fn(m->sp.arg, m->sp.send, m->sp.recv, lanes * rec * sizeof(float)) != 0)
+                return fail(ctx, PSSA_B200_ERR_CUDA, "sequence-parallel prefill: the caller's exchange failed at block %zu", l);
+            if ((rc = launch_seqpar_fold(ctx, m->sp.recv, rec, (int)m->sp.world, (int)m->sp.rank, (int)lanes, lanes * rec, b.rates,
+                                         m->state + l * ds, m->depth * ds, ws.lane_slot, m->sp.carry_in, d, s)))
+                return rc;
+            sp.carry = m->sp.carry_in, sp.carry_stride = ds, sp.lane_slots = nullptr, sp.single_token = 0;
+        }
         if ((rc = launch_ssm_fused(ctx, sp, exact))) return rc;
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
         if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
@@ -322,6 +342,8 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
             head_lane.push_back(l);
         }
     }
+    if (rows == 0 && m->sp.world > 1)  // the other ranks would wait in the exchange for ever
+        return fail(ctx, PSSA_B200_ERR_SHAPE, "sequence-parallel prefill: rank %u holds no token of any lane", m->sp.rank);
     if (rows == 0) return PSSA_B200_OK;
     if (span > m->max_rows)
         return fail(ctx, PSSA_B200_ERR_SHAPE, "prefill_batch_dev: %zu token rows exceed one pass of %zu rows (set_max_rows)", span, m->max_rows);
@@ -336,7 +358,10 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
     PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, h_slot.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
     PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
     float* feats = nullptr;
-    if ((rc = forward_rows(m, span, n_lanes, h_off.data(), h_len.data(), &feats))) return rc;
+    m->sp.active = m->sp.world > 1;
+    rc = forward_rows(m, span, n_lanes, h_off.data(), h_len.data(), &feats);
+    m->sp.active = false;
+    if (rc) return rc;
     if (logits_dev || greedy_dev) {
         if ((rc = head_rows(m, feats, h_last.size(), greedy_dev != nullptr))) return rc;
         size_t i = 0;
@@ -351,6 +376,27 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
             i = j + 1;
         }
     }
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev, size_t max_lanes,
+                                   pssa_b200_exchange_fn exchange, void* arg) {
+    if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
+    pssa_b200_ctx* ctx = m->ctx;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (m->sp.carry_in) cudaFree(m->sp.carry_in);
+    m->sp = pssa_b200_model::SeqPar{};
+    if (world <= 1 || !exchange) return PSSA_B200_OK;
+    if (rank >= world) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel rank %u outside world of %u", rank, world);
+    if (!send_dev || !recv_dev || max_lanes == 0)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel prefill needs exchange buffers and a lane capacity");
+    if (((uintptr_t)send_dev & 15) || ((uintptr_t)recv_dev & 15))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel exchange buffers must be 16-byte aligned");
+    float* tmp = nullptr;
+    PSSA_CUDA(ctx, cudaMalloc(&tmp, max_lanes * m->d * m->s * sizeof(float)));
+    m->sp.rank = rank, m->sp.world = world, m->sp.send = (float*)send_dev, m->sp.recv = (float*)recv_dev;
+    m->sp.max_lanes = max_lanes, m->sp.fn = exchange, m->sp.arg = arg, m->sp.carry_in = tmp;
     return PSSA_B200_OK;
 }
 

@@ -1,0 +1,97 @@
+"""Sequence-parallel prefill on two GPUs (NCCL): time-sharded prefill of ragged sequences gives the logits and the
+final recurrent state of the single-GPU prefill, on both ranks. Skipped on a one-GPU box."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(depth=3, d_vocab=257, d_latent=64, d_state=16, d_mem_key=16, mem_capacity=64)
+LENGTHS = (203, 64, 2, 131)
+
+
+def _build(gpu, precision):
+    import oracle as O
+    import pssa_b200
+    from helpers import fill_synthetic, upload
+    om = O.Model.new(CFG["depth"], CFG["d_vocab"], CFG["d_latent"], CFG["d_state"], CFG["d_mem_key"], CFG["mem_capacity"],
+                     tau_mem=0.1, seed=3)
+    fill_synthetic(om, 3)
+    gm = pssa_b200.PSSAModel(gpu, CFG["depth"], CFG["d_vocab"], CFG["d_latent"], CFG["d_state"], CFG["d_mem_key"],
+                             CFG["mem_capacity"], tau_mem=0.1, streams=len(LENGTHS), precision=precision)
+    upload(om, gm)
+    return gm
+
+
+def _prompts():
+    rng = np.random.default_rng(5)
+    return [rng.integers(1, CFG["d_vocab"], n) for n in LENGTHS]
+
+
+def _rank_main(rank, world, port, q):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import torch
+    import torch.distributed as dist
+    import pssa_b200
+    from pssa_b200 import seqpar as SP
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    out = {}
+    try:
+        gpu = pssa_b200.B200Dispatch(rank)
+        gpu.set_stream(torch.cuda.current_stream())
+        for precision in (1, 0):  # fp32 exact, then the bf16 mode
+            gm = _build(gpu, precision)
+            ref_logits, _ = gm.prefill_batch([list(p) for p in _prompts()])
+            ref_state = [gm.copy_recurrent_state_to(l) for l in range(len(LENGTHS))]
+            gm.reset_recurrent_state()
+            sp = SP.SequenceParallelPrefill(gm, max_lanes=len(LENGTHS))
+            logits = sp.prefill(_prompts())
+            torch.cuda.synchronize()
+            state = [gm.copy_recurrent_state_to(l) for l in range(len(LENGTHS))]
+            # decode continues locally from the shared final state
+            step, _ = gm.decode_step([7, 8, 9, 10], want_logits=True, want_greedy=True)
+            sp.close()
+            gm.close()
+            out[precision] = (ref_logits, logits, ref_state, state, step)
+        q.put((rank, out))
+        dist.barrier()
+        gpu.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpu_time_sharded_prefill_matches_one_gpu():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    for precision, tol in ((1, 1e-5), (0, 2e-3)):
+        r0, r1 = res[0][precision], res[1][precision]
+        ref_logits, logits0, ref_state, state0, step0 = r0
+        _, logits1, _, state1, step1 = r1
+        scale = np.abs(ref_logits).max()
+        assert np.max(np.abs(logits0 - ref_logits)) / scale <= tol, precision
+        assert np.array_equal(logits0, logits1)  # every rank returns the owner's rows
+        for l in range(len(LENGTHS)):
+            s_scale = max(1e-6, np.abs(ref_state[l]).max())
+            assert np.max(np.abs(state0[l] - ref_state[l])) / s_scale <= tol
+            assert np.max(np.abs(state1[l] - ref_state[l])) / s_scale <= tol
+        assert np.max(np.abs(step0 - step1)) / scale <= tol  # replicas stay in step after the sharded prefill
