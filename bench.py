@@ -436,6 +436,82 @@ def run_b200(args):
     gpu.close()
 
 
+def run_seqpar(args):
+    """BASELINE's long-context configuration: 8 sequences x 65536 tokens of the same 12-block model, time-sharded over
+    the N ranks (strong scaling: the job is fixed, a rank holds 8 x 65536/N token rows). One step = one sharded
+    prefill from zero state, per-block all-gather of the shard maps over NCCL inside the timed region."""
+    import torch
+    import torch.distributed as dist
+
+    import pssa_b200
+    from pssa_b200 import _native as N
+    from pssa_b200 import seqpar as SP
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus or world < 2:
+        raise SystemExit("--workload seqpar_c5 needs --gpus N >= 2 under torch.distributed.run")
+    lanes, t_full = 8, args.seq_len
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    gpu = pssa_b200.B200Dispatch(local)
+    stream = torch.cuda.current_stream()
+    gpu.set_stream(stream)
+    tensors, banks = synth_weights(1234)
+    model = pssa_b200.PSSAModel(gpu, tau_mem=0.1, streams=lanes, precision=N.PRECISION_BF16, **CFG)
+    for (layer, tid), arr in tensors.items():
+        model.set_tensor(layer, tid, arr)
+    for l, (keys, norm_sq, values) in enumerate(banks):
+        model.set_bank(l, keys, norm_sq, values, CFG["mem_capacity"])
+    rows_rank = lanes * ((t_full + world - 1) // world)
+    model.set_max_rows(rows_rank)
+    sp = SP.SequenceParallelPrefill(model, max_lanes=lanes)
+    prompts = np.random.default_rng(100).integers(1, CFG["d_vocab"], (lanes, t_full))  # the same job on every rank
+    ids, offsets, lengths = SP.pack_shard(list(prompts), world, rank)
+    ids_dev = torch.from_numpy(ids.astype(np.int64)).to(torch.int32).cuda()
+    logits_dev = torch.empty(lanes, CFG["d_vocab"], device="cuda")
+
+    def step():
+        model.reset_recurrent_state()
+        model.prefill_batch_dev(ids_dev, offsets, lengths, None, logits_dev, None)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    warm = max(3, args.warmup)
+    for _ in range(warm):
+        step()
+    barrier()
+    gpu.profile_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    prof = gpu.profile_end()
+    tmax = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    ms = float(tmax.item()) / args.steps
+    if rank == 0:
+        total = sum(v for _, v in prof.values())
+        print(json.dumps({
+            "metric": "prefill_tokens_per_s", "value": lanes * t_full / (ms / 1e3), "unit": "tok/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"seqpar_c5: 12-block PSSA, {lanes} sequences x {t_full} tokens time-sharded over {world} GPUs "
+                                   f"({rows_rank} token rows per GPU), per-block NCCL all-gather of the shard maps"},
+            "kernels": [{"kernel": k, "ms_per_step": v / args.steps, "share": v / total}
+                        for k, (_, v) in sorted(prof.items(), key=lambda kv: -kv[1][1])],
+            "exchange_bytes_per_rank_per_block": lanes * (CFG["d_latent"] + CFG["d_latent"] * CFG["d_state"]) * 4,
+        }))
+    sp.close()
+    dist.destroy_process_group()
+    gpu.close()
+
+
 def main():
     global LANES
     ap = argparse.ArgumentParser()
@@ -447,6 +523,9 @@ def main():
     ap.add_argument("--lanes", type=int, default=LANES,
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures, not the benchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and parity sample (profiler captures)")
+    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5"],
+                    help="prefill_c4 is the benchmark; seqpar_c5 is the long-context time-sharded prefill (N >= 2)")
+    ap.add_argument("--seq-len", type=int, default=65536, help="sequence length of the seqpar_c5 workload")
     args = ap.parse_args()
     if args.lanes != LANES:
         global WORKLOAD
@@ -454,6 +533,8 @@ def main():
         LANES = args.lanes
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "seqpar_c5":
+        run_seqpar(args)
     else:
         run_b200(args)
 

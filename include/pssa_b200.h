@@ -366,7 +366,9 @@ int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* stre
  * The library does not link a communication library: the caller supplies the all-gather.
  *   exchange(arg, send, recv, bytes) must, in stream order on the context's stream, place rank k's `bytes` at
  *   recv + k*bytes on every rank (an NCCL all-gather on that stream), and return 0.
- *   send / recv: DEVICE buffers owned by the caller, max_lanes * (d + d*s) floats and world times that.
+ *   send / recv: DEVICE buffers owned by the caller, `capacity` records of (d + d*s) floats and world times that. A
+ *   record is one (lane, time chunk): each lane's shard is cut into up to 16 chunks so that a launch fills the GPU
+ *   even with few lanes; capacity >= lanes is required, lanes * 16 lets the library choose freely.
  * While enabled (world > 1), pssa_b200_model_prefill_batch_dev treats its lanes as this rank's shards: lane l must be
  * the same sequence on every rank (a rank may hold zero tokens of it), every rank gets the same final recurrent
  * state, and the logits a rank returns are those of ITS last token of each lane (the caller keeps the last
@@ -374,7 +376,7 @@ int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* stre
  */
 typedef int32_t (*pssa_b200_exchange_fn)(void* arg, const void* send_dev, void* recv_dev, size_t bytes);
 int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev,
-                                   size_t max_lanes, pssa_b200_exchange_fn exchange, void* arg);
+                                   size_t capacity, pssa_b200_exchange_fn exchange, void* arg);
 /* Upper bound on token rows processed per pass (activation workspace = about 40 KB per row at d 768). */
 int32_t pssa_b200_model_set_max_rows(pssa_b200_model* model, size_t max_rows);
 

@@ -41,7 +41,7 @@ struct SsmParams {
     const uint32_t* lane_slots;
     size_t carry_stride;   // 0 = d*s
     int single_token;      // caller's promise that every lane is at most one token long (a decode step)
-    // optional: per lane and channel, the sum of delta over the lane's rows (accumulated in f64, stored f32) at
+    // optional (needs offsets / lengths): per lane and channel, the sum of delta over the lane's rows (f64 sum, f32 out) at
     // sum_delta + lane * sum_delta_stride + i. With a zero carry in, (sum_delta, carry out) is the affine map of the
     // lane's time shard: h_out = exp(A * sum_delta) * h_in + carry_out (sequence-parallel prefill).
     float* sum_delta;
@@ -58,10 +58,13 @@ inline bool ssm_vector_ok(const SsmParams& p) {
 
 // Sequence-parallel prefill: fold the gathered per-rank shard maps (records of `rec` floats per lane: d sums of delta,
 // then d*s shard states from a zero carry) into this rank's carry-in and into the sequence's final state.
-//   h = state(lane); for k in 0..world: { if (k == rank) carry_in = h; h = exp(A * sum_delta_k) * h + Q_k }; state = h
-int32_t launch_seqpar_fold(pssa_b200_ctx* ctx, const float* gathered, size_t rec, int world, int rank, int lanes, size_t lanes_stride,
-                           const float* rates, float* state, size_t state_stride, const uint32_t* lane_slots, float* carry_in,
-                           int d, int s);
+// Each lane's shard is itself `chunks` consecutive time chunks (records ordered [rank][lane][chunk]).
+//   h = state(lane); for k in 0..world, c in 0..chunks: { if (k == rank) carry_in(lane, c) = h; h = exp(A * sum_delta) * h + Q };
+//   state(lane) = h
+// world == 1 is the single-GPU time split of long sequences with few lanes.
+int32_t launch_seqpar_fold(pssa_b200_ctx* ctx, const float* gathered, size_t rec, int world, int rank, int chunks, int lanes,
+                           size_t rank_stride, const float* rates, float* state, size_t state_stride, const uint32_t* lane_slots,
+                           float* carry_in, int d, int s);
 
 // retrieve_poincare.cu
 struct RetrieveParams {

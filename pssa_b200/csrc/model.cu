@@ -132,7 +132,7 @@ void pssa_b200_model_destroy(pssa_b200_model* m) {
     cudaFree(m->unembed);
     cudaFree(m->unembed_bf16);
     cudaFree(m->state);
-    cudaFree(m->sp.carry_in);
+    cudaFree(m->chunks.off), cudaFree(m->chunks.len), cudaFree(m->chunks.records), cudaFree(m->chunks.carry_in);
     for (auto& b : m->blocks) {
         for (int id : kBlockTensors) cudaFree(b.w[id]);
         cudaFree(b.rates);

@@ -71,13 +71,19 @@ struct pssa_b200_model {
     // sequence-parallel prefill (world > 1): this process holds time shard `rank` of every lane
     struct SeqPar {
         uint32_t rank = 0, world = 1;
-        float* send = nullptr;      // caller-owned device buffer, max_lanes records of (d + d*s) floats
-        float* recv = nullptr;      // caller-owned device buffer, world * max_lanes records
-        size_t max_lanes = 0;
+        float* send = nullptr;      // caller-owned device buffer, `capacity` records of (d + d*s) floats
+        float* recv = nullptr;      // caller-owned device buffer, world * capacity records
+        size_t capacity = 0;        // records (lanes x time chunks) the exchange buffers hold
         pssa_b200_exchange_fn fn = nullptr;
         void* arg = nullptr;
-        float* carry_in = nullptr;  // [max_lanes][d*s], owned
         bool active = false;        // set for the duration of a sharded prefill call only (decode steps stay local)
     } sp;
+    // time chunks ("virtual lanes") of the two-pass SSM: chunk maps, chunk carry-ins and the chunk row ranges
+    struct Chunks {
+        size_t capacity = 0;        // virtual lanes the buffers hold
+        uint32_t *off = nullptr, *len = nullptr;
+        float* records = nullptr;   // [capacity][d + d*s]  (local mode; the sharded mode uses sp.send)
+        float* carry_in = nullptr;  // [capacity][d*s]
+    } chunks;
     std::vector<bool> tensor_set;  // [depth * T_COUNT + id] upload bookkeeping
 };

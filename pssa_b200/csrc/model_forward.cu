@@ -60,6 +60,23 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     return PSSA_B200_OK;
 }
 
+// buffers of the two-pass (time-chunked) SSM; grow on demand
+int32_t ensure_chunks(pssa_b200_model* m, size_t vlanes) {
+    auto& c = m->chunks;
+    if (vlanes <= c.capacity) return PSSA_B200_OK;
+    pssa_b200_ctx* ctx = m->ctx;
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaFree(c.off), cudaFree(c.len), cudaFree(c.records), cudaFree(c.carry_in);
+    c = pssa_b200_model::Chunks{};
+    const size_t ds = m->d * m->s;
+    PSSA_CUDA(ctx, cudaMalloc((void**)&c.off, vlanes * 4));
+    PSSA_CUDA(ctx, cudaMalloc((void**)&c.len, vlanes * 4));
+    PSSA_CUDA(ctx, cudaMalloc((void**)&c.records, vlanes * (m->d + ds) * sizeof(float)));
+    PSSA_CUDA(ctx, cudaMalloc((void**)&c.carry_in, vlanes * ds * sizeof(float)));
+    c.capacity = vlanes;
+    return PSSA_B200_OK;
+}
+
 // refresh the bf16 weight copies the tensor-core path reads (concatenated x-side projections)
 int32_t refresh_bf16(pssa_b200_model* m) {
     pssa_b200_ctx* ctx = m->ctx;
@@ -111,9 +128,42 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
     if (!exact && (rc = refresh_bf16(m))) return rc;
     float* feat_in = nullptr;
     float* feat_out = ws.feat_a;
-    (void)h_off;
     bool single_token = true;  // a decode step: the SSM stage is then one pass over the carries
-    for (size_t l = 0; l < lanes; ++l) single_token = single_token && h_len[l] <= 1;
+    uint32_t max_len = 0;
+    for (size_t l = 0; l < lanes; ++l) single_token = single_token && h_len[l] <= 1, max_len = std::max(max_len, h_len[l]);
+    // Time chunks. The fused SSM kernel parallelises over lanes x channels only; with few lanes (long sequences) that
+    // leaves most SMs idle, so each lane is cut into `n_chunks` consecutive time chunks that run as independent
+    // "virtual lanes" in two passes: chunk maps from a zero carry, a fold of the maps in time order, then the real pass
+    // with each chunk's carry-in. Every exp is paid twice, so this is only done when the plain launch would occupy at
+    // most one CTA per SM -- or in the sequence-parallel mode, where the two passes are paid anyway.
+    const size_t ctas = lanes * ((m->d + 63) / 64);
+    const size_t slots = (size_t)ctx->sm_count * 4;
+    size_t n_chunks = 1;
+    if (!single_token && (m->sp.active || ctas <= (size_t)ctx->sm_count)) {
+        n_chunks = std::min<size_t>(16, std::max<size_t>(1, slots / ctas));
+        if (m->sp.active)  // identical on every rank: depends on the lane count and the buffer capacity only
+            n_chunks = std::min(n_chunks, std::max<size_t>(1, m->sp.capacity / lanes));
+        else
+            n_chunks = std::min(n_chunks, std::max<size_t>(1, max_len / 128));
+    }
+    const bool two_pass = m->sp.active || n_chunks > 1;
+    const size_t vlanes = lanes * n_chunks;
+    if (two_pass) {
+        if (m->sp.active && vlanes > m->sp.capacity)
+            return fail(ctx, PSSA_B200_ERR_SHAPE, "sequence-parallel prefill: %zu lanes exceed the %zu records the exchange buffers hold",
+                        lanes, m->sp.capacity);
+        if ((rc = ensure_chunks(m, vlanes))) return rc;
+        std::vector<uint32_t> v_off(vlanes), v_len(vlanes);
+        for (size_t l = 0; l < lanes; ++l)
+            for (size_t c = 0; c < n_chunks; ++c) {
+                const uint32_t a = (uint32_t)((uint64_t)h_len[l] * c / n_chunks), e = (uint32_t)((uint64_t)h_len[l] * (c + 1) / n_chunks);
+                v_off[l * n_chunks + c] = h_off[l] + a, v_len[l * n_chunks + c] = e - a;
+            }
+        // pageable source: the copies complete before these vectors go out of scope
+        PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.off, v_off.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.len, v_len.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
+        PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
     for (size_t l = 0; l < m->depth; ++l) {
         DeviceBlock& b = m->blocks[l];
         // stage 1: gather + RMSNorm (src/gpu_batch.rs:445-472)
@@ -141,25 +191,32 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = m->depth * ds;
         sp.aligned = ssm_vector_ok(sp);
         sp.single_token = single_token;
-        if (m->sp.active) {
-            // sequence-parallel: this process holds one time shard of every lane. Reduce the shard to its affine map
-            // (zero carry in), all-gather the maps, fold the lower ranks' maps into the carry-in, then the real pass.
-            if (lanes > m->sp.max_lanes)
-                return fail(ctx, PSSA_B200_ERR_SHAPE, "sequence-parallel prefill: %zu lanes exceed the %zu the exchange buffers hold", lanes,
-                            m->sp.max_lanes);
+        if (two_pass) {
+            // pass 1: every chunk's affine map (sum of delta, end state from a zero carry), one record per virtual lane
             const size_t rec = (size_t)d + ds;
-            PSSA_CUDA(ctx, cudaMemsetAsync(m->sp.send, 0, lanes * rec * sizeof(float), ctx->stream));
+            float* records = m->sp.active ? m->sp.send : m->chunks.records;
+            PSSA_CUDA(ctx, cudaMemsetAsync(records, 0, vlanes * rec * sizeof(float), ctx->stream));
             SsmParams ag = sp;
-            ag.carry = m->sp.send + d, ag.carry_stride = rec, ag.lane_slots = nullptr;
-            ag.sum_delta = m->sp.send, ag.sum_delta_stride = rec;
+            ag.offsets = m->chunks.off, ag.lengths = m->chunks.len, ag.lanes = (int)vlanes;
+            ag.carry = records + d, ag.carry_stride = rec, ag.lane_slots = nullptr;
+            ag.sum_delta = records, ag.sum_delta_stride = rec;
             ag.y_bf16 = nullptr, ag.single_token = 0;  // y of this pass is scratch: the real pass below overwrites it
             if ((rc = launch_ssm_fused(ctx, ag, exact))) return rc;
-            if (m->sp.fn(m->sp.arg, m->sp.send, m->sp.recv, lanes * rec * sizeof(float)) != 0)
-                return fail(ctx, PSSA_B200_ERR_CUDA, "sequence-parallel prefill: the caller's exchange failed at block %zu", l);
-            if ((rc = launch_seqpar_fold(ctx, m->sp.recv, rec, (int)m->sp.world, (int)m->sp.rank, (int)lanes, lanes * rec, b.rates,
-                                         m->state + l * ds, m->depth * ds, ws.lane_slot, m->sp.carry_in, d, s)))
+            const float* gathered = records;
+            int world = 1, rank = 0;
+            if (m->sp.active) {
+                // all-gather of the records over the ranks (the caller's NCCL, in stream order)
+                if (m->sp.fn(m->sp.arg, m->sp.send, m->sp.recv, vlanes * rec * sizeof(float)) != 0)
+                    return fail(ctx, PSSA_B200_ERR_CUDA, "sequence-parallel prefill: the caller's exchange failed at block %zu", l);
+                gathered = m->sp.recv, world = (int)m->sp.world, rank = (int)m->sp.rank;
+            }
+            // fold in time order: carry-in of each of this rank's chunks, and the lanes' final state
+            if ((rc = launch_seqpar_fold(ctx, gathered, rec, world, rank, (int)n_chunks, (int)lanes, vlanes * rec, b.rates,
+                                         m->state + l * ds, m->depth * ds, ws.lane_slot, m->chunks.carry_in, d, s)))
                 return rc;
-            sp.carry = m->sp.carry_in, sp.carry_stride = ds, sp.lane_slots = nullptr, sp.single_token = 0;
+            // pass 2: the real one, over the virtual lanes with their carry-ins (carry-outs are scratch)
+            sp.offsets = m->chunks.off, sp.lengths = m->chunks.len, sp.lanes = (int)vlanes;
+            sp.carry = m->chunks.carry_in, sp.carry_stride = ds, sp.lane_slots = nullptr, sp.single_token = 0;
         }
         if ((rc = launch_ssm_fused(ctx, sp, exact))) return rc;
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
@@ -379,24 +436,21 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
     return PSSA_B200_OK;
 }
 
-int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev, size_t max_lanes,
+int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev, size_t capacity,
                                    pssa_b200_exchange_fn exchange, void* arg) {
     if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
     pssa_b200_ctx* ctx = m->ctx;
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    if (m->sp.carry_in) cudaFree(m->sp.carry_in);
     m->sp = pssa_b200_model::SeqPar{};
     if (world <= 1 || !exchange) return PSSA_B200_OK;
     if (rank >= world) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel rank %u outside world of %u", rank, world);
-    if (!send_dev || !recv_dev || max_lanes == 0)
-        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel prefill needs exchange buffers and a lane capacity");
+    if (!send_dev || !recv_dev || capacity == 0)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel prefill needs exchange buffers and a record capacity");
     if (((uintptr_t)send_dev & 15) || ((uintptr_t)recv_dev & 15))
         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sequence-parallel exchange buffers must be 16-byte aligned");
-    float* tmp = nullptr;
-    PSSA_CUDA(ctx, cudaMalloc(&tmp, max_lanes * m->d * m->s * sizeof(float)));
     m->sp.rank = rank, m->sp.world = world, m->sp.send = (float*)send_dev, m->sp.recv = (float*)recv_dev;
-    m->sp.max_lanes = max_lanes, m->sp.fn = exchange, m->sp.arg = arg, m->sp.carry_in = tmp;
+    m->sp.capacity = capacity, m->sp.fn = exchange, m->sp.arg = arg;
     return PSSA_B200_OK;
 }
 

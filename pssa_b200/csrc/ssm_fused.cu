@@ -139,8 +139,6 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
     }
 
     const int ntiles = (len + kTileTokens - 1) / kTileTokens;
-    const bool want_sum = TAPE && p.sum_delta != nullptr;  // rides in the tape instantiation: the hot one keeps its registers
-    double sum_dl = 0.0;
 
     auto load_tile = [&](int k) {
         if (k < ntiles) {
@@ -219,7 +217,6 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
             const float dl = dd[tt * CH + c];
             const float xv = dx[tt * CH + c];
             const size_t row = row0 + t0 + tt;
-            if (want_sum) sum_dl += (double)dl;
             static_assert(ST % 4 == 0, "states per thread are loaded as float4");
             float bj[ST], cj[ST];
 #pragma unroll
@@ -311,7 +308,6 @@ __global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMin
         }
     }
     cp_async_wait<0>();
-    if (want_sum && g == 0 && valid && len > 0) p.sum_delta[(size_t)lane * p.sum_delta_stride + i] = (float)sum_dl;
     if (carry && len > 0) {
         if (vec_state) {
 #pragma unroll
@@ -384,9 +380,34 @@ int32_t launch_step(pssa_b200_ctx* ctx, const SsmParams& p) {
     return after_launch(ctx, "ssm_step_kernel");
 }
 
-// One thread per (lane, channel, state): walks the ranks' shard maps in time order.
+// Sum of delta over each lane's rows, per channel (the decay half of a time shard's affine map: the product of
+// exp(delta_t * A) over the shard is exp(A * sum of delta)). One CTA = one lane x 32 channels; 8 row-strided partial sums
+// per channel in f64, combined in a fixed order.
+__global__ void __launch_bounds__(256) sum_delta_kernel(const float* __restrict__ delta, size_t ldd, const uint32_t* __restrict__ offsets,
+                                                        const uint32_t* __restrict__ lengths, int d, float* __restrict__ out,
+                                                        size_t out_stride) {
+    __shared__ double part[8][32];
+    const int lane = blockIdx.y;
+    const int c = threadIdx.x & 31, tq = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + c;
+    const size_t row0 = offsets[lane];
+    const int len = (int)lengths[lane];
+    double acc = 0.0;
+    if (i < d)
+        for (int t = tq; t < len; t += 8) acc += (double)__ldg(delta + (row0 + t) * ldd + i);
+    part[tq][c] = acc;
+    __syncthreads();
+    if (tq == 0 && i < d) {
+        double sum = 0.0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sum += part[k][c];
+        out[(size_t)lane * out_stride + i] = (float)sum;
+    }
+}
+
+// One thread per (lane, channel, state): walks the shard maps of every rank and time chunk in time order.
 __global__ void __launch_bounds__(256) seqpar_fold_kernel(const float* __restrict__ gathered, size_t rec, int world, int rank,
-                                                          size_t lanes_stride, const float* __restrict__ rates,
+                                                          int chunks, size_t rank_stride, const float* __restrict__ rates,
                                                           float* __restrict__ state, size_t state_stride,
                                                           const uint32_t* __restrict__ lane_slots, float* __restrict__ carry_in,
                                                           int d, int s) {
@@ -399,10 +420,13 @@ __global__ void __launch_bounds__(256) seqpar_fold_kernel(const float* __restric
     const float a = rates[e];
     float h = st[e];
     for (int k = 0; k < world; ++k) {
-        if (k == rank) carry_in[(size_t)lane * ds + e] = h;
-        const float* r = gathered + (size_t)k * lanes_stride + (size_t)lane * rec;
-        const float pk = expf(__fmul_rn(a, r[i]));
-        h = __fadd_rn(__fmul_rn(pk, h), r[d + e]);
+        for (int c = 0; c < chunks; ++c) {
+            const size_t v = (size_t)lane * chunks + c;
+            if (k == rank) carry_in[v * ds + e] = h;
+            const float* r = gathered + (size_t)k * rank_stride + v * rec;
+            const float pk = expf(__fmul_rn(a, r[i]));
+            h = __fadd_rn(__fmul_rn(pk, h), r[d + e]);
+        }
     }
     st[e] = h;
 }
@@ -431,27 +455,36 @@ int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
 // each; inference never asks for them, so they live in a separate instantiation.
 template <int ST, int G, bool EXACT>
 int32_t launch_one(pssa_b200_ctx* ctx, const SsmParams& p) {
-    if (p.states || p.bar_a || p.bar_b || p.sum_delta) return launch_cfg<ST, G, EXACT, true>(ctx, p);
+    if (p.states || p.bar_a || p.bar_b) return launch_cfg<ST, G, EXACT, true>(ctx, p);
     return launch_cfg<ST, G, EXACT, false>(ctx, p);
 }
 
 }  // namespace
 
-int32_t launch_seqpar_fold(pssa_b200_ctx* ctx, const float* gathered, size_t rec, int world, int rank, int lanes, size_t lanes_stride,
-                           const float* rates, float* state, size_t state_stride, const uint32_t* lane_slots, float* carry_in,
-                           int d, int s) {
+int32_t launch_seqpar_fold(pssa_b200_ctx* ctx, const float* gathered, size_t rec, int world, int rank, int chunks, int lanes,
+                           size_t rank_stride, const float* rates, float* state, size_t state_stride, const uint32_t* lane_slots,
+                           float* carry_in, int d, int s) {
     const size_t ds = (size_t)d * s;
     dim3 grid((unsigned)((ds + 255) / 256), (unsigned)lanes);
-    if (lanes < 1 || lanes > 65535) return fail(ctx, PSSA_B200_ERR_SHAPE, "sequence-parallel fold: %d lanes outside 1..65535", lanes);
-    seqpar_fold_kernel<<<grid, 256, 0, ctx->stream>>>(gathered, rec, world, rank, lanes_stride, rates, state, state_stride, lane_slots,
-                                                     carry_in, d, s);
+    if (lanes < 1 || lanes > 65535) return fail(ctx, PSSA_B200_ERR_SHAPE, "chunk fold: %d lanes outside 1..65535", lanes);
+    seqpar_fold_kernel<<<grid, 256, 0, ctx->stream>>>(gathered, rec, world, rank, chunks, rank_stride, rates, state, state_stride,
+                                                     lane_slots, carry_in, d, s);
     return after_launch(ctx, "seqpar_fold_kernel");
 }
 
 int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact) {
     const int s = p.s;
+    if (p.sum_delta) {
+        if (!p.offsets || !p.lengths) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 SSM: sum_delta needs lane offsets and lengths");
+        if (p.lanes > 65535) return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM: sum_delta supports at most 65535 lanes; refusing launch");
+        dim3 grid((unsigned)((p.d + 31) / 32), (unsigned)p.lanes);
+        sum_delta_kernel<<<grid, 256, 0, ctx->stream>>>(p.delta, p.ld_delta ? p.ld_delta : (size_t)p.d, p.offsets, p.lengths, p.d,
+                                                       p.sum_delta, p.sum_delta_stride);
+        int32_t rc = after_launch(ctx, "sum_delta_kernel");
+        if (rc != PSSA_B200_OK) return rc;
+    }
     const bool tape = p.states || p.bar_a || p.bar_b;
-    if (p.single_token && !p.sum_delta && !exact && !tape && p.aligned && s <= 128 && (reinterpret_cast<uintptr_t>(p.rates) & 15) == 0 &&
+    if (p.single_token && !exact && !tape && p.aligned && s <= 128 && (reinterpret_cast<uintptr_t>(p.rates) & 15) == 0 &&
         (reinterpret_cast<uintptr_t>(p.carry) & 15) == 0 && ((p.carry_stride ? p.carry_stride : (size_t)p.d * s) & 3) == 0) {
         if (s <= 16) return launch_step<4>(ctx, p);
         if (s <= 32) return launch_step<8>(ctx, p);

@@ -89,9 +89,10 @@ class SequenceParallelPrefill:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.max_lanes = max_lanes
         rec = model.d_latent + model.d_latent * model.d_state
+        capacity = max_lanes * 16  # records: the library cuts each lane's shard into up to 16 time chunks
         dev = torch.device("cuda", torch.cuda.current_device())
-        self._send = torch.zeros(max_lanes * rec, dtype=torch.float32, device=dev)
-        self._recv = torch.zeros(self.world * max_lanes * rec, dtype=torch.float32, device=dev)
+        self._send = torch.zeros(capacity * rec, dtype=torch.float32, device=dev)
+        self._recv = torch.zeros(self.world * capacity * rec, dtype=torch.float32, device=dev)
         self._error = None
 
         def exchange(_arg, _send, _recv, nbytes):
@@ -107,7 +108,7 @@ class SequenceParallelPrefill:
         self._callback = N.EXCHANGE_FN(exchange)  # keep alive as long as the library may call it
         model.gpu._check(model._lib.pssa_b200_model_set_seqpar(
             model._h, self.rank, self.world, C.c_void_p(self._send.data_ptr()), C.c_void_p(self._recv.data_ptr()),
-            max_lanes, self._callback, None))
+            capacity, self._callback, None))
 
     def close(self):
         if self.model is not None and getattr(self.model, "_h", None):

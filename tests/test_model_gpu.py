@@ -213,3 +213,22 @@ def test_device_resident_prefill_equals_the_host_entry_and_profile_rows_add_up(g
     assert np.array_equal(greedy_dev.cpu().numpy().astype(np.uint64), host_greedy)
     assert launched > 0 and sum(n for n, _ in rows.values()) == launched
     assert all(ms >= 0 for _, ms in rows.values()) and any("ssm_fused" in k for k in rows)
+
+
+def test_long_single_sequence_uses_time_chunks_and_matches_the_oracle(gpu):
+    """One lane of 700 tokens cannot fill the GPU by channels alone: the library cuts it into time chunks (chunk maps,
+    fold, second pass). Logits and the final state still match the token-serial oracle in the fp32 mode."""
+    om, gm = make_pair(gpu, 2, 61, 32, 8, 8, 12, seed=13, streams=1)
+    ids = (np.arange(700) * 7 + 3) % 61
+    gpu.profile_begin()
+    _, logits = gm.prefill_inference(ids)
+    rows = gpu.profile_end()
+    assert "seqpar_fold_kernel" in rows and rows["seqpar_fold_kernel"][0] == 2  # once per block
+    _, _, ref = om.prefill_inference(ids)
+    assert scale_err(logits, ref) <= 1e-5
+    ref_state = om.state()
+    assert np.max(np.abs(gm.copy_recurrent_state_to(0) - ref_state)) <= 1e-5 * max(1.0, np.abs(ref_state).max())
+    # continuing token by token from the chunked prefill equals continuing on the CPU
+    a = gm.forward_inference(5)
+    b = om.forward_inference(5)
+    assert scale_err(a, b) <= 1e-5
