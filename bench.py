@@ -228,6 +228,46 @@ def run_decode_extra(model, gpu, torch, peak_hbm):
                                  "launches of which 73 are M = 256 GEMM tiles bound by their own latency"}}
 
 
+def run_generate_c1(gpu):
+    """configs[0], the reference's own CPU case: one block, vocabulary 8192, d 192, state 64, 512 slots; batch 1,
+    prefill 512 tokens then 200 greedy tokens (the reference publishes 200 tokens in 226 ms on its CPU path)."""
+    import pssa_b200
+    from pssa_b200 import _native as N
+    from pssa_b200 import model as M
+    v, d, s, k, cap = 8192, 192, 64, 64, 512
+    rng = np.random.default_rng(3)
+    out = {}
+    for name, precision in (("fp32_exact", N.PRECISION_FP32_EXACT), ("bf16", N.PRECISION_BF16)):
+        m = pssa_b200.PSSAModel(gpu, 1, v, d, s, k, cap, tau_mem=0.1, streams=1, precision=precision)
+        nrm = lambda *shape: (rng.standard_normal(shape) * 0.02).astype(np.float32)  # noqa: E731
+        m.set_tensor(-1, M.EMBED, nrm(v, d))
+        m.set_tensor(-1, M.UNEMBED, nrm(v, d))
+        for tid, shape in ((M.W_DELTA, (d, d)), (M.W_B, (s, d)), (M.W_C, (s, d)), (M.W_QX, (k, d)), (M.W_QH, (k, d)),
+                           (M.W_GATE, (d, d)), (M.W_PROJ, (d, d)), (M.MLP_W1, (2 * d, d)), (M.MLP_W2, (d, 2 * d)),
+                           (M.AD_DOWN, (16, d)), (M.AD_UP, (d, 16)), (M.AD_CONS, (d, 16))):
+            m.set_tensor(0, tid, nrm(*shape))
+        u = rng.uniform(0.9, 0.999, d * s)
+        m.set_tensor(0, M.A_MAT, np.log(np.expm1(-np.log(u))).astype(np.float32))
+        dirs = rng.standard_normal((cap, k))
+        dirs /= np.linalg.norm(dirs, axis=1, keepdims=True)
+        keys = (dirs * rng.uniform(0, 0.9, (cap, 1))).astype(np.float32)
+        m.set_bank(0, keys, (keys.astype(np.float64) ** 2).sum(1).astype(np.float32), rng.standard_normal((cap, d)).astype(np.float32), cap)
+        ids = np.random.default_rng(0).integers(1, v, 512)
+        m.generate_greedy(ids, 8)  # warm-up
+        m.reset_recurrent_state()
+        t0 = time.perf_counter()
+        m.prefill_batch([ids], [0], want_logits=False, want_greedy=True)
+        t1 = time.perf_counter()
+        m.reset_recurrent_state()
+        toks = m.generate_greedy(ids, 200)
+        t2 = time.perf_counter()
+        out[name] = {"prefill_512_ms": (t1 - t0) * 1e3, "prefill_plus_200_tokens_ms": (t2 - t1) * 1e3,
+                     "decode_ms_per_token": ((t2 - t1) - (t1 - t0)) * 1e3 / 200, "tokens": int(len(toks))}
+        m.close()
+    out["workload"] = "one block, vocab 8192, d 192, state 64, 512 slots; batch 1, 512-token prefill + 200 greedy tokens, host wall clock"
+    return out
+
+
 def run_extras(gpu, torch, peak_hbm):
     """Operator-alone workloads of BASELINE.json (N = 1 only)."""
     extra = {}
@@ -259,6 +299,7 @@ def run_extras(gpu, torch, peak_hbm):
                                      "traffic": NCU_SCAN_TRAFFIC_BYTES_PER_ELEM * elems, "kernel": "scan_chunk_apply<4,4,false>"}}
     del a, b, h
     torch.cuda.empty_cache()
+    extra["generate_c1"] = run_generate_c1(gpu)
     # configs[2]: retrieval operator, 512 slots, key/value dim 128, 64 x 4096 queries in the ball, tau 0.1
     rows, dk, dv, cap = 64 * 4096, 128, 128, 512
     g = torch.Generator(device="cuda").manual_seed(5)
