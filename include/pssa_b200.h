@@ -358,6 +358,20 @@ int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* stre
                                     float* logits, uint64_t* greedy);
 
 /*
+ * `.pssa` checkpoint containers, versions 7 and 8 (and the version-6 single-block layout they extend), straight into a
+ * device-resident model: the reference's `load_checkpoint` (src/checkpoint.rs:1344-1411; container header 1-27,
+ * FNV-1a 89-95, block records 912-1010) reduced to what inference needs. Weights, banks with their metadata, the
+ * residual scales and the stored carry (into stream 0) are uploaded; optimizer moments, vocabulary strings and
+ * tokenizer metadata are validated for length and skipped. The whole file is checked on the host first (magic,
+ * version, payload length, checksum, every array length, finite values), so a rejected file creates nothing.
+ * `probe` is the host-only half: it needs no GPU and returns the configuration (error text into `error`).
+ */
+int32_t pssa_b200_checkpoint_probe(const void* bytes, size_t len, pssa_b200_config* config, uint32_t* version,
+                                   char* error, size_t error_len);
+int32_t pssa_b200_model_load_checkpoint(pssa_b200_ctx* ctx, const void* bytes, size_t len, uint32_t max_streams,
+                                        pssa_b200_model** out);
+
+/*
  * Sequence-parallel prefill: one long sequence (or several) split in TIME over `world` processes, one per GPU, each
  * holding contiguous time shard `rank` of every lane. Not a reference code path; it follows from the reference's scan
  * monoid (`compose_affine`, src/gpu_batch.rs:75-86): per block a rank reduces its shard to one affine map per

@@ -31,6 +31,29 @@ class PSSAModel:
         gpu._adopt(self)
         self.set_precision(precision)
 
+    @staticmethod
+    def probe_checkpoint(data: bytes):
+        """Host-only validation of a `.pssa` container: returns (config dict, version); raises ValueError otherwise."""
+        cfg, ver, err = N.Config(), C.c_uint32(), C.create_string_buffer(256)
+        if N.lib().pssa_b200_checkpoint_probe(data, len(data), C.byref(cfg), C.byref(ver), err, 256) != N.OK:
+            raise ValueError("invalid checkpoint: " + err.value.decode())
+        return ({f: getattr(cfg, f) for f, _ in cfg._fields_ if f != "reserved"}, int(ver.value))
+
+    @classmethod
+    def from_checkpoint(cls, gpu: B200Dispatch, data: bytes, streams=1, precision=N.PRECISION_BF16):
+        """`load_checkpoint` (src/checkpoint.rs:1344-1411) into a device-resident model; stream 0 gets the stored carry."""
+        cfg, _ = cls.probe_checkpoint(data)
+        self = cls.__new__(cls)
+        self.gpu, self._lib = gpu, gpu._lib
+        self.depth, self.d_vocab, self.d_latent, self.d_state = cfg["depth"], cfg["d_vocab"], cfg["d_latent"], cfg["d_state"]
+        self.d_mem_key, self.mem_capacity, self.tau_mem, self.streams = cfg["d_mem_key"], cfg["mem_capacity"], cfg["tau_mem"], streams
+        h = C.c_void_p()
+        gpu._check(self._lib.pssa_b200_model_load_checkpoint(gpu._h, data, len(data), streams, C.byref(h)))
+        self._h = h
+        gpu._adopt(self)
+        self.set_precision(precision)
+        return self
+
     def close(self):
         if getattr(self, "_h", None):
             if getattr(self.gpu, "_h", None):  # a model never outlives its context

@@ -44,3 +44,64 @@ def upload(oracle_model: "O.Model", gpu_model):
                            oracle_model.tensor(l, O.BANK_VALUES), count, head, oracle_model.tensor(l, O.BANK_CONFIDENCE),
                            oracle_model.bank_last_seen(l))
     gpu_model.copy_recurrent_state_from(oracle_model.state(), 0)
+
+
+def write_pssa_v8(m: "O.Model", step_counter: int = 0, rng_state: int = 1) -> bytes:
+    """Serialise an oracle model as a version-8 `.pssa` container (src/checkpoint.rs:979-1087 layout): config words,
+    depth, residual scales, counters, empty vocabulary, shared endpoints, one record per block, row marks. Optimizer
+    moments are written as zeros. Written independently of both readers under test."""
+    import struct
+    out = bytearray()
+
+    def u64(v):
+        out.extend(struct.pack("<Q", int(v)))
+
+    def f32(v):
+        out.extend(struct.pack("<f", float(v)))
+
+    def floats(a):
+        a = np.ascontiguousarray(a, np.float32).ravel()
+        u64(a.size)
+        out.extend(a.tobytes())
+
+    def param(a):
+        floats(a)
+        for _ in range(3):
+            floats(np.zeros(np.asarray(a).size, np.float32))
+
+    for v in (m.d_vocab, m.d_latent, m.d_state, m.d_mem_key, m.mem_capacity, m.chunk_len):
+        u64(v)
+    for v in (1e-3, 0.9, 0.999, 0.01, 1e-8, m.tau_mem, 0.99):
+        f32(v)
+    u64(m.depth)
+    floats(m.tensor(-1, O.RESIDUAL_SCALES) if m.depth > 1 else np.zeros(0, np.float32))
+    u64(step_counter)
+    u64(rng_state)
+    u64(0)  # vocabulary strings: none
+    param(m.tensor(-1, O.EMBED))
+    param(m.tensor(-1, O.UNEMBED))
+    state = m.state().reshape(m.depth, -1)
+    for l in range(m.depth):
+        for tid in (O.A_MAT, O.W_DELTA, O.W_B, O.W_C, O.W_QX, O.W_QH, O.W_GATE, O.W_PROJ, O.MLP_W1, O.MLP_W2, O.NORM_GAMMA,
+                    O.NORM_BETA):
+            param(m.tensor(l, tid))
+        floats(state[l])
+        count, head, _ = m.bank_meta(l)
+        u64(count)
+        u64(head)
+        for tid in (O.BANK_KEYS, O.BANK_VALUES, O.BANK_NORM_SQ, O.BANK_CONFIDENCE):
+            floats(m.tensor(l, tid))
+        seen = np.ascontiguousarray(m.bank_last_seen(l), np.uint64)
+        u64(seen.size)
+        out.extend(seen.tobytes())
+        param(m.tensor(l, O.AD_DOWN))
+        param(m.tensor(l, O.AD_UP))
+        floats(m.tensor(l, O.AD_CONS))
+    marks = np.zeros(m.d_vocab, np.uint64)
+    u64(marks.size)
+    out.extend(marks.tobytes())
+    payload = bytes(out)
+    h = 0xcbf29ce484222325
+    for byte in payload:
+        h = ((h ^ byte) * 0x100000001b3) & 0xFFFFFFFFFFFFFFFF
+    return b"PSSA" + struct.pack("<HQQ", 8, len(payload), h) + payload
