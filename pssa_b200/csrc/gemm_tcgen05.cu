@@ -34,7 +34,8 @@ constexpr int BK = 64;       // bf16 per stage row = 128 bytes = one swizzle ato
 constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit operands
 constexpr int EPI_WARPS = 8;  // two warps per TMEM lane quadrant, each draining half of the tile's columns
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
-__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 3 : 4; }
+// ring depth: as many 64-wide K blocks in flight as shared memory allows
+__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 3 : (bn >= 128 ? 5 : 7); }
 constexpr unsigned kSpinLimit = 1u << 24;
 constexpr int STG_PITCH = 36;  // floats per staged row: 32 + 4 keeps float4 rows 16-byte aligned and bank-spread
 
