@@ -358,6 +358,29 @@ int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* stre
                                     float* logits, uint64_t* greedy);
 
 /*
+ * Token sampling on the device for batched decode: `PSSAInferenceEngine::sample` (src/inference.rs:102-181) for `rows`
+ * streams at once. Per stream, in the reference's order: non-finite logits are an error; repetition penalty over the
+ * last <= 64 generated ids (an id repeated in the window is penalised repeatedly); temperature 0 is the greedy rule
+ * (ids 1..V-1, ties to the lowest id); otherwise softmax((l - max over ids >= 1) / T), candidates sorted by
+ * (probability desc, id asc), top-k, top-p on the running sum, one `SimpleRng` draw (src/linalg.rs:13-26), pick.
+ * DEVICE pointers: logits [rows, vocab] (modified by the penalty, as the reference modifies its slice), probs
+ * [rows, vocab] scratch, recent_ids [rows, 64] + recent_count [rows] (NULL: no history), rng_state [rows] in/out,
+ * ids_out [rows] (UINT32_MAX on error), status_out [rows] (0 ok, 1 "model emitted non-finite logits", 2 "invalid
+ * sampling probability mass", 3 "no valid generation candidates"). Parameter validation follows
+ * `validate` (src/inference.rs:87-101). PSSA_B200_SAMPLE_EXACT keeps the sequential f32 sum over the vocabulary.
+ */
+typedef struct pssa_b200_sampling {
+    float temperature;        /* >= 0, finite; 0 = greedy */
+    float top_p;              /* (0, 1] */
+    uint32_t top_k;           /* 1..4096 */
+    float repetition_penalty; /* >= 1, finite */
+} pssa_b200_sampling;
+#define PSSA_B200_SAMPLE_EXACT 1u
+int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, size_t rows, size_t vocab,
+                             const pssa_b200_sampling* cfg, const uint32_t* recent_ids, const uint32_t* recent_count,
+                             uint64_t* rng_state, uint32_t* ids_out, uint32_t* status_out, uint32_t flags);
+
+/*
  * `.pssa` checkpoint containers, versions 7 and 8 (and the version-6 single-block layout they extend), straight into a
  * device-resident model: the reference's `load_checkpoint` (src/checkpoint.rs:1344-1411; container header 1-27,
  * FNV-1a 89-95, block records 912-1010) reduced to what inference needs. Weights, banks with their metadata, the

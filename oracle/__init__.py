@@ -117,6 +117,9 @@ def lib() -> C.CDLL:
         L.pssa_oracle_rawbank_plastic_write.argtypes = [C.c_void_p, C.c_size_t, _fp, C.c_float, C.c_uint64, C.c_float]
         L.pssa_oracle_greedy.restype = C.c_long
         L.pssa_oracle_greedy.argtypes = [_fp, C.c_size_t]
+        L.pssa_oracle_sample.restype = C.c_long
+        L.pssa_oracle_sample.argtypes = [C.POINTER(C.c_uint64), C.c_float, C.c_float, C.c_size_t, C.c_float,
+                                         C.POINTER(C.c_uint64), C.c_size_t, _fp, C.c_size_t]
         L.pssa_oracle_hardware_threads.restype = C.c_int
         _lib = L
     return _lib
@@ -400,3 +403,13 @@ class RawBank:
     def set_meta(self, count, head, conf, last_seen):
         lib().pssa_oracle_rawbank_set_meta(self.h, count, head, fptr(np.asarray(conf, np.float32)),
                                            u64ptr(np.asarray(last_seen, np.uint64)))
+
+
+def sample(rng_state: int, logits, generated, temperature=0.8, top_p=0.95, top_k=40, repetition_penalty=1.1):
+    """`sample` (src/inference.rs:102-181). Returns (id or negative error, new rng state, logits after the penalty)."""
+    lg = np.ascontiguousarray(logits, np.float32).copy()
+    gen = np.ascontiguousarray(generated, np.uint64)
+    st = C.c_uint64(rng_state)
+    tok = lib().pssa_oracle_sample(C.byref(st), temperature, top_p, top_k, repetition_penalty, u64ptr(gen), len(gen), fptr(lg),
+                                   lg.size)
+    return int(tok), int(st.value), lg

@@ -430,6 +430,18 @@ long pssa_oracle_rawbank_plastic_write(void* b, size_t slot, const float* val, f
 
 long pssa_oracle_greedy(const float* logits, size_t v) { return greedy_token(logits, v); }
 
+// inference.rs:102-181; rng_state is read and written back (one draw when temperature > 0)
+long pssa_oracle_sample(uint64_t* rng_state, float temperature, float top_p, size_t top_k, float repetition_penalty,
+                        const uint64_t* generated, size_t n_generated, float* logits, size_t v) {
+    SimpleRng rng(1);
+    rng.state = *rng_state;
+    SamplingConfig cfg;
+    cfg.temperature = temperature, cfg.top_p = top_p, cfg.top_k = top_k, cfg.repetition_penalty = repetition_penalty;
+    long id = sample_token(rng, cfg, generated, n_generated, logits, v);
+    *rng_state = rng.state;
+    return id;
+}
+
 int pssa_oracle_hardware_threads() { return (int)std::thread::hardware_concurrency(); }
 
 }  // extern "C"

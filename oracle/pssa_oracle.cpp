@@ -621,6 +621,63 @@ void ssm_blelloch(const float* delta, const float* b_proj, const float* c_proj,
                          c_proj, states + stride, y, len, d_m, d_s);
 }
 
+long sample_token(SimpleRng& rng, const SamplingConfig& cfg, const uint64_t* generated, size_t n_generated, float* logits,
+                  size_t v) {  // inference.rs:102-181
+    for (size_t i = 0; i < v; ++i)
+        if (!std::isfinite(logits[i])) return -1;
+    if (cfg.repetition_penalty > 1.0f) {  // inference.rs:114-122: repeats in the window are penalised repeatedly
+        size_t start = n_generated > 64 ? n_generated - 64 : 0;
+        for (size_t g = start; g < n_generated; ++g) {
+            size_t id = (size_t)generated[g];
+            if (logits[id] > 0.0f)
+                logits[id] /= cfg.repetition_penalty;
+            else
+                logits[id] *= cfg.repetition_penalty;
+        }
+    }
+    if (cfg.temperature == 0.0f) return greedy_token(logits, v);
+    if (v < 2) return -3;
+    float mx = -INFINITY;  // id 0 (<unk>) is not a candidate and must not anchor the softmax (inference.rs:128-136)
+    for (size_t i = 1; i < v; ++i) mx = std::max(mx, logits[i]);
+    std::vector<float> probs(v, 0.0f);
+    float sum = 0.0f;
+    for (size_t i = 1; i < v; ++i) {
+        probs[i] = expf((logits[i] - mx) / cfg.temperature);  // subtract before dividing (inference.rs:139-143)
+        sum += probs[i];
+    }
+    if (!std::isfinite(sum) || sum <= 0.0f) return -2;
+    std::vector<std::pair<size_t, float>> cand;
+    cand.reserve(v);
+    for (size_t i = 1; i < v; ++i)
+        if (std::isfinite(probs[i])) cand.emplace_back(i, probs[i] / sum);
+    if (cand.empty()) return -3;
+    // probabilities are >= +0, so total_cmp is the ordinary order; ties go to the lower id (inference.rs:156)
+    std::sort(cand.begin(), cand.end(), [](const auto& a, const auto& b) { return a.second > b.second || (a.second == b.second && a.first < b.first); });
+    size_t k = std::min(cand.size(), cfg.top_k), cutoff = k;
+    float cumulative = 0.0f;
+    for (size_t i = 0; i < k; ++i) {
+        cumulative += cand[i].second;
+        if (cumulative >= cfg.top_p) {
+            cutoff = i + 1;
+            break;
+        }
+    }
+    size_t n = std::max<size_t>(cutoff, 1);
+    float mass = 0.0f;
+    for (size_t i = 0; i < n; ++i) mass += cand[i].second;
+    float draw = rng.gen_range_f32(0.0f, mass);
+    float running = 0.0f;
+    size_t id = cand[n - 1].first;
+    for (size_t i = 0; i < n; ++i) {
+        running += cand[i].second;
+        if (draw <= running) {
+            id = cand[i].first;
+            break;
+        }
+    }
+    return (long)id;
+}
+
 // ---------------------------------------------------------------- checkpoint.rs reader
 uint64_t fnv1a64(const uint8_t* bytes, size_t len) {  // checkpoint.rs:89-95
     uint64_t h = 0xcbf29ce484222325ULL;

@@ -132,6 +132,15 @@ void ssm_blelloch(const float* delta, const float* b_proj, const float* c_proj,
 void gemm_xwt(const float* x, const float* w, size_t m, size_t n, size_t k, float* out);
 // inference.rs:123-127: argmax over ids 1..V, ties to the lowest id; -1 on non-finite logits
 long greedy_token(const float* logits, size_t v);
+// src/inference.rs:102-181 (`sample`): repetition penalty over the last 64 generated ids, temperature softmax over ids
+// 1..V-1, candidates sorted by (probability desc, id asc), top-k, top-p, one SimpleRng draw. `logits` is modified by
+// the penalty exactly like the reference's slice. Returns the id, or -1 non-finite logits, -2 invalid probability mass,
+// -3 no candidates.
+struct SamplingConfig {
+    float temperature = 0.8f, top_p = 0.95f, repetition_penalty = 1.1f;
+    size_t top_k = 40;
+};
+long sample_token(SimpleRng& rng, const SamplingConfig& cfg, const uint64_t* generated, size_t n_generated, float* logits, size_t v);
 
 uint64_t fnv1a64(const uint8_t* bytes, size_t len);  // checkpoint.rs:89-95
 

@@ -61,6 +61,7 @@ SIGNATURES = {
     "pssa_b200_ctx_profile_row": (C.c_int32, [_vp, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64),
                                               C.POINTER(C.c_double)]),
     "pssa_b200_model_decode_step": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, _vp]),
+    "pssa_b200_sample_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "pssa_b200_checkpoint_probe": (C.c_int32, [_vp, _sz, _vp, _vp, _vp, _sz]),
     "pssa_b200_model_load_checkpoint": (C.c_int32, [_vp, _vp, _sz, C.c_uint32, _vp]),
     "pssa_b200_model_set_seqpar": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, _vp, _sz, _vp, _vp]),
@@ -72,6 +73,14 @@ EPI_NONE, EPI_SOFTPLUS, EPI_SIGMOID, EPI_SILU, EPI_SCALE, EPI_ADD_OUT = range(6)
 PRECISION_BF16, PRECISION_FP32_EXACT = 0, 1
 CANCEL_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)
 EXCHANGE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t)
+
+
+class Sampling(C.Structure):
+    """`pssa_b200_sampling`"""
+    _fields_ = [("temperature", C.c_float), ("top_p", C.c_float), ("top_k", C.c_uint32), ("repetition_penalty", C.c_float)]
+
+
+SAMPLE_EXACT = 1
 
 
 class Config(C.Structure):

@@ -581,6 +581,32 @@ int32_t pssa_b200_ctx_profile_row(pssa_b200_ctx* ctx, uint32_t index, const char
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, size_t rows, size_t vocab, const pssa_b200_sampling* cfg,
+                             const uint32_t* recent_ids, const uint32_t* recent_count, uint64_t* rng_state, uint32_t* ids_out,
+                             uint32_t* status_out, uint32_t flags) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    if (!logits || !probs || !cfg || !rng_state || !ids_out || !status_out)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sampling: null buffer");
+    if ((recent_ids == nullptr) != (recent_count == nullptr))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sampling: recent ids and their counts must both be given");
+    if (flags & ~PSSA_B200_SAMPLE_EXACT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sampling: unknown flags");
+    // src/inference.rs:87-101
+    if (!std::isfinite(cfg->temperature) || cfg->temperature < 0.0f) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "temperature must be finite and >= 0");
+    if (!(std::isfinite(cfg->top_p) && cfg->top_p > 0.0f && cfg->top_p <= 1.0f)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "top-p must be finite in (0, 1]");
+    if (cfg->top_k == 0) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "top-k must be positive");
+    if (!(std::isfinite(cfg->repetition_penalty) && cfg->repetition_penalty >= 1.0f))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "repetition penalty must be finite and >= 1");
+    if (vocab == 0 || vocab > 0x7fffffff) return fail(ctx, PSSA_B200_ERR_SHAPE, "sampling: vocabulary size %zu outside 1..2^31-1", vocab);
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    SampleParams p{};
+    p.logits = logits, p.probs = probs, p.rows = rows, p.vocab = (int)vocab, p.top_k = (int)std::min<uint32_t>(cfg->top_k, 0x7fffffff);
+    p.temperature = cfg->temperature, p.top_p = cfg->top_p, p.repetition_penalty = cfg->repetition_penalty;
+    p.recent_ids = recent_ids, p.recent_count = recent_count, p.rng_state = (unsigned long long*)rng_state;
+    p.ids_out = ids_out, p.status_out = status_out, p.exact = (flags & PSSA_B200_SAMPLE_EXACT) != 0;
+    if ((size_t)p.top_k > vocab) p.top_k = (int)vocab;  // min(candidates, top_k), src/inference.rs:157
+    return launch_sample(ctx, p);
+}
+
 /* Reads and clears the device status word written by bounded waits (0 = none expired). */
 int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx) {
     if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");

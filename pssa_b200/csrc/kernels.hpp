@@ -94,6 +94,22 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
 // values [cap, dv] fp32 -> v_split [dv, 3*cap] bf16 (transpose + three-way split); once per bank upload
 int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv);
 
+// sampling.cu
+struct SampleParams {
+    float* logits;               // [rows, vocab]; the repetition penalty is applied in place, like the reference
+    float* probs;                // [rows, vocab] scratch
+    size_t rows;
+    int vocab, top_k;
+    float temperature, top_p, repetition_penalty;
+    const unsigned* recent_ids;  // [rows, 64] last generated ids of each stream in generation order, may be null
+    const unsigned* recent_count;  // [rows] how many of them are valid (<= 64)
+    unsigned long long* rng_state;  // [rows] xorshift64* state, advanced by one draw when temperature > 0
+    unsigned* ids_out;           // [rows] sampled id, UINT32_MAX on error
+    unsigned* status_out;        // [rows] 0 ok, 1 non-finite logits, 2 invalid probability mass, 3 no candidates
+    int exact;                   // sequential f32 sum over the vocabulary (the reference's order)
+};
+int32_t launch_sample(pssa_b200_ctx* ctx, const SampleParams& p);
+
 // plastic_write.cu
 struct BankWriteParams {
     float* keys;                 // [cap, dk]

@@ -204,6 +204,15 @@ class B200Dispatch:
             self._mem_flags(exact, f32_distance)))
 
 
+    # ---- device-side sampling (src/inference.rs:102-181)
+    def sample_dev(self, logits, probs, rows, vocab, rng_state, ids_out, status_out, temperature=0.70, top_p=0.85, top_k=24,
+                   repetition_penalty=1.25, recent_ids=None, recent_count=None, exact=False):
+        """One sampled id per stream; all buffers are device buffers (torch tensors or raw pointers)."""
+        cfg = N.Sampling(temperature, top_p, top_k, repetition_penalty)
+        self._check(self._lib.pssa_b200_sample_dev(self._h, _ptr(logits), _ptr(probs), rows, vocab, C.byref(cfg), _ptr(recent_ids),
+                                                   _ptr(recent_count), _ptr(rng_state), _ptr(ids_out), _ptr(status_out),
+                                                   N.SAMPLE_EXACT if exact else 0))
+
     # ---- bank write / plastic fast weights (device pointers)
     def bank_insert_protected_dev(self, keys, norm_sq, values, confidence, last_seen_step, meta, capacity, d_key, d_val,
                                   key_pnc, val, surprise, step, n, slots_out=None, winning_slots=None, eta=0.0):
