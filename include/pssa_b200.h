@@ -381,6 +381,17 @@ int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, si
                              uint64_t* rng_state, uint32_t* ids_out, uint32_t* status_out, uint32_t flags);
 
 /*
+ * One decode step for `n` streams with the sampling done on the device: forward, vocabulary head, then
+ * pssa_b200_sample_dev's kernel on the head's logits, so only `n` ids cross PCIe. Every stream owns a generator
+ * (seed 1337 by default, like `PSSAInferenceEngine`, src/inference.rs:70-73) and the window of its last 64 sampled ids
+ * that the repetition penalty reads; `sampler_seed` resets both for one stream (seed 0 maps to the reference's
+ * non-zero constant, src/linalg.rs:7-11). ids_out [n] on the HOST.
+ */
+int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64_t seed);
+int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n,
+                                            const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out);
+
+/*
  * `.pssa` checkpoint containers, versions 7 and 8 (and the version-6 single-block layout they extend), straight into a
  * device-resident model: the reference's `load_checkpoint` (src/checkpoint.rs:1344-1411; container header 1-27,
  * FNV-1a 89-95, block records 912-1010) reduced to what inference needs. Weights, banks with their metadata, the

@@ -107,8 +107,10 @@ struct SampleParams {
     unsigned* ids_out;           // [rows] sampled id, UINT32_MAX on error
     unsigned* status_out;        // [rows] 0 ok, 1 non-finite logits, 2 invalid probability mass, 3 no candidates
     int exact;                   // sequential f32 sum over the vocabulary (the reference's order)
+    const unsigned* slots;       // optional [rows]: recent_* and rng_state are indexed by slots[row] instead of row
 };
 int32_t launch_sample(pssa_b200_ctx* ctx, const SampleParams& p);
+int32_t launch_push_recent(pssa_b200_ctx* ctx, const unsigned* ids, const unsigned* slots, unsigned* recent, unsigned* count, size_t rows);
 
 // plastic_write.cu
 struct BankWriteParams {

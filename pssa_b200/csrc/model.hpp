@@ -78,6 +78,16 @@ struct pssa_b200_model {
         void* arg = nullptr;
         bool active = false;        // set for the duration of a sharded prefill call only (decode steps stay local)
     } sp;
+    // per-stream sampler state for device-side sampling (src/inference.rs:37-41: one generator and one list of
+    // generated ids per engine); allocated on first use
+    struct Sampler {
+        unsigned* recent = nullptr;            // [max_streams][64]
+        unsigned* count = nullptr;             // [max_streams]
+        unsigned long long* rng = nullptr;     // [max_streams]
+        unsigned *ids = nullptr, *status = nullptr, *head_slot = nullptr;  // [lanes capacity]
+        float* probs = nullptr;                // [lanes capacity][vocab]
+        size_t lanes = 0;
+    } sampler;
     // time chunks ("virtual lanes") of the two-pass SSM: chunk maps, chunk carry-ins and the chunk row ranges
     struct Chunks {
         size_t capacity = 0;        // virtual lanes the buffers hold

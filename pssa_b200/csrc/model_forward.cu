@@ -276,8 +276,36 @@ int32_t head_rows(pssa_b200_model* m, const float* feats, size_t n_heads, bool w
 }
 
 // Shared driver: lanes described on the host; processes them in passes of at most max_rows rows.
+// per-stream sampler state (history window and generator), allocated on first use; generators start from seed 1337 like
+// the reference engine's (src/inference.rs:70-73)
+int32_t ensure_sampler(pssa_b200_model* m, size_t lanes) {
+    pssa_b200_ctx* ctx = m->ctx;
+    auto& sm = m->sampler;
+    if (!sm.recent) {
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.recent, (size_t)m->max_streams * 64 * 4));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.count, (size_t)m->max_streams * 4));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.rng, (size_t)m->max_streams * 8));
+        PSSA_CUDA(ctx, cudaMemsetAsync(sm.count, 0, (size_t)m->max_streams * 4, ctx->stream));
+        std::vector<unsigned long long> seeds(m->max_streams, 1337ull);
+        PSSA_CUDA(ctx, cudaMemcpyAsync(sm.rng, seeds.data(), seeds.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
+        PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    if (lanes > sm.lanes) {
+        PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(sm.ids), cudaFree(sm.status), cudaFree(sm.head_slot), cudaFree(sm.probs);
+        sm.ids = sm.status = sm.head_slot = nullptr, sm.probs = nullptr, sm.lanes = 0;
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.ids, lanes * 4));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.status, lanes * 4));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.head_slot, lanes * 4));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.probs, lanes * m->v * sizeof(float)));
+        sm.lanes = lanes;
+    }
+    return PSSA_B200_OK;
+}
+
 int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offsets, const uint32_t* lengths, const uint32_t* streams,
-                  size_t n_lanes, float* logits, uint64_t* greedy, int32_t (*cancelled)(void*), void* cancel_arg, size_t* processed) {
+                  size_t n_lanes, float* logits, uint64_t* greedy, int32_t (*cancelled)(void*), void* cancel_arg, size_t* processed,
+                  const pssa_b200_sampling* sampling = nullptr, uint32_t sample_flags = 0) {
     pssa_b200_ctx* ctx = m->ctx;
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     uint32_t max_len = 0;
@@ -307,7 +335,7 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
         // heads: a lane's last token is in this pass iff its length ends inside the window
         h_last.clear();
         std::vector<size_t> head_lane;
-        if (logits || greedy)
+        if (logits || greedy || sampling)
             for (size_t l = 0; l < n_lanes; ++l)
                 if (lengths[l] > t0 && lengths[l] <= t0 + window) {
                     h_last.push_back(h_off[l] + h_len[l] - 1);
@@ -324,9 +352,30 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
         float* feats = nullptr;
         if ((rc = forward_rows(m, rows, n_lanes, h_off.data(), h_len.data(), &feats))) return rc;
         if (!h_last.empty()) {
-            if ((rc = head_rows(m, feats, h_last.size(), greedy != nullptr))) return rc;
-            std::vector<uint32_t> g(h_last.size());
-            if (greedy) PSSA_CUDA(ctx, cudaMemcpyAsync(g.data(), ws.greedy, g.size() * 4, cudaMemcpyDeviceToHost, st));
+            if ((rc = head_rows(m, feats, h_last.size(), greedy != nullptr && !sampling))) return rc;
+            std::vector<uint32_t> g(h_last.size()), g_status(h_last.size(), 0);
+            if (sampling) {
+                // sample on the device from the logits the head just wrote; only ids come back
+                if ((rc = ensure_sampler(m, n_lanes))) return rc;
+                std::vector<uint32_t> head_slot(h_last.size());
+                for (size_t i = 0; i < head_lane.size(); ++i) head_slot[i] = h_slot[head_lane[i]];
+                PSSA_CUDA(ctx, cudaMemcpyAsync(m->sampler.head_slot, head_slot.data(), head_slot.size() * 4, cudaMemcpyHostToDevice, st));
+                PSSA_CUDA(ctx, cudaStreamSynchronize(st));  // head_slot is a local vector
+                SampleParams sp{};
+                sp.logits = ws.logits, sp.probs = m->sampler.probs, sp.rows = h_last.size(), sp.vocab = (int)m->v;
+                sp.top_k = (int)std::min<size_t>(sampling->top_k, m->v);
+                sp.temperature = sampling->temperature, sp.top_p = sampling->top_p, sp.repetition_penalty = sampling->repetition_penalty;
+                sp.recent_ids = m->sampler.recent, sp.recent_count = m->sampler.count, sp.rng_state = m->sampler.rng;
+                sp.ids_out = m->sampler.ids, sp.status_out = m->sampler.status, sp.exact = (sample_flags & PSSA_B200_SAMPLE_EXACT) != 0;
+                sp.slots = m->sampler.head_slot;
+                if ((rc = launch_sample(ctx, sp))) return rc;
+                if ((rc = launch_push_recent(ctx, m->sampler.ids, m->sampler.head_slot, m->sampler.recent, m->sampler.count, h_last.size())))
+                    return rc;
+                PSSA_CUDA(ctx, cudaMemcpyAsync(g.data(), m->sampler.ids, g.size() * 4, cudaMemcpyDeviceToHost, st));
+                PSSA_CUDA(ctx, cudaMemcpyAsync(g_status.data(), m->sampler.status, g.size() * 4, cudaMemcpyDeviceToHost, st));
+            } else if (greedy) {
+                PSSA_CUDA(ctx, cudaMemcpyAsync(g.data(), ws.greedy, g.size() * 4, cudaMemcpyDeviceToHost, st));
+            }
             if (logits) {
                 // contiguous runs of lanes are copied in one transfer
                 size_t i = 0;
@@ -341,7 +390,11 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
             PSSA_CUDA(ctx, cudaStreamSynchronize(st));
             if (greedy)
                 for (size_t i = 0; i < head_lane.size(); ++i) {
-                    if (g[i] == 0xffffffffu) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "model emitted non-finite logits");
+                    if (g[i] == 0xffffffffu) {  // src/inference.rs:111-113, 146-147, 153-154
+                        const char* why = g_status[i] == 2 ? "invalid sampling probability mass"
+                                          : g_status[i] == 3 ? "no valid generation candidates" : "model emitted non-finite logits";
+                        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "%s", why);
+                    }
                     greedy[head_lane[i]] = g[i];
                 }
         } else if (final_pass || cancelled) {
@@ -434,6 +487,47 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
         }
     }
     return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64_t seed) {
+    if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (stream >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u outside %u streams", stream, m->max_streams);
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t rc = ensure_sampler(m, 1);
+    if (rc) return rc;
+    const unsigned long long state = seed == 0 ? 0x853c49e6748fea9bull : seed;  // src/linalg.rs:7-11
+    const unsigned zero = 0;
+    PSSA_CUDA(ctx, cudaMemcpyAsync(m->sampler.rng + stream, &state, 8, cudaMemcpyHostToDevice, ctx->stream));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(m->sampler.count + stream, &zero, 4, cudaMemcpyHostToDevice, ctx->stream));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n,
+                                            const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out) {
+    if (!m || !ids || !cfg || !ids_out) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "decode_step_sampled: null argument");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (n == 0 || n > 0x7fffffff) return fail(ctx, PSSA_B200_ERR_SHAPE, "decode_step: stream count must be in 1..2^31-1");
+    if (flags & ~PSSA_B200_SAMPLE_EXACT) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sampling: unknown flags");
+    // src/inference.rs:87-101
+    if (!std::isfinite(cfg->temperature) || cfg->temperature < 0.0f) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "temperature must be finite and >= 0");
+    if (!(std::isfinite(cfg->top_p) && cfg->top_p > 0.0f && cfg->top_p <= 1.0f)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "top-p must be finite in (0, 1]");
+    if (cfg->top_k == 0) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "top-k must be positive");
+    if (cfg->top_k > 4096 && cfg->top_k < m->v) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "sampling: top-k %u outside 1..4096", cfg->top_k);
+    if (!(std::isfinite(cfg->repetition_penalty) && cfg->repetition_penalty >= 1.0f))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "repetition penalty must be finite and >= 1");
+    std::vector<bool> seen(m->max_streams, false);
+    for (size_t i = 0; i < n; ++i) {
+        uint32_t slot = streams ? streams[i] : (uint32_t)i;
+        if (slot >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "lane %zu uses stream %u outside %u streams", i, slot, m->max_streams);
+        if (seen[slot]) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u appears in more than one lane", slot);
+        seen[slot] = true;
+        if (ids[i] >= m->v) return fail(ctx, PSSA_B200_ERR_TOKEN, "token ID %llu outside model vocabulary", (unsigned long long)ids[i]);
+    }
+    std::vector<uint32_t> off(n), len(n, 1);
+    for (size_t i = 0; i < n; ++i) off[i] = (uint32_t)i;
+    return run_lanes(m, ids, off.data(), len.data(), streams, n, nullptr, ids_out, nullptr, nullptr, nullptr, cfg, flags);
 }
 
 int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev, size_t capacity,

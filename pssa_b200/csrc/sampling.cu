@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     __shared__ int s_flag;
     const int tid = threadIdx.x;
     const size_t row = blockIdx.x;
+    const size_t slot = p.slots ? p.slots[row] : row;  // where this row's history and generator live
     const int v = p.vocab;
     float* lg = p.logits + row * (size_t)v;
     float* pr = p.probs + row * (size_t)v;
@@ -71,8 +72,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     }
     // 2. repetition penalty, in the order the ids were generated
     if (tid == 0 && p.repetition_penalty > 1.0f && p.recent_ids) {
-        const unsigned n = min(p.recent_count[row], (unsigned)kRecent);
-        const unsigned* ids = p.recent_ids + row * kRecent;
+        const unsigned n = min(p.recent_count[slot], (unsigned)kRecent);
+        const unsigned* ids = p.recent_ids + slot * kRecent;
         for (unsigned g = 0; g < n; ++g) {
             const unsigned id = ids[g];
             if (id < (unsigned)v) lg[id] = lg[id] > 0.0f ? __fdiv_rn(lg[id], p.repetition_penalty) : __fmul_rn(lg[id], p.repetition_penalty);
@@ -173,9 +174,9 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
         float mass = 0.0f;
         for (int i = 0; i < n; ++i) mass = __fadd_rn(mass, sel_p[i]);
         // src/linalg.rs:13-26
-        unsigned long long x = p.rng_state[row];
+        unsigned long long x = p.rng_state[slot];
         x ^= x >> 12, x ^= x << 25, x ^= x >> 27;
-        p.rng_state[row] = x;
+        p.rng_state[slot] = x;
         const unsigned u = (unsigned)((x * 0x2545f4914f6cdd1dull) >> 32);
         const float norm = __fdiv_rn((float)u, 4294967296.0f);  // u32::MAX as f32 rounds to 2^32
         const float draw = __fadd_rn(0.0f, __fmul_rn(norm, __fsub_rn(mass, 0.0f)));
@@ -192,7 +193,28 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     }
 }
 
+// append each row's new id to its stream's window of the last 64 generated ids (oldest first)
+__global__ void push_recent_kernel(const unsigned* __restrict__ ids, const unsigned* __restrict__ slots, unsigned* __restrict__ recent,
+                                   unsigned* __restrict__ count, size_t rows) {
+    const size_t row = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows || ids[row] == 0xffffffffu) return;
+    const size_t slot = slots ? slots[row] : row;
+    unsigned* w = recent + slot * kRecent;
+    unsigned n = count[slot];
+    if (n >= (unsigned)kRecent) {
+        for (int i = 1; i < kRecent; ++i) w[i - 1] = w[i];
+        n = kRecent - 1;
+    }
+    w[n] = ids[row];
+    count[slot] = n + 1;
+}
+
 }  // namespace
+
+int32_t launch_push_recent(pssa_b200_ctx* ctx, const unsigned* ids, const unsigned* slots, unsigned* recent, unsigned* count, size_t rows) {
+    push_recent_kernel<<<(unsigned)((rows + 127) / 128), 128, 0, ctx->stream>>>(ids, slots, recent, count, rows);
+    return after_launch(ctx, "push_recent_kernel");
+}
 
 int32_t launch_sample(pssa_b200_ctx* ctx, const SampleParams& p) {
     if (p.rows == 0 || p.rows > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "sampling: row count must be in 1..2^31-1");

@@ -186,6 +186,20 @@ class PSSAModel:
             return logits, greedy
         return logits if want_logits else greedy
 
+    def sampler_seed(self, stream=0, seed=1337):
+        """Reset a stream's generator and its window of generated ids (`SimpleRng::new(seed)`, src/linalg.rs:7-11)."""
+        self.gpu._check(self._lib.pssa_b200_model_sampler_seed(self._h, stream, seed))
+
+    def decode_step_sampled(self, ids, streams=None, temperature=0.70, top_p=0.85, top_k=24, repetition_penalty=1.25, exact=False):
+        """Decode step with `sample` (src/inference.rs:102-181) on the device; returns the sampled ids."""
+        ids = np.ascontiguousarray(ids, np.uint64)
+        st = None if streams is None else np.ascontiguousarray(streams, np.uint32)
+        out = np.empty(ids.size, np.uint64)
+        cfg = N.Sampling(temperature, top_p, top_k, repetition_penalty)
+        self.gpu._check(self._lib.pssa_b200_model_decode_step_sampled(self._h, _ptr(st), _ptr(ids), ids.size, C.byref(cfg),
+                                                                      N.SAMPLE_EXACT if exact else 0, _ptr(out)))
+        return out
+
     def generate_greedy(self, prompt_ids, n_new, stream=0):
         """Prefill + greedy decode (src/inference.rs:348-418 at temperature 0): returns the generated ids."""
         _, g = self.prefill_batch([prompt_ids], [stream], want_logits=False, want_greedy=True)

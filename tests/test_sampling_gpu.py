@@ -96,3 +96,47 @@ def test_fast_sum_mode_keeps_the_distribution(gpu):
     a = run(gpu, logits, [[]] * rows, states, exact=True, **cfg)
     b = run(gpu, logits, [[]] * rows, states, exact=False, **cfg)
     assert np.array_equal(a[2], b[2]) and int(np.sum(a[0] != b[0])) <= 1
+
+
+def test_model_level_sampled_decode_follows_the_restatement(gpu):
+    """Forward + head + sampling on the device, ids only back to the host: two streams with their own generators and
+    repetition windows follow the CPU model sampled by the restatement with the same seeds."""
+    import pssa_b200
+    from helpers import fill_synthetic, upload
+    v = 300
+    om = O.Model.new(2, v, 48, 16, 16, 20, tau_mem=0.1, seed=8)
+    fill_synthetic(om, 8, std=0.3)  # wide logits so the distribution is far from uniform
+    gm = pssa_b200.PSSAModel(gpu, 2, v, 48, 16, 16, 20, tau_mem=0.1, streams=2, precision=1)
+    upload(om, gm)
+    cfg = dict(temperature=0.9, top_p=0.9, top_k=12, repetition_penalty=1.3)
+    oms = [om.clone(), om.clone()]
+    seeds = [1337, 99]
+    gm.sampler_seed(0, seeds[0])
+    gm.sampler_seed(1, seeds[1])
+    prompts = [np.array([5, 9, 2, 77]), np.array([11, 3])]
+    gm.prefill_batch([list(p) for p in prompts], want_logits=False)
+    states = list(seeds)
+    history = [[], []]
+    for s_, p_ in enumerate(prompts):  # the CPU replicas consume the same prompts
+        oms[s_].reset_recurrent_state()
+        oms[s_].prefill_inference(p_)
+    # both sides then decode from the same fixed tokens
+    toks = [7, 8]
+    mismatches = 0
+    for step in range(24):
+        got = gm.decode_step_sampled(toks, [0, 1], exact=True, **cfg)
+        nxt = []
+        for s in range(2):
+            lg = oms[s].forward_inference(toks[s])
+            ref_id, states[s], _ = O.sample(states[s], lg, history[s], **cfg)
+            if int(got[s]) != ref_id:
+                mismatches += 1
+            history[s].append(int(got[s]))  # follow the device's choice so the two sides stay on one sequence
+            nxt.append(int(got[s]))
+        toks = nxt
+    assert mismatches <= 1, mismatches
+    assert len(set(history[0])) > 3  # it really samples
+    # an id repeated in the window is what the penalty sees: windows are per stream
+    with pytest.raises(pssa_b200.B200Error, match="top-p must be finite"):
+        gm.decode_step_sampled(toks, [0, 1], top_p=1.5)
+    gm.close()
