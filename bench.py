@@ -36,9 +36,9 @@ LANES, T = 32, 2048
 WORKLOAD = ("prefill_c4: 12-block PSSA (d 768, state 64, key 64, 512 slots, vocab 16384), bf16 projections, fp32 scan "
             "and retrieval; 32 sequences x 2048 tokens per GPU")
 CPU_SAMPLE_LANES, CPU_SAMPLE_T = 16, 16
-# dram bytes per scan element from profiles/scan_chunk_apply_small_case.md
+# dram bytes per scan element, from the ncu capture of the scan kernel summarised under profiles/
 NCU_SCAN_TRAFFIC_BYTES_PER_ELEM = 11.87
-# dram bytes per token row of one ssm_fused_kernel launch, from profiles/ssm_fused_kernel_prefill_16_lanes.md
+# dram bytes per token row of one ssm_fused_kernel launch, from its ncu capture summarised under profiles/
 # (read 225.5 MB + write 119.9 MB over 32768 rows); traffic grows in proportion to the rows
 NCU_SSM_TRAFFIC_BYTES_PER_ROW = (225.52e6 + 119.92e6) / 32768
 

@@ -26,7 +26,9 @@ FILES = {
 
 
 def main() -> None:
-    ref = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference repository>")
+    ref = pathlib.Path(sys.argv[1])
     out = pathlib.Path(__file__).resolve().parent
     for name, sha in FILES.items():
         src = ref / "tests" / "fixtures" / name
