@@ -368,6 +368,8 @@ int32_t pssa_b200_model_decode_step(pssa_b200_model* model, const uint32_t* stre
  * ids_out [rows] (UINT32_MAX on error), status_out [rows] (0 ok, 1 "model emitted non-finite logits", 2 "invalid
  * sampling probability mass", 3 "no valid generation candidates"). Parameter validation follows
  * `validate` (src/inference.rs:87-101). PSSA_B200_SAMPLE_EXACT keeps the sequential f32 sum over the vocabulary.
+ * confidence_out [rows] (NULL to skip): the raw softmax probability of the selected id over ALL ids, before penalty,
+ * temperature and filtering (`raw_confidence`, src/inference.rs:526-545; what the scored generation callbacks report).
  */
 typedef struct pssa_b200_sampling {
     float temperature;        /* >= 0, finite; 0 = greedy */
@@ -378,18 +380,33 @@ typedef struct pssa_b200_sampling {
 #define PSSA_B200_SAMPLE_EXACT 1u
 int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, size_t rows, size_t vocab,
                              const pssa_b200_sampling* cfg, const uint32_t* recent_ids, const uint32_t* recent_count,
-                             uint64_t* rng_state, uint32_t* ids_out, uint32_t* status_out, uint32_t flags);
+                             uint64_t* rng_state, uint32_t* ids_out, uint32_t* status_out, float* confidence_out,
+                             uint32_t flags);
+
+/*
+ * Observer scratch: the reference keeps, per block, the retrieval state of the last token it processed
+ * (`inf_mem_weights`, `inf_q_pnc`, `inf_m_val`, `inf_z_final`, src/pssa.rs:609-619) and hands it to generation
+ * observers (src/inference.rs:257-313). With the observer enabled every forward call (prefill, batched prefill, decode
+ * step) publishes those four vectors for the LAST token of every lane that has one in the call; `index` counts those
+ * lanes in order. Each output may be NULL. HOST pointers: mem_weights [capacity], q_pnc [d_mem_key], m_val and z_final
+ * [d_latent]. Costs one small copy kernel per block and the fp32 copy of m in the bf16 mode; off by default.
+ */
+int32_t pssa_b200_model_set_observer(pssa_b200_model* m, int32_t enabled);
+int32_t pssa_b200_model_get_observation(pssa_b200_model* m, uint32_t layer, uint32_t index, float* mem_weights, float* q_pnc,
+                                        float* m_val, float* z_final);
 
 /*
  * One decode step for `n` streams with the sampling done on the device: forward, vocabulary head, then
  * pssa_b200_sample_dev's kernel on the head's logits, so only `n` ids cross PCIe. Every stream owns a generator
  * (seed 1337 by default, like `PSSAInferenceEngine`, src/inference.rs:70-73) and the window of its last 64 sampled ids
  * that the repetition penalty reads; `sampler_seed` resets both for one stream (seed 0 maps to the reference's
- * non-zero constant, src/linalg.rs:7-11). ids_out [n] on the HOST.
+ * non-zero constant, src/linalg.rs:7-11). ids_out [n] and confidence_out [n] (NULL to skip; see pssa_b200_sample_dev)
+ * on the HOST.
  */
 int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64_t seed);
 int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n,
-                                            const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out);
+                                            const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out,
+                                            float* confidence_out);
 
 /*
  * `.pssa` checkpoint containers, versions 7 and 8 (and the version-6 single-block layout they extend), straight into a

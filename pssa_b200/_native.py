@@ -61,9 +61,11 @@ SIGNATURES = {
     "pssa_b200_ctx_profile_row": (C.c_int32, [_vp, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64),
                                               C.POINTER(C.c_double)]),
     "pssa_b200_model_decode_step": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, _vp]),
-    "pssa_b200_sample_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
+    "pssa_b200_sample_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
+    "pssa_b200_model_set_observer": (C.c_int32, [_vp, C.c_int32]),
+    "pssa_b200_model_get_observation": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, _vp, _vp, _vp]),
     "pssa_b200_model_sampler_seed": (C.c_int32, [_vp, C.c_uint32, C.c_uint64]),
-    "pssa_b200_model_decode_step_sampled": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, C.c_uint32, _vp]),
+    "pssa_b200_model_decode_step_sampled": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, C.c_uint32, _vp, _vp]),
     "pssa_b200_checkpoint_probe": (C.c_int32, [_vp, _sz, _vp, _vp, _vp, _sz]),
     "pssa_b200_model_load_checkpoint": (C.c_int32, [_vp, _vp, _sz, C.c_uint32, _vp]),
     "pssa_b200_model_set_seqpar": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, _vp, _sz, _vp, _vp]),

@@ -583,7 +583,7 @@ int32_t pssa_b200_ctx_profile_row(pssa_b200_ctx* ctx, uint32_t index, const char
 
 int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, size_t rows, size_t vocab, const pssa_b200_sampling* cfg,
                              const uint32_t* recent_ids, const uint32_t* recent_count, uint64_t* rng_state, uint32_t* ids_out,
-                             uint32_t* status_out, uint32_t flags) {
+                             uint32_t* status_out, float* confidence_out, uint32_t flags) {
     if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
     if (!logits || !probs || !cfg || !rng_state || !ids_out || !status_out)
         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "sampling: null buffer");
@@ -603,6 +603,7 @@ int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, si
     p.temperature = cfg->temperature, p.top_p = cfg->top_p, p.repetition_penalty = cfg->repetition_penalty;
     p.recent_ids = recent_ids, p.recent_count = recent_count, p.rng_state = (unsigned long long*)rng_state;
     p.ids_out = ids_out, p.status_out = status_out, p.exact = (flags & PSSA_B200_SAMPLE_EXACT) != 0;
+    p.confidence_out = confidence_out;
     if ((size_t)p.top_k > vocab) p.top_k = (int)vocab;  // min(candidates, top_k), src/inference.rs:157
     return launch_sample(ctx, p);
 }

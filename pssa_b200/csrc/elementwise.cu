@@ -228,6 +228,32 @@ __global__ void __launch_bounds__(256) greedy_kernel(const float* __restrict__ l
     }
 }
 
+// Observer scratch: copy the last row of each lane out of the block's working buffers into
+// out[lane] = { weights[cap] | q_pnc[k] | m_val[d] | z_final[d] }. z_final is the block's output before the depth
+// residual (src/pssa.rs:1205-1207): z_direct when the caller has it, else (feat_out - feat_in) / scale.
+__global__ void __launch_bounds__(256) observe_rows_kernel(const uint32_t* __restrict__ last_rows, const float* __restrict__ weights,
+                                                           int cap, const float* __restrict__ q_pnc, int k,
+                                                           const float* __restrict__ m_val, const float* __restrict__ z_direct,
+                                                           const float* __restrict__ feat_out, const float* __restrict__ feat_in,
+                                                           float inv_scale, int d, float* __restrict__ out) {
+    const int lane = blockIdx.x;
+    const size_t row = last_rows[lane];
+    float* o = out + (size_t)lane * (cap + k + 2 * d);
+    for (int i = threadIdx.x; i < cap; i += blockDim.x) o[i] = weights[row * cap + i];
+    for (int i = threadIdx.x; i < k; i += blockDim.x) o[cap + i] = q_pnc[row * k + i];
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        o[cap + k + i] = m_val[row * d + i];
+        float z;
+        if (z_direct)
+            z = z_direct[row * d + i];
+        else if (feat_in)
+            z = __fmul_rn(__fsub_rn(feat_out[row * d + i], feat_in[row * d + i]), inv_scale);
+        else
+            z = feat_out[row * d + i];  // block 0: its output is F0(embed), no residual
+        o[cap + k + d + i] = z;
+    }
+}
+
 inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace
@@ -301,6 +327,15 @@ int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t*
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n) {
     to_bf16_kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(src, (__nv_bfloat16*)dst, n);
     return after_launch(ctx, "to_bf16_kernel");
+}
+
+int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_t lanes, const float* weights, int cap, const float* q_pnc,
+                            int k, const float* m_val, const float* z_direct, const float* feat_out, const float* feat_in, float scale,
+                            int d, float* out) {
+    if (lanes == 0) return PSSA_B200_OK;
+    observe_rows_kernel<<<(unsigned)lanes, 256, 0, ctx->stream>>>(last_rows, weights, cap, q_pnc, k, m_val, z_direct, feat_out, feat_in,
+                                                                 scale != 0.0f ? 1.0f / scale : 0.0f, d, out);
+    return after_launch(ctx, "observe_rows_kernel");
 }
 
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v) {

@@ -108,6 +108,7 @@ struct SampleParams {
     unsigned* status_out;        // [rows] 0 ok, 1 non-finite logits, 2 invalid probability mass, 3 no candidates
     int exact;                   // sequential f32 sum over the vocabulary (the reference's order)
     const unsigned* slots;       // optional [rows]: recent_* and rng_state are indexed by slots[row] instead of row
+    float* confidence_out;       // optional [rows]: raw softmax probability of the selected id (src/inference.rs:526-545)
 };
 int32_t launch_sample(pssa_b200_ctx* ctx, const SampleParams& p);
 int32_t launch_push_recent(pssa_b200_ctx* ctx, const unsigned* ids, const unsigned* slots, unsigned* recent, unsigned* count, size_t rows);
@@ -161,6 +162,9 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
 int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale);
 int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d);
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n);
+int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_t lanes, const float* weights, int cap, const float* q_pnc,
+                            int k, const float* m_val, const float* z_direct, const float* feat_out, const float* feat_in, float scale,
+                            int d, float* out);
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v);
 
 }  // namespace pssa

@@ -78,6 +78,15 @@ struct pssa_b200_model {
         void* arg = nullptr;
         bool active = false;        // set for the duration of a sharded prefill call only (decode steps stay local)
     } sp;
+    // observer scratch (src/pssa.rs:609-619: inf_q_pnc, inf_mem_weights, inf_m_val, inf_z_final of the last forward):
+    // when enabled, every block publishes those four vectors for the last token of every lane of the last call
+    struct Observer {
+        bool enabled = false;
+        float* q_pnc = nullptr;   // [rows capacity][k]   projected queries of the current block (all rows)
+        size_t q_rows = 0;
+        float* buf = nullptr;     // [depth][lanes capacity][cap + k + 2d]
+        size_t lanes = 0, valid_lanes = 0;
+    } obs;
     // per-stream sampler state for device-side sampling (src/inference.rs:37-41: one generator and one list of
     // generated ids per engine); allocated on first use
     struct Sampler {
@@ -86,6 +95,7 @@ struct pssa_b200_model {
         unsigned long long* rng = nullptr;     // [max_streams]
         unsigned *ids = nullptr, *status = nullptr, *head_slot = nullptr;  // [lanes capacity]
         float* probs = nullptr;                // [lanes capacity][vocab]
+        float* conf = nullptr;                 // [lanes capacity]
         size_t lanes = 0;
     } sampler;
     // time chunks ("virtual lanes") of the two-pass SSM: chunk maps, chunk carry-ins and the chunk row ranges

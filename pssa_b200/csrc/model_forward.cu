@@ -117,7 +117,8 @@ int32_t dense(pssa_b200_model* m, const float* x32, const void* x16, const float
 
 // One pass: `rows` packed token rows of `lanes` lanes already described in the workspace (ids, lane_off, lane_len,
 // lane_slot, last_rows). Leaves the final features of every row in ws.feat_a or feat_b (returned).
-int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32_t* h_off, const uint32_t* h_len, float** feats_out) {
+int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32_t* h_off, const uint32_t* h_len, float** feats_out,
+                     size_t n_obs = 0) {
     pssa_b200_ctx* ctx = m->ctx;
     Workspace& ws = m->ws;
     const bool exact = m->precision == PSSA_B200_PRECISION_FP32_EXACT;
@@ -163,6 +164,24 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.off, v_off.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
         PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.len, v_len.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
         PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    const bool observe = m->obs.enabled && n_obs > 0;
+    const size_t obs_rec = m->cap + m->k + 2 * m->d;
+    if (observe) {
+        auto& ob = m->obs;
+        if (rows > ob.q_rows) {
+            PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ob.q_pnc), ob.q_pnc = nullptr, ob.q_rows = 0;
+            PSSA_CUDA(ctx, cudaMalloc((void**)&ob.q_pnc, rows * m->k * sizeof(float)));
+            ob.q_rows = rows;
+        }
+        if (n_obs > ob.lanes) {
+            PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            cudaFree(ob.buf), ob.buf = nullptr, ob.lanes = 0;
+            PSSA_CUDA(ctx, cudaMalloc((void**)&ob.buf, m->depth * n_obs * obs_rec * sizeof(float)));
+            ob.lanes = n_obs;
+        }
+        ob.valid_lanes = n_obs;
     }
     for (size_t l = 0; l < m->depth; ++l) {
         DeviceBlock& b = m->blocks[l];
@@ -222,9 +241,9 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
         if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
         RetrieveParams rp{};
-        rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = nullptr, rp.q_norm = nullptr;
+        rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = observe ? m->obs.q_pnc : nullptr, rp.q_norm = nullptr;
         rp.keys = b.w[T_BANK_KEYS], rp.norm_sq = b.w[T_BANK_NORM_SQ], rp.values = b.w[T_BANK_VALUES];
-        rp.weights = ws.weights, rp.m_val = exact ? ws.m_val : nullptr, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
+        rp.weights = ws.weights, rp.m_val = (exact || observe) ? ws.m_val : nullptr, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
         rp.value_terms = exact ? 6 : 3;  // the bf16 mode keeps only the bf16 copy of m (the W_proj operand)
         rp.rows = rows, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
@@ -250,6 +269,10 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
                                                 m->d, 2 * m->d)))
                 return rc;
         }
+        if (observe && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, ws.weights, (int)m->cap, m->obs.q_pnc, k, ws.m_val,
+                                                 exact ? ws.z : nullptr, feat_out, l == 0 ? nullptr : feat_in, rscale, d,
+                                                 m->obs.buf + l * m->obs.lanes * obs_rec)))
+            return rc;
         feat_in = feat_out;
         feat_out = (feat_out == ws.feat_a) ? ws.feat_b : ws.feat_a;
     }
@@ -292,12 +315,13 @@ int32_t ensure_sampler(pssa_b200_model* m, size_t lanes) {
     }
     if (lanes > sm.lanes) {
         PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-        cudaFree(sm.ids), cudaFree(sm.status), cudaFree(sm.head_slot), cudaFree(sm.probs);
-        sm.ids = sm.status = sm.head_slot = nullptr, sm.probs = nullptr, sm.lanes = 0;
+        cudaFree(sm.ids), cudaFree(sm.status), cudaFree(sm.head_slot), cudaFree(sm.probs), cudaFree(sm.conf);
+        sm.ids = sm.status = sm.head_slot = nullptr, sm.probs = sm.conf = nullptr, sm.lanes = 0;
         PSSA_CUDA(ctx, cudaMalloc((void**)&sm.ids, lanes * 4));
         PSSA_CUDA(ctx, cudaMalloc((void**)&sm.status, lanes * 4));
         PSSA_CUDA(ctx, cudaMalloc((void**)&sm.head_slot, lanes * 4));
         PSSA_CUDA(ctx, cudaMalloc((void**)&sm.probs, lanes * m->v * sizeof(float)));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sm.conf, lanes * sizeof(float)));
         sm.lanes = lanes;
     }
     return PSSA_B200_OK;
@@ -305,7 +329,7 @@ int32_t ensure_sampler(pssa_b200_model* m, size_t lanes) {
 
 int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offsets, const uint32_t* lengths, const uint32_t* streams,
                   size_t n_lanes, float* logits, uint64_t* greedy, int32_t (*cancelled)(void*), void* cancel_arg, size_t* processed,
-                  const pssa_b200_sampling* sampling = nullptr, uint32_t sample_flags = 0) {
+                  const pssa_b200_sampling* sampling = nullptr, uint32_t sample_flags = 0, float* confidence = nullptr) {
     pssa_b200_ctx* ctx = m->ctx;
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     uint32_t max_len = 0;
@@ -335,7 +359,7 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
         // heads: a lane's last token is in this pass iff its length ends inside the window
         h_last.clear();
         std::vector<size_t> head_lane;
-        if (logits || greedy || sampling)
+        if (logits || greedy || sampling || m->obs.enabled)
             for (size_t l = 0; l < n_lanes; ++l)
                 if (lengths[l] > t0 && lengths[l] <= t0 + window) {
                     h_last.push_back(h_off[l] + h_len[l] - 1);
@@ -350,10 +374,11 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
         PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, h_slot.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
         if (!h_last.empty()) PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
         float* feats = nullptr;
-        if ((rc = forward_rows(m, rows, n_lanes, h_off.data(), h_len.data(), &feats))) return rc;
-        if (!h_last.empty()) {
+        if ((rc = forward_rows(m, rows, n_lanes, h_off.data(), h_len.data(), &feats, h_last.size()))) return rc;
+        if (!h_last.empty() && (logits || greedy || sampling)) {
             if ((rc = head_rows(m, feats, h_last.size(), greedy != nullptr && !sampling))) return rc;
             std::vector<uint32_t> g(h_last.size()), g_status(h_last.size(), 0);
+            std::vector<float> g_conf;
             if (sampling) {
                 // sample on the device from the logits the head just wrote; only ids come back
                 if ((rc = ensure_sampler(m, n_lanes))) return rc;
@@ -367,12 +392,16 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
                 sp.temperature = sampling->temperature, sp.top_p = sampling->top_p, sp.repetition_penalty = sampling->repetition_penalty;
                 sp.recent_ids = m->sampler.recent, sp.recent_count = m->sampler.count, sp.rng_state = m->sampler.rng;
                 sp.ids_out = m->sampler.ids, sp.status_out = m->sampler.status, sp.exact = (sample_flags & PSSA_B200_SAMPLE_EXACT) != 0;
-                sp.slots = m->sampler.head_slot;
+                sp.slots = m->sampler.head_slot, sp.confidence_out = confidence ? m->sampler.conf : nullptr;
                 if ((rc = launch_sample(ctx, sp))) return rc;
                 if ((rc = launch_push_recent(ctx, m->sampler.ids, m->sampler.head_slot, m->sampler.recent, m->sampler.count, h_last.size())))
                     return rc;
                 PSSA_CUDA(ctx, cudaMemcpyAsync(g.data(), m->sampler.ids, g.size() * 4, cudaMemcpyDeviceToHost, st));
                 PSSA_CUDA(ctx, cudaMemcpyAsync(g_status.data(), m->sampler.status, g.size() * 4, cudaMemcpyDeviceToHost, st));
+                if (confidence) {
+                    g_conf.resize(g.size());
+                    PSSA_CUDA(ctx, cudaMemcpyAsync(g_conf.data(), m->sampler.conf, g.size() * 4, cudaMemcpyDeviceToHost, st));
+                }
             } else if (greedy) {
                 PSSA_CUDA(ctx, cudaMemcpyAsync(g.data(), ws.greedy, g.size() * 4, cudaMemcpyDeviceToHost, st));
             }
@@ -396,6 +425,7 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
                         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "%s", why);
                     }
                     greedy[head_lane[i]] = g[i];
+                    if (confidence && !g_conf.empty()) confidence[head_lane[i]] = g_conf[i];
                 }
         } else if (final_pass || cancelled) {
             PSSA_CUDA(ctx, cudaStreamSynchronize(st));
@@ -469,7 +499,7 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
     PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
     float* feats = nullptr;
     m->sp.active = m->sp.world > 1;
-    rc = forward_rows(m, span, n_lanes, h_off.data(), h_len.data(), &feats);
+    rc = forward_rows(m, span, n_lanes, h_off.data(), h_len.data(), &feats, h_last.size());
     m->sp.active = false;
     if (rc) return rc;
     if (logits_dev || greedy_dev) {
@@ -489,6 +519,34 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_model_set_observer(pssa_b200_model* m, int32_t enabled) {
+    if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
+    m->obs.enabled = enabled != 0;
+    if (!m->obs.enabled) m->obs.valid_lanes = 0;
+    return PSSA_B200_OK;
+}
+
+int32_t pssa_b200_model_get_observation(pssa_b200_model* m, uint32_t layer, uint32_t index, float* mem_weights, float* q_pnc, float* m_val,
+                                        float* z_final) {
+    if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (!m->obs.enabled || m->obs.valid_lanes == 0)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "observer scratch is empty: enable the observer and run a forward call first");
+    if (layer >= m->depth || index >= m->obs.valid_lanes)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "observation (block %u, lane %u) outside %zu blocks x %zu lanes", layer, index, m->depth,
+                    m->obs.valid_lanes);
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t rec = m->cap + m->k + 2 * m->d;
+    const float* src = m->obs.buf + ((size_t)layer * m->obs.lanes + index) * rec;
+    cudaStream_t st = ctx->stream;
+    if (mem_weights) PSSA_CUDA(ctx, cudaMemcpyAsync(mem_weights, src, m->cap * 4, cudaMemcpyDeviceToHost, st));
+    if (q_pnc) PSSA_CUDA(ctx, cudaMemcpyAsync(q_pnc, src + m->cap, m->k * 4, cudaMemcpyDeviceToHost, st));
+    if (m_val) PSSA_CUDA(ctx, cudaMemcpyAsync(m_val, src + m->cap + m->k, m->d * 4, cudaMemcpyDeviceToHost, st));
+    if (z_final) PSSA_CUDA(ctx, cudaMemcpyAsync(z_final, src + m->cap + m->k + m->d, m->d * 4, cudaMemcpyDeviceToHost, st));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64_t seed) {
     if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
     pssa_b200_ctx* ctx = m->ctx;
@@ -505,7 +563,7 @@ int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64
 }
 
 int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n,
-                                            const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out) {
+                                            const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out, float* confidence_out) {
     if (!m || !ids || !cfg || !ids_out) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "decode_step_sampled: null argument");
     pssa_b200_ctx* ctx = m->ctx;
     if (n == 0 || n > 0x7fffffff) return fail(ctx, PSSA_B200_ERR_SHAPE, "decode_step: stream count must be in 1..2^31-1");
@@ -527,7 +585,7 @@ int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* 
     }
     std::vector<uint32_t> off(n), len(n, 1);
     for (size_t i = 0; i < n; ++i) off[i] = (uint32_t)i;
-    return run_lanes(m, ids, off.data(), len.data(), streams, n, nullptr, ids_out, nullptr, nullptr, nullptr, cfg, flags);
+    return run_lanes(m, ids, off.data(), len.data(), streams, n, nullptr, ids_out, nullptr, nullptr, nullptr, cfg, flags, confidence_out);
 }
 
 int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev, size_t capacity,

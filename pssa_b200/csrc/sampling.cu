@@ -50,6 +50,10 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     __shared__ unsigned long long s_red[kSampleThreads / 32];
     __shared__ float s_part[kSampleThreads];
     __shared__ int s_flag;
+    __shared__ unsigned s_pen_id[kRecent];
+    __shared__ float s_pen_orig[kRecent];
+    __shared__ unsigned s_pen_n;
+    __shared__ float s_raw_max, s_raw_sum;
     const int tid = threadIdx.x;
     const size_t row = blockIdx.x;
     const size_t slot = p.slots ? p.slots[row] : row;  // where this row's history and generator live
@@ -70,16 +74,61 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
         if (tid == 0) p.ids_out[row] = 0xffffffffu, p.status_out[row] = 1;
         return;
     }
+    // raw softmax statistics over ALL ids, before penalty / temperature / exclusion of id 0 (`raw_confidence`,
+    // src/inference.rs:526-545); only when the caller wants the selected token's raw probability
+    if (p.confidence_out) {
+        float mxr = -FLT_MAX;
+        for (int i = tid; i < v; i += kSampleThreads) mxr = fmaxf(mxr, lg[i]);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) mxr = fmaxf(mxr, __shfl_xor_sync(0xffffffffu, mxr, m));
+        s_part[tid] = mxr;
+        __syncthreads();
+        if (tid == 0) {
+            for (int t = 0; t < kSampleThreads; t += 32) mxr = fmaxf(mxr, s_part[t]);
+            s_raw_max = mxr;
+        }
+        __syncthreads();
+        mxr = s_raw_max;
+        float part = 0.0f;
+        for (int i = tid; i < v; i += kSampleThreads) part += expf(__fsub_rn(lg[i], mxr));
+        s_part[tid] = part;
+        __syncthreads();
+        if (tid == 0) {
+            float sum = 0.0f;
+            if (p.exact) {
+                for (int i = 0; i < v; ++i) sum = __fadd_rn(sum, expf(__fsub_rn(lg[i], mxr)));  // the reference's order
+            } else {
+                for (int t = 0; t < kSampleThreads; ++t) sum += s_part[t];
+            }
+            s_raw_sum = sum;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) s_pen_n = 0;
     // 2. repetition penalty, in the order the ids were generated
     if (tid == 0 && p.repetition_penalty > 1.0f && p.recent_ids) {
         const unsigned n = min(p.recent_count[slot], (unsigned)kRecent);
         const unsigned* ids = p.recent_ids + slot * kRecent;
         for (unsigned g = 0; g < n; ++g) {
             const unsigned id = ids[g];
-            if (id < (unsigned)v) lg[id] = lg[id] > 0.0f ? __fdiv_rn(lg[id], p.repetition_penalty) : __fmul_rn(lg[id], p.repetition_penalty);
+            if (id < (unsigned)v) {
+                bool known = false;  // remember the unpenalised value once per id (for the raw confidence)
+                for (unsigned q = 0; q < g && !known; ++q) known = ids[q] == id;
+                if (!known) s_pen_id[s_pen_n] = id, s_pen_orig[s_pen_n] = lg[id], ++s_pen_n;
+                lg[id] = lg[id] > 0.0f ? __fdiv_rn(lg[id], p.repetition_penalty) : __fmul_rn(lg[id], p.repetition_penalty);
+            }
         }
     }
     __syncthreads();
+    auto publish = [&](unsigned id) {  // thread 0 only: the selected id and, if wanted, its raw softmax probability
+        p.ids_out[row] = id, p.status_out[row] = 0;
+        if (p.confidence_out) {
+            float raw = lg[id];
+            for (unsigned q = 0; q < s_pen_n; ++q)
+                if (s_pen_id[q] == id) raw = s_pen_orig[q];
+            p.confidence_out[row] = __fdiv_rn(expf(__fsub_rn(raw, s_raw_max)), s_raw_sum);
+        }
+    };
     // 3 / 4a. maximum over ids 1..V-1 as (order key, lowest id wins)
     unsigned long long best = 0;
     for (int i = tid; i < v; i += kSampleThreads)
@@ -94,7 +143,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
     }
     const unsigned arg_max = 0xffffffffu - (unsigned)(best & 0xffffffffull);
     if (p.temperature == 0.0f) {
-        if (tid == 0) p.ids_out[row] = arg_max, p.status_out[row] = 0;
+        if (tid == 0) publish(arg_max);
         return;
     }
     const float mx = lg[arg_max];
@@ -189,7 +238,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(SampleParams p) 
                 break;
             }
         }
-        p.ids_out[row] = id, p.status_out[row] = 0;
+        publish(id);
     }
 }
 

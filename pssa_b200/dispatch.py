@@ -206,11 +206,12 @@ class B200Dispatch:
 
     # ---- device-side sampling (src/inference.rs:102-181)
     def sample_dev(self, logits, probs, rows, vocab, rng_state, ids_out, status_out, temperature=0.70, top_p=0.85, top_k=24,
-                   repetition_penalty=1.25, recent_ids=None, recent_count=None, exact=False):
+                   repetition_penalty=1.25, recent_ids=None, recent_count=None, exact=False, confidence_out=None):
         """One sampled id per stream; all buffers are device buffers (torch tensors or raw pointers)."""
         cfg = N.Sampling(temperature, top_p, top_k, repetition_penalty)
         self._check(self._lib.pssa_b200_sample_dev(self._h, _ptr(logits), _ptr(probs), rows, vocab, C.byref(cfg), _ptr(recent_ids),
                                                    _ptr(recent_count), _ptr(rng_state), _ptr(ids_out), _ptr(status_out),
+                                                   _ptr(confidence_out),
                                                    N.SAMPLE_EXACT if exact else 0))
 
     # ---- bank write / plastic fast weights (device pointers)

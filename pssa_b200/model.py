@@ -186,19 +186,35 @@ class PSSAModel:
             return logits, greedy
         return logits if want_logits else greedy
 
+    def set_observer(self, enabled=True):
+        """Publish each block's retrieval scratch of the last token of every lane (src/pssa.rs:609-619)."""
+        self.gpu._check(self._lib.pssa_b200_model_set_observer(self._h, 1 if enabled else 0))
+
+    def observation(self, layer, index=0):
+        """(mem_weights [cap], q_pnc [k], m_val [d], z_final [d]) of block `layer` for emitting lane `index`."""
+        w = np.empty(self.mem_capacity, np.float32)
+        q = np.empty(self.d_mem_key, np.float32)
+        mv = np.empty(self.d_latent, np.float32)
+        z = np.empty(self.d_latent, np.float32)
+        self.gpu._check(self._lib.pssa_b200_model_get_observation(self._h, layer, index, _ptr(w), _ptr(q), _ptr(mv), _ptr(z)))
+        return w, q, mv, z
+
     def sampler_seed(self, stream=0, seed=1337):
         """Reset a stream's generator and its window of generated ids (`SimpleRng::new(seed)`, src/linalg.rs:7-11)."""
         self.gpu._check(self._lib.pssa_b200_model_sampler_seed(self._h, stream, seed))
 
-    def decode_step_sampled(self, ids, streams=None, temperature=0.70, top_p=0.85, top_k=24, repetition_penalty=1.25, exact=False):
-        """Decode step with `sample` (src/inference.rs:102-181) on the device; returns the sampled ids."""
+    def decode_step_sampled(self, ids, streams=None, temperature=0.70, top_p=0.85, top_k=24, repetition_penalty=1.25, exact=False,
+                            want_confidence=False):
+        """Decode step with `sample` (src/inference.rs:102-181) on the device; returns the sampled ids (and, if asked,
+        the raw softmax probability of each: `raw_confidence`, src/inference.rs:526-545)."""
         ids = np.ascontiguousarray(ids, np.uint64)
         st = None if streams is None else np.ascontiguousarray(streams, np.uint32)
         out = np.empty(ids.size, np.uint64)
         cfg = N.Sampling(temperature, top_p, top_k, repetition_penalty)
+        conf = np.empty(ids.size, np.float32) if want_confidence else None
         self.gpu._check(self._lib.pssa_b200_model_decode_step_sampled(self._h, _ptr(st), _ptr(ids), ids.size, C.byref(cfg),
-                                                                      N.SAMPLE_EXACT if exact else 0, _ptr(out)))
-        return out
+                                                                      N.SAMPLE_EXACT if exact else 0, _ptr(out), _ptr(conf)))
+        return (out, conf) if want_confidence else out
 
     def generate_greedy(self, prompt_ids, n_new, stream=0):
         """Prefill + greedy decode (src/inference.rs:348-418 at temperature 0): returns the generated ids."""

@@ -259,3 +259,40 @@ def test_reference_cpu_case_prefill_512_then_200_greedy_tokens(gpu):
         followed += 1
         ref = om2.forward_inference(int(ref_tokens[t]))
     assert followed >= 1
+
+
+@pytest.mark.parametrize("top_k", [0, 3])
+def test_observer_scratch_matches_the_reference_buffers(gpu, top_k):
+    """`inf_mem_weights / inf_q_pnc / inf_m_val / inf_z_final` of every block for the last token processed
+    (src/pssa.rs:609-619), after a prefill and after decode steps, in both precision modes."""
+    for precision, tol in ((1, 1e-5), (0, 3e-2)):
+        om, gm = make_pair(gpu, 3, 80, 48, 16, 16, 20, seed=17, streams=2, bank_fill=0.8, precision=precision)
+        if top_k:
+            gm.set_memory_top_k(top_k)
+            for l in range(3):
+                c, h, _ = om.bank_meta(l)
+                om.set_bank_meta(l, c, h, top_k)
+        gm.set_observer(True)
+        ids = (np.arange(23) * 7 + 2) % 80
+
+        def check(where):
+            for l in range(3):
+                w, q, mv, z = gm.observation(l, 0)
+                ref = [om.tensor(l, t).copy() for t in (O.S_MEM_WEIGHTS, O.S_Q_PNC, O.S_M_VAL, O.S_Z_FINAL)]
+                for got, want, name in zip((w, q, mv, z), ref, ("weights", "q_pnc", "m_val", "z_final")):
+                    scale = max(1e-6, float(np.abs(want).max()))
+                    assert np.max(np.abs(got - want)) / scale <= tol, (where, l, name, precision)
+                if precision == 1 and top_k:
+                    assert np.array_equal(w != 0, ref[0] != 0)  # the same slots selected
+
+        gm.prefill_inference(ids)
+        om.prefill_inference(ids)
+        check("prefill")
+        for tok in (5, 9):
+            gm.forward_inference(tok)
+            om.forward_inference(tok)
+            check("decode")
+        gm.set_observer(False)
+        with pytest.raises(Exception, match="observer scratch is empty"):
+            gm.observation(0, 0)
+        gm.close()

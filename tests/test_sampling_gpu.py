@@ -29,11 +29,13 @@ def run(gpu, logits, recent, states, exact=True, **cfg):
     st = torch.from_numpy(np.asarray(states, np.uint64).view(np.int64).copy()).cuda()
     out = torch.zeros(rows, dtype=torch.int32, device="cuda")
     status = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    conf = torch.zeros(rows, device="cuda")
     gpu.set_stream(torch.cuda.current_stream())
     gpu.sample_dev(lg, probs, rows, v, st, out, status, recent_ids=torch.from_numpy(rid.view(np.int32)).cuda(),
-                   recent_count=torch.from_numpy(rcount.view(np.int32)).cuda(), exact=exact, **cfg)
+                   recent_count=torch.from_numpy(rcount.view(np.int32)).cuda(), exact=exact, confidence_out=conf, **cfg)
     torch.cuda.synchronize()
     gpu.set_stream(None)
+    run.confidence = conf.cpu().numpy()
     return (out.cpu().numpy().view(np.uint32), status.cpu().numpy(), st.cpu().numpy().view(np.uint64), lg.cpu().numpy())
 
 
@@ -56,6 +58,10 @@ def test_sampled_ids_rng_state_and_penalised_logits_match_the_restatement(gpu, c
     recent[5] = [min(7, v - 1)] * 80  # one id repeated through the whole window
     states = rng.integers(1, 2**63, rows, dtype=np.uint64)
     ids, status, new_states, lg_after = run(gpu, logits, recent, states, **cfg)
+    # raw confidence: softmax of the UNpenalised logits over all ids, at the selected id (src/inference.rs:526-545)
+    raw = np.exp(logits - logits.max(1, keepdims=True)).astype(np.float32)
+    raw /= np.cumsum(raw, axis=1, dtype=np.float32)[:, -1:]  # the reference sums in id order
+    assert np.max(np.abs(run.confidence - raw[np.arange(rows), ids.astype(np.int64)])) <= 1e-6
     mismatches = 0
     for r in range(rows):
         ref_id, ref_state, ref_lg = O.sample(int(states[r]), logits[r], recent[r], **cfg)
@@ -124,10 +130,13 @@ def test_model_level_sampled_decode_follows_the_restatement(gpu):
     toks = [7, 8]
     mismatches = 0
     for step in range(24):
-        got = gm.decode_step_sampled(toks, [0, 1], exact=True, **cfg)
+        got, conf = gm.decode_step_sampled(toks, [0, 1], exact=True, want_confidence=True, **cfg)
         nxt = []
         for s in range(2):
             lg = oms[s].forward_inference(toks[s])
+            raw = np.exp(lg - lg.max())
+            # logits of magnitude ~100 here: the 1e-5 relative agreement of the logits becomes ~1e-4 on a probability
+            assert abs(float(conf[s]) - float(raw[int(got[s])] / raw.sum())) <= 2e-4
             ref_id, states[s], _ = O.sample(states[s], lg, history[s], **cfg)
             if int(got[s]) != ref_id:
                 mismatches += 1
