@@ -384,6 +384,16 @@ int32_t pssa_b200_sample_dev(pssa_b200_ctx* ctx, float* logits, float* probs, si
                              uint32_t flags);
 
 /*
+ * Frozen-model scorer: the forward half of the reference's chunk forward (src/pssa.rs:2597-2750 with one loop), which
+ * `pssa score` / `pssa throughput` use on a frozen model (src/evaluation.rs:205-236): logits for EVERY position, then
+ * the mean over positions of (max - l[target]) + ln(sum exp(l - max)). The stream's carry advances like a prefill.
+ * Full-vocabulary logits are produced a tile of rows at a time and never held for the whole sequence.
+ * HOST pointers: ids / targets [n]; mean_loss; token_loss [n] (NULL to skip); logits_out [n, vocab] (NULL to skip).
+ */
+int32_t pssa_b200_model_score(pssa_b200_model* m, uint32_t stream, const uint64_t* ids, const uint64_t* targets, size_t n,
+                              float* mean_loss, float* token_loss, float* logits_out);
+
+/*
  * Observer scratch: the reference keeps, per block, the retrieval state of the last token it processed
  * (`inf_mem_weights`, `inf_q_pnc`, `inf_m_val`, `inf_z_final`, src/pssa.rs:609-619) and hands it to generation
  * observers (src/inference.rs:257-313). With the observer enabled every forward call (prefill, batched prefill, decode

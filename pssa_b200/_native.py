@@ -62,6 +62,7 @@ SIGNATURES = {
                                               C.POINTER(C.c_double)]),
     "pssa_b200_model_decode_step": (C.c_int32, [_vp, _vp, _vp, _sz, _vp, _vp]),
     "pssa_b200_sample_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
+    "pssa_b200_model_score": (C.c_int32, [_vp, C.c_uint32, _vp, _vp, _sz, _vp, _vp, _vp]),
     "pssa_b200_model_set_observer": (C.c_int32, [_vp, C.c_int32]),
     "pssa_b200_model_get_observation": (C.c_int32, [_vp, C.c_uint32, C.c_uint32, _vp, _vp, _vp, _vp]),
     "pssa_b200_model_sampler_seed": (C.c_int32, [_vp, C.c_uint32, C.c_uint64]),

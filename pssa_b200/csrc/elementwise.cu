@@ -2,6 +2,7 @@
 // depth residual, row gather, greedy argmax, fp32 -> bf16 conversion.
 #include <cuda_bf16.h>
 
+#include <cfloat>
 #include <climits>
 
 #include "context.hpp"
@@ -254,6 +255,38 @@ __global__ void __launch_bounds__(256) observe_rows_kernel(const uint32_t* __res
     }
 }
 
+// Cross entropy of one logits row against its target (src/pssa.rs:2597-2750, the scorer's per-row loss):
+// loss = (max - l[target]) + ln(sum exp(l - max)). One CTA per row; a non-finite row or a target outside the
+// vocabulary gives NaN, which the host reports.
+__global__ void __launch_bounds__(256) cross_entropy_kernel(const float* __restrict__ logits, const uint32_t* __restrict__ targets,
+                                                            float* __restrict__ loss, int v) {
+    __shared__ float s_red[256];
+    const size_t row = blockIdx.x;
+    const float* lg = logits + row * (size_t)v;
+    float mx = -FLT_MAX;
+    for (int i = threadIdx.x; i < v; i += 256) mx = fmaxf(mx, lg[i]);
+    s_red[threadIdx.x] = mx;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+        if (threadIdx.x < w) s_red[threadIdx.x] = fmaxf(s_red[threadIdx.x], s_red[threadIdx.x + w]);
+        __syncthreads();
+    }
+    mx = s_red[0];
+    __syncthreads();
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < v; i += 256) part += expf(__fsub_rn(lg[i], mx));
+    s_red[threadIdx.x] = part;
+    __syncthreads();
+    for (int w = 128; w > 0; w >>= 1) {
+        if (threadIdx.x < w) s_red[threadIdx.x] += s_red[threadIdx.x + w];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const uint32_t t = targets[row];
+        loss[row] = t < (uint32_t)v ? __fadd_rn(__fsub_rn(mx, lg[t]), logf(s_red[0])) : __int_as_float(0x7fc00000);
+    }
+}
+
 inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace
@@ -336,6 +369,13 @@ int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_
     observe_rows_kernel<<<(unsigned)lanes, 256, 0, ctx->stream>>>(last_rows, weights, cap, q_pnc, k, m_val, z_direct, feat_out, feat_in,
                                                                  scale != 0.0f ? 1.0f / scale : 0.0f, d, out);
     return after_launch(ctx, "observe_rows_kernel");
+}
+
+int32_t launch_cross_entropy(pssa_b200_ctx* ctx, const float* logits, const uint32_t* targets, float* loss, size_t rows, int v) {
+    if (rows == 0) return PSSA_B200_OK;
+    if (rows > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "cross entropy: %zu rows exceed grid limits; refusing launch", rows);
+    cross_entropy_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(logits, targets, loss, v);
+    return after_launch(ctx, "cross_entropy_kernel");
 }
 
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v) {

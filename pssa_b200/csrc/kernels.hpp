@@ -165,6 +165,7 @@ int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n
 int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_t lanes, const float* weights, int cap, const float* q_pnc,
                             int k, const float* m_val, const float* z_direct, const float* feat_out, const float* feat_in, float scale,
                             int d, float* out);
+int32_t launch_cross_entropy(pssa_b200_ctx* ctx, const float* logits, const uint32_t* targets, float* loss, size_t rows, int v);
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v);
 
 }  // namespace pssa

@@ -133,6 +133,7 @@ void pssa_b200_model_destroy(pssa_b200_model* m) {
     cudaFree(m->unembed_bf16);
     cudaFree(m->state);
     cudaFree(m->obs.q_pnc), cudaFree(m->obs.buf);
+    cudaFree(m->score.logits), cudaFree(m->score.targets), cudaFree(m->score.loss);
     cudaFree(m->sampler.recent), cudaFree(m->sampler.count), cudaFree(m->sampler.rng), cudaFree(m->sampler.ids);
     cudaFree(m->sampler.status), cudaFree(m->sampler.head_slot), cudaFree(m->sampler.probs), cudaFree(m->sampler.conf);
     cudaFree(m->chunks.off), cudaFree(m->chunks.len), cudaFree(m->chunks.records), cudaFree(m->chunks.carry_in);

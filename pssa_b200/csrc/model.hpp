@@ -78,6 +78,13 @@ struct pssa_b200_model {
         void* arg = nullptr;
         bool active = false;        // set for the duration of a sharded prefill call only (decode steps stay local)
     } sp;
+    // scorer buffers: a tile of full-vocabulary logits, targets and per-row losses
+    struct Score {
+        float* logits = nullptr;   // [tile][vocab]
+        uint32_t* targets = nullptr;
+        float* loss = nullptr;     // [rows capacity]
+        size_t tile = 0, rows = 0;
+    } score;
     // observer scratch (src/pssa.rs:609-619: inf_q_pnc, inf_mem_weights, inf_m_val, inf_z_final of the last forward):
     // when enabled, every block publishes those four vectors for the last token of every lane of the last call
     struct Observer {

@@ -519,6 +519,75 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_model_score(pssa_b200_model* m, uint32_t stream, const uint64_t* ids, const uint64_t* targets, size_t n, float* mean_loss,
+                              float* token_loss, float* logits_out) {
+    if (!m || !ids || !targets || !mean_loss) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "score: null argument");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (n == 0) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "score requires at least one token");
+    if (stream >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u outside %u streams", stream, m->max_streams);
+    for (size_t t = 0; t < n; ++t) {
+        if (ids[t] >= m->v) return fail(ctx, PSSA_B200_ERR_TOKEN, "token ID %llu outside model vocabulary", (unsigned long long)ids[t]);
+        if (targets[t] >= m->v) return fail(ctx, PSSA_B200_ERR_TOKEN, "target ID %llu outside model vocabulary", (unsigned long long)targets[t]);
+    }
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t window = std::min(n, m->max_rows);
+    // tile of full-vocabulary logits: at most 128 MiB
+    const size_t tile = std::max<size_t>(1, std::min(window, ((size_t)128 << 20) / (m->v * sizeof(float))));
+    auto& sc = m->score;
+    if (tile > sc.tile || window > sc.rows) {
+        PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(sc.logits), cudaFree(sc.targets), cudaFree(sc.loss);
+        sc = pssa_b200_model::Score{};
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sc.logits, tile * m->v * sizeof(float)));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sc.targets, window * 4));
+        PSSA_CUDA(ctx, cudaMalloc((void**)&sc.loss, window * 4));
+        sc.tile = tile, sc.rows = window;
+    }
+    const bool exact = m->precision == PSSA_B200_PRECISION_FP32_EXACT;
+    const float scale = 1.0f / std::sqrt((float)m->d);
+    std::vector<uint32_t> h_ids(window), h_tgt(window);
+    std::vector<float> h_loss(window);
+    double total = 0.0;
+    int32_t rc;
+    cudaStream_t st = ctx->stream;
+    for (size_t t0 = 0; t0 < n; t0 += window) {
+        const size_t rows = std::min(window, n - t0);
+        for (size_t t = 0; t < rows; ++t) h_ids[t] = (uint32_t)ids[t0 + t], h_tgt[t] = (uint32_t)targets[t0 + t];
+        if ((rc = ensure_workspace(m, rows, 1))) return rc;
+        Workspace& ws = m->ws;
+        const uint32_t off = 0, len = (uint32_t)rows, slot = stream;
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.ids, h_ids.data(), rows * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(sc.targets, h_tgt.data(), rows * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, &off, 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_len, &len, 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, &slot, 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaStreamSynchronize(st));  // the three scalars above live on this stack frame
+        float* feats = nullptr;
+        if ((rc = forward_rows(m, rows, 1, &off, &len, &feats))) return rc;
+        for (size_t r0 = 0; r0 < rows; r0 += tile) {
+            const size_t nr = std::min(tile, rows - r0);
+            if (exact) {
+                if ((rc = launch_gemm_exact(ctx, feats + r0 * m->d, m->unembed, sc.logits, nr, m->v, m->d, m->v, EPI_SCALE, scale))) return rc;
+            } else {
+                if ((rc = launch_to_bf16(ctx, feats + r0 * m->d, ws.z_bf16, nr * m->d))) return rc;
+                if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, m->unembed_bf16, sc.logits, nullptr, nr, m->v, m->d, m->v, EPI_SCALE, scale))) return rc;
+            }
+            if ((rc = launch_cross_entropy(ctx, sc.logits, sc.targets + r0, sc.loss + r0, nr, (int)m->v))) return rc;
+            if (logits_out)
+                PSSA_CUDA(ctx, cudaMemcpyAsync(logits_out + (t0 + r0) * m->v, sc.logits, nr * m->v * sizeof(float), cudaMemcpyDeviceToHost, st));
+        }
+        PSSA_CUDA(ctx, cudaMemcpyAsync(h_loss.data(), sc.loss, rows * 4, cudaMemcpyDeviceToHost, st));
+        PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+        for (size_t t = 0; t < rows; ++t) {
+            if (!std::isfinite(h_loss[t])) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "model emitted non-finite logits at token %zu", t0 + t);
+            total += (double)h_loss[t];
+            if (token_loss) token_loss[t0 + t] = h_loss[t];
+        }
+    }
+    *mean_loss = (float)(total / (double)n);
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_model_set_observer(pssa_b200_model* m, int32_t enabled) {
     if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
     m->obs.enabled = enabled != 0;

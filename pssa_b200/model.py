@@ -186,6 +186,18 @@ class PSSAModel:
             return logits, greedy
         return logits if want_logits else greedy
 
+    def score(self, ids, targets, stream=0, want_logits=False):
+        """Mean next-token cross entropy of a frozen model over `ids` (the forward half of the chunk forward,
+        src/pssa.rs:2597-2750). Returns (mean loss, per-token losses[, logits [n, vocab]])."""
+        ids = np.ascontiguousarray(ids, np.uint64)
+        targets = np.ascontiguousarray(targets, np.uint64)
+        mean = C.c_float()
+        per = np.empty(ids.size, np.float32)
+        logits = np.empty((ids.size, self.d_vocab), np.float32) if want_logits else None
+        self.gpu._check(self._lib.pssa_b200_model_score(self._h, stream, _ptr(ids), _ptr(targets), ids.size, C.byref(mean), _ptr(per),
+                                                        _ptr(logits)))
+        return (float(mean.value), per, logits) if want_logits else (float(mean.value), per)
+
     def set_observer(self, enabled=True):
         """Publish each block's retrieval scratch of the last token of every lane (src/pssa.rs:609-619)."""
         self.gpu._check(self._lib.pssa_b200_model_set_observer(self._h, 1 if enabled else 0))

@@ -296,3 +296,36 @@ def test_observer_scratch_matches_the_reference_buffers(gpu, top_k):
         with pytest.raises(Exception, match="observer scratch is empty"):
             gm.observation(0, 0)
         gm.close()
+
+
+def test_scorer_reproduces_the_reference_golden_loss_and_logits(gpu, golden_dir):
+    """The frozen-model scorer (all-position logits + cross entropy) against the reference's own vector: word 0 of the
+    golden file is the chunk-forward loss of the fresh depth-one model on ids [1, 2, 1] / targets [2, 1, 3], words
+    [1, 22) its logits (tests/depth_one_parity.rs)."""
+    import pssa_b200
+    data = (golden_dir / "depth_one_main85d9d33_initial.pssa").read_bytes()
+    obs = np.frombuffer((golden_dir / "depth_one_main014f617_avx2_observed.bin").read_bytes(), np.uint32)
+    want_loss = float(obs[:1].view(np.float32)[0])
+    want_logits = obs[1:22].view(np.float32).reshape(3, 7)
+    gm = pssa_b200.PSSAModel.from_checkpoint(gpu, data, precision=1)
+    loss, per, logits = gm.score([1, 2, 1], [2, 1, 3], want_logits=True)
+    assert abs(loss - want_loss) <= 1e-5 * abs(want_loss)
+    assert scale_err(logits, want_logits) <= 1e-5
+    assert abs(float(per.mean()) - loss) <= 1e-6
+    gm.close()
+
+
+def test_scorer_matches_the_oracle_over_passes_and_tiles(gpu):
+    om, gm = make_pair(gpu, 2, 97, 32, 16, 8, 16, seed=23)
+    ids = (np.arange(300) * 7 + 1) % 97
+    targets = (ids * 3 + 5) % 97
+    ref_loss, ref_logits = om.chunk_forward(ids, targets)
+    gm.set_max_rows(128)  # three passes
+    loss, per, logits = gm.score(ids, targets, want_logits=True)
+    assert abs(loss - ref_loss) <= 1e-5 * abs(ref_loss)
+    assert scale_err(logits, ref_logits) <= 1e-5
+    assert np.max(np.abs(gm.copy_recurrent_state_to(0) - om.state())) <= 1e-5 * max(1.0, np.abs(om.state()).max())
+    import pssa_b200
+    with pytest.raises(pssa_b200.B200Error, match="target ID 97 outside"):
+        gm.score([1, 2], [3, 97])
+    gm.close()
