@@ -429,6 +429,9 @@ def run_b200(args):
             roof = kernel_roofline(name, n / args.steps, ms / args.steps, rows, peak_hbm, peak_tf)
             if roof:
                 row["roofline"] = roof
+            if "gemm_bf16" in name:  # the tensor-core launches by epilogue family
+                row["parts"] = {k[k.index("[") + 1:-1] if "[" in k else k: {"launches_per_step": v[0] / args.steps, "ms_per_step": v[1] / args.steps}
+                                for k, v in prof.items() if "gemm_bf16" in k}
             kernels.append(row)
         top = kernels[0]
         roofline = dict(top.get("roofline") or {"bound": "hbm", "achieved": None, "peak": peak_hbm, "unit": "GB/s", "frac": None})

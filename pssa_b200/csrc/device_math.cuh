@@ -21,6 +21,7 @@ enum Epilogue : int {
     EPI_SCALE = 4,    // out = acc * alpha
     EPI_ADD_OUT = 5,  // out = out + acc   (second half of q = Wqx x + Wqh y; residual adds)
     EPI_RESIDUAL = 6, // tensor-core path only: acc + add_in, then the depth residual (see gemm_tcgen05.cu)
+    EPI_GATE = 7,     // tensor-core path only: res_in * acc + alpha * add_in  (gated memory projection + scaled SSM output)
 };
 
 __device__ __forceinline__ float apply_epilogue(int epi, float acc, float alpha, float prev) {

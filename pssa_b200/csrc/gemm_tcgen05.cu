@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EPI_WARPS][32 rows][STG_PITCH]
     const bool vec32 = e.out && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0);
-    const bool vec_res = e.epi == EPI_RESIDUAL && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
+    const bool vec_res = (e.epi == EPI_RESIDUAL || e.epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
                          (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & 15) == 0)));
     const bool vec16 = e.out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out16) & 7) == 0);
 
@@ -308,7 +308,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 // EPI_RESIDUAL reads two more fp32 arrays with the output's access pattern: issue those loads first so
                 // they are in flight during the TMEM load and the transpose
                 float4 pre_add[8], pre_res[8];
-                const bool prefetch = e.epi == EPI_RESIDUAL && interior && vec_res;
+                const bool two_in = e.epi == EPI_RESIDUAL || e.epi == EPI_GATE;
+                const bool prefetch = two_in && interior && vec_res;
                 if (prefetch) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                     *reinterpret_cast<float4*>(stg + lane * STG_PITCH + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 __syncwarp();
                 const int gcol = col0 + cq;
-                if (interior && kind != -1 && (!e.out || vec32) && (!e.out16 || vec16) && (kind != EPI_RESIDUAL || vec_res)) {
+                if (interior && kind != -1 && (!e.out || vec32) && (!e.out16 || vec16) && (!two_in || vec_res)) {
                     float* gp = e.out ? e.out + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
                     __nv_bfloat16* bp = e.out16 ? e.out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
                     const float* sp = stg + rsub * STG_PITCH + cq;
@@ -384,6 +385,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                                     val.x = fmaf(e.res_scale, val.x, rv.x), val.y = fmaf(e.res_scale, val.y, rv.y);
                                     val.z = fmaf(e.res_scale, val.z, rv.z), val.w = fmaf(e.res_scale, val.w, rv.w);
                                 }
+                            } else if (e.epi == EPI_GATE) {
+                                const float4 av = pre_add[i], gv = pre_res[i];
+                                val.x = fmaf(gv.x, val.x, av.x * e.alpha), val.y = fmaf(gv.y, val.y, av.y * e.alpha);
+                                val.z = fmaf(gv.z, val.z, av.z * e.alpha), val.w = fmaf(gv.w, val.w, av.w * e.alpha);
                             }
                             *g4 = val;
                         }
@@ -409,6 +414,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                             if (e.epi == EPI_RESIDUAL) {
                                 o[q] += e.add_in[(size_t)grow * e.ld_add + gcol + q];
                                 if (e.res_in) o[q] = fmaf(e.res_scale, o[q], e.res_in[(size_t)grow * e.ld_res + gcol + q]);
+                            } else if (e.epi == EPI_GATE) {
+                                o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q], o[q],
+                                            e.add_in[(size_t)grow * e.ld_add + gcol + q] * e.alpha);
                             }
                             if (e.out) {
                                 float* gp = e.out + (size_t)grow * e.ldo + gcol + q;
@@ -487,7 +495,16 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
     unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
     kern<<<grid, GEMM_THREADS, smem, ctx->stream>>>(map_a, map_b, e);
-    return after_launch(ctx, "gemm_bf16_tcgen05_kernel");
+    // the profile facility keys on this name: one entry per epilogue family
+    const char* name = e.n_pairs > 0            ? "gemm_bf16_tcgen05_kernel[split value read]"
+                       : e.epi < 0              ? "gemm_bf16_tcgen05_kernel[x-side concatenated]"
+                       : e.epi == EPI_GATE      ? "gemm_bf16_tcgen05_kernel[gated memory projection]"
+                       : e.epi == EPI_RESIDUAL  ? "gemm_bf16_tcgen05_kernel[MLP down + residuals]"
+                       : e.epi == EPI_SILU      ? "gemm_bf16_tcgen05_kernel[MLP up, SiLU]"
+                       : e.epi == EPI_ADD_OUT   ? "gemm_bf16_tcgen05_kernel[accumulate]"
+                       : e.epi == EPI_SCALE     ? "gemm_bf16_tcgen05_kernel[scaled]"
+                                                : "gemm_bf16_tcgen05_kernel[plain]";
+    return after_launch(ctx, name);
 }
 
 int32_t check_shape(pssa_b200_ctx* ctx, const void* a, const void* b, size_t M, size_t N, size_t K) {
@@ -515,11 +532,11 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
 }  // namespace
 
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
-                         size_t K, size_t ldo, int epi, float alpha) {
+                         size_t K, size_t ldo, int epi, float alpha, size_t ld16) {
     int32_t rc = check_shape(ctx, x16, w16, M, N, K);
     if (rc) return rc;
     GemmEpilogue e{};
-    e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
+    e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = ld16 ? ld16 : N;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = epi, e.alpha = alpha;
     return dispatch(ctx, x16, w16, e);
 }
@@ -533,6 +550,20 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
     e.out = out, e.out16 = nullptr, e.ldo = N, e.ld16 = 0;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = EPI_RESIDUAL, e.alpha = 1.0f;
     e.add_in = add_in, e.res_in = res_in, e.ld_add = N, e.ld_res = N, e.res_scale = res_scale;
+    return dispatch(ctx, x16, w16, e);
+}
+
+// z = gate * (X W^T) + alpha * y: the memory projection with its sigmoid gate and the scaled SSM output folded into the
+// epilogue (src/pssa.rs:1189-1192 without the adapter term, which rides in the MLP products as extra K columns).
+// gate [M, ld_gate] and y [M, N] fp32; out fp32 [M, N] and out16 bf16 [M, ld16] are both written.
+int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K) {
+    int32_t rc = check_shape(ctx, x16, w16, M, N, K);
+    if (rc) return rc;
+    GemmEpilogue e{};
+    e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = N, e.ld16 = ld16;
+    e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = EPI_GATE, e.alpha = alpha;
+    e.add_in = y, e.res_in = gate, e.ld_add = N, e.ld_res = ld_gate, e.res_scale = 1.0f;
     return dispatch(ctx, x16, w16, e);
 }
 

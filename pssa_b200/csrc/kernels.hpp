@@ -142,7 +142,10 @@ int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, fl
 
 // gemm_tcgen05.cu: bf16 operands [rows, K] row-major, fp32 accumulate in TMEM; out fp32 [M, ldo] and/or bf16 [M, N]
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
-                         size_t K, size_t ldo, int epi, float alpha);
+                         size_t K, size_t ldo, int epi, float alpha, size_t ld16 = 0);  // ld16: row pitch of out_bf16 (0 = N)
+// z = gate * (X W^T) + alpha * y, fp32 and bf16 (row pitch ld16) outputs
+int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K);
 // MLP output with both residuals fused: out = res_in ? res_in + res_scale*(X W^T + add_in) : X W^T + add_in
 int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const float* add_in,
                                   const float* res_in, float res_scale, size_t M, size_t N, size_t K);
@@ -165,6 +168,11 @@ int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n
 int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_t lanes, const float* weights, int cap, const float* q_pnc,
                             int k, const float* m_val, const float* z_direct, const float* feat_out, const float* feat_in, float scale,
                             int d, float* out);
+// adapter term folded into the MLP products (bf16 mode): see elementwise.cu
+int32_t launch_pack_act(pssa_b200_ctx* ctx, const float* act, size_t ldact, void* dst_a, size_t ld_a, int off_a, void* dst_b, size_t ld_b,
+                        int off_b, size_t rows);
+int32_t launch_pack_weight_cat(pssa_b200_ctx* ctx, const float* src, const float* tail, void* dst, size_t n, int k);
+int32_t launch_times_adapter(pssa_b200_ctx* ctx, const float* w, const float* u, float* out, size_t n, int k);
 int32_t launch_cross_entropy(pssa_b200_ctx* ctx, const float* logits, const uint32_t* targets, float* loss, size_t rows, int v);
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v);
 

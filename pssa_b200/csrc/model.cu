@@ -101,8 +101,9 @@ int32_t pssa_b200_model_create(pssa_b200_ctx* ctx, const pssa_b200_config* cfg, 
         guard(dev_alloc(ctx, &b.wcat_bf16, m->ncat * m->d * 2, true));
         guard(dev_alloc(ctx, &b.wqh_bf16, m->k * m->d * 2, true));
         guard(dev_alloc(ctx, &b.wproj_bf16, m->d * m->d * 2, true));
-        guard(dev_alloc(ctx, &b.w1_bf16, 2 * m->d * m->d * 2, true));
-        guard(dev_alloc(ctx, &b.w2_bf16, 2 * m->d * m->d * 2, true));
+        guard(dev_alloc(ctx, &b.w1cat_bf16, 2 * m->d * (m->d + 64) * 2, true));
+        guard(dev_alloc(ctx, &b.w2cat_bf16, m->d * (2 * m->d + 64) * 2, true));
+        guard(dev_alloc(ctx, (void**)&b.w1u, 2 * m->d * 16 * 4, true));
         guard(dev_alloc(ctx, &b.vsplit_bf16, m->d * 3 * m->cap * 2, true));
         b.host_up.assign(m->d * m->rank, 0.0f);
         b.host_cons.assign(m->d * m->rank, 0.0f);
@@ -144,8 +145,9 @@ void pssa_b200_model_destroy(pssa_b200_model* m) {
         cudaFree(b.wcat_bf16);
         cudaFree(b.wqh_bf16);
         cudaFree(b.wproj_bf16);
-        cudaFree(b.w1_bf16);
-        cudaFree(b.w2_bf16);
+        cudaFree(b.w1cat_bf16);
+        cudaFree(b.w2cat_bf16);
+        cudaFree(b.w1u);
         cudaFree(b.vsplit_bf16);
     }
     free_workspace(m->ws);

@@ -30,8 +30,11 @@ struct DeviceBlock {
     void* wcat_bf16 = nullptr;  // [ncat, d] rows: W_delta | W_B | W_C | W_qx | W_gate | adapter down
     void* wqh_bf16 = nullptr;
     void* wproj_bf16 = nullptr;
-    void* w1_bf16 = nullptr;
-    void* w2_bf16 = nullptr;
+    // MLP matrices with the adapter block appended as 64 extra K columns: [2d, d + 64] = W1 | W1*U | 0 and
+    // [d, 2d + 64] = W2 | U | 0 (U = effective adapter up weights); w1u is the fp32 [2d, 16] product W1*U
+    void* w1cat_bf16 = nullptr;
+    void* w2cat_bf16 = nullptr;
+    float* w1u = nullptr;
     void* vsplit_bf16 = nullptr;  // bank values transposed, three bf16 pieces [d, 3*cap] (tensor-core value read)
     bool bf16_dirty = true;
     bool vsplit_dirty = true;
@@ -44,6 +47,7 @@ struct Workspace {
     float *feat_a = nullptr, *feat_b = nullptr, *x_norm = nullptr, *proj = nullptr, *y = nullptr, *weights = nullptr,
           *m_val = nullptr, *m_proj = nullptr, *z = nullptr, *mlp_act = nullptr, *last_feat = nullptr, *logits = nullptr;
     void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr;
+    // z_bf16 is [rows, d + 64] and act_bf16 [rows, 2d + 64] when the adapter rides in the MLP products (rank 16)
     char* base = nullptr;
     size_t bytes = 0;
 };

@@ -37,8 +37,8 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_proj = c.take(rows * m->ncat * f), o_y = c.take(rows * d * f), o_w = c.take(rows * m->cap * f),
            o_mv = c.take(rows * d * f), o_mp = c.take(rows * d * f), o_z = c.take(rows * d * f),
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
-    size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * d * 2),
-           o_ab = c.take(rows * 2 * d * 2), o_wsp = c.take(rows * 3 * m->cap * 2);
+    size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * (d + 64) * 2),
+           o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2);
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -92,8 +92,10 @@ int32_t refresh_bf16(pssa_b200_model* m) {
             if ((rc = launch_to_bf16(ctx, b.w[p.id], cat + p.row_off * d * 2, p.rows * d))) return rc;
         if ((rc = launch_to_bf16(ctx, b.w[T_W_QH], b.wqh_bf16, m->k * d))) return rc;
         if ((rc = launch_to_bf16(ctx, b.w[T_W_PROJ], b.wproj_bf16, d * d))) return rc;
-        if ((rc = launch_to_bf16(ctx, b.w[T_MLP_W1], b.w1_bf16, 2 * d * d))) return rc;
-        if ((rc = launch_to_bf16(ctx, b.w[T_MLP_W2], b.w2_bf16, 2 * d * d))) return rc;
+        // MLP matrices with the adapter block appended (rank 16): W1 | W1*U | 0 and W2 | U | 0
+        if ((rc = launch_times_adapter(ctx, b.w[T_MLP_W1], b.u_eff, b.w1u, 2 * d, (int)d))) return rc;
+        if ((rc = launch_pack_weight_cat(ctx, b.w[T_MLP_W1], b.w1u, b.w1cat_bf16, 2 * d, (int)d))) return rc;
+        if ((rc = launch_pack_weight_cat(ctx, b.w[T_MLP_W2], b.u_eff, b.w2cat_bf16, d, (int)(2 * d)))) return rc;
         b.bf16_dirty = false;
     }
     for (auto& b : m->blocks) {
@@ -250,23 +252,31 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         rp.f32_distance = !exact;  // the bf16 mode's queries carry bf16 rounding already; f64 distances buy nothing there
         if (!exact && m->cap % 64 == 0) rp.w_split = ws.w_split, rp.v_split = b.vsplit_bf16;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
-        if ((rc = dense(m, ws.m_val, ws.m_bf16, b.w[T_W_PROJ], b.wproj_bf16, ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
-        if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z,
-                                      exact ? nullptr : ws.z_bf16, rows, d, (int)m->rank, ssm_scale, !exact)))
-            return rc;
-        // the tensor-core path needs the MLP activations only as the next GEMM's bf16 operand
-        if ((rc = dense(m, ws.z, ws.z_bf16, b.w[T_MLP_W1], b.w1_bf16, exact ? ws.mlp_act : nullptr, rows, 2 * m->d, m->d, 2 * m->d,
-                        EPI_SILU, 1.0f, exact ? nullptr : ws.act_bf16)))
-            return rc;
-        // MLP down projection + residual, then depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
         const float rscale = l == 0 ? 1.0f : m->residual_scales[l - 1];
         if (exact) {
+            if ((rc = launch_gemm_exact(ctx, ws.m_val, b.w[T_W_PROJ], ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
+            if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z, nullptr,
+                                          rows, d, (int)m->rank, ssm_scale, false)))
+                return rc;
+            if ((rc = launch_gemm_exact(ctx, ws.z, b.w[T_MLP_W1], ws.mlp_act, rows, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f))) return rc;
+            // MLP down projection + residual, then depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
             if ((rc = launch_gemm_exact(ctx, ws.mlp_act, b.w[T_MLP_W2], ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
             if ((rc = launch_residual(ctx, l == 0 ? nullptr : feat_in, ws.z, feat_out, rows * (size_t)d, rscale))) return rc;
         } else {
-            if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2_bf16, feat_out, ws.z, l == 0 ? nullptr : feat_in, rscale, rows,
-                                                m->d, 2 * m->d)))
+            // Tensor-core schedule: z = y/sqrt(s) + g*(W_proj m) + U*act never exists as one array. The memory projection's
+            // epilogue forms zp = g*acc + y/sqrt(s) (fp32 for the residual, bf16 as W1's operand); the rank-16 adapter
+            // term is one extra K block of both MLP products: W1*(zp + U act) = [W1 | W1 U] [zp; act] and
+            // W2*h + U*act = [W2 | U] [h; act]. The combine kernel and the m_proj round trip disappear.
+            const size_t ldz = m->d + 64, lda = 2 * m->d + 64;
+            if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, ws.z, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale, rows,
+                                            m->d, m->d)))
+                return rc;
+            if ((rc = launch_pack_act(ctx, ws.proj + m->off_act, nc, ws.z_bf16, ldz, (int)m->d, ws.act_bf16, lda, (int)(2 * m->d), rows))) return rc;
+            if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, b.w1cat_bf16, nullptr, ws.act_bf16, rows, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
+                return rc;
+            if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2cat_bf16, feat_out, ws.z, l == 0 ? nullptr : feat_in, rscale, rows, m->d,
+                                                lda)))
                 return rc;
         }
         if (observe && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, ws.weights, (int)m->cap, m->obs.q_pnc, k, ws.m_val,
