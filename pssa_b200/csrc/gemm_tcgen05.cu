@@ -34,10 +34,9 @@ constexpr int BK = 64;       // bf16 per stage row = 128 bytes = one swizzle ato
 constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit operands
 constexpr int EPI_WARPS = 8;  // two warps per TMEM lane quadrant, each draining half of the tile's columns
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
-// ring depth: as many 64-wide K blocks in flight as shared memory allows
-__host__ __device__ constexpr int stages_for(int bn) { return bn >= 256 ? 3 : (bn >= 128 ? 5 : 7); }
 constexpr unsigned kSpinLimit = 1u << 24;
-constexpr int STG_PITCH = 36;  // floats per staged row: 32 + 4 keeps float4 rows 16-byte aligned and bank-spread
+constexpr int STG_PITCH = 32;  // floats per staged row; 16-byte column quads are XOR-swizzled with the row (no padding, so four
+                               // 48 KB operand stages fit beside the staging tiles of a 128 x 256 product)
 
 struct GemmEpilogue {
     float* out;            // fp32 [M, ldo] or null
@@ -170,11 +169,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Persistent kernel: CTA c processes tiles c, c + gridDim.x, ... ; tile index -> (m, n) with n fastest, so the
 // CTAs running at the same time share A row blocks through L2 and A is read from HBM once. Two TMEM accumulators
 // let the epilogue of tile i run while the tensor cores work on tile i + 1.
-template <int BN>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_b,
                                                                             GemmEpilogue e) {
-    constexpr int STAGES = stages_for(BN);
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
     constexpr uint32_t TMEM_COLS = 2 * BN;  // 128, 256 or 512: a power of two >= 32
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -362,16 +360,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 // (8 lanes per output row) instead of 32 scattered 16-byte pieces per instruction
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4*>(stg + lane * STG_PITCH + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    *reinterpret_cast<float4*>(stg + lane * STG_PITCH + (((j >> 2) ^ (lane & 7)) << 2)) =
+                        make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 __syncwarp();
                 const int gcol = col0 + cq;
                 if (interior && kind != -1 && (!e.out || vec32) && (!e.out16 || vec16) && (!two_in || vec_res)) {
                     float* gp = e.out ? e.out + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
                     __nv_bfloat16* bp = e.out16 ? e.out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
-                    const float* sp = stg + rsub * STG_PITCH + cq;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        float4 val = *reinterpret_cast<const float4*>(sp + i * 4 * STG_PITCH);
+                        const int sr = i * 4 + rsub;  // staged row; its column quads are swizzled with (row & 7)
+                        float4 val = *reinterpret_cast<const float4*>(stg + sr * STG_PITCH + ((((cq >> 2) ^ (sr & 7))) << 2));
                         if (gp) {
                             float4* g4 = reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo);
                             if (e.epi == EPI_ADD_OUT) {
@@ -405,7 +404,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         const int r = i * 4 + rsub;
                         const int grow = rbase + r;
                         if (grow >= e.M || gcol >= e.N) continue;
-                        float4 val = *reinterpret_cast<const float4*>(stg + r * STG_PITCH + cq);
+                        float4 val = *reinterpret_cast<const float4*>(stg + r * STG_PITCH + (((cq >> 2) ^ (r & 7)) << 2));
                         float o[4] = {val.x, val.y, val.z, val.w};
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -478,15 +477,14 @@ int32_t make_map(pssa_b200_ctx* ctx, CUtensorMap* map, const void* base, size_t 
     return PSSA_B200_OK;
 }
 
-template <int BN>
+template <int BN, int STAGES>
 int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const GemmEpilogue& e) {
     CUtensorMap map_a, map_b;
     int32_t rc;
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
-    constexpr int STAGES = stages_for(BN);
     size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EPI_WARPS * 32 * STG_PITCH * 4;
-    auto kern = gemm_bf16_tcgen05_kernel<BN>;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES>;
     static bool attr = false;
     if (!attr) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -524,9 +522,13 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // widest tile that still gives every SM work: 256 columns halve the shared-memory operand traffic per flop,
     // narrow outputs (state / key projections) and short batches (decode) use smaller tiles to spread over SMs
     const long long m_tiles = (e.M + BM - 1) / BM;
-    if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2) return launch_tile<64>(ctx, a, b, e);
-    if (e.N <= 128 || m_tiles * ((e.N + 255) / 256) < ctx->sm_count) return launch_tile<128>(ctx, a, b, e);
-    return launch_tile<256>(ctx, a, b, e);
+    if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2) return launch_tile<64, 7>(ctx, a, b, e);
+    if (e.N <= 128 || m_tiles * ((e.N + 255) / 256) < ctx->sm_count) return launch_tile<128, 5>(ctx, a, b, e);
+    // Four 48 KB stages help the long-K split product (141 -> 126 us at the model's shape, +8 % on plain products timed
+    // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
+    // (their epilogue traffic is the limiter), so those keep three.
+    if (e.n_pairs > 0) return launch_tile<256, 4>(ctx, a, b, e);
+    return launch_tile<256, 3>(ctx, a, b, e);
 }
 
 }  // namespace
