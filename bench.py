@@ -311,15 +311,25 @@ def run_extras(gpu, torch, peak_hbm):
     q = qd / qd.norm(dim=1, keepdim=True) * torch.rand(rows, 1, device="cuda", generator=g) * 0.9
     w = torch.zeros(rows, cap, device="cuda")
     m = torch.zeros(rows, dv, device="cuda")
-    for name, top_k in (("top8", 8), ("all_slots", 0)):
+    ref_sel = None
+    for name, top_k, f32d in (("top8", 8, False), ("all_slots", 0, False), ("top8_f32_distance", 8, True),
+                              ("all_slots_f32_distance", 0, True)):
         ms = timed(lambda: gpu.memory_read_dev(q, keys, norm_sq, vals, rows, dk, dv, cap, cap, 0.1, m, top_k=top_k, weights=w,
-                                               q_is_euclidean=False), 5, warm=2)
+                                               q_is_euclidean=False, f32_distance=f32d), 5, warm=2)
         byts = rows * (dk * 4 + dv * 4 + (64 if top_k else cap * 4))
-        extra[f"retrieval_c3_{name}"] = {"workload": "Poincare retrieval, 512 slots, key/value dim 128, 262144 queries, tau 0.1",
-                                         "ms": ms, "queries_per_s": rows / (ms / 1e3),
-                                         "roofline": {"bound": "hbm", "achieved": byts / (ms / 1e3) / 1e9, "peak": peak_hbm,
-                                                      "unit": "GB/s", "frac": byts / (ms / 1e3) / 1e9 / peak_hbm,
-                                                      "limiter": "fp64 distance arithmetic"}}
+        row = {"workload": "Poincare retrieval, 512 slots, key/value dim 128, 262144 queries, tau 0.1"
+                           + (", distances accumulated in fp32 (differences first)" if f32d else ", distances in f64 like the reference"),
+               "ms": ms, "queries_per_s": rows / (ms / 1e3),
+               "roofline": {"bound": "hbm", "achieved": byts / (ms / 1e3) / 1e9, "peak": peak_hbm, "unit": "GB/s",
+                            "frac": byts / (ms / 1e3) / 1e9 / peak_hbm,
+                            "limiter": "FP32 FMA pipe (2 ops per key dimension per slot)" if f32d else "fp64 distance arithmetic"}}
+        if top_k:
+            sel = w != 0  # the selected slot sets of every query
+            if not f32d:
+                ref_sel = sel.clone()
+            elif ref_sel is not None:
+                row["queries_with_the_f64_slot_set"] = float((sel == ref_sel).all(dim=1).float().mean().item())
+        extra[f"retrieval_c3_{name}"] = row
     return extra
 
 

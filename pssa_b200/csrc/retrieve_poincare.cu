@@ -563,7 +563,7 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     }
     const int kpad4 = (p.dk + 3) / 4 * 4;
     const size_t smem_f = (size_t)(kpad4 / 2) * QT * sizeof(float2) + ((size_t)2 * STL * (kpad4 + 4) + QT + 2 * STL) * sizeof(float);
-    if (p.f32_distance && !exact && smem_f <= 72 * 1024) {  // wider keys keep the f64 kernel
+    if (p.f32_distance && !exact && smem_f <= 112 * 1024) {  // keys wider than 128 keep the f64 kernel
         static bool attr_f = false;
         if (smem_f > 48 * 1024 && !attr_f) {
             PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
