@@ -355,6 +355,8 @@ __device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v)
     return v;
 }
 
+constexpr int kTopkRegs = 16;  // distances per lane the register path of the top-k selection holds (capacity <= 512)
+
 template <bool EXACT>
 __device__ __forceinline__ float weight_of(float min_dist, float d, float tau) {
     // memory.rs:396-398 / 411-414: exp((min - d) / tau), subtraction before division
@@ -392,6 +394,76 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
     __syncwarp();
     const float tau = p.tau;
     const int k = p.top_k;
+    if (k != 0 && k < count && k <= 32 && count <= 32 * kTopkRegs && cap >= 64) {
+        // Register path of the selection below (same results): each lane keeps its count/32 distances in registers, a
+        // round is a local minimum plus one warp-wide minimum of (distance bits, slot); the k winners are then ranked by
+        // slot so that the sum, the weights and the value read walk them in ascending slot order (memory.rs:380-408)
+        // without touching the other count - k slots.
+        unsigned bits[kTopkRegs];
+#pragma unroll
+        for (int j = 0; j < kTopkRegs; ++j) {
+            const int i = lane + 32 * j;
+            bits[j] = i < count ? __float_as_uint(w[i]) : 0xffffffffu;  // distances are >= +0: their bits order them
+        }
+        unsigned my_slot = 0xffffffffu;  // lane r holds the r-th nearest slot
+        float my_dist = 0.0f;
+        for (int r = 0; r < k; ++r) {
+            unsigned best = 0xffffffffu;
+            int best_j = 0;
+#pragma unroll
+            for (int j = 0; j < kTopkRegs; ++j)
+                if (bits[j] < best) best = bits[j], best_j = j;  // strict: ties keep the lower slot of this lane
+            unsigned long long key = ((unsigned long long)best << 32) | (unsigned)(lane + 32 * best_j);
+            key = warp_min_u64(key);
+            const unsigned slot = (unsigned)(key & 0xffffffffu);
+            if ((int)(slot & 31) == lane) {
+#pragma unroll
+                for (int j = 0; j < kTopkRegs; ++j)
+                    if (j == (int)(slot >> 5)) bits[j] = 0xffffffffu;  // taken
+            }
+            if (lane == r) my_slot = slot, my_dist = __uint_as_float((unsigned)(key >> 32));
+        }
+        // rank of this lane's slot among the selected ones = its position in ascending slot order
+        int rank = 0;
+        for (int j = 0; j < k; ++j) rank += __shfl_sync(0xffffffffu, my_slot, j) < my_slot ? 1 : 0;
+        const float my_w = lane < k ? weight_of<EXACT>(mn, my_dist, tau) : 0.0f;
+        __syncwarp();  // every lane has read its distances out of w: the row is reused for the compacted list
+        unsigned* sel_slot = reinterpret_cast<unsigned*>(w);
+        float* sel_w = w + 32;
+        if (lane < k) sel_slot[rank] = my_slot, sel_w[rank] = my_w;
+        __syncwarp();
+        float sum = 0.0f;
+        for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, sel_w[j]);  // ascending slot order, like the reference's sum
+        for (int i = lane; i < cap; i += 32) row[i] = 0.0f;          // out_weights.fill(0.0)
+        __syncwarp();
+        if (lane < k) {
+            const float wn = __fdiv_rn(my_w, sum);
+            row[my_slot] = wn;
+            sel_w[rank] = wn;
+        }
+        __syncwarp();
+        for (int j0 = lane; j0 < dv; j0 += 32 * 4) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < k; ++j) {
+                const float wi = sel_w[j];
+                const float* v = p.values + (size_t)sel_slot[j] * dv;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c = j0 + e * 32;
+                    if (c < dv) acc[e] = __fadd_rn(acc[e], __fmul_rn(wi, __ldg(v + c)));
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int c = j0 + e * 32;
+                if (c < dv) {
+                    if (p.m_val) p.m_val[q * dv + c] = acc[e];
+                    if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + c] = __float2bfloat16_rn(acc[e]);
+                }
+            }
+        }
+        return;
+    }
     if (k != 0 && k < count) {
         // memory.rs:380-408: keep the k smallest (distance bits, slot); weights over those only, slot order
         // selected slots are marked by setting the sign bit of their distance in shared memory
