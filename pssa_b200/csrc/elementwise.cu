@@ -104,63 +104,6 @@ __global__ void __launch_bounds__(256) combine_zraw_kernel(const float* __restri
     }
 }
 
-// Tensor-core mode of the same stage (fused multiply-adds allowed): a thread owns two consecutive channels and their
-// 2 x 16 effective adapter weights in registers and walks kFastRows rows four at a time, all loads of a group issued
-// before any arithmetic; the rows' adapter activations sit in shared memory and are read as broadcasts. A third of the
-// instructions of the exact kernel and enough loads in flight to leave the stage bound by its 18 bytes per element.
-constexpr int kFastRows = 32;
-__global__ void __launch_bounds__(384, 2) combine_zraw_fast_kernel(const float* __restrict__ y, const float* __restrict__ g,
-                                                                   size_t ldg, const float* __restrict__ m_proj,
-                                                                   const float* __restrict__ act, size_t ldact,
-                                                                   const float* __restrict__ u_eff, float* __restrict__ z_raw,
-                                                                   __nv_bfloat16* __restrict__ z_bf16, size_t rows, int d,
-                                                                   float ssm_scale, int rows_per_cta) {
-    __shared__ __align__(16) float s_act[kFastRows][16];
-    const size_t row0 = (size_t)blockIdx.y * rows_per_cta;
-    const int nrows = (int)min((size_t)rows_per_cta, rows - row0);
-    for (int idx = threadIdx.x; idx < rows_per_cta * 4; idx += blockDim.x) {
-        const int r = idx >> 2, q = idx & 3;
-        const size_t row = min(row0 + r, rows - 1);
-        *reinterpret_cast<float4*>(&s_act[r][q * 4]) = *reinterpret_cast<const float4*>(act + row * ldact + q * 4);
-    }
-    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
-    float4 u[2][4];  // [channel][rank quad]
-    if (i < d) {
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) u[c][q] = __ldg(reinterpret_cast<const float4*>(u_eff + (size_t)(i + c) * 16) + q);
-    }
-    __syncthreads();
-    if (i >= d) return;
-    for (int r0 = 0; r0 < nrows; r0 += 4) {
-        float2 yv[4], gv[4], mv[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const size_t row = min(row0 + r0 + k, rows - 1);  // clamped for the loads; stores are predicated
-            yv[k] = *reinterpret_cast<const float2*>(y + row * d + i);
-            gv[k] = *reinterpret_cast<const float2*>(g + row * ldg + i);
-            mv[k] = *reinterpret_cast<const float2*>(m_proj + row * d + i);
-        }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            float z[2] = {fmaf(gv[k].x, mv[k].x, yv[k].x * ssm_scale), fmaf(gv[k].y, mv[k].y, yv[k].y * ssm_scale)};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const float4 a = *reinterpret_cast<const float4*>(&s_act[r0 + k][q * 4]);
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    z[c] = fmaf(u[c][q].x, a.x, fmaf(u[c][q].y, a.y, fmaf(u[c][q].z, a.z, fmaf(u[c][q].w, a.w, z[c]))));
-            }
-            if (r0 + k < nrows) {
-                const size_t o = (row0 + r0 + k) * d + i;
-                *reinterpret_cast<float2*>(z_raw + o) = make_float2(z[0], z[1]);
-                if (z_bf16) *reinterpret_cast<__nv_bfloat162*>(z_bf16 + o) = __floats2bfloat162_rn(z[0], z[1]);
-            }
-        }
-    }
-}
-
 // src/pssa.rs:2332-2337: features += scale * block_out  (prev == nullptr: features = z, block 0)
 __global__ void __launch_bounds__(256) residual_kernel(const float* __restrict__ prev, const float* __restrict__ z,
                                                        float* __restrict__ out, size_t n, float scale) {
@@ -355,18 +298,7 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
 
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
-                            float ssm_scale, bool fast) {
-    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    if (fast && rank == 16 && d % 4 == 0 && ldg % 4 == 0 && ldact % 4 == 0 && al16(y) && al16(g) && al16(m_proj) && al16(act) &&
-        al16(u_eff) && al16(z_raw) && (reinterpret_cast<uintptr_t>(z_bf16) & 7) == 0 && (rows + kFastRows - 1) / kFastRows <= 65535) {
-        const int threads = d / 2 >= 384 ? 384 : ((d / 2 + 31) / 32 * 32);
-        // short batches (decode steps) take 4 rows per CTA so the launch still covers the machine
-        const int rpc = rows >= (size_t)kFastRows * 296 ? kFastRows : 4;
-        dim3 grid((unsigned)((d / 2 + threads - 1) / threads), (unsigned)((rows + rpc - 1) / rpc));
-        combine_zraw_fast_kernel<<<grid, threads, 0, ctx->stream>>>(y, g, ldg, m_proj, act, ldact, u_eff, z_raw,
-                                                                    (__nv_bfloat16*)z_bf16, rows, d, ssm_scale, rpc);
-        return after_launch(ctx, "combine_zraw_fast_kernel");
-    }
+                            float ssm_scale) {
     dim3 grid((unsigned)((d + 255) / 256), (unsigned)((rows + kCombineRows - 1) / kCombineRows));
     if (grid.y > 65535) {
         // very long passes: fall back to several launches of at most 65535 row groups
@@ -374,7 +306,7 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
         for (size_t r0 = 0; r0 < rows; r0 += step) {
             size_t n = rows - r0 < step ? rows - r0 : step;
             int32_t rc = launch_combine_zraw(ctx, y + r0 * d, g + r0 * ldg, ldg, m_proj + r0 * d, act + r0 * ldact, ldact, u_eff,
-                                             z_raw + r0 * d, z_bf16 ? (char*)z_bf16 + r0 * d * 2 : nullptr, n, d, rank, ssm_scale, fast);
+                                             z_raw + r0 * d, z_bf16 ? (char*)z_bf16 + r0 * d * 2 : nullptr, n, d, rank, ssm_scale);
             if (rc) return rc;
         }
         return PSSA_B200_OK;

@@ -161,7 +161,7 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
                           const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact);
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
-                            float ssm_scale, bool fast = false);
+                            float ssm_scale);
 int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale);
 int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d);
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n);

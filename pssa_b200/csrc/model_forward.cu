@@ -257,7 +257,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         if (exact) {
             if ((rc = launch_gemm_exact(ctx, ws.m_val, b.w[T_W_PROJ], ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
             if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z, nullptr,
-                                          rows, d, (int)m->rank, ssm_scale, false)))
+                                          rows, d, (int)m->rank, ssm_scale)))
                 return rc;
             if ((rc = launch_gemm_exact(ctx, ws.z, b.w[T_MLP_W1], ws.mlp_act, rows, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f))) return rc;
             // MLP down projection + residual, then depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
