@@ -215,6 +215,20 @@ def run_decode_extra(model, gpu, torch, peak_hbm):
         ids = model.decode_step(ids, want_logits=False, want_greedy=True)
     torch.cuda.synchronize()
     sec = (time.perf_counter() - t0) / steps
+    # the same step captured as a CUDA graph, ids fed back on the device: no host round trip per token
+    ids_dev = torch.tensor(ids.astype(np.int32), device="cuda", dtype=torch.int32)
+    graph = model.capture_greedy_decode_graph(ids_dev)
+    for _ in range(warm):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    graph_sec = e0.elapsed_time(e1) / 1e3 / steps
+    gpu.poll_status()
     d, s = CFG["d_latent"], CFG["d_state"]
     state_bytes = streams * CFG["depth"] * d * s * 4 * 2  # every carry read and written once per step
     v, k = CFG["d_vocab"], CFG["d_mem_key"]
@@ -222,6 +236,8 @@ def run_decode_extra(model, gpu, torch, peak_hbm):
     weight_bytes = weight_elems * 2
     return {"workload": "greedy decode, 256 streams x 1 token per step, 12-block model, ids to host every step",
             "ms_per_step": sec * 1e3, "tokens_per_s": streams / sec, "steps": steps,
+            "cuda_graph": {"ms_per_step": graph_sec * 1e3, "tokens_per_s": streams / graph_sec,
+                           "note": "one captured greedy step replayed; ids stay on the device (CUDA events)"},
             "roofline": {"bound": "hbm", "achieved": (state_bytes + weight_bytes) / sec / 1e9, "peak": peak_hbm, "unit": "GB/s",
                          "frac": (state_bytes + weight_bytes) / sec / 1e9 / peak_hbm,
                          "note": "algorithmic bytes = recurrent state in and out + bf16 weights once; the step is 136 "

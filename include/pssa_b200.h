@@ -65,7 +65,9 @@ uint64_t pssa_b200_launch_count(const pssa_b200_ctx* ctx);
 int32_t pssa_b200_ctx_reserve(pssa_b200_ctx* ctx, size_t bytes);
 
 /* Device-side waits (mbarrier phases of the tensor-core pipeline) are bounded; when one expires the kernel
- * records it and returns. This reads and clears that record: PSSA_B200_OK or PSSA_B200_ERR_TIMEOUT. */
+ * records it and returns. This reads and clears that record: PSSA_B200_OK or PSSA_B200_ERR_TIMEOUT. The same word
+ * carries PSSA_B200_ERR_TOKEN when a DEVICE-resident token id (which the host cannot check) was outside the vocabulary:
+ * the embedding of id 0 was read in its place, so nothing is accessed out of bounds. */
 int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx);
 
 /*

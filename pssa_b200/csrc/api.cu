@@ -617,6 +617,8 @@ int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx) {
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (status != 0) {
         PSSA_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
+        if (status == PSSA_B200_ERR_TOKEN)
+            return fail(ctx, status, "a device-resident token ID was outside the model vocabulary (row 0 was read in its place)");
         return fail(ctx, status, "a bounded device-side wait expired (status %d)", status);
     }
     return PSSA_B200_OK;

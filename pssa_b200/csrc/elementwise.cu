@@ -19,12 +19,18 @@ template <bool EXACT>
 __global__ void __launch_bounds__(256) embed_norm_kernel(const float* __restrict__ embed, const uint32_t* __restrict__ ids,
                                                          const float* __restrict__ feats, const float* __restrict__ gamma,
                                                          const float* __restrict__ beta, float* __restrict__ x_norm,
-                                                         __nv_bfloat16* __restrict__ x_bf16, size_t rows, int d) {
+                                                         __nv_bfloat16* __restrict__ x_bf16, size_t rows, int d, uint32_t vocab,
+                                                         int* __restrict__ status) {
     extern __shared__ float sm[];  // [8 warps][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t row = (size_t)blockIdx.x * 8 + warp;
     if (row >= rows) return;
-    const float* src = ids ? embed + (size_t)ids[row] * d : feats + row * d;
+    uint32_t id = ids ? ids[row] : 0;
+    if (id >= vocab) {  // device-resident ids cannot be checked on the host: read row 0 and raise the status word
+        if (lane == 0 && status) atomicExch(status, PSSA_B200_ERR_TOKEN);
+        id = 0;
+    }
+    const float* src = ids ? embed + (size_t)id * d : feats + row * d;
     float* buf = sm + (size_t)warp * d;
     float part = 0.0f;
     for (int i = lane; i < d; i += 32) {
@@ -276,7 +282,7 @@ inline unsigned blocks_for(size_t n, int threads) { return (unsigned)((n + threa
 }  // namespace
 
 int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t* ids, const float* feats, const float* gamma,
-                          const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact) {
+                          const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact, size_t vocab) {
     size_t smem = (size_t)8 * d * sizeof(float);
     if (smem > 200 * 1024)
         return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 norm: latent width %d exceeds one CTA's shared memory; refusing launch", d);
@@ -290,9 +296,11 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
     }
     unsigned blocks = blocks_for(rows, 8);
     if (exact)
-        embed_norm_kernel<true><<<blocks, 256, smem, ctx->stream>>>(embed, ids, feats, gamma, beta, x_norm, (__nv_bfloat16*)x_bf16, rows, d);
+        embed_norm_kernel<true><<<blocks, 256, smem, ctx->stream>>>(embed, ids, feats, gamma, beta, x_norm, (__nv_bfloat16*)x_bf16, rows, d,
+                                                                   (uint32_t)vocab, ctx->status_dev);
     else
-        embed_norm_kernel<false><<<blocks, 256, smem, ctx->stream>>>(embed, ids, feats, gamma, beta, x_norm, (__nv_bfloat16*)x_bf16, rows, d);
+        embed_norm_kernel<false><<<blocks, 256, smem, ctx->stream>>>(embed, ids, feats, gamma, beta, x_norm, (__nv_bfloat16*)x_bf16, rows, d,
+                                                                    (uint32_t)vocab, ctx->status_dev);
     return after_launch(ctx, "embed_norm_kernel");
 }
 

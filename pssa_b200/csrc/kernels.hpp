@@ -158,7 +158,7 @@ int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w1
 
 // elementwise.cu
 int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t* ids, const float* feats, const float* gamma,
-                          const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact);
+                          const float* beta, float* x_norm, void* x_bf16, size_t rows, int d, bool exact, size_t vocab);
 int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, size_t ldg, const float* m_proj, const float* act,
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
                             float ssm_scale);

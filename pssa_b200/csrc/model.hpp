@@ -82,6 +82,11 @@ struct pssa_b200_model {
         void* arg = nullptr;
         bool active = false;        // set for the duration of a sharded prefill call only (decode steps stay local)
     } sp;
+    // lane description last uploaded by the device-resident entry point (skipped when unchanged: graph capture)
+    struct DevLayout {
+        const char* ws_base = nullptr;
+        std::vector<uint32_t> off, len, slot;
+    } dev_layout;
     // scorer buffers: a tile of full-vocabulary logits, targets and per-row losses
     struct Score {
         float* logits = nullptr;   // [tile][vocab]

@@ -189,7 +189,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         DeviceBlock& b = m->blocks[l];
         // stage 1: gather + RMSNorm (src/gpu_batch.rs:445-472)
         if ((rc = launch_embed_norm(ctx, m->embed, l == 0 ? ws.ids : nullptr, feat_in, b.w[T_NORM_GAMMA], b.w[T_NORM_BETA],
-                                    ws.x_norm, exact ? nullptr : ws.x_bf16, rows, d, exact)))
+                                    ws.x_norm, exact ? nullptr : ws.x_bf16, rows, d, exact, m->v)))
             return rc;
         // stage 2: x-side projections (src/gpu_batch.rs:477-536 plus the query/gate/adapter rows that read x_norm)
         if (exact) {
@@ -378,6 +378,7 @@ int32_t run_lanes(pssa_b200_model* m, const uint64_t* ids, const uint32_t* offse
         if ((rc = ensure_workspace(m, rows, n_lanes))) return rc;
         Workspace& ws = m->ws;
         cudaStream_t st = ctx->stream;
+        m->dev_layout.ws_base = nullptr;  // the cached layout of the device-resident entry no longer holds
         PSSA_CUDA(ctx, cudaMemcpyAsync(ws.ids, h_ids.data(), rows * 4, cudaMemcpyHostToDevice, st));
         PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, h_off.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
         PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_len, h_len.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
@@ -503,10 +504,17 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
     Workspace& ws = m->ws;
     cudaStream_t st = ctx->stream;
     PSSA_CUDA(ctx, cudaMemcpyAsync(ws.ids, ids_dev, span * 4, cudaMemcpyDeviceToDevice, st));
-    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, h_off.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
-    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_len, h_len.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
-    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, h_slot.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
-    PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
+    // The lane description is uploaded only when it differs from what the workspace already holds. A repeated call with
+    // the same layout (a decode loop) then consists of kernel launches and device-to-device copies only, so the caller can
+    // capture it in a CUDA graph on the context's stream.
+    auto& lay = m->dev_layout;
+    if (lay.ws_base != ws.base || lay.off != h_off || lay.len != h_len || lay.slot != h_slot) {
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, h_off.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_len, h_len.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_slot, h_slot.data(), n_lanes * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(ws.last_rows, h_last.data(), h_last.size() * 4, cudaMemcpyHostToDevice, st));
+        lay.ws_base = ws.base, lay.off = h_off, lay.len = h_len, lay.slot = h_slot;
+    }
     float* feats = nullptr;
     m->sp.active = m->sp.world > 1;
     rc = forward_rows(m, span, n_lanes, h_off.data(), h_len.data(), &feats, h_last.size());
@@ -566,6 +574,7 @@ int32_t pssa_b200_model_score(pssa_b200_model* m, uint32_t stream, const uint64_
         if ((rc = ensure_workspace(m, rows, 1))) return rc;
         Workspace& ws = m->ws;
         const uint32_t off = 0, len = (uint32_t)rows, slot = stream;
+        m->dev_layout.ws_base = nullptr;
         PSSA_CUDA(ctx, cudaMemcpyAsync(ws.ids, h_ids.data(), rows * 4, cudaMemcpyHostToDevice, st));
         PSSA_CUDA(ctx, cudaMemcpyAsync(sc.targets, h_tgt.data(), rows * 4, cudaMemcpyHostToDevice, st));
         PSSA_CUDA(ctx, cudaMemcpyAsync(ws.lane_off, &off, 4, cudaMemcpyHostToDevice, st));

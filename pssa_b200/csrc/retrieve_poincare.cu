@@ -29,28 +29,62 @@ namespace {
 
 constexpr int QT = 64;   // queries per CTA in kernel A
 constexpr int STL = 64;  // slots per pass
-constexpr int KC = 32;   // key dimensions per shared-memory chunk
 
 // ------------------------------------------------------------------ A: projection + distances
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
+}
+
+// Shared memory: P as f64 [dimension][query] (a thread's four queries are two 16-byte reads, broadcast over the slot
+// threads); key tiles stay fp32, row-major [slot][kpad + 4], in two buffers filled by cp.async one pass ahead and are
+// widened to f64 as they are read (exact). A thread owns queries tq*4 + a and slots ts + 16*b.
 __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int kpad = (p.dk + KC - 1) / KC * KC;
-    double* Ps = reinterpret_cast<double*>(smem_raw);  // [kpad][QT]
-    double* Ks = Ps + (size_t)kpad * QT;               // [KC][STL]
-    float* qsq = reinterpret_cast<float*>(Ks + KC * STL);  // [QT]
+    const int kpad = (p.dk + 3) / 4 * 4;
+    const int kpitch = kpad + 4;
+    double* Ps = reinterpret_cast<double*>(smem_raw);               // [kpad][QT]
+    float* Ks = reinterpret_cast<float*>(Ps + (size_t)kpad * QT);   // [2][STL][kpitch]
+    float* qsq = Ks + 2 * (size_t)STL * kpitch;                     // [QT]
 
     const int tid = threadIdx.x;
     const size_t q0 = (size_t)blockIdx.x * QT;
-    const int dk = p.dk;
+    const int dk = p.dk, count = p.count;
+    const bool vec_in = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(p.keys) & 15) == 0;
+
+    auto load_keys = [&](int pass, int buf) {
+        const int s0 = pass * STL;
+        if (s0 < count) {
+            float* dst = Ks + (size_t)buf * STL * kpitch;
+            if (vec_in) {
+                const int c4n = dk >> 2;
+                for (int idx = tid; idx < STL * c4n; idx += 256) {
+                    const int sl = idx / c4n, c4 = idx % c4n;
+                    if (s0 + sl < count)
+                        cp_async16(dst + sl * kpitch + c4 * 4, p.keys + (size_t)(s0 + sl) * dk + c4 * 4);
+                    else
+                        *reinterpret_cast<float4*>(dst + sl * kpitch + c4 * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            } else {
+                for (int idx = tid; idx < STL * kpad; idx += 256) {
+                    const int sl = idx / kpad, i = idx % kpad;
+                    dst[sl * kpitch + i] = (s0 + sl < count && i < dk) ? __ldg(p.keys + (size_t)(s0 + sl) * dk + i) : 0.0f;
+                }
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    load_keys(blockIdx.y, 0);
 
     // zero the padded rows of P
     for (int idx = tid; idx < (kpad - dk) * QT; idx += 256) Ps[(size_t)dk * QT + idx] = 0.0;
 
     if (tid < QT) {
         const size_t q = q0 + tid;
+        const bool publish = blockIdx.y == 0;  // the slot passes of one query tile may be spread over several CTAs
         if (q < p.rows) {
             const float* src = p.q + q * (p.ldq ? p.ldq : (size_t)dk);
-            float* dst = p.q_pnc ? p.q_pnc + q * dk : nullptr;
+            float* dst = (p.q_pnc && publish) ? p.q_pnc + q * dk : nullptr;
             float qs;
             if (p.q_is_euclidean) {
                 // memory.rs:198-211: r = sqrt(sum q^2) in f64, sequential; p = q * min(r/(1+r), R)/r
@@ -70,7 +104,7 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
                     Ps[(size_t)i * QT + tid] = pd;
                     n2 = __dadd_rn(n2, __dmul_rn(pd, pd));
                 }
-                if (p.q_norm) p.q_norm[q] = (float)fmin(r, (double)FLT_MAX);
+                if (p.q_norm && publish) p.q_norm[q] = (float)fmin(r, (double)FLT_MAX);
                 qs = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;  // memory.rs:181-188
             } else {
                 double n2 = 0.0;
@@ -89,41 +123,41 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
             qsq[tid] = 0.0f;
         }
     }
-    __syncthreads();
 
     const int ts = tid & 15, tq = tid >> 4;  // 16 slot threads x 16 query threads
-    const int count = p.count;
-    for (int s0 = 0; s0 < count; s0 += STL) {
+    const int npass = (count + STL - 1) / STL;
+    for (int pass = blockIdx.y, buf = 0; pass < npass; pass += gridDim.y, buf ^= 1) {
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();      // this tile (and, first time round, P) visible; everyone is done with the previous tile
+        load_keys(pass + gridDim.y, buf ^ 1);  // lands while this tile is consumed
+        const float* kt = Ks + (size_t)buf * STL * kpitch;
         double acc[4][4];
 #pragma unroll
         for (int a = 0; a < 4; ++a)
 #pragma unroll
             for (int b = 0; b < 4; ++b) acc[a][b] = 0.0;
-        for (int i0 = 0; i0 < kpad; i0 += KC) {
-            __syncthreads();  // previous chunk fully consumed
-            for (int idx = tid; idx < STL * KC; idx += 256) {
-                int sl = idx / KC, ii = idx % KC;
-                int slot = s0 + sl, i = i0 + ii;
-                float v = (slot < count && i < dk) ? __ldg(p.keys + (size_t)slot * dk + i) : 0.0f;
-                Ks[ii * STL + sl] = (double)v;
+        for (int i4 = 0; i4 < kpad / 4; ++i4) {
+            double kd[4][4];  // [slot b][dimension]
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float4 k = *reinterpret_cast<const float4*>(kt + (ts + 16 * b) * kpitch + i4 * 4);
+                kd[b][0] = (double)k.x, kd[b][1] = (double)k.y, kd[b][2] = (double)k.z, kd[b][3] = (double)k.w;
             }
-            __syncthreads();
-#pragma unroll 4
-            for (int ii = 0; ii < KC; ++ii) {
-                const double2* pp = reinterpret_cast<const double2*>(Ps + (size_t)(i0 + ii) * QT + tq * 4);
-                const double2* kp = reinterpret_cast<const double2*>(Ks + ii * STL + ts * 4);
-                double2 p01 = pp[0], p23 = pp[1], k01 = kp[0], k23 = kp[1];
-                double pv[4] = {p01.x, p01.y, p23.x, p23.y};
-                double kv[4] = {k01.x, k01.y, k23.x, k23.y};
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                const double2* pp = reinterpret_cast<const double2*>(Ps + (size_t)(i4 * 4 + h) * QT + tq * 4);
+                const double2 p01 = pp[0], p23 = pp[1];
+                const double pv[4] = {p01.x, p01.y, p23.x, p23.y};
 #pragma unroll
                 for (int a = 0; a < 4; ++a)
 #pragma unroll
                     for (int b = 0; b < 4; ++b) {
-                        double df = pv[a] - kv[b];
+                        const double df = pv[a] - kd[b][h];
                         acc[a][b] = fma(df, df, acc[a][b]);
                     }
             }
         }
+        const int s0 = pass * STL;
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
             const size_t q = q0 + tq * 4 + a;
@@ -131,7 +165,7 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
             const double one_minus_q = 1.0 - (double)qsq[tq * 4 + a];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                int slot = s0 + ts * 4 + b;
+                const int slot = s0 + ts + 16 * b;
                 if (slot < count) {
                     // memory.rs:245-262: 2*asinh(sqrt(sq/denom)); 2*asinh(z) = log1p(2u + 2*sqrt(u*u + u)), u = z^2
                     double denom = one_minus_q * (1.0 - (double)__ldg(p.norm_sq + slot));
@@ -142,6 +176,7 @@ __global__ void __launch_bounds__(256) poincare_distance_kernel(RetrieveParams p
             }
         }
     }
+    asm volatile("cp.async.wait_group 0;\n" ::);
 }
 
 // ------------------------------------------------------------------ A': fp32 distances (fast mode)
@@ -166,10 +201,6 @@ __device__ __forceinline__ float sum2(f32x2 v) {
     return lo + hi;
 }
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(gmem));
-}
 // 2*asinh(sqrt(u)) = log1p(z), z = 2u + 2*sqrt(u*u + u), with the hardware sqrt / log2 / reciprocal approximations:
 // log1p(z) = log(w) + (z - (w - 1))/w for w = fl(1 + z). lg2.approx is within 2^-22 absolute near one, 2^-22 relative
 // elsewhere, so the distance is good to about 2e-7 absolute near zero and 3e-7 relative beyond.
@@ -615,8 +646,8 @@ __global__ void __launch_bounds__(256) value_mix_kernel(RetrieveParams p) {
 }  // namespace
 
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact) {
-    const int kpad = (p.dk + KC - 1) / KC * KC;
-    size_t smem_a = ((size_t)kpad * QT + KC * STL) * sizeof(double) + QT * sizeof(float);
+    const int kpad = (p.dk + 3) / 4 * 4;
+    size_t smem_a = (size_t)kpad * QT * sizeof(double) + ((size_t)2 * STL * (kpad + 4) + QT) * sizeof(float);
     if (smem_a > 200 * 1024)
         return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 memory read: key width %d needs %zu bytes of shared memory; refusing launch",
                     p.dk, smem_a);
@@ -648,7 +679,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         poincare_distance_f32_kernel<<<dim3((unsigned)qblocks, ysplit), 256, smem_f, ctx->stream>>>(p);
         if ((rc = after_launch(ctx, "poincare_distance_f32_kernel")) != PSSA_B200_OK) return rc;
     } else {
-        poincare_distance_kernel<<<(unsigned)qblocks, 256, smem_a, ctx->stream>>>(p);
+        unsigned ysplit = 1;  // few query tiles (decode): spread the slot passes over up to 8 CTAs per tile
+        const unsigned npass = (unsigned)((p.count + STL - 1) / STL);
+        while (qblocks * ysplit < 148 && ysplit < 8 && ysplit * 2 <= (npass ? npass : 1)) ysplit *= 2;
+        poincare_distance_kernel<<<dim3((unsigned)qblocks, ysplit), 256, smem_a, ctx->stream>>>(p);
         if ((rc = after_launch(ctx, "poincare_distance_kernel")) != PSSA_B200_OK) return rc;
     }
     size_t wblocks = (p.rows + 7) / 8;

@@ -175,6 +175,35 @@ class PSSAModel:
         self.gpu._check(self._lib.pssa_b200_model_prefill_batch_dev(self._h, _ptr(ids_dev), _ptr(offsets), _ptr(lengths),
                                                                     _ptr(st), len(lengths), _ptr(logits_dev), _ptr(greedy_dev)))
 
+    def capture_greedy_decode_graph(self, ids_dev, streams=None):
+        """One greedy decode step for len(ids_dev) streams as a CUDA graph (torch.cuda.CUDAGraph).
+
+        `ids_dev` (int32 device tensor, one token per stream) is both the step's input and its output: every replay
+        feeds the ids of the previous one, so a generation loop is `graph.replay()` per token with no host round trip.
+        Works because the device-resident entry point only launches kernels and device-to-device copies once the lane
+        layout is on the device. The capture takes ONE real step first (it uploads the layout and sizes every buffer),
+        so on return ids and states have advanced by one token; the context's stream is switched to a capture stream for
+        the duration of the call.
+        """
+        import torch
+        n = int(ids_dev.numel())
+        offsets = np.arange(n, dtype=np.uint32)
+        lengths = np.ones(n, dtype=np.uint32)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        self.gpu.set_stream(side)
+        try:
+            with torch.cuda.stream(side):
+                self.prefill_batch_dev(ids_dev, offsets, lengths, streams, None, ids_dev)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side, capture_error_mode="relaxed"):
+                    self.prefill_batch_dev(ids_dev, offsets, lengths, streams, None, ids_dev)
+        finally:
+            side.synchronize()
+            self.gpu.set_stream(torch.cuda.current_stream())
+        return graph
+
     def decode_step(self, ids, streams=None, want_logits=True, want_greedy=False):
         ids = np.ascontiguousarray(ids, np.uint64)
         st = None if streams is None else np.ascontiguousarray(streams, np.uint32)

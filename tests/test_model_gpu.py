@@ -8,6 +8,8 @@ from parity import rel_err, scale_err
 
 pytestmark = pytest.mark.gpu
 
+N_ERR_TOKEN = 7  # PSSA_B200_ERR_TOKEN
+
 
 @pytest.fixture(scope="module")
 def gpu():
@@ -328,4 +330,50 @@ def test_scorer_matches_the_oracle_over_passes_and_tiles(gpu):
     import pssa_b200
     with pytest.raises(pssa_b200.B200Error, match="target ID 97 outside"):
         gm.score([1, 2], [3, 97])
+    gm.close()
+
+
+def test_greedy_decode_step_as_a_cuda_graph_equals_the_eager_steps(gpu):
+    """The device-resident entry is capturable once its lane layout is on the device: replays of the captured step
+    (ids fed back on the device) produce the tokens of eager decode steps."""
+    import torch
+    gpu.set_stream(torch.cuda.current_stream())
+    om, gm = make_pair(gpu, 2, 97, 32, 16, 8, 16, seed=31, streams=3, precision=0)
+    _, gm2 = make_pair(gpu, 2, 97, 32, 16, 8, 16, seed=31, streams=3, precision=0)
+    prompts = [[5, 9, 2], [11, 3], [7]]
+    _, g0 = gm.prefill_batch(prompts, want_logits=False, want_greedy=True)
+    _, g0b = gm2.prefill_batch(prompts, want_logits=False, want_greedy=True)
+    assert np.array_equal(g0, g0b)
+    # eager reference: 6 steps
+    eager = [g0b]
+    for _ in range(6):
+        eager.append(gm2.decode_step(eager[-1], want_logits=False, want_greedy=True))
+    ids_dev = torch.tensor(g0.astype(np.int32), device="cuda", dtype=torch.int32)
+    graph = gm.capture_greedy_decode_graph(ids_dev)          # takes one real step
+    torch.cuda.synchronize()
+    assert np.array_equal(ids_dev.cpu().numpy().astype(np.uint64), eager[1])
+    for step in range(2, 7):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(ids_dev.cpu().numpy().astype(np.uint64), eager[step]), step
+    gpu.poll_status()
+    gpu.set_stream(None)
+    gm.close()
+    gm2.close()
+
+
+def test_device_resident_ids_outside_the_vocabulary_raise_the_status_word(gpu):
+    import pssa_b200
+    import torch
+    gpu.set_stream(torch.cuda.current_stream())
+    _, gm = make_pair(gpu, 1, 50, 16, 4, 4, 8, seed=3, precision=1)
+    ids_dev = torch.tensor([3, 50, 4], device="cuda", dtype=torch.int32)
+    logits = torch.zeros(1, 50, device="cuda")
+    gm.prefill_batch_dev(ids_dev, np.array([0], np.uint32), np.array([3], np.uint32), None, logits, None)
+    torch.cuda.synchronize()
+    with pytest.raises(pssa_b200.B200Error) as e:
+        gpu.poll_status()
+    assert e.value.status == N_ERR_TOKEN
+    gpu.poll_status()  # cleared
+    gpu.set_stream(None)
     gm.close()
