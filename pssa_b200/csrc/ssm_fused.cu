@@ -32,7 +32,7 @@
 namespace pssa {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;  // default CTA size; the 16-state fast configuration also comes with 352 (see launch_ssm_fused)
 // tokens per staged tile; the widest state split keeps 8 so three stages stay inside the shared memory of one SM
 template <int G>
 constexpr int kTileTokensFor = G >= 32 ? 8 : 16;
@@ -78,8 +78,9 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     return r;
 }
 
-template <int ST, int G, bool EXACT, bool TAPE>
-__global__ void __launch_bounds__(kThreads, (ST <= 16 && !TAPE && !EXACT) ? kMinCtasFast : 1) ssm_fused_kernel(SsmParams p) {
+template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
+__global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 256 ? 2 : kMinCtasFast) : 1) ssm_fused_kernel(SsmParams p) {
+    constexpr int kThreads = THR;     // shadows the default: every stride below follows this instantiation's CTA size
     constexpr int CH = kThreads / G;  // channels per CTA
     constexpr int kTileTokens = kTileTokensFor<G>;
     constexpr int LPG = 32 / G;       // lanes of a warp that share one state group
@@ -431,13 +432,14 @@ __global__ void __launch_bounds__(256) seqpar_fold_kernel(const float* __restric
     st[e] = h;
 }
 
-template <int ST, int G, bool EXACT, bool TAPE>
+template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
 int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
+    constexpr int kThreads = THR;
     constexpr int CH = kThreads / G;
     constexpr int SP = (ST + 4) * G;
     constexpr int kTileTokens = kTileTokensFor<G>;
     size_t smem = (size_t)kStages * kTileTokens * (2 * CH + 2 * SP) * sizeof(float);
-    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE>;
+    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE, THR>;
     static bool attr_set = false;  // per instantiation; contexts share the device function
     if (smem > 48 * 1024 && !attr_set) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -502,7 +504,20 @@ int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact) {
         if (s <= 8) return launch_one<4, 2, false>(ctx, p);
         if (s <= 16) return launch_one<4, 4, false>(ctx, p);
         if (s <= 32) return launch_one<16, 2, false>(ctx, p);
-        if (s <= 64) return launch_one<16, 4, false>(ctx, p);
+        if (s <= 64) {
+            // CTA size by wave balance. Every CTA of a launch is resident at once and they all take the same time, so the
+            // launch lasts as long as the SM holding the most warps. 256 threads = 64 channels per CTA; 352 threads = 88
+            // channels. With d = 768 and 32 lanes: 384 CTAs put 3 x 8 warps on most SMs, 288 larger ones put 2 x 11.
+            if (!tape) {
+                auto busiest = [&](int threads, int cap) -> long long {
+                    const long long blocks = (long long)((p.d + threads / 4 - 1) / (threads / 4)) * p.lanes;
+                    const long long per_sm = (blocks + ctx->sm_count - 1) / ctx->sm_count;
+                    return per_sm > cap ? (1ll << 40) : per_sm * (threads / 32);  // more than one wave: not considered
+                };
+                if (busiest(352, 2) < busiest(256, 4)) return launch_cfg<16, 4, false, false, 352>(ctx, p);
+            }
+            return launch_one<16, 4, false>(ctx, p);
+        }
         if (s <= 128) return launch_one<16, 8, false>(ctx, p);
         if (s <= 256) return launch_one<16, 16, false>(ctx, p);
         if (s <= 512) return launch_one<16, 32, false>(ctx, p);
