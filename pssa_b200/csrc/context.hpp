@@ -89,6 +89,25 @@ inline void* arena_take(pssa_b200_ctx* ctx, size_t bytes) {
 inline size_t arena_round(size_t bytes) { return (bytes + 255) & ~size_t(255); }
 
 // Launch bookkeeping: every kernel launch of this library goes through here.
+// Programmatic dependent launch (stream order preserved, launch latency hidden): a kernel launched with
+// `launch_dependent` may start before its predecessor in the stream has finished, and must call pdl_wait() before it
+// reads or writes anything the predecessor touches; predecessors call pdl_trigger() early so that the dependent's
+// prologue (barrier set-up, TMEM allocation, descriptor fetch) overlaps their own tail. Both calls are no-ops for
+// kernels launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr, cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
 void profile_record(pssa_b200_ctx* ctx, const char* kernel);  // api.cu
 inline int32_t after_launch(pssa_b200_ctx* ctx, const char* kernel) {
     ctx->launches += 1;

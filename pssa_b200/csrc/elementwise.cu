@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const float* __restrict
                                                          const float* __restrict__ beta, float* __restrict__ x_norm,
                                                          __nv_bfloat16* __restrict__ x_bf16, size_t rows, int d, uint32_t vocab,
                                                          int* __restrict__ status) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     extern __shared__ float sm[];  // [8 warps][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t row = (size_t)blockIdx.x * 8 + warp;
@@ -120,6 +122,8 @@ __global__ void __launch_bounds__(256) residual_kernel(const float* __restrict__
 
 __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restrict__ src, const uint32_t* __restrict__ rows_idx,
                                                           float* __restrict__ dst, size_t n_rows, int d) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_rows * (size_t)d) return;
     size_t r = idx / d;
@@ -127,6 +131,8 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restric
 }
 
 __global__ void __launch_bounds__(256) to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx < n) dst[idx] = __float2bfloat16_rn(src[idx]);
 }
@@ -139,6 +145,8 @@ __device__ __forceinline__ int total_order_key(float v) {
 }
 __global__ void __launch_bounds__(256) greedy_kernel(const float* __restrict__ logits, uint32_t* __restrict__ out, size_t rows,
                                                      int v) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     __shared__ long long s_best[8];
     __shared__ int s_bad[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -210,6 +218,8 @@ __global__ void __launch_bounds__(256) observe_rows_kernel(const uint32_t* __res
 __global__ void __launch_bounds__(256) pack_act_kernel(const float* __restrict__ act, size_t ldact, __nv_bfloat16* __restrict__ dst_a,
                                                        size_t ld_a, int off_a, __nv_bfloat16* __restrict__ dst_b, size_t ld_b,
                                                        int off_b, size_t rows) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (row, group of 8 columns)
     const size_t row = idx >> 3;
     const int g = (int)(idx & 7);
@@ -296,11 +306,11 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
     }
     unsigned blocks = blocks_for(rows, 8);
     if (exact)
-        embed_norm_kernel<true><<<blocks, 256, smem, ctx->stream>>>(embed, ids, feats, gamma, beta, x_norm, (__nv_bfloat16*)x_bf16, rows, d,
-                                                                   (uint32_t)vocab, ctx->status_dev);
+        PSSA_CUDA(ctx, launch_dependent(embed_norm_kernel<true>, dim3(blocks), dim3(256), smem, ctx->stream, embed, ids, feats, gamma, beta,
+                                        x_norm, (__nv_bfloat16*)x_bf16, rows, d, (uint32_t)vocab, ctx->status_dev));
     else
-        embed_norm_kernel<false><<<blocks, 256, smem, ctx->stream>>>(embed, ids, feats, gamma, beta, x_norm, (__nv_bfloat16*)x_bf16, rows, d,
-                                                                    (uint32_t)vocab, ctx->status_dev);
+        PSSA_CUDA(ctx, launch_dependent(embed_norm_kernel<false>, dim3(blocks), dim3(256), smem, ctx->stream, embed, ids, feats, gamma, beta,
+                                        x_norm, (__nv_bfloat16*)x_bf16, rows, d, (uint32_t)vocab, ctx->status_dev));
     return after_launch(ctx, "embed_norm_kernel");
 }
 
@@ -334,12 +344,13 @@ int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, f
 }
 
 int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d) {
-    gather_rows_kernel<<<blocks_for(n_rows * (size_t)d, 256), 256, 0, ctx->stream>>>(src, rows_idx, dst, n_rows, d);
+    PSSA_CUDA(ctx, launch_dependent(gather_rows_kernel, dim3(blocks_for(n_rows * (size_t)d, 256)), dim3(256), 0, ctx->stream, src, rows_idx, dst,
+                                    n_rows, d));
     return after_launch(ctx, "gather_rows_kernel");
 }
 
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n) {
-    to_bf16_kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(src, (__nv_bfloat16*)dst, n);
+    PSSA_CUDA(ctx, launch_dependent(to_bf16_kernel, dim3(blocks_for(n, 256)), dim3(256), 0, ctx->stream, src, (__nv_bfloat16*)dst, n));
     return after_launch(ctx, "to_bf16_kernel");
 }
 
@@ -356,8 +367,8 @@ int32_t launch_pack_act(pssa_b200_ctx* ctx, const float* act, size_t ldact, void
                         int off_b, size_t rows) {
     if (ldact % 1 || ld_a % 8 || ld_b % 8 || off_a % 8 || off_b % 8 || ((uintptr_t)dst_a & 15) || ((uintptr_t)dst_b & 15))
         return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "adapter block packing needs 16-byte aligned bf16 rows");
-    pack_act_kernel<<<blocks_for(rows * 8, 256), 256, 0, ctx->stream>>>(act, ldact, (__nv_bfloat16*)dst_a, ld_a, off_a, (__nv_bfloat16*)dst_b,
-                                                                       ld_b, off_b, rows);
+    PSSA_CUDA(ctx, launch_dependent(pack_act_kernel, dim3(blocks_for(rows * 8, 256)), dim3(256), 0, ctx->stream, act, ldact, (__nv_bfloat16*)dst_a,
+                                    ld_a, off_a, (__nv_bfloat16*)dst_b, ld_b, off_b, rows));
     return after_launch(ctx, "pack_act_kernel");
 }
 
@@ -380,7 +391,7 @@ int32_t launch_cross_entropy(pssa_b200_ctx* ctx, const float* logits, const uint
 
 int32_t launch_greedy(pssa_b200_ctx* ctx, const float* logits, uint32_t* out, size_t rows, int v) {
     if (rows > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "greedy: %zu rows exceed grid limits; refusing launch", rows);
-    greedy_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(logits, out, rows, v);
+    PSSA_CUDA(ctx, launch_dependent(greedy_kernel, dim3((unsigned)rows), dim3(256), 0, ctx->stream, logits, out, rows, v));
     return after_launch(ctx, "greedy_kernel");
 }
 

@@ -216,6 +216,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched only this CTA's shared memory and TMEM; from here on the kernel reads what its
+    // predecessor in the stream wrote, so a dependent launch waits for that predecessor here
+    pdl_trigger();
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -492,7 +496,7 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     }
     long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
     unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
-    kern<<<grid, GEMM_THREADS, smem, ctx->stream>>>(map_a, map_b, e);
+    PSSA_CUDA(ctx, launch_dependent(kern, dim3(grid), dim3(GEMM_THREADS), smem, ctx->stream, map_a, map_b, e));
     // the profile facility keys on this name: one entry per epilogue family
     const char* name = e.n_pairs > 0            ? "gemm_bf16_tcgen05_kernel[split value read]"
                        : e.epi < 0              ? "gemm_bf16_tcgen05_kernel[x-side concatenated]"

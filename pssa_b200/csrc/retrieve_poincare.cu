@@ -220,6 +220,8 @@ __device__ __forceinline__ float fast_poincare_distance(float u) {
 // queries tq*4 + a and slots ts + 16*b: consecutive slot threads sit 68 floats apart, so their 16-byte key reads hit
 // disjoint banks and their distance stores are 64-byte runs.
 __global__ void __launch_bounds__(256, 3) poincare_distance_f32_kernel(RetrieveParams p) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int kpad = (p.dk + 3) / 4 * 4;
     const int kpitch = kpad + 4;
@@ -398,6 +400,8 @@ __device__ __forceinline__ float weight_of(float min_dist, float d, float tau) {
 // One warp per query. Distances are read from `weights` and replaced by the weights.
 template <bool EXACT>
 __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     extern __shared__ float sm[];  // [8 warps][cap] distances / weights
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t q = (size_t)blockIdx.x * 8 + warp;
@@ -676,7 +680,7 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         unsigned ysplit = 1;
         const unsigned npass = (unsigned)((p.count + STL - 1) / STL);
         while (qblocks * ysplit < 148 && ysplit < 8 && ysplit * 2 <= (npass ? npass : 1)) ysplit *= 2;
-        poincare_distance_f32_kernel<<<dim3((unsigned)qblocks, ysplit), 256, smem_f, ctx->stream>>>(p);
+        PSSA_CUDA(ctx, launch_dependent(poincare_distance_f32_kernel, dim3((unsigned)qblocks, ysplit), dim3(256), smem_f, ctx->stream, p));
         if ((rc = after_launch(ctx, "poincare_distance_f32_kernel")) != PSSA_B200_OK) return rc;
     } else {
         unsigned ysplit = 1;  // few query tiles (decode): spread the slot passes over up to 8 CTAs per tile
@@ -695,9 +699,9 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         attr_b[exact] = true;
     }
     if (exact)
-        softmax_topk_kernel<true><<<(unsigned)wblocks, 256, smem_b, ctx->stream>>>(p);
+        PSSA_CUDA(ctx, launch_dependent(softmax_topk_kernel<true>, dim3((unsigned)wblocks), dim3(256), smem_b, ctx->stream, p));
     else
-        softmax_topk_kernel<false><<<(unsigned)wblocks, 256, smem_b, ctx->stream>>>(p);
+        PSSA_CUDA(ctx, launch_dependent(softmax_topk_kernel<false>, dim3((unsigned)wblocks), dim3(256), smem_b, ctx->stream, p));
     if ((rc = after_launch(ctx, "softmax_topk_kernel")) != PSSA_B200_OK) return rc;
     bool topk = p.top_k != 0 && p.top_k < p.count;
     if (p.count > 0 && !topk && p.w_split && p.v_split && !exact) {

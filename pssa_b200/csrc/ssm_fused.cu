@@ -80,6 +80,8 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 
 template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
 __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 256 ? 2 : kMinCtasFast) : 1) ssm_fused_kernel(SsmParams p) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     constexpr int kThreads = THR;     // shadows the default: every stride below follows this instantiation's CTA size
     constexpr int CH = kThreads / G;  // channels per CTA
     constexpr int kTileTokens = kTileTokensFor<G>;
@@ -329,6 +331,8 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 25
 // TPC threads of the channel. Same arithmetic as the fast mode of the tiled kernel (ex2.approx, fused multiply-adds).
 template <int TPC>
 __global__ void __launch_bounds__(256) ssm_step_kernel(SsmParams p) {
+    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
+    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     constexpr int CPB = 256 / TPC;  // channels per CTA
     const int tid = threadIdx.x;
     const int q = tid % TPC, c = tid / TPC;
@@ -377,7 +381,7 @@ int32_t launch_step(pssa_b200_ctx* ctx, const SsmParams& p) {
     size_t blocks = (size_t)((p.d + CPB - 1) / CPB) * p.lanes;
     if (blocks > 0x7fffffffull)
         return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM grid (%zu, 1) exceeds grid limits; refusing launch", blocks);
-    ssm_step_kernel<TPC><<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+    PSSA_CUDA(ctx, launch_dependent(ssm_step_kernel<TPC>, dim3((unsigned)blocks), dim3(256), 0, ctx->stream, p));
     return after_launch(ctx, "ssm_step_kernel");
 }
 
@@ -449,7 +453,7 @@ int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
     size_t blocks = (size_t)ncb * p.lanes;
     if (blocks > 0x7fffffffull)
         return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 SSM grid (%zu, 1) exceeds grid limits; refusing launch", blocks);
-    kern<<<(unsigned)blocks, kThreads, smem, ctx->stream>>>(p);
+    PSSA_CUDA(ctx, launch_dependent(kern, dim3((unsigned)blocks), dim3(kThreads), smem, ctx->stream, p));
     return after_launch(ctx, "ssm_fused_kernel");
 }
 
