@@ -169,7 +169,11 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Persistent kernel: CTA c processes tiles c, c + gridDim.x, ... ; tile index -> (m, n) with n fastest, so the
 // CTAs running at the same time share A row blocks through L2 and A is read from HBM once. Two TMEM accumulators
 // let the epilogue of tile i run while the tensor cores work on tile i + 1.
-template <int BN, int STAGES>
+// MODE fixes the epilogue family at compile time (kRuntimeMode: read it from the launch parameters). The epilogue's
+// element loops are unrolled 32 wide, so every family it has to carry costs kilobytes of code in each instantiation and
+// the epilogue warps stall on instruction fetch; the products of the model's block schedule get their own instantiations.
+constexpr int kRuntimeMode = -100;
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_b,
                                                                             GemmEpilogue e) {
@@ -187,7 +191,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EPI_WARPS][32 rows][STG_PITCH]
     const bool vec32 = e.out && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0);
-    const bool vec_res = (e.epi == EPI_RESIDUAL || e.epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
+    const int epi = MODE == kRuntimeMode ? e.epi : MODE;  // a compile-time constant in the specialised instantiations
+    const bool vec_res = (epi == EPI_RESIDUAL || epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
                          (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & 15) == 0)));
     const bool vec16 = e.out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out16) & 7) == 0);
 
@@ -310,7 +315,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 // EPI_RESIDUAL reads two more fp32 arrays with the output's access pattern: issue those loads first so
                 // they are in flight during the TMEM load and the transpose
                 float4 pre_add[8], pre_res[8];
-                const bool two_in = e.epi == EPI_RESIDUAL || e.epi == EPI_GATE;
+                const bool two_in = epi == EPI_RESIDUAL || epi == EPI_GATE;
                 const bool prefetch = two_in && interior && vec_res;
                 if (prefetch) {
 #pragma unroll
@@ -335,7 +340,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 // switch made the instruction stream jump between kilobytes of unrolled code and stalled on
                 // instruction fetch). The column table's boundaries are multiples of 32 for every model shape;
                 // a chunk that straddles one is activated element by element after the transpose (kind == -1).
-                int kind = e.epi;
+                int kind = epi;
                 if (kind < 0) {
                     const int first = col_kind(e, col0), last = col_kind(e, min(col0 + 31, e.N - 1));
                     kind = first == last ? first : -1;
@@ -377,10 +382,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         float4 val = *reinterpret_cast<const float4*>(stg + sr * STG_PITCH + ((((cq >> 2) ^ (sr & 7))) << 2));
                         if (gp) {
                             float4* g4 = reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo);
-                            if (e.epi == EPI_ADD_OUT) {
+                            if (epi == EPI_ADD_OUT) {
                                 float4 pv = *g4;
                                 val.x += pv.x, val.y += pv.y, val.z += pv.z, val.w += pv.w;
-                            } else if (e.epi == EPI_RESIDUAL) {
+                            } else if (epi == EPI_RESIDUAL) {
                                 const float4 av = pre_add[i];
                                 val.x += av.x, val.y += av.y, val.z += av.z, val.w += av.w;
                                 if (e.res_in) {
@@ -388,7 +393,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                                     val.x = fmaf(e.res_scale, val.x, rv.x), val.y = fmaf(e.res_scale, val.y, rv.y);
                                     val.z = fmaf(e.res_scale, val.z, rv.z), val.w = fmaf(e.res_scale, val.w, rv.w);
                                 }
-                            } else if (e.epi == EPI_GATE) {
+                            } else if (epi == EPI_GATE) {
                                 const float4 av = pre_add[i], gv = pre_res[i];
                                 val.x = fmaf(gv.x, val.x, av.x * e.alpha), val.y = fmaf(gv.y, val.y, av.y * e.alpha);
                                 val.z = fmaf(gv.z, val.z, av.z * e.alpha), val.w = fmaf(gv.w, val.w, av.w * e.alpha);
@@ -414,16 +419,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         for (int q = 0; q < 4; ++q) {
                             if (gcol + q >= e.N) continue;
                             if (kind == -1) o[q] = fast_epilogue(e, o[q], gcol + q, 0.0f);
-                            if (e.epi == EPI_RESIDUAL) {
+                            if (epi == EPI_RESIDUAL) {
                                 o[q] += e.add_in[(size_t)grow * e.ld_add + gcol + q];
                                 if (e.res_in) o[q] = fmaf(e.res_scale, o[q], e.res_in[(size_t)grow * e.ld_res + gcol + q]);
-                            } else if (e.epi == EPI_GATE) {
+                            } else if (epi == EPI_GATE) {
                                 o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q], o[q],
                                             e.add_in[(size_t)grow * e.ld_add + gcol + q] * e.alpha);
                             }
                             if (e.out) {
                                 float* gp = e.out + (size_t)grow * e.ldo + gcol + q;
-                                if (e.epi == EPI_ADD_OUT) o[q] += *gp;
+                                if (epi == EPI_ADD_OUT) o[q] += *gp;
                                 *gp = o[q];
                             }
                             if (e.out16) e.out16[(size_t)grow * e.ld16 + gcol + q] = __float2bfloat16_rn(o[q]);
@@ -481,14 +486,14 @@ int32_t make_map(pssa_b200_ctx* ctx, CUtensorMap* map, const void* base, size_t 
     return PSSA_B200_OK;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MODE = kRuntimeMode>
 int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const GemmEpilogue& e) {
     CUtensorMap map_a, map_b;
     int32_t rc;
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
     size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EPI_WARPS * 32 * STG_PITCH * 4;
-    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES>;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE>;
     static bool attr = false;
     if (!attr) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -531,8 +536,14 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // Four 48 KB stages help the long-K split product (141 -> 126 us at the model's shape, +8 % on plain products timed
     // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
     // (their epilogue traffic is the limiter), so those keep three.
-    if (e.n_pairs > 0) return launch_tile<256, 4>(ctx, a, b, e);
-    return launch_tile<256, 3>(ctx, a, b, e);
+    if (e.n_pairs > 0) return e.epi == EPI_NONE ? launch_tile<256, 4, EPI_NONE>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
+    switch (e.epi) {  // the block schedule's products: one epilogue family per instantiation
+        case -1: return launch_tile<256, 3, -1>(ctx, a, b, e);
+        case EPI_GATE: return launch_tile<256, 3, EPI_GATE>(ctx, a, b, e);
+        case EPI_RESIDUAL: return launch_tile<256, 3, EPI_RESIDUAL>(ctx, a, b, e);
+        case EPI_SILU: return launch_tile<256, 3, EPI_SILU>(ctx, a, b, e);
+        default: return launch_tile<256, 3>(ctx, a, b, e);
+    }
 }
 
 }  // namespace
