@@ -173,7 +173,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // element loops are unrolled 32 wide, so every family it has to carry costs kilobytes of code in each instantiation and
 // the epilogue warps stall on instruction fetch; the products of the model's block schedule get their own instantiations.
 constexpr int kRuntimeMode = -100;
-template <int BN, int STAGES, int MODE>
+// OUTS fixes which outputs exist: 0 = read the pointers at run time, 1 = fp32 only, 2 = bf16 only.
+template <int BN, int STAGES, int MODE, int OUTS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_b,
                                                                             GemmEpilogue e) {
@@ -190,11 +191,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     uint64_t* acc_empty = acc_full + 2;        // [2] accumulator drained by the epilogue warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EPI_WARPS][32 rows][STG_PITCH]
-    const bool vec32 = e.out && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0);
+    float* const out32 = OUTS == 2 ? nullptr : e.out;
+    __nv_bfloat16* const out16 = OUTS == 1 ? nullptr : e.out16;
+    const bool vec32 = out32 && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out32) & 15) == 0);
     const int epi = MODE == kRuntimeMode ? e.epi : MODE;  // a compile-time constant in the specialised instantiations
     const bool vec_res = (epi == EPI_RESIDUAL || epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
                          (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & 15) == 0)));
-    const bool vec16 = e.out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(e.out16) & 7) == 0);
+    const bool vec16 = out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(out16) & 7) == 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = e.n_pairs > 0 ? e.n_pairs * e.seg_kb : (e.K + BK - 1) / BK;
@@ -373,9 +376,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 __syncwarp();
                 const int gcol = col0 + cq;
-                if (interior && kind != -1 && (!e.out || vec32) && (!e.out16 || vec16) && (!two_in || vec_res)) {
-                    float* gp = e.out ? e.out + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
-                    __nv_bfloat16* bp = e.out16 ? e.out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
+                if (interior && kind != -1 && (!out32 || vec32) && (!out16 || vec16) && (!two_in || vec_res)) {
+                    float* gp = out32 ? out32 + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
+                    __nv_bfloat16* bp = out16 ? out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int sr = i * 4 + rsub;  // staged row; its column quads are swizzled with (row & 7)
@@ -426,12 +429,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                                 o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q], o[q],
                                             e.add_in[(size_t)grow * e.ld_add + gcol + q] * e.alpha);
                             }
-                            if (e.out) {
-                                float* gp = e.out + (size_t)grow * e.ldo + gcol + q;
+                            if (out32) {
+                                float* gp = out32 + (size_t)grow * e.ldo + gcol + q;
                                 if (epi == EPI_ADD_OUT) o[q] += *gp;
                                 *gp = o[q];
                             }
-                            if (e.out16) e.out16[(size_t)grow * e.ld16 + gcol + q] = __float2bfloat16_rn(o[q]);
+                            if (out16) out16[(size_t)grow * e.ld16 + gcol + q] = __float2bfloat16_rn(o[q]);
                         }
                     }
                 }
@@ -486,14 +489,14 @@ int32_t make_map(pssa_b200_ctx* ctx, CUtensorMap* map, const void* base, size_t 
     return PSSA_B200_OK;
 }
 
-template <int BN, int STAGES, int MODE = kRuntimeMode>
+template <int BN, int STAGES, int MODE = kRuntimeMode, int OUTS = 0>
 int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const GemmEpilogue& e) {
     CUtensorMap map_a, map_b;
     int32_t rc;
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
     size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EPI_WARPS * 32 * STG_PITCH * 4;
-    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE>;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS>;
     static bool attr = false;
     if (!attr) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -536,14 +539,14 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // Four 48 KB stages help the long-K split product (141 -> 126 us at the model's shape, +8 % on plain products timed
     // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
     // (their epilogue traffic is the limiter), so those keep three.
-    if (e.n_pairs > 0) return e.epi == EPI_NONE ? launch_tile<256, 4, EPI_NONE>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
-    switch (e.epi) {  // the block schedule's products: one epilogue family per instantiation
-        case -1: return launch_tile<256, 3, -1>(ctx, a, b, e);
-        case EPI_GATE: return launch_tile<256, 3, EPI_GATE>(ctx, a, b, e);
-        case EPI_RESIDUAL: return launch_tile<256, 3, EPI_RESIDUAL>(ctx, a, b, e);
-        case EPI_SILU: return launch_tile<256, 3, EPI_SILU>(ctx, a, b, e);
-        default: return launch_tile<256, 3>(ctx, a, b, e);
-    }
+    const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
+    if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
+    // the block schedule's products: one epilogue family and one output set per instantiation
+    if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1>(ctx, a, b, e);
+    if (e.epi == EPI_GATE) return launch_tile<256, 3, EPI_GATE, 0>(ctx, a, b, e);
+    if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 3, EPI_RESIDUAL, 1>(ctx, a, b, e);
+    if (e.epi == EPI_SILU && only16) return launch_tile<256, 3, EPI_SILU, 2>(ctx, a, b, e);
+    return launch_tile<256, 3>(ctx, a, b, e);
 }
 
 }  // namespace
