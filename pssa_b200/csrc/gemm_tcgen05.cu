@@ -57,7 +57,6 @@ struct GemmEpilogue {
     const float* res_in;
     size_t ld_add, ld_res;
     float res_scale;
-    int res_is_bf16;       // EPI_GATE: res_in points at bf16 values (row pitch ld_res in elements)
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -197,7 +196,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     const bool vec32 = out32 && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out32) & 15) == 0);
     const int epi = MODE == kRuntimeMode ? e.epi : MODE;  // a compile-time constant in the specialised instantiations
     const bool vec_res = (epi == EPI_RESIDUAL || epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
-                         (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & (e.res_is_bf16 ? 7 : 15)) == 0)));
+                         (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & 15) == 0)));
     const bool vec16 = out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(out16) & 7) == 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -319,7 +318,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 // EPI_RESIDUAL reads two more fp32 arrays with the output's access pattern: issue those loads first so
                 // they are in flight during the TMEM load and the transpose
                 float4 pre_add[8], pre_res[8];
-                uint2 pre_raw[8];
                 const bool two_in = epi == EPI_RESIDUAL || epi == EPI_GATE;
                 const bool prefetch = two_in && interior && vec_res;
                 if (prefetch) {
@@ -327,14 +325,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                     for (int i = 0; i < 8; ++i) {
                         const size_t ro = (size_t)(rbase + rsub + i * 4);
                         pre_add[i] = *reinterpret_cast<const float4*>(e.add_in + ro * e.ld_add + col0 + cq);
-                        if (epi == EPI_GATE && e.res_is_bf16) {
-                            // kept as raw bits: converting here would wait for the load before the TMEM read is issued
-                            pre_raw[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(e.res_in) +
-                                                                         ro * e.ld_res + col0 + cq);
-                        } else {
-                            pre_res[i] = e.res_in ? *reinterpret_cast<const float4*>(e.res_in + ro * e.ld_res + col0 + cq)
-                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
+                        pre_res[i] = e.res_in ? *reinterpret_cast<const float4*>(e.res_in + ro * e.ld_res + col0 + cq)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
                 }
                 float v[32];
@@ -385,13 +377,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                 __syncwarp();
                 const int gcol = col0 + cq;
                 if (interior && kind != -1 && (!out32 || vec32) && (!out16 || vec16) && (!two_in || vec_res)) {
-                    // column-range table with a bf16 side buffer: the sigmoid range [c2, c3) (the gate) is stored there, as bf16
-                    // only, at column (col - c2); every other range goes to the fp32 output as usual
-                    const bool cat16 = epi < 0 && out16;
-                    const bool to16 = cat16 && col0 >= e.c2 && col0 + 32 <= e.c3;
-                    float* gp = (out32 && !to16) ? out32 + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
-                    __nv_bfloat16* bp = (out16 && (!cat16 || to16)) ? out16 + (size_t)(rbase + rsub) * e.ld16 + gcol - (to16 ? e.c2 : 0)
-                                                                    : nullptr;
+                    float* gp = out32 ? out32 + (size_t)(rbase + rsub) * e.ldo + gcol : nullptr;
+                    __nv_bfloat16* bp = out16 ? out16 + (size_t)(rbase + rsub) * e.ld16 + gcol : nullptr;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int sr = i * 4 + rsub;  // staged row; its column quads are swizzled with (row & 7)
@@ -410,13 +397,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                                     val.z = fmaf(e.res_scale, val.z, rv.z), val.w = fmaf(e.res_scale, val.w, rv.w);
                                 }
                             } else if (epi == EPI_GATE) {
-                                const float4 av = pre_add[i];
-                                float4 gv = pre_res[i];
-                                if (e.res_is_bf16) {
-                                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pre_raw[i].x));
-                                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pre_raw[i].y));
-                                    gv = make_float4(lo.x, lo.y, hi.x, hi.y);
-                                }
+                                const float4 av = pre_add[i], gv = pre_res[i];
                                 val.x = fmaf(gv.x, val.x, av.x * e.alpha), val.y = fmaf(gv.y, val.y, av.y * e.alpha);
                                 val.z = fmaf(gv.z, val.z, av.z * e.alpha), val.w = fmaf(gv.w, val.w, av.w * e.alpha);
                             }
@@ -445,20 +426,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                                 o[q] += e.add_in[(size_t)grow * e.ld_add + gcol + q];
                                 if (e.res_in) o[q] = fmaf(e.res_scale, o[q], e.res_in[(size_t)grow * e.ld_res + gcol + q]);
                             } else if (epi == EPI_GATE) {
-                                const size_t gi = (size_t)grow * e.ld_res + gcol + q;
-                                const float gate = e.res_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.res_in)[gi])
-                                                                 : e.res_in[gi];
-                                o[q] = fmaf(gate, o[q], e.add_in[(size_t)grow * e.ld_add + gcol + q] * e.alpha);
+                                o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q], o[q],
+                                            e.add_in[(size_t)grow * e.ld_add + gcol + q] * e.alpha);
                             }
-                            const bool cat16s = epi < 0 && out16;
-                            const bool to16s = cat16s && gcol + q >= e.c2 && gcol + q < e.c3;
-                            if (out32 && !to16s) {
+                            if (out32) {
                                 float* gp = out32 + (size_t)grow * e.ldo + gcol + q;
                                 if (epi == EPI_ADD_OUT) o[q] += *gp;
                                 *gp = o[q];
                             }
-                            if (out16 && (!cat16s || to16s))
-                                out16[(size_t)grow * e.ld16 + gcol + q - (to16s ? e.c2 : 0)] = __float2bfloat16_rn(o[q]);
+                            if (out16) out16[(size_t)grow * e.ld16 + gcol + q] = __float2bfloat16_rn(o[q]);
                         }
                     }
                 }
@@ -567,7 +543,6 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
     if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1>(ctx, a, b, e);
-    if (e.epi == -1) return launch_tile<256, 3, -1, 0>(ctx, a, b, e);  // with the bf16 side buffer for the gate range
     if (e.epi == EPI_GATE) return launch_tile<256, 3, EPI_GATE, 0>(ctx, a, b, e);
     if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 3, EPI_RESIDUAL, 1>(ctx, a, b, e);
     if (e.epi == EPI_SILU && only16) return launch_tile<256, 3, EPI_SILU, 2>(ctx, a, b, e);
@@ -602,14 +577,13 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
 // epilogue (src/pssa.rs:1189-1192 without the adapter term, which rides in the MLP products as extra K columns).
 // gate [M, ld_gate] and y [M, N] fp32; out fp32 [M, N] and out16 bf16 [M, ld16] are both written.
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
-                              const void* gate, size_t ld_gate, bool gate_is_bf16, const float* y, float alpha, size_t M, size_t N,
-                              size_t K) {
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K) {
     int32_t rc = check_shape(ctx, x16, w16, M, N, K);
     if (rc) return rc;
     GemmEpilogue e{};
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = N, e.ld16 = ld16;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = EPI_GATE, e.alpha = alpha;
-    e.add_in = y, e.res_in = (const float*)gate, e.ld_add = N, e.ld_res = ld_gate, e.res_scale = 1.0f, e.res_is_bf16 = gate_is_bf16 ? 1 : 0;
+    e.add_in = y, e.res_in = gate, e.ld_add = N, e.ld_res = ld_gate, e.res_scale = 1.0f;
     return dispatch(ctx, x16, w16, e);
 }
 
@@ -631,11 +605,11 @@ int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void*
 }
 
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
-                             size_t ldo, int c1, int c2, int c3, void* gate_bf16, size_t ld_gate16) {
+                             size_t ldo, int c1, int c2, int c3) {
     int32_t rc = check_shape(ctx, x16, w16, M, N, K);
     if (rc) return rc;
     GemmEpilogue e{};
-    e.out = out, e.out16 = (__nv_bfloat16*)gate_bf16, e.ldo = ldo, e.ld16 = ld_gate16;
+    e.out = out, e.out16 = nullptr, e.ldo = ldo, e.ld16 = 0;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = -1, e.alpha = 1.0f, e.c1 = c1, e.c2 = c2, e.c3 = c3;
     return dispatch(ctx, x16, w16, e);
 }

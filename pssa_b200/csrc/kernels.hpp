@@ -145,18 +145,16 @@ int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, f
                          size_t K, size_t ldo, int epi, float alpha, size_t ld16 = 0);  // ld16: row pitch of out_bf16 (0 = N)
 // z = gate * (X W^T) + alpha * y, fp32 and bf16 (row pitch ld16) outputs
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
-                              const void* gate, size_t ld_gate, bool gate_is_bf16, const float* y, float alpha, size_t M, size_t N,
-                              size_t K);
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K);
 // MLP output with both residuals fused: out = res_in ? res_in + res_scale*(X W^T + add_in) : X W^T + add_in
 int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const float* add_in,
                                   const float* res_in, float res_scale, size_t M, size_t N, size_t K);
 // fp32-accurate product of operands pre-split into three bf16 pieces: a16 [M, 3K], b16 [N, 3K] (six partial products)
 int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
                                 size_t N, size_t K, size_t ldo, int terms = 6);
-// concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU; with gate_bf16
-// the sigmoid range is written there as bf16 [M, ld_gate16] (column c2 first) instead of into `out`
+// concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
-                             size_t ldo, int c1, int c2, int c3, void* gate_bf16 = nullptr, size_t ld_gate16 = 0);
+                             size_t ldo, int c1, int c2, int c3);
 
 // elementwise.cu
 int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t* ids, const float* feats, const float* gamma,

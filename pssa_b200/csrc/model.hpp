@@ -46,8 +46,7 @@ struct Workspace {
              *greedy = nullptr;
     float *feat_a = nullptr, *feat_b = nullptr, *x_norm = nullptr, *proj = nullptr, *y = nullptr, *weights = nullptr,
           *m_val = nullptr, *m_proj = nullptr, *z = nullptr, *mlp_act = nullptr, *last_feat = nullptr, *logits = nullptr;
-    void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr,
-         *gate_bf16 = nullptr;  // sigmoid gate of the tensor-core schedule [rows, d]
+    void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr;
     // z_bf16 is [rows, d + 64] and act_bf16 [rows, 2d + 64] when the adapter rides in the MLP products (rank 16)
     char* base = nullptr;
     size_t bytes = 0;

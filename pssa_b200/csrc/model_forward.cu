@@ -38,7 +38,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_mv = c.take(rows * d * f), o_mp = c.take(rows * d * f), o_z = c.take(rows * d * f),
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
     size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * (d + 64) * 2),
-           o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2), o_gb = c.take(rows * d * 2);
+           o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2);
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -56,7 +56,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     ws.proj = (float*)(b + o_proj), ws.y = (float*)(b + o_y), ws.weights = (float*)(b + o_w), ws.m_val = (float*)(b + o_mv);
     ws.m_proj = (float*)(b + o_mp), ws.z = (float*)(b + o_z), ws.mlp_act = (float*)(b + o_act);
     ws.last_feat = (float*)(b + o_lf), ws.logits = (float*)(b + o_lg);
-    ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab, ws.w_split = b + o_wsp, ws.gate_bf16 = b + o_gb;
+    ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab, ws.w_split = b + o_wsp;
     return PSSA_B200_OK;
 }
 
@@ -201,7 +201,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
                 if ((rc = launch_gemm_exact(ctx, ws.x_norm, b.w[p.id], ws.proj + p.off, rows, p.n, m->d, nc, p.epi, 1.0f))) return rc;
         } else {
             if ((rc = launch_gemm_bf16_cat(ctx, ws.x_bf16, b.wcat_bf16, ws.proj, rows, nc, m->d, nc, (int)m->off_b, (int)m->off_gate,
-                                           (int)m->off_act, ws.gate_bf16, m->d)))
+                                           (int)m->off_act)))
                 return rc;
         }
         // stage 3: SSM with the lane carries of this block (src/gpu_batch.rs:582-619)
@@ -269,7 +269,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             // term is one extra K block of both MLP products: W1*(zp + U act) = [W1 | W1 U] [zp; act] and
             // W2*h + U*act = [W2 | U] [h; act]. The combine kernel and the m_proj round trip disappear.
             const size_t ldz = m->d + 64, lda = 2 * m->d + 64;
-            if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, ws.z, ws.z_bf16, ldz, ws.gate_bf16, m->d, true, ws.y, ssm_scale, rows,
+            if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, ws.z, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale, rows,
                                             m->d, m->d)))
                 return rc;
             if ((rc = launch_pack_act(ctx, ws.proj + m->off_act, nc, ws.z_bf16, ldz, (int)m->d, ws.act_bf16, lda, (int)(2 * m->d), rows))) return rc;
