@@ -171,7 +171,7 @@ def run_reference(args):
     }))
 
 
-def kernel_roofline(name, launches, ms, rows, peak_hbm, peak_tf):
+def kernel_roofline(name, launches, ms, rows, peak_hbm, peak_tf, tc_distances=False):
     """Algorithmic work of one launch of `name` on `rows` token rows of the C4 block -> achieved rate."""
     d, s, k, cap = CFG["d_latent"], CFG["d_state"], CFG["d_mem_key"], CFG["mem_capacity"]
     per = ms / launches / 1e3
@@ -187,6 +187,8 @@ def kernel_roofline(name, launches, ms, rows, peak_hbm, peak_tf):
     if "gemm_bf16" in name:
         # algorithmic flops of a block's dense products (the value read counts once, not its six bf16 partial products)
         flop = 2 * rows * d * ((2 * d + 2 * s + k + 16) + k + d + 2 * d + 2 * d) + 2 * rows * d * cap
+        if tc_distances:  # the query-key inner products of the distance stage run there too (counted once, like the value read)
+            flop += 2 * rows * cap * k
         # `ms` covers every tensor-core launch of the step: report the aggregate rate
         return {"bound": "tensor", "achieved": flop * CFG["depth"] / (ms / 1e3) / 1e12, "peak": peak_tf, "unit": "TFLOP/s",
                 "frac": flop * CFG["depth"] / (ms / 1e3) / 1e12 / peak_tf}
@@ -452,7 +454,8 @@ def run_b200(args):
         merged["gemm_bf16_tcgen05_kernel (all tiles)"] = (gemm_launches, gemm_ms)
         for name, (n, ms) in sorted(merged.items(), key=lambda kv: -kv[1][1]):
             row = {"kernel": name, "launches_per_step": n / args.steps, "ms_per_step": ms / args.steps, "share": ms / total_prof}
-            roof = kernel_roofline(name, n / args.steps, ms / args.steps, rows, peak_hbm, peak_tf)
+            roof = kernel_roofline(name, n / args.steps, ms / args.steps, rows, peak_hbm, peak_tf,
+                                   tc_distances=any("Poincare" in k for k in prof))
             if roof:
                 row["roofline"] = roof
             if "gemm_bf16" in name:  # the tensor-core launches by epilogue family

@@ -177,6 +177,13 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
  * Differences are still formed first, so the distance keeps a relative error near 1e-6; the projection stays f64.
  * About four times faster; what the model's bf16 precision mode uses. Ignored together with PSSA_B200_MEM_EXACT. */
 #define PSSA_B200_MEM_F32_DISTANCE 2u
+/* Distances from the inner product on the tensor cores: |p - k|^2 = |p|^2 + |k|^2 - 2 p.k with p and k each split into
+ * three bf16 pieces and the distance formula in the product's epilogue. The projection stays f64. Absolute error of
+ * |p - k|^2 up to about 2e-6 (tensor-core fp32 accumulation is not correctly rounded), so a query that coincides with
+ * a key gets a distance of up to 1e-2 instead of 0; meant for queries that already carry bf16 rounding (the model's
+ * bf16 precision mode uses it). Needs d_key % 64 == 0, otherwise PSSA_B200_MEM_F32_DISTANCE behaviour applies.
+ * Ignored together with PSSA_B200_MEM_EXACT. */
+#define PSSA_B200_MEM_TC_DISTANCE 4u
 
 /*
  * Poincare-ball memory read for `rows` queries against one immutable bank. Replaces

@@ -74,6 +74,7 @@ SIGNATURES = {
 SSM_EXACT = 1
 MEM_EXACT = 1
 MEM_F32_DISTANCE = 2
+MEM_TC_DISTANCE = 4
 EPI_NONE, EPI_SOFTPLUS, EPI_SIGMOID, EPI_SILU, EPI_SCALE, EPI_ADD_OUT = range(6)
 PRECISION_BF16, PRECISION_FP32_EXACT = 0, 1
 CANCEL_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)

@@ -349,15 +349,19 @@ int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_
     if (rc != PSSA_B200_OK) return rc;
     if (!q || !keys || !norm_sq || !values || !m_val)
         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
-    if (flags & ~(PSSA_B200_MEM_EXACT | PSSA_B200_MEM_F32_DISTANCE)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
+    if (flags & ~(PSSA_B200_MEM_EXACT | PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     // scratch from the arena: the weight rows when the caller does not want them, and the bf16 pieces of the
     // weights and of the transposed values for the tensor-core value read (all-slots mode, capacity % 64 == 0)
     const bool exact = (flags & PSSA_B200_MEM_EXACT) != 0;
     const bool topk = top_k != 0 && top_k < count;
     const bool tc_read = !exact && !topk && count > 0 && capacity % 64 == 0;
+    const bool tc_dist = !exact && (flags & PSSA_B200_MEM_TC_DISTANCE) != 0 && d_key % 64 == 0 && count > 0;
     size_t need = (weights ? 0 : arena_round(rows * capacity * 4)) +
-                  (tc_read ? arena_round(rows * 3 * capacity * 2) + arena_round(d_val * 3 * capacity * 2) : 0);
+                  (tc_read ? arena_round(rows * 3 * capacity * 2) + arena_round(d_val * 3 * capacity * 2) : 0) +
+                  (tc_dist ? arena_round(rows * 3 * d_key * 2) + arena_round(rows * 8) + arena_round(capacity * 3 * d_key * 2) +
+                                 arena_round(capacity * 8)
+                           : 0);
     void* w_split = nullptr;
     void* v_split = nullptr;
     if (need) {
@@ -371,13 +375,20 @@ int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_
         }
     }
     RetrieveParams p{};
+    if (tc_dist) {
+        void* k_split = arena_take(ctx, capacity * 3 * d_key * 2);
+        float2* k_stat = (float2*)arena_take(ctx, capacity * 8);
+        p.q_split = arena_take(ctx, rows * 3 * d_key * 2), p.q_stat = (float2*)arena_take(ctx, rows * 8);
+        if ((rc = launch_split_keys(ctx, keys, norm_sq, k_split, k_stat, (int)capacity, (int)d_key)) != PSSA_B200_OK) return rc;
+        p.k_split = k_split, p.k_stat = k_stat;
+    }
     p.q = q, p.q_is_euclidean = q_is_euclidean, p.q_pnc = q_pnc, p.q_norm = q_norm;
     p.keys = keys, p.norm_sq = norm_sq, p.values = values;
     p.weights = weights, p.m_val = m_val, p.min_dist = min_dist;
     p.w_split = w_split, p.v_split = v_split;
     p.rows = rows, p.dk = (int)d_key, p.dv = (int)d_val, p.cap = (int)capacity, p.count = (int)count;
     p.top_k = (int)(top_k > capacity ? capacity : top_k), p.tau = tau;
-    p.f32_distance = (flags & PSSA_B200_MEM_F32_DISTANCE) != 0;
+    p.f32_distance = (flags & (PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE)) != 0;
     return launch_memory_read(ctx, p, (flags & PSSA_B200_MEM_EXACT) != 0);
 }
 

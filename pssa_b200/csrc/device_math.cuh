@@ -22,6 +22,7 @@ enum Epilogue : int {
     EPI_ADD_OUT = 5,  // out = out + acc   (second half of q = Wqx x + Wqh y; residual adds)
     EPI_RESIDUAL = 6, // tensor-core path only: acc + add_in, then the depth residual (see gemm_tcgen05.cu)
     EPI_GATE = 7,     // tensor-core path only: res_in * acc + alpha * add_in  (gated memory projection + scaled SSM output)
+    EPI_POINCARE = 8, // tensor-core path only: acc = p.k; out = Poincare distance from |p|^2 + |k|^2 - 2 acc (see gemm_tcgen05.cu)
 };
 
 __device__ __forceinline__ float apply_epilogue(int epi, float acc, float alpha, float prev) {
@@ -33,6 +34,20 @@ __device__ __forceinline__ float apply_epilogue(int epi, float acc, float alpha,
         case EPI_ADD_OUT: return __fadd_rn(prev, acc);
         default: return acc;
     }
+}
+
+// 2*asinh(sqrt(u)) = log1p(z), z = 2u + 2*sqrt(u*u + u), with the hardware sqrt / log2 / reciprocal approximations:
+// log1p(z) = log(w) + (z - (w - 1))/w for w = fl(1 + z). lg2.approx is within 2^-22 absolute near one, 2^-22 relative
+// elsewhere, so the distance is good to about 2e-7 absolute near zero and 3e-7 relative beyond.
+__device__ __forceinline__ float fast_poincare_distance(float u) {
+    float r, lg, rc;
+    const float t = fmaf(u, u, u);
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+    const float z = 2.0f * u + 2.0f * r;
+    const float w = 1.0f + z;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(w));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(w));
+    return fmaf(lg, 0.69314718055994531f, (z - (w - 1.0f)) * rc);
 }
 
 }  // namespace pssa

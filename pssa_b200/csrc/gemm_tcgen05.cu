@@ -57,6 +57,10 @@ struct GemmEpilogue {
     const float* res_in;
     size_t ld_add, ld_res;
     float res_scale;
+    // EPI_POINCARE: the accumulator is the inner product p.k of a point in the ball (row) and a bank key (column);
+    // row_stat[row] = (|p|^2, 1/(1-|p|^2)), col_stat[col] = (|k|^2, 1/(1-|k|^2)); out = d(p, k)
+    const float2* row_stat;
+    const float2* col_stat;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -365,6 +369,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
 #pragma unroll
                         for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
                         break;
+                    case EPI_POINCARE: {
+                        // |p - k|^2 = |p|^2 + |k|^2 - 2 p.k, then u = |p - k|^2 / ((1-|p|^2)(1-|k|^2)) (src/memory.rs:245-262);
+                        // this thread's row is one query, the column statistics are warp-wide broadcast loads
+                        const float2 rs = __ldg(e.row_stat + min(rbase + lane, e.M - 1));
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float2 cs = __ldg(e.col_stat + min(col0 + j, e.N - 1));
+                            // two differences first: both are exact when the points nearly coincide (|p|^2, |k|^2 and p.k
+                            // within a factor of two of each other), so no rounding happens at the magnitude of the norms
+                            const float sq = fmaxf((rs.x - v[j]) + (cs.x - v[j]), 0.0f);
+                            v[j] = fast_poincare_distance(sq * (rs.y * cs.y));
+                        }
+                        break;
+                    }
                     default:
                         break;  // EPI_NONE, EPI_ADD_OUT (added after the transpose)
                 }
@@ -506,7 +524,8 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
     PSSA_CUDA(ctx, launch_dependent(kern, dim3(grid), dim3(GEMM_THREADS), smem, ctx->stream, map_a, map_b, e));
     // the profile facility keys on this name: one entry per epilogue family
-    const char* name = e.n_pairs > 0            ? "gemm_bf16_tcgen05_kernel[split value read]"
+    const char* name = e.epi == EPI_POINCARE    ? "gemm_bf16_tcgen05_kernel[Poincare distances]"
+                       : e.n_pairs > 0          ? "gemm_bf16_tcgen05_kernel[split value read]"
                        : e.epi < 0              ? "gemm_bf16_tcgen05_kernel[x-side concatenated]"
                        : e.epi == EPI_GATE      ? "gemm_bf16_tcgen05_kernel[gated memory projection]"
                        : e.epi == EPI_RESIDUAL  ? "gemm_bf16_tcgen05_kernel[MLP down + residuals]"
@@ -540,6 +559,7 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
     // (their epilogue traffic is the limiter), so those keep three.
     const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
+    if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
     if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1>(ctx, a, b, e);
@@ -601,6 +621,23 @@ int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void*
     e.n_pairs = terms == 3 ? 3 : 6, e.seg_kb = (int)(K / BK);
     const unsigned char pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
     for (int i = 0; i < 6; ++i) e.pair_a[i] = pa[i], e.pair_b[i] = pb[i];
+    return dispatch(ctx, a16, b16, e);
+}
+
+// dist[M, ldo] (first N columns) = Poincare distance between M points of the ball and N bank keys, from the inner products
+// of their three-piece bf16 splits a16 [M, 3*K], b16 [N, 3*K] (all six partial products: fp32-accurate p.k).
+int32_t launch_gemm_bf16_poincare(pssa_b200_ctx* ctx, const void* a16, const void* b16, const float2* row_stat,
+                                  const float2* col_stat, float* dist, size_t M, size_t N, size_t K, size_t ldo) {
+    if (K % BK != 0) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 split GEMM needs K %% 64 == 0; K = %zu", K);
+    int32_t rc = check_shape(ctx, a16, b16, M, N, 3 * K);
+    if (rc) return rc;
+    GemmEpilogue e{};
+    e.out = dist, e.out16 = nullptr, e.ldo = ldo, e.ld16 = 0;
+    e.M = (int)M, e.N = (int)N, e.K = (int)(3 * K), e.epi = EPI_POINCARE, e.alpha = 1.0f;
+    e.n_pairs = 6, e.seg_kb = (int)(K / BK);
+    const unsigned char pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
+    for (int i = 0; i < 6; ++i) e.pair_a[i] = pa[i], e.pair_b[i] = pb[i];
+    e.row_stat = row_stat, e.col_stat = col_stat;
     return dispatch(ctx, a16, b16, e);
 }
 

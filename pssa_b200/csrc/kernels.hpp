@@ -89,10 +89,20 @@ struct RetrieveParams {
     float tau;
     int value_terms;       // tensor-core value read: 3 = leading partial products only (bf16-grade result), else all six
     int f32_distance;      // fast mode: squared differences accumulated in fp32 instead of f64 (ignored when exact)
+    int skip_weights;      // all-slots, non-exact, w_split set: do not write the fp32 weight rows back (only the pieces are read)
+    // tensor-core distances (non-exact, dk % 64 == 0; used when all four are set): q_split [rows, 3*dk] bf16 and
+    // q_stat [rows] are scratch written by the projection kernel; k_split [cap, 3*dk] bf16 and k_stat [cap] come from
+    // launch_split_keys, once per bank upload
+    void* q_split;
+    float2* q_stat;
+    const void* k_split;
+    const float2* k_stat;
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
 // values [cap, dv] fp32 -> v_split [dv, 3*cap] bf16 (transpose + three-way split); once per bank upload
 int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv);
+// keys [cap, dk] fp32 -> k_split [cap, 3*dk] bf16 pieces and k_stat[slot] = (|k|^2, 1/(1-|k|^2)); once per bank upload
+int32_t launch_split_keys(pssa_b200_ctx* ctx, const float* keys, const float* norm_sq, void* k_split, float2* k_stat, int cap, int dk);
 
 // sampling.cu
 struct SampleParams {
@@ -152,6 +162,10 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
 // fp32-accurate product of operands pre-split into three bf16 pieces: a16 [M, 3K], b16 [N, 3K] (six partial products)
 int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
                                 size_t N, size_t K, size_t ldo, int terms = 6);
+// Poincare distances of M points of the ball to N bank keys from the inner products of their three-piece splits
+// (a16 [M, 3K], b16 [N, 3K]); row_stat / col_stat = (|.|^2, 1/(1-|.|^2)); dist fp32 [M, ldo]
+int32_t launch_gemm_bf16_poincare(pssa_b200_ctx* ctx, const void* a16, const void* b16, const float2* row_stat,
+                                  const float2* col_stat, float* dist, size_t M, size_t N, size_t K, size_t ldo);
 // concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
                              size_t ldo, int c1, int c2, int c3);

@@ -105,6 +105,8 @@ int32_t pssa_b200_model_create(pssa_b200_ctx* ctx, const pssa_b200_config* cfg, 
         guard(dev_alloc(ctx, &b.w2cat_bf16, m->d * (2 * m->d + 64) * 2, true));
         guard(dev_alloc(ctx, (void**)&b.w1u, 2 * m->d * 16 * 4, true));
         guard(dev_alloc(ctx, &b.vsplit_bf16, m->d * 3 * m->cap * 2, true));
+        guard(dev_alloc(ctx, &b.ksplit_bf16, m->cap * 3 * m->k * 2, true));
+        guard(dev_alloc(ctx, (void**)&b.kstat, m->cap * sizeof(float2), true));
         b.host_up.assign(m->d * m->rank, 0.0f);
         b.host_cons.assign(m->d * m->rank, 0.0f);
         b.confidence.assign(m->cap, 1.0f);
@@ -149,6 +151,8 @@ void pssa_b200_model_destroy(pssa_b200_model* m) {
         cudaFree(b.w2cat_bf16);
         cudaFree(b.w1u);
         cudaFree(b.vsplit_bf16);
+        cudaFree(b.ksplit_bf16);
+        cudaFree(b.kstat);
     }
     free_workspace(m->ws);
     delete m;

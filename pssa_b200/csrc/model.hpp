@@ -36,6 +36,8 @@ struct DeviceBlock {
     void* w2cat_bf16 = nullptr;
     float* w1u = nullptr;
     void* vsplit_bf16 = nullptr;  // bank values transposed, three bf16 pieces [d, 3*cap] (tensor-core value read)
+    void* ksplit_bf16 = nullptr;  // bank keys as three bf16 pieces [cap, 3*k] and (|k|^2, 1/(1-|k|^2)) per slot
+    float2* kstat = nullptr;      //   (tensor-core distances); rebuilt together with vsplit_bf16
     bool bf16_dirty = true;
     bool vsplit_dirty = true;
 };
@@ -47,6 +49,8 @@ struct Workspace {
     float *feat_a = nullptr, *feat_b = nullptr, *x_norm = nullptr, *proj = nullptr, *y = nullptr, *weights = nullptr,
           *m_val = nullptr, *m_proj = nullptr, *z = nullptr, *mlp_act = nullptr, *last_feat = nullptr, *logits = nullptr;
     void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr;
+    void* q_split = nullptr;     // projected queries as three bf16 pieces [rows, 3*k] (tensor-core distances)
+    float2* q_stat = nullptr;    // [rows] (|p|^2, 1/(1-|p|^2))
     // z_bf16 is [rows, d + 64] and act_bf16 [rows, 2d + 64] when the adapter rides in the MLP products (rank 16)
     char* base = nullptr;
     size_t bytes = 0;

@@ -38,7 +38,8 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_mv = c.take(rows * d * f), o_mp = c.take(rows * d * f), o_z = c.take(rows * d * f),
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
     size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * (d + 64) * 2),
-           o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2);
+           o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2), o_qsp = c.take(rows * 3 * m->k * 2),
+           o_qst = c.take(rows * sizeof(float2));
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -57,6 +58,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     ws.m_proj = (float*)(b + o_mp), ws.z = (float*)(b + o_z), ws.mlp_act = (float*)(b + o_act);
     ws.last_feat = (float*)(b + o_lf), ws.logits = (float*)(b + o_lg);
     ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab, ws.w_split = b + o_wsp;
+    ws.q_split = b + o_qsp, ws.q_stat = (float2*)(b + o_qst);
     return PSSA_B200_OK;
 }
 
@@ -101,6 +103,7 @@ int32_t refresh_bf16(pssa_b200_model* m) {
     for (auto& b : m->blocks) {
         if (!b.vsplit_dirty) continue;
         if ((rc = launch_split_values(ctx, b.w[T_BANK_VALUES], b.vsplit_bf16, (int)m->cap, (int)d))) return rc;
+        if ((rc = launch_split_keys(ctx, b.w[T_BANK_KEYS], b.w[T_BANK_NORM_SQ], b.ksplit_bf16, b.kstat, (int)m->cap, (int)m->k))) return rc;
         b.vsplit_dirty = false;
     }
     if (m->unembed_dirty) {
@@ -251,6 +254,9 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
         rp.f32_distance = !exact;  // the bf16 mode's queries carry bf16 rounding already; f64 distances buy nothing there
         if (!exact && m->cap % 64 == 0) rp.w_split = ws.w_split, rp.v_split = b.vsplit_bf16;
+        // only the observer reads the fp32 weight rows after the value read
+        rp.skip_weights = rp.w_split && !observe && !(rp.top_k != 0 && rp.top_k < rp.count);
+        if (!exact && k % 64 == 0) rp.q_split = ws.q_split, rp.q_stat = ws.q_stat, rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
         const float rscale = l == 0 ? 1.0f : m->residual_scales[l - 1];

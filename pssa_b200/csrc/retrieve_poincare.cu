@@ -18,10 +18,13 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cfloat>
+#include <math_constants.h>
 
 #include "bounds.hpp"
 #include "context.hpp"
+#include "device_math.cuh"
 #include "kernels.hpp"
 
 namespace pssa {
@@ -201,20 +204,6 @@ __device__ __forceinline__ float sum2(f32x2 v) {
     return lo + hi;
 }
 
-// 2*asinh(sqrt(u)) = log1p(z), z = 2u + 2*sqrt(u*u + u), with the hardware sqrt / log2 / reciprocal approximations:
-// log1p(z) = log(w) + (z - (w - 1))/w for w = fl(1 + z). lg2.approx is within 2^-22 absolute near one, 2^-22 relative
-// elsewhere, so the distance is good to about 2e-7 absolute near zero and 3e-7 relative beyond.
-__device__ __forceinline__ float fast_poincare_distance(float u) {
-    float r, lg, rc;
-    const float t = fmaf(u, u, u);
-    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
-    const float z = 2.0f * u + 2.0f * r;
-    const float w = 1.0f + z;
-    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(w));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rc) : "f"(w));
-    return fmaf(lg, 0.69314718055994531f, (z - (w - 1.0f)) * rc);
-}
-
 // Shared memory: P as [dimension pair][query] float2 (a thread's four queries are one 32-byte read, broadcast over the
 // slot threads), key tiles row-major [slot][kpad + 4] in two buffers filled by cp.async one pass ahead. A thread owns
 // queries tq*4 + a and slots ts + 16*b: consecutive slot threads sit 68 floats apart, so their 16-byte key reads hit
@@ -373,6 +362,78 @@ __global__ void __launch_bounds__(256) split_values_kernel(const float* __restri
     row[slot] = a, row[cap + slot] = b, row[2 * cap + slot] = c;
 }
 
+// keys [cap, dk] fp32 -> k_split [cap, 3*dk] bf16 (three pieces side by side) and k_stat[slot] = (|k|^2, 1/(1-|k|^2))
+__global__ void __launch_bounds__(256) split_keys_kernel(const float* __restrict__ keys, const float* __restrict__ norm_sq,
+                                                         __nv_bfloat16* __restrict__ out, float2* __restrict__ stat, int cap, int dk) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < (size_t)cap) {
+        const float n = __ldg(norm_sq + idx);
+        stat[idx] = make_float2(n, (float)(1.0 / (1.0 - (double)n)));
+    }
+    if (idx >= (size_t)cap * dk) return;
+    int slot = (int)(idx / dk), col = (int)(idx % dk);
+    __nv_bfloat16 a, b, c;
+    split3(keys[idx], a, b, c);
+    __nv_bfloat16* row = out + (size_t)slot * 3 * dk;
+    row[col] = a, row[dk + col] = b, row[2 * dk + col] = c;
+}
+
+// Queries for the tensor-core distance: the reference's projection into the ball (src/memory.rs:198-211, f64, the same
+// sequential sums as the distance kernels, so q_pnc has the same bits), then the point as three bf16 pieces
+// q_split [rows, 3*dk] and q_stat[row] = (|p|^2, 1/(1-|p|^2)). One CTA = 64 rows: the tile is staged in shared memory
+// with coalesced loads, 64 threads walk one row each, all 256 write the pieces.
+__global__ void __launch_bounds__(256) project_split_kernel(RetrieveParams p) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ float tile[];  // [QT][dk + 1]
+    const int dk = p.dk, pitch = dk + 1, tid = threadIdx.x;
+    const size_t q0 = (size_t)blockIdx.x * QT;
+    const size_t ldq = p.ldq ? p.ldq : (size_t)dk;
+    for (int idx = tid; idx < QT * dk; idx += 256) {
+        const int r = idx / dk, c = idx % dk;
+        tile[r * pitch + c] = q0 + r < p.rows ? p.q[(q0 + r) * ldq + c] : 0.0f;
+    }
+    __syncthreads();
+    if (tid < QT && q0 + tid < p.rows) {
+        float* row = tile + tid * pitch;
+        double scale = 1.0;
+        if (p.q_is_euclidean) {
+            double r2 = 0.0;
+            for (int i = 0; i < dk; ++i) {
+                double v = (double)row[i];
+                r2 = __dadd_rn(r2, __dmul_rn(v, v));
+            }
+            double r = sqrt(r2);
+            const double max_radius = 1.0 - 8.0 * (double)FLT_EPSILON;
+            scale = (r == 0.0) ? 1.0 : fmin(r / (1.0 + r), max_radius) / r;
+            if (p.q_norm) p.q_norm[q0 + tid] = (float)fmin(r, (double)FLT_MAX);
+        }
+        double n2 = 0.0;
+        for (int i = 0; i < dk; ++i) {
+            float pv = p.q_is_euclidean ? (float)__dmul_rn((double)row[i], scale) : row[i];
+            row[i] = pv;
+            n2 = __dadd_rn(n2, __dmul_rn((double)pv, (double)pv));
+        }
+        const float qs = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;  // memory.rs:181-188
+        p.q_stat[q0 + tid] = make_float2(qs, (float)(1.0 / (1.0 - (double)qs)));
+    }
+    __syncthreads();
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.q_split);
+    for (int idx = tid; idx < QT * dk / 2; idx += 256) {
+        const int r = idx / (dk / 2), c = (idx % (dk / 2)) * 2;
+        if (q0 + r >= p.rows) break;
+        const float v0 = tile[r * pitch + c], v1 = tile[r * pitch + c + 1];
+        if (p.q_pnc) *reinterpret_cast<float2*>(p.q_pnc + (q0 + r) * dk + c) = make_float2(v0, v1);
+        __nv_bfloat16 a0, b0, c0, a1, b1, c1;
+        split3(v0, a0, b0, c0);
+        split3(v1, a1, b1, c1);
+        __nv_bfloat16* o = out + (q0 + r) * 3 * dk + c;
+        *reinterpret_cast<__nv_bfloat162*>(o) = __halves2bfloat162(a0, a1);
+        *reinterpret_cast<__nv_bfloat162*>(o + dk) = __halves2bfloat162(b0, b1);
+        *reinterpret_cast<__nv_bfloat162*>(o + 2 * dk) = __halves2bfloat162(c0, c1);
+    }
+}
+
 // ------------------------------------------------------------------ B: softmax / top-k (+ fused value read)
 __device__ __forceinline__ float warp_min(float v) {
 #pragma unroll
@@ -388,6 +449,13 @@ __device__ __forceinline__ unsigned long long warp_min_u64(unsigned long long v)
     return v;
 }
 
+__device__ __forceinline__ float exp2f_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr int kSoftmaxGroups = 8;  // 128-slot groups the register path of the all-slots softmax holds (capacity <= 1024)
 constexpr int kTopkRegs = 16;  // distances per lane the register path of the top-k selection holds (capacity <= 512)
 
 template <bool EXACT>
@@ -395,6 +463,95 @@ __device__ __forceinline__ float weight_of(float min_dist, float d, float tau) {
     // memory.rs:396-398 / 411-414: exp((min - d) / tau), subtraction before division
     float x = __fdiv_rn(__fsub_rn(min_dist, d), tau);
     return expf(x);
+}
+
+// All-slots softmax out of registers (non-exact mode, capacity a multiple of 128 and at most 128 * GROUPS, at least one
+// stored slot): a lane owns four consecutive slots of every 128 and rows move as 16-byte pieces; a warp walks rows
+// q, q + stride, ... with the next row's distances already in flight. Same formulas as the general kernel below (the sum
+// is grouped differently). value_terms == 3: the consumer keeps bf16-grade results (two leading pieces of every weight),
+// so the weights may use ex2.approx and one reciprocal per row (relative error near 1e-6 instead of 1e-7); a temperature
+// too small for a finite reciprocal keeps the division.
+template <int GROUPS>
+__global__ void __launch_bounds__(256) softmax_all_slots_kernel(RetrieveParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cap = p.cap, count = p.count;
+    const float tau = p.tau;
+    const float inv_tau = 1.0f / tau;
+    const bool lite = p.value_terms == 3 && inv_tau < CUDART_INF_F;
+    const float scale2 = inv_tau * 1.4426950408889634f;
+    const size_t stride = (size_t)gridDim.x * 8;
+    size_t q = (size_t)blockIdx.x * 8 + warp;
+    if (q >= p.rows) return;
+    auto load_row = [&](size_t qq, float4* dst) {
+        const float* src = p.weights + qq * cap;
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+            const int i = g * 128 + lane * 4;
+            if (i < count) dst[g] = *reinterpret_cast<const float4*>(src + i);
+        }
+    };
+    float4 nxt[GROUPS];
+    load_row(q, nxt);
+    for (; q < p.rows; q += stride) {
+        float4 dg[GROUPS];
+        float mn = FLT_MAX;
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+            const int i = g * 128 + lane * 4;
+            // slots past `count` hold nothing: an infinite distance gives them weight zero
+            float4 d4 = nxt[g];
+            d4.x = i + 0 < count ? d4.x : CUDART_INF_F, d4.y = i + 1 < count ? d4.y : CUDART_INF_F;
+            d4.z = i + 2 < count ? d4.z : CUDART_INF_F, d4.w = i + 3 < count ? d4.w : CUDART_INF_F;
+            dg[g] = d4;
+            mn = fminf(fminf(mn, fminf(d4.x, d4.y)), fminf(d4.z, d4.w));
+        }
+        if (q + stride < p.rows) load_row(q + stride, nxt);
+        mn = warp_min(mn);
+        if (p.min_dist && lane == 0) p.min_dist[q] = mn;
+        auto wt = [&](float d) { return lite ? exp2f_approx((mn - d) * scale2) : weight_of<false>(mn, d, tau); };
+        float sum = 0.0f;
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+            if (g * 128 < cap) {
+                dg[g].x = wt(dg[g].x), dg[g].y = wt(dg[g].y), dg[g].z = wt(dg[g].z), dg[g].w = wt(dg[g].w);
+                sum += (dg[g].x + dg[g].y) + (dg[g].z + dg[g].w);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        float* row = p.weights + q * cap;
+        __nv_bfloat16* ws = p.w_split ? reinterpret_cast<__nv_bfloat16*>(p.w_split) + q * 3 * (size_t)cap : nullptr;
+        const float inv_sum = __fdiv_rn(1.0f, sum);
+#pragma unroll
+        for (int g = 0; g < GROUPS; ++g) {
+            const int i = g * 128 + lane * 4;
+            if (i < cap) {
+                float wn[4] = {dg[g].x, dg[g].y, dg[g].z, dg[g].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) wn[e] = lite ? wn[e] * inv_sum : __fdiv_rn(wn[e], sum);
+                if (!p.skip_weights) *reinterpret_cast<float4*>(row + i) = make_float4(wn[0], wn[1], wn[2], wn[3]);
+                if (ws && lite) {  // the three-term read never touches the last piece
+                    __nv_bfloat16 pa[4], pb[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        pa[e] = __float2bfloat16_rn(wn[e]);
+                        pb[e] = __float2bfloat16_rn(wn[e] - __bfloat162float(pa[e]));
+                    }
+                    *reinterpret_cast<uint2*>(ws + i) = *reinterpret_cast<const uint2*>(pa);
+                    *reinterpret_cast<uint2*>(ws + cap + i) = *reinterpret_cast<const uint2*>(pb);
+                } else if (ws) {
+                    __nv_bfloat16 pa[4], pb[4], pc[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) split3(wn[e], pa[e], pb[e], pc[e]);
+                    *reinterpret_cast<uint2*>(ws + i) = *reinterpret_cast<const uint2*>(pa);
+                    *reinterpret_cast<uint2*>(ws + cap + i) = *reinterpret_cast<const uint2*>(pb);
+                    *reinterpret_cast<uint2*>(ws + 2 * cap + i) = *reinterpret_cast<const uint2*>(pc);
+                }
+            }
+        }
+    }
 }
 
 // One warp per query. Distances are read from `weights` and replaced by the weights.
@@ -418,6 +575,8 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
         if (p.min_dist) p.min_dist[q] = 0.0f;
         return;
     }
+    const float tau = p.tau;
+    const int k = p.top_k;
     float mn = FLT_MAX;
     for (int i = lane; i < count; i += 32) {
         float d = row[i];
@@ -427,8 +586,6 @@ __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
     mn = warp_min(mn);
     if (p.min_dist && lane == 0) p.min_dist[q] = mn;
     __syncwarp();
-    const float tau = p.tau;
-    const int k = p.top_k;
     if (k != 0 && k < count && k <= 32 && count <= 32 * kTopkRegs && cap >= 64) {
         // Register path of the selection below (same results): each lane keeps its count/32 distances in registers, a
         // round is a local minimum plus one warp-wide minimum of (distance bits, slot); the k winners are then ranked by
@@ -670,7 +827,23 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     }
     const int kpad4 = (p.dk + 3) / 4 * 4;
     const size_t smem_f = (size_t)(kpad4 / 2) * QT * sizeof(float2) + ((size_t)2 * STL * (kpad4 + 4) + QT + 2 * STL) * sizeof(float);
-    if (p.f32_distance && !exact && smem_f <= 112 * 1024) {  // keys wider than 128 keep the f64 kernel
+    const bool tc_dist = !exact && p.q_split && p.k_split && p.q_stat && p.k_stat && p.dk % 64 == 0 && p.dk <= 256 &&
+                         (!p.q_pnc || (reinterpret_cast<uintptr_t>(p.q_pnc) & 7) == 0);
+    if (tc_dist) {
+        // distances from the inner product on the tensor cores: projection + three-way split of the queries, then one
+        // product against the split keys whose epilogue turns p.k into d(p, k)
+        const size_t smem_p = (size_t)QT * (p.dk + 1) * sizeof(float);
+        static bool attr_p = false;
+        if (smem_p > 48 * 1024 && !attr_p) {
+            PSSA_CUDA(ctx, cudaFuncSetAttribute(project_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            attr_p = true;
+        }
+        PSSA_CUDA(ctx, launch_dependent(project_split_kernel, dim3((unsigned)qblocks), dim3(256), smem_p, ctx->stream, p));
+        if ((rc = after_launch(ctx, "project_split_kernel")) != PSSA_B200_OK) return rc;
+        if (p.count > 0 && (rc = launch_gemm_bf16_poincare(ctx, p.q_split, p.k_split, p.q_stat, p.k_stat, p.weights, p.rows,
+                                                           (size_t)p.count, (size_t)p.dk, (size_t)p.cap)))
+            return rc;
+    } else if (p.f32_distance && !exact && smem_f <= 112 * 1024) {  // keys wider than 128 keep the f64 kernel
         static bool attr_f = false;
         if (smem_f > 48 * 1024 && !attr_f) {
             PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -698,11 +871,24 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
             PSSA_CUDA(ctx, cudaFuncSetAttribute(softmax_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_b[exact] = true;
     }
-    if (exact)
-        PSSA_CUDA(ctx, launch_dependent(softmax_topk_kernel<true>, dim3((unsigned)wblocks), dim3(256), smem_b, ctx->stream, p));
-    else
-        PSSA_CUDA(ctx, launch_dependent(softmax_topk_kernel<false>, dim3((unsigned)wblocks), dim3(256), smem_b, ctx->stream, p));
-    if ((rc = after_launch(ctx, "softmax_topk_kernel")) != PSSA_B200_OK) return rc;
+    const bool all_regs = !exact && !(p.top_k != 0 && p.top_k < p.count) && p.count > 0 && p.cap % 128 == 0 && p.cap <= 1024 &&
+                          (reinterpret_cast<uintptr_t>(p.weights) & 15) == 0;
+    if (all_regs) {
+        // a few rows per warp, so that a row's loads overlap the arithmetic of the one before
+        const size_t want = (p.rows + 31) / 32, full = (size_t)ctx->sm_count * 8;
+        const unsigned grid = (unsigned)std::min(wblocks, std::max(want, std::min(wblocks, full)));
+        if (p.cap <= 512)
+            PSSA_CUDA(ctx, launch_dependent(softmax_all_slots_kernel<4>, dim3(grid), dim3(256), 0, ctx->stream, p));
+        else
+            PSSA_CUDA(ctx, launch_dependent(softmax_all_slots_kernel<8>, dim3(grid), dim3(256), 0, ctx->stream, p));
+        if ((rc = after_launch(ctx, "softmax_all_slots_kernel")) != PSSA_B200_OK) return rc;
+    } else {
+        if (exact)
+            PSSA_CUDA(ctx, launch_dependent(softmax_topk_kernel<true>, dim3((unsigned)wblocks), dim3(256), smem_b, ctx->stream, p));
+        else
+            PSSA_CUDA(ctx, launch_dependent(softmax_topk_kernel<false>, dim3((unsigned)wblocks), dim3(256), smem_b, ctx->stream, p));
+        if ((rc = after_launch(ctx, "softmax_topk_kernel")) != PSSA_B200_OK) return rc;
+    }
     bool topk = p.top_k != 0 && p.top_k < p.count;
     if (p.count > 0 && !topk && p.w_split && p.v_split && !exact) {
         // all-slots value read on the tensor cores: m = W x V as six bf16 partial products (fp32-accurate), or the
@@ -719,6 +905,12 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         if ((rc = after_launch(ctx, "value_mix_kernel")) != PSSA_B200_OK) return rc;
     }
     return PSSA_B200_OK;
+}
+
+int32_t launch_split_keys(pssa_b200_ctx* ctx, const float* keys, const float* norm_sq, void* k_split, float2* k_stat, int cap, int dk) {
+    size_t n = (size_t)cap * dk;
+    split_keys_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(keys, norm_sq, (__nv_bfloat16*)k_split, k_stat, cap, dk);
+    return after_launch(ctx, "split_keys_kernel");
 }
 
 int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv) {

@@ -169,11 +169,12 @@ class B200Dispatch:
 
     # ---- episodic memory read
     @staticmethod
-    def _mem_flags(exact, f32_distance):
-        return (N.MEM_EXACT if exact else 0) | (N.MEM_F32_DISTANCE if f32_distance else 0)
+    def _mem_flags(exact, f32_distance, tc_distance=False):
+        return ((N.MEM_EXACT if exact else 0) | (N.MEM_F32_DISTANCE if f32_distance else 0) |
+                (N.MEM_TC_DISTANCE if tc_distance else 0))
 
     def memory_read(self, q, keys, norm_sq, values, count, tau, top_k=0, q_is_euclidean=True, exact=False,
-                    f32_distance=False):
+                    f32_distance=False, tc_distance=False):
         """Bank read on host arrays: returns (q_pnc, q_norm, weights, m_val, min_dist). Mirrors
         `retrieve_memory_rows` (src/gpu_batch.rs:700-741): project, distances, softmax / top-k, value read."""
         _host(q, "q")
@@ -193,15 +194,16 @@ class B200Dispatch:
         self._check(self._lib.pssa_b200_memory_read(
             self._h, _ptr(q), 1 if q_is_euclidean else 0, _ptr(keys), _ptr(norm_sq), _ptr(values), rows, dk, dv, cap,
             count, tau, top_k or 0, _ptr(q_pnc), _ptr(q_norm), _ptr(weights), _ptr(m_val), _ptr(md),
-            self._mem_flags(exact, f32_distance)))
+            self._mem_flags(exact, f32_distance, tc_distance)))
         return q_pnc, q_norm, weights, m_val, md
 
     def memory_read_dev(self, q, keys, norm_sq, values, rows, dk, dv, cap, count, tau, m_val, top_k=0, q_pnc=None,
-                        q_norm=None, weights=None, min_dist=None, q_is_euclidean=True, exact=False, f32_distance=False):
+                        q_norm=None, weights=None, min_dist=None, q_is_euclidean=True, exact=False, f32_distance=False,
+                        tc_distance=False):
         self._check(self._lib.pssa_b200_memory_read_dev(
             self._h, _ptr(q), 1 if q_is_euclidean else 0, _ptr(keys), _ptr(norm_sq), _ptr(values), rows, dk, dv, cap,
             count, tau, top_k or 0, _ptr(q_pnc), _ptr(q_norm), _ptr(weights), _ptr(m_val), _ptr(min_dist),
-            self._mem_flags(exact, f32_distance)))
+            self._mem_flags(exact, f32_distance, tc_distance)))
 
 
     # ---- device-side sampling (src/inference.rs:102-181)

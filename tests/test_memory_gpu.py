@@ -66,6 +66,40 @@ def test_fp32_distance_mode_stays_within_its_stated_error(gpu, rows, dk, dv, cap
     assert abs(float(w[0].sum()) - 1.0) <= 1e-5
 
 
+@pytest.mark.parametrize("top_k", [0, 8])
+@pytest.mark.parametrize("rows,dk,dv,cap,count", [(1, 64, 64, 64, 1), (65, 64, 64, 32, 32), (300, 64, 192, 512, 512),
+                                                  (130, 64, 70, 100, 77), (17, 128, 128, 512, 300), (64, 33, 16, 64, 64)])
+def test_tensor_core_distance_mode_stays_within_its_stated_error(gpu, rows, dk, dv, cap, count, top_k):
+    """Distances from |p|^2 + |k|^2 - 2 p.k with the inner product on the tensor cores (three bf16 pieces per operand):
+    the projection is still bit-exact; |p - k|^2 carries an absolute error below 2.5e-6 (the tensor cores' fp32 accumulation is not correctly rounded), so u = |p - k|^2 / ((1-|p|^2)(1-|k|^2))
+    is off by at most 2.5e-6 / ((1-|p|^2)(1-|k|^2)) and the distance by that over sqrt(u^2 + u), or by 2*sqrt of it near zero.
+    A key width that is not a multiple of 64 (last case) falls back to the fp32 difference kernel."""
+    keys, norm_sq, values = make_bank(cap, dk, dv, rows + dk + cap)
+    rng = np.random.default_rng(rows * 11 + top_k)
+    q = (rng.standard_normal((rows, dk)) * rng.uniform(0.02, 0.5, (rows, 1))).astype(np.float32)
+    q[0] = keys[0] / (1.0 - np.linalg.norm(keys[0]))  # projects back onto slot 0 up to rounding: distance near zero
+    tau = 0.1
+    ref_p, ref_m, ref_w, ref_md = O.memory_read(keys, norm_sq, values, count, q, tau, top_k, True)
+    q_pnc, _, w, m, md = gpu.memory_read(q, keys, norm_sq, values, count, tau, top_k, True, False, tc_distance=True)
+    assert np.array_equal(q_pnc.view(np.uint32), ref_p.view(np.uint32))
+    pn = (ref_p.astype(np.float64) ** 2).sum(1)
+    conf = 1.0 / ((1.0 - pn) * (1.0 - float(norm_sq[:count].max())))
+    du = 2.5e-6 * conf
+    # d(u) = log1p(2u + 2 sqrt(u^2 + u)) is concave with d(0) = 0: |d(u + du) - d(u)| <= d(du)
+    bound = np.log1p(2 * du + 2 * np.sqrt(du * du + du)) + 1e-5
+    assert np.all(np.abs(md - ref_md) <= bound), (np.abs(md - ref_md).max(), bound.max())
+    assert bound.max() <= 2.5e-2
+    # weights exp(-d / tau) / sum: a distance error e moves a weight by at most about e / tau of itself (twice with the sum)
+    if top_k == 0:
+        assert np.all(np.abs(w - ref_w).max(1) <= 2.5 * bound / tau + 1e-6)
+        scale = np.maximum(1e-6, np.abs(values[:count]).max())
+        assert np.all(np.abs(m - ref_m).max(1) / scale <= 2.5 * bound / tau + 1e-5)
+    else:
+        same = (w != 0) == (ref_w != 0)
+        assert same.all(1).mean() >= 0.97  # near-ties at the k-th place may swap
+    assert abs(float(w[0].sum()) - 1.0) <= 1e-5
+
+
 @pytest.mark.parametrize("exact", [False, True])
 @pytest.mark.parametrize("top_k", [0, 1, 2, 8])
 @pytest.mark.parametrize("rows,dk,dv,cap,count", [(1, 1, 1, 1, 1), (3, 2, 4, 3, 2), (65, 16, 64, 32, 32),
