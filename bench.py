@@ -330,20 +330,23 @@ def run_extras(gpu, torch, peak_hbm):
     w = torch.zeros(rows, cap, device="cuda")
     m = torch.zeros(rows, dv, device="cuda")
     ref_sel = None
-    for name, top_k, f32d in (("top8", 8, False), ("all_slots", 0, False), ("top8_f32_distance", 8, True),
-                              ("all_slots_f32_distance", 0, True)):
+    for name, top_k, f32d, tcd in (("top8", 8, False, False), ("all_slots", 0, False, False), ("top8_f32_distance", 8, True, False),
+                                   ("all_slots_f32_distance", 0, True, False), ("top8_tc_distance", 8, False, True),
+                                   ("all_slots_tc_distance", 0, False, True)):
         ms = timed(lambda: gpu.memory_read_dev(q, keys, norm_sq, vals, rows, dk, dv, cap, cap, 0.1, m, top_k=top_k, weights=w,
-                                               q_is_euclidean=False, f32_distance=f32d), 5, warm=2)
+                                               q_is_euclidean=False, f32_distance=f32d, tc_distance=tcd), 5, warm=2)
         byts = rows * (dk * 4 + dv * 4 + (64 if top_k else cap * 4))
         row = {"workload": "Poincare retrieval, 512 slots, key/value dim 128, 262144 queries, tau 0.1"
-                           + (", distances accumulated in fp32 (differences first)" if f32d else ", distances in f64 like the reference"),
+                           + (", distances from tensor-core inner products (three bf16 pieces per operand)" if tcd else
+                              ", distances accumulated in fp32 (differences first)" if f32d else ", distances in f64 like the reference"),
                "ms": ms, "queries_per_s": rows / (ms / 1e3),
                "roofline": {"bound": "hbm", "achieved": byts / (ms / 1e3) / 1e9, "peak": peak_hbm, "unit": "GB/s",
                             "frac": byts / (ms / 1e3) / 1e9 / peak_hbm,
-                            "limiter": "FP32 FMA pipe (2 ops per key dimension per slot)" if f32d else "fp64 distance arithmetic"}}
+                            "limiter": "distance epilogue + softmax (the inner products run on the tensor cores)" if tcd else
+                                       "FP32 FMA pipe (2 ops per key dimension per slot)" if f32d else "fp64 distance arithmetic"}}
         if top_k:
             sel = w != 0  # the selected slot sets of every query
-            if not f32d:
+            if not f32d and not tcd:
                 ref_sel = sel.clone()
             elif ref_sel is not None:
                 row["queries_with_the_f64_slot_set"] = float((sel == ref_sel).all(dim=1).float().mean().item())
