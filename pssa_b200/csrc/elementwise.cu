@@ -35,10 +35,23 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const float* __restrict
     const float* src = ids ? embed + (size_t)id * d : feats + row * d;
     float* buf = sm + (size_t)warp * d;
     float part = 0.0f;
-    for (int i = lane; i < d; i += 32) {
-        float v = __ldg(src + i);
-        buf[i] = v;
-        part = fmaf(v, v, part);
+    // 16-byte accesses when every row starts on a 16-byte boundary (the model's widths do)
+    const bool vec = (d & 3) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(x_norm) |
+                                       reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(x_bf16) & 7) == 0;
+    if (vec) {
+#pragma unroll 2
+        for (int i = lane * 4; i < d; i += 128) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(src + i));
+            *reinterpret_cast<float4*>(buf + i) = v;
+            part = fmaf(v.x, v.x, part), part = fmaf(v.y, v.y, part), part = fmaf(v.z, v.z, part), part = fmaf(v.w, v.w, part);
+        }
+    } else {
+        for (int i = lane; i < d; i += 32) {
+            float v = __ldg(src + i);
+            buf[i] = v;
+            part = fmaf(v, v, part);
+        }
     }
     float sum;
     if (EXACT) {
@@ -53,6 +66,23 @@ __global__ void __launch_bounds__(256) embed_norm_kernel(const float* __restrict
         for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
     }
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)d), 1e-5f)));
+    if (vec) {
+        for (int i = lane * 4; i < d; i += 128) {
+            const float4 b4 = *reinterpret_cast<const float4*>(buf + i);
+            const float4 g4 = __ldg(reinterpret_cast<const float4*>(gamma + i)), t4 = __ldg(reinterpret_cast<const float4*>(beta + i));
+            float4 o;
+            o.x = __fadd_rn(__fmul_rn(g4.x, __fmul_rn(b4.x, inv)), t4.x), o.y = __fadd_rn(__fmul_rn(g4.y, __fmul_rn(b4.y, inv)), t4.y);
+            o.z = __fadd_rn(__fmul_rn(g4.z, __fmul_rn(b4.z, inv)), t4.z), o.w = __fadd_rn(__fmul_rn(g4.w, __fmul_rn(b4.w, inv)), t4.w);
+            *reinterpret_cast<float4*>(x_norm + row * d + i) = o;
+            if (x_bf16) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo), pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(x_bf16 + row * d + i) = pk;
+            }
+        }
+        return;
+    }
     for (int i = lane; i < d; i += 32) {
         float v = __fadd_rn(__fmul_rn(__ldg(gamma + i), __fmul_rn(buf[i], inv)), __ldg(beta + i));
         x_norm[row * d + i] = v;

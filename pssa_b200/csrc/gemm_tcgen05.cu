@@ -332,6 +332,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         pre_res[i] = e.res_in ? *reinterpret_cast<const float4*>(e.res_in + ro * e.ld_res + col0 + cq)
                                               : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
+                } else if (epi == EPI_ADD_OUT && interior && out32 && vec32) {
+                    // the rows this chunk adds to, requested before the TMEM load instead of one dependent round trip
+                    // per row group inside the store loop
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        pre_add[i] = *reinterpret_cast<const float4*>(out32 + (size_t)(rbase + rsub + i * 4) * e.ldo + col0 + cq);
                 }
                 float v[32];
                 if (col0 < e.N) tcgen05_ld_32x32(taddr + (uint32_t)c0, v);  // warp-uniform
@@ -404,7 +410,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
                         if (gp) {
                             float4* g4 = reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo);
                             if (epi == EPI_ADD_OUT) {
-                                float4 pv = *g4;
+                                const float4 pv = pre_add[i];
                                 val.x += pv.x, val.y += pv.y, val.z += pv.z, val.w += pv.w;
                             } else if (epi == EPI_RESIDUAL) {
                                 const float4 av = pre_add[i];
@@ -553,7 +559,9 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // widest tile that still gives every SM work: 256 columns halve the shared-memory operand traffic per flop,
     // narrow outputs (state / key projections) and short batches (decode) use smaller tiles to spread over SMs
     const long long m_tiles = (e.M + BM - 1) / BM;
-    if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2) return launch_tile<64, 7>(ctx, a, b, e);
+    if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2)
+        return (e.epi == EPI_ADD_OUT && e.out && !e.out16 && e.n_pairs == 0) ? launch_tile<64, 7, EPI_ADD_OUT, 1>(ctx, a, b, e)
+                                                                            : launch_tile<64, 7>(ctx, a, b, e);
     if (e.N <= 128 || m_tiles * ((e.N + 255) / 256) < ctx->sm_count) return launch_tile<128, 5>(ctx, a, b, e);
     // Four 48 KB stages help the long-K split product (141 -> 126 us at the model's shape, +8 % on plain products timed
     // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them

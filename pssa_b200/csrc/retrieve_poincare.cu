@@ -389,9 +389,11 @@ __global__ void __launch_bounds__(256) project_split_kernel(RetrieveParams p) {
     const int dk = p.dk, pitch = dk + 1, tid = threadIdx.x;
     const size_t q0 = (size_t)blockIdx.x * QT;
     const size_t ldq = p.ldq ? p.ldq : (size_t)dk;
-    for (int idx = tid; idx < QT * dk; idx += 256) {
+    const float* __restrict__ qsrc = p.q;
+#pragma unroll 8
+    for (int idx = tid; idx < QT * dk; idx += 256) {  // unrolled so that a thread's loads are in flight together
         const int r = idx / dk, c = idx % dk;
-        tile[r * pitch + c] = q0 + r < p.rows ? p.q[(q0 + r) * ldq + c] : 0.0f;
+        tile[r * pitch + c] = q0 + r < p.rows ? __ldg(qsrc + (q0 + r) * ldq + c) : 0.0f;
     }
     __syncthreads();
     if (tid < QT && q0 + tid < p.rows) {
