@@ -33,7 +33,10 @@ constexpr int BM = 128;      // rows per tile = UMMA M
 constexpr int BK = 64;       // bf16 per stage row = 128 bytes = one swizzle atom
 constexpr int UMMA_K = 16;   // K per tcgen05.mma for 16-bit operands
 constexpr int EPI_WARPS = 8;  // two warps per TMEM lane quadrant, each draining half of the tile's columns
-constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
+// Epilogue warps of the 3-stage 128 x 256 products of the block schedule. Sixteen (four per TMEM lane quadrant, 96
+// registers per thread) were measured: the products with light epilogues kept their times, the ones that prefetch two
+// fp32 inputs spilled and lost 60 %, so the epilogue is not short of warps and eight stay.
+constexpr int kWideEpiWarps = EPI_WARPS;
 constexpr unsigned kSpinLimit = 1u << 24;
 constexpr int STG_PITCH = 32;  // floats per staged row; 16-byte column quads are XOR-swizzled with the row (no padding, so four
                                // 48 KB operand stages fit beside the staging tiles of a 128 x 256 product)
@@ -178,8 +181,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // the epilogue warps stall on instruction fetch; the products of the model's block schedule get their own instantiations.
 constexpr int kRuntimeMode = -100;
 // OUTS fixes which outputs exist: 0 = read the pointers at run time, 1 = fp32 only, 2 = bf16 only.
-template <int BN, int STAGES, int MODE, int OUTS>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+// EW epilogue warps: EW / 4 per TMEM lane quadrant, each draining BN / (EW / 4) of the tile's columns.
+template <int BN, int STAGES, int MODE, int OUTS, int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_b,
                                                                             GemmEpilogue e) {
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -194,7 +198,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
     uint64_t* acc_full = empty_bar + STAGES;   // [2] accumulator written by the tensor cores
     uint64_t* acc_empty = acc_full + 2;        // [2] accumulator drained by the epilogue warps
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EPI_WARPS][32 rows][STG_PITCH]
+    float* stage = reinterpret_cast<float*>(tmem_slot + 4);  // [EW][32 rows][STG_PITCH]
     float* const out32 = OUTS == 2 ? nullptr : e.out;
     __nv_bfloat16* const out16 = OUTS == 1 ? nullptr : e.out16;
     const bool vec32 = out32 && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out32) & 15) == 0);
@@ -216,7 +220,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], EPI_WARPS);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], EW);  // one arrival per epilogue warp
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -294,10 +298,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_bf16_tcgen05_kernel(cons
             }
         }
     } else {
-        // epilogue warps 2..9: TMEM lane quadrant = warp % 4 (a hardware rule), column half = (warp - 2) / 4
+        // epilogue warps 2..EW+1: TMEM lane quadrant = warp % 4 (a hardware rule), column part = (warp - 2) / 4
         const int quad = warp & 3;
         const int half = (warp - 2) >> 2;
-        constexpr int HALF_COLS = BN / 2;
+        constexpr int HALF_COLS = BN / (EW / 4);
+        static_assert(EW % 4 == 0 && HALF_COLS % 32 == 0, "every epilogue warp drains whole 32-column chunks");
         float* stg = stage + (warp - 2) * (32 * STG_PITCH);
         const int cq = (lane & 7) * 4;   // column quad this lane stores after the transpose
         const int rsub = lane >> 3;      // row within each group of 4 rows
@@ -513,14 +518,14 @@ int32_t make_map(pssa_b200_ctx* ctx, CUtensorMap* map, const void* base, size_t 
     return PSSA_B200_OK;
 }
 
-template <int BN, int STAGES, int MODE = kRuntimeMode, int OUTS = 0>
+template <int BN, int STAGES, int MODE = kRuntimeMode, int OUTS = 0, int EW = EPI_WARPS>
 int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const GemmEpilogue& e) {
     CUtensorMap map_a, map_b;
     int32_t rc;
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
-    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EPI_WARPS * 32 * STG_PITCH * 4;
-    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS>;
+    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EW * 32 * STG_PITCH * 4;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS, EW>;
     static bool attr = false;
     if (!attr) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -528,7 +533,7 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     }
     long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
     unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
-    PSSA_CUDA(ctx, launch_dependent(kern, dim3(grid), dim3(GEMM_THREADS), smem, ctx->stream, map_a, map_b, e));
+    PSSA_CUDA(ctx, launch_dependent(kern, dim3(grid), dim3(64 + 32 * EW), smem, ctx->stream, map_a, map_b, e));
     // the profile facility keys on this name: one entry per epilogue family
     const char* name = e.epi == EPI_POINCARE    ? "gemm_bf16_tcgen05_kernel[Poincare distances]"
                        : e.n_pairs > 0          ? "gemm_bf16_tcgen05_kernel[split value read]"
@@ -567,13 +572,13 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
     // (their epilogue traffic is the limiter), so those keep three.
     const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
-    if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1>(ctx, a, b, e);
+    if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
-    if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1>(ctx, a, b, e);
-    if (e.epi == EPI_GATE) return launch_tile<256, 3, EPI_GATE, 0>(ctx, a, b, e);
-    if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 3, EPI_RESIDUAL, 1>(ctx, a, b, e);
-    if (e.epi == EPI_SILU && only16) return launch_tile<256, 3, EPI_SILU, 2>(ctx, a, b, e);
+    if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_GATE) return launch_tile<256, 3, EPI_GATE, 0, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 3, EPI_RESIDUAL, 1, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_SILU && only16) return launch_tile<256, 3, EPI_SILU, 2, kWideEpiWarps>(ctx, a, b, e);
     return launch_tile<256, 3>(ctx, a, b, e);
 }
 
