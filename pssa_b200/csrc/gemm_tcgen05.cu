@@ -60,6 +60,7 @@ struct GemmEpilogue {
     const float* res_in;
     size_t ld_add, ld_res;
     float res_scale;
+    int add_is_bf16;       // EPI_RESIDUAL: add_in points at bf16 values (row pitch ld_add in elements)
     // EPI_POINCARE: the accumulator is the inner product p.k of a point in the ball (row) and a bank key (column);
     // row_stat[row] = (|p|^2, 1/(1-|p|^2)), col_stat[col] = (|k|^2, 1/(1-|k|^2)); out = d(p, k)
     const float2* row_stat;
@@ -203,7 +204,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
     __nv_bfloat16* const out16 = OUTS == 1 ? nullptr : e.out16;
     const bool vec32 = out32 && (e.ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out32) & 15) == 0);
     const int epi = MODE == kRuntimeMode ? e.epi : MODE;  // a compile-time constant in the specialised instantiations
-    const bool vec_res = (epi == EPI_RESIDUAL || epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & 15) == 0) &&
+    const bool vec_res = (epi == EPI_RESIDUAL || epi == EPI_GATE) && e.ld_add % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.add_in) & (e.add_is_bf16 ? 7 : 15)) == 0) &&
                          (!e.res_in || (e.ld_res % 4 == 0 && ((reinterpret_cast<uintptr_t>(e.res_in) & 15) == 0)));
     const bool vec16 = out16 && (e.ld16 % 4 == 0) && ((reinterpret_cast<uintptr_t>(out16) & 7) == 0);
 
@@ -327,13 +328,19 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                 // EPI_RESIDUAL reads two more fp32 arrays with the output's access pattern: issue those loads first so
                 // they are in flight during the TMEM load and the transpose
                 float4 pre_add[8], pre_res[8];
+                uint2 raw_add[8];
                 const bool two_in = epi == EPI_RESIDUAL || epi == EPI_GATE;
                 const bool prefetch = two_in && interior && vec_res;
                 if (prefetch) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const size_t ro = (size_t)(rbase + rsub + i * 4);
-                        pre_add[i] = *reinterpret_cast<const float4*>(e.add_in + ro * e.ld_add + col0 + cq);
+                        if (epi == EPI_RESIDUAL && e.add_is_bf16)
+                            // kept as raw bits: converting here would wait for the load before the TMEM read is issued
+                            raw_add[i] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(e.add_in) +
+                                                                         ro * e.ld_add + col0 + cq);
+                        else
+                            pre_add[i] = *reinterpret_cast<const float4*>(e.add_in + ro * e.ld_add + col0 + cq);
                         pre_res[i] = e.res_in ? *reinterpret_cast<const float4*>(e.res_in + ro * e.ld_res + col0 + cq)
                                               : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
@@ -418,7 +425,12 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                                 const float4 pv = pre_add[i];
                                 val.x += pv.x, val.y += pv.y, val.z += pv.z, val.w += pv.w;
                             } else if (epi == EPI_RESIDUAL) {
-                                const float4 av = pre_add[i];
+                                float4 av = pre_add[i];
+                                if (e.add_is_bf16) {
+                                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw_add[i].x));
+                                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw_add[i].y));
+                                    av = make_float4(lo.x, lo.y, hi.x, hi.y);
+                                }
                                 val.x += av.x, val.y += av.y, val.z += av.z, val.w += av.w;
                                 if (e.res_in) {
                                     const float4 rv = pre_res[i];
@@ -452,7 +464,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                             if (gcol + q >= e.N) continue;
                             if (kind == -1) o[q] = fast_epilogue(e, o[q], gcol + q, 0.0f);
                             if (epi == EPI_RESIDUAL) {
-                                o[q] += e.add_in[(size_t)grow * e.ld_add + gcol + q];
+                                const size_t ai = (size_t)grow * e.ld_add + gcol + q;
+                                o[q] += e.add_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.add_in)[ai]) : e.add_in[ai];
                                 if (e.res_in) o[q] = fmaf(e.res_scale, o[q], e.res_in[(size_t)grow * e.ld_res + gcol + q]);
                             } else if (epi == EPI_GATE) {
                                 o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q], o[q],
@@ -576,7 +589,7 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
     if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1, kWideEpiWarps>(ctx, a, b, e);
-    if (e.epi == EPI_GATE) return launch_tile<256, 3, EPI_GATE, 0, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_GATE) return only16 ? launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e) : launch_tile<256, 3, EPI_GATE, 0, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 3, EPI_RESIDUAL, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_SILU && only16) return launch_tile<256, 3, EPI_SILU, 2, kWideEpiWarps>(ctx, a, b, e);
     return launch_tile<256, 3>(ctx, a, b, e);
@@ -595,14 +608,15 @@ int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, f
 }
 
 // out = res_in ? res_in + res_scale * (X W^T + add_in) : X W^T + add_in   (all fp32 [M, N] dense)
-int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const float* add_in,
-                                  const float* res_in, float res_scale, size_t M, size_t N, size_t K) {
+int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const void* add_in,
+                                  const float* res_in, float res_scale, size_t M, size_t N, size_t K, size_t ld_add_bf16) {
     int32_t rc = check_shape(ctx, x16, w16, M, N, K);
     if (rc) return rc;
     GemmEpilogue e{};
     e.out = out, e.out16 = nullptr, e.ldo = N, e.ld16 = 0;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = EPI_RESIDUAL, e.alpha = 1.0f;
-    e.add_in = add_in, e.res_in = res_in, e.ld_add = N, e.ld_res = N, e.res_scale = res_scale;
+    e.add_in = (const float*)add_in, e.res_in = res_in, e.ld_add = ld_add_bf16 ? ld_add_bf16 : N, e.ld_res = N, e.res_scale = res_scale;
+    e.add_is_bf16 = ld_add_bf16 ? 1 : 0;
     return dispatch(ctx, x16, w16, e);
 }
 

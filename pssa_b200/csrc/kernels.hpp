@@ -157,8 +157,9 @@ int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, f
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
                               const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K);
 // MLP output with both residuals fused: out = res_in ? res_in + res_scale*(X W^T + add_in) : X W^T + add_in
-int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const float* add_in,
-                                  const float* res_in, float res_scale, size_t M, size_t N, size_t K);
+// add_in is fp32 [M, N], or bf16 [M, ld_add_bf16] when ld_add_bf16 != 0
+int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const void* add_in,
+                                  const float* res_in, float res_scale, size_t M, size_t N, size_t K, size_t ld_add_bf16 = 0);
 // fp32-accurate product of operands pre-split into three bf16 pieces: a16 [M, 3K], b16 [N, 3K] (six partial products)
 int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void* b16, float* out, void* out_bf16, size_t M,
                                 size_t N, size_t K, size_t ldo, int terms = 6);
