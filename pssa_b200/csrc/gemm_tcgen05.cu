@@ -319,12 +319,15 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
             tcgen05_fence_after();
             const uint32_t taddr = tmem_base + buf * BN + half * HALF_COLS + ((uint32_t)(quad * 32) << 16);
             const int rbase = m0 + quad * 32;
-            // whole 32-row band and all of this warp's columns inside the matrix: no per-element bounds checks
-            const bool interior = rbase + 32 <= e.M && n0 + HALF_COLS <= e.N;
+            const bool rows_in = rbase + 32 <= e.M;  // whole 32-row band inside the matrix
             bool released = false;
 #pragma unroll 1
             for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
                 const int col0 = n0 + c0;
+                // Chunks that lie inside the matrix take the 16-byte path without per-element bounds checks; so does the
+                // matrix's last, partial chunk when N is a multiple of 4 (a lane's column quad is then all in or all out)
+                const bool interior = rows_in && (col0 + 32 <= e.N || (e.N & 3) == 0);
+                const bool lane_in = col0 + (lane & 7) * 4 + 4 <= e.N;
                 // EPI_RESIDUAL reads two more fp32 arrays with the output's access pattern: issue those loads first so
                 // they are in flight during the TMEM load and the transpose
                 float4 pre_add[8], pre_res[8];
@@ -334,6 +337,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                 if (prefetch) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
+                        if (!lane_in) break;
                         const size_t ro = (size_t)(rbase + rsub + i * 4);
                         if (epi == EPI_RESIDUAL && e.add_is_bf16)
                             // kept as raw bits: converting here would wait for the load before the TMEM read is issued
@@ -349,7 +353,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                     // per row group inside the store loop
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        pre_add[i] = *reinterpret_cast<const float4*>(out32 + (size_t)(rbase + rsub + i * 4) * e.ldo + col0 + cq);
+                        if (lane_in) pre_add[i] = *reinterpret_cast<const float4*>(out32 + (size_t)(rbase + rsub + i * 4) * e.ldo + col0 + cq);
                 }
                 float v[32];
                 if (col0 < e.N) tcgen05_ld_32x32(taddr + (uint32_t)c0, v);  // warp-uniform
@@ -419,9 +423,9 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                     for (int i = 0; i < 8; ++i) {
                         const int sr = i * 4 + rsub;  // staged row; its column quads are swizzled with (row & 7)
                         float4 val = *reinterpret_cast<const float4*>(stg + sr * STG_PITCH + ((((cq >> 2) ^ (sr & 7))) << 2));
-                        if (gp) {
-                            float4* g4 = reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo);
-                            if (epi == EPI_ADD_OUT) {
+                        if (!lane_in) break;
+                        {
+                            if (epi == EPI_ADD_OUT && gp) {
                                 const float4 pv = pre_add[i];
                                 val.x += pv.x, val.y += pv.y, val.z += pv.z, val.w += pv.w;
                             } else if (epi == EPI_RESIDUAL) {
@@ -442,8 +446,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                                 val.x = fmaf(gv.x, val.x, av.x * e.alpha), val.y = fmaf(gv.y, val.y, av.y * e.alpha);
                                 val.z = fmaf(gv.z, val.z, av.z * e.alpha), val.w = fmaf(gv.w, val.w, av.w * e.alpha);
                             }
-                            *g4 = val;
                         }
+                        if (gp) *reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo) = val;
                         if (bp) {
                             __nv_bfloat162 p0 = __floats2bfloat162_rn(val.x, val.y), p1 = __floats2bfloat162_rn(val.z, val.w);
                             uint2 pk;

@@ -9,10 +9,6 @@
 #include "kernels.hpp"
 #include "model.hpp"
 
-#ifndef PSSA_Z_FP32
-#define PSSA_Z_FP32 1
-#endif
-
 using namespace pssa;
 
 namespace {
@@ -275,18 +271,19 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             if ((rc = launch_residual(ctx, l == 0 ? nullptr : feat_in, ws.z, feat_out, rows * (size_t)d, rscale))) return rc;
         } else {
             // Tensor-core schedule: z = y/sqrt(s) + g*(W_proj m) + U*act never exists as one array. The memory projection's
-            // epilogue forms zp = g*acc + y/sqrt(s) (fp32 for the residual, bf16 as W1's operand); the rank-16 adapter
+            // epilogue forms zp = g*acc + y/sqrt(s), kept as bf16 only: it is W1's operand and W2's additive input (an fp32
+            // copy for the latter moved 200 MB more per block each way and did not change the logit error); the rank-16 adapter
             // term is one extra K block of both MLP products: W1*(zp + U act) = [W1 | W1 U] [zp; act] and
             // W2*h + U*act = [W2 | U] [h; act]. The combine kernel and the m_proj round trip disappear.
             const size_t ldz = m->d + 64, lda = 2 * m->d + 64;
-            if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, PSSA_Z_FP32 ? ws.z : nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale, rows,
+            if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale, rows,
                                             m->d, m->d)))
                 return rc;
             if ((rc = launch_pack_act(ctx, ws.proj + m->off_act, nc, ws.z_bf16, ldz, (int)m->d, ws.act_bf16, lda, (int)(2 * m->d), rows))) return rc;
             if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, b.w1cat_bf16, nullptr, ws.act_bf16, rows, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
                 return rc;
-            if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2cat_bf16, feat_out, PSSA_Z_FP32 ? (const void*)ws.z : ws.z_bf16,
-                                                l == 0 ? nullptr : feat_in, rscale, rows, m->d, lda, PSSA_Z_FP32 ? 0 : ldz)))
+            if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2cat_bf16, feat_out, ws.z_bf16,
+                                                l == 0 ? nullptr : feat_in, rscale, rows, m->d, lda, ldz)))
                 return rc;
         }
         if (observe && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, ws.weights, (int)m->cap, m->obs.q_pnc, k, ws.m_val,
