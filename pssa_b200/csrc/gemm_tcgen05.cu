@@ -649,7 +649,7 @@ int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void*
     GemmEpilogue e{};
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = ldo, e.ld16 = N;
     e.M = (int)M, e.N = (int)N, e.K = (int)(3 * K), e.epi = EPI_NONE, e.alpha = 1.0f;
-    e.n_pairs = terms == 3 ? 3 : 6, e.seg_kb = (int)(K / BK);
+    e.n_pairs = terms == 3 ? 3 : terms == 1 ? 1 : 6, e.seg_kb = (int)(K / BK);
     const unsigned char pa[6] = {0, 0, 1, 0, 1, 2}, pb[6] = {0, 1, 0, 2, 1, 0};
     for (int i = 0; i < 6; ++i) e.pair_a[i] = pa[i], e.pair_b[i] = pb[i];
     return dispatch(ctx, a16, b16, e);

@@ -87,7 +87,8 @@ struct RetrieveParams {
     size_t rows;
     int dk, dv, cap, count, top_k;
     float tau;
-    int value_terms;       // tensor-core value read: 3 = leading partial products only (bf16-grade result), else all six
+    int value_terms;       // tensor-core value read: 1 = leading pieces only (a plain bf16 product), 3 = the three leading
+                           // partial products (error near 2^-16), else all six (fp32-accurate)
     int f32_distance;      // fast mode: squared differences accumulated in fp32 instead of f64 (ignored when exact)
     int skip_weights;      // all-slots, non-exact, w_split set: do not write the fp32 weight rows back (only the pieces are read)
     // tensor-core distances (non-exact, dk % 64 == 0; used when all four are set): q_split [rows, 3*dk] bf16 and

@@ -470,7 +470,7 @@ __device__ __forceinline__ float weight_of(float min_dist, float d, float tau) {
 // All-slots softmax out of registers (non-exact mode, capacity a multiple of 128 and at most 128 * GROUPS, at least one
 // stored slot): a lane owns four consecutive slots of every 128 and rows move as 16-byte pieces; a warp walks rows
 // q, q + stride, ... with the next row's distances already in flight. Same formulas as the general kernel below (the sum
-// is grouped differently). value_terms == 3: the consumer keeps bf16-grade results (two leading pieces of every weight),
+// is grouped differently). value_terms == 1 or 3: the consumer keeps bf16-grade results (one or two leading pieces of every weight),
 // so the weights may use ex2.approx and one reciprocal per row (relative error near 1e-6 instead of 1e-7); a temperature
 // too small for a finite reciprocal keeps the division.
 template <int GROUPS>
@@ -481,7 +481,8 @@ __global__ void __launch_bounds__(256) softmax_all_slots_kernel(RetrieveParams p
     const int cap = p.cap, count = p.count;
     const float tau = p.tau;
     const float inv_tau = 1.0f / tau;
-    const bool lite = p.value_terms == 3 && inv_tau < CUDART_INF_F;
+    const bool lite = (p.value_terms == 3 || p.value_terms == 1) && inv_tau < CUDART_INF_F;
+    const bool second = p.value_terms != 1;  // the one-term read uses the leading piece only
     const float scale2 = inv_tau * 1.4426950408889634f;
     const size_t stride = (size_t)gridDim.x * 8;
     size_t q = (size_t)blockIdx.x * 8 + warp;
@@ -542,7 +543,7 @@ __global__ void __launch_bounds__(256) softmax_all_slots_kernel(RetrieveParams p
                         pb[e] = __float2bfloat16_rn(wn[e] - __bfloat162float(pa[e]));
                     }
                     *reinterpret_cast<uint2*>(ws + i) = *reinterpret_cast<const uint2*>(pa);
-                    *reinterpret_cast<uint2*>(ws + cap + i) = *reinterpret_cast<const uint2*>(pb);
+                    if (second) *reinterpret_cast<uint2*>(ws + cap + i) = *reinterpret_cast<const uint2*>(pb);
                 } else if (ws) {
                     __nv_bfloat16 pa[4], pb[4], pc[4];
 #pragma unroll
@@ -896,7 +897,7 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         // all-slots value read on the tensor cores: m = W x V as six bf16 partial products (fp32-accurate), or the
         // leading three (error near 2^-16 of the row scale) when the caller only keeps a bf16 result
         if ((rc = launch_gemm_bf16_split3(ctx, p.w_split, p.v_split, p.m_val, p.m_bf16, p.rows, p.dv, p.cap, p.dv,
-                                          p.value_terms == 3 ? 3 : 6)))
+                                          p.value_terms == 3 ? 3 : p.value_terms == 1 ? 1 : 6)))
             return rc;
     } else if (p.count > 0 && !topk) {
         dim3 grid((unsigned)qblocks, (unsigned)((p.dv + 63) / 64));
