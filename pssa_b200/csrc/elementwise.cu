@@ -242,25 +242,6 @@ __global__ void __launch_bounds__(256) observe_rows_kernel(const uint32_t* __res
     }
 }
 
-// The adapter's rank-16 term U * act rides in the two MLP products as one extra 64-wide K block (16 activations + 48
-// zeros): this kernel writes that block, as bf16, behind the K columns of both products' A operands.
-//   dst_a [rows, ld_a] gets it at column off_a, dst_b [rows, ld_b] at column off_b.
-__global__ void __launch_bounds__(256) pack_act_kernel(const float* __restrict__ act, size_t ldact, __nv_bfloat16* __restrict__ dst_a,
-                                                       size_t ld_a, int off_a, __nv_bfloat16* __restrict__ dst_b, size_t ld_b,
-                                                       int off_b, size_t rows) {
-    pdl_trigger();  // the next kernel in the stream may start its prologue now ...
-    pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (row, group of 8 columns)
-    const size_t row = idx >> 3;
-    const int g = (int)(idx & 7);
-    if (row >= rows) return;
-    __nv_bfloat16 v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn(g < 2 ? act[row * ldact + g * 8 + j] : 0.0f);
-    *reinterpret_cast<uint4*>(dst_a + row * ld_a + off_a + g * 8) = *reinterpret_cast<const uint4*>(v);
-    *reinterpret_cast<uint4*>(dst_b + row * ld_b + off_b + g * 8) = *reinterpret_cast<const uint4*>(v);
-}
-
 // bf16 weight rows with the adapter block appended: dst [n, k + 64] = bf16(src [n, k]) | bf16(tail [n, 16]) | 48 zeros
 __global__ void __launch_bounds__(256) pack_weight_cat_kernel(const float* __restrict__ src, const float* __restrict__ tail,
                                                               __nv_bfloat16* __restrict__ dst, size_t n, int k) {
@@ -391,15 +372,6 @@ int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_
     observe_rows_kernel<<<(unsigned)lanes, 256, 0, ctx->stream>>>(last_rows, weights, cap, q_pnc, k, m_val, z_direct, feat_out, feat_in,
                                                                  scale != 0.0f ? 1.0f / scale : 0.0f, d, out);
     return after_launch(ctx, "observe_rows_kernel");
-}
-
-int32_t launch_pack_act(pssa_b200_ctx* ctx, const float* act, size_t ldact, void* dst_a, size_t ld_a, int off_a, void* dst_b, size_t ld_b,
-                        int off_b, size_t rows) {
-    if (ldact % 1 || ld_a % 8 || ld_b % 8 || off_a % 8 || off_b % 8 || ((uintptr_t)dst_a & 15) || ((uintptr_t)dst_b & 15))
-        return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "adapter block packing needs 16-byte aligned bf16 rows");
-    PSSA_CUDA(ctx, launch_dependent(pack_act_kernel, dim3(blocks_for(rows * 8, 256)), dim3(256), 0, ctx->stream, act, ldact, (__nv_bfloat16*)dst_a,
-                                    ld_a, off_a, (__nv_bfloat16*)dst_b, ld_b, off_b, rows));
-    return after_launch(ctx, "pack_act_kernel");
 }
 
 int32_t launch_pack_weight_cat(pssa_b200_ctx* ctx, const float* src, const float* tail, void* dst, size_t n, int k) {

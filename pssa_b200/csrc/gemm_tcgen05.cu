@@ -65,6 +65,11 @@ struct GemmEpilogue {
     // row_stat[row] = (|p|^2, 1/(1-|p|^2)), col_stat[col] = (|k|^2, 1/(1-|k|^2)); out = d(p, k)
     const float2* row_stat;
     const float2* col_stat;
+    // column-range table only: the last range [c3, N) is also stored as bf16 at column (col - c3) of two side buffers
+    // (the adapter activations, which ride as extra K columns of both MLP products); null = not wanted
+    __nv_bfloat16* side_a;
+    __nv_bfloat16* side_b;
+    size_t ld_side_a, ld_side_b;
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------------
@@ -448,6 +453,14 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                             }
                         }
                         if (gp) *reinterpret_cast<float4*>(gp + (size_t)i * 4 * e.ldo) = val;
+                        if (epi < 0 && e.side_a && gcol >= e.c3) {
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(val.x, val.y), p1 = __floats2bfloat162_rn(val.z, val.w);
+                            uint2 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&p0), pk.y = *reinterpret_cast<uint32_t*>(&p1);
+                            const size_t srow = (size_t)(rbase + rsub + i * 4);
+                            *reinterpret_cast<uint2*>(e.side_a + srow * e.ld_side_a + (gcol - e.c3)) = pk;
+                            *reinterpret_cast<uint2*>(e.side_b + srow * e.ld_side_b + (gcol - e.c3)) = pk;
+                        }
                         if (bp) {
                             __nv_bfloat162 p0 = __floats2bfloat162_rn(val.x, val.y), p1 = __floats2bfloat162_rn(val.z, val.w);
                             uint2 pk;
@@ -481,6 +494,10 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                                 *gp = o[q];
                             }
                             if (out16) out16[(size_t)grow * e.ld16 + gcol + q] = __float2bfloat16_rn(o[q]);
+                            if (epi < 0 && e.side_a && gcol + q >= e.c3) {
+                                e.side_a[(size_t)grow * e.ld_side_a + (gcol + q - e.c3)] = __float2bfloat16_rn(o[q]);
+                                e.side_b[(size_t)grow * e.ld_side_b + (gcol + q - e.c3)] = __float2bfloat16_rn(o[q]);
+                            }
                         }
                     }
                 }
@@ -673,12 +690,17 @@ int32_t launch_gemm_bf16_poincare(pssa_b200_ctx* ctx, const void* a16, const voi
 }
 
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
-                             size_t ldo, int c1, int c2, int c3) {
+                             size_t ldo, int c1, int c2, int c3, void* side_a, size_t ld_side_a, void* side_b, size_t ld_side_b) {
     int32_t rc = check_shape(ctx, x16, w16, M, N, K);
     if (rc) return rc;
     GemmEpilogue e{};
     e.out = out, e.out16 = nullptr, e.ldo = ldo, e.ld16 = 0;
     e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = -1, e.alpha = 1.0f, e.c1 = c1, e.c2 = c2, e.c3 = c3;
+    if (side_a && side_b) {
+        if (c3 % 4 != 0 || ld_side_a % 4 != 0 || ld_side_b % 4 != 0 || (reinterpret_cast<uintptr_t>(side_a) & 7) || (reinterpret_cast<uintptr_t>(side_b) & 7))
+            return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 concatenated GEMM: side buffers need 8-byte aligned rows");
+        e.side_a = (__nv_bfloat16*)side_a, e.side_b = (__nv_bfloat16*)side_b, e.ld_side_a = ld_side_a, e.ld_side_b = ld_side_b;
+    }
     return dispatch(ctx, x16, w16, e);
 }
 

@@ -169,8 +169,10 @@ int32_t launch_gemm_bf16_split3(pssa_b200_ctx* ctx, const void* a16, const void*
 int32_t launch_gemm_bf16_poincare(pssa_b200_ctx* ctx, const void* a16, const void* b16, const float2* row_stat,
                                   const float2* col_stat, float* dist, size_t M, size_t N, size_t K, size_t ldo);
 // concatenated x-side projections: columns [0,c1) softplus, [c1,c2) identity, [c2,c3) sigmoid, [c3,N) SiLU
+// side_a / side_b (both or neither): the last range is also stored as bf16 at column (col - c3) of two more buffers
 int32_t launch_gemm_bf16_cat(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, size_t M, size_t N, size_t K,
-                             size_t ldo, int c1, int c2, int c3);
+                             size_t ldo, int c1, int c2, int c3, void* side_a = nullptr, size_t ld_side_a = 0, void* side_b = nullptr,
+                             size_t ld_side_b = 0);
 
 // elementwise.cu
 int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t* ids, const float* feats, const float* gamma,
@@ -185,8 +187,6 @@ int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_
                             int k, const float* m_val, const float* z_direct, const float* feat_out, const float* feat_in, float scale,
                             int d, float* out);
 // adapter term folded into the MLP products (bf16 mode): see elementwise.cu
-int32_t launch_pack_act(pssa_b200_ctx* ctx, const float* act, size_t ldact, void* dst_a, size_t ld_a, int off_a, void* dst_b, size_t ld_b,
-                        int off_b, size_t rows);
 int32_t launch_pack_weight_cat(pssa_b200_ctx* ctx, const float* src, const float* tail, void* dst, size_t n, int k);
 int32_t launch_times_adapter(pssa_b200_ctx* ctx, const float* w, const float* u, float* out, size_t n, int k);
 int32_t launch_cross_entropy(pssa_b200_ctx* ctx, const float* logits, const uint32_t* targets, float* loss, size_t rows, int v);

@@ -49,6 +49,8 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
         ws = Workspace();
         return cuda_fail(ctx, e, "activation workspace allocation");
     }
+    // the 48 pad columns of the MLP operands' extra K block are never written again and must read as zero
+    PSSA_CUDA(ctx, cudaMemsetAsync(ws.base, 0, total, ctx->stream));
     ws.bytes = total, ws.rows = rows, ws.lanes = lanes;
     char* b = ws.base;
     ws.ids = (uint32_t*)(b + o_ids), ws.lane_off = (uint32_t*)(b + o_off), ws.lane_len = (uint32_t*)(b + o_len);
@@ -203,8 +205,10 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             for (auto& p : ps)
                 if ((rc = launch_gemm_exact(ctx, ws.x_norm, b.w[p.id], ws.proj + p.off, rows, p.n, m->d, nc, p.epi, 1.0f))) return rc;
         } else {
+            // the adapter activations (last column range) also go, as bf16, into the extra K block of both MLP operands
             if ((rc = launch_gemm_bf16_cat(ctx, ws.x_bf16, b.wcat_bf16, ws.proj, rows, nc, m->d, nc, (int)m->off_b, (int)m->off_gate,
-                                           (int)m->off_act)))
+                                           (int)m->off_act, (char*)ws.z_bf16 + m->d * 2, m->d + 64, (char*)ws.act_bf16 + 2 * m->d * 2,
+                                           2 * m->d + 64)))
                 return rc;
         }
         // stage 3: SSM with the lane carries of this block (src/gpu_batch.rs:582-619)
@@ -281,7 +285,6 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale, rows,
                                             m->d, m->d)))
                 return rc;
-            if ((rc = launch_pack_act(ctx, ws.proj + m->off_act, nc, ws.z_bf16, ldz, (int)m->d, ws.act_bf16, lda, (int)(2 * m->d), rows))) return rc;
             if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, b.w1cat_bf16, nullptr, ws.act_bf16, rows, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
                 return rc;
             if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2cat_bf16, feat_out, ws.z_bf16,
