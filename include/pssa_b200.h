@@ -38,7 +38,8 @@ typedef enum pssa_b200_status {
     PSSA_B200_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up */
     PSSA_B200_ERR_UNSUPPORTED = 6,      /* option the device path refuses (src/pssa.rs:2080-2243) */
     PSSA_B200_ERR_TOKEN = 7,            /* token id outside the vocabulary */
-    PSSA_B200_ERR_CANCELLED = 8         /* the caller's cancellation callback fired */
+    PSSA_B200_ERR_CANCELLED = 8,        /* the caller's cancellation callback fired */
+    PSSA_B200_ERR_BANK = 9              /* device-resident bank metadata / slot id out of range, or a key outside the ball */
 } pssa_b200_status;
 
 typedef struct pssa_b200_ctx pssa_b200_ctx;     /* one device, one stream, one scratch arena */
@@ -67,8 +68,16 @@ int32_t pssa_b200_ctx_reserve(pssa_b200_ctx* ctx, size_t bytes);
 /* Device-side waits (mbarrier phases of the tensor-core pipeline) are bounded; when one expires the kernel
  * records it and returns. This reads and clears that record: PSSA_B200_OK or PSSA_B200_ERR_TIMEOUT. The same word
  * carries PSSA_B200_ERR_TOKEN when a DEVICE-resident token id (which the host cannot check) was outside the vocabulary:
- * the embedding of id 0 was read in its place, so nothing is accessed out of bounds. */
+ * the embedding of id 0 was read in its place, so nothing is accessed out of bounds; and PSSA_B200_ERR_BANK when
+ * pssa_b200_bank_insert_protected_dev refused a write. */
 int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx);
+
+/* Failure-detection self-test (the role of the reference's host-injected driver failures, tests/backend_cuda.rs:599-649,
+ * for the one failure class that lives on the device): enqueues a one-warp kernel that waits at most `polls`
+ * (1..2^20) polls on a barrier nothing arrives at, using the tensor-core pipeline's own bounded-wait helper. The wait
+ * expires, the kernel records it and returns; pssa_b200_ctx_poll_status then reports PSSA_B200_ERR_TIMEOUT once and
+ * the context stays usable. Nothing faults or hangs. */
+int32_t pssa_b200_ctx_selftest_wait_expiry(pssa_b200_ctx* ctx, uint32_t polls);
 
 /*
  * Per-kernel device timing, the role of the reference's `StageTrace` spans (src/training_diagnostics.rs:74-125,
@@ -217,8 +226,11 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
  * the ring insert (src/memory.rs:268-303) as called by `insert_training_memory_at` (src/pssa.rs:3705-3737).
  * All DEVICE pointers: keys [cap,d_key], norm_sq [cap], values [cap,d_val], confidence [cap], last_seen_step [cap]
  * (u64), meta = {count, write_head} (u64, updated), key_pnc [n,d_key] (points inside the ball), val [n,d_val],
- * surprise [n], step [n] (u64). slots_out [n] (i64, NULL to skip): the slot written, or -1 when the slot defended
- * itself. While count < capacity a write appends; afterwards the ring head is gated: gain = max((1-exp(-dt/60))^2,
+ * surprise [n], step [n] (u64). slots_out [n] (i64, NULL to skip): the slot written, -1 when the slot defended
+ * itself, or -2 when the write was refused: meta and winning_slots live on the device where the host cannot check
+ * them, so a count above capacity, a ring head or winning slot >= capacity, or a key that is not inside the open unit
+ * ball (the reference asserts it, src/memory.rs:273-277) skips that write, touches nothing out of bounds and raises
+ * PSSA_B200_ERR_BANK in the context's status word (pssa_b200_ctx_poll_status). While count < capacity a write appends; afterwards the ring head is gated: gain = max((1-exp(-dt/60))^2,
  * 0.005), damage = 0.08*surprise*gain; confidence > damage keeps the slot (confidence -= damage), otherwise the
  * slot is overwritten, confidence = 1 and the head advances.
  *
@@ -456,7 +468,10 @@ int32_t pssa_b200_model_load_checkpoint(pssa_b200_ctx* ctx, const void* bytes, s
  * While enabled (world > 1), pssa_b200_model_prefill_batch_dev treats its lanes as this rank's shards: lane l must be
  * the same sequence on every rank (a rank may hold zero tokens of it), every rank gets the same final recurrent
  * state, and the logits a rank returns are those of ITS last token of each lane (the caller keeps the last
- * non-empty rank's). world <= 1 or exchange == NULL switches it off.
+ * non-empty rank's). Every rank must hold at least one token of some lane; the library can only check its own rank, so
+ * the caller validates this on all ranks together (from the sequence lengths, which every rank knows) before any rank
+ * calls, otherwise the ranks that do hold tokens wait in the exchange for the one that returned an error.
+ * world <= 1 or exchange == NULL switches it off.
  */
 typedef int32_t (*pssa_b200_exchange_fn)(void* arg, const void* send_dev, void* recv_dev, size_t bytes);
 int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t world, void* send_dev, void* recv_dev,

@@ -7,7 +7,7 @@ PKG = pathlib.Path(__file__).resolve().parent
 LIB_PATH = PKG / "libpssa_b200.so"
 
 OK, ERR_INVALID_ARGUMENT, ERR_SHAPE, ERR_CUDA, ERR_FATAL_CUDA, ERR_TIMEOUT, ERR_UNSUPPORTED, ERR_TOKEN, \
-    ERR_CANCELLED = range(9)
+    ERR_CANCELLED, ERR_BANK = range(10)
 
 _fp = C.POINTER(C.c_float)
 _vp = C.c_void_p
@@ -40,6 +40,7 @@ SIGNATURES = {
     "pssa_b200_adapter_plastic_update_dev": (C.c_int32, [_vp] * 5 + [_sz, _sz]),
     "pssa_b200_adapter_consolidate_dev": (C.c_int32, [_vp, _vp, _vp, _sz, C.c_float]),
     "pssa_b200_ctx_poll_status": (C.c_int32, [_vp]),
+    "pssa_b200_ctx_selftest_wait_expiry": (C.c_int32, [_vp, C.c_uint32]),
     "pssa_b200_gemm_xwt": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _vp, C.c_int32, C.c_float, C.c_int32]),
     "pssa_b200_gemm_xwt_dev": (C.c_int32, [_vp, _vp, _vp, _sz, _sz, _sz, _vp, _sz, C.c_int32, C.c_float, C.c_int32]),
     "pssa_b200_model_create": (C.c_int32, [_vp, _vp, C.c_uint32, C.POINTER(_vp)]),

@@ -153,6 +153,13 @@ int32_t pssa_b200_ctx_set_scan_chunks(pssa_b200_ctx* ctx, uint32_t chunks) {
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_ctx_selftest_wait_expiry(pssa_b200_ctx* ctx, uint32_t polls) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    if (polls == 0 || polls > (1u << 20)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "selftest: polls must be in 1..2^20");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    return launch_wait_expiry_selftest(ctx, polls);
+}
+
 // ------------------------------------------------------------------ scan operator
 
 int32_t pssa_b200_affine_scan_dev(pssa_b200_ctx* ctx, float* scan_a, float* scan_b, size_t lanes, size_t len,
@@ -630,6 +637,8 @@ int32_t pssa_b200_ctx_poll_status(pssa_b200_ctx* ctx) {
         PSSA_CUDA(ctx, cudaMemsetAsync(ctx->status_dev, 0, sizeof(int), ctx->stream));
         if (status == PSSA_B200_ERR_TOKEN)
             return fail(ctx, status, "a device-resident token ID was outside the model vocabulary (row 0 was read in its place)");
+        if (status == PSSA_B200_ERR_BANK)
+            return fail(ctx, status, "a protected bank write was refused: slot id or bank metadata out of range, or key outside the unit ball");
         return fail(ctx, status, "a bounded device-side wait expired (status %d)", status);
     }
     return PSSA_B200_OK;

@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -75,6 +76,16 @@ inline int32_t cuda_fail(pssa_b200_ctx* ctx, cudaError_t e, const char* what) {
         cudaError_t e__ = (call);                                 \
         if (e__ != cudaSuccess) return pssa::cuda_fail(ctx, e__, #call); \
     } while (0)
+
+// Function attributes such as the opt-in dynamic shared memory size are per DEVICE, while a launcher's static flag is per
+// process: a host that opens contexts on several GPUs must set the attribute once on each. One bit per CUDA ordinal.
+struct PerDeviceOnce {
+    std::atomic<unsigned long long> mask{0};
+    bool need(int device) const { return device < 0 || device >= 64 || !(mask.load(std::memory_order_acquire) >> device & 1ull); }
+    void done(int device) {
+        if (device >= 0 && device < 64) mask.fetch_or(1ull << device, std::memory_order_release);
+    }
+};
 
 // Arena: reset at the start of an entry point, then bump-allocate 256-byte aligned blocks.
 int32_t arena_reserve(pssa_b200_ctx* ctx, size_t bytes);

@@ -307,13 +307,13 @@ int32_t launch_embed_norm(pssa_b200_ctx* ctx, const float* embed, const uint32_t
     size_t smem = (size_t)8 * d * sizeof(float);
     if (smem > 200 * 1024)
         return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 norm: latent width %d exceeds one CTA's shared memory; refusing launch", d);
-    static bool attr[2] = {false, false};
-    if (smem > 48 * 1024 && !attr[exact]) {
+    static PerDeviceOnce attr[2];
+    if (smem > 48 * 1024 && attr[exact].need(ctx->device)) {
         if (exact)
             PSSA_CUDA(ctx, cudaFuncSetAttribute(embed_norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         else
             PSSA_CUDA(ctx, cudaFuncSetAttribute(embed_norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr[exact] = true;
+        attr[exact].done(ctx->device);
     }
     unsigned blocks = blocks_for(rows, 8);
     if (exact)

@@ -82,9 +82,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 // bounded wait: false when the phase did not complete within the spin budget
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned limit = kSpinLimit) {
     uint32_t addr = smem_u32(bar);
-    for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    for (unsigned spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
@@ -560,10 +560,10 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
     size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EW * 32 * STG_PITCH * 4;
     auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS, EW>;
-    static bool attr = false;
-    if (!attr) {
+    static PerDeviceOnce attr;  // per instantiation and per device
+    if (attr.need(ctx->device)) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr = true;
+        attr.done(ctx->device);
     }
     long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
     unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
@@ -616,7 +616,24 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     return launch_tile<256, 3>(ctx, a, b, e);
 }
 
+// Self-test of the bounded wait: one warp initialises an mbarrier that nothing ever arrives at (no copy in flight, no
+// other CTA) and waits on it with the pipeline's own helper and a caller-chosen poll limit. The wait gives up, the kernel
+// records PSSA_B200_ERR_TIMEOUT in the status word exactly as the GEMM pipeline does, and returns normally.
+__global__ void __launch_bounds__(32) wait_expiry_selftest_kernel(int* status, unsigned polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!mbar_wait(&bar, 0, polls)) atomicExch(status, PSSA_B200_ERR_TIMEOUT);
+    }
+}
+
 }  // namespace
+
+int32_t launch_wait_expiry_selftest(pssa_b200_ctx* ctx, unsigned polls) {
+    wait_expiry_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, polls);
+    return after_launch(ctx, "wait_expiry_selftest_kernel");
+}
 
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
                          size_t K, size_t ldo, int epi, float alpha, size_t ld16) {

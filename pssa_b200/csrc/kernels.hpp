@@ -141,6 +141,7 @@ struct BankWriteParams {
     long long* slots_out;        // [n] written slot or -1 (defended); may be null
     const unsigned* winning_slots;  // null = reference behaviour (ring head); else the slot each write targets
     float eta;                   // rank-1 step of the winning-slot mode
+    int* status;                 // context status word (set by the launcher): PSSA_B200_ERR_BANK on a refused write
 };
 int32_t launch_bank_insert_protected(pssa_b200_ctx* ctx, const BankWriteParams& p);
 int32_t launch_plastic_update(pssa_b200_ctx* ctx, float* up_fast, const float* value, const float* ad_out, const float* ad_act,
@@ -151,6 +152,8 @@ int32_t launch_consolidate(pssa_b200_ctx* ctx, float* up_fast, float* up_slow, s
 int32_t launch_gemm_exact(pssa_b200_ctx* ctx, const float* x, const float* w, float* out, size_t M, size_t N, size_t K,
                           size_t ldo, int epi, float alpha);
 
+// gemm_tcgen05.cu: one warp waits `polls` polls on an mbarrier nobody arrives at and records the expiry (self-test)
+int32_t launch_wait_expiry_selftest(pssa_b200_ctx* ctx, unsigned polls);
 // gemm_tcgen05.cu: bf16 operands [rows, K] row-major, fp32 accumulate in TMEM; out fp32 [M, ldo] and/or bf16 [M, N]
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
                          size_t K, size_t ldo, int epi, float alpha, size_t ld16 = 0);  // ld16: row pitch of out_bf16 (0 = N)

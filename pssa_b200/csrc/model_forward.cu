@@ -147,12 +147,15 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
     const size_t ctas = lanes * ((m->d + 63) / 64);
     const size_t slots = (size_t)ctx->sm_count * 4;
     size_t n_chunks = 1;
-    if (!single_token && (m->sp.active || ctas <= (size_t)ctx->sm_count)) {
+    if (m->sp.active) {
+        // Must be identical on every rank (it sizes the all-gather and the record order the fold walks), so it depends
+        // only on quantities every rank shares: the lane count, the model width, the SM count and the exchange capacity --
+        // never on this rank's shard lengths, which differ between ranks (a shard may even be a single token).
         n_chunks = std::min<size_t>(16, std::max<size_t>(1, slots / ctas));
-        if (m->sp.active)  // identical on every rank: depends on the lane count and the buffer capacity only
-            n_chunks = std::min(n_chunks, std::max<size_t>(1, m->sp.capacity / lanes));
-        else
-            n_chunks = std::min(n_chunks, std::max<size_t>(1, max_len / 128));
+        n_chunks = std::min(n_chunks, std::max<size_t>(1, m->sp.capacity / lanes));
+    } else if (!single_token && ctas <= (size_t)ctx->sm_count) {
+        n_chunks = std::min<size_t>(16, std::max<size_t>(1, slots / ctas));
+        n_chunks = std::min(n_chunks, std::max<size_t>(1, max_len / 128));
     }
     const bool two_pass = m->sp.active || n_chunks > 1;
     const size_t vlanes = lanes * n_chunks;
@@ -505,7 +508,10 @@ int32_t pssa_b200_model_prefill_batch_dev(pssa_b200_model* m, const uint32_t* id
             head_lane.push_back(l);
         }
     }
-    if (rows == 0 && m->sp.world > 1)  // the other ranks would wait in the exchange for ever
+    // A rank with no token at all cannot take part in the per-block exchange. This check is local: the CALLER must make
+    // the same decision on every rank before calling (every rank knows all sequence lengths), or the other ranks would
+    // enqueue an all-gather this rank never joins.
+    if (rows == 0 && m->sp.world > 1)
         return fail(ctx, PSSA_B200_ERR_SHAPE, "sequence-parallel prefill: rank %u holds no token of any lane", m->sp.rank);
     if (rows == 0) return PSSA_B200_OK;
     if (span > m->max_rows)

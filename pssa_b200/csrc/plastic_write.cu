@@ -27,6 +27,10 @@ __device__ __forceinline__ float refractory_gain(unsigned long long delta_tokens
 }
 
 // One CTA walks the writes in order. meta = {count, write_head}.
+// Slot ids and the two meta words live on the device, where the host cannot validate them: a write whose target would
+// fall outside the bank (count > cap, head or winning slot >= cap) or whose key is not inside the open unit ball
+// (the reference asserts this, src/memory.rs:273-277) is skipped, reported as slot -2 and recorded in the context's
+// status word; nothing is read or written out of bounds.
 __global__ void __launch_bounds__(256) bank_insert_protected_kernel(BankWriteParams p) {
     __shared__ long long s_slot;   // slot to write, -1 = defended
     __shared__ float s_norm_sq;
@@ -38,13 +42,29 @@ __global__ void __launch_bounds__(256) bank_insert_protected_kernel(BankWritePar
             unsigned long long count = p.meta[0], head = p.meta[1];
             const unsigned long long step = p.step[w];
             long long slot;
-            if (p.winning_slots == nullptr && count < (unsigned long long)p.cap) {
+            const unsigned long long target = p.winning_slots ? (unsigned long long)p.winning_slots[w] : head;
+            float key_norm_sq = 0.0f;
+            bool bad = count > (unsigned long long)p.cap || ((p.winning_slots || count == (unsigned long long)p.cap) && target >= (unsigned long long)p.cap);
+            if (!bad && p.winning_slots == nullptr) {
+                // memory.rs:181-192: f64 sum of squares, nudged below one
+                double n2 = 0.0;
+                for (int i = 0; i < p.dk; ++i) {
+                    double v = (double)key[i];
+                    n2 = __dadd_rn(n2, __dmul_rn(v, v));
+                }
+                bad = !(n2 < 1.0);  // also catches NaN
+                key_norm_sq = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;
+            }
+            if (bad) {
+                slot = -2;
+                if (p.status) atomicExch(p.status, PSSA_B200_ERR_BANK);
+            } else if (p.winning_slots == nullptr && count < (unsigned long long)p.cap) {
                 slot = (long long)count;  // memory.rs:316-320: append while the bank is not full
                 p.meta[0] = count + 1;
                 p.confidence[slot] = 1.0f;
                 p.last_seen[slot] = step;
             } else {
-                const unsigned long long idx = p.winning_slots ? (unsigned long long)p.winning_slots[w] : head;
+                const unsigned long long idx = target;
                 // defense.rs:45-67
                 const unsigned long long seen = p.last_seen[idx];
                 const unsigned long long dt = step >= seen ? step - seen : 0;
@@ -61,15 +81,7 @@ __global__ void __launch_bounds__(256) bank_insert_protected_kernel(BankWritePar
                     if (p.winning_slots == nullptr) p.meta[1] = (head + 1) % (unsigned long long)p.cap;  // memory.rs:279-283
                 }
             }
-            if (slot >= 0 && p.winning_slots == nullptr) {
-                // memory.rs:181-192: f64 sum of squares, nudged below one
-                double n2 = 0.0;
-                for (int i = 0; i < p.dk; ++i) {
-                    double v = (double)key[i];
-                    n2 = __dadd_rn(n2, __dmul_rn(v, v));
-                }
-                s_norm_sq = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;
-            }
+            s_norm_sq = key_norm_sq;
             s_slot = slot;
             if (p.slots_out) p.slots_out[w] = slot;
         }
@@ -128,7 +140,9 @@ __global__ void __launch_bounds__(256) consolidate_kernel(float* __restrict__ up
 }  // namespace
 
 int32_t launch_bank_insert_protected(pssa_b200_ctx* ctx, const BankWriteParams& p) {
-    bank_insert_protected_kernel<<<1, 256, 0, ctx->stream>>>(p);
+    BankWriteParams q = p;
+    q.status = ctx->status_dev;
+    bank_insert_protected_kernel<<<1, 256, 0, ctx->stream>>>(q);
     return after_launch(ctx, "bank_insert_protected_kernel");
 }
 

@@ -823,10 +823,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     if (qblocks > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 memory read grid exceeds grid limits; refusing launch");
     int32_t rc;
     // with an empty bank the launch still publishes the projection (gpu_batch.rs:682-698 projects first)
-    static bool attr_a = false;
-    if (smem_a > 48 * 1024 && !attr_a) {
+    static PerDeviceOnce attr_a;
+    if (smem_a > 48 * 1024 && attr_a.need(ctx->device)) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_a = true;
+        attr_a.done(ctx->device);
     }
     const int kpad4 = (p.dk + 3) / 4 * 4;
     const size_t smem_f = (size_t)(kpad4 / 2) * QT * sizeof(float2) + ((size_t)2 * STL * (kpad4 + 4) + QT + 2 * STL) * sizeof(float);
@@ -836,10 +836,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         // distances from the inner product on the tensor cores: projection + three-way split of the queries, then one
         // product against the split keys whose epilogue turns p.k into d(p, k)
         const size_t smem_p = (size_t)QT * (p.dk + 1) * sizeof(float);
-        static bool attr_p = false;
-        if (smem_p > 48 * 1024 && !attr_p) {
+        static PerDeviceOnce attr_p;
+        if (smem_p > 48 * 1024 && attr_p.need(ctx->device)) {
             PSSA_CUDA(ctx, cudaFuncSetAttribute(project_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            attr_p = true;
+            attr_p.done(ctx->device);
         }
         PSSA_CUDA(ctx, launch_dependent(project_split_kernel, dim3((unsigned)qblocks), dim3(256), smem_p, ctx->stream, p));
         if ((rc = after_launch(ctx, "project_split_kernel")) != PSSA_B200_OK) return rc;
@@ -847,10 +847,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
                                                            (size_t)p.count, (size_t)p.dk, (size_t)p.cap)))
             return rc;
     } else if (p.f32_distance && !exact && smem_f <= 112 * 1024) {  // keys wider than 128 keep the f64 kernel
-        static bool attr_f = false;
-        if (smem_f > 48 * 1024 && !attr_f) {
+        static PerDeviceOnce attr_f;
+        if (smem_f > 48 * 1024 && attr_f.need(ctx->device)) {
             PSSA_CUDA(ctx, cudaFuncSetAttribute(poincare_distance_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-            attr_f = true;
+            attr_f.done(ctx->device);
         }
         // few query tiles (decode): spread the slot passes over up to 8 CTAs per tile
         unsigned ysplit = 1;
@@ -866,13 +866,13 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         if ((rc = after_launch(ctx, "poincare_distance_kernel")) != PSSA_B200_OK) return rc;
     }
     size_t wblocks = (p.rows + 7) / 8;
-    static bool attr_b[2] = {false, false};
-    if (smem_b > 48 * 1024 && !attr_b[exact]) {
+    static PerDeviceOnce attr_b[2];
+    if (smem_b > 48 * 1024 && attr_b[exact].need(ctx->device)) {
         if (exact)
             PSSA_CUDA(ctx, cudaFuncSetAttribute(softmax_topk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         else
             PSSA_CUDA(ctx, cudaFuncSetAttribute(softmax_topk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_b[exact] = true;
+        attr_b[exact].done(ctx->device);
     }
     const bool all_regs = !exact && !(p.top_k != 0 && p.top_k < p.count) && p.count > 0 && p.cap % 128 == 0 && p.cap <= 1024 &&
                           (reinterpret_cast<uintptr_t>(p.weights) & 15) == 0;

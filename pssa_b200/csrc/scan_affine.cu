@@ -305,22 +305,24 @@ static __device__ __align__(256) float g_scan_static_scratch[kStaticScanFloats];
 // a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
 static float* static_scratch_for_current_device(pssa_b200_ctx* ctx, int32_t* rc) {
     constexpr int kMaxDevices = 64;
-    static float* cached[kMaxDevices] = {};
+    static std::atomic<float*> cached[kMaxDevices];  // two host threads may make their first call at once
     *rc = PSSA_B200_OK;
     if (ctx->device < 0 || ctx->device >= kMaxDevices) {
         *rc = fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "static scan scratch: device ordinal %d is outside 0..%d", ctx->device, kMaxDevices - 1);
         return nullptr;
     }
-    if (cached[ctx->device] == nullptr) {
+    float* known = cached[ctx->device].load(std::memory_order_acquire);
+    if (known == nullptr) {
         float* ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_scan_static_scratch);
         if (e != cudaSuccess || ptr == nullptr) {
             *rc = cuda_fail(ctx, e, "cudaGetSymbolAddress(g_scan_static_scratch)");
             return nullptr;
         }
-        cached[ctx->device] = ptr;
+        cached[ctx->device].store(ptr, std::memory_order_release);
+        known = ptr;
     }
-    return cached[ctx->device];
+    return known;
 }
 
 template <int V>

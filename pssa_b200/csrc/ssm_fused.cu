@@ -444,10 +444,10 @@ int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
     constexpr int kTileTokens = kTileTokensFor<G>;
     size_t smem = (size_t)kStages * kTileTokens * (2 * CH + 2 * SP) * sizeof(float);
     auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE, THR>;
-    static bool attr_set = false;  // per instantiation; contexts share the device function
-    if (smem > 48 * 1024 && !attr_set) {
+    static PerDeviceOnce attr_set;  // per instantiation and per device
+    if (smem > 48 * 1024 && attr_set.need(ctx->device)) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
+        attr_set.done(ctx->device);
     }
     int ncb = (p.d + CH - 1) / CH;
     size_t blocks = (size_t)ncb * p.lanes;

@@ -274,6 +274,11 @@ class B200Dispatch:
     def poll_status(self):
         self._check(self._lib.pssa_b200_ctx_poll_status(self._h))
 
+    def selftest_wait_expiry(self, polls=4096):
+        """Enqueue the bounded-wait self-test: a wait that nothing satisfies runs out after `polls` polls and is
+        recorded; the next poll_status() raises with status ERR_TIMEOUT, and the context stays usable."""
+        self._check(self._lib.pssa_b200_ctx_selftest_wait_expiry(self._h, polls))
+
 
 class Device:
     """`Device` of src/backend.rs:1012-1018 reduced to the arm this package adds."""

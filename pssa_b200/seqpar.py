@@ -43,6 +43,16 @@ def last_token_owner(length: int, world: int) -> int:
     return owner
 
 
+def check_every_rank_has_tokens(lengths, world: int):
+    """Raise unless every rank's packed shard holds at least one token. Decided from the global sequence lengths, which
+    every rank holds identically, so that all ranks raise together and none is left waiting in the per-block all-gather
+    for a peer that returned early."""
+    for rank in range(world):
+        if not any(time_shards(int(n), world)[rank][1] > time_shards(int(n), world)[rank][0] for n in lengths):
+            raise ValueError(f"every rank needs at least one token: rank {rank} of {world} would hold none "
+                             f"(longest sequence has {max([int(n) for n in lengths], default=0)} tokens)")
+
+
 def pack_shard(prompts, world: int, rank: int):
     """This rank's shards of all prompts in the batched entry point's packed layout: (ids uint32, offsets, lengths)."""
     if not 0 <= rank < world:
@@ -124,9 +134,8 @@ class SequenceParallelPrefill:
         if len(prompts) > self.max_lanes:
             raise ValueError(f"{len(prompts)} sequences exceed the {self.max_lanes} lanes the exchange buffers hold")
         lengths = [len(p) for p in prompts]
+        check_every_rank_has_tokens(lengths, self.world)  # the same verdict on every rank, before any device work
         ids, offsets, shard_len = pack_shard(prompts, self.world, self.rank)
-        if ids.size == 0:
-            raise ValueError("every rank needs at least one token: sequences are shorter than the world size")
         dev = self._send.device
         ids_dev = torch.from_numpy(ids.astype(np.int64)).to(torch.int32).to(dev)
         logits = torch.zeros(len(prompts), self.model.d_vocab, dtype=torch.float32, device=dev)

@@ -118,3 +118,29 @@ def test_two_ranks_exchange_and_fold_reproduce_the_single_pass():
     for r in (0, 1):  # both ranks end with the same, correct, final state
         assert np.max(np.abs(res[r][1] - ref_h)) / scale <= REL_TOL
     assert np.array_equal(res[0][1], res[1][1])
+
+
+def test_the_empty_shard_verdict_is_the_same_on_every_rank():
+    """A prompt shorter than the world leaves the last ranks without tokens. The check runs on the global lengths, so
+    every rank raises (or none does) before any of them enqueues the per-block all-gather."""
+    for lengths, world, ok in (([3], 4, False), ([3, 0, 2], 4, False), ([4], 4, True), ([1, 9], 4, True), ([5, 7], 2, True),
+                               ([0, 0], 2, False), ([2, 3], 2, True), ([1], 1, True)):
+        verdicts = []
+        for rank in range(world):  # what each rank would conclude: the function does not look at the rank at all
+            try:
+                SP.check_every_rank_has_tokens(lengths, world)
+                verdicts.append(True)
+            except ValueError:
+                verdicts.append(False)
+        assert verdicts == [ok] * world, (lengths, world)
+        # and it agrees with what the ranks' packed shards actually hold
+        holds = [int(SP.pack_shard([np.zeros(n, np.int64) for n in lengths], world, r)[2].sum()) > 0 for r in range(world)]
+        assert all(holds) == ok
+
+
+def test_shard_lengths_between_world_and_twice_world_differ_by_rank():
+    """With world <= len < 2*world some ranks hold two tokens and some one: anything a rank derives for the exchange
+    (record counts, chunking) must therefore not depend on its own shard length."""
+    world = 4
+    sizes = [[b - a for a, b in SP.time_shards(n, world)] for n in (4, 5, 7)]
+    assert sizes == [[1, 1, 1, 1], [2, 1, 1, 1], [2, 2, 2, 1]]

@@ -1,5 +1,6 @@
 """Sequence-parallel prefill on two GPUs (NCCL): time-sharded prefill of ragged sequences gives the logits and the
-final recurrent state of the single-GPU prefill, on both ranks. Skipped on a one-GPU box."""
+final recurrent state of the CPU oracle's token-serial prefill (and of the single-GPU prefill), on both ranks, including
+sequences so short that the two ranks' shards are two tokens and one token long. Skipped on a one-GPU box."""
 import os
 import socket
 
@@ -10,6 +11,7 @@ pytestmark = pytest.mark.gpu
 
 CFG = dict(depth=3, d_vocab=257, d_latent=64, d_state=16, d_mem_key=16, mem_capacity=64)
 LENGTHS = (203, 64, 2, 131)
+SHORT_LENGTHS = (3, 2)  # world <= len < 2*world: rank 0 holds (2, 1) tokens, rank 1 holds (1, 1)
 
 
 def _build(gpu, precision):
@@ -22,12 +24,24 @@ def _build(gpu, precision):
     gm = pssa_b200.PSSAModel(gpu, CFG["depth"], CFG["d_vocab"], CFG["d_latent"], CFG["d_state"], CFG["d_mem_key"],
                              CFG["mem_capacity"], tau_mem=0.1, streams=len(LENGTHS), precision=precision)
     upload(om, gm)
-    return gm
+    return gm, om
 
 
-def _prompts():
+def _prompts(lengths=LENGTHS):
     rng = np.random.default_rng(5)
-    return [rng.integers(1, CFG["d_vocab"], n) for n in LENGTHS]
+    return [rng.integers(1, CFG["d_vocab"], n) for n in lengths]
+
+
+def _oracle(om, prompts):
+    """Token-serial CPU prefill of every prompt: (logits [n, V], final states [n, depth*d*s])."""
+    logits, states = [], []
+    for p in prompts:
+        m = om.clone()
+        m.reset_recurrent_state()
+        _, _, lg = m.prefill_inference(p)
+        logits.append(lg)
+        states.append(m.state().copy())
+    return np.stack(logits), np.stack(states)
 
 
 def _rank_main(rank, world, port, q):
@@ -46,7 +60,8 @@ def _rank_main(rank, world, port, q):
         gpu = pssa_b200.B200Dispatch(rank)
         gpu.set_stream(torch.cuda.current_stream())
         for precision in (1, 0):  # fp32 exact, then the bf16 mode
-            gm = _build(gpu, precision)
+            gm, om = _build(gpu, precision)
+            cpu_logits, cpu_state = _oracle(om, _prompts())
             ref_logits, _ = gm.prefill_batch([list(p) for p in _prompts()])
             ref_state = [gm.copy_recurrent_state_to(l) for l in range(len(LENGTHS))]
             gm.reset_recurrent_state()
@@ -56,9 +71,15 @@ def _rank_main(rank, world, port, q):
             state = [gm.copy_recurrent_state_to(l) for l in range(len(LENGTHS))]
             # decode continues locally from the shared final state
             step, _ = gm.decode_step([7, 8, 9, 10], want_logits=True, want_greedy=True)
+            # shards of two tokens and of one token on different ranks
+            gm.reset_recurrent_state()
+            short_logits = sp.prefill(_prompts(SHORT_LENGTHS))
+            torch.cuda.synchronize()
+            short_state = [gm.copy_recurrent_state_to(l) for l in range(len(SHORT_LENGTHS))]
+            short_cpu = _oracle(om, _prompts(SHORT_LENGTHS))
             sp.close()
             gm.close()
-            out[precision] = (ref_logits, logits, ref_state, state, step)
+            out[precision] = (ref_logits, logits, ref_state, state, step, cpu_logits, cpu_state, short_logits, short_state, short_cpu)
         q.put((rank, out))
         dist.barrier()
         gpu.close()
@@ -85,8 +106,8 @@ def test_two_gpu_time_sharded_prefill_matches_one_gpu():
         assert p.exitcode == 0
     for precision, tol in ((1, 1e-5), (0, 2e-3)):
         r0, r1 = res[0][precision], res[1][precision]
-        ref_logits, logits0, ref_state, state0, step0 = r0
-        _, logits1, _, state1, step1 = r1
+        ref_logits, logits0, ref_state, state0, step0, cpu_logits, cpu_state, short0, short_state0, short_cpu = r0
+        _, logits1, _, state1, step1, _, _, short1, short_state1, _ = r1
         scale = np.abs(ref_logits).max()
         assert np.max(np.abs(logits0 - ref_logits)) / scale <= tol, precision
         assert np.array_equal(logits0, logits1)  # every rank returns the owner's rows
@@ -95,3 +116,16 @@ def test_two_gpu_time_sharded_prefill_matches_one_gpu():
             assert np.max(np.abs(state0[l] - ref_state[l])) / s_scale <= tol
             assert np.max(np.abs(state1[l] - ref_state[l])) / s_scale <= tol
         assert np.max(np.abs(step0 - step1)) / scale <= tol  # replicas stay in step after the sharded prefill
+        # against the CPU oracle: 1e-5 of scale in the fp32 mode, the bf16 logit bar otherwise
+        cpu_tol = 1e-5 if precision == 1 else 2e-2 / np.abs(cpu_logits).max()
+        assert np.max(np.abs(logits0 - cpu_logits)) / np.abs(cpu_logits).max() <= cpu_tol, precision
+        for l in range(len(LENGTHS)):
+            s_scale = max(1e-6, np.abs(cpu_state[l]).max())
+            assert np.max(np.abs(state0[l] - cpu_state[l])) / s_scale <= (1e-5 if precision == 1 else 5e-2)
+        short_logits_cpu, short_state_cpu = short_cpu
+        assert np.array_equal(short0, short1)
+        assert np.max(np.abs(short0 - short_logits_cpu)) / np.abs(short_logits_cpu).max() <= cpu_tol
+        for l in range(len(SHORT_LENGTHS)):
+            s_scale = max(1e-6, np.abs(short_state_cpu[l]).max())
+            for got in (short_state0[l], short_state1[l]):
+                assert np.max(np.abs(got - short_state_cpu[l])) / s_scale <= (1e-5 if precision == 1 else 5e-2)

@@ -143,3 +143,52 @@ def test_write_argument_errors(gpu):
     with pytest.raises(pssa_b200.B200Error, match="must be positive"):
         gpu.bank_insert_protected_dev(bank.keys, bank.norm_sq, bank.values, bank.conf, bank.seen, bank.meta, 0, 2, 2,
                                       bank.keys, bank.values, bank.conf, bank.seen, 1)
+
+
+def test_out_of_range_device_metadata_is_refused_without_touching_memory(gpu):
+    """Slot ids and {count, write_head} live on the device, where the host cannot check them. A winning slot or ring
+    head >= capacity, a count above capacity, or a key outside the open unit ball (src/memory.rs:273-277 asserts it)
+    must skip that write, report slot -2, raise PSSA_B200_ERR_BANK in the status word and leave the bank alone."""
+    import torch
+
+    import pssa_b200
+    cap, dk, dv = 4, 3, 5
+    rng = np.random.default_rng(2)
+    bank = DeviceBank(cap, dk, dv)
+    keys = rng.uniform(-0.3, 0.3, (cap, dk)).astype(np.float32)
+    vals = rng.standard_normal((cap, dv)).astype(np.float32)
+    assert bank.write(gpu, keys, vals, np.ones(cap), np.arange(cap)).tolist() == [0, 1, 2, 3]
+    gpu.poll_status()
+    snap = [t.clone() for t in (bank.keys, bank.values, bank.norm_sq, bank.conf, bank.seen, bank.meta)]
+
+    def unchanged():
+        return all(torch.equal(a, b) for a, b in zip(snap, (bank.keys, bank.values, bank.norm_sq, bank.conf, bank.seen, bank.meta)))
+
+    def refused():
+        with pytest.raises(pssa_b200.B200Error) as e:
+            gpu.poll_status()
+        assert e.value.status == 9
+        gpu.poll_status()  # cleared
+
+    # winning slot outside the bank
+    assert bank.write(gpu, keys[:1], vals[:1], [1.0], [9], winning=[cap + 3], eta=0.5).tolist() == [-2]
+    refused()
+    assert unchanged()
+    # key on / outside the unit sphere
+    assert bank.write(gpu, [[1.0, 0.0, 0.0]], vals[:1], [50.0], [10]).tolist() == [-2]
+    refused()
+    assert bank.write(gpu, [[np.nan, 0.0, 0.0]], vals[:1], [50.0], [10]).tolist() == [-2]
+    refused()
+    assert unchanged()
+    # corrupted metadata: ring head beyond the bank, then a count beyond capacity
+    bank.meta.copy_(torch.tensor([cap, cap + 1], dtype=torch.int64))
+    assert bank.write(gpu, keys[:1], vals[:1], [50.0], [11]).tolist() == [-2]
+    refused()
+    bank.meta.copy_(torch.tensor([cap + 2, 0], dtype=torch.int64))
+    assert bank.write(gpu, keys[:1], vals[:1], [50.0], [12]).tolist() == [-2]
+    refused()
+    bank.meta.copy_(snap[5])
+    assert unchanged()
+    # a good write still works afterwards
+    assert bank.write(gpu, keys[:1] * 0.5, vals[:1], [50.0], [1000]).tolist() == [0]
+    gpu.poll_status()

@@ -7,6 +7,8 @@ or that cannot accept the implicit device synchronisation of cudaMalloc / cudaFr
 import numpy as np
 import pytest
 
+import oracle as O
+
 pytestmark = pytest.mark.gpu
 
 
@@ -28,8 +30,18 @@ def test_noalloc_scan_matches_the_arena_backed_scan_on_two_calls_in_a_row():
             gpu.set_scan_chunks(chunks)
             gpu.scan_states_dev(a, b, h0, want, want_last, lanes, T, stride)
             gpu.set_scan_chunks(0)
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
             gpu.scan_states_noalloc_dev(a, b, h0, got, got_last, lanes, T, stride, chunks)
             torch.cuda.synchronize()
+            # the property the entry point exists for: the device's free memory does not move across the call (the
+            # first call only looks up the address of the array that was loaded with the library)
+            assert torch.cuda.mem_get_info()[0] == free_before, f"call {call}: device memory in use changed"
+            # against the CPU oracle's ordered recurrence, not only against the library's other entry point
+            ref = O.scan_states(a.cpu().numpy(), b.cpu().numpy(), h0.cpu().numpy())
+            ref_scale = np.maximum(1e-6, np.abs(ref).max(axis=1, keepdims=True))
+            assert float(np.max(np.abs(got.cpu().numpy() - ref) / ref_scale)) <= 1e-5
+            assert float(np.max(np.abs(got_last.cpu().numpy() - ref[:, -1]) / ref_scale[:, 0])) <= 1e-5
             # same kernels, same chunking: the tolerance of the chunked-scan tests (1e-5 of the channel's scale)
             scale = want.abs().amax(dim=1, keepdim=True).clamp_min(1e-6)
             assert float(((got - want).abs() / scale).max()) <= 1e-5
