@@ -104,7 +104,9 @@ def test_two_gpu_time_sharded_prefill_matches_one_gpu():
     for p in procs:
         p.join(120)
         assert p.exitcode == 0
-    for precision, tol in ((1, 1e-5), (0, 2e-3)):
+    # bf16 mode, sharded against unsharded on the GPU: the fp32 states differ in the last bits with the chunking, which
+    # flips bf16 roundings of y here and there (4e-3 relative each, diluted over the products that follow)
+    for precision, tol in ((1, 1e-5), (0, 5e-3)):
         r0, r1 = res[0][precision], res[1][precision]
         ref_logits, logits0, ref_state, state0, step0, cpu_logits, cpu_state, short0, short_state0, short_cpu = r0
         _, logits1, _, state1, step1, _, _, short1, short_state1, _ = r1
