@@ -218,6 +218,52 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
                               size_t top_k, float* q_pnc, float* q_norm, float* weights, float* m_val,
                               float* min_dist, uint32_t flags);
 
+/* ------------------------------------------------------------------ memory stage and resident SSM, one call each */
+
+/*
+ * `GpuDispatch::memory_forward` (src/backend.rs:1342-1385) with its argument list: the whole memory stage of a block for
+ * seq_len token rows, the CPU twin being `stage_memory_impl` (src/gpu_batch.rs:758-929):
+ *   q_euc = W_qx x + W_qh y; q_pnc, q_norm = projection into the ball; weights, m_val = all-slots read of the bank;
+ *   g_mem = sigmoid(W_gate x); m_proj = W_proj m_val; m_inj = g_mem * m_proj.
+ * HOST pointers, row-major fp32: x_norm, y_ssm [seq_len, d_m]; w_qx, w_qh [d_k, d_m]; w_gate [d_m, d_m]; w_proj
+ * [d_m, d_val]; keys [capacity, d_k]; norm_sq [capacity]; values [capacity, d_val]. Outputs: q_euc, q_pnc [seq_len, d_k];
+ * q_norm [seq_len]; weights [seq_len, capacity]; m_val [seq_len, d_val]; g_mem, m_proj, m_inj [seq_len, d_m]; all left
+ * untouched on failure. `precision` (not in the reference's list): PSSA_B200_PRECISION_FP32_EXACT keeps the reference's
+ * dot-product and summation orders; PSSA_B200_PRECISION_BF16 runs the four products on the tensor cores (d_m and d_val
+ * multiples of 8) with the read's f64 distances unchanged. The _dev form takes DEVICE pointers and only enqueues.
+ */
+int32_t pssa_b200_memory_forward(pssa_b200_ctx* ctx, const float* x_norm, const float* y_ssm, const float* w_qx, const float* w_qh,
+                                 const float* w_gate, const float* w_proj, const float* keys, const float* norm_sq, const float* values,
+                                 size_t seq_len, size_t d_m, size_t d_k, size_t d_val, size_t capacity, size_t count, float tau,
+                                 float* q_euc, float* q_pnc, float* q_norm, float* weights, float* m_val, float* g_mem, float* m_proj,
+                                 float* m_inj, int32_t precision);
+int32_t pssa_b200_memory_forward_dev(pssa_b200_ctx* ctx, const float* x_norm, const float* y_ssm, const float* w_qx, const float* w_qh,
+                                     const float* w_gate, const float* w_proj, const float* keys, const float* norm_sq,
+                                     const float* values, size_t seq_len, size_t d_m, size_t d_k, size_t d_val, size_t capacity,
+                                     size_t count, float tau, float* q_euc, float* q_pnc, float* q_norm, float* weights, float* m_val,
+                                     float* g_mem, float* m_proj, float* m_inj, int32_t precision);
+/*
+ * `GpuDispatch::ssm_forward_resident` (src/backend.rs:1186-1212): the SSM stage of one lane whose results (y, every
+ * state, the discretised maps) stay on the device, in buffers the context owns, until the memory stage consumes them.
+ * HOST pointers as for pssa_b200_ssm_forward; delta_raw is the reference's backward-only input and may be NULL.
+ */
+int32_t pssa_b200_ssm_forward_resident(pssa_b200_ctx* ctx, const float* delta, const float* delta_raw, const float* b_proj,
+                                       const float* x_norm, const float* rates, const float* c_proj, const float* initial,
+                                       size_t seq_len, size_t d_m, size_t d_s, uint32_t flags);
+/*
+ * `GpuDispatch::memory_forward_after_ssm` (src/backend.rs:1246-1289): publishes the resident SSM tape to the host
+ * (bar_a, bar_b [seq_len, d_m*d_s], states [(seq_len+1), d_m*d_s] with row 0 the initial carry, y_ssm [seq_len, d_m];
+ * the first three may be NULL) and runs pssa_b200_memory_forward on the resident y. Fails with the reference's messages
+ * when no SSM result is resident or its shape differs (src/cuda/stages.rs:714, 733-735); the tape is published before
+ * the memory stage runs, so it survives a failure of that stage (src/cuda/stages.rs:737-771).
+ */
+int32_t pssa_b200_memory_forward_after_ssm(pssa_b200_ctx* ctx, const float* x_norm, const float* w_qx, const float* w_qh, const float* w_gate,
+                                           const float* w_proj, const float* keys, const float* norm_sq, const float* values,
+                                           size_t seq_len, size_t d_m, size_t d_k, size_t d_val, size_t capacity, size_t count, float tau,
+                                           float* bar_a, float* bar_b, float* states, float* y_ssm, float* q_euc, float* q_pnc,
+                                           float* q_norm, float* weights, float* m_val, float* g_mem, float* m_proj, float* m_inj,
+                                           int32_t precision);
+
 /* ------------------------------------------------------------------ bank write and plastic fast weights */
 
 /*

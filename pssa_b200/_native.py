@@ -36,6 +36,10 @@ SIGNATURES = {
                                               _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "pssa_b200_memory_read": (C.c_int32, [_vp, _vp, C.c_int32, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _sz,
                                           _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
+    "pssa_b200_memory_forward": (C.c_int32, [_vp] * 10 + [_sz] * 6 + [C.c_float] + [_vp] * 8 + [C.c_int32]),
+    "pssa_b200_memory_forward_dev": (C.c_int32, [_vp] * 10 + [_sz] * 6 + [C.c_float] + [_vp] * 8 + [C.c_int32]),
+    "pssa_b200_ssm_forward_resident": (C.c_int32, [_vp] * 8 + [_sz, _sz, _sz, C.c_uint32]),
+    "pssa_b200_memory_forward_after_ssm": (C.c_int32, [_vp] * 9 + [_sz] * 6 + [C.c_float] + [_vp] * 12 + [C.c_int32]),
     "pssa_b200_bank_insert_protected_dev": (C.c_int32, [_vp] * 7 + [_sz, _sz, _sz] + [_vp] * 4 + [_sz, _vp, _vp, C.c_float]),
     "pssa_b200_adapter_plastic_update_dev": (C.c_int32, [_vp] * 5 + [_sz, _sz]),
     "pssa_b200_adapter_consolidate_dev": (C.c_int32, [_vp, _vp, _vp, _sz, C.c_float]),

@@ -104,6 +104,7 @@ void pssa_b200_ctx_destroy(pssa_b200_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->arena) cudaFree(ctx->arena);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
+    cudaFree(ctx->resident.y), cudaFree(ctx->resident.states), cudaFree(ctx->resident.bar_a), cudaFree(ctx->resident.bar_b);
     for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
     for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);

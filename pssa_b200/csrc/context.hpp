@@ -27,6 +27,13 @@ struct pssa_b200_ctx {
     // device status word for bounded waits (0 = ok)
     int* status_dev = nullptr;
     int scan_chunks = 0;  // 0 = choose automatically; tests force the multi-chunk passes with it
+    // Resident SSM result (`ssm_forward_resident` -> `memory_forward_after_ssm`, src/backend.rs:1186-1289): the tape of the
+    // last resident SSM call stays on the device until the memory stage consumes it.
+    struct ResidentSsm {
+        float *y = nullptr, *states = nullptr, *bar_a = nullptr, *bar_b = nullptr;  // [T, d], [(T+1), d*s], [T, d*s] x 2
+        size_t seq_len = 0, d_m = 0, d_s = 0, capacity_rows = 0, capacity_stride = 0;
+        bool valid = false;
+    } resident;
     // Stage profile (the role of the reference's StageTrace, src/training_diagnostics.rs:74-125, with device
     // events instead of wall clock): while enabled, an event is recorded after every kernel launch; the time
     // between consecutive events on the (serial) stream is attributed to the kernel launched in between.

@@ -150,6 +150,14 @@ __global__ void __launch_bounds__(256) residual_kernel(const float* __restrict__
     out[idx] = prev ? __fadd_rn(prev[idx], __fmul_rn(scale, z[idx])) : z[idx];
 }
 
+// m_inj = g_mem * m_proj (the reference's `sigmoid_mul`, src/cuda/stages.ptx:565-571: a plain product, the gate is
+// already a sigmoid)
+__global__ void __launch_bounds__(256) multiply_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                                                       size_t n) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) out[idx] = __fmul_rn(a[idx], b[idx]);
+}
+
 __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restrict__ src, const uint32_t* __restrict__ rows_idx,
                                                           float* __restrict__ dst, size_t n_rows, int d) {
     pdl_trigger();  // the next kernel in the stream may start its prologue now ...
@@ -352,6 +360,11 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
 int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale) {
     residual_kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(prev, z, out, n, scale);
     return after_launch(ctx, "residual_kernel");
+}
+
+int32_t launch_multiply(pssa_b200_ctx* ctx, const float* a, const float* b, float* out, size_t n) {
+    multiply_kernel<<<blocks_for(n, 256), 256, 0, ctx->stream>>>(a, b, out, n);
+    return after_launch(ctx, "multiply_kernel");
 }
 
 int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d) {

@@ -607,6 +607,7 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // (their epilogue traffic is the limiter), so those keep three.
     const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
     if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_GATE && e.n_pairs > 0 && only16) return launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
     if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1, kWideEpiWarps>(ctx, a, b, e);
@@ -662,13 +663,15 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
 // epilogue (src/pssa.rs:1189-1192 without the adapter term, which rides in the MLP products as extra K columns).
 // gate [M, ld_gate] and y [M, N] fp32; out fp32 [M, N] and out16 bf16 [M, ld16] are both written.
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
-                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K) {
-    int32_t rc = check_shape(ctx, x16, w16, M, N, K);
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K, bool split_k) {
+    if (split_k && K % BK != 0) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 split GEMM needs K %% 64 == 0; K = %zu", K);
+    int32_t rc = check_shape(ctx, x16, w16, M, N, split_k ? 3 * K : K);
     if (rc) return rc;
     GemmEpilogue e{};
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = N, e.ld16 = ld16;
-    e.M = (int)M, e.N = (int)N, e.K = (int)K, e.epi = EPI_GATE, e.alpha = alpha;
+    e.M = (int)M, e.N = (int)N, e.K = (int)(split_k ? 3 * K : K), e.epi = EPI_GATE, e.alpha = alpha;
     e.add_in = y, e.res_in = gate, e.ld_add = N, e.ld_res = ld_gate, e.res_scale = 1.0f;
+    if (split_k) e.n_pairs = 1, e.seg_kb = (int)(K / BK);  // pair (0, 0): leading piece of each operand
     return dispatch(ctx, x16, w16, e);
 }
 

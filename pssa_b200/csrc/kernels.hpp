@@ -91,6 +91,7 @@ struct RetrieveParams {
                            // partial products (error near 2^-16), else all six (fp32-accurate)
     int f32_distance;      // fast mode: squared differences accumulated in fp32 instead of f64 (ignored when exact)
     int skip_weights;      // all-slots, non-exact, w_split set: do not write the fp32 weight rows back (only the pieces are read)
+    int skip_value_read;   // all-slots, non-exact, w_split set: stop after the softmax; the caller multiplies the weight pieces itself
     // tensor-core distances (non-exact, dk % 64 == 0; used when all four are set): q_split [rows, 3*dk] bf16 and
     // q_stat [rows] are scratch written by the projection kernel; k_split [cap, 3*dk] bf16 and k_stat [cap] come from
     // launch_split_keys, once per bank upload
@@ -157,9 +158,11 @@ int32_t launch_wait_expiry_selftest(pssa_b200_ctx* ctx, unsigned polls);
 // gemm_tcgen05.cu: bf16 operands [rows, K] row-major, fp32 accumulate in TMEM; out fp32 [M, ldo] and/or bf16 [M, N]
 int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t M, size_t N,
                          size_t K, size_t ldo, int epi, float alpha, size_t ld16 = 0);  // ld16: row pitch of out_bf16 (0 = N)
-// z = gate * (X W^T) + alpha * y, fp32 and bf16 (row pitch ld16) outputs
+// z = gate * (X W^T) + alpha * y, fp32 and bf16 (row pitch ld16) outputs. split_k: both operands are [., 3*K] three-piece
+// splits (K % 64 == 0) and only the leading pieces are multiplied.
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
-                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K);
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K,
+                              bool split_k = false);
 // MLP output with both residuals fused: out = res_in ? res_in + res_scale*(X W^T + add_in) : X W^T + add_in
 // add_in is fp32 [M, N], or bf16 [M, ld_add_bf16] when ld_add_bf16 != 0
 int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const void* add_in,
@@ -184,6 +187,7 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
                             size_t ldact, const float* u_eff, float* z_raw, void* z_bf16, size_t rows, int d, int rank,
                             float ssm_scale);
 int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale);
+int32_t launch_multiply(pssa_b200_ctx* ctx, const float* a, const float* b, float* out, size_t n);
 int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d);
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n);
 int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_t lanes, const float* weights, int cap, const float* q_pnc,

@@ -105,6 +105,8 @@ int32_t pssa_b200_model_create(pssa_b200_ctx* ctx, const pssa_b200_config* cfg, 
         guard(dev_alloc(ctx, &b.w2cat_bf16, m->d * (2 * m->d + 64) * 2, true));
         guard(dev_alloc(ctx, (void**)&b.w1u, 2 * m->d * 16 * 4, true));
         guard(dev_alloc(ctx, &b.vsplit_bf16, m->d * 3 * m->cap * 2, true));
+        guard(dev_alloc(ctx, &b.vpsplit_bf16, m->d * 3 * m->cap * 2, true));
+        guard(dev_alloc(ctx, (void**)&b.vp, m->cap * m->d * sizeof(float), true));
         guard(dev_alloc(ctx, &b.ksplit_bf16, m->cap * 3 * m->k * 2, true));
         guard(dev_alloc(ctx, (void**)&b.kstat, m->cap * sizeof(float2), true));
         b.host_up.assign(m->d * m->rank, 0.0f);
@@ -151,6 +153,8 @@ void pssa_b200_model_destroy(pssa_b200_model* m) {
         cudaFree(b.w2cat_bf16);
         cudaFree(b.w1u);
         cudaFree(b.vsplit_bf16);
+        cudaFree(b.vpsplit_bf16);
+        cudaFree(b.vp);
         cudaFree(b.ksplit_bf16);
         cudaFree(b.kstat);
     }
@@ -186,6 +190,7 @@ int32_t pssa_b200_model_set_tensor(pssa_b200_model* m, int32_t layer, int32_t id
         DeviceBlock& b = m->blocks[layer];
         PSSA_CUDA(ctx, cudaMemcpyAsync(b.w[id], data, len * 4, cudaMemcpyHostToDevice, st));
         b.bf16_dirty = true;
+        if (id == T_W_PROJ) b.vp_dirty = true;
         if (id == T_A_MAT) {  // refresh_ssm_rates (src/pssa.rs:787-796): A = -softplus(raw), host libm like the reference
             std::vector<float> rates(len);
             for (size_t i = 0; i < len; ++i) rates[i] = -(data[i] > 20.0f ? data[i] : log1pf(expf(data[i])));
@@ -225,6 +230,7 @@ int32_t pssa_b200_model_set_bank(pssa_b200_model* m, int32_t layer, const float*
     b.count = count;
     b.write_head = write_head;
     b.vsplit_dirty = true;
+    b.vp_dirty = true;
     if (confidence) b.confidence.assign(confidence, confidence + m->cap);
     if (last_seen_step) b.last_seen.assign(last_seen_step, last_seen_step + m->cap);
     PSSA_CUDA(ctx, cudaStreamSynchronize(st));

@@ -38,8 +38,14 @@ struct DeviceBlock {
     void* vsplit_bf16 = nullptr;  // bank values transposed, three bf16 pieces [d, 3*cap] (tensor-core value read)
     void* ksplit_bf16 = nullptr;  // bank keys as three bf16 pieces [cap, 3*k] and (|k|^2, 1/(1-|k|^2)) per slot
     float2* kstat = nullptr;      //   (tensor-core distances); rebuilt together with vsplit_bf16
+    // bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s), so the bank's values are carried through the memory
+    // projection once per upload: vp = V W_proj^T [cap, d] fp32, vpsplit_bf16 = its transpose as bf16 pieces [d, 3*cap]
+    // (the layout of vsplit_bf16; the read uses the leading piece). The all-slots read then yields W_proj m directly.
+    float* vp = nullptr;
+    void* vpsplit_bf16 = nullptr;
     bool bf16_dirty = true;
     bool vsplit_dirty = true;
+    bool vp_dirty = true;
 };
 
 struct Workspace {

@@ -108,6 +108,13 @@ int32_t refresh_bf16(pssa_b200_model* m) {
         if ((rc = launch_split_keys(ctx, b.w[T_BANK_KEYS], b.w[T_BANK_NORM_SQ], b.ksplit_bf16, b.kstat, (int)m->cap, (int)m->k))) return rc;
         b.vsplit_dirty = false;
     }
+    for (auto& b : m->blocks) {
+        if (!b.vp_dirty) continue;
+        // vp = V W_proj^T in fp32 (every entry one dot product in the reference's order), then transposed bf16 pieces
+        if ((rc = launch_gemm_exact(ctx, b.w[T_BANK_VALUES], b.w[T_W_PROJ], b.vp, m->cap, d, d, d, EPI_NONE, 1.0f))) return rc;
+        if ((rc = launch_split_values(ctx, b.vp, b.vpsplit_bf16, (int)m->cap, (int)d))) return rc;
+        b.vp_dirty = false;
+    }
     if (m->unembed_dirty) {
         if ((rc = launch_to_bf16(ctx, m->unembed, m->unembed_bf16, m->v * d))) return rc;
         m->unembed_dirty = false;
@@ -266,6 +273,12 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // only the observer reads the fp32 weight rows after the value read
         rp.skip_weights = rp.w_split && !observe && !(rp.top_k != 0 && rp.top_k < rp.count);
         if (!exact && k % 64 == 0) rp.q_split = ws.q_split, rp.q_stat = ws.q_stat, rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
+        // All-slots read in the bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s). The bank's values were carried
+        // through W_proj at upload (vpsplit_bf16), so the product of the weight rows with them IS the memory projection and
+        // takes the gate epilogue directly: the value read stops after the softmax (no m, no separate W_proj launch). The
+        // observer wants m itself and keeps the two-product schedule.
+        const bool proj_in_read = !exact && !observe && rp.w_split && !(rp.top_k != 0 && rp.top_k < rp.count) && rp.count > 0;
+        rp.skip_value_read = proj_in_read;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
         const float rscale = l == 0 ? 1.0f : m->residual_scales[l - 1];
@@ -285,8 +298,12 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             // term is one extra K block of both MLP products: W1*(zp + U act) = [W1 | W1 U] [zp; act] and
             // W2*h + U*act = [W2 | U] [h; act]. The combine kernel and the m_proj round trip disappear.
             const size_t ldz = m->d + 64, lda = 2 * m->d + 64;
-            if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale, rows,
-                                            m->d, m->d)))
+            if (proj_in_read) {
+                if ((rc = launch_gemm_bf16_gate(ctx, ws.w_split, b.vpsplit_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale,
+                                                rows, m->d, m->cap, /*split_k=*/true)))
+                    return rc;
+            } else if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale,
+                                                   rows, m->d, m->d)))
                 return rc;
             if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, b.w1cat_bf16, nullptr, ws.act_bf16, rows, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
                 return rc;

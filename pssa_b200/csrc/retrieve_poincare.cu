@@ -896,7 +896,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     if (p.count > 0 && !topk && p.w_split && p.v_split && !exact) {
         // all-slots value read on the tensor cores: m = W x V as six bf16 partial products (fp32-accurate), or the
         // leading three (error near 2^-16 of the row scale) when the caller only keeps a bf16 result
-        if ((rc = launch_gemm_bf16_split3(ctx, p.w_split, p.v_split, p.m_val, p.m_bf16, p.rows, p.dv, p.cap, p.dv,
+        // (skip_value_read: the caller multiplies the weight pieces by its own operand, e.g. values already carried
+        // through the memory projection)
+        if (!p.skip_value_read &&
+            (rc = launch_gemm_bf16_split3(ctx, p.w_split, p.v_split, p.m_val, p.m_bf16, p.rows, p.dv, p.cap, p.dv,
                                           p.value_terms == 3 ? 3 : p.value_terms == 1 ? 1 : 6)))
             return rc;
     } else if (p.count > 0 && !topk) {

@@ -206,6 +206,46 @@ class B200Dispatch:
             self._mem_flags(exact, f32_distance, tc_distance)))
 
 
+    # ---- stage-level operators with the reference's argument lists (src/backend.rs:1186-1289, 1342-1385)
+    def _memory_outputs(self, seq_len, d_m, d_k, d_val, capacity):
+        z = lambda *shape: np.zeros(shape, np.float32)  # noqa: E731
+        return dict(q_euc=z(seq_len, d_k), q_pnc=z(seq_len, d_k), q_norm=z(seq_len), weights=z(seq_len, capacity),
+                    m_val=z(seq_len, d_val), g_mem=z(seq_len, d_m), m_proj=z(seq_len, d_m), m_inj=z(seq_len, d_m))
+
+    def memory_forward(self, x_norm, y_ssm, w_qx, w_qh, w_gate, w_proj, keys, norm_sq, values, seq_len, d_m, d_k, d_val,
+                       capacity, count, tau, precision=N.PRECISION_FP32_EXACT, out=None):
+        """`GpuDispatch::memory_forward` (src/backend.rs:1342-1385) on host arrays; returns the eight outputs as a dict
+        (or fills `out`, a dict of preallocated arrays, which stays untouched on failure)."""
+        ins = [x_norm, y_ssm, w_qx, w_qh, w_gate, w_proj, keys, norm_sq, values]
+        for name, arr in zip(("x_norm", "y_ssm", "w_qx", "w_qh", "w_gate", "w_proj", "keys", "norm_sq", "values"), ins):
+            _host(arr, name)
+        o = out or self._memory_outputs(seq_len, d_m, d_k, d_val, capacity)
+        self._check(self._lib.pssa_b200_memory_forward(
+            self._h, *[_ptr(a) for a in ins], seq_len, d_m, d_k, d_val, capacity, count, tau,
+            *[_ptr(o[k]) for k in ("q_euc", "q_pnc", "q_norm", "weights", "m_val", "g_mem", "m_proj", "m_inj")], precision))
+        return o
+
+    def ssm_forward_resident(self, delta, b_proj, x_norm, rates, c_proj, initial, seq_len, d_m, d_s, delta_raw=None, exact=False):
+        """`GpuDispatch::ssm_forward_resident` (src/backend.rs:1186-1212): results stay on the device."""
+        self._check(self._lib.pssa_b200_ssm_forward_resident(
+            self._h, _ptr(delta), _ptr(delta_raw), _ptr(b_proj), _ptr(x_norm), _ptr(rates), _ptr(c_proj), _ptr(initial), seq_len,
+            d_m, d_s, N.SSM_EXACT if exact else 0))
+
+    def memory_forward_after_ssm(self, x_norm, w_qx, w_qh, w_gate, w_proj, keys, norm_sq, values, seq_len, d_m, d_s, d_k, d_val,
+                                 capacity, count, tau, precision=N.PRECISION_FP32_EXACT):
+        """`GpuDispatch::memory_forward_after_ssm` (src/backend.rs:1246-1289): publishes the resident SSM tape and runs the
+        memory stage on it; returns (tape dict, memory outputs dict)."""
+        ins = [x_norm, w_qx, w_qh, w_gate, w_proj, keys, norm_sq, values]
+        stride = d_m * d_s
+        tape = dict(bar_a=np.zeros((seq_len, stride), np.float32), bar_b=np.zeros((seq_len, stride), np.float32),
+                    states=np.zeros((seq_len + 1, stride), np.float32), y_ssm=np.zeros((seq_len, d_m), np.float32))
+        o = self._memory_outputs(seq_len, d_m, d_k, d_val, capacity)
+        self._check(self._lib.pssa_b200_memory_forward_after_ssm(
+            self._h, *[_ptr(a) for a in ins], seq_len, d_m, d_k, d_val, capacity, count, tau,
+            *[_ptr(tape[k]) for k in ("bar_a", "bar_b", "states", "y_ssm")],
+            *[_ptr(o[k]) for k in ("q_euc", "q_pnc", "q_norm", "weights", "m_val", "g_mem", "m_proj", "m_inj")], precision))
+        return tape, o
+
     # ---- device-side sampling (src/inference.rs:102-181)
     def sample_dev(self, logits, probs, rows, vocab, rng_state, ids_out, status_out, temperature=0.70, top_p=0.85, top_k=24,
                    repetition_penalty=1.25, recent_ids=None, recent_count=None, exact=False, confidence_out=None):
