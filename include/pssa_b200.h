@@ -380,14 +380,16 @@ int32_t pssa_b200_model_set_bank(pssa_b200_model* model, int32_t layer, const fl
  * GPU device; here it is the one runtime option the device path adds. */
 int32_t pssa_b200_model_set_top_k(pssa_b200_model* model, size_t top_k);
 int32_t pssa_b200_model_set_precision(pssa_b200_model* model, int32_t precision);
-/* Runtime options the reference refuses on any GPU device (src/pssa.rs:2080-2105, 2232-2243): always
- * PSSA_B200_ERR_UNSUPPORTED with the reference's message. option: 0 local_conv, 1 ssm_skip, 2 hybrid_read,
- * 3 grow_memory, 4 loops > 1. */
+/* Runtime options. 0 local_conv, 1 ssm_skip, 2 hybrid_read, 3 grow_memory: the reference refuses these on any GPU device
+ * (src/pssa.rs:2080-2105, 2189-2192, 2232-2243); enabling one returns PSSA_B200_ERR_UNSUPPORTED with the reference's
+ * message. 4 = `set_loops` (src/pssa.rs:2171-2184): the runtime number of weight-shared Ouro passes per block, 1..32
+ * (src/pssa.rs:2338-2376). Every pass owns a recurrent carry; changing the count keeps pass 0's carries and zeroes the
+ * others (`resize_loop_tape`, src/pssa.rs:2147-2167), and the per-stream state becomes [block][pass][d*s]. */
 int32_t pssa_b200_model_set_option(pssa_b200_model* model, int32_t option, int32_t value);
 
 /* `reset_recurrent_state` (src/pssa.rs:2245-2250) for one stream. */
 int32_t pssa_b200_model_reset_state(pssa_b200_model* model, uint32_t stream);
-/* `copy_recurrent_state_to / from` (src/pssa.rs:2263-2310): [block][d*s] fp32, len = depth*d*s. */
+/* `copy_recurrent_state_to / from` (src/pssa.rs:2263-2310): [block][pass][d*s] fp32, len = depth*loops*d*s. */
 int32_t pssa_b200_model_get_state(pssa_b200_model* model, uint32_t stream, float* out, size_t len);
 int32_t pssa_b200_model_set_state(pssa_b200_model* model, uint32_t stream, const float* data, size_t len);
 

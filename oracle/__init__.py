@@ -52,6 +52,11 @@ def lib() -> C.CDLL:
         L.pssa_oracle_model_clone.restype = C.c_void_p
         L.pssa_oracle_model_clone.argtypes = [C.c_void_p]
         L.pssa_oracle_model_free.argtypes = [C.c_void_p]
+        L.pssa_oracle_set_loops.argtypes = [C.c_void_p, C.c_size_t]
+        L.pssa_oracle_state_len.restype = C.c_size_t
+        L.pssa_oracle_state_len.argtypes = [C.c_void_p]
+        L.pssa_oracle_copy_state_to.argtypes = [C.c_void_p, _fp]
+        L.pssa_oracle_copy_state_from.argtypes = [C.c_void_p, _fp]
         L.pssa_oracle_model_config.argtypes = [C.c_void_p, _u64p, _fp, _u64p]
         L.pssa_oracle_tensor.restype = _fp
         L.pssa_oracle_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
@@ -253,14 +258,21 @@ class Model:
         sec = lib().pssa_oracle_prefill_lanes_timed(self.h, u64ptr(ids), n, T, threads, fptr(logits))
         return float(sec), logits
 
+    def set_loops(self, loops: int):
+        """Runtime Ouro pass count (pssa.rs:2171-2184); passes >= 1 start from zero carries."""
+        if lib().pssa_oracle_set_loops(self.h, loops) != 0:
+            raise ValueError("--loops must be between 1 and 32; use --loops 1 for the original model")
+
     def state(self) -> np.ndarray:
-        """Recurrent carry in the reference's `[block][d*s]` order (pssa.rs:2263-2310)."""
-        return np.concatenate([self.tensor(l, H_PERSISTENT) for l in range(self.depth)])
+        """Recurrent carry in the reference's `[block][pass][d*s]` order (pssa.rs:2263-2310)."""
+        out = np.empty(lib().pssa_oracle_state_len(self.h), np.float32)
+        lib().pssa_oracle_copy_state_to(self.h, fptr(out))
+        return out
 
     def set_state(self, flat: np.ndarray):
-        n = self.d_latent * self.d_state
-        for l in range(self.depth):
-            self.tensor(l, H_PERSISTENT)[:] = flat[l * n:(l + 1) * n]
+        flat = np.ascontiguousarray(flat, np.float32)
+        assert flat.size == lib().pssa_oracle_state_len(self.h)
+        lib().pssa_oracle_copy_state_from(self.h, fptr(flat))
 
 
 def rng_fill(seed: int, low: float, high: float, n: int) -> np.ndarray:

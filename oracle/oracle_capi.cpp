@@ -181,6 +181,10 @@ float pssa_oracle_bank_retrieve(void* h, int layer, const float* q_pnc, float ta
 }
 
 void pssa_oracle_reset_state(void* h) { ((Model*)h)->reset_recurrent_state(); }
+int pssa_oracle_set_loops(void* h, size_t loops) { return ((Model*)h)->set_loops(loops) ? 0 : -1; }
+size_t pssa_oracle_state_len(void* h) { return ((Model*)h)->state_len(); }
+void pssa_oracle_copy_state_to(void* h, float* out) { ((Model*)h)->copy_state_to(out); }
+void pssa_oracle_copy_state_from(void* h, const float* in) { ((Model*)h)->copy_state_from(in); }
 
 int pssa_oracle_forward_inference(void* h, uint64_t id, float* logits) {
     Model* m = (Model*)h;

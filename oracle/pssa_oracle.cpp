@@ -413,17 +413,79 @@ void Model::init(const Config& c, uint64_t seed) {  // pssa.rs:2019-2072
     step_counter = 0;
 }
 
-void Model::reset_recurrent_state() {
-    for (auto& b : blocks) std::fill(b.h_persistent.begin(), b.h_persistent.end(), 0.f);
+void Model::reset_recurrent_state() {  // pssa.rs:798-804, 2245-2250
+    for (auto& b : blocks) {
+        std::fill(b.h_persistent.begin(), b.h_persistent.end(), 0.f);
+        std::fill(b.loop_carry.begin(), b.loop_carry.end(), 0.f);
+    }
 }
 
-void Model::forward_features(size_t id) {  // pssa.rs:2312-2337
+bool Model::set_loops(size_t n) {  // pssa.rs:2171-2184
+    if (n < 1 || n > 32) {
+        error = "--loops must be between 1 and 32; use --loops 1 for the original model";
+        return false;
+    }
+    if (n != loops) {
+        loops = n;
+        // resize_loop_tape (pssa.rs:2147-2167) builds a fresh tape: the carries of passes >= 1 start from zero
+        for (auto& b : blocks) b.loop_carry.assign((n - 1) * b.h_persistent.size(), 0.f);
+    }
+    return true;
+}
+
+void Block::forward_loop(const float* x_features, float* z_out, size_t loop_index) {  // pssa.rs:1065-1069, 940-951
+    const size_t hs = h_persistent.size();
+    if (loop_index != 0) std::swap_ranges(h_persistent.begin(), h_persistent.end(), loop_carry.begin() + (loop_index - 1) * hs);
+    forward_token(x_features, z_out);
+    if (loop_index != 0) std::swap_ranges(h_persistent.begin(), h_persistent.end(), loop_carry.begin() + (loop_index - 1) * hs);
+}
+
+void Model::copy_state_to(float* out) const {  // pssa.rs:2263-2286
+    const size_t hs = cfg.d_latent * cfg.d_state;
+    for (size_t l = 0; l < blocks.size(); ++l) {
+        float* dst = out + l * loops * hs;
+        std::copy(blocks[l].h_persistent.begin(), blocks[l].h_persistent.end(), dst);
+        if (loops > 1) std::copy(blocks[l].loop_carry.begin(), blocks[l].loop_carry.end(), dst + hs);
+    }
+}
+
+void Model::copy_state_from(const float* in) {  // pssa.rs:2288-2310
+    const size_t hs = cfg.d_latent * cfg.d_state;
+    for (size_t l = 0; l < blocks.size(); ++l) {
+        const float* src = in + l * loops * hs;
+        std::copy(src, src + hs, blocks[l].h_persistent.begin());
+        if (loops > 1) std::copy(src + hs, src + loops * hs, blocks[l].loop_carry.begin());
+    }
+}
+
+void Model::forward_features(size_t id) {  // pssa.rs:2312-2377
     size_t d = cfg.d_latent;
-    blocks[0].forward_token(&embed[id * d], features.data());
+    if (loops == 1) {
+        blocks[0].forward_token(&embed[id * d], features.data());
+        for (size_t l = 1; l < blocks.size(); ++l) {
+            blocks[l].forward_token(features.data(), block_out.data());
+            float scale = residual_scales[l - 1];
+            for (size_t i = 0; i < d; ++i) features[i] += scale * block_out[i];
+        }
+        return;
+    }
+    // Ouro passes (pssa.rs:2338-2376): the block is applied `loops` times with shared weights and one carry per pass,
+    // every pass adding its output / loops to the features it read
+    std::copy(&embed[id * d], &embed[id * d] + d, features.begin());
+    const float loop_scale = 1.0f / (float)loops;
+    for (size_t li = 0; li < loops; ++li) {
+        blocks[0].forward_loop(features.data(), block_out.data(), li);
+        for (size_t i = 0; i < d; ++i) features[i] += loop_scale * block_out[i];
+    }
+    continuous_input.resize(d);
     for (size_t l = 1; l < blocks.size(); ++l) {
-        blocks[l].forward_token(features.data(), block_out.data());
-        float scale = residual_scales[l - 1];
-        for (size_t i = 0; i < d; ++i) features[i] += scale * block_out[i];
+        const float scale = residual_scales[l - 1];
+        std::copy(features.begin(), features.end(), continuous_input.begin());
+        for (size_t li = 0; li < loops; ++li) {
+            blocks[l].forward_loop(features.data(), block_out.data(), li);
+            for (size_t i = 0; i < d; ++i) features[i] += loop_scale * block_out[i];
+        }
+        for (size_t i = 0; i < d; ++i) features[i] = continuous_input[i] + scale * features[i];
     }
 }
 
@@ -463,8 +525,16 @@ float Model::chunk_forward(const uint64_t* ids, const uint64_t* targets, size_t 
     // pssa.rs:2597-2750 with loops == 1: token-serial blocks, then head + cross entropy per row.
     size_t d = cfg.d_latent, v = cfg.d_vocab;
     std::vector<float> acts(n * d), next(n * d), z(d);
-    for (size_t t = 0; t < n; ++t) blocks[0].forward_token(&embed[ids[t] * d], &acts[t * d]);
-    for (size_t l = 1; l < blocks.size(); ++l) {
+    if (loops > 1) {
+        // Ouro passes: the reference proves its chunk forward equal to token inference (tests/stacked_depth.rs:296-317,
+        // src/inference.rs:1069-1113 at loops 3), so the rows are the token-serial features
+        for (size_t t = 0; t < n; ++t) {
+            forward_features((size_t)ids[t]);
+            std::copy(features.begin(), features.end(), &acts[t * d]);
+        }
+    } else
+        for (size_t t = 0; t < n; ++t) blocks[0].forward_token(&embed[ids[t] * d], &acts[t * d]);
+    for (size_t l = 1; loops == 1 && l < blocks.size(); ++l) {
         float scale = residual_scales[l - 1];
         for (size_t t = 0; t < n; ++t) {
             blocks[l].forward_token(&acts[t * d], z.data());

@@ -75,6 +75,9 @@ struct Block {
     std::vector<float> a_mat, w_delta, w_b, w_c, w_qx, w_qh, w_gate, w_proj, mlp_w1, mlp_w2;
     std::vector<float> ad_down, ad_up, ad_cons;
     std::vector<float> h_persistent;
+    // carries of the Ouro passes 1..loops-1 (pass 0 owns h_persistent): [(loops-1)][d*s], the tail of the reference's
+    // tape.h_states (pssa.rs:934-951)
+    std::vector<float> loop_carry;
     Bank memory;
     // derived: A = -softplus(raw) (pssa.rs:787-796)
     std::vector<float> rates;
@@ -86,6 +89,8 @@ struct Block {
     void refresh_rates();
     // pssa.rs:1072-1209: one token, carry updated in place
     void forward_token(const float* x_features, float* z_out);
+    // pssa.rs:1065-1069: one Ouro pass = the same token step on that pass's own carry
+    void forward_loop(const float* x_features, float* z_out, size_t loop_index);
     void consolidate(float alpha);                      // adapter.rs:65-72
     void dream_replay_value(const float* target);       // pssa.rs:1814-1832 (uses last ad_act/ad_out)
 };
@@ -98,19 +103,24 @@ struct Model {
     std::vector<float> embed, unembed;
     std::vector<Block> blocks;
     std::vector<float> residual_scales;
-    std::vector<float> features, block_out;
+    std::vector<float> features, block_out, continuous_input;
+    size_t loops = 1;  // runtime Ouro pass count (pssa.rs:2171-2184); not part of the checkpoint
     std::string error;
     void init(const Config& c, uint64_t seed);                  // pssa.rs:2019-2072
     bool load(const uint8_t* bytes, size_t len);                // checkpoint.rs V7 / V8
     void reset_recurrent_state();                               // pssa.rs:2245-2250
-    void forward_features(size_t id);                           // pssa.rs:2312-2337 (loops == 1)
+    // pssa.rs:2171-2184 + resize_loop_tape 2147-2167: pass 0 keeps its carry, the other passes start from zero
+    bool set_loops(size_t n);
+    void forward_features(size_t id);                           // pssa.rs:2312-2377 (single pass and Ouro passes)
     void logits(float* out) const;                              // pssa.rs:2379-2385
     void forward_inference(size_t id, float* logits_out);       // pssa.rs:2387-2391
     // pssa.rs:2399-2442. returns 1 ok, 0 cancelled (never here), -1 error; *processed = tokens advanced
     int prefill_inference(const uint64_t* ids, size_t n, float* logits_or_null, size_t* processed);
     // token-serial training-style forward over one chunk (pssa.rs:2597-2750): fills logits[T*V], returns loss
     float chunk_forward(const uint64_t* ids, const uint64_t* targets, size_t n, float* logits_out);
-    size_t state_len() const { return cfg.depth * cfg.d_latent * cfg.d_state; }
+    size_t state_len() const { return cfg.depth * loops * cfg.d_latent * cfg.d_state; }  // pssa.rs:2255-2261
+    void copy_state_to(float* out) const;     // pssa.rs:2263-2286: [block][pass][d*s]
+    void copy_state_from(const float* in);    // pssa.rs:2288-2310
 };
 
 // src/gpu_batch.rs:84-164

@@ -158,14 +158,21 @@ __global__ void __launch_bounds__(256) multiply_kernel(const float* __restrict__
     if (idx < n) out[idx] = __fmul_rn(a[idx], b[idx]);
 }
 
+// src_rows != 0: indices come from the caller's device memory and are checked here; an index outside the table reads row 0
+// and raises PSSA_B200_ERR_TOKEN in the status word (the rule of the embedding kernel)
 __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restrict__ src, const uint32_t* __restrict__ rows_idx,
-                                                          float* __restrict__ dst, size_t n_rows, int d) {
+                                                          float* __restrict__ dst, size_t n_rows, int d, size_t src_rows, int* status) {
     pdl_trigger();  // the next kernel in the stream may start its prologue now ...
     pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n_rows * (size_t)d) return;
     size_t r = idx / d;
-    dst[idx] = src[(size_t)rows_idx[r] * d + idx % d];
+    size_t row = rows_idx[r];
+    if (src_rows != 0 && row >= src_rows) {
+        if (status && idx % d == 0) atomicExch(status, PSSA_B200_ERR_TOKEN);
+        row = 0;
+    }
+    dst[idx] = src[row * d + idx % d];
 }
 
 __global__ void __launch_bounds__(256) to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
@@ -367,9 +374,9 @@ int32_t launch_multiply(pssa_b200_ctx* ctx, const float* a, const float* b, floa
     return after_launch(ctx, "multiply_kernel");
 }
 
-int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d) {
+int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d, size_t src_rows) {
     PSSA_CUDA(ctx, launch_dependent(gather_rows_kernel, dim3(blocks_for(n_rows * (size_t)d, 256)), dim3(256), 0, ctx->stream, src, rows_idx, dst,
-                                    n_rows, d));
+                                    n_rows, d, src_rows, ctx->status_dev));
     return after_launch(ctx, "gather_rows_kernel");
 }
 

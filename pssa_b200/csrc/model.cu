@@ -262,9 +262,33 @@ int32_t pssa_b200_model_set_option(pssa_b200_model* m, int32_t option, int32_t v
             if (!value) return PSSA_B200_OK;
             return mfail(m, PSSA_B200_ERR_UNSUPPORTED, "hybrid read currently requires the CPU backend");
         case 3: return mfail(m, PSSA_B200_ERR_UNSUPPORTED, "grow memory on the CPU checkpoint before selecting a GPU backend");
-        case 4:
-            if (value == 1) return PSSA_B200_OK;
-            return mfail(m, PSSA_B200_ERR_UNSUPPORTED, "Ouro loops above 1 are not implemented on the B200 path");
+        case 4: {  // set_loops (src/pssa.rs:2171-2184): pass 0 keeps its carry, the other passes start from zero
+            if (value < 1 || value > 32)
+                return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "--loops must be between 1 and 32; use --loops 1 for the original model");
+            if ((size_t)value == m->loops) return PSSA_B200_OK;
+            pssa_b200_ctx* ctx = m->ctx;
+            PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+            PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            const size_t ds = m->d * m->s, nl = (size_t)value, blocks = (size_t)m->max_streams * m->depth;
+            float* fresh = nullptr;
+            PSSA_CUDA(ctx, cudaMalloc((void**)&fresh, blocks * nl * ds * 4));
+            cudaError_t e = cudaMemsetAsync(fresh, 0, blocks * nl * ds * 4, ctx->stream);
+            if (e == cudaSuccess)  // [stream][block] rows of `loops` carries: copy the first carry of every row
+                e = cudaMemcpy2DAsync(fresh, nl * ds * 4, m->state, m->loops * ds * 4, ds * 4, blocks, cudaMemcpyDeviceToDevice, ctx->stream);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+            if (e != cudaSuccess) {
+                cudaFree(fresh);
+                return cuda_fail(ctx, e, "resizing the recurrent state for the Ouro passes");
+            }
+            cudaFree(m->state);
+            m->state = fresh;
+            m->loops = nl;
+            // the extra feature buffer of the passes lives in the activation workspace: rebuild it on the next call
+            if (m->ws.base) cudaFree(m->ws.base);
+            m->ws = pssa::Workspace();
+            m->dev_layout.ws_base = nullptr;
+            return PSSA_B200_OK;
+        }
         default: return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }
@@ -279,14 +303,14 @@ int32_t pssa_b200_model_reset_state(pssa_b200_model* m, uint32_t stream) {
     if (!m) return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
     if (stream >= m->max_streams) return fail(m->ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u outside %u streams", stream, m->max_streams);
     PSSA_CUDA(m->ctx, cudaSetDevice(m->ctx->device));
-    size_t n = m->depth * m->d * m->s;
+    size_t n = m->depth * m->loops * m->d * m->s;
     PSSA_CUDA(m->ctx, cudaMemsetAsync(m->state + (size_t)stream * n, 0, n * 4, m->ctx->stream));
     return PSSA_B200_OK;
 }
 
 int32_t pssa_b200_model_get_state(pssa_b200_model* m, uint32_t stream, float* out, size_t len) {
     if (!m || !out) return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "null argument");
-    size_t n = m->depth * m->d * m->s;
+    size_t n = m->depth * m->loops * m->d * m->s;
     if (stream >= m->max_streams || len != n)
         return fail(m->ctx, PSSA_B200_ERR_SHAPE, "recurrent state: stream %u of %u, length %zu, expected %zu", stream, m->max_streams, len, n);
     PSSA_CUDA(m->ctx, cudaSetDevice(m->ctx->device));
@@ -297,7 +321,7 @@ int32_t pssa_b200_model_get_state(pssa_b200_model* m, uint32_t stream, float* ou
 
 int32_t pssa_b200_model_set_state(pssa_b200_model* m, uint32_t stream, const float* data, size_t len) {
     if (!m || !data) return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "null argument");
-    size_t n = m->depth * m->d * m->s;
+    size_t n = m->depth * m->loops * m->d * m->s;
     if (stream >= m->max_streams || len != n)
         return fail(m->ctx, PSSA_B200_ERR_SHAPE, "recurrent state: stream %u of %u, length %zu, expected %zu", stream, m->max_streams, len, n);
     PSSA_CUDA(m->ctx, cudaSetDevice(m->ctx->device));

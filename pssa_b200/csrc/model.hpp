@@ -52,6 +52,7 @@ struct Workspace {
     size_t rows = 0, lanes = 0;
     uint32_t *ids = nullptr, *lane_off = nullptr, *lane_len = nullptr, *lane_slot = nullptr, *last_rows = nullptr,
              *greedy = nullptr;
+    float* feat_c = nullptr;  // Ouro passes only: a block's input features, kept for its depth residual
     float *feat_a = nullptr, *feat_b = nullptr, *x_norm = nullptr, *proj = nullptr, *y = nullptr, *weights = nullptr,
           *m_val = nullptr, *m_proj = nullptr, *z = nullptr, *mlp_act = nullptr, *last_feat = nullptr, *logits = nullptr;
     void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr;
@@ -73,6 +74,7 @@ struct pssa_b200_model {
     uint32_t max_streams = 1;
     uint32_t precision = 0;  // PSSA_B200_PRECISION_*
     size_t top_k = 0;
+    size_t loops = 1;  // Ouro passes per block (src/pssa.rs:2171-2184): shared weights, one carry per pass
     size_t max_rows = 65536;
     float* embed = nullptr;
     float* unembed = nullptr;
@@ -80,7 +82,7 @@ struct pssa_b200_model {
     bool unembed_dirty = true;
     std::vector<pssa::DeviceBlock> blocks;
     std::vector<float> residual_scales;
-    float* state = nullptr;  // [max_streams][depth][d*s]
+    float* state = nullptr;  // [max_streams][depth][loops][d*s]  (src/pssa.rs:2255-2310)
     pssa::Workspace ws;
     // sequence-parallel prefill (world > 1): this process holds time shard `rank` of every lane
     struct SeqPar {

@@ -33,6 +33,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     Carver c;
     size_t o_ids = c.take(rows * 4), o_off = c.take(lanes * 4), o_len = c.take(lanes * 4), o_slot = c.take(lanes * 4),
            o_last = c.take(lanes * 4), o_greedy = c.take(lanes * 4);
+    size_t o_fc = c.take(m->loops > 1 ? rows * d * f : 0);
     size_t o_fa = c.take(rows * d * f), o_fb = c.take(rows * d * f), o_xn = c.take(rows * d * f),
            o_proj = c.take(rows * m->ncat * f), o_y = c.take(rows * d * f), o_w = c.take(rows * m->cap * f),
            o_mv = c.take(rows * d * f), o_mp = c.take(rows * d * f), o_z = c.take(rows * d * f),
@@ -55,6 +56,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     char* b = ws.base;
     ws.ids = (uint32_t*)(b + o_ids), ws.lane_off = (uint32_t*)(b + o_off), ws.lane_len = (uint32_t*)(b + o_len);
     ws.lane_slot = (uint32_t*)(b + o_slot), ws.last_rows = (uint32_t*)(b + o_last), ws.greedy = (uint32_t*)(b + o_greedy);
+    ws.feat_c = m->loops > 1 ? (float*)(b + o_fc) : nullptr;
     ws.feat_a = (float*)(b + o_fa), ws.feat_b = (float*)(b + o_fb), ws.x_norm = (float*)(b + o_xn);
     ws.proj = (float*)(b + o_proj), ws.y = (float*)(b + o_y), ws.weights = (float*)(b + o_w), ws.m_val = (float*)(b + o_mv);
     ws.m_proj = (float*)(b + o_mp), ws.z = (float*)(b + o_z), ws.mlp_act = (float*)(b + o_act);
@@ -200,10 +202,14 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         }
         ob.valid_lanes = n_obs;
     }
-    for (size_t l = 0; l < m->depth; ++l) {
+    // One application of block `l` on carry `li` (Ouro pass; 0 for the ordinary model): reads `feat_in` (nullptr: the
+    // embedding rows of the ids), writes feat_out = res_in ? res_in + rscale * z : z, z being the block's output.
+    auto run_pass = [&](size_t l, size_t li, const float* feat_in, const float* res_in, float rscale, float* feat_out, bool publish) -> int32_t {
         DeviceBlock& b = m->blocks[l];
+        float* const carry_base = m->state + (l * m->loops + li) * ds;
+        const size_t carry_stride = m->depth * m->loops * ds;
         // stage 1: gather + RMSNorm (src/gpu_batch.rs:445-472)
-        if ((rc = launch_embed_norm(ctx, m->embed, l == 0 ? ws.ids : nullptr, feat_in, b.w[T_NORM_GAMMA], b.w[T_NORM_BETA],
+        if ((rc = launch_embed_norm(ctx, m->embed, feat_in ? nullptr : ws.ids, feat_in, b.w[T_NORM_GAMMA], b.w[T_NORM_BETA],
                                     ws.x_norm, exact ? nullptr : ws.x_bf16, rows, d, exact, m->v)))
             return rc;
         // stage 2: x-side projections (src/gpu_batch.rs:477-536 plus the query/gate/adapter rows that read x_norm)
@@ -224,9 +230,9 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // stage 3: SSM with the lane carries of this block (src/gpu_batch.rs:582-619)
         SsmParams sp{};
         sp.delta = ws.proj + m->off_delta, sp.x_norm = ws.x_norm, sp.b_proj = ws.proj + m->off_b, sp.c_proj = ws.proj + m->off_c;
-        sp.rates = b.rates, sp.carry = m->state + l * ds, sp.y = ws.y, sp.y_bf16 = exact ? nullptr : ws.y_bf16;
+        sp.rates = b.rates, sp.carry = carry_base, sp.y = ws.y, sp.y_bf16 = exact ? nullptr : ws.y_bf16;
         sp.offsets = ws.lane_off, sp.lengths = ws.lane_len, sp.rows = rows, sp.d = d, sp.s = s, sp.lanes = (int)lanes;
-        sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = m->depth * ds;
+        sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = carry_stride;
         sp.aligned = ssm_vector_ok(sp);
         sp.single_token = single_token;
         if (two_pass) {
@@ -250,7 +256,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             }
             // fold in time order: carry-in of each of this rank's chunks, and the lanes' final state
             if ((rc = launch_seqpar_fold(ctx, gathered, rec, world, rank, (int)n_chunks, (int)lanes, vlanes * rec, b.rates,
-                                         m->state + l * ds, m->depth * ds, ws.lane_slot, m->chunks.carry_in, d, s)))
+                                         carry_base, carry_stride, ws.lane_slot, m->chunks.carry_in, d, s)))
                 return rc;
             // pass 2: the real one, over the virtual lanes with their carry-ins (carry-outs are scratch)
             sp.offsets = m->chunks.off, sp.lengths = m->chunks.len, sp.lanes = (int)vlanes;
@@ -260,9 +266,10 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
         if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
         RetrieveParams rp{};
-        rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = observe ? m->obs.q_pnc : nullptr, rp.q_norm = nullptr;
+        const bool obs_now = observe && publish;
+        rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = obs_now ? m->obs.q_pnc : nullptr, rp.q_norm = nullptr;
         rp.keys = b.w[T_BANK_KEYS], rp.norm_sq = b.w[T_BANK_NORM_SQ], rp.values = b.w[T_BANK_VALUES];
-        rp.weights = ws.weights, rp.m_val = (exact || observe) ? ws.m_val : nullptr, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
+        rp.weights = ws.weights, rp.m_val = (exact || obs_now) ? ws.m_val : nullptr, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
         // the bf16 mode keeps only the bf16 copy of m (the W_proj operand), so its value read is one plain bf16 product of the
         // leading pieces (the three-term read cost 70 us more per block for a logit error of 9.1e-3 instead of 9.3e-3)
         rp.value_terms = exact ? 6 : 1;
@@ -271,17 +278,16 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         rp.f32_distance = !exact;  // the bf16 mode's queries carry bf16 rounding already; f64 distances buy nothing there
         if (!exact && m->cap % 64 == 0) rp.w_split = ws.w_split, rp.v_split = b.vsplit_bf16;
         // only the observer reads the fp32 weight rows after the value read
-        rp.skip_weights = rp.w_split && !observe && !(rp.top_k != 0 && rp.top_k < rp.count);
+        rp.skip_weights = rp.w_split && !obs_now && !(rp.top_k != 0 && rp.top_k < rp.count);
         if (!exact && k % 64 == 0) rp.q_split = ws.q_split, rp.q_stat = ws.q_stat, rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
         // All-slots read in the bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s). The bank's values were carried
         // through W_proj at upload (vpsplit_bf16), so the product of the weight rows with them IS the memory projection and
         // takes the gate epilogue directly: the value read stops after the softmax (no m, no separate W_proj launch). The
         // observer wants m itself and keeps the two-product schedule.
-        const bool proj_in_read = !exact && !observe && rp.w_split && !(rp.top_k != 0 && rp.top_k < rp.count) && rp.count > 0;
+        const bool proj_in_read = !exact && !(observe && publish) && rp.w_split && !(rp.top_k != 0 && rp.top_k < rp.count) && rp.count > 0;
         rp.skip_value_read = proj_in_read;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
-        const float rscale = l == 0 ? 1.0f : m->residual_scales[l - 1];
         if (exact) {
             if ((rc = launch_gemm_exact(ctx, ws.m_val, b.w[T_W_PROJ], ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
             if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z, nullptr,
@@ -290,7 +296,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             if ((rc = launch_gemm_exact(ctx, ws.z, b.w[T_MLP_W1], ws.mlp_act, rows, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f))) return rc;
             // MLP down projection + residual, then depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
             if ((rc = launch_gemm_exact(ctx, ws.mlp_act, b.w[T_MLP_W2], ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
-            if ((rc = launch_residual(ctx, l == 0 ? nullptr : feat_in, ws.z, feat_out, rows * (size_t)d, rscale))) return rc;
+            if ((rc = launch_residual(ctx, res_in, ws.z, feat_out, rows * (size_t)d, rscale))) return rc;
         } else {
             // Tensor-core schedule: z = y/sqrt(s) + g*(W_proj m) + U*act never exists as one array. The memory projection's
             // epilogue forms zp = g*acc + y/sqrt(s), kept as bf16 only: it is W1's operand and W2's additive input (an fp32
@@ -308,15 +314,40 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, b.w1cat_bf16, nullptr, ws.act_bf16, rows, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
                 return rc;
             if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2cat_bf16, feat_out, ws.z_bf16,
-                                                l == 0 ? nullptr : feat_in, rscale, rows, m->d, lda, ldz)))
+                                                res_in, rscale, rows, m->d, lda, ldz)))
                 return rc;
         }
-        if (observe && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, ws.weights, (int)m->cap, m->obs.q_pnc, k, ws.m_val,
-                                                 exact ? ws.z : nullptr, feat_out, l == 0 ? nullptr : feat_in, rscale, d,
+        if (obs_now && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, ws.weights, (int)m->cap, m->obs.q_pnc, k, ws.m_val,
+                                                 exact ? ws.z : nullptr, feat_out, res_in, rscale, d,
                                                  m->obs.buf + l * m->obs.lanes * obs_rec)))
             return rc;
-        feat_in = feat_out;
-        feat_out = (feat_out == ws.feat_a) ? ws.feat_b : ws.feat_a;
+        return PSSA_B200_OK;
+    };
+    auto other = [&](float* f) { return f == ws.feat_a ? ws.feat_b : ws.feat_a; };
+    if (m->loops == 1) {
+        // src/pssa.rs:2327-2337: block 0's output replaces the embedding, every further block adds its scaled output
+        for (size_t l = 0; l < m->depth; ++l) {
+            if ((rc = run_pass(l, 0, feat_in, feat_in, l == 0 ? 1.0f : m->residual_scales[l - 1], feat_out, true))) return rc;
+            feat_in = feat_out;
+            feat_out = other(feat_out);
+        }
+    } else {
+        // Ouro passes (src/pssa.rs:2338-2376): features start as the embedding rows; every pass of a block reads the
+        // running features and adds its output / loops; a stacked block's passes then fold into the depth residual
+        // features = input + scale * features.
+        const float loop_scale = 1.0f / (float)m->loops;
+        float* feat = ws.feat_a;
+        if ((rc = launch_gather_rows(ctx, m->embed, ws.ids, feat, rows, d, m->v))) return rc;
+        for (size_t l = 0; l < m->depth; ++l) {
+            if (l > 0 && (rc = launch_residual(ctx, nullptr, feat, ws.feat_c, rows * (size_t)d, 1.0f))) return rc;  // keep the block's input
+            for (size_t li = 0; li < m->loops; ++li) {
+                float* next = other(feat);
+                if ((rc = run_pass(l, li, feat, feat, loop_scale, next, li + 1 == m->loops))) return rc;
+                feat = next;
+            }
+            if (l > 0 && (rc = launch_residual(ctx, ws.feat_c, feat, feat, rows * (size_t)d, m->residual_scales[l - 1]))) return rc;
+        }
+        feat_in = feat;
     }
     *feats_out = feat_in;
     return PSSA_B200_OK;

@@ -110,13 +110,14 @@ class PSSAModel:
         if not 1 <= loops <= 32:
             raise N.B200Error(N.ERR_INVALID_ARGUMENT, "--loops must be between 1 and 32; use --loops 1 for the original model")
         self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 4, int(loops)))
+        self.loops = int(loops)
 
     def set_max_rows(self, rows):
         self.gpu._check(self._lib.pssa_b200_model_set_max_rows(self._h, rows))
 
     # ---- recurrent state (src/pssa.rs:2245-2310)
     def recurrent_state_len(self):
-        return self.depth * self.d_latent * self.d_state
+        return self.depth * getattr(self, "loops", 1) * self.d_latent * self.d_state
 
     def reset_recurrent_state(self, stream=None):
         for s in (range(self.streams) if stream is None else [stream]):

@@ -233,3 +233,48 @@ def test_reference_cpu_scans_differ_elementwise_at_cancellations():
     assert np.max(np.abs(st0 - st1)) < 2e-5
     assert rel_err(st0[1:], st1[1:]) > 1e-5
     assert chan_err(st1[1:], st0[1:], 0) < 1e-5
+
+
+def test_ouro_passes_first_pass_keeps_the_single_pass_math_and_prefill_equals_the_token_loop():
+    """Runtime Ouro passes (src/pssa.rs:2338-2376). Reference-held properties: the first shared pass preserves the
+    single-pass math (tests/loops.rs:42-62: pass 0 of a loops-2 model reproduces the loops-1 states bit for bit, because it
+    reads the same embedding rows on its own carry), prefill == token loop bitwise at loops 3 with non-reset carries
+    (src/inference.rs:1069-1113), and set_loops keeps pass 0's carry while the new passes start from zero."""
+    from helpers import fill_synthetic
+    ids = (np.arange(40) * 5 + 1) % 31
+    one = O.Model.new(1, 31, 8, 4, 4, 6, seed=0xfeed)
+    fill_synthetic(one, 2)
+    two = one.clone()
+    two.set_loops(2)
+    assert two.state().size == 2 * one.state().size
+    for t in ids:
+        one.forward_inference(int(t))
+        two.forward_inference(int(t))
+    hs = one.state().size
+    assert np.array_equal(two.state()[:hs].view(np.uint32), one.state().view(np.uint32))
+    assert np.any(two.state()[hs:] != 0)
+    # prefill == token loop at loops 3, depth 2, carries not reset in between
+    a = O.Model.new(2, 31, 8, 4, 4, 6, seed=11)
+    fill_synthetic(a, 3)
+    a.set_loops(3)
+    b = a.clone()
+    a.prefill_inference(ids[:7])
+    for t in ids[:7]:
+        b.forward_inference(int(t))
+    _, _, la = a.prefill_inference(ids[7:])
+    for t in ids[7:]:
+        lb = b.forward_inference(int(t))
+    assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    assert np.array_equal(a.state().view(np.uint32), b.state().view(np.uint32))
+    assert a.state().size == 2 * 3 * 8 * 4
+    # the state round-trips in [block][pass][d*s] order, and changing the count keeps pass 0 only
+    st = a.state()
+    c = a.clone()
+    c.set_state(st[::-1].copy())
+    assert np.array_equal(c.state(), st[::-1])
+    c.set_state(st)
+    c.set_loops(2)
+    got = c.state().reshape(2, 2, 32)
+    assert np.array_equal(got[:, 0], st.reshape(2, 3, 32)[:, 0]) and not got[:, 1].any()
+    with pytest.raises(ValueError, match="--loops must be between 1 and 32"):
+        c.set_loops(33)
