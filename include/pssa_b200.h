@@ -193,6 +193,14 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
  * bf16 precision mode uses it). Needs d_key % 64 == 0, otherwise PSSA_B200_MEM_F32_DISTANCE behaviour applies.
  * Ignored together with PSSA_B200_MEM_EXACT. */
 #define PSSA_B200_MEM_TC_DISTANCE 4u
+/* Top-k reads whose shape allows it (capacity 128 / 256 / 512, d_key 64 or 128, top_k <= 12, a mostly full bank) run as
+ * ONE kernel: tensor-core inner products only pre-filter the slots, the candidates are re-scored with the reference's f64
+ * arithmetic and selected by (distance bits, slot), and a row whose selection cannot be proven from the candidates is
+ * handed to an exact pass over every slot. Results are those of the default f64 path. This flag keeps the separate
+ * distance / selection kernels instead (for comparison). */
+#define PSSA_B200_MEM_NO_FUSED 8u
+/* Test hook: the one-kernel top-k read hands every third row to its exact pass regardless of the proof. */
+#define PSSA_B200_MEM_HANDOVER_SELFTEST 16u
 
 /*
  * Poincare-ball memory read for `rows` queries against one immutable bank. Replaces
@@ -217,6 +225,19 @@ int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_e
                               size_t d_key, size_t d_val, size_t capacity, size_t count, float tau,
                               size_t top_k, float* q_pnc, float* q_norm, float* weights, float* m_val,
                               float* min_dist, uint32_t flags);
+/*
+ * Top-k read (0 < top_k < count) with COMPACT results instead of the reference's dense weight row (src/memory.rs:380-408
+ * zero-fills `out_weights` and sets k entries): slots_out [rows, top_k] (u32) and weights_out [rows, top_k], the selected
+ * slots in ascending slot order -- the order the reference sums and mixes them in -- and their normalised weights;
+ * either may be NULL. 8 * top_k bytes per query instead of 4 * capacity. handed_over (DEVICE u32, NULL to skip) receives
+ * the number of rows the one-kernel read gave to its exact pass. Other arguments as pssa_b200_memory_read_dev. Shapes
+ * outside the one-kernel read's range run the separate kernels with scratch weight rows and are compacted afterwards
+ * (a selected slot whose weight underflowed to zero is then reported as 0xffffffff).
+ */
+int32_t pssa_b200_memory_read_topk_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys,
+                                       const float* norm_sq, const float* values, size_t rows, size_t d_key, size_t d_val,
+                                       size_t capacity, size_t count, float tau, size_t top_k, float* q_pnc, float* q_norm, float* m_val,
+                                       float* min_dist, uint32_t* slots_out, float* weights_out, uint32_t* handed_over, uint32_t flags);
 
 /* ------------------------------------------------------------------ memory stage and resident SSM, one call each */
 

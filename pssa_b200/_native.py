@@ -34,6 +34,8 @@ SIGNATURES = {
     "pssa_b200_ssm_forward": (C.c_int32, [_vp] * 7 + [_sz, _sz, _sz] + [_vp] * 4 + [C.c_uint32]),
     "pssa_b200_memory_read_dev": (C.c_int32, [_vp, _vp, C.c_int32, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _sz,
                                               _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
+    "pssa_b200_memory_read_topk_dev": (C.c_int32, [_vp, _vp, C.c_int32, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _sz,
+                                                   _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "pssa_b200_memory_read": (C.c_int32, [_vp, _vp, C.c_int32, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, C.c_float, _sz,
                                           _vp, _vp, _vp, _vp, _vp, C.c_uint32]),
     "pssa_b200_memory_forward": (C.c_int32, [_vp] * 10 + [_sz] * 6 + [C.c_float] + [_vp] * 8 + [C.c_int32]),
@@ -80,6 +82,8 @@ SSM_EXACT = 1
 MEM_EXACT = 1
 MEM_F32_DISTANCE = 2
 MEM_TC_DISTANCE = 4
+MEM_NO_FUSED = 8
+MEM_HANDOVER_SELFTEST = 16
 EPI_NONE, EPI_SOFTPLUS, EPI_SIGMOID, EPI_SILU, EPI_SCALE, EPI_ADD_OUT = range(6)
 PRECISION_BF16, PRECISION_FP32_EXACT = 0, 1
 CANCEL_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)

@@ -348,56 +348,105 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
 
 // ------------------------------------------------------------------ episodic memory read
 
+// Shared body of the device-pointer read entry points. `slots_out` / `topk_w_out` [rows, top_k] are the compact results of
+// a top-k read (ascending slot order); `handed_over` receives the number of rows the one-kernel read gave to its exact pass.
+static int32_t memory_read_impl(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys, const float* norm_sq,
+                                const float* values, size_t rows, size_t d_key, size_t d_val, size_t capacity, size_t count, float tau,
+                                size_t top_k, float* q_pnc, float* q_norm, float* weights, float* m_val, float* min_dist,
+                                uint32_t* slots_out, float* topk_w_out, uint32_t* handed_over, uint32_t flags) {
+    int32_t rc = memory_shape(ctx, rows, d_key, d_val, capacity, count, tau);
+    if (rc != PSSA_B200_OK) return rc;
+    if (!q || !keys || !norm_sq || !values || !m_val)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
+    const uint32_t known = PSSA_B200_MEM_EXACT | PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE | PSSA_B200_MEM_NO_FUSED |
+                           PSSA_B200_MEM_HANDOVER_SELFTEST;
+    if (flags & ~known) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    // scratch from the arena: the weight rows when the caller does not want them, the bf16 pieces of the weights and of the
+    // transposed values for the tensor-core value read (all-slots mode, capacity % 64 == 0), the key pieces of the
+    // tensor-core distances / of the one-kernel top-k read with its hand-over list
+    const bool exact = (flags & PSSA_B200_MEM_EXACT) != 0;
+    const bool topk = top_k != 0 && top_k < count;
+    const bool approx = !exact && (flags & (PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE)) != 0;
+    RetrieveParams p{};
+    p.q = q, p.q_is_euclidean = q_is_euclidean, p.q_pnc = q_pnc, p.q_norm = q_norm;
+    p.keys = keys, p.norm_sq = norm_sq, p.values = values;
+    p.m_val = m_val, p.min_dist = min_dist;
+    p.rows = rows, p.dk = (int)d_key, p.dv = (int)d_val, p.cap = (int)capacity, p.count = (int)count;
+    p.top_k = (int)(top_k > capacity ? capacity : top_k), p.tau = tau;
+    p.f32_distance = (flags & (PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE)) != 0;
+    p.no_fused = approx || (flags & PSSA_B200_MEM_NO_FUSED) != 0;
+    p.selftest_every = (flags & PSSA_B200_MEM_HANDOVER_SELFTEST) ? 3 : 0;
+    // would the one-kernel top-k read take this call? (decided on the shape; its scratch pointers are filled in below)
+    RetrieveParams probe = p;
+    probe.k_split = probe.k_stat = nullptr;
+    unsigned dummy = 0;
+    probe.k_split = &dummy, probe.k_stat = reinterpret_cast<const float2*>(&dummy), probe.fixup_list = &dummy, probe.fixup_count = &dummy;
+    const bool fused = topk && !p.no_fused && retrieve_fused_eligible(probe);
+    const bool tc_read = !exact && !topk && count > 0 && capacity % 64 == 0;
+    const bool tc_dist = !exact && !fused && (flags & PSSA_B200_MEM_TC_DISTANCE) != 0 && d_key % 64 == 0 && count > 0;
+    const bool need_dense = !weights && !fused;
+    const bool key_pieces = tc_dist || fused;
+    size_t need = (need_dense ? arena_round(rows * capacity * 4) : 0) +
+                  (tc_read ? arena_round(rows * 3 * capacity * 2) + arena_round(d_val * 3 * capacity * 2) : 0) +
+                  (tc_dist ? arena_round(rows * 3 * d_key * 2) + arena_round(rows * 8) : 0) +
+                  (key_pieces ? arena_round(capacity * 3 * d_key * 2) + arena_round(capacity * 8) : 0) +
+                  (fused ? arena_round((rows + 1) * 4) : 0);
+    if (need) {
+        arena_reset(ctx);
+        if ((rc = arena_reserve(ctx, need)) != PSSA_B200_OK) return rc;
+        if (need_dense) weights = (float*)arena_take(ctx, rows * capacity * 4);
+        if (tc_read) {
+            p.w_split = arena_take(ctx, rows * 3 * capacity * 2);
+            void* v_split = arena_take(ctx, d_val * 3 * capacity * 2);
+            if ((rc = launch_split_values(ctx, values, v_split, (int)capacity, (int)d_val)) != PSSA_B200_OK) return rc;
+            p.v_split = v_split;
+        }
+        if (key_pieces) {
+            void* k_split = arena_take(ctx, capacity * 3 * d_key * 2);
+            float2* k_stat = (float2*)arena_take(ctx, capacity * 8);
+            if ((rc = launch_split_keys(ctx, keys, norm_sq, k_split, k_stat, (int)capacity, (int)d_key)) != PSSA_B200_OK) return rc;
+            p.k_split = k_split, p.k_stat = k_stat;
+        }
+        if (tc_dist) p.q_split = arena_take(ctx, rows * 3 * d_key * 2), p.q_stat = (float2*)arena_take(ctx, rows * 8);
+        if (fused) {
+            uint32_t* fx = (uint32_t*)arena_take(ctx, (rows + 1) * 4);
+            p.fixup_count = fx, p.fixup_list = fx + 1;
+        }
+    }
+    p.weights = weights;
+    if (fused) p.topk_slots = slots_out, p.topk_weights = topk_w_out;
+    if ((rc = launch_memory_read(ctx, p, exact)) != PSSA_B200_OK) return rc;
+    if (!fused && topk && (slots_out || topk_w_out) &&
+        (rc = launch_compact_topk(ctx, weights, (int)capacity, p.top_k, rows, slots_out, topk_w_out)) != PSSA_B200_OK)
+        return rc;
+    if (handed_over) {
+        if (fused)
+            PSSA_CUDA(ctx, cudaMemcpyAsync(handed_over, p.fixup_count, 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        else
+            PSSA_CUDA(ctx, cudaMemsetAsync(handed_over, 0, 4, ctx->stream));
+    }
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_memory_read_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys,
                                   const float* norm_sq, const float* values, size_t rows, size_t d_key, size_t d_val,
                                   size_t capacity, size_t count, float tau, size_t top_k, float* q_pnc, float* q_norm,
                                   float* weights, float* m_val, float* min_dist, uint32_t flags) {
     if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
-    int32_t rc = memory_shape(ctx, rows, d_key, d_val, capacity, count, tau);
-    if (rc != PSSA_B200_OK) return rc;
-    if (!q || !keys || !norm_sq || !values || !m_val)
-        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
-    if (flags & ~(PSSA_B200_MEM_EXACT | PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE)) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
-    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
-    // scratch from the arena: the weight rows when the caller does not want them, and the bf16 pieces of the
-    // weights and of the transposed values for the tensor-core value read (all-slots mode, capacity % 64 == 0)
-    const bool exact = (flags & PSSA_B200_MEM_EXACT) != 0;
-    const bool topk = top_k != 0 && top_k < count;
-    const bool tc_read = !exact && !topk && count > 0 && capacity % 64 == 0;
-    const bool tc_dist = !exact && (flags & PSSA_B200_MEM_TC_DISTANCE) != 0 && d_key % 64 == 0 && count > 0;
-    size_t need = (weights ? 0 : arena_round(rows * capacity * 4)) +
-                  (tc_read ? arena_round(rows * 3 * capacity * 2) + arena_round(d_val * 3 * capacity * 2) : 0) +
-                  (tc_dist ? arena_round(rows * 3 * d_key * 2) + arena_round(rows * 8) + arena_round(capacity * 3 * d_key * 2) +
-                                 arena_round(capacity * 8)
-                           : 0);
-    void* w_split = nullptr;
-    void* v_split = nullptr;
-    if (need) {
-        arena_reset(ctx);
-        if ((rc = arena_reserve(ctx, need)) != PSSA_B200_OK) return rc;
-        if (!weights) weights = (float*)arena_take(ctx, rows * capacity * 4);
-        if (tc_read) {
-            w_split = arena_take(ctx, rows * 3 * capacity * 2);
-            v_split = arena_take(ctx, d_val * 3 * capacity * 2);
-            if ((rc = launch_split_values(ctx, values, v_split, (int)capacity, (int)d_val)) != PSSA_B200_OK) return rc;
-        }
-    }
-    RetrieveParams p{};
-    if (tc_dist) {
-        void* k_split = arena_take(ctx, capacity * 3 * d_key * 2);
-        float2* k_stat = (float2*)arena_take(ctx, capacity * 8);
-        p.q_split = arena_take(ctx, rows * 3 * d_key * 2), p.q_stat = (float2*)arena_take(ctx, rows * 8);
-        if ((rc = launch_split_keys(ctx, keys, norm_sq, k_split, k_stat, (int)capacity, (int)d_key)) != PSSA_B200_OK) return rc;
-        p.k_split = k_split, p.k_stat = k_stat;
-    }
-    p.q = q, p.q_is_euclidean = q_is_euclidean, p.q_pnc = q_pnc, p.q_norm = q_norm;
-    p.keys = keys, p.norm_sq = norm_sq, p.values = values;
-    p.weights = weights, p.m_val = m_val, p.min_dist = min_dist;
-    p.w_split = w_split, p.v_split = v_split;
-    p.rows = rows, p.dk = (int)d_key, p.dv = (int)d_val, p.cap = (int)capacity, p.count = (int)count;
-    p.top_k = (int)(top_k > capacity ? capacity : top_k), p.tau = tau;
-    p.f32_distance = (flags & (PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE)) != 0;
-    return launch_memory_read(ctx, p, (flags & PSSA_B200_MEM_EXACT) != 0);
+    return memory_read_impl(ctx, q, q_is_euclidean, keys, norm_sq, values, rows, d_key, d_val, capacity, count, tau, top_k, q_pnc, q_norm,
+                            weights, m_val, min_dist, nullptr, nullptr, nullptr, flags);
+}
+
+int32_t pssa_b200_memory_read_topk_dev(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys,
+                                       const float* norm_sq, const float* values, size_t rows, size_t d_key, size_t d_val,
+                                       size_t capacity, size_t count, float tau, size_t top_k, float* q_pnc, float* q_norm, float* m_val,
+                                       float* min_dist, uint32_t* slots_out, float* weights_out, uint32_t* handed_over, uint32_t flags) {
+    if (!ctx) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null context");
+    if (top_k == 0 || top_k >= count)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 top-k read: top_k must be in 1..count-1 (use the all-slots read otherwise)");
+    return memory_read_impl(ctx, q, q_is_euclidean, keys, norm_sq, values, rows, d_key, d_val, capacity, count, tau, top_k, q_pnc, q_norm,
+                            nullptr, m_val, min_dist, slots_out, weights_out, handed_over, flags);
 }
 
 int32_t pssa_b200_memory_read(pssa_b200_ctx* ctx, const float* q, int32_t q_is_euclidean, const float* keys,

@@ -99,8 +99,24 @@ struct RetrieveParams {
     float2* q_stat;
     const void* k_split;
     const float2* k_stat;
+    // exact top-k in one kernel (retrieve_fused.cu): compact outputs [rows, top_k] in ascending slot order (either may be
+    // null), the list of rows handed to the exact fix-up pass with its counter (scratch, rows + 1 words), and a test hook
+    // that hands every n-th row over regardless (0 = off)
+    unsigned* topk_slots;
+    float* topk_weights;
+    unsigned* fixup_list;
+    unsigned* fixup_count;
+    int selftest_every;
+    int no_fused;          // keep the multi-kernel path even where the one-kernel top-k read applies
+    int* status;           // context status word (set by the launcher)
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);
+// retrieve_fused.cu: projection, tensor-core pre-filter, exact f64 re-scoring of the candidates, (bits, slot) selection,
+// softmax and value read of a top-k read in one kernel; same results as the f64 path of launch_memory_read
+bool retrieve_fused_eligible(const RetrieveParams& p);
+int32_t launch_retrieve_fused(pssa_b200_ctx* ctx, const RetrieveParams& p);
+// dense weight rows [rows, cap] -> selected slots and weights [rows, k] in ascending slot order
+int32_t launch_compact_topk(pssa_b200_ctx* ctx, const float* weights, int cap, int k, size_t rows, unsigned* slots, float* w_out);
 // values [cap, dv] fp32 -> v_split [dv, 3*cap] bf16 (transpose + three-way split); once per bank upload
 int32_t launch_split_values(pssa_b200_ctx* ctx, const float* values, void* v_split, int cap, int dv);
 // keys [cap, dk] fp32 -> k_split [cap, 3*dk] bf16 pieces and k_stat[slot] = (|k|^2, 1/(1-|k|^2)); once per bank upload

@@ -231,6 +231,7 @@ int32_t pssa_b200_model_set_bank(pssa_b200_model* m, int32_t layer, const float*
     b.write_head = write_head;
     b.vsplit_dirty = true;
     b.vp_dirty = true;
+    b.ksplit_dirty = true;
     if (confidence) b.confidence.assign(confidence, confidence + m->cap);
     if (last_seen_step) b.last_seen.assign(last_seen_step, last_seen_step + m->cap);
     PSSA_CUDA(ctx, cudaStreamSynchronize(st));

@@ -40,7 +40,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
     size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * (d + 64) * 2),
            o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2), o_qsp = c.take(rows * 3 * m->k * 2),
-           o_qst = c.take(rows * sizeof(float2));
+           o_qst = c.take(rows * sizeof(float2)), o_fix = c.take((rows + 1) * 4);
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -62,7 +62,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
     ws.m_proj = (float*)(b + o_mp), ws.z = (float*)(b + o_z), ws.mlp_act = (float*)(b + o_act);
     ws.last_feat = (float*)(b + o_lf), ws.logits = (float*)(b + o_lg);
     ws.x_bf16 = b + o_xb, ws.y_bf16 = b + o_yb, ws.m_bf16 = b + o_mb, ws.z_bf16 = b + o_zb, ws.act_bf16 = b + o_ab, ws.w_split = b + o_wsp;
-    ws.q_split = b + o_qsp, ws.q_stat = (float2*)(b + o_qst);
+    ws.q_split = b + o_qsp, ws.q_stat = (float2*)(b + o_qst), ws.fixup = (uint32_t*)(b + o_fix);
     return PSSA_B200_OK;
 }
 
@@ -107,7 +107,6 @@ int32_t refresh_bf16(pssa_b200_model* m) {
     for (auto& b : m->blocks) {
         if (!b.vsplit_dirty) continue;
         if ((rc = launch_split_values(ctx, b.w[T_BANK_VALUES], b.vsplit_bf16, (int)m->cap, (int)d))) return rc;
-        if ((rc = launch_split_keys(ctx, b.w[T_BANK_KEYS], b.w[T_BANK_NORM_SQ], b.ksplit_bf16, b.kstat, (int)m->cap, (int)m->k))) return rc;
         b.vsplit_dirty = false;
     }
     for (auto& b : m->blocks) {
@@ -120,6 +119,17 @@ int32_t refresh_bf16(pssa_b200_model* m) {
     if (m->unembed_dirty) {
         if ((rc = launch_to_bf16(ctx, m->unembed, m->unembed_bf16, m->v * d))) return rc;
         m->unembed_dirty = false;
+    }
+    return PSSA_B200_OK;
+}
+
+// the bank's keys as bf16 pieces (tensor-core distances of the bf16 mode; the pre-filter of the exact top-k read in both modes)
+int32_t refresh_key_splits(pssa_b200_model* m) {
+    int32_t rc;
+    for (auto& b : m->blocks) {
+        if (!b.ksplit_dirty) continue;
+        if ((rc = launch_split_keys(m->ctx, b.w[T_BANK_KEYS], b.w[T_BANK_NORM_SQ], b.ksplit_bf16, b.kstat, (int)m->cap, (int)m->k))) return rc;
+        b.ksplit_dirty = false;
     }
     return PSSA_B200_OK;
 }
@@ -143,6 +153,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
     const float ssm_scale = 1.0f / std::sqrt((float)s);
     int32_t rc;
     if (!exact && (rc = refresh_bf16(m))) return rc;
+    if ((rc = refresh_key_splits(m))) return rc;
     float* feat_in = nullptr;
     float* feat_out = ws.feat_a;
     bool single_token = true;  // a decode step: the SSM stage is then one pass over the carries
@@ -279,7 +290,10 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         if (!exact && m->cap % 64 == 0) rp.w_split = ws.w_split, rp.v_split = b.vsplit_bf16;
         // only the observer reads the fp32 weight rows after the value read
         rp.skip_weights = rp.w_split && !obs_now && !(rp.top_k != 0 && rp.top_k < rp.count);
-        if (!exact && k % 64 == 0) rp.q_split = ws.q_split, rp.q_stat = ws.q_stat, rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
+        if (k % 64 == 0) rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
+        if (!exact && k % 64 == 0) rp.q_split = ws.q_split, rp.q_stat = ws.q_stat;
+        rp.fixup_list = ws.fixup + 1, rp.fixup_count = ws.fixup;  // exact top-k in one kernel when the shape allows it
+        if (!obs_now) rp.weights = (rp.top_k != 0 && rp.top_k < rp.count && retrieve_fused_eligible(rp)) ? nullptr : ws.weights;
         // All-slots read in the bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s). The bank's values were carried
         // through W_proj at upload (vpsplit_bf16), so the product of the weight rows with them IS the memory projection and
         // takes the gate epilogue directly: the value read stops after the softmax (no m, no separate W_proj launch). The

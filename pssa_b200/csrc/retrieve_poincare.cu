@@ -822,6 +822,10 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     size_t qblocks = (p.rows + QT - 1) / QT;
     if (qblocks > 0x7fffffffull) return fail(ctx, PSSA_B200_ERR_SHAPE, "B200 memory read grid exceeds grid limits; refusing launch");
     int32_t rc;
+    // top-k reads whose shape fits take the one-kernel path (tensor-core pre-filter, exact f64 decision): same results
+    // as the f64 distance kernel below, without the [rows, capacity] matrix in HBM
+    if (!p.no_fused && retrieve_fused_eligible(p)) return launch_retrieve_fused(ctx, p);
+    if (!p.weights) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: this shape needs the [rows, capacity] weight rows as scratch");
     // with an empty bank the launch still publishes the projection (gpu_batch.rs:682-698 projects first)
     static PerDeviceOnce attr_a;
     if (smem_a > 48 * 1024 && attr_a.need(ctx->device)) {
