@@ -193,7 +193,8 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
  * bf16 precision mode uses it). Needs d_key % 64 == 0, otherwise PSSA_B200_MEM_F32_DISTANCE behaviour applies.
  * Ignored together with PSSA_B200_MEM_EXACT. */
 #define PSSA_B200_MEM_TC_DISTANCE 4u
-/* Top-k reads whose shape allows it (capacity 128 / 256 / 512, d_key 64 or 128, top_k <= 12, a mostly full bank) run as
+/* Top-k reads whose shape allows it (capacity 128 / 256 / 512, d_key 64 or 128, top_k <= 12, at least 8 * (top_k + 6)
+ * occupied slots) run as
  * ONE kernel: tensor-core inner products only pre-filter the slots, the candidates are re-scored with the reference's f64
  * arithmetic and selected by (distance bits, slot), and a row whose selection cannot be proven from the candidates is
  * handed to an exact pass over every slot. Results are those of the default f64 path. This flag keeps the separate

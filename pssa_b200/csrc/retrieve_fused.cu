@@ -12,8 +12,8 @@
 //      same way once per upload, streamed by TMA through a 3-stage ring); the 128 x capacity accumulator fills the SM's
 //      TMEM (512 fp32 columns);
 //   3. one thread per query row reads its accumulator row twice with tcgen05.ld: a first sweep finds a threshold that at
-//      least C = k + 4 slots pass (the C-th smallest of 16 group minima of v = |p-k|^2 / (1-|k|^2)), a second sweep lists the
-//      slots under it (about 20 of 512); the C smallest of the list are the row's candidates;
+//      least C = k + 4 slots pass (the C-th smallest of the minima of v = |p-k|^2 / (1-|k|^2) over groups of 32, 16 or 8
+//      slots), a second sweep lists the slots under it (about 20 of 512); the C smallest of the list are the candidates;
 //   4. one warp per row re-scores the candidates exactly as `poincare_distance` does (f64 differences and sum, f64
 //      log1p form of 2 asinh sqrt, rounded to f32), selects k by (bits, slot) and proves the selection: every slot
 //      outside the candidate set has an approximate v >= the largest candidate's, so its true distance is at least
@@ -187,7 +187,10 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
     const int nh = cap >= 256 ? 256 : cap;   // slots per MMA (N) and per TMA box
     const int halves = cap / nh;
     const int n_cand = min(k + kMargin, kCandMax);
-    const int group = cap / 16;              // columns per group minimum: 16 groups cover the bank
+    // columns per group minimum: 32 when that leaves enough fully occupied groups to bound n_cand slots (plus two to
+    // keep the bound tight), else 16 or 8; smaller groups give a lower threshold and shorter lists but more insertions
+    int group = 32;
+    while (group > 8 && count / group < n_cand + 2) group >>= 1;
     const long long n_tiles = (long long)((p.rows + BM - 1) / BM);
     const uint32_t tmem_cols = (uint32_t)cap;  // 128, 256 or 512: a power of two >= 32
 
@@ -611,7 +614,7 @@ bool retrieve_fused_eligible(const RetrieveParams& p) {
     const bool topk = p.top_k != 0 && p.top_k < p.count;
     const int n_cand = p.top_k + kMargin < kCandMax ? p.top_k + kMargin : kCandMax;
     return topk && p.top_k <= kCandMax - kMargin && (p.cap == 128 || p.cap == 256 || p.cap == 512) && (p.dk == 64 || p.dk == 128) &&
-           p.count > (n_cand - 1) * (p.cap / 16) && p.k_split && p.k_stat && p.fixup_list && p.fixup_count && p.rows > 0 &&
+           p.count / 8 >= n_cand + 2 && p.k_split && p.k_stat && p.fixup_list && p.fixup_count && p.rows > 0 &&
            p.rows <= 0xffffffffull && p.dv > 0;
 }
 
