@@ -494,21 +494,43 @@ def run_extras(gpu, torch, peak_hbm):
     w = torch.zeros(rows, cap, device="cuda")
     m = torch.zeros(rows, dv, device="cuda")
     ref_sel = None
-    for name, top_k, f32d, tcd in (("top8", 8, False, False), ("all_slots", 0, False, False), ("top8_f32_distance", 8, True, False),
+    # the headline form of configs[2]: exact top-8 in ONE kernel with compact results (8 slots + 8 weights per query)
+    slots8 = torch.zeros(rows, 8, dtype=torch.int32, device="cuda")
+    w8 = torch.zeros(rows, 8, device="cuda")
+    handed = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def fused_top8(values=vals):
+        gpu.memory_read_topk_dev(q, keys, norm_sq, values, rows, dk, dv, cap, cap, 0.1, 8, m, slots8, w8, handed_over=handed,
+                                 q_is_euclidean=False)
+
+    for name, top_k, f32d, tcd in (("top8_separate_f64_kernels", 8, False, False), ("all_slots", 0, False, False), ("top8_f32_distance", 8, True, False),
                                    ("all_slots_f32_distance", 0, True, False), ("top8_tc_distance", 8, False, True),
-                                   ("all_slots_tc_distance", 0, False, True)):
-        ms = timed(lambda: gpu.memory_read_dev(q, keys, norm_sq, vals, rows, dk, dv, cap, cap, 0.1, m, top_k=top_k, weights=w,
-                                               q_is_euclidean=False, f32_distance=f32d, tc_distance=tcd), 5, warm=2)
+                                   ("all_slots_tc_distance", 0, False, True), ("top8", 8, False, False)):
+        one_kernel = name == "top8"
+        if one_kernel:
+            ms = timed(fused_top8, 10, warm=3)
+        else:
+            ms = timed(lambda: gpu.memory_read_dev(q, keys, norm_sq, vals, rows, dk, dv, cap, cap, 0.1, m, top_k=top_k, weights=w,
+                                                   q_is_euclidean=False, f32_distance=f32d, tc_distance=tcd, no_fused=True), 5, warm=2)
         byts = rows * (dk * 4 + dv * 4 + (64 if top_k else cap * 4))
         row = {"workload": "Poincare retrieval, 512 slots, key/value dim 128, 262144 queries, tau 0.1"
-                           + (", distances from tensor-core inner products (three bf16 pieces per operand)" if tcd else
+                           + (", exact top-8 in one kernel: tensor-core pre-filter in TMEM, f64 re-scoring of the candidates, "
+                              "(distance bits, slot) selection, softmax and value read; compact results" if one_kernel else
+                              ", distances from tensor-core inner products (three bf16 pieces per operand)" if tcd else
                               ", distances accumulated in fp32 (differences first)" if f32d else ", distances in f64 like the reference"),
                "ms": ms, "queries_per_s": rows / (ms / 1e3),
                "roofline": {"bound": "hbm", "achieved": byts / (ms / 1e3) / 1e9, "peak": peak_hbm, "unit": "GB/s",
                             "frac": byts / (ms / 1e3) / 1e9 / peak_hbm,
-                            "limiter": "distance epilogue + softmax (the inner products run on the tensor cores)" if tcd else
+                            "limiter": "tensor-core pre-filter + per-row sweeps of the accumulator + L2 reads of the candidates' keys and values" if one_kernel else
+                                       "distance epilogue + softmax (the inner products run on the tensor cores)" if tcd else
                                        "FP32 FMA pipe (2 ops per key dimension per slot)" if f32d else "fp64 distance arithmetic"}}
-        if top_k:
+        if one_kernel:
+            sel = torch.zeros(rows, cap, dtype=torch.bool, device="cuda")
+            sel.scatter_(1, slots8.long(), True)
+            row["queries_with_the_f64_slot_set"] = float((sel == ref_sel).all(dim=1).float().mean().item())
+            row["rows_handed_to_the_exact_pass"] = int(handed.item())
+            del sel
+        elif top_k:
             sel = w != 0  # the selected slot sets of every query
             if not f32d and not tcd:
                 ref_sel = sel.clone()
@@ -531,12 +553,13 @@ def run_extras(gpu, torch, peak_hbm):
     key_rows = q[last].contiguous()
 
     def write_only():
-        win = w[last].argmax(dim=1).to(torch.int32)  # the winning slot = largest weight of the read just done
+        # the winning slot = the selected slot with the largest weight (the nearest) of the read just done
+        win = slots8[last].gather(1, w8[last].argmax(dim=1, keepdim=True)).squeeze(1).to(torch.int32)
         gpu.bank_insert_protected_dev(keys, norm_sq, vals_rw, conf, seen, meta, cap, dk, dv, key_rows, target, surprise, steps_t,
                                       n_seq, slots_out, win, 0.1)
 
     def read_write():
-        gpu.memory_read_dev(q, keys, norm_sq, vals_rw, rows, dk, dv, cap, cap, 0.1, m, top_k=8, weights=w, q_is_euclidean=False)
+        fused_top8(vals_rw)
         write_only()
 
     read_write()
@@ -546,7 +569,7 @@ def run_extras(gpu, torch, peak_hbm):
     ms_w = timed(write_only, 20, warm=2)
     byts = rows * (dk * 4 + dv * 4 + 64) + n_seq * (dk + dv + 3) * 4
     extra["retrieval_c3_top8_read_plus_write"] = {
-        "workload": "Poincare retrieval as BASELINE configs[2] words it: top-8 read of 262144 queries (f64 distances) plus 64 "
+        "workload": "Poincare retrieval as BASELINE configs[2] words it: exact top-8 read of 262144 queries (one kernel) plus 64 "
                     "refractory-gated rank-1 writes to the winning slots (one per sequence, ordered, one launch)",
         "ms": ms_rw, "write_only_ms": ms_w, "writes": n_seq, "writes_accepted_first_round": accepted, "queries_per_s": rows / (ms_rw / 1e3),
         "roofline": {"bound": "hbm", "achieved": byts / (ms_rw / 1e3) / 1e9, "peak": peak_hbm, "unit": "GB/s",

@@ -202,6 +202,11 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
 #define PSSA_B200_MEM_NO_FUSED 8u
 /* Test hook: the one-kernel top-k read hands every third row to its exact pass regardless of the proof. */
 #define PSSA_B200_MEM_HANDOVER_SELFTEST 16u
+/* Diagnostic of pssa_b200_memory_read_topk_dev: `handed_over` then points at 14 u32 words (8-byte aligned): the count,
+ * one pad word, then six 64-bit counters of SM clock cycles summed over the CTAs of the one-kernel read: loading the
+ * queries, projecting, splitting into bf16 pieces, waiting for the tensor cores, the two sweeps with the candidate
+ * selection, and the per-row exact stage. */
+#define PSSA_B200_MEM_PHASE_CLOCKS 32u
 
 /*
  * Poincare-ball memory read for `rows` queries against one immutable bank. Replaces
@@ -406,7 +411,10 @@ int32_t pssa_b200_model_set_precision(pssa_b200_model* model, int32_t precision)
  * (src/pssa.rs:2080-2105, 2189-2192, 2232-2243); enabling one returns PSSA_B200_ERR_UNSUPPORTED with the reference's
  * message. 4 = `set_loops` (src/pssa.rs:2171-2184): the runtime number of weight-shared Ouro passes per block, 1..32
  * (src/pssa.rs:2338-2376). Every pass owns a recurrent carry; changing the count keeps pass 0's carries and zeroes the
- * others (`resize_loop_tape`, src/pssa.rs:2147-2167), and the per-stream state becomes [block][pass][d*s]. */
+ * others (`resize_loop_tape`, src/pssa.rs:2147-2167), and the per-stream state becomes [block][pass][d*s].
+ * 5 (no counterpart in the reference) = lane groups: a pass over several lanes can be enqueued as up to four groups of
+ * consecutive lanes on side streams of the context, joined by events before the call returns (the groups share only
+ * read-only weights, so results do not change): 0 = chosen from the shape, 1 = off, 2..4 = that many groups. */
 int32_t pssa_b200_model_set_option(pssa_b200_model* model, int32_t option, int32_t value);
 
 /* `reset_recurrent_state` (src/pssa.rs:2245-2250) for one stream. */

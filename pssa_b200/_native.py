@@ -84,6 +84,7 @@ MEM_F32_DISTANCE = 2
 MEM_TC_DISTANCE = 4
 MEM_NO_FUSED = 8
 MEM_HANDOVER_SELFTEST = 16
+MEM_PHASE_CLOCKS = 32
 EPI_NONE, EPI_SOFTPLUS, EPI_SIGMOID, EPI_SILU, EPI_SCALE, EPI_ADD_OUT = range(6)
 PRECISION_BF16, PRECISION_FP32_EXACT = 0, 1
 CANCEL_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p)

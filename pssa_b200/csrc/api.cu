@@ -45,6 +45,7 @@ void profile_record(pssa_b200_ctx* ctx, const char* kernel) {
     cudaEventRecord(e, ctx->stream);
     ctx->prof_events.push_back(e);
     ctx->prof_names.push_back(kernel);
+    ctx->prof_chain.push_back(ctx->chain);
 }
 
 // RAII device buffers for the host-pointer entry points (freed on every exit path)
@@ -105,6 +106,11 @@ void pssa_b200_ctx_destroy(pssa_b200_ctx* ctx) {
     if (ctx->arena) cudaFree(ctx->arena);
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     cudaFree(ctx->resident.y), cudaFree(ctx->resident.states), cudaFree(ctx->resident.bar_a), cudaFree(ctx->resident.bar_b);
+    for (int i = 0; i < 3; ++i) {
+        if (ctx->side[i]) cudaStreamDestroy(ctx->side[i]);
+        if (ctx->join_ev[i]) cudaEventDestroy(ctx->join_ev[i]);
+    }
+    if (ctx->fork_ev) cudaEventDestroy(ctx->fork_ev);
     for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
     for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -359,7 +365,7 @@ static int32_t memory_read_impl(pssa_b200_ctx* ctx, const float* q, int32_t q_is
     if (!q || !keys || !norm_sq || !values || !m_val)
         return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: null buffer");
     const uint32_t known = PSSA_B200_MEM_EXACT | PSSA_B200_MEM_F32_DISTANCE | PSSA_B200_MEM_TC_DISTANCE | PSSA_B200_MEM_NO_FUSED |
-                           PSSA_B200_MEM_HANDOVER_SELFTEST;
+                           PSSA_B200_MEM_HANDOVER_SELFTEST | PSSA_B200_MEM_PHASE_CLOCKS;
     if (flags & ~known) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: unknown flags");
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     // scratch from the arena: the weight rows when the caller does not want them, the bf16 pieces of the weights and of the
@@ -416,6 +422,10 @@ static int32_t memory_read_impl(pssa_b200_ctx* ctx, const float* q, int32_t q_is
     }
     p.weights = weights;
     if (fused) p.topk_slots = slots_out, p.topk_weights = topk_w_out;
+    if (fused && handed_over && (flags & PSSA_B200_MEM_PHASE_CLOCKS)) {
+        p.phase_cycles = reinterpret_cast<unsigned long long*>(handed_over + 2);
+        PSSA_CUDA(ctx, cudaMemsetAsync(handed_over + 2, 0, 6 * sizeof(unsigned long long), ctx->stream));
+    }
     if ((rc = launch_memory_read(ctx, p, exact)) != PSSA_B200_OK) return rc;
     if (!fused && topk && (slots_out || topk_w_out) &&
         (rc = launch_compact_topk(ctx, weights, (int)capacity, p.top_k, rows, slots_out, topk_w_out)) != PSSA_B200_OK)
@@ -607,10 +617,13 @@ int32_t pssa_b200_ctx_profile_begin(pssa_b200_ctx* ctx) {
     for (cudaEvent_t e : ctx->prof_events) ctx->prof_pool.push_back(e);
     ctx->prof_events.clear();
     ctx->prof_names.clear();
+    ctx->prof_chain.clear();
     cudaEvent_t e = prof_event(ctx);
     if (!e) return fail(ctx, PSSA_B200_ERR_CUDA, "profile: cannot create an event");
     PSSA_CUDA(ctx, cudaEventRecord(e, ctx->stream));
     ctx->prof_events.push_back(e);
+    ctx->prof_names.push_back(nullptr);
+    ctx->prof_chain.push_back(0);
     ctx->profiling = true;
     return PSSA_B200_OK;
 }
@@ -620,11 +633,20 @@ int32_t pssa_b200_ctx_profile_end(pssa_b200_ctx* ctx, uint32_t* n_rows) {
     ctx->profiling = false;
     PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < 3; ++i)
+        if (ctx->side[i]) PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->side[i]));
     ctx->prof_rows.clear();
-    for (size_t i = 0; i + 1 < ctx->prof_events.size(); ++i) {
-        float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, ctx->prof_events[i], ctx->prof_events[i + 1]) != cudaSuccess) continue;
+    // time of a kernel = from the previous event on ITS chain (stream) to its own; with several lane groups the chains
+    // overlap on the device, so the rows add up to more than the wall time
+    cudaEvent_t last[4] = {nullptr, nullptr, nullptr, nullptr};
+    for (size_t i = 0; i < ctx->prof_events.size(); ++i) {
+        const int chain = ctx->prof_chain[i] & 3;
+        cudaEvent_t prev = last[chain];
+        last[chain] = ctx->prof_events[i];
         const char* name = ctx->prof_names[i];
+        if (!name || !prev) continue;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, prev, ctx->prof_events[i]) != cudaSuccess) continue;
         bool found = false;
         for (auto& r : ctx->prof_rows)
             if (r.name == name) {
@@ -636,6 +658,7 @@ int32_t pssa_b200_ctx_profile_end(pssa_b200_ctx* ctx, uint32_t* n_rows) {
     for (cudaEvent_t e : ctx->prof_events) ctx->prof_pool.push_back(e);
     ctx->prof_events.clear();
     ctx->prof_names.clear();
+    ctx->prof_chain.clear();
     if (n_rows) *n_rows = (uint32_t)ctx->prof_rows.size();
     return PSSA_B200_OK;
 }

@@ -27,6 +27,10 @@ struct pssa_b200_ctx {
     // device status word for bounded waits (0 = ok)
     int* status_dev = nullptr;
     int scan_chunks = 0;  // 0 = choose automatically; tests force the multi-chunk passes with it
+    // lane groups of the model path: up to three side streams beside `stream`, joined by events (model_forward.cu)
+    cudaStream_t side[3] = {nullptr, nullptr, nullptr};
+    cudaEvent_t fork_ev = nullptr, join_ev[3] = {nullptr, nullptr, nullptr};
+    int chain = 0;  // which of those streams `stream` currently is (0 = the caller's); keys the stage profile
     // Resident SSM result (`ssm_forward_resident` -> `memory_forward_after_ssm`, src/backend.rs:1186-1289): the tape of the
     // last resident SSM call stays on the device until the memory stage consumes it.
     struct ResidentSsm {
@@ -38,8 +42,9 @@ struct pssa_b200_ctx {
     // events instead of wall clock): while enabled, an event is recorded after every kernel launch; the time
     // between consecutive events on the (serial) stream is attributed to the kernel launched in between.
     bool profiling = false;
-    std::vector<cudaEvent_t> prof_events;      // prof_events[0] is the start mark
-    std::vector<const char*> prof_names;       // prof_names[i] ran between events i and i+1
+    std::vector<cudaEvent_t> prof_events;      // one per launch, plus one start mark per chain
+    std::vector<const char*> prof_names;       // kernel that finished at event i (nullptr: a chain starts here)
+    std::vector<int> prof_chain;               // stream (chain) event i was recorded on: times are differences along a chain
     std::vector<cudaEvent_t> prof_pool;        // recycled events
     struct ProfRow {
         std::string name;

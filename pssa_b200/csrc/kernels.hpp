@@ -108,6 +108,7 @@ struct RetrieveParams {
     unsigned* fixup_count;
     int selftest_every;
     int no_fused;          // keep the multi-kernel path even where the one-kernel top-k read applies
+    unsigned long long* phase_cycles;  // optional [6] device counters: clock cycles one worker thread per CTA spent per phase
     int* status;           // context status word (set by the launcher)
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);

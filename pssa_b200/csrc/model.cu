@@ -290,6 +290,10 @@ int32_t pssa_b200_model_set_option(pssa_b200_model* m, int32_t option, int32_t v
             m->dev_layout.ws_base = nullptr;
             return PSSA_B200_OK;
         }
+        case 5:  // lane groups (not a reference option): 0 = by shape, 1 = one stream, 2..4 = that many groups
+            if (value < 0 || value > 4) return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "lane groups must be in 0..4");
+            m->lane_groups = (size_t)value;
+            return PSSA_B200_OK;
         default: return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "unknown option");
     }
 }

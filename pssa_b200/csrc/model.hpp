@@ -77,6 +77,7 @@ struct pssa_b200_model {
     uint32_t precision = 0;  // PSSA_B200_PRECISION_*
     size_t top_k = 0;
     size_t loops = 1;  // Ouro passes per block (src/pssa.rs:2171-2184): shared weights, one carry per pass
+    size_t lane_groups = 0;  // lane groups on side streams per pass: 0 = choose by shape, 1 = off, 2..4 forced
     size_t max_rows = 65536;
     float* embed = nullptr;
     float* unembed = nullptr;

@@ -40,7 +40,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
     size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * (d + 64) * 2),
            o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2), o_qsp = c.take(rows * 3 * m->k * 2),
-           o_qst = c.take(rows * sizeof(float2)), o_fix = c.take((rows + 1) * 4);
+           o_qst = c.take(rows * sizeof(float2)), o_fix = c.take((rows + 8) * 4);  // 8 counters (one per lane group), then the lists
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -124,6 +124,16 @@ int32_t refresh_bf16(pssa_b200_model* m) {
 }
 
 // the bank's keys as bf16 pieces (tensor-core distances of the bf16 mode; the pre-filter of the exact top-k read in both modes)
+// side streams and fork / join events of the lane groups, created on first use
+int32_t ensure_side_streams(pssa_b200_ctx* ctx, size_t n) {
+    for (size_t i = 0; i < n && i < 3; ++i) {
+        if (!ctx->side[i]) PSSA_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->side[i], cudaStreamNonBlocking));
+        if (!ctx->join_ev[i]) PSSA_CUDA(ctx, cudaEventCreateWithFlags(&ctx->join_ev[i], cudaEventDisableTiming));
+    }
+    if (!ctx->fork_ev) PSSA_CUDA(ctx, cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming));
+    return PSSA_B200_OK;
+}
+
 int32_t refresh_key_splits(pssa_b200_model* m) {
     int32_t rc;
     for (auto& b : m->blocks) {
@@ -213,15 +223,93 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         }
         ob.valid_lanes = n_obs;
     }
-    // One application of block `l` on carry `li` (Ouro pass; 0 for the ordinary model): reads `feat_in` (nullptr: the
-    // embedding rows of the ids), writes feat_out = res_in ? res_in + rscale * z : z, z being the block's output.
+    // Lane groups. The lanes of a pass can be cut into up to four groups of consecutive lanes, each enqueued on its own
+    // stream: the groups share nothing but the read-only weights and banks (every activation buffer is per row, every
+    // carry per lane), so the device is free to run one group's tensor-core products beside another group's SSM (the two
+    // are bound by different pipes), to fill the tail of one kernel's last wave with the next group's CTAs, and, for a
+    // decode step (a chain of small, latency-bound launches), to run the chains side by side. Fork and join are events
+    // between the context's stream and the side streams, so a caller capturing the call in a CUDA graph gets the same
+    // parallel branches. Off for the two-pass SSM and the observer, whose scratch is not per row.
+    size_t n_groups = 1;
+    {
+        bool contiguous = true;  // groups are row ranges: lane l must start where lane l-1 ends
+        size_t expect = 0;
+        for (size_t l = 0; l < lanes; ++l) contiguous = contiguous && h_off[l] == expect, expect += h_len[l];
+        // Measured at the benchmark's shapes (32 x 2048-token lanes; 256 decode streams) two groups are SLOWER than one
+        // stream (24.1 against 23.1 ms per prefill step, 1.70 against 1.37 ms per decode step): every tensor-core CTA
+        // takes a whole SM's registers and shared memory, so kernels of different groups queue behind each other instead
+        // of sharing SMs, and each is smaller. The automatic choice is therefore one group; the option stays for shapes
+        // and kernel variants where co-residency is possible.
+        size_t want = m->lane_groups == 0 ? 1 : m->lane_groups;
+        if (!two_pass && !observe && contiguous)
+            n_groups = std::max<size_t>(1, std::min<size_t>(std::min<size_t>(want, 4), lanes));
+    }
+    struct Group { size_t r0, nr, l0, nl; };
+    Group groups[4];
+    {
+        size_t lane = 0, row = 0;
+        for (size_t g = 0; g < n_groups; ++g) {
+            Group& gr = groups[g];
+            gr.l0 = lane, gr.r0 = row;
+            if (g + 1 == n_groups) {
+                lane = lanes, row = rows;
+            } else {  // at least one lane, at least one left for every later group, rows as even as whole lanes allow
+                const size_t target = rows * (g + 1) / n_groups;
+                do row += h_len[lane], ++lane;
+                while (lane < lanes - (n_groups - 1 - g) && row + h_len[lane] / 2 <= target);
+            }
+            gr.nl = lane - gr.l0, gr.nr = row - gr.r0;
+        }
+    }
+    if (n_groups > 1 && (rc = ensure_side_streams(ctx, n_groups - 1))) return rc;
+    cudaStream_t const main_stream = ctx->stream;
+    // the slice the stages below work on (set per group by the driver loop)
+    size_t r0 = 0, nr = rows, l0 = 0, nl = lanes, gi = 0;
+    Workspace v = ws;
+    auto select = [&](size_t g) {
+        const Group& gr = groups[g];
+        gi = g, r0 = gr.r0, nr = gr.nr, l0 = gr.l0, nl = gr.nl;
+        v = ws;
+        const size_t dd = m->d;
+        v.ids += r0, v.x_norm += r0 * dd, v.proj += r0 * nc, v.y += r0 * dd, v.weights += r0 * m->cap, v.m_val += r0 * dd, v.m_proj += r0 * dd;
+        v.z += r0 * dd, v.mlp_act += r0 * 2 * dd, v.q_stat += r0;
+        v.x_bf16 = (char*)ws.x_bf16 + r0 * dd * 2, v.y_bf16 = (char*)ws.y_bf16 + r0 * dd * 2, v.m_bf16 = (char*)ws.m_bf16 + r0 * dd * 2;
+        v.z_bf16 = (char*)ws.z_bf16 + r0 * (dd + 64) * 2, v.act_bf16 = (char*)ws.act_bf16 + r0 * (2 * dd + 64) * 2;
+        v.w_split = (char*)ws.w_split + r0 * 3 * m->cap * 2, v.q_split = (char*)ws.q_split + r0 * 3 * m->k * 2;
+        ctx->stream = g == 0 ? main_stream : ctx->side[g - 1];
+        ctx->chain = (int)g;
+    };
+    auto fork = [&]() -> int32_t {
+        if (n_groups <= 1) return PSSA_B200_OK;
+        PSSA_CUDA(ctx, cudaEventRecord(ctx->fork_ev, main_stream));
+        for (size_t g = 1; g < n_groups; ++g) {
+            PSSA_CUDA(ctx, cudaStreamWaitEvent(ctx->side[g - 1], ctx->fork_ev, 0));
+            if (ctx->profiling) ctx->stream = ctx->side[g - 1], ctx->chain = (int)g, profile_record(ctx, nullptr);  // a chain starts here
+        }
+        ctx->stream = main_stream, ctx->chain = 0;
+        return PSSA_B200_OK;
+    };
+    auto join = [&]() -> int32_t {
+        ctx->stream = main_stream, ctx->chain = 0;
+        for (size_t g = 1; g < n_groups; ++g) {
+            PSSA_CUDA(ctx, cudaEventRecord(ctx->join_ev[g - 1], ctx->side[g - 1]));
+            PSSA_CUDA(ctx, cudaStreamWaitEvent(main_stream, ctx->join_ev[g - 1], 0));
+        }
+        return PSSA_B200_OK;
+    };
+    // One application of block `l` on carry `li` (Ouro pass; 0 for the ordinary model) for the selected group: reads
+    // `feat_in` (nullptr: the embedding rows of the ids), writes feat_out = res_in ? res_in + rscale * z : z, z being the
+    // block's output. Feature pointers are absolute; the group's row offset is applied here.
     auto run_pass = [&](size_t l, size_t li, const float* feat_in, const float* res_in, float rscale, float* feat_out, bool publish) -> int32_t {
         DeviceBlock& b = m->blocks[l];
         float* const carry_base = m->state + (l * m->loops + li) * ds;
         const size_t carry_stride = m->depth * m->loops * ds;
+        if (feat_in) feat_in += r0 * (size_t)d;
+        if (res_in) res_in += r0 * (size_t)d;
+        feat_out += r0 * (size_t)d;
         // stage 1: gather + RMSNorm (src/gpu_batch.rs:445-472)
-        if ((rc = launch_embed_norm(ctx, m->embed, feat_in ? nullptr : ws.ids, feat_in, b.w[T_NORM_GAMMA], b.w[T_NORM_BETA],
-                                    ws.x_norm, exact ? nullptr : ws.x_bf16, rows, d, exact, m->v)))
+        if ((rc = launch_embed_norm(ctx, m->embed, feat_in ? nullptr : v.ids, feat_in, b.w[T_NORM_GAMMA], b.w[T_NORM_BETA],
+                                    v.x_norm, exact ? nullptr : v.x_bf16, nr, d, exact, m->v)))
             return rc;
         // stage 2: x-side projections (src/gpu_batch.rs:477-536 plus the query/gate/adapter rows that read x_norm)
         if (exact) {
@@ -230,11 +318,11 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
                       {T_W_C, m->off_c, m->s, EPI_NONE},            {T_W_QX, m->off_q, m->k, EPI_NONE},
                       {T_W_GATE, m->off_gate, m->d, EPI_SIGMOID},   {T_AD_DOWN, m->off_act, m->rank, EPI_SILU}};
             for (auto& p : ps)
-                if ((rc = launch_gemm_exact(ctx, ws.x_norm, b.w[p.id], ws.proj + p.off, rows, p.n, m->d, nc, p.epi, 1.0f))) return rc;
+                if ((rc = launch_gemm_exact(ctx, v.x_norm, b.w[p.id], v.proj + p.off, nr, p.n, m->d, nc, p.epi, 1.0f))) return rc;
         } else {
             // the adapter activations (last column range) also go, as bf16, into the extra K block of both MLP operands
-            if ((rc = launch_gemm_bf16_cat(ctx, ws.x_bf16, b.wcat_bf16, ws.proj, rows, nc, m->d, nc, (int)m->off_b, (int)m->off_gate,
-                                           (int)m->off_act, (char*)ws.z_bf16 + m->d * 2, m->d + 64, (char*)ws.act_bf16 + 2 * m->d * 2,
+            if ((rc = launch_gemm_bf16_cat(ctx, v.x_bf16, b.wcat_bf16, v.proj, nr, nc, m->d, nc, (int)m->off_b, (int)m->off_gate,
+                                           (int)m->off_act, (char*)v.z_bf16 + m->d * 2, m->d + 64, (char*)v.act_bf16 + 2 * m->d * 2,
                                            2 * m->d + 64)))
                 return rc;
         }
@@ -242,8 +330,8 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         SsmParams sp{};
         sp.delta = ws.proj + m->off_delta, sp.x_norm = ws.x_norm, sp.b_proj = ws.proj + m->off_b, sp.c_proj = ws.proj + m->off_c;
         sp.rates = b.rates, sp.carry = carry_base, sp.y = ws.y, sp.y_bf16 = exact ? nullptr : ws.y_bf16;
-        sp.offsets = ws.lane_off, sp.lengths = ws.lane_len, sp.rows = rows, sp.d = d, sp.s = s, sp.lanes = (int)lanes;
-        sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot, sp.carry_stride = carry_stride;
+        sp.offsets = ws.lane_off + l0, sp.lengths = ws.lane_len + l0, sp.rows = rows, sp.d = d, sp.s = s, sp.lanes = (int)nl;  // lanes of this group; rows stay absolute
+        sp.ld_delta = nc, sp.ld_bc = nc, sp.lane_slots = ws.lane_slot + l0, sp.carry_stride = carry_stride;
         sp.aligned = ssm_vector_ok(sp);
         sp.single_token = single_token;
         if (two_pass) {
@@ -275,25 +363,25 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         }
         if ((rc = launch_ssm_fused(ctx, sp, exact))) return rc;
         // stage 4: query, projection into the ball, bank read, gate (src/gpu_batch.rs:748-929)
-        if ((rc = dense(m, ws.y, ws.y_bf16, b.w[T_W_QH], b.wqh_bf16, ws.proj + m->off_q, rows, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
+        if ((rc = dense(m, v.y, v.y_bf16, b.w[T_W_QH], b.wqh_bf16, v.proj + m->off_q, nr, m->k, m->d, nc, EPI_ADD_OUT, 1.0f))) return rc;
         RetrieveParams rp{};
         const bool obs_now = observe && publish;
-        rp.q = ws.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = obs_now ? m->obs.q_pnc : nullptr, rp.q_norm = nullptr;
+        rp.q = v.proj + m->off_q, rp.ldq = nc, rp.q_is_euclidean = 1, rp.q_pnc = obs_now ? m->obs.q_pnc : nullptr, rp.q_norm = nullptr;
         rp.keys = b.w[T_BANK_KEYS], rp.norm_sq = b.w[T_BANK_NORM_SQ], rp.values = b.w[T_BANK_VALUES];
-        rp.weights = ws.weights, rp.m_val = (exact || obs_now) ? ws.m_val : nullptr, rp.m_bf16 = exact ? nullptr : ws.m_bf16, rp.min_dist = nullptr;
+        rp.weights = v.weights, rp.m_val = (exact || obs_now) ? v.m_val : nullptr, rp.m_bf16 = exact ? nullptr : v.m_bf16, rp.min_dist = nullptr;
         // the bf16 mode keeps only the bf16 copy of m (the W_proj operand), so its value read is one plain bf16 product of the
         // leading pieces (the three-term read cost 70 us more per block for a logit error of 9.1e-3 instead of 9.3e-3)
         rp.value_terms = exact ? 6 : 1;
-        rp.rows = rows, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
+        rp.rows = nr, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
         rp.f32_distance = !exact;  // the bf16 mode's queries carry bf16 rounding already; f64 distances buy nothing there
-        if (!exact && m->cap % 64 == 0) rp.w_split = ws.w_split, rp.v_split = b.vsplit_bf16;
+        if (!exact && m->cap % 64 == 0) rp.w_split = v.w_split, rp.v_split = b.vsplit_bf16;
         // only the observer reads the fp32 weight rows after the value read
         rp.skip_weights = rp.w_split && !obs_now && !(rp.top_k != 0 && rp.top_k < rp.count);
         if (k % 64 == 0) rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
-        if (!exact && k % 64 == 0) rp.q_split = ws.q_split, rp.q_stat = ws.q_stat;
-        rp.fixup_list = ws.fixup + 1, rp.fixup_count = ws.fixup;  // exact top-k in one kernel when the shape allows it
-        if (!obs_now) rp.weights = (rp.top_k != 0 && rp.top_k < rp.count && retrieve_fused_eligible(rp)) ? nullptr : ws.weights;
+        if (!exact && k % 64 == 0) rp.q_split = v.q_split, rp.q_stat = v.q_stat;
+        rp.fixup_list = ws.fixup + 8 + r0, rp.fixup_count = ws.fixup + gi;  // exact top-k in one kernel when the shape allows it
+        if (!obs_now) rp.weights = (rp.top_k != 0 && rp.top_k < rp.count && retrieve_fused_eligible(rp)) ? nullptr : v.weights;
         // All-slots read in the bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s). The bank's values were carried
         // through W_proj at upload (vpsplit_bf16), so the product of the weight rows with them IS the memory projection and
         // takes the gate epilogue directly: the value read stops after the softmax (no m, no separate W_proj launch). The
@@ -303,14 +391,14 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
         if (exact) {
-            if ((rc = launch_gemm_exact(ctx, ws.m_val, b.w[T_W_PROJ], ws.m_proj, rows, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
-            if ((rc = launch_combine_zraw(ctx, ws.y, ws.proj + m->off_gate, nc, ws.m_proj, ws.proj + m->off_act, nc, b.u_eff, ws.z, nullptr,
-                                          rows, d, (int)m->rank, ssm_scale)))
+            if ((rc = launch_gemm_exact(ctx, v.m_val, b.w[T_W_PROJ], v.m_proj, nr, m->d, m->d, m->d, EPI_NONE, 1.0f))) return rc;
+            if ((rc = launch_combine_zraw(ctx, v.y, v.proj + m->off_gate, nc, v.m_proj, v.proj + m->off_act, nc, b.u_eff, v.z, nullptr,
+                                          nr, d, (int)m->rank, ssm_scale)))
                 return rc;
-            if ((rc = launch_gemm_exact(ctx, ws.z, b.w[T_MLP_W1], ws.mlp_act, rows, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f))) return rc;
+            if ((rc = launch_gemm_exact(ctx, v.z, b.w[T_MLP_W1], v.mlp_act, nr, 2 * m->d, m->d, 2 * m->d, EPI_SILU, 1.0f))) return rc;
             // MLP down projection + residual, then depth stacking (src/pssa.rs:2332-2337): block 0 has no outer residual
-            if ((rc = launch_gemm_exact(ctx, ws.mlp_act, b.w[T_MLP_W2], ws.z, rows, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
-            if ((rc = launch_residual(ctx, res_in, ws.z, feat_out, rows * (size_t)d, rscale))) return rc;
+            if ((rc = launch_gemm_exact(ctx, v.mlp_act, b.w[T_MLP_W2], v.z, nr, m->d, 2 * m->d, m->d, EPI_ADD_OUT, 1.0f))) return rc;
+            if ((rc = launch_residual(ctx, res_in, v.z, feat_out, nr * (size_t)d, rscale))) return rc;
         } else {
             // Tensor-core schedule: z = y/sqrt(s) + g*(W_proj m) + U*act never exists as one array. The memory projection's
             // epilogue forms zp = g*acc + y/sqrt(s), kept as bf16 only: it is W1's operand and W2's additive input (an fp32
@@ -319,29 +407,41 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             // W2*h + U*act = [W2 | U] [h; act]. The combine kernel and the m_proj round trip disappear.
             const size_t ldz = m->d + 64, lda = 2 * m->d + 64;
             if (proj_in_read) {
-                if ((rc = launch_gemm_bf16_gate(ctx, ws.w_split, b.vpsplit_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale,
-                                                rows, m->d, m->cap, /*split_k=*/true)))
+                if ((rc = launch_gemm_bf16_gate(ctx, v.w_split, b.vpsplit_bf16, nullptr, v.z_bf16, ldz, v.proj + m->off_gate, nc, v.y, ssm_scale,
+                                                nr, m->d, m->cap, /*split_k=*/true)))
                     return rc;
-            } else if ((rc = launch_gemm_bf16_gate(ctx, ws.m_bf16, b.wproj_bf16, nullptr, ws.z_bf16, ldz, ws.proj + m->off_gate, nc, ws.y, ssm_scale,
-                                                   rows, m->d, m->d)))
+            } else if ((rc = launch_gemm_bf16_gate(ctx, v.m_bf16, b.wproj_bf16, nullptr, v.z_bf16, ldz, v.proj + m->off_gate, nc, v.y, ssm_scale,
+                                                   nr, m->d, m->d)))
                 return rc;
-            if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, b.w1cat_bf16, nullptr, ws.act_bf16, rows, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
+            if ((rc = launch_gemm_bf16(ctx, v.z_bf16, b.w1cat_bf16, nullptr, v.act_bf16, nr, 2 * m->d, ldz, 2 * m->d, EPI_SILU, 1.0f, lda)))
                 return rc;
-            if ((rc = launch_gemm_bf16_residual(ctx, ws.act_bf16, b.w2cat_bf16, feat_out, ws.z_bf16,
-                                                res_in, rscale, rows, m->d, lda, ldz)))
+            if ((rc = launch_gemm_bf16_residual(ctx, v.act_bf16, b.w2cat_bf16, feat_out, v.z_bf16,
+                                                res_in, rscale, nr, m->d, lda, ldz)))
                 return rc;
         }
-        if (obs_now && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, ws.weights, (int)m->cap, m->obs.q_pnc, k, ws.m_val,
-                                                 exact ? ws.z : nullptr, feat_out, res_in, rscale, d,
+        if (obs_now && (rc = launch_observe_rows(ctx, ws.last_rows, n_obs, v.weights, (int)m->cap, m->obs.q_pnc, k, v.m_val,
+                                                 exact ? v.z : nullptr, feat_out, res_in, rscale, d,
                                                  m->obs.buf + l * m->obs.lanes * obs_rec)))
             return rc;
         return PSSA_B200_OK;
     };
     auto other = [&](float* f) { return f == ws.feat_a ? ws.feat_b : ws.feat_a; };
+    // every stage is enqueued group by group, so the chains advance together on the host side too
+    auto each_group = [&](auto&& fn) -> int32_t {
+        int32_t r = PSSA_B200_OK;
+        for (size_t g = 0; g < n_groups && r == PSSA_B200_OK; ++g) {
+            if (groups[g].nr == 0) continue;  // only empty lanes: nothing to compute, their carries stay as they are
+            select(g);
+            r = fn();
+        }
+        ctx->stream = main_stream, ctx->chain = 0;
+        return r;
+    };
+    if ((rc = fork())) return rc;
     if (m->loops == 1) {
         // src/pssa.rs:2327-2337: block 0's output replaces the embedding, every further block adds its scaled output
-        for (size_t l = 0; l < m->depth; ++l) {
-            if ((rc = run_pass(l, 0, feat_in, feat_in, l == 0 ? 1.0f : m->residual_scales[l - 1], feat_out, true))) return rc;
+        for (size_t l = 0; l < m->depth && rc == PSSA_B200_OK; ++l) {
+            rc = each_group([&] { return run_pass(l, 0, feat_in, feat_in, l == 0 ? 1.0f : m->residual_scales[l - 1], feat_out, true); });
             feat_in = feat_out;
             feat_out = other(feat_out);
         }
@@ -351,18 +451,29 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // features = input + scale * features.
         const float loop_scale = 1.0f / (float)m->loops;
         float* feat = ws.feat_a;
-        if ((rc = launch_gather_rows(ctx, m->embed, ws.ids, feat, rows, d, m->v))) return rc;
-        for (size_t l = 0; l < m->depth; ++l) {
-            if (l > 0 && (rc = launch_residual(ctx, nullptr, feat, ws.feat_c, rows * (size_t)d, 1.0f))) return rc;  // keep the block's input
-            for (size_t li = 0; li < m->loops; ++li) {
+        rc = each_group([&] { return launch_gather_rows(ctx, m->embed, v.ids, feat + r0 * (size_t)d, nr, d, m->v); });
+        for (size_t l = 0; l < m->depth && rc == PSSA_B200_OK; ++l) {
+            if (l > 0)  // keep the block's input
+                rc = each_group([&] { return launch_residual(ctx, nullptr, feat + r0 * (size_t)d, ws.feat_c + r0 * (size_t)d, nr * (size_t)d, 1.0f); });
+            for (size_t li = 0; li < m->loops && rc == PSSA_B200_OK; ++li) {
                 float* next = other(feat);
-                if ((rc = run_pass(l, li, feat, feat, loop_scale, next, li + 1 == m->loops))) return rc;
+                rc = each_group([&] { return run_pass(l, li, feat, feat, loop_scale, next, li + 1 == m->loops); });
                 feat = next;
             }
-            if (l > 0 && (rc = launch_residual(ctx, ws.feat_c, feat, feat, rows * (size_t)d, m->residual_scales[l - 1]))) return rc;
+            if (l > 0 && rc == PSSA_B200_OK)
+                rc = each_group([&] {
+                    return launch_residual(ctx, ws.feat_c + r0 * (size_t)d, feat + r0 * (size_t)d, feat + r0 * (size_t)d, nr * (size_t)d,
+                                           m->residual_scales[l - 1]);
+                });
         }
         feat_in = feat;
     }
+    ctx->stream = main_stream, ctx->chain = 0;
+    {
+        const int32_t jr = join();  // always re-join, even after a failed launch: the side streams must not run past this call
+        if (rc == PSSA_B200_OK) rc = jr;
+    }
+    if (rc) return rc;
     *feats_out = feat_in;
     return PSSA_B200_OK;
 }

@@ -15,10 +15,10 @@
 //      least C = k + 4 slots pass (the C-th smallest of the minima of v = |p-k|^2 / (1-|k|^2) over groups of 32, 16 or 8
 //      slots), a second sweep lists the slots under it (about 20 of 512); the C smallest of the list are the candidates;
 //   4. one warp per row re-scores the candidates exactly as `poincare_distance` does (f64 differences and sum, f64
-//      log1p form of 2 asinh sqrt, rounded to f32), selects k by (bits, slot) and proves the selection: every slot
-//      outside the candidate set has an approximate v >= the largest candidate's, so its true distance is at least
-//      d(u_lb) with u_lb = (v_C - eps * max 1/(1-|k|^2)) / (1-|p|^2); if the k-th selected distance is strictly below
-//      that, no other slot can enter or tie. Otherwise (or if the list overflowed) the row is flagged and a second,
+//      log1p form of 2 asinh sqrt, rounded to f32), selects k by (bits, slot) and proves the selection: the sweeps
+//      also produced v_lb, the smallest (approximate v - its error bound) over every slot that did NOT become a candidate,
+//      so the true distance of each of those is at least d(v_lb / (1-|p|^2)); if the k-th selected distance is strictly
+//      below that, no other slot can enter or tie. Otherwise (or if the list overflowed) the row is flagged and a second,
 //      tiny kernel recomputes that row with f64 distances to every slot. Rare: a few rows per million.
 //   5. softmax over the k selected slots (sum in ascending slot order) and the value read, fused.
 // Every mbarrier wait is bounded like the GEMM pipeline's: on expiry the status word gets PSSA_B200_ERR_TIMEOUT and the
@@ -45,9 +45,12 @@ constexpr int kWorkWarps = 8;  // warps 2..9; the first four own the 128 TMEM la
 constexpr int kThreads = 64 + 32 * kWorkWarps;
 constexpr int kStages = 3;
 constexpr int kRingStage = 256 * BK * 2;  // one key k-block of up to 256 slots: 32 KB
-// absolute error bound of |p - k|^2 from the six-piece tensor-core product (measured below 2.5e-6 for points of the unit
-// ball; see the tensor-core distance test), with headroom
-constexpr float kEpsAbs = 8e-6f;
+// Error bound of the pre-filter's t = |p - k|^2 = (|p|^2 - p.k) + (|k|^2 - p.k): the tensor-core product p.k (six piece
+// products, fp32 accumulation that is not correctly rounded) is off by at most kEpsDot * |p| |k| (about fifty accumulation
+// steps of 2^-23 relative to sum |p_i k_i| <= |p| |k|; measured below 3.1e-6 |p| |k|, see the tensor-core distance test),
+// and the two fp32 subtractions and the addition by kEpsSum * (|p|^2 + |k|^2).
+constexpr float kEpsDot = 8e-6f;
+constexpr float kEpsSum = 5e-7f;
 
 __device__ __forceinline__ void bar_workers() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kWorkWarps) : "memory"); }
 
@@ -99,45 +102,53 @@ __device__ __forceinline__ float project_row(float* row, int dk, bool euclid, fl
 }
 
 // Last stage of a row, shared by the fused kernel and the exact fix-up: the k selected slots arrive in ASCENDING SLOT ORDER
-// (sel_slot / sel_dist in shared memory, one warp per row); weights exp((min - d) / tau) summed in that order
-// (memory.rs:391-398), normalised, value read in that order with separately rounded multiply and add (memory.rs:399-406).
+// (sel_slot / sel_dist in shared memory); weights exp((min - d) / tau) summed in that order (memory.rs:391-398),
+// normalised, value read in that order with separately rounded multiply and add (memory.rs:399-406). LANES threads of a
+// warp work on one row (32: a warp per row; 16: two rows per warp, `hl` the lane within the half); every lane of the warp
+// calls it, `active` says whether its row exists.
+template <int LANES>
 __device__ __forceinline__ void finish_row(const RetrieveParams& p, size_t q, const unsigned* sel_slot, float* sel_w, int k, float dmin,
-                                           int lane) {
+                                           int hl, bool active) {
     const float tau = p.tau;
-    const float my_w = lane < k ? expf(__fdiv_rn(__fsub_rn(dmin, sel_w[lane]), tau)) : 0.0f;  // sel_w holds distances on entry
+    const float my_w = (active && hl < k) ? expf(__fdiv_rn(__fsub_rn(dmin, sel_w[hl]), tau)) : 0.0f;  // sel_w holds distances on entry
     __syncwarp();
-    if (lane < k) sel_w[lane] = my_w;
+    if (active && hl < k) sel_w[hl] = my_w;
     __syncwarp();
     float sum = 0.0f;
-    for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, sel_w[j]);
-    const float wn = __fdiv_rn(my_w, sum);
+    if (active)
+        for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, sel_w[j]);
+    const float wn = active ? __fdiv_rn(my_w, sum) : 0.0f;
     __syncwarp();
-    if (lane < k) sel_w[lane] = wn;
+    if (active && hl < k) sel_w[hl] = wn;
     __syncwarp();
-    if (p.min_dist && lane == 0) p.min_dist[q] = dmin;
-    if (p.topk_slots && lane < k) p.topk_slots[q * k + lane] = sel_slot[lane];
-    if (p.topk_weights && lane < k) p.topk_weights[q * k + lane] = wn;
-    if (p.weights) {  // the reference's dense row: zero except the selected slots
+    if (!active) return;  // no warp-wide operation below
+    if (p.min_dist && hl == 0) p.min_dist[q] = dmin;
+    if (p.topk_slots && hl < k) p.topk_slots[q * k + hl] = sel_slot[hl];
+    if (p.topk_weights && hl < k) p.topk_weights[q * k + hl] = wn;
+    if (p.weights) {  // the reference's dense row: zero except the selected slots; every address is written once, by the
+                      // lane that owns it, so no ordering between a zero and a weight is needed
         float* row = p.weights + q * p.cap;
-        for (int i = lane; i < p.cap; i += 32) row[i] = 0.0f;
-        __syncwarp();
-        if (lane < k) row[sel_slot[lane]] = wn;
+        for (int i = hl; i < p.cap; i += LANES) {
+            float w = 0.0f;
+            for (int j = 0; j < k; ++j) w = sel_slot[j] == (unsigned)i ? sel_w[j] : w;
+            row[i] = w;
+        }
     }
     const int dv = p.dv;
-    for (int j0 = lane; j0 < dv; j0 += 32 * 4) {
+    for (int j0 = hl; j0 < dv; j0 += LANES * 4) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         for (int j = 0; j < k; ++j) {
             const float wi = sel_w[j];
             const float* v = p.values + (size_t)sel_slot[j] * dv;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int c = j0 + e * 32;
+                const int c = j0 + e * LANES;
                 if (c < dv) acc[e] = __fadd_rn(acc[e], __fmul_rn(wi, __ldg(v + c)));
             }
         }
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int c = j0 + e * 32;
+            const int c = j0 + e * LANES;
             if (c < dv) {
                 if (p.m_val) p.m_val[q * dv + c] = acc[e];
                 if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + c] = __float2bfloat16_rn(acc[e]);
@@ -146,10 +157,10 @@ __device__ __forceinline__ void finish_row(const RetrieveParams& p, size_t q, co
     }
 }
 
-// lane j < n holds (bits, slot): rank of this lane's pair among the n pairs by (bits, slot)
-__device__ __forceinline__ int rank_by_key(unsigned long long key, int n) {
+// lane base + j (j < n) holds (bits, slot): rank of this lane's pair among the n pairs by (bits, slot)
+__device__ __forceinline__ int rank_by_key(unsigned long long key, int n, int base) {
     int rank = 0;
-    for (int i = 0; i < n; ++i) rank += __shfl_sync(0xffffffffu, key, i) < key ? 1 : 0;
+    for (int i = 0; i < n; ++i) rank += __shfl_sync(0xffffffffu, key, base + i) < key ? 1 : 0;
     return rank;
 }
 
@@ -159,7 +170,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
     constexpr int KB_A = 3 * KB_PIECE;       // k-blocks of the A operand (three pieces)
     constexpr uint32_t A_BLOCK = BM * BK * 2;  // 16 KB
     constexpr int PITCH = DK + 1;            // staging pitch in floats (bank spreading for one-thread-per-row walks)
-    constexpr int EPL = DK / 32;             // key dimensions per lane in the re-scoring
+    constexpr int EPL = DK / 16;             // key dimensions per lane in the re-scoring (16 lanes per row)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* smem_a = smem;                         // [KB_A][128 x 64 bf16], swizzled
@@ -170,10 +181,10 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
     unsigned char* tail = ring + kStages * kRingStage;
     float2* kstat_s = reinterpret_cast<float2*>(tail);                     // [cap <= 512]
     float* stat_qs = reinterpret_cast<float*>(kstat_s + 512);              // [128] |p|^2
-    float* stat_vc = stat_qs + BM;                                         // [128] approximate v of the last candidate
+    float* stat_vc = stat_qs + BM;                                         // [128] lower bound of the true v of every non-candidate
     int* stat_cnt = reinterpret_cast<int*>(stat_vc + BM);                  // [128] listed slots (> kListCap: overflow)
-    float* stat_max_rk = reinterpret_cast<float*>(stat_cnt + BM);          // [1] largest 1/(1-|k|^2) of the occupied slots
-    unsigned short* cand_slot = reinterpret_cast<unsigned short*>(stat_max_rk + 4);  // [128][kCandMax]
+    float* knorm_s = reinterpret_cast<float*>(stat_cnt + BM);              // [cap <= 512] |k|
+    unsigned short* cand_slot = reinterpret_cast<unsigned short*>(knorm_s + 512);  // [128][kCandMax]
     unsigned* sel_slot_s = reinterpret_cast<unsigned*>(cand_slot + BM * kCandMax);  // [kWorkWarps][32]
     float* sel_w_s = reinterpret_cast<float*>(sel_slot_s + kWorkWarps * 32);        // [kWorkWarps][32]
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(sel_w_s + kWorkWarps * 32);
@@ -204,7 +215,11 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < cap; i += kThreads) kstat_s[i] = p.k_stat[i];
+    for (int i = threadIdx.x; i < cap; i += kThreads) {
+        const float2 ks = p.k_stat[i];
+        kstat_s[i] = ks;
+        knorm_s[i] = sqrtf(ks.x) * 1.0000002f;  // rounded up: it scales an error bound
+    }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
@@ -281,18 +296,15 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
         const bool vec_q = (((p.ldq ? p.ldq : (size_t)dk) & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0);
         uint32_t it = 0;
         bool alive = true;
-        if (wid == 0) {
-            float m = 0.0f;
-            for (int i = lane; i < count; i += 32) m = fmaxf(m, kstat_s[i].y);
-#pragma unroll
-            for (int sh = 16; sh > 0; sh >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, sh));
-            if (lane == 0) *stat_max_rk = m;
-        }
-        bar_workers();
-        const float max_rk = *stat_max_rk;
+        long long clk[6] = {0, 0, 0, 0, 0, 0};
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
             const size_t q0 = (size_t)tile * BM;
             const size_t ldq = p.ldq ? p.ldq : (size_t)dk;
+            long long t_prev = clock64();
+            auto lap = [&](int i) {
+                const long long now = clock64();
+                clk[i] += now - t_prev, t_prev = now;
+            };
             // ---- P0: the tile's raw queries, coalesced, into the staging rows
             if (vec_q) {
                 for (int idx = wtid; idx < BM * (DK / 4); idx += 32 * kWorkWarps) {
@@ -308,6 +320,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                 }
             }
             bar_workers();
+            lap(0);
             // ---- P1: one thread per row projects it (memory.rs:198-211), in place
             if (wtid < BM) {
                 float qn = 0.0f;
@@ -316,6 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                 if (p.q_norm && p.q_is_euclidean && q0 + wtid < p.rows) p.q_norm[q0 + wtid] = qn;
             }
             bar_workers();
+            lap(1);
             // ---- P2: three bf16 pieces of every coordinate into the swizzled A operand; q_pnc goes out
             for (int idx = wtid; idx < BM * (DK / 2); idx += 32 * kWorkWarps) {
                 const int r = idx / (DK / 2), c = (idx % (DK / 2)) * 2;
@@ -337,6 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             tcgen05_fence_before();
             bar_workers();
             if (wtid == 0) mbar_arrive(a_ready);  // releases the ring to the producer and the operand to the issuer
+            lap(2);
             // ---- P3: two sweeps over the accumulator row (row warps only)
             if (row_warp) {
                 if (alive) {  // every lane waits (each needs the barrier's acquire); the verdict is made warp-uniform
@@ -345,7 +360,10 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                     if (!alive && lane == 0) atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
                 }
                 tcgen05_fence_after();
+                lap(3);  // waiting for the tensor cores
                 const float qs = stat_qs[my_row];
+                const float pn = sqrtf(qs) * 1.0000002f;
+                float excl = CUDART_INF_F;  // smallest lower bound of the true v over the slots that do not become candidates
                 const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
                 float best[kCandMax];
 #pragma unroll
@@ -378,6 +396,10 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                             } else if (v <= theta) {
                                 if (cnt < kListCap) list_v[cnt * BM + my_row] = v, list_s[cnt * BM + my_row] = (unsigned short)col;
                                 ++cnt;
+                            } else {
+                                // not listed: v minus its own error bound (both scaled by 1/(1-|k|^2))
+                                const float err = fmaf(kEpsDot * pn, knorm_s[col], kEpsSum * (qs + ks.x));
+                                excl = fminf(excl, fmaf(-err, ks.y, v));
                             }
                         }
                     }
@@ -397,121 +419,126 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                     unsigned long long x = ((unsigned long long)__float_as_uint(list_v[e * BM + my_row]) << 32) | list_s[e * BM + my_row];
 #pragma unroll
                     for (int i = 0; i < kCandMax; ++i) {
-                        const unsigned long long lo = umin64(top[i], x), hi = umax64(top[i], x);
-                        top[i] = lo, x = hi;
+                        if (i < n_cand) {  // entries past the candidates stay empty: what falls out of the first n_cand is excluded
+                            const unsigned long long lo = umin64(top[i], x), hi = umax64(top[i], x);
+                            top[i] = lo, x = hi;
+                        }
+                    }
+                    if (x != ~0ull) {  // a listed slot that is not (or no longer) a candidate
+                        const unsigned slot = (unsigned)(x & 0xffffu);
+                        const float2 ks = kstat_s[slot];
+                        const float err = fmaf(kEpsDot * pn, knorm_s[slot], kEpsSum * (qs + ks.x));
+                        excl = fminf(excl, fmaf(-err, ks.y, __uint_as_float((unsigned)(x >> 32))));
                     }
                 }
-                float vc = 0.0f;
 #pragma unroll
-                for (int i = 0; i < kCandMax; ++i) {
-                    cand_slot[my_row * kCandMax + i] = (unsigned short)(top[i] & 0xffffu);
-                    if (i == n_cand - 1) vc = __uint_as_float((unsigned)(top[i] >> 32));
-                }
-                stat_vc[my_row] = vc;
+                for (int i = 0; i < kCandMax; ++i) cand_slot[my_row * kCandMax + i] = (unsigned short)(top[i] & 0xffffu);
+                stat_vc[my_row] = excl;
                 stat_cnt[my_row] = alive ? cnt : kListCap + 1;
             }
             bar_workers();
-            // ---- P5: one warp per row: exact re-scoring, selection, proof, softmax, value read
-            unsigned* sel_slot = sel_slot_s + wid * 32;
-            float* sel_w = sel_w_s + wid * 32;
-            for (int r = wid; r < BM; r += kWorkWarps) {
-                const size_t q = q0 + r;
-                if (q >= p.rows) break;  // rows of a tile are consecutive: the rest are padding too
-                if (stat_cnt[r] > kListCap) {  // list overflow (or an abandoned accumulator): no candidates to trust
-                    if (lane == 0) p.fixup_list[atomicAdd(p.fixup_count, 1u)] = (unsigned)q;
-                    continue;
-                }
-                // the projected point from its three pieces (their sum is exact)
-                float pf[EPL];
+            lap(4);
+            // ---- P5: half a warp per row (two rows per warp in flight): exact re-scoring, selection, proof, softmax, value read
+            {
+                const int half = lane >> 4, hl = lane & 15, base = lane & 16;
+                unsigned* sel_slot = sel_slot_s + wid * 32 + half * 16;
+                float* sel_w = sel_w_s + wid * 32 + half * 16;
+                for (int rb = wid * 2; rb < BM; rb += kWorkWarps * 2) {
+                    const int r = rb + half;
+                    const size_t q = q0 + r;
+                    const bool exists = q < p.rows;
+                    // a list overflow (or an abandoned accumulator) leaves no candidates to trust
+                    const bool trusted = exists && stat_cnt[r] <= kListCap;
+                    // the projected point from its three pieces (their sum is exact); lane hl owns dimensions hl + 16 e
+                    float pf[EPL];
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) {
-                    const int c = lane + 32 * e;
-                    const uint32_t off = sw128_offset(r, c % BK);
-                    const int kb = c / BK;
-                    const float x0 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off));
-                    const float x1 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off));
-                    const float x2 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off));
-                    pf[e] = x0 + (x1 + x2);
-                }
-                double part[kCandMax];
+                    for (int e = 0; e < EPL; ++e) {
+                        const int c = hl + 16 * e;
+                        const uint32_t off = sw128_offset(r, c % BK);
+                        const int kb = c / BK;
+                        const float x0 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off));
+                        const float x1 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off));
+                        const float x2 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off));
+                        pf[e] = x0 + (x1 + x2);
+                    }
+                    double part[kCandMax];
 #pragma unroll
-                for (int j = 0; j < kCandMax; ++j) {
-                    part[j] = 0.0;
-                    if (j < n_cand) {
-                        const float* krow = p.keys + (size_t)cand_slot[r * kCandMax + j] * dk;
+                    for (int j = 0; j < kCandMax; ++j) {
+                        part[j] = 0.0;
+                        if (j < n_cand && trusted) {
+                            const float* krow = p.keys + (size_t)cand_slot[r * kCandMax + j] * dk;
 #pragma unroll
-                        for (int e = 0; e < EPL; ++e) {
-                            const double df = (double)pf[e] - (double)__ldg(krow + lane + 32 * e);
-                            part[j] = fma(df, df, part[j]);
+                            for (int e = 0; e < EPL; ++e) {
+                                const double df = (double)pf[e] - (double)__ldg(krow + hl + 16 * e);
+                                part[j] = fma(df, df, part[j]);
+                            }
                         }
                     }
-                }
-                // transpose-reduce: after the five steps lane L holds the full sum of candidate
-                // ((L >> 4) & 1) * 8 + ((L >> 3) & 1) * 4 + ((L >> 2) & 1) * 2 + ((L >> 1) & 1)
+                    // transpose-reduce over the 16 lanes of the half: after the four steps lane hl holds the full sum of candidate hl
 #pragma unroll
-                for (int half = 8, mask = 16; half >= 1; half >>= 1, mask >>= 1) {
-                    const bool upper = (lane & mask) != 0;
+                    for (int n = 8, mask = 8; n >= 1; n >>= 1, mask >>= 1) {
+                        const bool upper = (lane & mask) != 0;
 #pragma unroll
-                    for (int i = 0; i < half; ++i) {
-                        const double send = upper ? part[i] : part[i + half];
-                        const double keep = upper ? part[i + half] : part[i];
-                        part[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+                        for (int i = 0; i < n; ++i) {
+                            const double send = upper ? part[i] : part[i + n];
+                            const double keep = upper ? part[i + n] : part[i];
+                            part[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
+                        }
                     }
-                }
-                part[0] += __shfl_xor_sync(0xffffffffu, part[0], 1);
-                const int my_cand = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
-                const double one_minus_q = 1.0 - (double)stat_qs[r];
-                float d_mine = CUDART_INF_F;
-                unsigned slot_mine = 0xffffu;
-                if (my_cand < n_cand) {
-                    slot_mine = cand_slot[r * kCandMax + my_cand];
-                    d_mine = exact_distance(part[0], one_minus_q, __ldg(p.norm_sq + slot_mine));
-                }
-                // lane j takes candidate j
-                const int src = ((lane & 8) ? 16 : 0) | ((lane & 4) ? 8 : 0) | ((lane & 2) ? 4 : 0) | ((lane & 1) ? 2 : 0);
-                const float d_j = __shfl_sync(0xffffffffu, d_mine, src);
-                const unsigned slot_j = __shfl_sync(0xffffffffu, slot_mine, src);
-                const bool has = lane < n_cand;
-                const unsigned long long key = has ? (((unsigned long long)__float_as_uint(d_j) << 32) | slot_j) : ~0ull;
-                const int rank = rank_by_key(key, n_cand);
-                const bool selected = has && rank < k;
-                // the largest selected distance and the smallest of all
-                unsigned kth_bits = selected ? __float_as_uint(d_j) : 0u;
-                unsigned min_bits = has ? __float_as_uint(d_j) : 0xffffffffu;
-#pragma unroll
-                for (int m = 16; m > 0; m >>= 1) {
-                    kth_bits = max(kth_bits, __shfl_xor_sync(0xffffffffu, kth_bits, m));
-                    min_bits = min(min_bits, __shfl_xor_sync(0xffffffffu, min_bits, m));
-                }
-                // proof that no slot outside the candidate set can enter or tie
-                bool decisive = false;
-                if (lane == 0) {
-                    const double v_lb = (double)stat_vc[r] * (1.0 - 4e-7) - (double)kEpsAbs * (double)max_rk;
-                    if (v_lb > 0.0) {
-                        const double u_lb = v_lb / one_minus_q;
-                        const float d_lb = (float)log1p(2.0 * u_lb + 2.0 * sqrt(fma(u_lb, u_lb, u_lb)));
-                        decisive = kth_bits < __float_as_uint(d_lb);
+                    const double one_minus_q = 1.0 - (double)stat_qs[r];
+                    const bool has = trusted && hl < n_cand;
+                    float d_j = CUDART_INF_F;
+                    unsigned slot_j = 0xffffu;
+                    if (has) {
+                        slot_j = cand_slot[r * kCandMax + hl];
+                        d_j = exact_distance(part[0], one_minus_q, __ldg(p.norm_sq + slot_j));
                     }
-                    if (p.selftest_every > 0 && q % (size_t)p.selftest_every == 0) decisive = false;
-                    if (!decisive) p.fixup_list[atomicAdd(p.fixup_count, 1u)] = (unsigned)q;
+                    const unsigned long long key = has ? (((unsigned long long)__float_as_uint(d_j) << 32) | slot_j) : ~0ull;
+                    const int rank = rank_by_key(key, n_cand, base);
+                    const bool selected = has && rank < k;
+                    // the largest selected distance and the smallest of all, within the half
+                    unsigned kth_bits = selected ? __float_as_uint(d_j) : 0u;
+                    unsigned min_bits = has ? __float_as_uint(d_j) : 0xffffffffu;
+#pragma unroll
+                    for (int mk = 8; mk > 0; mk >>= 1) {
+                        kth_bits = max(kth_bits, __shfl_xor_sync(0xffffffffu, kth_bits, mk));
+                        min_bits = min(min_bits, __shfl_xor_sync(0xffffffffu, min_bits, mk));
+                    }
+                    // proof that no slot outside the candidate set can enter or tie
+                    int decisive = 0;
+                    if (hl == 0 && exists) {
+                        if (trusted) {
+                            // every slot outside the candidate set has a true v of at least this (1 - 4e-7: the f32 rounding of v itself)
+                            const double v_lb = (double)stat_vc[r] * (1.0 - 4e-7);
+                            if (v_lb > 0.0) {
+                                const double u_lb = v_lb / one_minus_q;
+                                const float d_lb = (float)log1p(2.0 * u_lb + 2.0 * sqrt(fma(u_lb, u_lb, u_lb)));
+                                decisive = kth_bits < __float_as_uint(d_lb);
+                            }
+                            if (p.selftest_every > 0 && q % (size_t)p.selftest_every == 0) decisive = 0;
+                        }
+                        if (!decisive) p.fixup_list[atomicAdd(p.fixup_count, 1u)] = (unsigned)q;  // the exact pass writes this row
+                    }
+                    decisive = __shfl_sync(0xffffffffu, decisive, base);
+                    // ascending slot order among the selected
+                    int srank = 0;
+                    for (int i = 0; i < n_cand; ++i) {
+                        const unsigned other_slot = __shfl_sync(0xffffffffu, slot_j, base + i);
+                        const bool other_sel = __shfl_sync(0xffffffffu, selected ? 1 : 0, base + i) != 0;
+                        srank += (other_sel && other_slot < slot_j) ? 1 : 0;
+                    }
+                    __syncwarp();
+                    if (selected && decisive) sel_slot[srank] = slot_j, sel_w[srank] = d_j;
+                    __syncwarp();
+                    finish_row<16>(p, q, sel_slot, sel_w, k, __uint_as_float(min_bits), hl, decisive != 0);
+                    __syncwarp();
                 }
-                decisive = __shfl_sync(0xffffffffu, decisive ? 1 : 0, 0) != 0;
-                if (!decisive) continue;  // the exact fix-up kernel writes this row
-                // ascending slot order among the selected
-                int srank = 0;
-                for (int i = 0; i < n_cand; ++i) {
-                    const unsigned other_slot = __shfl_sync(0xffffffffu, slot_j, i);
-                    const bool other_sel = __shfl_sync(0xffffffffu, selected ? 1 : 0, i) != 0;
-                    srank += (other_sel && other_slot < slot_j) ? 1 : 0;
-                }
-                __syncwarp();
-                if (selected) sel_slot[srank] = slot_j, sel_w[srank] = d_j;
-                __syncwarp();
-                finish_row(p, q, sel_slot, sel_w, k, __uint_as_float(min_bits), lane);
-                __syncwarp();
             }
             bar_workers();  // the lists and the operand are free for the next tile
+            lap(5);
         }
+        if (p.phase_cycles && wtid == 0)
+            for (int i = 0; i < 6; ++i) atomicAdd(p.phase_cycles + i, (unsigned long long)clk[i]);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -574,7 +601,7 @@ __global__ void __launch_bounds__(256) retrieve_topk_fixup_kernel(RetrieveParams
     for (int i = 0; i < k; ++i) srank += __shfl_sync(0xffffffffu, my_slot, i) < my_slot ? 1 : 0;
     if (lane < k) sel_slot_s[warp][srank] = my_slot, sel_w_s[warp][srank] = my_dist;
     __syncwarp();
-    finish_row(p, q, sel_slot_s[warp], sel_w_s[warp], k, dmin, lane);
+    finish_row<32>(p, q, sel_slot_s[warp], sel_w_s[warp], k, dmin, lane, true);
     }
 }
 
@@ -604,7 +631,7 @@ __global__ void __launch_bounds__(256) compact_topk_kernel(const float* __restri
 
 size_t fused_smem(int dk) {
     const size_t a = (size_t)3 * (dk / BK) * BM * BK * 2;
-    const size_t tail = 512 * sizeof(float2) + 3 * BM * 4 + 16 + BM * kCandMax * 2 + 2 * kWorkWarps * 32 * 4 + (2 * kStages + 2) * 8 + 16;
+    const size_t tail = 512 * sizeof(float2) + 3 * BM * 4 + 512 * 4 + BM * kCandMax * 2 + 2 * kWorkWarps * 32 * 4 + (2 * kStages + 2) * 8 + 16;
     return 1024 + a + (size_t)kStages * kRingStage + tail;
 }
 

@@ -169,19 +169,19 @@ class B200Dispatch:
 
     # ---- episodic memory read
     @staticmethod
-    def _mem_flags(exact, f32_distance, tc_distance=False, no_fused=False, handover_selftest=False):
+    def _mem_flags(exact, f32_distance, tc_distance=False, no_fused=False, handover_selftest=False, phase_clocks=False):
         return ((N.MEM_EXACT if exact else 0) | (N.MEM_F32_DISTANCE if f32_distance else 0) |
                 (N.MEM_TC_DISTANCE if tc_distance else 0) | (N.MEM_NO_FUSED if no_fused else 0) |
-                (N.MEM_HANDOVER_SELFTEST if handover_selftest else 0))
+                (N.MEM_HANDOVER_SELFTEST if handover_selftest else 0) | (N.MEM_PHASE_CLOCKS if phase_clocks else 0))
 
     def memory_read_topk_dev(self, q, keys, norm_sq, values, rows, dk, dv, cap, count, tau, top_k, m_val, slots_out=None,
                              weights_out=None, q_pnc=None, q_norm=None, min_dist=None, handed_over=None, q_is_euclidean=True,
-                             exact=False, no_fused=False, handover_selftest=False):
+                             exact=False, no_fused=False, handover_selftest=False, phase_clocks=False):
         """Top-k read with compact results (device buffers): see pssa_b200_memory_read_topk_dev in include/pssa_b200.h."""
         self._check(self._lib.pssa_b200_memory_read_topk_dev(
             self._h, _ptr(q), 1 if q_is_euclidean else 0, _ptr(keys), _ptr(norm_sq), _ptr(values), rows, dk, dv, cap, count, tau,
             top_k, _ptr(q_pnc), _ptr(q_norm), _ptr(m_val), _ptr(min_dist), _ptr(slots_out), _ptr(weights_out), _ptr(handed_over),
-            self._mem_flags(exact, False, False, no_fused, handover_selftest)))
+            self._mem_flags(exact, False, False, no_fused, handover_selftest, phase_clocks)))
 
     def memory_read(self, q, keys, norm_sq, values, count, tau, top_k=0, q_is_euclidean=True, exact=False,
                     f32_distance=False, tc_distance=False, no_fused=False, handover_selftest=False):

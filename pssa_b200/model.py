@@ -112,6 +112,10 @@ class PSSAModel:
         self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 4, int(loops)))
         self.loops = int(loops)
 
+    def set_lane_groups(self, groups):
+        """Lane groups on side streams per pass: 0 = chosen from the shape, 1 = off, 2..4 = that many groups."""
+        self.gpu._check(self._lib.pssa_b200_model_set_option(self._h, 5, int(groups)))
+
     def set_max_rows(self, rows):
         self.gpu._check(self._lib.pssa_b200_model_set_max_rows(self._h, rows))
 

@@ -27,6 +27,7 @@ pub const PSSA_B200_MEM_F32_DISTANCE: u32 = 2;
 pub const PSSA_B200_MEM_TC_DISTANCE: u32 = 4;
 pub const PSSA_B200_MEM_NO_FUSED: u32 = 8;
 pub const PSSA_B200_MEM_HANDOVER_SELFTEST: u32 = 16;
+pub const PSSA_B200_MEM_PHASE_CLOCKS: u32 = 32;
 pub const PSSA_B200_SAMPLE_EXACT: u32 = 1;
 
 /// `pssa_b200_epilogue`

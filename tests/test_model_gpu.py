@@ -377,3 +377,67 @@ def test_device_resident_ids_outside_the_vocabulary_raise_the_status_word(gpu):
     gpu.poll_status()  # cleared
     gpu.set_stream(None)
     gm.close()
+
+
+@pytest.mark.parametrize("precision", [1, 0])
+def test_lane_groups_on_side_streams_do_not_change_results(gpu, precision):
+    """A pass over several lanes may be enqueued as up to four groups of consecutive lanes on side streams (the groups
+    share only read-only weights). Logits, greedy tokens and carries must be bit-identical to the single-stream schedule,
+    for ragged prefill (including an empty lane), for decode steps, with top-k reads, and under the stage profile."""
+    om, gm = make_pair(gpu, 2, 300, 192, 64, 64, 512, seed=77, streams=7, precision=precision)
+    rng = np.random.default_rng(8)
+    lanes = [list(rng.integers(1, 300, n)) for n in (40, 3, 0, 65, 17, 1, 30)]
+    results = []
+    for groups, top_k in ((1, None), (2, None), (4, None), (3, None), (1, 8), (4, 8)):
+        if top_k:
+            gm.set_memory_top_k(top_k)
+        gm.set_lane_groups(groups)
+        gm.reset_recurrent_state()
+        if groups == 4:
+            gpu.profile_begin()
+        logits, greedy = gm.prefill_batch(lanes, want_greedy=True)
+        ids = np.where(np.array([len(x) for x in lanes]) > 0, greedy, 1)
+        for _ in range(3):
+            step_logits, ids = gm.decode_step(ids, want_logits=True, want_greedy=True)
+        if groups == 4:
+            rows = gpu.profile_end()
+            assert any("ssm" in k for k in rows)
+        states = np.stack([gm.copy_recurrent_state_to(s) for s in range(7)])
+        results.append((top_k, logits, greedy, step_logits, ids, states))
+    for top_k in (None, 8):
+        same = [r for r in results if r[0] == top_k]
+        for other in same[1:]:
+            for a, b in zip(same[0][1:], other[1:]):
+                assert np.array_equal(a.view(np.uint32) if a.dtype == np.float32 else a, b.view(np.uint32) if b.dtype == np.float32 else b)
+    gm.set_lane_groups(0)
+    gpu.poll_status()
+    gm.close()
+
+
+def test_decode_graph_with_lane_groups_replays_the_eager_tokens(gpu):
+    """Fork and join of the lane groups are events between streams, so the captured step keeps its parallel branches."""
+    import torch
+    gpu.set_stream(torch.cuda.current_stream())
+    _, gm = make_pair(gpu, 2, 97, 32, 16, 8, 16, seed=31, streams=6, precision=0)
+    _, gm2 = make_pair(gpu, 2, 97, 32, 16, 8, 16, seed=31, streams=6, precision=0)
+    gm.set_lane_groups(3)
+    gm2.set_lane_groups(1)
+    prompts = [[5, 9, 2], [11, 3], [7], [8, 8], [1, 2, 3, 4], [9]]
+    _, g0 = gm.prefill_batch(prompts, want_logits=False, want_greedy=True)
+    _, g0b = gm2.prefill_batch(prompts, want_logits=False, want_greedy=True)
+    assert np.array_equal(g0, g0b)
+    eager = [g0b]
+    for _ in range(5):
+        eager.append(gm2.decode_step(eager[-1], want_logits=False, want_greedy=True))
+    ids_dev = torch.tensor(g0.astype(np.int32), device="cuda", dtype=torch.int32)
+    graph = gm.capture_greedy_decode_graph(ids_dev)
+    torch.cuda.synchronize()
+    assert np.array_equal(ids_dev.cpu().numpy().astype(np.uint64), eager[1])
+    for step in range(2, 6):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(ids_dev.cpu().numpy().astype(np.uint64), eager[step]), step
+    gpu.poll_status()
+    gpu.set_stream(None)
+    gm.close()
+    gm2.close()
