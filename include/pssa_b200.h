@@ -193,7 +193,7 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
  * bf16 precision mode uses it). Needs d_key % 64 == 0, otherwise PSSA_B200_MEM_F32_DISTANCE behaviour applies.
  * Ignored together with PSSA_B200_MEM_EXACT. */
 #define PSSA_B200_MEM_TC_DISTANCE 4u
-/* Top-k reads whose shape allows it (capacity 128 / 256 / 512, d_key 64 or 128, top_k <= 12, at least 8 * (top_k + 6)
+/* Top-k reads whose shape allows it (capacity 128 / 256 / 512, d_key 64 or 128, top_k <= 12, at least 8 * (top_k + 3)
  * occupied slots) run as
  * ONE kernel: tensor-core inner products only pre-filter the slots, the candidates are re-scored with the reference's f64
  * arithmetic and selected by (distance bits, slot), and a row whose selection cannot be proven from the candidates is
@@ -202,10 +202,11 @@ int32_t pssa_b200_ssm_forward(pssa_b200_ctx* ctx, const float* delta, const floa
 #define PSSA_B200_MEM_NO_FUSED 8u
 /* Test hook: the one-kernel top-k read hands every third row to its exact pass regardless of the proof. */
 #define PSSA_B200_MEM_HANDOVER_SELFTEST 16u
-/* Diagnostic of pssa_b200_memory_read_topk_dev: `handed_over` then points at 14 u32 words (8-byte aligned): the count,
- * one pad word, then six 64-bit counters of SM clock cycles summed over the CTAs of the one-kernel read: loading the
- * queries, projecting, splitting into bf16 pieces, waiting for the tensor cores, the two sweeps with the candidate
- * selection, and the per-row exact stage. */
+/* Diagnostic of pssa_b200_memory_read_topk_dev: `handed_over` then points at 26 u32 words (8-byte aligned): the count,
+ * one pad word, then twelve 64-bit counters of SM clock cycles summed over the CTAs of the one-kernel read: loading the
+ * queries, projecting, splitting into bf16 pieces, waiting for the tensor cores, the first sweep (group minima), the
+ * threshold, the second sweep (listing), the candidate selection, the exact squared distances, the distances, selection
+ * proof + softmax, and the value read. */
 #define PSSA_B200_MEM_PHASE_CLOCKS 32u
 
 /*

@@ -387,7 +387,7 @@ static int32_t memory_read_impl(pssa_b200_ctx* ctx, const float* q, int32_t q_is
     RetrieveParams probe = p;
     probe.k_split = probe.k_stat = nullptr;
     unsigned dummy = 0;
-    probe.k_split = &dummy, probe.k_stat = reinterpret_cast<const float2*>(&dummy), probe.fixup_list = &dummy, probe.fixup_count = &dummy;
+    probe.k_split = &dummy, probe.k_stat = reinterpret_cast<const float2*>(&dummy), probe.fixup_count = &dummy;
     const bool fused = topk && !p.no_fused && retrieve_fused_eligible(probe);
     const bool tc_read = !exact && !topk && count > 0 && capacity % 64 == 0;
     const bool tc_dist = !exact && !fused && (flags & PSSA_B200_MEM_TC_DISTANCE) != 0 && d_key % 64 == 0 && count > 0;
@@ -416,15 +416,14 @@ static int32_t memory_read_impl(pssa_b200_ctx* ctx, const float* q, int32_t q_is
         }
         if (tc_dist) p.q_split = arena_take(ctx, rows * 3 * d_key * 2), p.q_stat = (float2*)arena_take(ctx, rows * 8);
         if (fused) {
-            uint32_t* fx = (uint32_t*)arena_take(ctx, (rows + 1) * 4);
-            p.fixup_count = fx, p.fixup_list = fx + 1;
+            p.fixup_count = (uint32_t*)arena_take(ctx, 4);
         }
     }
     p.weights = weights;
     if (fused) p.topk_slots = slots_out, p.topk_weights = topk_w_out;
     if (fused && handed_over && (flags & PSSA_B200_MEM_PHASE_CLOCKS)) {
         p.phase_cycles = reinterpret_cast<unsigned long long*>(handed_over + 2);
-        PSSA_CUDA(ctx, cudaMemsetAsync(handed_over + 2, 0, 6 * sizeof(unsigned long long), ctx->stream));
+        PSSA_CUDA(ctx, cudaMemsetAsync(handed_over + 2, 0, kRetrievePhases * sizeof(unsigned long long), ctx->stream));
     }
     if ((rc = launch_memory_read(ctx, p, exact)) != PSSA_B200_OK) return rc;
     if (!fused && topk && (slots_out || topk_w_out) &&

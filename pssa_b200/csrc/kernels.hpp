@@ -67,6 +67,7 @@ int32_t launch_seqpar_fold(pssa_b200_ctx* ctx, const float* gathered, size_t rec
                            float* carry_in, int d, int s);
 
 // retrieve_poincare.cu
+constexpr int kRetrievePhases = 12;  // cycle counters of the one-kernel top-k read (see PSSA_B200_MEM_PHASE_CLOCKS)
 struct RetrieveParams {
     const float* q;        // [rows, dk] Euclidean queries (projected here) or points already in the ball
     int q_is_euclidean;
@@ -100,15 +101,14 @@ struct RetrieveParams {
     const void* k_split;
     const float2* k_stat;
     // exact top-k in one kernel (retrieve_fused.cu): compact outputs [rows, top_k] in ascending slot order (either may be
-    // null), the list of rows handed to the exact fix-up pass with its counter (scratch, rows + 1 words), and a test hook
-    // that hands every n-th row over regardless (0 = off)
+    // null), the counter of rows whose selection the candidates could not prove (recomputed over every slot by the same
+    // kernel; one scratch word), and a test hook that treats every n-th row that way regardless (0 = off)
     unsigned* topk_slots;
     float* topk_weights;
-    unsigned* fixup_list;
     unsigned* fixup_count;
     int selftest_every;
     int no_fused;          // keep the multi-kernel path even where the one-kernel top-k read applies
-    unsigned long long* phase_cycles;  // optional [6] device counters: clock cycles one worker thread per CTA spent per phase
+    unsigned long long* phase_cycles;  // optional [kRetrievePhases] device counters: clock cycles one worker thread per CTA spent per phase
     int* status;           // context status word (set by the launcher)
 };
 int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exact);

@@ -59,7 +59,7 @@ struct Workspace {
     void *x_bf16 = nullptr, *y_bf16 = nullptr, *m_bf16 = nullptr, *z_bf16 = nullptr, *act_bf16 = nullptr, *w_split = nullptr;
     void* q_split = nullptr;     // projected queries as three bf16 pieces [rows, 3*k] (tensor-core distances)
     float2* q_stat = nullptr;    // [rows] (|p|^2, 1/(1-|p|^2))
-    uint32_t* fixup = nullptr;   // [rows + 1] rows the fused top-k read hands to its exact pass, and their count
+    uint32_t* fixup = nullptr;   // [8] rows the fused top-k read recomputed over every slot, per lane group
     // z_bf16 is [rows, d + 64] and act_bf16 [rows, 2d + 64] when the adapter rides in the MLP products (rank 16)
     char* base = nullptr;
     size_t bytes = 0;

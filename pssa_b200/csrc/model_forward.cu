@@ -40,7 +40,7 @@ int32_t ensure_workspace(pssa_b200_model* m, size_t rows, size_t lanes) {
            o_act = c.take(rows * 2 * d * f), o_lf = c.take(lanes * d * f), o_lg = c.take(lanes * m->v * f);
     size_t o_xb = c.take(rows * d * 2), o_yb = c.take(rows * d * 2), o_mb = c.take(rows * d * 2), o_zb = c.take(rows * (d + 64) * 2),
            o_ab = c.take(rows * (2 * d + 64) * 2), o_wsp = c.take(rows * 3 * m->cap * 2), o_qsp = c.take(rows * 3 * m->k * 2),
-           o_qst = c.take(rows * sizeof(float2)), o_fix = c.take((rows + 8) * 4);  // 8 counters (one per lane group), then the lists
+           o_qst = c.take(rows * sizeof(float2)), o_fix = c.take(8 * 4);  // counters of the one-kernel top-k read, one per lane group
     size_t total = c.take(0);
     PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (ws.base) cudaFree(ws.base);
@@ -380,7 +380,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         rp.skip_weights = rp.w_split && !obs_now && !(rp.top_k != 0 && rp.top_k < rp.count);
         if (k % 64 == 0) rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
         if (!exact && k % 64 == 0) rp.q_split = v.q_split, rp.q_stat = v.q_stat;
-        rp.fixup_list = ws.fixup + 8 + r0, rp.fixup_count = ws.fixup + gi;  // exact top-k in one kernel when the shape allows it
+        rp.fixup_count = ws.fixup + gi;  // exact top-k in one kernel when the shape allows it
         if (!obs_now) rp.weights = (rp.top_k != 0 && rp.top_k < rp.count && retrieve_fused_eligible(rp)) ? nullptr : v.weights;
         // All-slots read in the bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s). The bank's values were carried
         // through W_proj at upload (vpsplit_bf16), so the product of the weight rows with them IS the memory projection and
@@ -437,7 +437,11 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         ctx->stream = main_stream, ctx->chain = 0;
         return r;
     };
-    if ((rc = fork())) return rc;
+    ctx->slim = n_groups > 1;
+    if ((rc = fork())) {
+        ctx->slim = false;
+        return rc;
+    }
     if (m->loops == 1) {
         // src/pssa.rs:2327-2337: block 0's output replaces the embedding, every further block adds its scaled output
         for (size_t l = 0; l < m->depth && rc == PSSA_B200_OK; ++l) {
@@ -468,7 +472,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         }
         feat_in = feat;
     }
-    ctx->stream = main_stream, ctx->chain = 0;
+    ctx->stream = main_stream, ctx->chain = 0, ctx->slim = false;
     {
         const int32_t jr = join();  // always re-join, even after a failed launch: the side streams must not run past this call
         if (rc == PSSA_B200_OK) rc = jr;

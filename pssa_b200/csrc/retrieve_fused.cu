@@ -8,18 +8,20 @@
 // The idea: the tensor cores are a PRE-FILTER, the reference's f64 arithmetic decides.
 //   1. worker warps project the tile's queries into the ball (f64, the reference's sequential sums: same bits) and write
 //      the points as three bf16 pieces straight into the 128-byte-swizzled A operand in shared memory;
-//   2. one thread issues tcgen05.mma for the six piece products above 2^-24 of p.k against the bank's keys (split the
+//   2. one thread issues tcgen05.mma for the three piece products above 2^-16 of p.k against the bank's keys (split the
 //      same way once per upload, streamed by TMA through a 3-stage ring); the 128 x capacity accumulator fills the SM's
 //      TMEM (512 fp32 columns);
-//   3. one thread per query row reads its accumulator row twice with tcgen05.ld: a first sweep finds a threshold that at
-//      least C = k + 4 slots pass (the C-th smallest of the minima of v = |p-k|^2 / (1-|k|^2) over groups of 32, 16 or 8
-//      slots), a second sweep lists the slots under it (about 20 of 512); the C smallest of the list are the candidates;
-//   4. one warp per row re-scores the candidates exactly as `poincare_distance` does (f64 differences and sum, f64
-//      log1p form of 2 asinh sqrt, rounded to f32), selects k by (bits, slot) and proves the selection: the sweeps
+//   3. every worker thread owns one query row (its TMEM lane) and one half of the slots and reads that part of the
+//      accumulator twice with tcgen05.ld: a first sweep finds a threshold that at least C = k + 1 slots pass (the C-th
+//      smallest of the minima of v = |p-k|^2 / (1-|k|^2) over groups of 32, 16 or 8 slots, both halves merged), a second
+//      sweep lists the slots under it (about a dozen of 512); the C smallest of the lists are the row's candidates;
+//   4. four threads per row re-score the candidates as `poincare_distance` does (f64 differences squared and summed, f64
+//      log1p form of 2 asinh sqrt, rounded to f32); one thread per row selects k by (bits, slot)
+//      and proves the selection: the sweeps
 //      also produced v_lb, the smallest (approximate v - its error bound) over every slot that did NOT become a candidate,
 //      so the true distance of each of those is at least d(v_lb / (1-|p|^2)); if the k-th selected distance is strictly
-//      below that, no other slot can enter or tie. Otherwise (or if the list overflowed) the row is flagged and a second,
-//      tiny kernel recomputes that row with f64 distances to every slot. Rare: a few rows per million.
+//      below that, no other slot can enter or tie. Otherwise (or if the list overflowed) the row is flagged and the CTA
+//      recomputes it at the end of the tile with f64 distances to every slot. Rare: a few rows per million.
 //   5. softmax over the k selected slots (sum in ascending slot order) and the value read, fused.
 // Every mbarrier wait is bounded like the GEMM pipeline's: on expiry the status word gets PSSA_B200_ERR_TIMEOUT and the
 // kernel stops issuing work and frees its TMEM.
@@ -38,19 +40,24 @@ namespace pssa {
 namespace {
 using namespace tc;
 
-constexpr int kListCap = 48;   // slots a row can list under its threshold (about 20 expected)
-constexpr int kCandMax = 16;   // candidates re-scored per row: top_k + kMargin, at most this many
-constexpr int kMargin = 4;
+constexpr int kListHalf = 32;  // slots one column half of a row can list under its threshold (about 10 expected)
+constexpr int kCandMax = 13;   // candidates re-scored per row: top_k + kMargin, at most this many (the kernel is
+                               // instantiated for 9 and for 13)
+constexpr int kMargin = 1;     // one spare candidate: the proof needs the k-th exact distance strictly under the bound of
+                               // everything that is not a candidate, and the (k+1)-th nearest slot is the usual binder
 constexpr int kWorkWarps = 8;  // warps 2..9; the first four own the 128 TMEM lanes (one query row per thread)
 constexpr int kThreads = 64 + 32 * kWorkWarps;
 constexpr int kStages = 3;
+constexpr int kPhases = kRetrievePhases;
 constexpr int kRingStage = 256 * BK * 2;  // one key k-block of up to 256 slots: 32 KB
-// Error bound of the pre-filter's t = |p - k|^2 = (|p|^2 - p.k) + (|k|^2 - p.k): the tensor-core product p.k (six piece
-// products, fp32 accumulation that is not correctly rounded) is off by at most kEpsDot * |p| |k| (about fifty accumulation
-// steps of 2^-23 relative to sum |p_i k_i| <= |p| |k|; measured below 3.1e-6 |p| |k|, see the tensor-core distance test),
-// and the two fp32 subtractions and the addition by kEpsSum * (|p|^2 + |k|^2).
-constexpr float kEpsDot = 8e-6f;
-constexpr float kEpsSum = 5e-7f;
+// Error bound of the pre-filter's t = |p - k|^2 = (|p|^2 - p.k) + (|k|^2 - p.k). The tensor cores multiply the three piece
+// products above 2^-16 of p.k -- (p0, k0), (p0, k1), (p1, k0) with x = x0 + x1 + x2, |x1| <= 2^-9 |x|, |x2| <= 2^-17 |x| --
+// so the dropped products are at most (2^-18 + 2 * 2^-17) sum |p_i k_i| <= 1.9e-5 |p| |k|, and the fp32 accumulation (not
+// correctly rounded, about two dozen steps of 2^-23) adds at most 3e-6 |p| |k|: kEpsDot * |p| |k| covers both. The two fp32
+// subtractions and the addition are covered by kEpsSum * (|p|^2 + |k|^2). A pre-filter this coarse is enough because its
+// only job is to shortlist; the decision is made on exact distances.
+constexpr float kEpsDot = 3e-5f;
+constexpr float kEpsSum = 8e-7f;
 
 __device__ __forceinline__ void bar_workers() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kWorkWarps) : "memory"); }
 
@@ -101,103 +108,168 @@ __device__ __forceinline__ float project_row(float* row, int dk, bool euclid, fl
     return (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;
 }
 
-// Last stage of a row, shared by the fused kernel and the exact fix-up: the k selected slots arrive in ASCENDING SLOT ORDER
-// (sel_slot / sel_dist in shared memory); weights exp((min - d) / tau) summed in that order (memory.rs:391-398),
-// normalised, value read in that order with separately rounded multiply and add (memory.rs:399-406). LANES threads of a
-// warp work on one row (32: a warp per row; 16: two rows per warp, `hl` the lane within the half); every lane of the warp
-// calls it, `active` says whether its row exists.
-template <int LANES>
-__device__ __forceinline__ void finish_row(const RetrieveParams& p, size_t q, const unsigned* sel_slot, float* sel_w, int k, float dmin,
-                                           int hl, bool active) {
-    const float tau = p.tau;
-    const float my_w = (active && hl < k) ? expf(__fdiv_rn(__fsub_rn(dmin, sel_w[hl]), tau)) : 0.0f;  // sel_w holds distances on entry
+// Last stage of a row of the exact stage, one warp: the k selected slots arrive in ASCENDING SLOT ORDER (sel_slot / sel_w
+// in shared memory, sel_w holding the distances); weights exp((min - d) / tau) summed in that order (memory.rs:391-398),
+// normalised, value read in that order with separately rounded multiply and add (memory.rs:399-406).
+__device__ __forceinline__ void finish_row(const RetrieveParams& p, size_t q, const unsigned* sel_slot, float* sel_w, int k, float dmin, int lane) {
+    const float my_w = lane < k ? expf(__fdiv_rn(__fsub_rn(dmin, sel_w[lane]), p.tau)) : 0.0f;
     __syncwarp();
-    if (active && hl < k) sel_w[hl] = my_w;
+    if (lane < k) sel_w[lane] = my_w;
     __syncwarp();
     float sum = 0.0f;
-    if (active)
-        for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, sel_w[j]);
-    const float wn = active ? __fdiv_rn(my_w, sum) : 0.0f;
+    for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, sel_w[j]);
+    const float wn = __fdiv_rn(my_w, sum);
     __syncwarp();
-    if (active && hl < k) sel_w[hl] = wn;
+    if (lane < k) sel_w[lane] = wn;
     __syncwarp();
-    if (!active) return;  // no warp-wide operation below
-    if (p.min_dist && hl == 0) p.min_dist[q] = dmin;
-    if (p.topk_slots && hl < k) p.topk_slots[q * k + hl] = sel_slot[hl];
-    if (p.topk_weights && hl < k) p.topk_weights[q * k + hl] = wn;
+    if (p.min_dist && lane == 0) p.min_dist[q] = dmin;
+    if (p.topk_slots && lane < k) p.topk_slots[q * k + lane] = sel_slot[lane];
+    if (p.topk_weights && lane < k) p.topk_weights[q * k + lane] = wn;
     if (p.weights) {  // the reference's dense row: zero except the selected slots; every address is written once, by the
                       // lane that owns it, so no ordering between a zero and a weight is needed
         float* row = p.weights + q * p.cap;
-        for (int i = hl; i < p.cap; i += LANES) {
+        for (int i = lane; i < p.cap; i += 32) {
             float w = 0.0f;
             for (int j = 0; j < k; ++j) w = sel_slot[j] == (unsigned)i ? sel_w[j] : w;
             row[i] = w;
         }
     }
     const int dv = p.dv;
-    for (int j0 = hl; j0 < dv; j0 += LANES * 4) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int j = 0; j < k; ++j) {
-            const float wi = sel_w[j];
-            const float* v = p.values + (size_t)sel_slot[j] * dv;
+    for (int c = lane; c < dv; c += 32) {
+        float v[kCandMax - kMargin];  // every selected row's element is requested before the first is used
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int c = j0 + e * LANES;
-                if (c < dv) acc[e] = __fadd_rn(acc[e], __fmul_rn(wi, __ldg(v + c)));
-            }
-        }
+        for (int j = 0; j < kCandMax - kMargin; ++j)
+            if (j < k) v[j] = __ldg(p.values + (size_t)sel_slot[j] * dv + c);
+        float acc = 0.0f;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int c = j0 + e * LANES;
-            if (c < dv) {
-                if (p.m_val) p.m_val[q * dv + c] = acc[e];
-                if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + c] = __float2bfloat16_rn(acc[e]);
-            }
-        }
+        for (int j = 0; j < kCandMax - kMargin; ++j)
+            if (j < k) acc = __fadd_rn(acc, __fmul_rn(sel_w[j], v[j]));
+        if (p.m_val) p.m_val[q * dv + c] = acc;
+        if (p.m_bf16) reinterpret_cast<__nv_bfloat16*>(p.m_bf16)[q * dv + c] = __float2bfloat16_rn(acc);
     }
 }
 
-// lane base + j (j < n) holds (bits, slot): rank of this lane's pair among the n pairs by (bits, slot)
-__device__ __forceinline__ int rank_by_key(unsigned long long key, int n, int base) {
-    int rank = 0;
-    for (int i = 0; i < n; ++i) rank += __shfl_sync(0xffffffffu, key, base + i) < key ? 1 : 0;
-    return rank;
+// The exact stage of the one-kernel read, called by all worker threads with the same arguments: for each flagged row of
+// the tile, f64 distances to EVERY occupied slot, each the reference's sequential sum (src/memory.rs:245-262), then k
+// rounds of a warp-wide minimum over (distance bits, slot) and the row's outputs.
+template <int DK>
+__device__ __noinline__ void exact_rows(const RetrieveParams& p, size_t q0, const unsigned char* smem_a, const float* stat_qs, const int* flag_rows,
+                                        int n_flag, float* fx_p, float* fx_dist, unsigned* fx_slot, float* fx_w, int wtid) {
+    constexpr int KB_PIECE = DK / BK;
+    constexpr uint32_t A_BLOCK = BM * BK * 2;
+    const int lane = wtid & 31, wid = wtid >> 5, count = p.count, k = p.top_k;
+    for (int f = 0; f < n_flag; ++f) {
+        const int r = flag_rows[f];
+        if (wtid < DK) {  // the projected point from its pieces
+            const int c = wtid;
+            const uint32_t off = sw128_offset(r, c % BK);
+            const int kb = c / BK;
+            const float x0 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off));
+            const float x1 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off));
+            const float x2 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off));
+            fx_p[c] = x0 + (x1 + x2);
+        }
+        bar_workers();
+        const double one_minus_q = 1.0 - (double)stat_qs[r];
+        for (int s = wtid; s < count; s += 2 * 32 * kWorkWarps) {  // two slots per pass: two independent f64 chains
+            const int s2 = min(s + 32 * kWorkWarps, count - 1);      // (the last pass may compute a slot twice)
+            const float4* ka = reinterpret_cast<const float4*>(p.keys + (size_t)s * DK);
+            const float4* kb = reinterpret_cast<const float4*>(p.keys + (size_t)s2 * DK);
+            double sa = 0.0, sb = 0.0;
+            for (int i = 0; i < DK / 4; ++i) {
+                const float4 a = __ldg(ka + i), b = __ldg(kb + i);
+                const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const double pe = (double)fx_p[4 * i + e];
+                    const double da = pe - (double)av[e], db = pe - (double)bv[e];
+                    sa = fma(da, da, sa), sb = fma(db, db, sb);
+                }
+            }
+            const float d_a = exact_distance(sa, one_minus_q, __ldg(p.norm_sq + s));
+            const float d_b = exact_distance(sb, one_minus_q, __ldg(p.norm_sq + s2));
+            fx_dist[s] = d_a;
+            fx_dist[s2] = d_b;
+        }
+        bar_workers();
+        if (wid == 0) {
+            unsigned my_slot = 0xffffffffu;
+            float my_dist = 0.0f, dmin = 0.0f;
+            for (int round = 0; round < k; ++round) {
+                unsigned long long local = ~0ull;
+                for (int s = lane; s < count; s += 32) {
+                    const unsigned bits = __float_as_uint(fx_dist[s]);
+                    if (bits & 0x80000000u) continue;  // taken (distances are >= +0)
+                    local = umin64(local, ((unsigned long long)bits << 32) | (unsigned)s);
+                }
+#pragma unroll
+                for (int m = 16; m > 0; m >>= 1) local = umin64(local, __shfl_xor_sync(0xffffffffu, local, m));
+                const unsigned slot = (unsigned)(local & 0xffffffffu);
+                const float d = __uint_as_float((unsigned)(local >> 32));
+                if (lane == 0) fx_dist[slot] = __uint_as_float(__float_as_uint(d) | 0x80000000u);
+                if (lane == round) my_slot = slot, my_dist = d;
+                if (round == 0) dmin = d;
+                __syncwarp();
+            }
+            int srank = 0;
+            for (int i = 0; i < k; ++i) srank += __shfl_sync(0xffffffffu, my_slot, i) < my_slot ? 1 : 0;
+            if (lane < k) fx_slot[srank] = my_slot, fx_w[srank] = my_dist;
+            __syncwarp();
+            finish_row(p, q0 + r, fx_slot, fx_w, k, dmin, lane);
+            if (lane == 0) atomicAdd(p.fixup_count, 1u);
+        }
+        bar_workers();
+    }
 }
 
-template <int DK>
+template <int DK, int NC>
 __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const __grid_constant__ CUtensorMap map_b, RetrieveParams p) {
     constexpr int KB_PIECE = DK / BK;        // k-blocks per bf16 piece
     constexpr int KB_A = 3 * KB_PIECE;       // k-blocks of the A operand (three pieces)
     constexpr uint32_t A_BLOCK = BM * BK * 2;  // 16 KB
     constexpr int PITCH = DK + 1;            // staging pitch in floats (bank spreading for one-thread-per-row walks)
-    constexpr int EPL = DK / 16;             // key dimensions per lane in the re-scoring (16 lanes per row)
+    constexpr int L = DK / 16;               // lanes that share one row's exact sums (four float4 groups each)
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* smem_a = smem;                         // [KB_A][128 x 64 bf16], swizzled
-    unsigned char* ring = smem_a + KB_A * A_BLOCK;        // [kStages][<=256 x 64 bf16]; between tiles: staging, then the lists
-    float* staging = reinterpret_cast<float*>(ring);      // [128][PITCH] raw queries, then the projected points
-    float* list_v = reinterpret_cast<float*>(ring);       // [kListCap][128]
-    unsigned short* list_s = reinterpret_cast<unsigned short*>(list_v + kListCap * BM);  // [kListCap][128]
+    unsigned char* ring = smem_a + KB_A * A_BLOCK;        // [kStages][<=256 x 64 bf16] while the tensor cores run; otherwise:
+    float* staging = reinterpret_cast<float*>(ring);      //   P0-P2: [128][PITCH] raw queries, then the projected points
+    float* xbest = reinterpret_cast<float*>(ring);        //   P3: [2][NC][128] each column half's smallest group minima
+    uint2* list_e = reinterpret_cast<uint2*>(xbest + 2 * NC * BM);  // P3-P4: [2][kListHalf + 1][128] listed (v bits, slot); the last row
+                                                          //   takes the stores of slots that are not listed: no branch in the sweep
+    double* sqbuf = reinterpret_cast<double*>(ring);      //   P5: [128][NC] exact squared distances of the candidates (f64)
+    float* d32 = reinterpret_cast<float*>(sqbuf + BM * NC);  // P5: [128][NC + 1] exact distances of the candidates
+    float* selw = d32 + BM * (NC + 1);                    //   P5: [128][NC] weights of the selected slots, ascending slot order
+    unsigned* sels = reinterpret_cast<unsigned*>(selw + BM * NC);  // P5: [128][NC] the selected slots
+    float* fx_p = reinterpret_cast<float*>(sels + BM * NC);       //   P5e: [DK] a flagged row's point
+    float* fx_dist = fx_p + DK;                                   //   P5e: [512] its distance to every slot
+    unsigned* fx_slot = reinterpret_cast<unsigned*>(fx_dist + 512);  // P5e: [32] selected slots, ascending
+    float* fx_w = reinterpret_cast<float*>(fx_slot + 32);         //   P5e: [32] their distances, then weights
+    int* flag_rows = reinterpret_cast<int*>(fx_w + 32);           //   P5c-P5e: [128] rows of the tile whose selection is not proven
+    int* flag_count = flag_rows + BM;                             //   and how many
     unsigned char* tail = ring + kStages * kRingStage;
-    float2* kstat_s = reinterpret_cast<float2*>(tail);                     // [cap <= 512]
-    float* stat_qs = reinterpret_cast<float*>(kstat_s + 512);              // [128] |p|^2
-    float* stat_vc = stat_qs + BM;                                         // [128] lower bound of the true v of every non-candidate
-    int* stat_cnt = reinterpret_cast<int*>(stat_vc + BM);                  // [128] listed slots (> kListCap: overflow)
-    float* knorm_s = reinterpret_cast<float*>(stat_cnt + BM);              // [cap <= 512] |k|
-    unsigned short* cand_slot = reinterpret_cast<unsigned short*>(knorm_s + 512);  // [128][kCandMax]
-    unsigned* sel_slot_s = reinterpret_cast<unsigned*>(cand_slot + BM * kCandMax);  // [kWorkWarps][32]
-    float* sel_w_s = reinterpret_cast<float*>(sel_slot_s + kWorkWarps * 32);        // [kWorkWarps][32]
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sel_w_s + kWorkWarps * 32);
+    float2* kcol_s = reinterpret_cast<float2*>(tail);                      // [cap <= 512] per-slot constants (|k|^2, 1/(1-|k|^2)), see below
+    float* kerr_s = reinterpret_cast<float*>(kcol_s + 512);                // [cap <= 512] kEpsDot |k| / (1-|k|^2)
+    float* stat_qs = kerr_s + 512;                                         // [128] |p|^2
+    float* stat_excl = stat_qs + BM;                                       // [2][128] lower bound of the true v of: the unlisted slots; every non-candidate
+    int* stat_cnt = reinterpret_cast<int*>(stat_excl + 2 * BM);            // [2][128] listed slots per column half
+    unsigned* stat_dlb = reinterpret_cast<unsigned*>(stat_cnt + 2 * BM);   // [128] bits of the distance no non-candidate can be under
+    unsigned* stat_mark = stat_dlb + BM;                                   // [128] 1 = the row's candidates are re-scored; 0 = handed over (or past the end)
+    int* row_ok = reinterpret_cast<int*>(stat_mark + BM);                  // [128] 1 = selection proven, results in selw / sels
+    unsigned short* cand_slot = reinterpret_cast<unsigned short*>(row_ok + BM);  // [128][kCandMax]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(cand_slot + BM * kCandMax);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* a_ready = empty_bar + kStages;
     uint64_t* acc_full = a_ready + 1;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    long long* phase_clk = reinterpret_cast<long long*>(acc_full + 1);  // [kPhases]
+    int* kmax_i = reinterpret_cast<int*>(phase_clk + kPhases);          // [4] maxima over the occupied slots of kcol_s .w, .y, .x (floats >= 0)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kmax_i + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int dk = DK, cap = p.cap, count = p.count, k = p.top_k;
     const int nh = cap >= 256 ? 256 : cap;   // slots per MMA (N) and per TMA box
     const int halves = cap / nh;
-    const int n_cand = min(k + kMargin, kCandMax);
+    const int n_cand = min(k + kMargin, NC);
     // columns per group minimum: 32 when that leaves enough fully occupied groups to bound n_cand slots (plus two to
     // keep the bound tight), else 16 or 8; smaller groups give a lower threshold and shorter lists but more insertions
     int group = 32;
@@ -211,14 +283,30 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (threadIdx.x < 4) kmax_i[threadIdx.x] = 0;
+    __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < cap; i += kThreads) {
-        const float2 ks = p.k_stat[i];
-        kstat_s[i] = ks;
-        knorm_s[i] = sqrtf(ks.x) * 1.0000002f;  // rounded up: it scales an error bound
+    // Per slot, with n = |k|^2 and s = 1 / (1 - n) from the upload: for a row with |p|^2 = q and accumulator a = p.k the
+    // pre-filter value is v = (q + n - 2 a) s, computed as fma(-2, a, q + n) * s: nothing is rounded at a size above
+    // (q + n) s, which kEpsSum covers; its error bound is (kEpsDot |p| |k| + kEpsSum (q + n)) s. Slots past `count` get
+    // n = 3e38, s = 1: v = 3e38, never listed. The maxima of the error-bound terms over the occupied slots give a bound
+    // that holds for EVERY slot of a row.
+    {
+        float m_e = 0.0f, m_s = 0.0f, m_ns = 0.0f;
+        for (int i = threadIdx.x; i < cap; i += kThreads) {
+            const float2 ks = p.k_stat[i];
+            const float kn = sqrtf(ks.x) * 1.0000002f;  // rounded up: it scales an error bound
+            const float e = kEpsDot * kn * ks.y * 1.0000002f;
+            kcol_s[i] = i < count ? ks : make_float2(3.0e38f, 1.0f);
+            kerr_s[i] = i < count ? e : 0.0f;
+            if (i < count) m_e = fmaxf(m_e, e), m_s = fmaxf(m_s, ks.y), m_ns = fmaxf(m_ns, ks.x * ks.y * 1.0000002f);
+        }
+        atomicMax(&kmax_i[0], __float_as_int(m_e));  // non-negative floats order like their bits
+        atomicMax(&kmax_i[1], __float_as_int(m_s));
+        atomicMax(&kmax_i[2], __float_as_int(m_ns));
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -227,8 +315,9 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
     pdl_trigger();
     pdl_wait();
 
-    const unsigned char pair_a[6] = {0, 0, 1, 0, 1, 2}, pair_b[6] = {0, 1, 0, 2, 1, 0};
-    const int n_kb = 6 * KB_PIECE;  // k-blocks per half
+    // Stages per half: every k-block of key piece 0, then of key piece 1. A stage of piece 0 is multiplied with point
+    // pieces 0 and 1, a stage of piece 1 with point piece 0: three products from two loads.
+    const int n_kb = 2 * KB_PIECE;
 
     if (warp == 0) {
         // ---------------- producer: key pieces through the ring, after the workers have released it for this tile
@@ -250,8 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                             break;
                         }
                         mbar_expect_tx(&full_bar[s], (uint32_t)nh * BK * 2);
-                        const int pair = kb / KB_PIECE, within = kb % KB_PIECE;
-                        tma_load_2d(ring + s * kRingStage, &map_b, &full_bar[s], (pair_b[pair] * KB_PIECE + within) * BK, h * nh);
+                        tma_load_2d(ring + s * kRingStage, &map_b, &full_bar[s], kb * BK, h * nh);  // piece kb / KB_PIECE, block kb % KB_PIECE
                     }
             }
         }
@@ -276,12 +364,14 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                             break;
                         }
                         tcgen05_fence_after();
-                        const int pair = kb / KB_PIECE, within = kb % KB_PIECE;
-                        const uint64_t da = umma_desc_sw128(smem_u32(smem_a + (pair_a[pair] * KB_PIECE + within) * A_BLOCK));
+                        const int key_piece = kb / KB_PIECE, within = kb % KB_PIECE;
                         const uint64_t db = umma_desc_sw128(smem_u32(ring + s * kRingStage));
+                        for (int a = 0; a < (key_piece == 0 ? 2 : 1); ++a) {
+                            const uint64_t da = umma_desc_sw128(smem_u32(smem_a + (a * KB_PIECE + within) * A_BLOCK));
 #pragma unroll
-                        for (int kk = 0; kk < BK / UMMA_K; ++kk)
-                            tcgen05_mma_bf16(tmem_base + h * nh, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                            for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                                tcgen05_mma_bf16(tmem_base + h * nh, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || a > 0 || kk > 0) ? 1u : 0u);
+                        }
                         tcgen05_commit(&empty_bar[s]);
                     }
                 tcgen05_commit(acc_full);  // all products of this tile are in TMEM (or abandoned)
@@ -291,19 +381,20 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
         // ---------------- workers
         const int wid = warp - 2;                 // 0..7
         const int wtid = threadIdx.x - 64;        // 0..255
-        const bool row_warp = wid < 4;            // warps 2..5 own TMEM lane quadrants 2, 3, 0, 1
         const int my_row = (warp & 3) * 32 + lane;
         const bool vec_q = (((p.ldq ? p.ldq : (size_t)dk) & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0);
         uint32_t it = 0;
         bool alive = true;
-        long long clk[6] = {0, 0, 0, 0, 0, 0};
+        if (wtid < kPhases) phase_clk[wtid] = 0;  // (ordered before the first lap by the first worker barrier)
         for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
             const size_t q0 = (size_t)tile * BM;
             const size_t ldq = p.ldq ? p.ldq : (size_t)dk;
             long long t_prev = clock64();
-            auto lap = [&](int i) {
-                const long long now = clock64();
-                clk[i] += now - t_prev, t_prev = now;
+            auto lap = [&](int i) {  // one thread's view of the phases; in shared memory to keep registers free
+                if (wtid == 0) {
+                    const long long now = clock64();
+                    phase_clk[i] += now - t_prev, t_prev = now;
+                }
             };
             // ---- P0: the tile's raw queries, coalesced, into the staging rows
             if (vec_q) {
@@ -352,256 +443,377 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             bar_workers();
             if (wtid == 0) mbar_arrive(a_ready);  // releases the ring to the producer and the operand to the issuer
             lap(2);
-            // ---- P3: two sweeps over the accumulator row (row warps only)
-            if (row_warp) {
-                if (alive) {  // every lane waits (each needs the barrier's acquire); the verdict is made warp-uniform
-                    const bool ok = mbar_wait(acc_full, it & 1);
-                    alive = __all_sync(0xffffffffu, ok);
-                    if (!alive && lane == 0) atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
-                }
-                tcgen05_fence_after();
-                lap(3);  // waiting for the tensor cores
-                const float qs = stat_qs[my_row];
-                const float pn = sqrtf(qs) * 1.0000002f;
-                float excl = CUDART_INF_F;  // smallest lower bound of the true v over the slots that do not become candidates
-                const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-                float best[kCandMax];
-#pragma unroll
-                for (int i = 0; i < kCandMax; ++i) best[i] = CUDART_INF_F;
-                int cnt = 0;
-                float theta = CUDART_INF_F;
-                for (int sweep = 0; sweep < 2 && alive; ++sweep) {
-                    for (int c0 = 0; c0 < cap; c0 += 32) {
-                        float acc[32];
-                        tcgen05_ld_32x32(taddr + c0, acc);
-                        float gmin = CUDART_INF_F;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int col = c0 + j;
-                            const float2 ks = kstat_s[col];
-                            // |p - k|^2 = (|p|^2 - p.k) + (|k|^2 - p.k): nothing rounded at the size of the norms
-                            float v = fmaxf(((qs - acc[j]) + (ks.x - acc[j])) * ks.y, 0.0f);
-                            v = col < count ? v : CUDART_INF_F;
-                            if (sweep == 0) {
-                                gmin = fminf(gmin, v);
-                                if (((j + 1) & (group - 1)) == 0) {  // end of a group: keep the kCandMax smallest group minima, sorted
-                                    float x = gmin;
-#pragma unroll
-                                    for (int i = 0; i < kCandMax; ++i) {
-                                        const float lo = fminf(best[i], x), hi = fmaxf(best[i], x);
-                                        best[i] = lo, x = hi;
-                                    }
-                                    gmin = CUDART_INF_F;
-                                }
-                            } else if (v <= theta) {
-                                if (cnt < kListCap) list_v[cnt * BM + my_row] = v, list_s[cnt * BM + my_row] = (unsigned short)col;
-                                ++cnt;
-                            } else {
-                                // not listed: v minus its own error bound (both scaled by 1/(1-|k|^2))
-                                const float err = fmaf(kEpsDot * pn, knorm_s[col], kEpsSum * (qs + ks.x));
-                                excl = fminf(excl, fmaf(-err, ks.y, v));
-                            }
-                        }
-                    }
-                    if (sweep == 0) {
-#pragma unroll
-                        for (int i = 0; i < kCandMax; ++i)
-                            if (i == n_cand - 1) theta = best[i];  // at least n_cand slots (one per group) lie at or under it
-                    }
-                }
-                tcgen05_fence_before();
-                // ---- P4: the n_cand smallest of the list by (v, slot), sorted
-                unsigned long long top[kCandMax];
-#pragma unroll
-                for (int i = 0; i < kCandMax; ++i) top[i] = ~0ull;
-                const int n_list = min(cnt, kListCap);
-                for (int e = 0; e < n_list; ++e) {
-                    unsigned long long x = ((unsigned long long)__float_as_uint(list_v[e * BM + my_row]) << 32) | list_s[e * BM + my_row];
-#pragma unroll
-                    for (int i = 0; i < kCandMax; ++i) {
-                        if (i < n_cand) {  // entries past the candidates stay empty: what falls out of the first n_cand is excluded
-                            const unsigned long long lo = umin64(top[i], x), hi = umax64(top[i], x);
-                            top[i] = lo, x = hi;
-                        }
-                    }
-                    if (x != ~0ull) {  // a listed slot that is not (or no longer) a candidate
-                        const unsigned slot = (unsigned)(x & 0xffffu);
-                        const float2 ks = kstat_s[slot];
-                        const float err = fmaf(kEpsDot * pn, knorm_s[slot], kEpsSum * (qs + ks.x));
-                        excl = fminf(excl, fmaf(-err, ks.y, __uint_as_float((unsigned)(x >> 32))));
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < kCandMax; ++i) cand_slot[my_row * kCandMax + i] = (unsigned short)(top[i] & 0xffffu);
-                stat_vc[my_row] = excl;
-                stat_cnt[my_row] = alive ? cnt : kListCap + 1;
+            // ---- P3: two sweeps over the accumulator. All eight warps: a thread owns one query row (its TMEM lane) and one
+            // half of the slots (columns): warps 2..5 the lower half, warps 6..9 the upper.
+            const int ch = wid >> 2;
+            const int c_begin = ch * (cap / 2), c_end = c_begin + cap / 2;
+            if (alive) {  // every lane waits (each needs the barrier's acquire); the verdict is made warp-uniform
+                const bool ok = mbar_wait(acc_full, it & 1);
+                alive = __all_sync(0xffffffffu, ok);
+                if (!alive && lane == 0) atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
             }
+            tcgen05_fence_after();
+            lap(3);  // waiting for the tensor cores
+            const float qs = stat_qs[my_row];
+            const float pn = sqrtf(qs) * 1.0000002f;
+            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            float best[NC];
+#pragma unroll
+            for (int i = 0; i < NC; ++i) best[i] = CUDART_INF_F;
+            auto insert_best = [&](float x) {  // keep the NC smallest, sorted; branch-free
+#pragma unroll
+                for (int i = 0; i < NC; ++i) {
+                    const float lo = fminf(best[i], x), hi = fmaxf(best[i], x);
+                    best[i] = lo, x = hi;
+                }
+            };
+            // both sweeps read 32 columns per tcgen05.ld into one of two register buffers, the next load in flight while
+            // the current buffer is used
+            uint32_t buf0[32], buf1[32];
+            if (alive) {
+                // sweep 1: group minima
+                auto minima = [&](const uint32_t (&acc)[32], int c0) {
+                    float vmin[4] = {CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, CUDART_INF_F};  // minima of the four groups of 8 columns
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float2 kc = kcol_s[c0 + j];
+                        vmin[j >> 3] = fminf(vmin[j >> 3], fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y);
+                    }
+                    if (group == 32) {
+                        insert_best(fminf(fminf(vmin[0], vmin[1]), fminf(vmin[2], vmin[3])));
+                    } else if (group == 16) {
+                        insert_best(fminf(vmin[0], vmin[1]));
+                        insert_best(fminf(vmin[2], vmin[3]));
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) insert_best(vmin[g]);
+                    }
+                };
+                tcgen05_ld_32x32_issue(taddr + c_begin, buf0);
+                for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                    tcgen05_wait_ld(buf0);
+                    tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
+                    minima(buf0, c0);
+                    tcgen05_wait_ld(buf1);
+                    tcgen05_ld_32x32_issue(taddr + (c0 + 64 < c_end ? c0 + 64 : c_begin), buf0);  // wraps to the second sweep's first columns
+                    minima(buf1, c0 + 32);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < NC; ++i) xbest[(ch * NC + i) * BM + my_row] = best[i];
             bar_workers();
             lap(4);
-            // ---- P5: half a warp per row (two rows per warp in flight): exact re-scoring, selection, proof, softmax, value read
+            // the threshold: the n_cand-th smallest group minimum over BOTH halves (at least n_cand slots lie at or under it)
             {
-                const int half = lane >> 4, hl = lane & 15, base = lane & 16;
-                unsigned* sel_slot = sel_slot_s + wid * 32 + half * 16;
-                float* sel_w = sel_w_s + wid * 32 + half * 16;
-                for (int rb = wid * 2; rb < BM; rb += kWorkWarps * 2) {
-                    const int r = rb + half;
-                    const size_t q = q0 + r;
-                    const bool exists = q < p.rows;
-                    // a list overflow (or an abandoned accumulator) leaves no candidates to trust
-                    const bool trusted = exists && stat_cnt[r] <= kListCap;
-                    // the projected point from its three pieces (their sum is exact); lane hl owns dimensions hl + 16 e
-                    float pf[EPL];
+                const int other = 1 - ch;
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) {
-                        const int c = hl + 16 * e;
-                        const uint32_t off = sw128_offset(r, c % BK);
-                        const int kb = c / BK;
-                        const float x0 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off));
-                        const float x1 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off));
-                        const float x2 = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off));
-                        pf[e] = x0 + (x1 + x2);
-                    }
-                    double part[kCandMax];
+                for (int i = 0; i < NC; ++i) insert_best(xbest[(other * NC + i) * BM + my_row]);
+            }
+            float theta = CUDART_INF_F;
 #pragma unroll
-                    for (int j = 0; j < kCandMax; ++j) {
-                        part[j] = 0.0;
-                        if (j < n_cand && trusted) {
-                            const float* krow = p.keys + (size_t)cand_slot[r * kCandMax + j] * dk;
+            for (int i = 0; i < NC; ++i)
+                if (i == n_cand - 1) theta = best[i];
+            // e_cap bounds the pre-filter error of EVERY slot of this row. Slots up to theta + 2.5 e_cap are listed, so an
+            // unlisted slot's true v is above theta + 1.5 e_cap; theta + e_cap (rounded) is the bound that goes on.
+            const float e_cap = fmaf(pn, __int_as_float(kmax_i[0]), kEpsSum * fmaf(qs, __int_as_float(kmax_i[1]), __int_as_float(kmax_i[2]))) * 1.000001f;
+            const float t2 = fmaf(2.5f, e_cap, theta);
+            if (ch == 0) stat_excl[my_row] = theta + e_cap;
+            lap(5);
+            int cnt = 0;
+            if (alive) {
+                uint2* my_list = list_e + (size_t)ch * (kListHalf + 1) * BM + my_row;
+                // sweep 2: list the slots at or under the widened threshold. Every column stores: a listed slot at the list's
+                // end, the others (and what overflows the list) into the spare row.
+                auto listing = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
-                            for (int e = 0; e < EPL; ++e) {
-                                const double df = (double)pf[e] - (double)__ldg(krow + hl + 16 * e);
-                                part[j] = fma(df, df, part[j]);
-                            }
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const float2 kc = kcol_s[c0 + j];
+                        const float v = fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y;
+                        const bool listed = v <= t2;
+                        const int pos = listed ? min(cnt, kListHalf) : kListHalf;
+                        my_list[pos * BM] = make_uint2(__float_as_uint(v), (unsigned)(c0 + j));
+                        cnt += listed ? 1 : 0;
                     }
-                    // transpose-reduce over the 16 lanes of the half: after the four steps lane hl holds the full sum of candidate hl
-#pragma unroll
-                    for (int n = 8, mask = 8; n >= 1; n >>= 1, mask >>= 1) {
-                        const bool upper = (lane & mask) != 0;
-#pragma unroll
-                        for (int i = 0; i < n; ++i) {
-                            const double send = upper ? part[i] : part[i + n];
-                            const double keep = upper ? part[i + n] : part[i];
-                            part[i] = keep + __shfl_xor_sync(0xffffffffu, send, mask);
-                        }
-                    }
-                    const double one_minus_q = 1.0 - (double)stat_qs[r];
-                    const bool has = trusted && hl < n_cand;
-                    float d_j = CUDART_INF_F;
-                    unsigned slot_j = 0xffffu;
-                    if (has) {
-                        slot_j = cand_slot[r * kCandMax + hl];
-                        d_j = exact_distance(part[0], one_minus_q, __ldg(p.norm_sq + slot_j));
-                    }
-                    const unsigned long long key = has ? (((unsigned long long)__float_as_uint(d_j) << 32) | slot_j) : ~0ull;
-                    const int rank = rank_by_key(key, n_cand, base);
-                    const bool selected = has && rank < k;
-                    // the largest selected distance and the smallest of all, within the half
-                    unsigned kth_bits = selected ? __float_as_uint(d_j) : 0u;
-                    unsigned min_bits = has ? __float_as_uint(d_j) : 0xffffffffu;
-#pragma unroll
-                    for (int mk = 8; mk > 0; mk >>= 1) {
-                        kth_bits = max(kth_bits, __shfl_xor_sync(0xffffffffu, kth_bits, mk));
-                        min_bits = min(min_bits, __shfl_xor_sync(0xffffffffu, min_bits, mk));
-                    }
-                    // proof that no slot outside the candidate set can enter or tie
-                    int decisive = 0;
-                    if (hl == 0 && exists) {
-                        if (trusted) {
-                            // every slot outside the candidate set has a true v of at least this (1 - 4e-7: the f32 rounding of v itself)
-                            const double v_lb = (double)stat_vc[r] * (1.0 - 4e-7);
-                            if (v_lb > 0.0) {
-                                const double u_lb = v_lb / one_minus_q;
-                                const float d_lb = (float)log1p(2.0 * u_lb + 2.0 * sqrt(fma(u_lb, u_lb, u_lb)));
-                                decisive = kth_bits < __float_as_uint(d_lb);
-                            }
-                            if (p.selftest_every > 0 && q % (size_t)p.selftest_every == 0) decisive = 0;
-                        }
-                        if (!decisive) p.fixup_list[atomicAdd(p.fixup_count, 1u)] = (unsigned)q;  // the exact pass writes this row
-                    }
-                    decisive = __shfl_sync(0xffffffffu, decisive, base);
-                    // ascending slot order among the selected
-                    int srank = 0;
-                    for (int i = 0; i < n_cand; ++i) {
-                        const unsigned other_slot = __shfl_sync(0xffffffffu, slot_j, base + i);
-                        const bool other_sel = __shfl_sync(0xffffffffu, selected ? 1 : 0, base + i) != 0;
-                        srank += (other_sel && other_slot < slot_j) ? 1 : 0;
-                    }
-                    __syncwarp();
-                    if (selected && decisive) sel_slot[srank] = slot_j, sel_w[srank] = d_j;
-                    __syncwarp();
-                    finish_row<16>(p, q, sel_slot, sel_w, k, __uint_as_float(min_bits), hl, decisive != 0);
-                    __syncwarp();
+                };
+                for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                    tcgen05_wait_ld(buf0);
+                    tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
+                    listing(buf0, c0);
+                    tcgen05_wait_ld(buf1);
+                    if (c0 + 64 < c_end) tcgen05_ld_32x32_issue(taddr + c0 + 64, buf0);
+                    listing(buf1, c0 + 32);
                 }
             }
+            tcgen05_fence_before();
+            stat_cnt[ch * BM + my_row] = alive ? cnt : kListHalf + 1;
+            bar_workers();
+            lap(6);
+            // ---- P4: one thread per row: the n_cand smallest of the two lists by (v, slot) and the lower bound of the true v
+            // of everything else
+            if (wtid < BM) {
+                const int r = wtid;
+                const float qs_r = stat_qs[r];
+                const float pn_r = sqrtf(qs_r) * 1.0000002f;
+                float excl_r = stat_excl[r];
+                const int cnt0 = stat_cnt[r], cnt1 = stat_cnt[BM + r];
+                const bool trusted = cnt0 <= kListHalf && cnt1 <= kListHalf;
+                // keys (v bits, slot): v >= -tiny; a value rounded below zero sorts by its magnitude, still among the smallest
+                unsigned long long top[NC];
+#pragma unroll
+                for (int i = 0; i < NC; ++i) top[i] = ~0ull;
+                for (int h = 0; h < 2; ++h) {
+                    const int n_list = min(h == 0 ? cnt0 : cnt1, kListHalf);
+                    for (int e = 0; e < n_list; ++e) {
+                        const uint2 le = list_e[(h * (kListHalf + 1) + e) * BM + r];
+                        unsigned long long x = ((unsigned long long)(le.x & 0x7fffffffu) << 32) | le.y;
+#pragma unroll
+                        for (int i = 0; i < NC; ++i) {
+                            if (i < n_cand) {  // entries past the candidates stay empty: what falls out of the first n_cand is excluded
+                                const unsigned long long lo = umin64(top[i], x), hi = umax64(top[i], x);
+                                top[i] = lo, x = hi;
+                            }
+                        }
+                        if (x != ~0ull) {  // a listed slot that is not (or no longer) a candidate: v minus its own error bound
+                            const unsigned slot = (unsigned)(x & 0xffffu);
+                            const float2 kc = kcol_s[slot];
+                            const float w = (qs_r + kc.x) * kc.y * 1.0000002f;
+                            excl_r = fminf(excl_r, fmaf(-pn_r, kerr_s[slot], fmaf(-kEpsSum, w, __uint_as_float((unsigned)(x >> 32)))));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < NC; ++i) cand_slot[r * kCandMax + i] = (unsigned short)(top[i] & 0xffffu);
+                stat_excl[BM + r] = excl_r;
+                // untrusted (a list overflowed), nothing to bound with, or past the end: no re-scoring; P5c hands the row over
+                stat_mark[r] = (trusted && excl_r > 0.0f && q0 + r < p.rows) ? 1u : 0u;
+            }
+            bar_workers();  // the lists are consumed: their memory becomes the exact stage's
+            if (wtid == 0) *flag_count = 0;  // (ordered before P5c's increments by the barriers in between)
+            lap(7);
+            // the next tile's queries towards the L2 while this tile is finished
+            {
+                const long long next = tile + gridDim.x;
+                if (next < n_tiles) {
+                    constexpr int LPR = DK * 4 / 128;  // 128-byte lines per row
+                    for (int idx = wtid; idx < BM * LPR; idx += 32 * kWorkWarps) {
+                        const size_t r = (size_t)next * BM + idx / LPR;
+                        if (r < p.rows) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q + r * ldq + (idx % LPR) * 32));
+                    }
+                }
+            }
+            // ---- P5a: exact squared distances, L = DK/16 lanes per row: lane g of a row holds the coordinates 4 (L s + g) .. + 3
+            // (s = 0..3) of the projected point as f64 -- the sum of the three bf16 pieces is the fp32 point, exactly -- and walks
+            // the row's candidates with the next two candidates' keys in flight: f64 differences to the key, squared and summed in
+            // four partial sums that are combined in a fixed order within the lane and then across the L lanes. Like the
+            // separate f64 kernel's fused multiply-adds this differs from the reference's one sequential sum only in the last
+            // bits of an f64 that is then rounded to f32. Conversions to f64 are the slow instructions here: the point is
+            // converted once per row.
+            for (int item = wtid; item < BM * L; item += 32 * kWorkWarps) {
+                const int r = item / L, g = item % L;
+                const bool active = stat_mark[r] != 0u;  // uniform over the lanes of a row
+                double pd[4][4];
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const int c = 4 * (L * s + g);
+                    const uint32_t off = sw128_offset(r, c % BK);
+                    const int kb = c / BK;
+                    const uint2 x0 = *reinterpret_cast<const uint2*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off);
+                    const uint2 x1 = *reinterpret_cast<const uint2*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off);
+                    const uint2 x2 = *reinterpret_cast<const uint2*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off);
+                    // a bf16 is the upper half of its fp32
+                    pd[s][0] = (double)(__uint_as_float(x0.x << 16) + (__uint_as_float(x1.x << 16) + __uint_as_float(x2.x << 16)));
+                    pd[s][1] = (double)(__uint_as_float(x0.x & 0xffff0000u) + (__uint_as_float(x1.x & 0xffff0000u) + __uint_as_float(x2.x & 0xffff0000u)));
+                    pd[s][2] = (double)(__uint_as_float(x0.y << 16) + (__uint_as_float(x1.y << 16) + __uint_as_float(x2.y << 16)));
+                    pd[s][3] = (double)(__uint_as_float(x0.y & 0xffff0000u) + (__uint_as_float(x1.y & 0xffff0000u) + __uint_as_float(x2.y & 0xffff0000u)));
+                }
+                const unsigned short* cs = cand_slot + r * kCandMax;
+                float4 kv[3][4];  // a ring of three keys: two in flight ahead of the one in use
+                auto fetch = [&](int j, float4 (&dst)[4]) {
+                    const float4* krow = reinterpret_cast<const float4*>(p.keys + (size_t)cs[j] * dk) + g;
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) dst[s] = __ldg(krow + L * s);
+                };
+                double tot[NC];
+                if (active) {
+                    fetch(0, kv[0]);
+                    if (1 < n_cand) fetch(1, kv[1]);
+                }
+#pragma unroll
+                for (int j = 0; j < NC; ++j) {
+                    tot[j] = 0.0;
+                    if (active && j < n_cand) {
+                        if (j + 2 < n_cand) fetch(j + 2, kv[(j + 2) % 3]);
+                        double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            const float4 kk = kv[j % 3][s];
+                            const double d0 = pd[s][0] - (double)kk.x, d1 = pd[s][1] - (double)kk.y;
+                            const double d2 = pd[s][2] - (double)kk.z, d3 = pd[s][3] - (double)kk.w;
+                            s0 = fma(d0, d0, s0), s1 = fma(d1, d1, s1), s2 = fma(d2, d2, s2), s3 = fma(d3, d3, s3);
+                        }
+                        tot[j] = (s0 + s1) + (s2 + s3);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NC; ++j) {
+                    if (j < n_cand) {  // uniform over the warp
+                        double t = tot[j];
+#pragma unroll
+                        for (int m = 1; m < L; m <<= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+                        if (g == 0) sqbuf[r * NC + j] = t;
+                    }
+                }
+            }
+            bar_workers();
+            lap(8);
+            // ---- P5b: one thread per (row, candidate), three at a time (f64 latency): the distance from the squared distance as
+            // `poincare_distance` computes it (f64 log1p form of 2 asinh sqrt, rounded to f32). Item n_cand of a row is the
+            // bound: every non-candidate has a true v of at least excl (1 - 4e-7: the f32 rounding of v itself), so its
+            // distance is at least d(v_lb / (1 - |p|^2)); the selection is proven when its largest distance is strictly smaller.
+            {
+                const int per_row = n_cand + 1, n_items = BM * per_row;
+                auto item_distance = [&](int t) {
+                    const int r = t / per_row, j = t - r * per_row;
+                    const bool bound = j == n_cand;
+                    const double sq = bound ? (double)stat_excl[BM + r] * (1.0 - 4e-7) : sqbuf[r * NC + j];
+                    const float ns = bound ? 0.0f : __ldg(p.norm_sq + cand_slot[r * kCandMax + j]);
+                    return exact_distance(sq, 1.0 - (double)stat_qs[r], ns);
+                };
+                auto item_store = [&](int t, float d) {
+                    const int r = t / per_row, j = t - r * per_row;
+                    if (j == n_cand)
+                        stat_dlb[r] = __float_as_uint(d);
+                    else
+                        d32[r * (NC + 1) + j] = d;
+                };
+                for (int t = wtid; t < n_items; t += 3 * 32 * kWorkWarps) {
+                    // the last pass may compute an item twice (same value, same address)
+                    const int ta = t, tb = min(t + 32 * kWorkWarps, n_items - 1), tc = min(t + 2 * 32 * kWorkWarps, n_items - 1);
+                    const float da = item_distance(ta), db = item_distance(tb), dc = item_distance(tc);
+                    item_store(ta, da), item_store(tb, db), item_store(tc, dc);
+                }
+            }
+            bar_workers();
+            lap(9);
+            // ---- P5c: one thread per row: selection by (distance bits, slot), the proof, softmax over the selected slots
+            if (wtid < BM) {
+                const int r = wtid;
+                const size_t q = q0 + r;
+                int ok = 0;
+                if (q < p.rows) {
+                    bool decisive = false;
+                    if (stat_mark[r] != 0u) {
+                        unsigned long long key[NC];
+#pragma unroll
+                        for (int j = 0; j < NC; ++j)
+                            key[j] = j < n_cand ? (((unsigned long long)__float_as_uint(d32[r * (NC + 1) + j]) << 32) | cand_slot[r * kCandMax + j]) : ~0ull;
+                        unsigned kth = 0u, mn = 0xffffffffu;
+                        unsigned selected = 0;  // bit j: candidate j is among the k smallest (bits, slot)
+#pragma unroll
+                        for (int j = 0; j < NC; ++j) {
+                            int rank = 0;
+#pragma unroll
+                            for (int i = 0; i < NC; ++i) rank += key[i] < key[j] ? 1 : 0;
+                            const unsigned bits = (unsigned)(key[j] >> 32);
+                            if (j < n_cand && rank < k) selected |= 1u << j, kth = max(kth, bits);
+                            if (j < n_cand) mn = min(mn, bits);
+                        }
+                        decisive = kth < stat_dlb[r];
+                        if (p.selftest_every > 0 && q % (size_t)p.selftest_every == 0) decisive = false;
+                        if (decisive) {
+                            const float dmin = __uint_as_float(mn);
+                            // ascending slot order (memory.rs:389-390), weights exp((min - d) / tau), their sum in that order
+#pragma unroll
+                            for (int j = 0; j < NC; ++j) {
+                                if (!(selected >> j & 1u)) continue;
+                                const unsigned slot = (unsigned)key[j] & 0xffffu;
+                                int srank = 0;
+#pragma unroll
+                                for (int i = 0; i < NC; ++i) srank += ((selected >> i & 1u) && ((unsigned)key[i] & 0xffffu) < slot) ? 1 : 0;
+                                sels[r * NC + srank] = slot;
+                                selw[r * NC + srank] = expf(__fdiv_rn(__fsub_rn(dmin, __uint_as_float((unsigned)(key[j] >> 32))), p.tau));
+                            }
+                            float sum = 0.0f;
+                            for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, selw[r * NC + j]);
+                            for (int j = 0; j < k; ++j) {
+                                const float wn = __fdiv_rn(selw[r * NC + j], sum);
+                                selw[r * NC + j] = wn;
+                                if (p.topk_slots) p.topk_slots[q * k + j] = sels[r * NC + j];
+                                if (p.topk_weights) p.topk_weights[q * k + j] = wn;
+                            }
+                            if (p.min_dist) p.min_dist[q] = dmin;
+                            ok = 1;
+                        }
+                    }
+                    if (!decisive) flag_rows[atomicAdd(flag_count, 1)] = r;  // the exact stage writes this row
+                }
+                row_ok[r] = ok;
+            }
+            bar_workers();
+            lap(10);
+            // ---- P5d: the value read, all threads: m = sum over the selected slots in ascending slot order of w * v, multiply
+            // and add separately rounded (memory.rs:399-406); four rows' loads are in flight before the first is used. (Staging
+            // the rows in shared memory with bulk or 16-byte asynchronous copies measured two to three times slower: the
+            // gather is bound by the L2's throughput on 512-byte rows, not by registers.) Then the reference's dense weight
+            // row if the caller wants it.
+            {
+                const int dv = p.dv, dv4 = dv >> 2;
+                for (int idx = wtid; idx < BM * dv4; idx += 32 * kWorkWarps) {
+                    const int r = idx / dv4, c4 = idx - r * dv4;
+                    if (!row_ok[r]) continue;
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j0 = 0; j0 < k; j0 += 4) {
+                        float4 vv[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (j0 + e < k) vv[e] = __ldg(reinterpret_cast<const float4*>(p.values + (size_t)sels[r * NC + j0 + e] * dv) + c4);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            if (j0 + e < k) {
+                                const float wi = selw[r * NC + j0 + e];
+                                acc.x = __fadd_rn(acc.x, __fmul_rn(wi, vv[e].x)), acc.y = __fadd_rn(acc.y, __fmul_rn(wi, vv[e].y));
+                                acc.z = __fadd_rn(acc.z, __fmul_rn(wi, vv[e].z)), acc.w = __fadd_rn(acc.w, __fmul_rn(wi, vv[e].w));
+                            }
+                        }
+                    }
+                    const size_t o = (q0 + r) * (size_t)dv + (size_t)c4 * 4;
+                    if (p.m_val) *reinterpret_cast<float4*>(p.m_val + o) = acc;
+                    if (p.m_bf16) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+                        uint2 pk;
+                        pk.x = *reinterpret_cast<unsigned*>(&lo), pk.y = *reinterpret_cast<unsigned*>(&hi);
+                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.m_bf16) + o) = pk;
+                    }
+                }
+                if (p.weights) {
+                    for (int idx = wtid; idx < BM * cap; idx += 32 * kWorkWarps) {
+                        const int r = idx / cap, i = idx % cap;
+                        if (!row_ok[r]) continue;
+                        float w = 0.0f;
+                        for (int j = 0; j < k; ++j) w = sels[r * NC + j] == (unsigned)i ? selw[r * NC + j] : w;
+                        p.weights[(q0 + r) * (size_t)cap + i] = w;
+                    }
+                }
+            }
+            // ---- P5e: the rows whose selection the candidates could not prove (or a list overflowed, or the test hook) are
+            // recomputed over every slot. Rare, and uniform over the CTA (the count is shared); kept out of line so that it
+            // costs the common path no registers.
+            bar_workers();
+            if (*flag_count > 0) {
+                const RetrieveParams pc = p;  // a local copy for the out-of-line call: the common path keeps reading the parameter bank
+                exact_rows<DK>(pc, q0, smem_a, stat_qs, flag_rows, *flag_count, fx_p, fx_dist, fx_slot, fx_w, wtid);
+            }
             bar_workers();  // the lists and the operand are free for the next tile
-            lap(5);
+            lap(11);
         }
         if (p.phase_cycles && wtid == 0)
-            for (int i = 0; i < 6; ++i) atomicAdd(p.phase_cycles + i, (unsigned long long)clk[i]);
+            for (int i = 0; i < kPhases; ++i) atomicAdd(p.phase_cycles + i, (unsigned long long)phase_clk[i]);
     }
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
-    }
-}
-
-// Exact pass for the rows the fused kernel could not prove (or was told to hand over): one warp per flagged row, f64
-// distances to every occupied slot, k rounds of a warp-wide minimum over (distance bits, slot).
-__global__ void __launch_bounds__(256) retrieve_topk_fixup_kernel(RetrieveParams p) {
-    __shared__ float ps[8][256];
-    __shared__ float dist[8][512];
-    __shared__ unsigned sel_slot_s[8][32];
-    __shared__ float sel_w_s[8][32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int dk = p.dk, count = p.count, k = p.top_k;
-    const size_t ldq = p.ldq ? p.ldq : (size_t)dk;
-    const unsigned n_rows = *p.fixup_count;
-    for (unsigned item = blockIdx.x * 8 + warp; item < n_rows; item += gridDim.x * 8) {
-    const size_t q = p.fixup_list[item];
-    __syncwarp();
-    for (int i = lane; i < dk; i += 32) ps[warp][i] = p.q[q * ldq + i];
-    __syncwarp();
-    float qs = 0.0f;
-    if (lane == 0) qs = project_row(ps[warp], dk, p.q_is_euclidean != 0, nullptr);
-    qs = __shfl_sync(0xffffffffu, qs, 0);
-    __syncwarp();
-    const double one_minus_q = 1.0 - (double)qs;
-    for (int s = lane; s < count; s += 32) {
-        const float* krow = p.keys + (size_t)s * dk;
-        double sq = 0.0;
-        for (int i = 0; i < dk; ++i) {
-            const double df = (double)ps[warp][i] - (double)__ldg(krow + i);
-            sq = fma(df, df, sq);
-        }
-        dist[warp][s] = exact_distance(sq, one_minus_q, __ldg(p.norm_sq + s));
-    }
-    __syncwarp();
-    unsigned my_slot = 0xffffffffu;
-    float my_dist = 0.0f, dmin = 0.0f;
-    for (int r = 0; r < k; ++r) {
-        unsigned long long local = ~0ull;
-        for (int s = lane; s < count; s += 32) {
-            const unsigned bits = __float_as_uint(dist[warp][s]);
-            if (bits & 0x80000000u) continue;  // taken (distances are >= +0)
-            local = umin64(local, ((unsigned long long)bits << 32) | (unsigned)s);
-        }
-#pragma unroll
-        for (int m = 16; m > 0; m >>= 1) local = umin64(local, __shfl_xor_sync(0xffffffffu, local, m));
-        const unsigned slot = (unsigned)(local & 0xffffffffu);
-        const float d = __uint_as_float((unsigned)(local >> 32));
-        if (lane == 0) dist[warp][slot] = __uint_as_float(__float_as_uint(d) | 0x80000000u);
-        if (lane == r) my_slot = slot, my_dist = d;
-        if (r == 0) dmin = d;
-        __syncwarp();
-    }
-    int srank = 0;
-    for (int i = 0; i < k; ++i) srank += __shfl_sync(0xffffffffu, my_slot, i) < my_slot ? 1 : 0;
-    if (lane < k) sel_slot_s[warp][srank] = my_slot, sel_w_s[warp][srank] = my_dist;
-    __syncwarp();
-    finish_row<32>(p, q, sel_slot_s[warp], sel_w_s[warp], k, dmin, lane, true);
     }
 }
 
@@ -631,7 +843,9 @@ __global__ void __launch_bounds__(256) compact_topk_kernel(const float* __restri
 
 size_t fused_smem(int dk) {
     const size_t a = (size_t)3 * (dk / BK) * BM * BK * 2;
-    const size_t tail = 512 * sizeof(float2) + 3 * BM * 4 + 512 * 4 + BM * kCandMax * 2 + 2 * kWorkWarps * 32 * 4 + (2 * kStages + 2) * 8 + 16;
+    // tail: per-slot constants, per-row statistics (|p|^2, two bounds, two counts, the proof distance, the flag),
+    // candidate slots, barriers
+    const size_t tail = 512 * sizeof(float2) + 512 * 4 + (1 + 2 + 2 + 1 + 1 + 1) * BM * 4 + BM * kCandMax * 2 + (2 * kStages + 2 + kPhases) * 8 + 16 + 16;
     return 1024 + a + (size_t)kStages * kRingStage + tail;
 }
 
@@ -641,8 +855,10 @@ bool retrieve_fused_eligible(const RetrieveParams& p) {
     const bool topk = p.top_k != 0 && p.top_k < p.count;
     const int n_cand = p.top_k + kMargin < kCandMax ? p.top_k + kMargin : kCandMax;
     return topk && p.top_k <= kCandMax - kMargin && (p.cap == 128 || p.cap == 256 || p.cap == 512) && (p.dk == 64 || p.dk == 128) &&
-           p.count / 8 >= n_cand + 2 && p.k_split && p.k_stat && p.fixup_list && p.fixup_count && p.rows > 0 &&
-           p.rows <= 0xffffffffull && p.dv > 0;
+           p.count / 8 >= n_cand + 2 && p.k_split && p.k_stat && p.fixup_count && p.rows > 0 &&
+           p.rows <= 0xffffffffull && p.dv > 0 && p.dv % 4 == 0 && (reinterpret_cast<uintptr_t>(p.values) & 15) == 0 &&
+           (reinterpret_cast<uintptr_t>(p.keys) & 15) == 0 &&
+           (!p.m_val || (reinterpret_cast<uintptr_t>(p.m_val) & 15) == 0) && (!p.m_bf16 || (reinterpret_cast<uintptr_t>(p.m_bf16) & 7) == 0);
 }
 
 int32_t launch_retrieve_fused(pssa_b200_ctx* ctx, const RetrieveParams& p) {
@@ -657,24 +873,22 @@ int32_t launch_retrieve_fused(pssa_b200_ctx* ctx, const RetrieveParams& p) {
     const size_t smem = fused_smem(p.dk);
     const long long tiles = (long long)((p.rows + BM - 1) / BM);
     const unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-    static PerDeviceOnce attr[2];
-    if (p.dk == 64) {
-        if (attr[0].need(ctx->device)) {
-            PSSA_CUDA(ctx, cudaFuncSetAttribute(retrieve_topk_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr[0].done(ctx->device);
+    static PerDeviceOnce attr[4];
+    auto go = [&](auto kernel, int which) -> int32_t {
+        if (attr[which].need(ctx->device)) {
+            PSSA_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr[which].done(ctx->device);
         }
-        PSSA_CUDA(ctx, launch_dependent(retrieve_topk_fused_kernel<64>, dim3(grid), dim3(kThreads), smem, ctx->stream, map_b, q));
-    } else {
-        if (attr[1].need(ctx->device)) {
-            PSSA_CUDA(ctx, cudaFuncSetAttribute(retrieve_topk_fused_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attr[1].done(ctx->device);
-        }
-        PSSA_CUDA(ctx, launch_dependent(retrieve_topk_fused_kernel<128>, dim3(grid), dim3(kThreads), smem, ctx->stream, map_b, q));
-    }
-    if ((rc = after_launch(ctx, "retrieve_topk_fused_kernel"))) return rc;
-    // the rows the fused kernel handed over (their count is only known on the device): a fixed small grid walks the list
-    retrieve_topk_fixup_kernel<<<(unsigned)ctx->sm_count, 256, 0, ctx->stream>>>(q);
-    return after_launch(ctx, "retrieve_topk_fixup_kernel");
+        PSSA_CUDA(ctx, launch_dependent(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, map_b, q));
+        return PSSA_B200_OK;
+    };
+    const bool few = p.top_k + kMargin <= 9;  // the instantiation with nine candidate registers per thread
+    if (p.dk == 64)
+        rc = few ? go(retrieve_topk_fused_kernel<64, 9>, 0) : go(retrieve_topk_fused_kernel<64, kCandMax>, 1);
+    else
+        rc = few ? go(retrieve_topk_fused_kernel<128, 9>, 2) : go(retrieve_topk_fused_kernel<128, kCandMax>, 3);
+    if (rc) return rc;
+    return after_launch(ctx, "retrieve_topk_fused_kernel");
 }
 
 int32_t launch_compact_topk(pssa_b200_ctx* ctx, const float* weights, int cap, int k, size_t rows, unsigned* slots, float* w_out) {
