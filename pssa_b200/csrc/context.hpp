@@ -31,9 +31,6 @@ struct pssa_b200_ctx {
     cudaStream_t side[3] = {nullptr, nullptr, nullptr};
     cudaEvent_t fork_ev = nullptr, join_ev[3] = {nullptr, nullptr, nullptr};
     int chain = 0;  // which of those streams `stream` currently is (0 = the caller's); keys the stage profile
-    // set while a pass runs as several lane groups: launchers pick the kernel variants that leave room on an SM for a
-    // kernel of another group (tensor-core CTAs with four epilogue warps and a two-stage ring, SSM CTAs with a two-stage ring)
-    bool slim = false;
     // Resident SSM result (`ssm_forward_resident` -> `memory_forward_after_ssm`, src/backend.rs:1186-1289): the tape of the
     // last resident SSM call stays on the device until the memory stage consumes it.
     struct ResidentSsm {

@@ -106,7 +106,7 @@ constexpr int kRuntimeMode = -100;
 // OUTS fixes which outputs exist: 0 = read the pointers at run time, 1 = fp32 only, 2 = bf16 only.
 // EW epilogue warps: EW / 4 per TMEM lane quadrant, each draining BN / (EW / 4) of the tile's columns.
 template <int BN, int STAGES, int MODE, int OUTS, int EW>
-__global__ void __launch_bounds__(64 + 32 * EW, EW == 4 ? 2 : 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_b,
                                                                             GemmEpilogue e) {
     constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -443,10 +443,6 @@ int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const Gemm
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
     if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
     size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EW * 32 * STG_PITCH * 4;
-    // The slim variants (four epilogue warps) share an SM with CTAs of other kernels, but never with each other: each
-    // allocates most of the SM's TMEM, and a second one would sit in tcgen05.alloc until the first has finished. Asking for
-    // more than half of the SM's shared memory keeps them one per SM.
-    if (EW == 4 && smem < 116 * 1024) smem = 116 * 1024;
     auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS, EW>;
     static PerDeviceOnce attr;  // per instantiation and per device
     if (attr.need(ctx->device)) {
@@ -486,7 +482,6 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // widest tile that still gives every SM work: 256 columns halve the shared-memory operand traffic per flop,
     // narrow outputs (state / key projections) and short batches (decode) use smaller tiles to spread over SMs
     const long long m_tiles = (e.M + BM - 1) / BM;
-    if (ctx->slim && e.N <= 128) return e.N <= 64 ? launch_tile<64, 3, kRuntimeMode, 0, 4>(ctx, a, b, e) : launch_tile<128, 3, kRuntimeMode, 0, 4>(ctx, a, b, e);
     if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2)
         return (e.epi == EPI_ADD_OUT && e.out && !e.out16 && e.n_pairs == 0) ? launch_tile<64, 7, EPI_ADD_OUT, 1>(ctx, a, b, e)
                                                                             : launch_tile<64, 7>(ctx, a, b, e);
@@ -495,14 +490,6 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
     // (their epilogue traffic is the limiter), so those keep three.
     const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
-    if (ctx->slim) {  // lane groups: leave room on the SM for the other group's SSM CTAs
-        if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 2, EPI_POINCARE, 1, 4>(ctx, a, b, e);
-        if (e.epi == -1 && only32) return launch_tile<256, 2, -1, 1, 4>(ctx, a, b, e);
-        if (e.epi == EPI_GATE && only16) return launch_tile<256, 2, EPI_GATE, 2, 4>(ctx, a, b, e);
-        if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 2, EPI_RESIDUAL, 1, 4>(ctx, a, b, e);
-        if (e.epi == EPI_SILU && only16) return launch_tile<256, 2, EPI_SILU, 2, 4>(ctx, a, b, e);
-        return launch_tile<256, 2, kRuntimeMode, 0, 4>(ctx, a, b, e);
-    }
     if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_GATE && e.n_pairs > 0 && only16) return launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);

@@ -238,8 +238,10 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // Measured at the benchmark's shapes (32 x 2048-token lanes; 256 decode streams) two groups are SLOWER than one
         // stream (24.1 against 23.1 ms per prefill step, 1.70 against 1.37 ms per decode step): every tensor-core CTA
         // takes a whole SM's registers and shared memory, so kernels of different groups queue behind each other instead
-        // of sharing SMs, and each is smaller. The automatic choice is therefore one group; the option stays for shapes
-        // and kernel variants where co-residency is possible.
+        // of sharing SMs, and each is smaller. Kernel variants slim enough for two CTAs per SM (tensor-core CTAs with four
+        // epilogue warps and a two-stage ring under 116 KB, SSM CTAs with a two-stage ring) were tried for the grouped case
+        // and measured slower still (28.4 ms, 1.77 ms), so they are not kept. The automatic choice is one group; the
+        // option stays for other shapes.
         size_t want = m->lane_groups == 0 ? 1 : m->lane_groups;
         if (!two_pass && !observe && contiguous)
             n_groups = std::max<size_t>(1, std::min<size_t>(std::min<size_t>(want, 4), lanes));
@@ -437,11 +439,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         ctx->stream = main_stream, ctx->chain = 0;
         return r;
     };
-    ctx->slim = n_groups > 1;
-    if ((rc = fork())) {
-        ctx->slim = false;
-        return rc;
-    }
+    if ((rc = fork())) return rc;
     if (m->loops == 1) {
         // src/pssa.rs:2327-2337: block 0's output replaces the embedding, every further block adds its scaled output
         for (size_t l = 0; l < m->depth && rc == PSSA_B200_OK; ++l) {
@@ -472,7 +470,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         }
         feat_in = feat;
     }
-    ctx->stream = main_stream, ctx->chain = 0, ctx->slim = false;
+    ctx->stream = main_stream, ctx->chain = 0;
     {
         const int32_t jr = join();  // always re-join, even after a failed launch: the side streams must not run past this call
         if (rc == PSSA_B200_OK) rc = jr;

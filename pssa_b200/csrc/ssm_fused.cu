@@ -39,7 +39,7 @@ constexpr int kTileTokensFor = G >= 32 ? 8 : 16;
 // The 16-state fast configuration is capped at 64 registers so four CTAs (32 warps) share an SM: the kernel is bound by
 // dependent-issue latency, not by a pipe, and the extra warps are worth more than the 16 bytes of spill they cost.
 constexpr int kMinCtasFast = 4;
-constexpr int kDefaultStages = 3;  // cp.async ring depth; the co-resident variant (lane groups) runs with two
+constexpr int kStages = 3;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -78,7 +78,7 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     return r;
 }
 
-template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads, int kStages = kDefaultStages>
+template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
 __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 256 ? 2 : kMinCtasFast) : 1) ssm_fused_kernel(SsmParams p) {
     pdl_trigger();  // the next kernel in the stream may start its prologue now ...
     pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
@@ -436,14 +436,14 @@ __global__ void __launch_bounds__(256) seqpar_fold_kernel(const float* __restric
     st[e] = h;
 }
 
-template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads, int kStages = kDefaultStages>
+template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
 int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
     constexpr int kThreads = THR;
     constexpr int CH = kThreads / G;
     constexpr int SP = (ST + 4) * G;
     constexpr int kTileTokens = kTileTokensFor<G>;
     size_t smem = (size_t)kStages * kTileTokens * (2 * CH + 2 * SP) * sizeof(float);
-    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE, THR, kStages>;
+    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE, THR>;
     static PerDeviceOnce attr_set;  // per instantiation and per device
     if (smem > 48 * 1024 && attr_set.need(ctx->device)) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -512,9 +512,6 @@ int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact) {
             // CTA size by wave balance. Every CTA of a launch is resident at once and they all take the same time, so the
             // launch lasts as long as the SM holding the most warps. 256 threads = 64 channels per CTA; 352 threads = 88
             // channels. With d = 768 and 32 lanes: 384 CTAs put 3 x 8 warps on most SMs, 288 larger ones put 2 x 11.
-            // beside a tensor-core CTA (lane groups): 256 threads, 64 registers and a two-stage ring, so that two of these
-            // CTAs fit into what the slim GEMM variant leaves of an SM
-            if (!tape && ctx->slim) return launch_cfg<16, 4, false, false, 256, 2>(ctx, p);
             if (!tape) {
                 auto busiest = [&](int threads, int cap) -> long long {
                     const long long blocks = (long long)((p.d + threads / 4 - 1) / (threads / 4)) * p.lanes;
