@@ -528,7 +528,7 @@ def run_extras(gpu, torch, peak_hbm):
             sel = torch.zeros(rows, cap, dtype=torch.bool, device="cuda")
             sel.scatter_(1, slots8.long(), True)
             row["queries_with_the_f64_slot_set"] = float((sel == ref_sel).all(dim=1).float().mean().item())
-            row["rows_handed_to_the_exact_pass"] = int(handed.item())
+            row["rows_handed_to_the_exact_stage"] = int(handed.item())
             del sel
         elif top_k:
             sel = w != 0  # the selected slot sets of every query
@@ -864,6 +864,55 @@ def run_scan_c2(args):
     gpu.close()
 
 
+def run_retrieval_c3(args):
+    """BASELINE configs[2]'s read alone: the exact top-8 Poincare read of 64 x 4096 queries against one 512-slot bank in
+    one kernel (the same inputs as the `retrieval_c3_top8` entry of the benchmark's extras); for profiler captures."""
+    import torch
+
+    import pssa_b200
+    torch.cuda.set_device(0)
+    gpu = pssa_b200.B200Dispatch(0)
+    stream = torch.cuda.current_stream()
+    gpu.set_stream(stream)
+    rows, dk, dv, cap = 64 * 4096, 128, 128, 512
+    g = torch.Generator(device="cuda").manual_seed(5)
+    dirs = torch.randn(cap, dk, device="cuda", generator=g)
+    keys = dirs / dirs.norm(dim=1, keepdim=True) * torch.rand(cap, 1, device="cuda", generator=g) * 0.9
+    norm_sq = (keys.double() ** 2).sum(1).float()
+    vals = torch.randn(cap, dv, device="cuda", generator=g)
+    qd = torch.randn(rows, dk, device="cuda", generator=g)
+    q = qd / qd.norm(dim=1, keepdim=True) * torch.rand(rows, 1, device="cuda", generator=g) * 0.9
+    m = torch.zeros(rows, dv, device="cuda")
+    slots8 = torch.zeros(rows, 8, dtype=torch.int32, device="cuda")
+    w8 = torch.zeros(rows, 8, device="cuda")
+    handed = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def read():
+        gpu.memory_read_topk_dev(q, keys, norm_sq, vals, rows, dk, dv, cap, cap, 0.1, 8, m, slots8, w8, handed_over=handed,
+                                 q_is_euclidean=False)
+
+    for _ in range(max(3, args.warmup)):
+        read()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        read()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak_hbm, _, kind = measured_peaks()
+    byts = rows * (dk * 4 + dv * 4 + 64)
+    print(json.dumps({"metric": "retrieval_queries_per_s", "value": rows / (ms / 1e3), "unit": "queries/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "f64 distances of the candidates, bf16 x 3 pre-filter", "data": "synthetic",
+                      "config": {"workload": "retrieval_c3: exact top-8 Poincare read, 512 slots, key/value dim 128, 262144 queries, one kernel"},
+                      "roofline": {"bound": "hbm", "achieved": byts / (ms / 1e3) / 1e9, "peak": peak_hbm, "unit": "GB/s",
+                                   "frac": byts / (ms / 1e3) / 1e9 / peak_hbm, "peak_kind": f"of {kind}"},
+                      "rows_handed_to_the_exact_stage": int(handed.item()), "gpu_launches": int(gpu.launch_count())}))
+    gpu.close()
+
+
 def main():
     global LANES
     ap = argparse.ArgumentParser()
@@ -875,13 +924,15 @@ def main():
     ap.add_argument("--lanes", type=int, default=LANES,
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures, not the benchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and parity sample (profiler captures)")
-    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5", "scan_c2"],
+    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5", "scan_c2", "retrieval_c3"],
                     help="prefill_c4 is the benchmark; seqpar_c5 is the long-context time-sharded prefill (N >= 2); scan_c2 is "
-                         "the scan operator alone")
+                         "the scan operator alone; retrieval_c3 is the one-kernel top-8 memory read alone")
     ap.add_argument("--seq-len", type=int, default=65536, help="sequence length of the seqpar_c5 workload")
     args = ap.parse_args()
     if args.workload == "scan_c2":
         return run_scan_c2(args)
+    if args.workload == "retrieval_c3":
+        return run_retrieval_c3(args)
     if args.lanes != LANES:
         global WORKLOAD
         WORKLOAD = WORKLOAD.replace(f"{LANES} sequences", f"{args.lanes} sequences (REDUCED CASE, not the benchmark)")

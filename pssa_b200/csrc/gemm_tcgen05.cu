@@ -486,18 +486,20 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
         return (e.epi == EPI_ADD_OUT && e.out && !e.out16 && e.n_pairs == 0) ? launch_tile<64, 7, EPI_ADD_OUT, 1>(ctx, a, b, e)
                                                                             : launch_tile<64, 7>(ctx, a, b, e);
     if (e.N <= 128 || m_tiles * ((e.N + 255) / 256) < ctx->sm_count) return launch_tile<128, 5>(ctx, a, b, e);
-    // Four 48 KB stages help the long-K split product (141 -> 126 us at the model's shape, +8 % on plain products timed
-    // alone); inside the block schedule the K = 768 products with heavy epilogues measured the same or slower with them
-    // (their epilogue traffic is the limiter), so those keep three.
+    // Four 48 KB stages: with three, the issuing thread of the K = 768 products spent 56 % of its cycles waiting for
+    // operands (cycle counters around its two waits, 32 x 2048-token lanes) and 40 % with four (its loop 8-14 % shorter);
+    // what then limits these products is the epilogue (its warps wait for an accumulator 9 % of the time). The gated
+    // split value read and the distance product are bound by their epilogues already (the issuing thread waits for a
+    // drained accumulator, not for operands) and measured slower with four stages (1.98 against 1.45 ms per step): three.
     const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
     if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_GATE && e.n_pairs > 0 && only16) return launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
-    if (e.epi == -1 && only32) return launch_tile<256, 3, -1, 1, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == -1 && only32) return launch_tile<256, 4, -1, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_GATE) return only16 ? launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e) : launch_tile<256, 3, EPI_GATE, 0, kWideEpiWarps>(ctx, a, b, e);
-    if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 3, EPI_RESIDUAL, 1, kWideEpiWarps>(ctx, a, b, e);
-    if (e.epi == EPI_SILU && only16) return launch_tile<256, 3, EPI_SILU, 2, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_RESIDUAL && only32) return launch_tile<256, 4, EPI_RESIDUAL, 1, kWideEpiWarps>(ctx, a, b, e);
+    if (e.epi == EPI_SILU && only16) return launch_tile<256, 4, EPI_SILU, 2, kWideEpiWarps>(ctx, a, b, e);
     return launch_tile<256, 3>(ctx, a, b, e);
 }
 
