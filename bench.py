@@ -913,6 +913,32 @@ def run_retrieval_c3(args):
     gpu.close()
 
 
+def run_decode(args):
+    """The decode half of BASELINE's long-context configuration alone on one GPU (256 streams, `--steps` greedy tokens
+    each after 16-token prompts); the same leg as `extra.decode_c5` of the benchmark line, for profiler captures."""
+    import torch
+
+    import pssa_b200
+    from pssa_b200 import _native as N
+    torch.cuda.set_device(0)
+    gpu = pssa_b200.B200Dispatch(0)
+    gpu.set_stream(torch.cuda.current_stream())
+    tensors, banks = synth_weights(1234)
+    model = pssa_b200.PSSAModel(gpu, tau_mem=0.1, streams=256, precision=N.PRECISION_BF16, **CFG)
+    for (layer, tid), arr in tensors.items():
+        model.set_tensor(layer, tid, arr)
+    for l, (keys, norm_sq, values) in enumerate(banks):
+        model.set_bank(l, keys, norm_sq, values, CFG["mem_capacity"])
+    peak_hbm, _, kind = measured_peaks()
+    leg = run_decode_c5(model, gpu, torch, None, 1, 0, peak_hbm, steps=args.steps)
+    print(json.dumps({"metric": "decode_tokens_per_s", "value": leg["tokens_per_s"], "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": 4, "ms_per_step": leg["ms_per_step"], "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "decode_c5: " + leg["workload"]}, "roofline": dict(leg["roofline"], peak_kind=f"of {kind}"),
+                      "e2e": leg["e2e"], "cuda_graph": leg.get("cuda_graph"), "gpu_launches": int(leg["gpu_launches_per_step"] * args.steps)}))
+    model.close()
+    gpu.close()
+
+
 def main():
     global LANES
     ap = argparse.ArgumentParser()
@@ -924,15 +950,17 @@ def main():
     ap.add_argument("--lanes", type=int, default=LANES,
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures, not the benchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and parity sample (profiler captures)")
-    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5", "scan_c2", "retrieval_c3"],
+    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5", "scan_c2", "retrieval_c3", "decode_c5"],
                     help="prefill_c4 is the benchmark; seqpar_c5 is the long-context time-sharded prefill (N >= 2); scan_c2 is "
-                         "the scan operator alone; retrieval_c3 is the one-kernel top-8 memory read alone")
+                         "the scan operator alone; retrieval_c3 is the one-kernel top-8 memory read alone; decode_c5 is the 256-stream greedy decode alone")
     ap.add_argument("--seq-len", type=int, default=65536, help="sequence length of the seqpar_c5 workload")
     args = ap.parse_args()
     if args.workload == "scan_c2":
         return run_scan_c2(args)
     if args.workload == "retrieval_c3":
         return run_retrieval_c3(args)
+    if args.workload == "decode_c5":
+        return run_decode(args)
     if args.lanes != LANES:
         global WORKLOAD
         WORKLOAD = WORKLOAD.replace(f"{LANES} sequences", f"{args.lanes} sequences (REDUCED CASE, not the benchmark)")

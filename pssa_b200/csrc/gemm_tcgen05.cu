@@ -482,6 +482,20 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // widest tile that still gives every SM work: 256 columns halve the shared-memory operand traffic per flop,
     // narrow outputs (state / key projections) and short batches (decode) use smaller tiles to spread over SMs
     const long long m_tiles = (e.M + BM - 1) / BM;
+    const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
+    // Decode steps (a few hundred rows against a whole weight matrix): 128 x 32 tiles put 48 to 110 CTAs on a product that
+    // 128 x 64 tiles covered with 24 to 56, and ten 20 KB stages keep nearly all of a K = 768 product's operands in
+    // flight at once. Each CTA is a short chain of latencies (launch, one operand round trip, epilogue), so what counts
+    // is how many run side by side and how little code each has to fetch: the step's products get the specialised
+    // epilogues here too.
+    if (m_tiles <= 2 && e.N >= 256 && e.N <= 4096) {
+        if (e.epi == -1 && only32) return launch_tile<32, 10, -1, 1, 4>(ctx, a, b, e);
+        if (e.epi == EPI_POINCARE && only32) return launch_tile<32, 10, EPI_POINCARE, 1, 4>(ctx, a, b, e);
+        if (e.epi == EPI_GATE && only16) return launch_tile<32, 10, EPI_GATE, 2, 4>(ctx, a, b, e);
+        if (e.epi == EPI_SILU && only16) return launch_tile<32, 10, EPI_SILU, 2, 4>(ctx, a, b, e);
+        if (e.epi == EPI_RESIDUAL && only32) return launch_tile<32, 10, EPI_RESIDUAL, 1, 4>(ctx, a, b, e);
+        return launch_tile<32, 10, kRuntimeMode, 0, 4>(ctx, a, b, e);
+    }
     if (e.N <= 64 || m_tiles * ((e.N + 127) / 128) < ctx->sm_count / 2)
         return (e.epi == EPI_ADD_OUT && e.out && !e.out16 && e.n_pairs == 0) ? launch_tile<64, 7, EPI_ADD_OUT, 1>(ctx, a, b, e)
                                                                             : launch_tile<64, 7>(ctx, a, b, e);
@@ -491,7 +505,6 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     // what then limits these products is the epilogue (its warps wait for an accumulator 9 % of the time). The gated
     // split value read and the distance product are bound by their epilogues already (the issuing thread waits for a
     // drained accumulator, not for operands) and measured slower with four stages (1.98 against 1.45 ms per step): three.
-    const bool only32 = e.out && !e.out16, only16 = !e.out && e.out16;
     if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_GATE && e.n_pairs > 0 && only16) return launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
