@@ -19,6 +19,8 @@
 // status word, stops issuing work, and still frees its TMEM.
 #include <cuda.h>
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 #include <cuda_runtime.h>
 
 #include "bounds.hpp"
@@ -105,11 +107,15 @@ __device__ __forceinline__ int col_kind(const GemmEpilogue& e, int col) {
 constexpr int kRuntimeMode = -100;
 // OUTS fixes which outputs exist: 0 = read the pointers at run time, 1 = fp32 only, 2 = bf16 only.
 // EW epilogue warps: EW / 4 per TMEM lane quadrant, each draining BN / (EW / 4) of the tile's columns.
-template <int BN, int STAGES, int MODE, int OUTS, int EW>
+// PAIR: the kernel runs as clusters of two CTAs on 256 x BN tiles (cta_group::2): each CTA keeps its own 128 rows of A,
+// loads only its half of the B tile (32 KB instead of 48 KB per K block and CTA at BN = 256) and drains its own 128
+// accumulator rows; the even CTA issues the MMAs for both and its barriers count both CTAs' operand bytes.
+template <int BN, int STAGES, int MODE, int OUTS, int EW, bool PAIR>
 __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                             const __grid_constant__ CUtensorMap map_b,
                                                                             GemmEpilogue e) {
-    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+    constexpr int B_ROWS = PAIR ? BN / 2 : BN;  // rows of B (output columns) this CTA loads per K block
+    constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2;
     constexpr uint32_t TMEM_COLS = 2 * BN;  // 128, 256 or 512: a power of two >= 32
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte alignment is required by the 128-byte swizzle
@@ -133,8 +139,12 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = e.n_pairs > 0 ? e.n_pairs * e.seg_kb : (e.K + BK - 1) / BK;
     const int n_tiles = (e.N + BN - 1) / BN;
-    const int m_tiles = (e.M + BM - 1) / BM;
+    constexpr int TILE_M = PAIR ? 2 * BM : BM;  // rows of one scheduled tile
+    const int m_tiles = (e.M + TILE_M - 1) / TILE_M;
     const long long total_tiles = (long long)n_tiles * m_tiles;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;               // 0: the CTA that issues the MMAs
+    const long long first_tile = PAIR ? (blockIdx.x >> 1) : blockIdx.x;  // both CTAs of a pair walk the same tiles
+    const long long tile_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -143,16 +153,22 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&acc_full[b], 1);
-            mbar_init(&acc_empty[b], EW);  // one arrival per epilogue warp
+            mbar_init(&acc_empty[b], PAIR ? 2 * EW : EW);  // one arrival per epilogue warp (of both CTAs of a pair)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {  // TMEM allocation is a warp-wide operation
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (warp == 1) {  // TMEM allocation is a warp-wide operation (for a pair: the same warp of both CTAs, same slot)
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync();  // the peer's barriers are initialised before anything of this CTA can signal them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // everything above touched only this CTA's shared memory and TMEM; from here on the kernel reads what its
@@ -164,8 +180,9 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
         if (lane == 0) {
             uint32_t it = 0;  // k-block counter across all tiles of this CTA
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (int)(tile / n_tiles) * BM, n0 = (int)(tile % n_tiles) * BN;
+            const uint32_t leader_full = PAIR ? mapa_shared(smem_u32(full_bar), 0) : 0u;  // the even CTA's full barriers
+            for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+                const int m0 = (int)(tile / n_tiles) * TILE_M + (int)rank * BM, n0 = (int)(tile % n_tiles) * BN + (int)rank * B_ROWS;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
@@ -174,24 +191,32 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                         ok = false;
                         break;
                     }
-                    mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                    if (!PAIR)
+                        mbar_expect_tx(&full_bar[s], A_BYTES + B_BYTES);
+                    else if (rank == 0)
+                        mbar_expect_tx(&full_bar[s], 2 * (A_BYTES + B_BYTES));  // this CTA's bytes and the peer's
                     int ka = kb, kbb = kb;
                     if (e.n_pairs > 0) {
                         const int pair = kb / e.seg_kb, within = kb % e.seg_kb;
                         ka = e.pair_a[pair] * e.seg_kb + within;
                         kbb = e.pair_b[pair] * e.seg_kb + within;
                     }
-                    tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], ka * BK, m0);
-                    tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kbb * BK, n0);
+                    if (PAIR) {
+                        tma_load_2d_pair(smem_a + s * A_BYTES, &map_a, leader_full + s * 8, ka * BK, m0);
+                        tma_load_2d_pair(smem_b + s * B_BYTES, &map_b, leader_full + s * 8, kbb * BK, n0);
+                    } else {
+                        tma_load_2d(smem_a + s * A_BYTES, &map_a, &full_bar[s], ka * BK, m0);
+                        tma_load_2d(smem_b + s * B_BYTES, &map_b, &full_bar[s], kbb * BK, n0);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(TILE_M, BN);
             uint32_t it = 0, t = 0;
             bool ok = true;
-            for (long long tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            for (long long tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++t) {
                 const uint32_t buf = t & 1, use = t >> 1;
                 if (use > 0 && !mbar_wait(&acc_empty[buf], (use - 1) & 1)) {
                     atomicExch(e.status, PSSA_B200_ERR_TIMEOUT);
@@ -213,11 +238,16 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // advance 32 bytes (16 bf16) inside the swizzle atom: +2 in 16-byte units
-                        tcgen05_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (PAIR)
+                            tcgen05_mma_bf16_pair(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        else
+                            tcgen05_mma_bf16(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
-                    tcgen05_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+                    // stage reusable once these MMAs have read it (in both CTAs of a pair)
+                    if (PAIR) tcgen05_commit_pair(&empty_bar[s]); else tcgen05_commit(&empty_bar[s]);
                 }
-                tcgen05_commit(&acc_full[buf]);  // accumulator complete (or abandoned)
+                // accumulator complete (or abandoned)
+                if (PAIR) tcgen05_commit_pair(&acc_full[buf]); else tcgen05_commit(&acc_full[buf]);
             }
         }
     } else {
@@ -230,8 +260,9 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
         const int cq = (lane & 7) * 4;   // column quad this lane stores after the transpose
         const int rsub = lane >> 3;      // row within each group of 4 rows
         uint32_t t = 0;
-        for (long long tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
-            const int m0 = (int)(tile / n_tiles) * BM, n0 = (int)(tile % n_tiles) * BN + half * HALF_COLS;
+        const uint32_t leader_acc_empty = PAIR ? mapa_shared(smem_u32(acc_empty), 0) : 0u;
+        for (long long tile = first_tile; tile < total_tiles; tile += tile_step, ++t) {
+            const int m0 = (int)(tile / n_tiles) * TILE_M + (int)rank * BM, n0 = (int)(tile % n_tiles) * BN + half * HALF_COLS;
             const uint32_t buf = t & 1, use = t >> 1;
             const bool ready = mbar_wait(&acc_full[buf], use & 1);
             if (!ready) {
@@ -283,7 +314,9 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                     // this warp's last chunk of the accumulator is in registers: hand its share of the buffer back
                     tcgen05_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    if (lane == 0) {
+                        if (PAIR) mbar_arrive_cluster(leader_acc_empty + buf * 8); else mbar_arrive(&acc_empty[buf]);
+                    }
                     released = true;
                 }
                 if (col0 >= e.N) break;
@@ -423,35 +456,58 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
             if (!released) {  // this warp's column half lies entirely outside the matrix
                 tcgen05_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                if (lane == 0) {
+                    if (PAIR) mbar_arrive_cluster(leader_acc_empty + buf * 8); else mbar_arrive(&acc_empty[buf]);
+                }
             }
         }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync();  // neither CTA leaves (or frees TMEM) while the other may still signal its barriers or read its operands
     if (warp == 1) {
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
 // ---- host side --------------------------------------------------------------------------------
-template <int BN, int STAGES, int MODE = kRuntimeMode, int OUTS = 0, int EW = EPI_WARPS>
+template <int BN, int STAGES, int MODE = kRuntimeMode, int OUTS = 0, int EW = EPI_WARPS, bool PAIR = false>
 int32_t launch_tile(pssa_b200_ctx* ctx, const void* a, const void* b, const GemmEpilogue& e) {
     CUtensorMap map_a, map_b;
     int32_t rc;
+    constexpr int B_ROWS = PAIR ? BN / 2 : BN;
     if ((rc = make_map(ctx, &map_a, a, e.M, e.K, BM))) return rc;
-    if ((rc = make_map(ctx, &map_b, b, e.N, e.K, BN))) return rc;
-    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EW * 32 * STG_PITCH * 4;
-    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS, EW>;
+    if ((rc = make_map(ctx, &map_b, b, e.N, e.K, B_ROWS))) return rc;
+    size_t smem = 1024 + (size_t)STAGES * (BM * BK * 2 + B_ROWS * BK * 2) + (2 * STAGES + 4) * 8 + 16 + EW * 32 * STG_PITCH * 4;
+    auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, MODE, OUTS, EW, PAIR>;
     static PerDeviceOnce attr;  // per instantiation and per device
     if (attr.need(ctx->device)) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr.done(ctx->device);
     }
-    long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
-    unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
-    PSSA_CUDA(ctx, launch_dependent(kern, dim3(grid), dim3(64 + 32 * EW), smem, ctx->stream, map_a, map_b, e));
+    if (PAIR) {
+        // one persistent pair per two SMs; both attributes: the cluster of two, and the dependent launch
+        const long long tiles = (long long)((e.M + 2 * BM - 1) / (2 * BM)) * ((e.N + BN - 1) / BN);
+        const long long pairs = ctx->sm_count / 2;
+        const unsigned grid = 2u * (unsigned)(tiles < pairs ? tiles : pairs);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid), cfg.blockDim = dim3(64 + 32 * EW), cfg.dynamicSmemBytes = smem, cfg.stream = ctx->stream;
+        cudaLaunchAttribute attrs[2]{};
+        attrs[0].id = cudaLaunchAttributeClusterDimension;
+        attrs[0].val.clusterDim.x = 2, attrs[0].val.clusterDim.y = 1, attrs[0].val.clusterDim.z = 1;
+        attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attrs, cfg.numAttrs = 2;
+        PSSA_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, map_a, map_b, e));
+    } else {
+        long long tiles = (long long)((e.M + BM - 1) / BM) * ((e.N + BN - 1) / BN);
+        unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);  // one persistent CTA per SM
+        PSSA_CUDA(ctx, launch_dependent(kern, dim3(grid), dim3(64 + 32 * EW), smem, ctx->stream, map_a, map_b, e));
+    }
     // the profile facility keys on this name: one entry per epilogue family
     const char* name = e.epi == EPI_POINCARE    ? "gemm_bf16_tcgen05_kernel[Poincare distances]"
                        : e.n_pairs > 0          ? "gemm_bf16_tcgen05_kernel[split value read]"
@@ -508,6 +564,15 @@ int32_t dispatch(pssa_b200_ctx* ctx, const void* a, const void* b, GemmEpilogue&
     if (e.epi == EPI_POINCARE && only32) return launch_tile<256, 3, EPI_POINCARE, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_GATE && e.n_pairs > 0 && only16) return launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e);
     if (e.n_pairs > 0) return (e.epi == EPI_NONE && only16) ? launch_tile<256, 4, EPI_NONE, 2>(ctx, a, b, e) : launch_tile<256, 4>(ctx, a, b, e);
+    // Plain products run as CTA pairs (cta_group::2) when there are enough 256-row tiles for every pair of SMs: the
+    // operand traffic per SM, the limiter of the 128 x 256 tile's main loop, drops by a third and six 32 KB stages fit:
+    // 8192^3 at 1463 TFLOP/s against 1132, 65536 x 1536 x 768 at 1160 against 804. The block schedule's x-side and MLP
+    // products were measured as pairs too (same results, parity green) and were not faster (2.27 / 1.72 / 2.05 ms per
+    // step against 2.22 / 1.65 / 2.03): their epilogues and output traffic are the limiters, so they stay single CTAs.
+    static const bool use_pairs = std::getenv("PSSA_B200_NO_CTA_PAIRS") == nullptr;  // (for comparisons)
+    const bool pair_ok = use_pairs && e.n_pairs == 0 && ((e.M + 2 * BM - 1) / (2 * BM)) * ((e.N + 255) / 256) >= ctx->sm_count / 2;
+    if (pair_ok && e.epi == EPI_NONE && only32) return launch_tile<256, 6, EPI_NONE, 1, kWideEpiWarps, true>(ctx, a, b, e);
+    if (pair_ok && e.epi == EPI_NONE && only16) return launch_tile<256, 6, EPI_NONE, 2, kWideEpiWarps, true>(ctx, a, b, e);
     // the block schedule's products: one epilogue family and one output set per instantiation
     if (e.epi == -1 && only32) return launch_tile<256, 4, -1, 1, kWideEpiWarps>(ctx, a, b, e);
     if (e.epi == EPI_GATE) return only16 ? launch_tile<256, 3, EPI_GATE, 2, kWideEpiWarps>(ctx, a, b, e) : launch_tile<256, 3, EPI_GATE, 0, kWideEpiWarps>(ctx, a, b, e);

@@ -108,3 +108,20 @@ def test_bf16_gemm_epilogues_and_k_alignment(gpu):
     with pytest.raises(pssa_b200.B200Error) as e:
         gpu.dispatch_gemm(x[:, :60].copy(), w[:, :60].copy(), m, n, 60, 1, precision=N.PRECISION_BF16)
     assert e.value.status == 6 and "K % 8" in str(e.value)
+
+
+@pytest.mark.parametrize("m,n,k", [(4096, 2304, 512), (3900, 2000, 264), (5000, 4104, 128)])
+def test_bf16_gemm_as_cta_pairs(gpu, m, n, k):
+    """Plain products with enough 256-row tiles for every pair of SMs run as clusters of two CTAs (cta_group::2: the
+    even CTA issues the MMAs over both CTAs' operand halves). Full and ragged shapes (rows and columns that are not
+    multiples of the 256 x 256 tile, an odd number of 128-row blocks, K that is not a multiple of the 64-wide K block)
+    against an f64 product of the bf16-rounded operands; the profile shows which kernel ran."""
+    from pssa_b200 import _native as N
+    rng = np.random.default_rng(m + n + k)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    ref = bf16_round(x).astype(np.float64) @ bf16_round(w).astype(np.float64).T
+    got = gpu.dispatch_gemm(x, w, m, n, k, 1, precision=N.PRECISION_BF16).reshape(m, n)
+    gpu.poll_status()
+    scale = np.abs(ref).max()
+    assert np.max(np.abs(got - ref)) <= 2e-5 * scale + 1e-6
