@@ -392,13 +392,23 @@ typedef enum pssa_b200_tensor {
 } pssa_b200_tensor;
 
 /* Allocates device storage for a model of `cfg` and `max_streams` independent recurrent carries
- * (`PSSALayerV2::new`, src/pssa.rs:2019-2072, without the random init: weights are uploaded). */
+ * (`PSSALayerV2::new`, src/pssa.rs:2019-2072, without the random init: weights are uploaded, or drawn by
+ * pssa_b200_model_init_random below). */
 int32_t pssa_b200_model_create(pssa_b200_ctx* ctx, const pssa_b200_config* cfg, uint32_t max_streams,
                                pssa_b200_model** out);
 void pssa_b200_model_destroy(pssa_b200_model* model);
 /* Upload one parameter (host fp32). Replaces the reference backends' host-pointer-keyed weight cache and
  * its invalidation calls (src/cuda.rs:198-252, src/backend.rs:1113-1133): the caller re-uploads what changed. */
 int32_t pssa_b200_model_set_tensor(pssa_b200_model* model, int32_t layer, int32_t tensor, const float* data, size_t len);
+/* Read one parameter back (host fp32, `len` must be the tensor's length): what the reference reads straight from its
+ * host-resident `ParamMatrix` fields when it saves a checkpoint (src/checkpoint.rs) or inspects a model. */
+int32_t pssa_b200_model_get_tensor(pssa_b200_model* model, int32_t layer, int32_t tensor, float* out, size_t len);
+/* Random initialisation with the reference's generator and draw order, so that the model holds the tensors of
+ * `PSSALayerV2::new(cfg, seed)` bit for bit (src/pssa.rs:2019-2072, 630-690; src/linalg.rs:1-28, 338-344;
+ * src/adapter.rs:16-24): embedding, block 0, head, further blocks; norm gain 1, bias 0, MLP down and the adapter's up
+ * matrices zero, residual scales 1/sqrt(depth). Banks and carries are left as they are. `rng_state_out` (may be NULL)
+ * receives the generator state after the last draw, which the reference keeps in the model for later draws. */
+int32_t pssa_b200_model_init_random(pssa_b200_model* model, uint64_t seed, uint64_t* rng_state_out);
 /* Upload one block's bank (src/memory.rs:4-33): keys [cap,k], norm_sq [cap], values [cap,d], count,
  * write_head, confidence [cap], last_seen_step [cap]. Checks the invariants of src/checkpoint.rs:1060-1066. */
 int32_t pssa_b200_model_set_bank(pssa_b200_model* model, int32_t layer, const float* keys, const float* norm_sq,

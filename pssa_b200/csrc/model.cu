@@ -209,6 +209,27 @@ int32_t pssa_b200_model_set_tensor(pssa_b200_model* m, int32_t layer, int32_t id
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_model_get_tensor(pssa_b200_model* m, int32_t layer, int32_t id, float* out, size_t len) {
+    if (!m || !out) return mfail(m, PSSA_B200_ERR_INVALID_ARGUMENT, "pssa_b200_model_get_tensor: null argument");
+    pssa_b200_ctx* ctx = m->ctx;
+    bool model_level = id == T_EMBED || id == T_UNEMBED || id == T_RESIDUAL_SCALES;
+    bool block_level = id >= T_NORM_GAMMA && id <= T_AD_CONS;
+    if (!model_level && !block_level) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "get_tensor: unknown tensor id %d", id);
+    if (block_level && (layer < 0 || (size_t)layer >= m->depth))
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "get_tensor: layer %d outside depth %zu", layer, m->depth);
+    size_t want = tensor_len(m, id);
+    if (len != want) return fail(ctx, PSSA_B200_ERR_SHAPE, "get_tensor: tensor %d length %zu, expected %zu", id, len, want);
+    if (id == T_RESIDUAL_SCALES) {
+        for (size_t i = 0; i < len; ++i) out[i] = m->residual_scales[i];
+        return PSSA_B200_OK;
+    }
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const float* src = id == T_EMBED ? m->embed : id == T_UNEMBED ? m->unembed : m->blocks[layer].w[id];
+    PSSA_CUDA(ctx, cudaMemcpyAsync(out, src, len * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_model_set_bank(pssa_b200_model* m, int32_t layer, const float* keys, const float* norm_sq,
                                  const float* values, uint64_t count, uint64_t write_head, const float* confidence,
                                  const uint64_t* last_seen_step) {

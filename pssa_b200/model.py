@@ -71,6 +71,17 @@ class PSSAModel:
         a = np.ascontiguousarray(data, np.float32).ravel()
         self.gpu._check(self._lib.pssa_b200_model_set_tensor(self._h, layer, tensor, _ptr(a), a.size))
 
+    def get_tensor(self, layer: int, tensor: int, length: int):
+        out = np.empty(length, np.float32)
+        self.gpu._check(self._lib.pssa_b200_model_get_tensor(self._h, layer, tensor, _ptr(out), out.size))
+        return out
+
+    def init_random(self, seed: int) -> int:
+        """`PSSALayerV2::new(cfg, seed)`'s tensors (src/pssa.rs:2019-2072); returns the generator state after the last draw."""
+        state = C.c_uint64()
+        self.gpu._check(self._lib.pssa_b200_model_init_random(self._h, seed, C.byref(state)))
+        return int(state.value)
+
     def set_bank(self, layer, keys, norm_sq, values, count, write_head=0, confidence=None, last_seen_step=None):
         keys = np.ascontiguousarray(keys, np.float32)
         norm_sq = np.ascontiguousarray(norm_sq, np.float32)

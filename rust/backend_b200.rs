@@ -281,6 +281,18 @@ impl B200Model {
         self.call(|m| unsafe { sys::pssa_b200_model_set_tensor(m, layer, tensor, data.as_ptr(), data.len()) })
     }
 
+    /// Reads a parameter back into a host slice (what checkpoint saving reads from `ParamMatrix` fields).
+    pub fn get_tensor(&self, layer: i32, tensor: i32, out: &mut [f32]) -> Result<(), String> {
+        self.call(|m| unsafe { sys::pssa_b200_model_get_tensor(m, layer, tensor, out.as_mut_ptr(), out.len()) })
+    }
+
+    /// `PSSALayerV2::new(cfg, seed)`'s random init on the device model; returns the generator state to keep.
+    pub fn init_random(&self, seed: u64) -> Result<u64, String> {
+        let mut state = 0u64;
+        self.call(|m| unsafe { sys::pssa_b200_model_init_random(m, seed, &mut state) })?;
+        Ok(state)
+    }
+
     /// Upload one block's `HyperbolicEpisodicBankV2` (src/memory.rs:4-33).
     #[allow(clippy::too_many_arguments)]
     pub fn set_bank(&self, layer: i32, keys: &[f32], norm_sq: &[f32], values: &[f32], count: usize, write_head: usize, confidence: &[f32],

@@ -454,6 +454,18 @@ extern "C" {
         data: *const f32,
         len: usize,
     ) -> i32;
+    pub fn pssa_b200_model_get_tensor(
+        model: *mut pssa_b200_model,
+        layer: i32,
+        tensor: i32,
+        out: *mut f32,
+        len: usize,
+    ) -> i32;
+    pub fn pssa_b200_model_init_random(
+        model: *mut pssa_b200_model,
+        seed: u64,
+        rng_state_out: *mut u64,
+    ) -> i32;
     pub fn pssa_b200_model_set_bank(
         model: *mut pssa_b200_model,
         layer: i32,
