@@ -567,6 +567,11 @@ int32_t pssa_b200_model_set_seqpar(pssa_b200_model* m, uint32_t rank, uint32_t w
                                    size_t capacity, pssa_b200_exchange_fn exchange, void* arg);
 /* Upper bound on token rows processed per pass (activation workspace = about 40 KB per row at d 768). */
 int32_t pssa_b200_model_set_max_rows(pssa_b200_model* model, size_t max_rows);
+/* Allocates now everything a later call of at most `rows` token rows (capped by max_rows per pass) over at most `lanes`
+ * lanes would allocate on first use: the activation workspace, the time-chunk buffers and the sampler state. The
+ * reference sizes its scratch at construction (`ChunkActivationTape::new`, src/pssa.rs:630-700; packed lanes
+ * src/cuda/packed.rs:282-366); here it grows on demand unless reserved, and growth synchronises the stream. */
+int32_t pssa_b200_model_reserve(pssa_b200_model* model, size_t rows, size_t lanes);
 
 #ifdef __cplusplus
 }

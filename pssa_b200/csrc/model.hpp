@@ -133,6 +133,7 @@ struct pssa_b200_model {
     struct Chunks {
         size_t capacity = 0;        // virtual lanes the buffers hold
         uint32_t *off = nullptr, *len = nullptr;
+        std::vector<uint32_t> host_off, host_len;  // what `off` / `len` hold on the device: an unchanged description is not uploaded again
         float* records = nullptr;   // [capacity][d + d*s]  (local mode; the sharded mode uses sp.send)
         float* carry_in = nullptr;  // [capacity][d*s]
     } chunks;

@@ -200,10 +200,15 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
                 const uint32_t a = (uint32_t)((uint64_t)h_len[l] * c / n_chunks), e = (uint32_t)((uint64_t)h_len[l] * (c + 1) / n_chunks);
                 v_off[l * n_chunks + c] = h_off[l] + a, v_len[l * n_chunks + c] = e - a;
             }
-        // pageable source: the copies complete before these vectors go out of scope
-        PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.off, v_off.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
-        PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.len, v_len.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
-        PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        // Uploaded only when the description changed: a repeated call (every step of a benchmark, every pass of a long
+        // prompt with equal pass lengths) makes no copy and no synchronisation. The source vectors live in the model;
+        // the one wait below is for earlier copies that may still read the vectors about to be replaced.
+        if (v_off != m->chunks.host_off || v_len != m->chunks.host_len) {
+            PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // earlier copies out of the vectors about to be replaced
+            m->chunks.host_off.swap(v_off), m->chunks.host_len.swap(v_len);
+            PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.off, m->chunks.host_off.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
+            PSSA_CUDA(ctx, cudaMemcpyAsync(m->chunks.len, m->chunks.host_len.data(), vlanes * 4, cudaMemcpyHostToDevice, ctx->stream));
+        }
     }
     const bool observe = m->obs.enabled && n_obs > 0;
     const size_t obs_rec = m->cap + m->k + 2 * m->d;
@@ -915,6 +920,16 @@ int32_t pssa_b200_model_decode_step(pssa_b200_model* m, const uint32_t* streams,
     std::vector<uint32_t> off(n), len(n, 1);
     for (size_t i = 0; i < n; ++i) off[i] = (uint32_t)i;
     return pssa_b200_model_prefill_batch(m, ids, off.data(), len.data(), streams, n, logits, greedy);
+}
+
+int32_t pssa_b200_model_reserve(pssa_b200_model* m, size_t rows, size_t lanes) {
+    if (!m || rows == 0 || lanes == 0) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "reserve: rows and lanes must be positive");
+    pssa_b200_ctx* ctx = m->ctx;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t rc;
+    if ((rc = ensure_workspace(m, std::min(rows, m->max_rows), lanes))) return rc;
+    if ((rc = ensure_chunks(m, lanes * 16))) return rc;  // the most time chunks a lane is ever cut into
+    return ensure_sampler(m, lanes);
 }
 
 }  // extern "C"

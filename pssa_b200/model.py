@@ -71,6 +71,10 @@ class PSSAModel:
         a = np.ascontiguousarray(data, np.float32).ravel()
         self.gpu._check(self._lib.pssa_b200_model_set_tensor(self._h, layer, tensor, _ptr(a), a.size))
 
+    def reserve(self, rows: int, lanes: int):
+        """Allocate now what calls of at most `rows` rows over `lanes` lanes would allocate on first use."""
+        self.gpu._check(self._lib.pssa_b200_model_reserve(self._h, rows, lanes))
+
     def get_tensor(self, layer: int, tensor: int, length: int):
         out = np.empty(length, np.float32)
         self.gpu._check(self._lib.pssa_b200_model_get_tensor(self._h, layer, tensor, _ptr(out), out.size))

@@ -441,3 +441,26 @@ def test_decode_graph_with_lane_groups_replays_the_eager_tokens(gpu):
     gpu.set_stream(None)
     gm.close()
     gm2.close()
+
+
+def test_reserved_model_allocates_nothing_during_calls(gpu):
+    """`pssa_b200_model_reserve`: after it, prefill (plain and time-chunked) and decode calls within the reserved size
+    leave the device's free memory unchanged (growth of the workspace, the chunk buffers and the sampler state is what
+    would otherwise allocate, and synchronise, in the middle of a call)."""
+    import torch
+    import pssa_b200
+    cfg = dict(depth=2, d_vocab=101, d_latent=64, d_state=16, d_mem_key=16, mem_capacity=64)
+    om = O.Model.new(cfg["depth"], cfg["d_vocab"], cfg["d_latent"], cfg["d_state"], cfg["d_mem_key"], cfg["mem_capacity"], tau_mem=0.1, seed=2)
+    fill_synthetic(om, 2)
+    gm = pssa_b200.PSSAModel(gpu, tau_mem=0.1, streams=4, precision=1, **cfg)
+    upload(om, gm)
+    gm.reserve(4 * 700, 4)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    rng = np.random.default_rng(3)
+    gm.prefill_batch([rng.integers(1, cfg["d_vocab"], n) for n in (700, 50, 1, 333)])
+    gm.prefill_inference(rng.integers(1, cfg["d_vocab"], 700))  # one long lane: the time-chunked path
+    gm.decode_step([1, 2, 3, 4], want_logits=True, want_greedy=True)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    gm.close()
