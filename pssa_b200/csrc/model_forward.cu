@@ -388,7 +388,16 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         if (k % 64 == 0) rp.k_split = b.ksplit_bf16, rp.k_stat = b.kstat;
         if (!exact && k % 64 == 0) rp.q_split = v.q_split, rp.q_stat = v.q_stat;
         rp.fixup_count = ws.fixup + gi;  // exact top-k in one kernel when the shape allows it
-        if (!obs_now) rp.weights = (rp.top_k != 0 && rp.top_k < rp.count && retrieve_fused_eligible(rp)) ? nullptr : v.weights;
+        const bool topk_now = rp.top_k != 0 && rp.top_k < rp.count;
+        const bool topk_fused = topk_now && retrieve_fused_eligible(rp);
+        if (topk_now && !topk_fused) {
+            // A top-k read the one-kernel path cannot take (capacity, key width or fill outside its shapes) keeps the
+            // reference's f64 distances in both precisions: a selection made from approximate distances can differ from the
+            // reference's where the k-th and (k+1)-th slots are closer than the approximation, and identical slot sets
+            // are worth more here than the speed of the fast distances.
+            rp.f32_distance = 0, rp.q_split = nullptr, rp.q_stat = nullptr;
+        }
+        if (!obs_now) rp.weights = topk_fused ? nullptr : v.weights;
         // All-slots read in the bf16 mode: W_proj (sum_s w_s v_s) = sum_s w_s (W_proj v_s). The bank's values were carried
         // through W_proj at upload (vpsplit_bf16), so the product of the weight rows with them IS the memory projection and
         // takes the gate epilogue directly: the value read stops after the softmax (no m, no separate W_proj launch). The
