@@ -939,6 +939,41 @@ def run_decode(args):
     gpu.close()
 
 
+def run_gemm_plain(args):
+    """One plain bf16 tensor-core product alone (8192 x 8192 x 8192, fp32 out), the shape the GEMM kernel's own ceiling
+    is quoted on; runs as CTA pairs. For profiler captures and for comparing against MEASURED_PEAKS.json's cuBLAS rate."""
+    import torch
+
+    import pssa_b200
+    torch.cuda.set_device(0)
+    gpu = pssa_b200.B200Dispatch(0)
+    stream = torch.cuda.current_stream()
+    gpu.set_stream(stream)
+    m = n = k = 8192
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(n, k, device="cuda") * 0.02
+    out = torch.empty(m, n, device="cuda")
+    for _ in range(max(3, args.warmup)):
+        gpu.gemm_xwt_dev(x, w, m, n, k, out)
+    torch.cuda.synchronize()
+    gpu.profile_begin()  # the entry point also rounds both operands to bf16 (two small kernels): time the product alone
+    for _ in range(args.steps):
+        gpu.gemm_xwt_dev(x, w, m, n, k, out)
+    torch.cuda.synchronize()
+    prof = gpu.profile_end()
+    launches, ms = next(v for name, v in prof.items() if name.startswith("gemm_bf16_tcgen05_kernel"))
+    ms /= launches
+    _, peak_tf, kind = measured_peaks()
+    tf = 2.0 * m * n * k / (ms / 1e3) / 1e12
+    print(json.dumps({"metric": "gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+                      "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "gemm_plain: 8192 x 8192 x 8192 bf16 operands, fp32 accumulate and output, clusters of two CTAs on 256 x 256 tiles"},
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
+                                   "peak_kind": f"of {kind} (sustained cuBLAS bf16)"},
+                      "gpu_launches": int(gpu.launch_count())}))
+    gpu.close()
+
+
 def main():
     global LANES
     ap = argparse.ArgumentParser()
@@ -950,9 +985,9 @@ def main():
     ap.add_argument("--lanes", type=int, default=LANES,
                     help="sequences per GPU; anything but the default is a reduced case for profiler captures, not the benchmark")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline and parity sample (profiler captures)")
-    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5", "scan_c2", "retrieval_c3", "decode_c5"],
+    ap.add_argument("--workload", default="prefill_c4", choices=["prefill_c4", "seqpar_c5", "scan_c2", "retrieval_c3", "decode_c5", "gemm_plain"],
                     help="prefill_c4 is the benchmark; seqpar_c5 is the long-context time-sharded prefill (N >= 2); scan_c2 is "
-                         "the scan operator alone; retrieval_c3 is the one-kernel top-8 memory read alone; decode_c5 is the 256-stream greedy decode alone")
+                         "the scan operator alone; retrieval_c3 is the one-kernel top-8 memory read alone; decode_c5 is the 256-stream greedy decode alone; gemm_plain is one 8192^3 product")
     ap.add_argument("--seq-len", type=int, default=65536, help="sequence length of the seqpar_c5 workload")
     args = ap.parse_args()
     if args.workload == "scan_c2":
@@ -961,6 +996,8 @@ def main():
         return run_retrieval_c3(args)
     if args.workload == "decode_c5":
         return run_decode(args)
+    if args.workload == "gemm_plain":
+        return run_gemm_plain(args)
     if args.lanes != LANES:
         global WORKLOAD
         WORKLOAD = WORKLOAD.replace(f"{LANES} sequences", f"{args.lanes} sequences (REDUCED CASE, not the benchmark)")
