@@ -424,13 +424,29 @@ __global__ void __launch_bounds__(256) seqpar_fold_kernel(const float* __restric
     float* st = state + (size_t)(lane_slots ? lane_slots[lane] : lane) * state_stride;
     const float a = rates[e];
     float h = st[e];
-    for (int k = 0; k < world; ++k) {
-        for (int c = 0; c < chunks; ++c) {
-            const size_t v = (size_t)lane * chunks + c;
-            if (k == rank) carry_in[v * ds + e] = h;
-            const float* r = gathered + (size_t)k * rank_stride + v * rec;
-            const float pk = expf(__fmul_rn(a, r[i]));
-            h = __fadd_rn(__fmul_rn(pk, h), r[d + e]);
+    // the records are independent of h: four of them are requested (and their decay factors formed) before the
+    // dependent multiply-adds, so the walk is not one memory round trip per record
+    const int n = world * chunks;
+    for (int j0 = 0; j0 < n; j0 += 4) {
+        float pk[4], add[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u;
+            if (j < n) {
+                const int k = j / chunks, c = j - k * chunks;
+                const float* r = gathered + (size_t)k * rank_stride + ((size_t)lane * chunks + c) * rec;
+                pk[u] = expf(__fmul_rn(a, __ldg(r + i)));
+                add[u] = __ldg(r + d + e);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = j0 + u;
+            if (j < n) {
+                const int k = j / chunks, c = j - k * chunks;
+                if (k == rank) carry_in[((size_t)lane * chunks + c) * ds + e] = h;
+                h = __fadd_rn(__fmul_rn(pk[u], h), add[u]);
+            }
         }
     }
     st[e] = h;
