@@ -557,6 +557,174 @@ __global__ void __launch_bounds__(256) softmax_all_slots_kernel(RetrieveParams p
     }
 }
 
+// A few hundred queries at most (a decode step): projection, distances, softmax and the weight pieces of the all-slots
+// read in ONE launch, one CTA per four queries (a key row is loaded once for the four). With so few rows each of the
+// separate kernels is a chain of launch and memory latencies, not work; here the rows never leave the CTA. Same
+// formulas as the separate fast-mode kernels: the projection in f64 (lane-partial sums combined in a fixed order
+// instead of one sequential sum: the f64 result differs in its last bits, the f32 point almost never), squared
+// differences accumulated in fp32 (differences first), the hardware-approximation distance, ex2.approx weights with one
+// reciprocal per row, bf16 pieces for the tensor-core value read. Only for the bf16-grade consumers (value_terms 1 or 3).
+constexpr int kSmallRows = 4;
+__global__ void __launch_bounds__(256) retrieve_small_rows_kernel(RetrieveParams p) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int R = kSmallRows;
+    __shared__ __align__(16) float pt[R][256];  // the queries, then the projected points (dk <= 256)
+    __shared__ float red[8][R];
+    __shared__ float row_inv[R];                // 1 / (1 - |p|^2)
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int dk = p.dk, cap = p.cap, count = p.count;
+    const size_t q0 = (size_t)blockIdx.x * R;
+    const size_t ldq = p.ldq ? p.ldq : (size_t)dk;
+    for (int idx = tid; idx < R * dk; idx += 256) {
+        const int r = idx / dk, i = idx - r * dk;
+        pt[r][i] = q0 + r < p.rows ? __ldg(p.q + (q0 + r) * ldq + i) : 0.0f;
+    }
+    __syncthreads();
+    if (warp < R) {  // one warp per query: src/memory.rs:198-211, 181-188
+        const int r = warp;
+        const size_t q = q0 + r;
+        double scale = 1.0;
+        if (p.q_is_euclidean) {
+            double r2 = 0.0;
+            for (int i = lane; i < dk; i += 32) r2 += (double)pt[r][i] * (double)pt[r][i];
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) r2 += __shfl_xor_sync(0xffffffffu, r2, m);
+            const double rad = sqrt(r2);
+            const double max_radius = 1.0 - 8.0 * (double)FLT_EPSILON;
+            scale = (rad == 0.0) ? 1.0 : fmin(rad / (1.0 + rad), max_radius) / rad;
+            if (p.q_norm && lane == 0 && q < p.rows) p.q_norm[q] = (float)fmin(rad, (double)FLT_MAX);
+        }
+        double n2 = 0.0;
+        for (int i = lane; i < dk; i += 32) {
+            const float pv = p.q_is_euclidean ? (float)((double)pt[r][i] * scale) : pt[r][i];
+            pt[r][i] = pv;
+            if (p.q_pnc && q < p.rows) p.q_pnc[q * dk + i] = pv;
+            n2 += (double)pv * (double)pv;
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) n2 += __shfl_xor_sync(0xffffffffu, n2, m);
+        if (lane == 0) {
+            const float qs = (n2 < 1.0 && (float)n2 == 1.0f) ? __uint_as_float(0x3f7fffffu) : (float)n2;
+            row_inv[r] = (float)(1.0 / (1.0 - (double)qs));
+        }
+    }
+    __syncthreads();
+    constexpr int PER = 4;  // slots per thread: capacity <= 1024
+    float d[R][PER];
+    float mn[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) mn[r] = FLT_MAX;
+    const bool vec = (dk & 3) == 0 && (reinterpret_cast<uintptr_t>(p.keys) & 15) == 0;
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+        const int s = tid + u * 256;
+#pragma unroll
+        for (int r = 0; r < R; ++r) d[r][u] = CUDART_INF_F;  // slots past `count` hold nothing: weight zero
+        if (s < count) {
+            const float* krow = p.keys + (size_t)s * dk;
+            float sq[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) sq[r] = 0.0f;
+            if (vec && (dk & 31) == 0) {
+                // eight 16-byte loads of the key row in flight before they are used: the row comes from L2 and the walk
+                // is otherwise one round trip per load
+                for (int i0 = 0; i0 < dk; i0 += 32) {
+                    float4 kv[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) kv[j] = __ldg(reinterpret_cast<const float4*>(krow + i0) + j);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                        for (int r = 0; r < R; ++r) {
+                            const float4 pv = *reinterpret_cast<const float4*>(&pt[r][i0 + 4 * j]);
+                            const float a = pv.x - kv[j].x, b = pv.y - kv[j].y, c = pv.z - kv[j].z, e = pv.w - kv[j].w;
+                            sq[r] = fmaf(a, a, sq[r]), sq[r] = fmaf(b, b, sq[r]), sq[r] = fmaf(c, c, sq[r]), sq[r] = fmaf(e, e, sq[r]);
+                        }
+                    }
+                }
+            } else if (vec) {
+                for (int i = 0; i < dk; i += 4) {
+                    const float4 kv = __ldg(reinterpret_cast<const float4*>(krow + i));
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const float4 pv = *reinterpret_cast<const float4*>(&pt[r][i]);
+                        const float a = pv.x - kv.x, b = pv.y - kv.y, c = pv.z - kv.z, e = pv.w - kv.w;
+                        sq[r] = fmaf(a, a, sq[r]), sq[r] = fmaf(b, b, sq[r]), sq[r] = fmaf(c, c, sq[r]), sq[r] = fmaf(e, e, sq[r]);
+                    }
+                }
+            } else {
+                for (int i = 0; i < dk; ++i) {
+                    const float kv = __ldg(krow + i);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const float a = pt[r][i] - kv;
+                        sq[r] = fmaf(a, a, sq[r]);
+                    }
+                }
+            }
+            const float inv_k = __fdividef(1.0f, 1.0f - __ldg(p.norm_sq + s));
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                d[r][u] = fast_poincare_distance(sq[r] * (row_inv[r] * inv_k));
+                mn[r] = fminf(mn[r], d[r][u]);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        mn[r] = warp_min(mn[r]);
+        if (lane == 0) red[warp][r] = mn[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        float m = red[0][r];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fminf(m, red[w][r]);
+        mn[r] = m;
+    }
+    __syncthreads();
+    if (p.min_dist && tid < R && q0 + tid < p.rows) p.min_dist[q0 + tid] = mn[tid];
+    const float inv_tau = 1.0f / p.tau;
+    const bool lite = inv_tau < CUDART_INF_F;  // a temperature too small for a finite reciprocal keeps the exact form
+    const float scale2 = inv_tau * 1.4426950408889634f;
+    float sum[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        sum[r] = 0.0f;
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            d[r][u] = lite ? exp2f_approx((mn[r] - d[r][u]) * scale2) : weight_of<false>(mn[r], d[r][u], p.tau);
+            sum[r] += d[r][u];
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], m);
+        if (lane == 0) red[warp][r] = sum[r];
+    }
+    __syncthreads();
+    const bool second = p.value_terms != 1;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const size_t q = q0 + r;
+        if (q >= p.rows) break;
+        const float total = ((red[0][r] + red[1][r]) + (red[2][r] + red[3][r])) + ((red[4][r] + red[5][r]) + (red[6][r] + red[7][r]));
+        const float inv_sum = __fdiv_rn(1.0f, total);
+        __nv_bfloat16* ws = reinterpret_cast<__nv_bfloat16*>(p.w_split) + q * 3 * (size_t)cap;
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int s = tid + u * 256;
+            if (s < cap) {
+                const float wn = d[r][u] * inv_sum;
+                if (!p.skip_weights && p.weights) p.weights[q * cap + s] = wn;
+                const __nv_bfloat16 pa = __float2bfloat16_rn(wn);
+                ws[s] = pa;
+                if (second) ws[cap + s] = __float2bfloat16_rn(wn - __bfloat162float(pa));
+            }
+        }
+    }
+}
+
 // One warp per query. Distances are read from `weights` and replaced by the weights.
 template <bool EXACT>
 __global__ void __launch_bounds__(256) softmax_topk_kernel(RetrieveParams p) {
@@ -836,7 +1004,14 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     const size_t smem_f = (size_t)(kpad4 / 2) * QT * sizeof(float2) + ((size_t)2 * STL * (kpad4 + 4) + QT + 2 * STL) * sizeof(float);
     const bool tc_dist = !exact && p.q_split && p.k_split && p.q_stat && p.k_stat && p.dk % 64 == 0 && p.dk <= 256 &&
                          (!p.q_pnc || (reinterpret_cast<uintptr_t>(p.q_pnc) & 7) == 0);
-    if (tc_dist) {
+    const bool small_rows = !exact && !(p.top_k != 0 && p.top_k < p.count) && p.rows <= 1024 && p.count > 0 && p.w_split &&
+                            (p.value_terms == 1 || p.value_terms == 3) && p.dk <= 256 && p.cap <= 1024 && (p.skip_weights || p.weights) &&
+                            (p.f32_distance || tc_dist);
+    if (small_rows) {
+        // a decode step: projection, distances, softmax and weight pieces in one launch (see the kernel)
+        PSSA_CUDA(ctx, launch_dependent(retrieve_small_rows_kernel, dim3((unsigned)((p.rows + kSmallRows - 1) / kSmallRows)), dim3(256), 0, ctx->stream, p));
+        if ((rc = after_launch(ctx, "retrieve_small_rows_kernel")) != PSSA_B200_OK) return rc;
+    } else if (tc_dist) {
         // distances from the inner product on the tensor cores: projection + three-way split of the queries, then one
         // product against the split keys whose epilogue turns p.k into d(p, k)
         const size_t smem_p = (size_t)QT * (p.dk + 1) * sizeof(float);
@@ -880,7 +1055,9 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     }
     const bool all_regs = !exact && !(p.top_k != 0 && p.top_k < p.count) && p.count > 0 && p.cap % 128 == 0 && p.cap <= 1024 &&
                           (reinterpret_cast<uintptr_t>(p.weights) & 15) == 0;
-    if (all_regs) {
+    if (small_rows) {
+        // the weights and their pieces are already formed
+    } else if (all_regs) {
         // a few rows per warp, so that a row's loads overlap the arithmetic of the one before
         const size_t want = (p.rows + 31) / 32, full = (size_t)ctx->sm_count * 8;
         const unsigned grid = (unsigned)std::min(wblocks, std::max(want, std::min(wblocks, full)));
