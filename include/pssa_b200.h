@@ -524,6 +524,10 @@ int32_t pssa_b200_model_get_observation(pssa_b200_model* m, uint32_t layer, uint
  * on the HOST.
  */
 int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64_t seed);
+/* Appends ids to a stream's repetition window without sampling: the reference's penalty reads the last 64 entries of
+ * `generated_ids`, which starts as a copy of the PROMPT (src/inference.rs:343-345, 114-121), so a host loop pushes the
+ * prompt here before its first sampled step. Ids outside the vocabulary are refused like prompt ids. */
+int32_t pssa_b200_model_sampler_push(pssa_b200_model* m, uint32_t stream, const uint64_t* ids, size_t n);
 int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n,
                                             const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out,
                                             float* confidence_out);

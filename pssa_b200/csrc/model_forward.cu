@@ -857,6 +857,32 @@ int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_model_sampler_push(pssa_b200_model* m, uint32_t stream, const uint64_t* ids, size_t n) {
+    if (!m || (!ids && n)) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "sampler_push: null argument");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (stream >= m->max_streams) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "stream %u outside %u streams", stream, m->max_streams);
+    for (size_t i = 0; i < n; ++i)
+        if (ids[i] >= m->v) return fail(ctx, PSSA_B200_ERR_TOKEN, "prompt ID %llu outside model vocabulary", (unsigned long long)ids[i]);
+    if (n == 0) return PSSA_B200_OK;
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    int32_t rc = ensure_sampler(m, 1);
+    if (rc) return rc;
+    // the window holds the last 64 ids, oldest first (src/inference.rs:114-121 reads `generated_ids[len - 64..]`)
+    unsigned count = 0, window[64];
+    PSSA_CUDA(ctx, cudaMemcpyAsync(&count, m->sampler.count + stream, 4, cudaMemcpyDeviceToHost, ctx->stream));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(window, m->sampler.recent + (size_t)stream * 64, sizeof(window), cudaMemcpyDeviceToHost, ctx->stream));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    std::vector<unsigned> all(window, window + std::min<unsigned>(count, 64u));
+    for (size_t i = n > 64 ? n - 64 : 0; i < n; ++i) all.push_back((unsigned)ids[i]);
+    const size_t keep = std::min<size_t>(all.size(), 64), from = all.size() - keep;
+    for (size_t i = 0; i < keep; ++i) window[i] = all[from + i];
+    count = (unsigned)keep;
+    PSSA_CUDA(ctx, cudaMemcpyAsync(m->sampler.recent + (size_t)stream * 64, window, keep * 4, cudaMemcpyHostToDevice, ctx->stream));
+    PSSA_CUDA(ctx, cudaMemcpyAsync(m->sampler.count + stream, &count, 4, cudaMemcpyHostToDevice, ctx->stream));
+    PSSA_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_model_decode_step_sampled(pssa_b200_model* m, const uint32_t* streams, const uint64_t* ids, size_t n,
                                             const pssa_b200_sampling* cfg, uint32_t flags, uint64_t* ids_out, float* confidence_out) {
     if (!m || !ids || !cfg || !ids_out) return fail(m ? m->ctx : nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "decode_step_sampled: null argument");

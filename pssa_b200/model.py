@@ -277,6 +277,45 @@ class PSSAModel:
                                                                       N.SAMPLE_EXACT if exact else 0, _ptr(out), _ptr(conf)))
         return (out, conf) if want_confidence else out
 
+    def sampler_push(self, ids, stream=0):
+        """Append ids (the prompt) to a stream's repetition window (`generated_ids` starts as the prompt, src/inference.rs:343-345)."""
+        ids = np.ascontiguousarray(ids, np.uint64)
+        self.gpu._check(self._lib.pssa_b200_model_sampler_push(self._h, stream, _ptr(ids), ids.size))
+
+    def generate(self, prompt_ids, max_new_tokens=50, temperature=0.70, top_p=0.85, top_k=24, repetition_penalty=1.25, seed=1337,
+                 stream=0, cancelled=None, on_token=None, scored=False, exact=False):
+        """The id-level loop of `PSSAInferenceEngine::try_generate_chat_turn_impl` (src/inference.rs:317-418; tokenizer and
+        text assembly stay with the caller): reset the carry, seed the generator, the prompt becomes the head of the
+        repetition window, prefill, then `max_new_tokens` steps of forward + `sample` on the device. The first sampled
+        token comes from the logits of the last prompt token, which is run as the first sampled step (prefill == token
+        loop, src/inference.rs:1069-1113). `cancelled()` is polled before the prompt and before every step and returns
+        what was generated so far; `on_token(count, previous_id, selected_id, probability)` follows the reference's
+        callback / observer order. Returns (ids, raw probabilities or None)."""
+        prompt = np.ascontiguousarray(prompt_ids, np.uint64)
+        if prompt.size == 0:
+            raise ValueError("prompt is empty after tokenization")  # src/inference.rs:333-335
+        if cancelled is not None and cancelled():
+            return np.zeros(0, np.uint64), (np.zeros(0, np.float32) if scored else None)
+        self.reset_recurrent_state(stream)
+        self.sampler_seed(stream, seed)
+        self.sampler_push(prompt, stream)
+        if prompt.size > 1:
+            ok, _ = self.prefill_inference(prompt[:-1], want_logits=False, cancelled=cancelled, stream=stream)
+            if not ok:
+                return np.zeros(0, np.uint64), (np.zeros(0, np.float32) if scored else None)
+        out, probs, tok = [], [], int(prompt[-1])
+        for step in range(max_new_tokens):
+            if cancelled is not None and cancelled():
+                break
+            got = self.decode_step_sampled([tok], [stream], temperature, top_p, top_k, repetition_penalty, exact=exact,
+                                           want_confidence=scored)
+            nxt, p = (int(got[0][0]), float(got[1][0])) if scored else (int(got[0]), 0.0)
+            if on_token is not None:
+                on_token(step + 1, tok, nxt, p)
+            out.append(nxt), probs.append(p)
+            tok = nxt
+        return np.array(out, np.uint64), (np.array(probs, np.float32) if scored else None)
+
     def generate_greedy(self, prompt_ids, n_new, stream=0):
         """Prefill + greedy decode (src/inference.rs:348-418 at temperature 0): returns the generated ids."""
         _, g = self.prefill_batch([prompt_ids], [stream], want_logits=False, want_greedy=True)

@@ -281,6 +281,11 @@ impl B200Model {
         self.call(|m| unsafe { sys::pssa_b200_model_set_tensor(m, layer, tensor, data.as_ptr(), data.len()) })
     }
 
+    /// Appends the prompt to a stream's repetition window (`generated_ids` starts as a copy of the prompt).
+    pub fn sampler_push(&self, stream: u32, ids: &[u64]) -> Result<(), String> {
+        self.call(|m| unsafe { sys::pssa_b200_model_sampler_push(m, stream, ids.as_ptr(), ids.len()) })
+    }
+
     /// Reads a parameter back into a host slice (what checkpoint saving reads from `ParamMatrix` fields).
     pub fn get_tensor(&self, layer: i32, tensor: i32, out: &mut [f32]) -> Result<(), String> {
         self.call(|m| unsafe { sys::pssa_b200_model_get_tensor(m, layer, tensor, out.as_mut_ptr(), out.len()) })

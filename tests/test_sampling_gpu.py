@@ -149,3 +149,60 @@ def test_model_level_sampled_decode_follows_the_restatement(gpu):
     with pytest.raises(pssa_b200.B200Error, match="top-p must be finite"):
         gm.decode_step_sampled(toks, [0, 1], top_p=1.5)
     gm.close()
+
+
+def test_generate_loop_follows_the_engine_order_with_the_prompt_in_the_repetition_window(gpu):
+    """`PSSAModel.generate`: reset, seed, the PROMPT heads the repetition window (`generated_ids` starts as a copy of it,
+    src/inference.rs:343-345), prefill, then forward + sample per step. The CPU side replays the engine's loop with the
+    restatement of `sample` on the oracle's logits, following the device's choice after each step so that a draw landing
+    within an ulp of a candidate boundary cannot fork the two sequences."""
+    import pssa_b200
+    from helpers import fill_synthetic, upload
+    v = 200
+    om = O.Model.new(2, v, 48, 16, 16, 20, tau_mem=0.1, seed=5)
+    fill_synthetic(om, 5, std=0.3)
+    gm = pssa_b200.PSSAModel(gpu, 2, v, 48, 16, 16, 20, tau_mem=0.1, streams=1, precision=1)
+    upload(om, gm)
+    cfg = dict(temperature=0.9, top_p=0.9, top_k=12, repetition_penalty=1.4)
+    prompt = [5, 9, 2, 77, 9, 9, 31]
+    ref = om.clone()
+    ref.reset_recurrent_state()
+    _, _, logits = ref.prefill_inference(prompt)
+    state = {"rng": 4242, "logits": logits, "history": list(prompt), "mismatch": 0, "calls": 0, "prob_err": 0.0}
+
+    def on_token(count, previous, selected, probability):
+        state["calls"] += 1
+        assert count == state["calls"] and previous == state["history"][-1]
+        lg = state["logits"].copy()
+        raw = np.exp(lg - lg.max())
+        state["prob_err"] = max(state["prob_err"], abs(probability - float(raw[selected] / raw.sum())))
+        ref_id, state["rng"], _ = O.sample(state["rng"], lg, state["history"], **cfg)
+        state["mismatch"] += int(ref_id != selected)
+        state["history"].append(int(selected))
+        state["logits"] = ref.forward_inference(int(selected))
+
+    ids, probs = gm.generate(prompt, max_new_tokens=24, seed=4242, on_token=on_token, scored=True, exact=True, **cfg)
+    assert len(ids) == 24 and state["calls"] == 24 and state["mismatch"] <= 1 and state["prob_err"] <= 2e-4
+    assert list(ids) == state["history"][len(prompt):] and probs.shape == (24,)
+    # the prompt really is in the window: without it the penalised logits of the first step, and so the ids, differ
+    gm.reset_recurrent_state(0)
+    gm.sampler_seed(0, 4242)
+    gm.prefill_inference(prompt[:-1], want_logits=False)
+    first_without = int(gm.decode_step_sampled([prompt[-1]], [0], exact=True, **dict(cfg, temperature=0.0))[0])
+    gm.reset_recurrent_state(0)
+    gm.sampler_seed(0, 4242)
+    gm.sampler_push(prompt, 0)
+    gm.prefill_inference(prompt[:-1], want_logits=False)
+    first_with = int(gm.decode_step_sampled([prompt[-1]], [0], exact=True, **dict(cfg, temperature=0.0))[0])
+    lg = logits.copy()
+    greedy_plain = int(np.argmax(lg[1:]) + 1)
+    pen = lg.copy()
+    for t in prompt[-64:]:
+        pen[t] = pen[t] / cfg["repetition_penalty"] if pen[t] > 0 else pen[t] * cfg["repetition_penalty"]
+    assert first_without == greedy_plain and first_with == int(np.argmax(pen[1:]) + 1)
+    # cancellation before the first step returns nothing; ids outside the vocabulary are refused when pushed
+    ids, _ = gm.generate(prompt, max_new_tokens=5, cancelled=lambda: True)
+    assert len(ids) == 0
+    with pytest.raises(pssa_b200.B200Error, match="outside model vocabulary"):
+        gm.sampler_push([v + 3], 0)
+    gm.close()
