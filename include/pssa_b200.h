@@ -516,6 +516,17 @@ int32_t pssa_b200_model_get_observation(pssa_b200_model* m, uint32_t layer, uint
                                         float* m_val, float* z_final);
 
 /*
+ * `insert_training_memory_at` (src/pssa.rs:3705-3737) on the model's device-resident banks: if loss > 3.5, every block
+ * gets one protected insert (refractory gate and ring insert of pssa_b200_bank_insert_protected_dev; hybrid read is
+ * not supported, so never the gated variant) whose key is `q_poincare` and whose value is `z_final` of the LAST token of
+ * observed lane `index` of the previous forward call -- the observer scratch, which must be enabled. `step` is the
+ * reference's step counter (the gate's clock). slots_out [depth] (NULL to skip): the slot written, -1 defended, -2
+ * refused, -3 nothing attempted (loss <= 3.5). A bank that changed gets its derived copies (key and value pieces, values
+ * carried through W_proj) rebuilt before the next forward call. On replicas, apply the same writes in the same order.
+ */
+int32_t pssa_b200_model_insert_memory(pssa_b200_model* m, uint32_t index, float loss, uint64_t step, int64_t* slots_out);
+
+/*
  * One decode step for `n` streams with the sampling done on the device: forward, vocabulary head, then
  * pssa_b200_sample_dev's kernel on the head's logits, so only `n` ids cross PCIe. Every stream owns a generator
  * (seed 1337 by default, like `PSSAInferenceEngine`, src/inference.rs:70-73) and the window of its last 64 sampled ids

@@ -212,6 +212,12 @@ class Model:
         val = np.ascontiguousarray(val, np.float32)
         return int(lib().pssa_oracle_bank_insert(self.h, layer, fptr(key), fptr(val)))
 
+    def bank_insert_protected(self, layer, key, val, surprise, step) -> int:
+        """`insert_protected_with_device` (src/memory.rs:315-342): the slot written, or -1 when the slot defended itself."""
+        key = np.ascontiguousarray(key, np.float32)
+        val = np.ascontiguousarray(val, np.float32)
+        return int(lib().pssa_oracle_bank_insert_protected(self.h, layer, fptr(key), fptr(val), surprise, step))
+
     def reset_recurrent_state(self):
         lib().pssa_oracle_reset_state(self.h)
 

@@ -52,6 +52,7 @@ SIGNATURES = {
     "pssa_b200_model_create": (C.c_int32, [_vp, _vp, C.c_uint32, C.POINTER(_vp)]),
     "pssa_b200_model_destroy": (None, [_vp]),
     "pssa_b200_model_set_tensor": (C.c_int32, [_vp, C.c_int32, C.c_int32, _vp, _sz]),
+    "pssa_b200_model_insert_memory": (C.c_int32, [_vp, C.c_uint32, C.c_float, C.c_uint64, _vp]),
     "pssa_b200_model_sampler_push": (C.c_int32, [_vp, C.c_uint32, _vp, _sz]),
     "pssa_b200_model_reserve": (C.c_int32, [_vp, _sz, _sz]),
     "pssa_b200_model_get_tensor": (C.c_int32, [_vp, C.c_int32, C.c_int32, _vp, _sz]),

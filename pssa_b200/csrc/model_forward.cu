@@ -842,6 +842,63 @@ int32_t pssa_b200_model_get_observation(pssa_b200_model* m, uint32_t layer, uint
     return PSSA_B200_OK;
 }
 
+int32_t pssa_b200_model_insert_memory(pssa_b200_model* m, uint32_t index, float loss, uint64_t step, int64_t* slots_out) {
+    if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
+    pssa_b200_ctx* ctx = m->ctx;
+    if (slots_out)
+        for (size_t l = 0; l < m->depth; ++l) slots_out[l] = -3;  // nothing attempted
+    if (!(loss > 3.5f)) return PSSA_B200_OK;  // src/pssa.rs:3706-3708 (also false for NaN)
+    if (!m->obs.enabled || m->obs.valid_lanes == 0)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "insert_memory: enable the observer and run a forward call first (the write takes its key and value from the observer scratch)");
+    if (index >= m->obs.valid_lanes)
+        return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "insert_memory: lane %u outside the %zu observed lanes", index, m->obs.valid_lanes);
+    PSSA_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t cap = m->cap, rec = m->cap + m->k + 2 * m->d;
+    cudaStream_t st = ctx->stream;
+    for (size_t l = 0; l < m->depth; ++l) {
+        DeviceBlock& b = m->blocks[l];
+        if (b.confidence.size() != cap) b.confidence.assign(cap, 0.0f);  // a bank uploaded without metadata: src/memory.rs:44-45
+        if (b.last_seen.size() != cap) b.last_seen.assign(cap, 0);
+        // the gate's history-dependent words travel to the device for the one write and come back
+        arena_reset(ctx);
+        int32_t rc_a = arena_reserve(ctx, arena_round(cap * 4) + arena_round(cap * 8) + 4 * 256);
+        if (rc_a) return rc_a;
+        float* conf = (float*)arena_take(ctx, cap * 4);
+        unsigned long long* seen = (unsigned long long*)arena_take(ctx, cap * 8);
+        unsigned long long* meta = (unsigned long long*)arena_take(ctx, 16);
+        unsigned long long* step_dev = (unsigned long long*)arena_take(ctx, 8);
+        float* surprise = (float*)arena_take(ctx, 4);
+        long long* slot_dev = (long long*)arena_take(ctx, 8);
+        if (!conf || !seen || !meta || !step_dev || !surprise || !slot_dev) return fail(ctx, PSSA_B200_ERR_CUDA, "insert_memory: scratch allocation failed");
+        const unsigned long long meta_h[2] = {b.count, b.write_head}, step_h = step;
+        PSSA_CUDA(ctx, cudaMemcpyAsync(conf, b.confidence.data(), cap * 4, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(seen, b.last_seen.data(), cap * 8, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(meta, meta_h, 16, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(step_dev, &step_h, 8, cudaMemcpyHostToDevice, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(surprise, &loss, 4, cudaMemcpyHostToDevice, st));
+        const float* obs = m->obs.buf + (l * m->obs.lanes + index) * rec;
+        BankWriteParams p{};
+        p.keys = b.w[T_BANK_KEYS], p.norm_sq = b.w[T_BANK_NORM_SQ], p.values = b.w[T_BANK_VALUES], p.confidence = conf, p.last_seen = seen, p.meta = meta;
+        p.cap = (int)cap, p.dk = (int)m->k, p.dv = (int)m->d;
+        p.key_pnc = obs + cap;                    // q_poincare of the lane's last token (src/pssa.rs:3717)
+        p.val = obs + cap + m->k + m->d;          // z_final of the same token (src/pssa.rs:3718)
+        p.surprise = surprise, p.step = step_dev, p.n = 1, p.slots_out = slot_dev, p.winning_slots = nullptr, p.eta = 0.0f;
+        int32_t rc = launch_bank_insert_protected(ctx, p);
+        if (rc) return rc;
+        unsigned long long meta_back[2];
+        long long slot = -1;
+        PSSA_CUDA(ctx, cudaMemcpyAsync(b.confidence.data(), conf, cap * 4, cudaMemcpyDeviceToHost, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(b.last_seen.data(), seen, cap * 8, cudaMemcpyDeviceToHost, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(meta_back, meta, 16, cudaMemcpyDeviceToHost, st));
+        PSSA_CUDA(ctx, cudaMemcpyAsync(&slot, slot_dev, 8, cudaMemcpyDeviceToHost, st));
+        PSSA_CUDA(ctx, cudaStreamSynchronize(st));
+        b.count = meta_back[0], b.write_head = meta_back[1];
+        if (slot >= 0) b.ksplit_dirty = b.vsplit_dirty = b.vp_dirty = true;  // the derived copies of keys and values are stale
+        if (slots_out) slots_out[l] = slot;
+    }
+    return PSSA_B200_OK;
+}
+
 int32_t pssa_b200_model_sampler_seed(pssa_b200_model* m, uint32_t stream, uint64_t seed) {
     if (!m) return fail(nullptr, PSSA_B200_ERR_INVALID_ARGUMENT, "null model");
     pssa_b200_ctx* ctx = m->ctx;

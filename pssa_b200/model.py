@@ -277,6 +277,13 @@ class PSSAModel:
                                                                       N.SAMPLE_EXACT if exact else 0, _ptr(out), _ptr(conf)))
         return (out, conf) if want_confidence else out
 
+    def insert_memory(self, loss: float, step: int, index=0):
+        """`insert_training_memory_at` (src/pssa.rs:3705-3737) with the last observed token of lane `index`; returns the
+        per-block slots (written slot, -1 defended, -2 refused, -3 loss not above 3.5)."""
+        slots = np.empty(self.depth, np.int64)
+        self.gpu._check(self._lib.pssa_b200_model_insert_memory(self._h, index, loss, step, _ptr(slots)))
+        return slots
+
     def sampler_push(self, ids, stream=0):
         """Append ids (the prompt) to a stream's repetition window (`generated_ids` starts as the prompt, src/inference.rs:343-345)."""
         ids = np.ascontiguousarray(ids, np.uint64)

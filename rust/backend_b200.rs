@@ -281,6 +281,11 @@ impl B200Model {
         self.call(|m| unsafe { sys::pssa_b200_model_set_tensor(m, layer, tensor, data.as_ptr(), data.len()) })
     }
 
+    /// `insert_training_memory_at` on the device-resident banks; returns the per-block slots.
+    pub fn insert_memory(&self, index: u32, loss: f32, step: u64, slots_out: &mut [i64]) -> Result<(), String> {
+        self.call(|m| unsafe { sys::pssa_b200_model_insert_memory(m, index, loss, step, slots_out.as_mut_ptr()) })
+    }
+
     /// Appends the prompt to a stream's repetition window (`generated_ids` starts as a copy of the prompt).
     pub fn sampler_push(&self, stream: u32, ids: &[u64]) -> Result<(), String> {
         self.call(|m| unsafe { sys::pssa_b200_model_sampler_push(m, stream, ids.as_ptr(), ids.len()) })

@@ -454,6 +454,7 @@ extern "C" {
         data: *const f32,
         len: usize,
     ) -> i32;
+    pub fn pssa_b200_model_insert_memory(model: *mut pssa_b200_model, index: u32, loss: f32, step: u64, slots_out: *mut i64) -> i32;
     pub fn pssa_b200_model_sampler_push(model: *mut pssa_b200_model, stream: u32, ids: *const u64, n: usize) -> i32;
     pub fn pssa_b200_model_reserve(model: *mut pssa_b200_model, rows: usize, lanes: usize) -> i32;
     pub fn pssa_b200_model_get_tensor(

@@ -192,3 +192,41 @@ def test_out_of_range_device_metadata_is_refused_without_touching_memory(gpu):
     # a good write still works afterwards
     assert bank.write(gpu, keys[:1] * 0.5, vals[:1], [50.0], [1000]).tolist() == [0]
     gpu.poll_status()
+
+
+def test_model_level_memory_insert_follows_insert_training_memory_at(gpu):
+    """`pssa_b200_model_insert_memory`: if loss > 3.5 every block's bank gets a protected insert of (q_poincare, z_final)
+    of the lane's last token (src/pssa.rs:3705-3737). A small bank fills up and then the refractory gate decides, so the
+    sequence of slots (including defended writes) must equal the oracle's, and so must the logits of forward calls
+    made after the writes (they read the rewritten banks)."""
+    import pssa_b200
+    from helpers import fill_synthetic, upload
+    cfg = dict(depth=2, d_vocab=61, d_latent=32, d_state=8, d_mem_key=16, mem_capacity=6)
+    om = O.Model.new(cfg["depth"], cfg["d_vocab"], cfg["d_latent"], cfg["d_state"], cfg["d_mem_key"], cfg["mem_capacity"], tau_mem=0.1, seed=4)
+    fill_synthetic(om, 4, bank_fill=0.5)
+    gm = pssa_b200.PSSAModel(gpu, tau_mem=0.1, streams=1, precision=1, **cfg)
+    upload(om, gm)
+    gm.set_observer(True)
+    rng = np.random.default_rng(9)
+    # below the threshold nothing is attempted (and no observation is needed for that verdict)
+    assert list(gm.insert_memory(3.5, 10)) == [-3, -3]
+    step = 0
+    for round_ in range(14):
+        tok = int(rng.integers(1, cfg["d_vocab"]))
+        ok, logits = gm.prefill_inference([tok])
+        ref_logits = om.forward_inference(tok)
+        assert ok and np.max(np.abs(logits - ref_logits)) <= 1e-5 * max(1.0, float(np.abs(ref_logits).max())), round_
+        loss = float(rng.uniform(3.0, 9.0))
+        step += int(rng.integers(1, 90))  # some writes come soon after the last one (small refractory gain), some late
+        got = gm.insert_memory(loss, step)
+        for l in range(cfg["depth"]):
+            if loss > 3.5:
+                want = om.bank_insert_protected(l, om.tensor(l, O.S_Q_PNC), om.tensor(l, O.S_Z_FINAL), loss, step)
+                assert int(got[l]) == want, (round_, l, got, want)
+            else:
+                assert int(got[l]) == -3
+    # without the observer the entry point refuses (its key and value live in the observer scratch)
+    gm.set_observer(False)
+    with pytest.raises(pssa_b200.B200Error, match="observer"):
+        gm.insert_memory(5.0, step + 1)
+    gm.close()
