@@ -24,7 +24,7 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// bounded wait: false when the phase did not complete within the spin budget
+// bounded wait: false when the phase did not complete within the poll limit
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned limit = kSpinLimit) {
     uint32_t addr = smem_u32(bar);
     for (unsigned spin = 0; spin < limit; ++spin) {
