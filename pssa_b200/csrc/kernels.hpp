@@ -108,6 +108,9 @@ struct RetrieveParams {
     unsigned* fixup_count;
     int selftest_every;
     int no_fused;          // keep the multi-kernel path even where the one-kernel top-k read applies
+    int single_token;      // the caller's rows are one token per stream (a decode step): the all-slots read of the fast modes
+                           // then takes its one-launch front end, whatever the number of streams -- the choice must not
+                           // depend on the row count, or the same stream would see different arithmetic alone and in a batch
     unsigned long long* phase_cycles;  // optional [kRetrievePhases] device counters: clock cycles one worker thread per CTA spent per phase
     int* status;           // context status word (set by the launcher)
 };

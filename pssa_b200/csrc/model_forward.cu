@@ -381,6 +381,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         rp.value_terms = exact ? 6 : 1;
         rp.rows = nr, rp.dk = k, rp.dv = d, rp.cap = (int)m->cap, rp.count = (int)b.count;
         rp.top_k = (int)std::min(m->top_k, m->cap), rp.tau = m->cfg.tau_mem;
+        rp.single_token = single_token ? 1 : 0;
         rp.f32_distance = !exact;  // the bf16 mode's queries carry bf16 rounding already; f64 distances buy nothing there
         if (!exact && m->cap % 64 == 0) rp.w_split = v.w_split, rp.v_split = b.vsplit_bf16;
         // only the observer reads the fp32 weight rows after the value read

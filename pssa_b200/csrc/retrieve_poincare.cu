@@ -557,8 +557,8 @@ __global__ void __launch_bounds__(256) softmax_all_slots_kernel(RetrieveParams p
     }
 }
 
-// A few hundred queries at most (a decode step): projection, distances, softmax and the weight pieces of the all-slots
-// read in ONE launch, one CTA per four queries (a key row is loaded once for the four). With so few rows each of the
+// One token per stream (a decode step): projection, distances, softmax and the weight pieces of the all-slots
+// read in ONE launch, one CTA per four queries (a key row is loaded once for the four). With a few hundred rows each of the
 // separate kernels is a chain of launch and memory latencies, not work; here the rows never leave the CTA. Same
 // formulas as the separate fast-mode kernels: the projection in f64 (lane-partial sums combined in a fixed order
 // instead of one sequential sum: the f64 result differs in its last bits, the f32 point almost never), squared
@@ -1004,7 +1004,7 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     const size_t smem_f = (size_t)(kpad4 / 2) * QT * sizeof(float2) + ((size_t)2 * STL * (kpad4 + 4) + QT + 2 * STL) * sizeof(float);
     const bool tc_dist = !exact && p.q_split && p.k_split && p.q_stat && p.k_stat && p.dk % 64 == 0 && p.dk <= 256 &&
                          (!p.q_pnc || (reinterpret_cast<uintptr_t>(p.q_pnc) & 7) == 0);
-    const bool small_rows = !exact && !(p.top_k != 0 && p.top_k < p.count) && p.rows <= 1024 && p.count > 0 && p.w_split &&
+    const bool small_rows = !exact && !(p.top_k != 0 && p.top_k < p.count) && p.single_token && p.count > 0 && p.w_split &&
                             (p.value_terms == 1 || p.value_terms == 3) && p.dk <= 256 && p.cap <= 1024 && (p.skip_weights || p.weights) &&
                             (p.f32_distance || tc_dist);
     if (small_rows) {

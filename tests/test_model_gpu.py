@@ -160,6 +160,27 @@ def test_bf16_path_logits_within_tolerance_and_greedy_tokens(gpu):
     assert agree == total
 
 
+def test_a_stream_decodes_the_same_alone_and_inside_a_large_batch(gpu):
+    """Kernel choices (tile shapes, the one-launch front end of a decode step's read) follow the shape of the step,
+    never the number of rows in it in a way that changes arithmetic: the first 8 of 96 streams, run as a batch of 8
+    on a second model with the same weights, give bit-identical logits after the 16-token prompts (1536 rows against
+    128) and after every one of 12 greedy steps (96 rows against 8)."""
+    import pssa_b200
+    om, big = make_pair(gpu, 2, 512, 192, 64, 64, 64, seed=33, streams=96, precision=0)
+    small = pssa_b200.PSSAModel(gpu, 2, 512, 192, 64, 64, 64, tau_mem=0.1, streams=8, precision=0)
+    upload(om, small)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(1, 512, 16) for _ in range(96)]
+    lb, gb = big.prefill_batch(prompts, want_greedy=True)
+    ls, gs = small.prefill_batch(prompts[:8], want_greedy=True)
+    assert np.array_equal(lb[:8], ls) and np.array_equal(gb[:8], gs)
+    for _ in range(12):
+        lb, gb = big.decode_step(gb, want_greedy=True)
+        ls, gs = small.decode_step(gs, want_greedy=True)
+        assert np.array_equal(lb[:8], ls) and np.array_equal(gb[:8], gs)
+    big.close(), small.close()
+
+
 def test_closing_the_context_first_closes_its_models():
     """A model holds a pointer into its context; closing the context must retire the model rather than
     leave it to free device memory through a dead context later."""
