@@ -45,8 +45,9 @@ constexpr int kCandMax = 13;   // candidates re-scored per row: top_k + kMargin,
                                // instantiated for 9 and for 13)
 constexpr int kMargin = 1;     // one spare candidate: the proof needs the k-th exact distance strictly under the bound of
                                // everything that is not a candidate, and the (k+1)-th nearest slot is the usual binder
-constexpr int kWorkWarps = 8;  // warps 2..9; the first four own the 128 TMEM lanes (one query row per thread)
-constexpr int kThreads = 64 + 32 * kWorkWarps;
+constexpr int kValueBatch = 8;  // value rows a thread has in flight in the value read
+constexpr int kWorkWarps = 8;  // every warp works; warps w and w + 4 share the TMEM lanes 32 (w % 4) .. + 31 (one query row per thread)
+constexpr int kThreads = 32 * kWorkWarps;  // eight warps, two per scheduler: the whole register file (255 per thread) is usable
 constexpr int kStages = 3;
 constexpr int kPhases = kRetrievePhases;
 constexpr int kRingStage = 256 * BK * 2;  // one key k-block of up to 256 slots: 32 KB
@@ -222,6 +223,54 @@ __device__ __noinline__ void exact_rows(const RetrieveParams& p, size_t q0, cons
     }
 }
 
+// The value read of the proven rows (all worker threads; kept out of line so that the eight rows in flight have registers
+// to live in): m = sum over the selected
+// slots in ascending slot order of w * v, multiply and add separately rounded (memory.rs:399-406); a thread owns four
+// columns of a row and has kValueBatch value rows in flight before the first is used. (Staging the rows in shared memory
+// with bulk or 16-byte asynchronous copies measured two to three times slower: the gather is bound by the bytes a thread
+// keeps in flight on 512-byte rows of L2.) Then the reference's dense weight row if the caller wants it.
+template <int NC>
+__device__ __noinline__ void read_selected_values(const float* __restrict__ values, int dv, float* m_val, void* m_bf16, float* weights, int cap, int k,
+                                                  size_t q0, const unsigned* sels, const float* selw, const int* row_ok, int wtid) {
+    const int dv4 = dv >> 2;
+    for (int idx = wtid; idx < BM * dv4; idx += 32 * kWorkWarps) {
+        const int r = idx / dv4, c4 = idx - r * dv4;
+        if (!row_ok[r]) continue;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j0 = 0; j0 < k; j0 += kValueBatch) {
+            float4 vv[kValueBatch];
+#pragma unroll
+            for (int e = 0; e < kValueBatch; ++e)
+                if (j0 + e < k) vv[e] = __ldg(reinterpret_cast<const float4*>(values + (size_t)sels[r * NC + j0 + e] * dv) + c4);
+#pragma unroll
+            for (int e = 0; e < kValueBatch; ++e) {
+                if (j0 + e < k) {
+                    const float wi = selw[r * NC + j0 + e];
+                    acc.x = __fadd_rn(acc.x, __fmul_rn(wi, vv[e].x)), acc.y = __fadd_rn(acc.y, __fmul_rn(wi, vv[e].y));
+                    acc.z = __fadd_rn(acc.z, __fmul_rn(wi, vv[e].z)), acc.w = __fadd_rn(acc.w, __fmul_rn(wi, vv[e].w));
+                }
+            }
+        }
+        const size_t o = (q0 + r) * (size_t)dv + (size_t)c4 * 4;
+        if (m_val) *reinterpret_cast<float4*>(m_val + o) = acc;
+        if (m_bf16) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            uint2 pk;
+            pk.x = *reinterpret_cast<unsigned*>(&lo), pk.y = *reinterpret_cast<unsigned*>(&hi);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(m_bf16) + o) = pk;
+        }
+    }
+    if (weights) {
+        for (int idx = wtid; idx < BM * cap; idx += 32 * kWorkWarps) {
+            const int r = idx / cap, i = idx % cap;
+            if (!row_ok[r]) continue;
+            float w = 0.0f;
+            for (int j = 0; j < k; ++j) w = sels[r * NC + j] == (unsigned)i ? selw[r * NC + j] : w;
+            weights[(q0 + r) * (size_t)cap + i] = w;
+        }
+    }
+}
+
 template <int DK, int NC>
 __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const __grid_constant__ CUtensorMap map_b, RetrieveParams p) {
     constexpr int KB_PIECE = DK / BK;        // k-blocks per bf16 piece
@@ -259,8 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
     unsigned short* cand_slot = reinterpret_cast<unsigned short*>(row_ok + BM);  // [128][kCandMax]
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(cand_slot + BM * kCandMax);
     uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* a_ready = empty_bar + kStages;
-    uint64_t* acc_full = a_ready + 1;
+    uint64_t* acc_full = empty_bar + kStages;
     long long* phase_clk = reinterpret_cast<long long*>(acc_full + 1);  // [kPhases]
     int* kmax_i = reinterpret_cast<int*>(phase_clk + kPhases);          // [4] maxima over the occupied slots of kcol_s .w, .y, .x (floats >= 0)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kmax_i + 4);
@@ -279,7 +327,6 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) mbar_init(&full_bar[s], 1), mbar_init(&empty_bar[s], 1);
-        mbar_init(a_ready, 1);
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -319,68 +366,10 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
     // pieces 0 and 1, a stage of piece 1 with point piece 0: three products from two loads.
     const int n_kb = 2 * KB_PIECE;
 
-    if (warp == 0) {
-        // ---------------- producer: key pieces through the ring, after the workers have released it for this tile
-        if (lane == 0) {
-            uint32_t g = 0, it = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-                if (!mbar_wait(a_ready, it & 1)) {
-                    atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
-                    break;
-                }
-                for (int h = 0; h < halves && ok; ++h)
-                    for (int kb = 0; kb < n_kb; ++kb, ++g) {
-                        const int s = g % kStages;
-                        const uint32_t round = g / kStages;
-                        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-                            atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
-                            ok = false;
-                            break;
-                        }
-                        mbar_expect_tx(&full_bar[s], (uint32_t)nh * BK * 2);
-                        tma_load_2d(ring + s * kRingStage, &map_b, &full_bar[s], kb * BK, h * nh);  // piece kb / KB_PIECE, block kb % KB_PIECE
-                    }
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------- issuer: 128 x nh x 16 MMAs into TMEM columns [h * nh, (h + 1) * nh)
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_bf16(BM, nh);
-            uint32_t g = 0, it = 0;
-            bool ok = true;
-            for (long long tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
-                if (!mbar_wait(a_ready, it & 1)) {
-                    atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
-                    break;
-                }
-                tcgen05_fence_after();
-                for (int h = 0; h < halves && ok; ++h)
-                    for (int kb = 0; kb < n_kb; ++kb, ++g) {
-                        const int s = g % kStages;
-                        if (!mbar_wait(&full_bar[s], (g / kStages) & 1)) {
-                            atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
-                            ok = false;
-                            break;
-                        }
-                        tcgen05_fence_after();
-                        const int key_piece = kb / KB_PIECE, within = kb % KB_PIECE;
-                        const uint64_t db = umma_desc_sw128(smem_u32(ring + s * kRingStage));
-                        for (int a = 0; a < (key_piece == 0 ? 2 : 1); ++a) {
-                            const uint64_t da = umma_desc_sw128(smem_u32(smem_a + (a * KB_PIECE + within) * A_BLOCK));
-#pragma unroll
-                            for (int kk = 0; kk < BK / UMMA_K; ++kk)
-                                tcgen05_mma_bf16(tmem_base + h * nh, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || a > 0 || kk > 0) ? 1u : 0u);
-                        }
-                        tcgen05_commit(&empty_bar[s]);
-                    }
-                tcgen05_commit(acc_full);  // all products of this tile are in TMEM (or abandoned)
-            }
-        }
-    } else {
+    {
         // ---------------- workers
-        const int wid = warp - 2;                 // 0..7
-        const int wtid = threadIdx.x - 64;        // 0..255
+        const int wid = warp;                     // 0..7
+        const int wtid = threadIdx.x;             // 0..255
         const int my_row = (warp & 3) * 32 + lane;
         const bool vec_q = (((p.ldq ? p.ldq : (size_t)dk) & 3) == 0) && ((reinterpret_cast<uintptr_t>(p.q) & 15) == 0);
         uint32_t it = 0;
@@ -440,11 +429,60 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes -> visible to the tensor cores
             tcgen05_fence_before();
-            bar_workers();
-            if (wtid == 0) mbar_arrive(a_ready);  // releases the ring to the producer and the operand to the issuer
+            bar_workers();  // the ring is free for key pieces and the operand is complete
             lap(2);
+            // ---- the tensor-core phase: while the other warps wait for the accumulator, one thread of warp 0 sends the key
+            // pieces through the ring and one thread of warp 1 issues the MMAs (128 x nh x 16 into TMEM columns
+            // [h * nh, (h + 1) * nh)). Stages per half: every k-block of key piece 0, then of key piece 1.
+            if (wid == 0) {
+                if (lane == 0) {
+                    uint32_t g = it * (uint32_t)(halves * n_kb);
+                    bool ok = true;
+                    for (int h = 0; h < halves && ok; ++h)
+                        for (int kb = 0; kb < n_kb; ++kb, ++g) {
+                            const int s = g % kStages;
+                            const uint32_t round = g / kStages;
+                            if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+                                atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
+                                ok = false;
+                                break;
+                            }
+                            mbar_expect_tx(&full_bar[s], (uint32_t)nh * BK * 2);
+                            tma_load_2d(ring + s * kRingStage, &map_b, &full_bar[s], kb * BK, h * nh);  // piece kb / KB_PIECE, block kb % KB_PIECE
+                        }
+                }
+                __syncwarp();
+            } else if (wid == 1) {
+                if (lane == 0) {
+                    const uint32_t idesc = umma_idesc_bf16(BM, nh);
+                    uint32_t g = it * (uint32_t)(halves * n_kb);
+                    bool ok = true;
+                    tcgen05_fence_after();
+                    for (int h = 0; h < halves && ok; ++h)
+                        for (int kb = 0; kb < n_kb; ++kb, ++g) {
+                            const int s = g % kStages;
+                            if (!mbar_wait(&full_bar[s], (g / kStages) & 1)) {
+                                atomicExch(p.status, PSSA_B200_ERR_TIMEOUT);
+                                ok = false;
+                                break;
+                            }
+                            tcgen05_fence_after();
+                            const int key_piece = kb / KB_PIECE, within = kb % KB_PIECE;
+                            const uint64_t db = umma_desc_sw128(smem_u32(ring + s * kRingStage));
+                            for (int a = 0; a < (key_piece == 0 ? 2 : 1); ++a) {
+                                const uint64_t da = umma_desc_sw128(smem_u32(smem_a + (a * KB_PIECE + within) * A_BLOCK));
+#pragma unroll
+                                for (int kk = 0; kk < BK / UMMA_K; ++kk)
+                                    tcgen05_mma_bf16(tmem_base + h * nh, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > 0 || a > 0 || kk > 0) ? 1u : 0u);
+                            }
+                            tcgen05_commit(&empty_bar[s]);
+                        }
+                    tcgen05_commit(acc_full);  // all products of this tile are in TMEM (or abandoned)
+                }
+                __syncwarp();
+            }
             // ---- P3: two sweeps over the accumulator. All eight warps: a thread owns one query row (its TMEM lane) and one
-            // half of the slots (columns): warps 2..5 the lower half, warps 6..9 the upper.
+            // half of the slots (columns): warps 0..3 the lower half, warps 4..7 the upper.
             const int ch = wid >> 2;
             const int c_begin = ch * (cap / 2), c_end = c_begin + cap / 2;
             if (alive) {  // every lane waits (each needs the barrier's acquire); the verdict is made warp-uniform
@@ -751,50 +789,8 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             }
             bar_workers();
             lap(10);
-            // ---- P5d: the value read, all threads: m = sum over the selected slots in ascending slot order of w * v, multiply
-            // and add separately rounded (memory.rs:399-406); four rows' loads are in flight before the first is used. (Staging
-            // the rows in shared memory with bulk or 16-byte asynchronous copies measured two to three times slower: the
-            // gather is bound by the L2's throughput on 512-byte rows, not by registers.) Then the reference's dense weight
-            // row if the caller wants it.
-            {
-                const int dv = p.dv, dv4 = dv >> 2;
-                for (int idx = wtid; idx < BM * dv4; idx += 32 * kWorkWarps) {
-                    const int r = idx / dv4, c4 = idx - r * dv4;
-                    if (!row_ok[r]) continue;
-                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int j0 = 0; j0 < k; j0 += 4) {
-                        float4 vv[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            if (j0 + e < k) vv[e] = __ldg(reinterpret_cast<const float4*>(p.values + (size_t)sels[r * NC + j0 + e] * dv) + c4);
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            if (j0 + e < k) {
-                                const float wi = selw[r * NC + j0 + e];
-                                acc.x = __fadd_rn(acc.x, __fmul_rn(wi, vv[e].x)), acc.y = __fadd_rn(acc.y, __fmul_rn(wi, vv[e].y));
-                                acc.z = __fadd_rn(acc.z, __fmul_rn(wi, vv[e].z)), acc.w = __fadd_rn(acc.w, __fmul_rn(wi, vv[e].w));
-                            }
-                        }
-                    }
-                    const size_t o = (q0 + r) * (size_t)dv + (size_t)c4 * 4;
-                    if (p.m_val) *reinterpret_cast<float4*>(p.m_val + o) = acc;
-                    if (p.m_bf16) {
-                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-                        uint2 pk;
-                        pk.x = *reinterpret_cast<unsigned*>(&lo), pk.y = *reinterpret_cast<unsigned*>(&hi);
-                        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.m_bf16) + o) = pk;
-                    }
-                }
-                if (p.weights) {
-                    for (int idx = wtid; idx < BM * cap; idx += 32 * kWorkWarps) {
-                        const int r = idx / cap, i = idx % cap;
-                        if (!row_ok[r]) continue;
-                        float w = 0.0f;
-                        for (int j = 0; j < k; ++j) w = sels[r * NC + j] == (unsigned)i ? selw[r * NC + j] : w;
-                        p.weights[(q0 + r) * (size_t)cap + i] = w;
-                    }
-                }
-            }
+            // ---- P5d: the value read of the proven rows
+            read_selected_values<NC>(p.values, p.dv, p.m_val, p.m_bf16, p.weights, cap, k, q0, sels, selw, row_ok, wtid);
             // ---- P5e: the rows whose selection the candidates could not prove (or a list overflowed, or the test hook) are
             // recomputed over every slot. Rare, and uniform over the CTA (the count is shared); kept out of line so that it
             // costs the common path no registers.
