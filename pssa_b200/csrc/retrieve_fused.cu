@@ -6,16 +6,19 @@
 // reference GPU's one-thread-per-token `memory_forward` (src/cuda/stages.ptx:358-446).
 //
 // The idea: the tensor cores are a PRE-FILTER, the reference's f64 arithmetic decides.
-//   1. worker warps project the tile's queries into the ball (f64, the reference's sequential sums: same bits) and write
+//   1. the CTA's eight warps project the tile's queries into the ball (f64, the reference's sequential sums: same bits) and write
 //      the points as three bf16 pieces straight into the 128-byte-swizzled A operand in shared memory;
 //   2. one thread issues tcgen05.mma for the three piece products above 2^-16 of p.k against the bank's keys (split the
-//      same way once per upload, streamed by TMA through a 3-stage ring); the 128 x capacity accumulator fills the SM's
-//      TMEM (512 fp32 columns);
-//   3. every worker thread owns one query row (its TMEM lane) and one half of the slots and reads that part of the
+//      same way once per upload, streamed by TMA through a 3-stage ring by one thread of another warp); the 128 x capacity
+//      accumulator fills the SM's TMEM (512 fp32 columns). There are no dedicated producer or issuer warps: nothing else
+//      can run while the product is formed (the ring is the other phases' scratch memory), so two of the eight warps take
+//      the roles for that phase, and eight warps -- two per scheduler -- may use 255 registers each where ten were held
+//      to 168 and spilled in the exact sums (1.22 -> 0.99 ms per 262,144 queries on the same GPU);
+//   3. every thread owns one query row (its TMEM lane) and one half of the slots and reads that part of the
 //      accumulator twice with tcgen05.ld: a first sweep finds a threshold that at least C = k + 1 slots pass (the C-th
 //      smallest of the minima of v = |p-k|^2 / (1-|k|^2) over groups of 32, 16 or 8 slots, both halves merged), a second
 //      sweep lists the slots under it (about a dozen of 512); the C smallest of the lists are the row's candidates;
-//   4. four threads per row re-score the candidates as `poincare_distance` does (f64 differences squared and summed, f64
+//   4. DK/16 threads per row re-score the candidates as `poincare_distance` does (f64 differences squared and summed, f64
 //      log1p form of 2 asinh sqrt, rounded to f32); one thread per row selects k by (bits, slot)
 //      and proves the selection: the sweeps
 //      also produced v_lb, the smallest (approximate v - its error bound) over every slot that did NOT become a candidate,
@@ -559,18 +562,20 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             lap(5);
             int cnt = 0;
             if (alive) {
-                uint2* my_list = list_e + (size_t)ch * (kListHalf + 1) * BM + my_row;
-                // sweep 2: list the slots at or under the widened threshold. Every column stores: a listed slot at the list's
-                // end, the others (and what overflows the list) into the spare row.
+                uint2* const my_list = list_e + (size_t)ch * (kListHalf + 1) * BM + my_row;
+                uint2* const spare = my_list + kListHalf * BM;
+                uint2* wp = my_list;  // the list's end
+                // sweep 2: list the slots at or under the widened threshold: a predicated store at the list's end, which
+                // stops advancing at the spare row (a list that reaches it counts as overflowed)
                 auto listing = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float2 kc = kcol_s[c0 + j];
                         const float v = fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y;
-                        const bool listed = v <= t2;
-                        const int pos = listed ? min(cnt, kListHalf) : kListHalf;
-                        my_list[pos * BM] = make_uint2(__float_as_uint(v), (unsigned)(c0 + j));
-                        cnt += listed ? 1 : 0;
+                        if (v <= t2) {
+                            *wp = make_uint2(__float_as_uint(v), (unsigned)(c0 + j));
+                            if (wp != spare) wp += BM;
+                        }
                     }
                 };
                 for (int c0 = c_begin; c0 < c_end; c0 += 64) {
@@ -581,6 +586,8 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                     if (c0 + 64 < c_end) tcgen05_ld_32x32_issue(taddr + c0 + 64, buf0);
                     listing(buf1, c0 + 32);
                 }
+                cnt = (int)((wp - my_list) / BM);
+                if (cnt == kListHalf) cnt = kListHalf + 1;
             }
             tcgen05_fence_before();
             stat_cnt[ch * BM + my_row] = alive ? cnt : kListHalf + 1;
