@@ -80,12 +80,17 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     return r;
 }
 
-template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
-__global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 256 ? 2 : kMinCtasFast) : 1) ssm_fused_kernel(SsmParams p) {
+template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads, int CPT = 1>
+__global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 256 || CPT > 1) ? 2 : kMinCtasFast) : 1) ssm_fused_kernel(SsmParams p) {
+    // CPT channels per thread (fast mode without tape only): a token's B and C rows are loaded once for both channels and
+    // the two recurrences are independent instruction streams, so a warp-token of twice the work takes fewer than twice
+    // the instructions.
+    static_assert(CPT == 1 || (CPT == 2 && !EXACT && !TAPE), "two channels per thread exist for the fast mode only");
     pdl_trigger();  // the next kernel in the stream may start its prologue now ...
     pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     constexpr int kThreads = THR;     // shadows the default: every stride below follows this instantiation's CTA size
-    constexpr int CH = kThreads / G;  // channels per CTA
+    constexpr int HALF = kThreads / G;  // channels per CTA and per thread slot: thread slot u owns channel c + u * HALF
+    constexpr int CH = HALF * CPT;      // channels per CTA
     constexpr int kTileTokens = kTileTokensFor<G>;
     constexpr int LPG = 32 / G;       // lanes of a warp that share one state group
     constexpr int SG = ST + 4;        // shared-memory pitch of a state group (bank spreading)
@@ -116,32 +121,39 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 25
                            : nullptr;
 
     float A[ST], h[ST];
+    float A1[CPT > 1 ? ST : 1], h1[CPT > 1 ? ST : 1];  // the second channel of a two-channel thread
+    const int i1 = i + HALF;
+    const bool valid1 = CPT > 1 && i1 < p.d;
     // a thread's states are contiguous in `rates` and in the carry: 16-byte accesses when the layout allows (decode
     // steps are one token long, so this load and the store at the end are most of their traffic)
     const bool vec_state = p.aligned && (s & 3) == 0 && (reinterpret_cast<uintptr_t>(p.rates) & 15) == 0 &&
                            (reinterpret_cast<uintptr_t>(carry) & 15) == 0;
-    if (vec_state) {
+    auto load_state = [&](float* Av, float* hv, int ch, bool ok_ch) {
+        if (vec_state) {
 #pragma unroll
-        for (int q = 0; q < ST / 4; ++q) {
-            const bool ok = valid && (j0 + q * 4) < s;
-            const float4 r4 = ok ? __ldg(reinterpret_cast<const float4*>(p.rates + (size_t)i * s + j0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            const float4 h4 = (ok && carry) ? *(reinterpret_cast<const float4*>(carry + (size_t)i * s + j0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
-            A[q * 4] = r4.x, A[q * 4 + 1] = r4.y, A[q * 4 + 2] = r4.z, A[q * 4 + 3] = r4.w;
-            h[q * 4] = h4.x, h[q * 4 + 1] = h4.y, h[q * 4 + 2] = h4.z, h[q * 4 + 3] = h4.w;
-        }
-        if (!EXACT) {
+            for (int q = 0; q < ST / 4; ++q) {
+                const bool ok = ok_ch && (j0 + q * 4) < s;
+                const float4 r4 = ok ? __ldg(reinterpret_cast<const float4*>(p.rates + (size_t)ch * s + j0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 h4 = (ok && carry) ? *(reinterpret_cast<const float4*>(carry + (size_t)ch * s + j0) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                Av[q * 4] = r4.x, Av[q * 4 + 1] = r4.y, Av[q * 4 + 2] = r4.z, Av[q * 4 + 3] = r4.w;
+                hv[q * 4] = h4.x, hv[q * 4 + 1] = h4.y, hv[q * 4 + 2] = h4.z, hv[q * 4 + 3] = h4.w;
+            }
+            if (!EXACT) {
 #pragma unroll
-            for (int jj = 0; jj < ST; ++jj) A[jj] *= 1.4426950408889634f;
-        }
-    } else {
+                for (int jj = 0; jj < ST; ++jj) Av[jj] *= 1.4426950408889634f;
+            }
+        } else {
 #pragma unroll
-        for (int jj = 0; jj < ST; ++jj) {
-            bool ok = valid && (j0 + jj) < s;
-            float rate = ok ? __ldg(p.rates + (size_t)i * s + j0 + jj) : 0.0f;
-            A[jj] = EXACT ? rate : rate * 1.4426950408889634f;
-            h[jj] = (ok && carry) ? carry[(size_t)i * s + j0 + jj] : 0.0f;
+            for (int jj = 0; jj < ST; ++jj) {
+                bool ok = ok_ch && (j0 + jj) < s;
+                float rate = ok ? __ldg(p.rates + (size_t)ch * s + j0 + jj) : 0.0f;
+                Av[jj] = EXACT ? rate : rate * 1.4426950408889634f;
+                hv[jj] = (ok && carry) ? carry[(size_t)ch * s + j0 + jj] : 0.0f;
+            }
         }
-    }
+    };
+    load_state(A, h, i, valid);
+    if constexpr (CPT > 1) load_state(A1, h1, i1, valid1);
 
     const int ntiles = (len + kTileTokens - 1) / kTileTokens;
 
@@ -231,7 +243,7 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 25
                 bj[q * 4] = vb.x, bj[q * 4 + 1] = vb.y, bj[q * 4 + 2] = vb.z, bj[q * 4 + 3] = vb.w;
                 cj[q * 4] = vc.x, cj[q * 4 + 1] = vc.y, cj[q * 4 + 2] = vc.z, cj[q * 4 + 3] = vc.w;
             }
-            float yp = 0.0f;
+            float yp = 0.0f, ypb = 0.0f;
             float av[TAPE ? ST : 1], bv[TAPE ? ST : 1];
             if (EXACT) {
 #pragma unroll
@@ -246,23 +258,45 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 25
                 const float w = dl * xv;
                 const f32x2 dl2 = pack2(dl, dl), w2 = pack2(w, w);
                 f32x2 y2 = pack2(0.0f, 0.0f);
+                const float dlb = CPT > 1 ? dd[tt * CH + c + HALF] : 0.0f;
+                const float wb = CPT > 1 ? dlb * dx[tt * CH + c + HALF] : 0.0f;
+                const f32x2 dlb2 = pack2(dlb, dlb), wb2 = pack2(wb, wb);
+                f32x2 yb2 = pack2(0.0f, 0.0f);
 #pragma unroll
                 for (int jj = 0; jj < ST; jj += 2) {
+                    const f32x2 b2 = pack2(bj[jj], bj[jj + 1]), c2 = pack2(cj[jj], cj[jj + 1]);
                     float e0, e1;
                     unpack2(mul2(dl2, pack2(A[jj], A[jj + 1])), e0, e1);
                     const float a0 = ex2_approx(e0), a1 = ex2_approx(e1);
-                    f32x2 h2 = fma2(pack2(a0, a1), pack2(h[jj], h[jj + 1]), mul2(w2, pack2(bj[jj], bj[jj + 1])));
+                    f32x2 h2 = fma2(pack2(a0, a1), pack2(h[jj], h[jj + 1]), mul2(w2, b2));
                     unpack2(h2, h[jj], h[jj + 1]);
-                    y2 = fma2(h2, pack2(cj[jj], cj[jj + 1]), y2);
+                    y2 = fma2(h2, c2, y2);
                     if (TAPE) av[jj] = a0, av[jj + 1] = a1, bv[jj] = dl * bj[jj], bv[jj + 1] = dl * bj[jj + 1];
+                    if constexpr (CPT > 1) {
+                        float f0, f1;
+                        unpack2(mul2(dlb2, pack2(A1[jj], A1[jj + 1])), f0, f1);
+                        const float g0 = ex2_approx(f0), g1 = ex2_approx(f1);
+                        f32x2 hb2 = fma2(pack2(g0, g1), pack2(h1[jj], h1[jj + 1]), mul2(wb2, b2));
+                        unpack2(hb2, h1[jj], h1[jj + 1]);
+                        yb2 = fma2(hb2, c2, yb2);
+                    }
                 }
                 float y_lo, y_hi;
                 unpack2(y2, y_lo, y_hi);
                 yp = y_lo + y_hi;
+                if constexpr (CPT > 1) {
+                    unpack2(yb2, y_lo, y_hi);
+                    ypb = y_lo + y_hi;
+                }
             }
 #pragma unroll
             for (int m = LPG; m < 32; m <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, m);
             if (g == 0) dd[tt * CH + c] = yp;  // every reader of this delta slot sits in this warp and has read it
+            if constexpr (CPT > 1) {
+#pragma unroll
+                for (int m = LPG; m < 32; m <<= 1) ypb += __shfl_xor_sync(0xffffffffu, ypb, m);
+                if (g == 0) dd[tt * CH + c + HALF] = ypb;
+            }
             if (TAPE) {
 #pragma unroll
                 for (int jj = 0; jj < ST; ++jj) {
@@ -314,16 +348,20 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? (THR > 25
     }
     cp_async_wait<0>();
     if (carry && len > 0) {
-        if (vec_state) {
+        auto store_state = [&](const float* hv, int ch, bool ok_ch) {
+            if (vec_state) {
 #pragma unroll
-            for (int q = 0; q < ST / 4; ++q)
-                if (valid && j0 + q * 4 < s)
-                    *(reinterpret_cast<float4*>(carry + (size_t)i * s + j0) + q) = make_float4(h[q * 4], h[q * 4 + 1], h[q * 4 + 2], h[q * 4 + 3]);
-        } else {
+                for (int q = 0; q < ST / 4; ++q)
+                    if (ok_ch && j0 + q * 4 < s)
+                        *(reinterpret_cast<float4*>(carry + (size_t)ch * s + j0) + q) = make_float4(hv[q * 4], hv[q * 4 + 1], hv[q * 4 + 2], hv[q * 4 + 3]);
+            } else {
 #pragma unroll
-            for (int jj = 0; jj < ST; ++jj)
-                if (valid && j0 + jj < s) carry[(size_t)i * s + j0 + jj] = h[jj];
-        }
+                for (int jj = 0; jj < ST; ++jj)
+                    if (ok_ch && j0 + jj < s) carry[(size_t)ch * s + j0 + jj] = hv[jj];
+            }
+        };
+        store_state(h, i, valid);
+        if constexpr (CPT > 1) store_state(h1, i1, valid1);
     }
 }
 
@@ -454,14 +492,14 @@ __global__ void __launch_bounds__(256) seqpar_fold_kernel(const float* __restric
     st[e] = h;
 }
 
-template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads>
+template <int ST, int G, bool EXACT, bool TAPE, int THR = kThreads, int CPT = 1>
 int32_t launch_cfg(pssa_b200_ctx* ctx, const SsmParams& p) {
     constexpr int kThreads = THR;
-    constexpr int CH = kThreads / G;
+    constexpr int CH = kThreads / G * CPT;
     constexpr int SP = (ST + 4) * G;
     constexpr int kTileTokens = kTileTokensFor<G>;
     size_t smem = (size_t)kStages * kTileTokens * (2 * CH + 2 * SP) * sizeof(float);
-    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE, THR>;
+    auto kern = ssm_fused_kernel<ST, G, EXACT, TAPE, THR, CPT>;
     static PerDeviceOnce attr_set;  // per instantiation and per device
     if (smem > 48 * 1024 && attr_set.need(ctx->device)) {
         PSSA_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -527,16 +565,25 @@ int32_t launch_ssm_fused(pssa_b200_ctx* ctx, const SsmParams& p, bool exact) {
         if (s <= 16) return launch_one<4, 4, false>(ctx, p);
         if (s <= 32) return launch_one<16, 2, false>(ctx, p);
         if (s <= 64) {
-            // CTA size by wave balance. Every CTA of a launch is resident at once and they all take the same time, so the
-            // launch lasts as long as the SM holding the most warps. 256 threads = 64 channels per CTA; 352 threads = 88
-            // channels. With d = 768 and 32 lanes: 384 CTAs put 3 x 8 warps on most SMs, 288 larger ones put 2 x 11.
+            // CTA shape by wave balance. Every CTA of a launch is resident at once and a warp's time per token is fixed by
+            // its exponentials (16 per lane and channel, 8 cycles each on its scheduler's XU pipe), so the launch lasts as
+            // long as the busiest scheduler: count, per shape, the channel-warps the fullest SM puts on one scheduler.
+            // 256 threads = 64 channels per CTA (4 CTAs per SM), 352 threads = 88 channels (2 per SM), 128 threads with two
+            // channels per thread = 64 channels (3 per SM). With d = 768 and 32 lanes: 384 CTAs put 3 x 8 warps on most SMs
+            // (6 per scheduler), 288 of 352 threads put 2 x 11 (6 on two schedulers, 5 on the others), 384 two-channel CTAs
+            // put 3 x 4 double warps (6). On a tie the two-channel shape wins: a token's B and C rows are loaded once
+            // for both channels (11.93 -> 11.67 ms for the 12 launches of the benchmark step).
             if (!tape) {
-                auto busiest = [&](int threads, int cap) -> long long {
-                    const long long blocks = (long long)((p.d + threads / 4 - 1) / (threads / 4)) * p.lanes;
+                auto busiest = [&](int threads, int cpt, int cap) -> long long {
+                    const int ch = threads / 4 * cpt;
+                    const long long blocks = (long long)((p.d + ch - 1) / ch) * p.lanes;
                     const long long per_sm = (blocks + ctx->sm_count - 1) / ctx->sm_count;
-                    return per_sm > cap ? (1ll << 40) : per_sm * (threads / 32);  // more than one wave: not considered
+                    if (per_sm > cap) return 1ll << 40;  // more than one wave: not considered
+                    return (per_sm * (threads / 32) + 3) / 4 * cpt;
                 };
-                if (busiest(352, 2) < busiest(256, 4)) return launch_cfg<16, 4, false, false, 352>(ctx, p);
+                const long long two = busiest(128, 2, 3), wide = busiest(352, 1, 2), plain = busiest(256, 1, 4);
+                if (two <= wide && two <= plain) return launch_cfg<16, 4, false, false, 128, 2>(ctx, p);
+                if (wide < plain) return launch_cfg<16, 4, false, false, 352>(ctx, p);
             }
             return launch_one<16, 4, false>(ctx, p);
         }
