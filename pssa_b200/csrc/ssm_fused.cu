@@ -89,8 +89,7 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 2
     pdl_trigger();  // the next kernel in the stream may start its prologue now ...
     pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     constexpr int kThreads = THR;     // shadows the default: every stride below follows this instantiation's CTA size
-    constexpr int HALF = kThreads / G;  // channels per CTA and per thread slot: thread slot u owns channel c + u * HALF
-    constexpr int CH = HALF * CPT;      // channels per CTA
+    constexpr int CH = kThreads / G * CPT;  // channels per CTA
     constexpr int kTileTokens = kTileTokensFor<G>;
     constexpr int LPG = 32 / G;       // lanes of a warp that share one state group
     constexpr int SG = ST + 4;        // shared-memory pitch of a state group (bank spreading)
@@ -108,7 +107,7 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 2
     const int ncb = (p.d + CH - 1) / CH;
     const int lane = blockIdx.x / ncb;
     const int i0 = (blockIdx.x % ncb) * CH;
-    const int i = i0 + c;
+    const int i = i0 + CPT * c;  // a two-channel thread owns the adjacent channels CPT * c and CPT * c + 1
     const bool valid = i < p.d;
     const size_t row0 = p.offsets ? p.offsets[lane] : 0;
     const int len = p.lengths ? (int)p.lengths[lane] : (int)p.rows;
@@ -122,7 +121,7 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 2
 
     float A[ST], h[ST];
     float A1[CPT > 1 ? ST : 1], h1[CPT > 1 ? ST : 1];  // the second channel of a two-channel thread
-    const int i1 = i + HALF;
+    const int i1 = i + 1;
     const bool valid1 = CPT > 1 && i1 < p.d;
     // a thread's states are contiguous in `rates` and in the carry: 16-byte accesses when the layout allows (decode
     // steps are one token long, so this load and the store at the end are most of their traffic)
@@ -231,8 +230,14 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 2
         const float* db = sm_b + st * kTileTokens * SP + g * SG;
         const float* dc = sm_c + st * kTileTokens * SP + g * SG;
         auto token = [&](int tt) {
-            const float dl = dd[tt * CH + c];
-            const float xv = dx[tt * CH + c];
+            float dl, xv, dlb = 0.0f, xvb = 0.0f;
+            if constexpr (CPT > 1) {  // both channels' values with one 8-byte load each
+                const float2 d2 = *reinterpret_cast<const float2*>(dd + tt * CH + 2 * c);
+                const float2 x2 = *reinterpret_cast<const float2*>(dx + tt * CH + 2 * c);
+                dl = d2.x, dlb = d2.y, xv = x2.x, xvb = x2.y;
+            } else {
+                dl = dd[tt * CH + c], xv = dx[tt * CH + c];
+            }
             const size_t row = row0 + t0 + tt;
             static_assert(ST % 4 == 0, "states per thread are loaded as float4");
             float bj[ST], cj[ST];
@@ -258,8 +263,7 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 2
                 const float w = dl * xv;
                 const f32x2 dl2 = pack2(dl, dl), w2 = pack2(w, w);
                 f32x2 y2 = pack2(0.0f, 0.0f);
-                const float dlb = CPT > 1 ? dd[tt * CH + c + HALF] : 0.0f;
-                const float wb = CPT > 1 ? dlb * dx[tt * CH + c + HALF] : 0.0f;
+                const float wb = dlb * xvb;
                 const f32x2 dlb2 = pack2(dlb, dlb), wb2 = pack2(wb, wb);
                 f32x2 yb2 = pack2(0.0f, 0.0f);
 #pragma unroll
@@ -291,11 +295,12 @@ __global__ void __launch_bounds__(THR, (ST <= 16 && !TAPE && !EXACT) ? ((THR > 2
             }
 #pragma unroll
             for (int m = LPG; m < 32; m <<= 1) yp += __shfl_xor_sync(0xffffffffu, yp, m);
-            if (g == 0) dd[tt * CH + c] = yp;  // every reader of this delta slot sits in this warp and has read it
             if constexpr (CPT > 1) {
 #pragma unroll
                 for (int m = LPG; m < 32; m <<= 1) ypb += __shfl_xor_sync(0xffffffffu, ypb, m);
-                if (g == 0) dd[tt * CH + c + HALF] = ypb;
+                if (g == 0) *reinterpret_cast<float2*>(dd + tt * CH + 2 * c) = make_float2(yp, ypb);
+            } else {
+                if (g == 0) dd[tt * CH + c] = yp;  // every reader of this delta slot sits in this warp and has read it
             }
             if (TAPE) {
 #pragma unroll
