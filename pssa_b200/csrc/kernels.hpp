@@ -118,6 +118,8 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
 // retrieve_fused.cu: projection, tensor-core pre-filter, exact f64 re-scoring of the candidates, (bits, slot) selection,
 // softmax and value read of a top-k read in one kernel; same results as the f64 path of launch_memory_read
 bool retrieve_fused_eligible(const RetrieveParams& p);
+bool retrieve_all_fused_eligible(const RetrieveParams& p);
+int32_t launch_retrieve_all_fused(pssa_b200_ctx* ctx, const RetrieveParams& p);
 int32_t launch_retrieve_fused(pssa_b200_ctx* ctx, const RetrieveParams& p);
 // dense weight rows [rows, cap] -> selected slots and weights [rows, k] in ascending slot order
 int32_t launch_compact_topk(pssa_b200_ctx* ctx, const float* weights, int cap, int k, size_t rows, unsigned* slots, float* w_out);

@@ -43,6 +43,12 @@ namespace pssa {
 namespace {
 using namespace tc;
 
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 constexpr int kListHalf = 32;  // slots one column half of a row can list under its threshold (about 10 expected)
 constexpr int kCandMax = 13;   // candidates re-scored per row: top_k + kMargin, at most this many (the kernel is
                                // instantiated for 9 and for 13)
@@ -274,7 +280,15 @@ __device__ __noinline__ void read_selected_values(const float* __restrict__ valu
     }
 }
 
-template <int DK, int NC>
+// ALL: the all-slots read's front end instead of the top-k read. Same projection, split and pre-filter product; then the
+// weights of EVERY slot leave as the bf16 operand of the value product, and nothing else: a thread owns one query row
+// and one half of the slots, a first sweep over the accumulator finds the row's smallest v (the distance is monotone
+// in it), a second one turns every v into exp((d_min - d) / tau) with three hardware approximations per slot
+// (sqrt, lg2, ex2: the weight is (1 + z)^(-1/tau) for z = 2u + 2 sqrt(u^2 + u), so the logarithm of the distance
+// and the exponential of the weight meet in one multiplication), sums them and parks them as bf16 in the shared memory
+// the operands no longer need; a last pass scales the rows by one over their sums and writes them out as whole rows.
+// The [rows, capacity] fp32 distance matrix and the projected points never reach HBM.
+template <int DK, int NC, bool ALL = false>
 __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const __grid_constant__ CUtensorMap map_b, RetrieveParams p) {
     constexpr int KB_PIECE = DK / BK;        // k-blocks per bf16 piece
     constexpr int KB_A = 3 * KB_PIECE;       // k-blocks of the A operand (three pieces)
@@ -404,8 +418,34 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             }
             bar_workers();
             lap(0);
-            // ---- P1: one thread per row projects it (memory.rs:198-211), in place
-            if (wtid < BM) {
+            // ---- P1: one thread per row projects it (memory.rs:198-211), in place. The all-slots front end, whose consumers
+            // keep bf16-grade weights, only forms the row's scale here (two threads per row, fp32 partial sums) and applies
+            // it while splitting; |p|^2 follows from the norm and the scale.
+            float* row_scale = reinterpret_cast<float*>(stat_dlb);  // [128], all-slots mode only
+            if constexpr (ALL) {
+                const int r = wtid >> 1, half = wtid & 1;
+                const float* row = staging + r * PITCH + half * (DK / 2);
+                float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+                for (int i = 0; i < DK / 2; i += 4)
+                    s0 = fmaf(row[i], row[i], s0), s1 = fmaf(row[i + 1], row[i + 1], s1), s2 = fmaf(row[i + 2], row[i + 2], s2),
+                    s3 = fmaf(row[i + 3], row[i + 3], s3);
+                float r2 = (s0 + s1) + (s2 + s3);
+                r2 += __shfl_xor_sync(0xffffffffu, r2, 1);
+                if (half == 0) {
+                    float scale = 1.0f, n2 = r2;
+                    if (p.q_is_euclidean) {
+                        const double rr = sqrt((double)r2);
+                        const double max_radius = 1.0 - 8.0 * (double)FLT_EPSILON;
+                        const double sc = (rr == 0.0) ? 1.0 : fmin(rr / (1.0 + rr), max_radius) / rr;
+                        scale = (float)sc;
+                        n2 = (float)((rr * sc) * (rr * sc));
+                        if (p.q_norm && q0 + r < p.rows) p.q_norm[q0 + r] = (float)fmin(rr, (double)FLT_MAX);
+                    }
+                    row_scale[r] = scale;
+                    stat_qs[r] = fminf(n2, __uint_as_float(0x3f7fffffu));
+                }
+            } else if (wtid < BM) {
                 float qn = 0.0f;
                 const float qs = project_row(staging + wtid * PITCH, dk, p.q_is_euclidean != 0, &qn);
                 stat_qs[wtid] = qs;
@@ -416,7 +456,8 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             // ---- P2: three bf16 pieces of every coordinate into the swizzled A operand; q_pnc goes out
             for (int idx = wtid; idx < BM * (DK / 2); idx += 32 * kWorkWarps) {
                 const int r = idx / (DK / 2), c = (idx % (DK / 2)) * 2;
-                const float v0 = staging[r * PITCH + c], v1 = staging[r * PITCH + c + 1];
+                float v0 = staging[r * PITCH + c], v1 = staging[r * PITCH + c + 1];
+                if constexpr (ALL) v0 *= row_scale[r], v1 *= row_scale[r];
                 if (p.q_pnc && q0 + r < p.rows) {
                     p.q_pnc[(q0 + r) * dk + c] = v0;
                     p.q_pnc[(q0 + r) * dk + c + 1] = v1;
@@ -495,319 +536,440 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             }
             tcgen05_fence_after();
             lap(3);  // waiting for the tensor cores
-            const float qs = stat_qs[my_row];
-            const float pn = sqrtf(qs) * 1.0000002f;
-            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-            float best[NC];
+            if constexpr (ALL) {
+                const int ch = wid >> 2;
+                const int c_begin = ch * (cap / 2), c_end = c_begin + cap / 2;
+                const float qs = stat_qs[my_row];
+                const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+                const float inv1mq = __fdividef(1.0f, 1.0f - qs);
+                const float inv_tau = __fdividef(1.0f, p.tau);
+                constexpr int W_PITCH = 512 + 8;  // bf16 elements per parked row: 16 bytes of padding spread the banks
+                __nv_bfloat16* park = reinterpret_cast<__nv_bfloat16*>(smem_a);  // [128][W_PITCH]: over the operand and the ring
+                float* row_min = stat_excl;                                     // [2][128] smallest v per column half
+                float* row_sum = reinterpret_cast<float*>(stat_cnt);            // [2][128] sum of the weights per column half
+                uint32_t buf0[32], buf1[32];
+                float vmin = CUDART_INF_F, sum = 0.0f, lg_min_t = 0.0f;
+                if (alive) {
+                    auto minimum = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
-            for (int i = 0; i < NC; ++i) best[i] = CUDART_INF_F;
-            auto insert_best = [&](float x) {  // keep the NC smallest, sorted; branch-free
-#pragma unroll
-                for (int i = 0; i < NC; ++i) {
-                    const float lo = fminf(best[i], x), hi = fmaxf(best[i], x);
-                    best[i] = lo, x = hi;
-                }
-            };
-            // both sweeps read 32 columns per tcgen05.ld into one of two register buffers, the next load in flight while
-            // the current buffer is used
-            uint32_t buf0[32], buf1[32];
-            if (alive) {
-                // sweep 1: group minima
-                auto minima = [&](const uint32_t (&acc)[32], int c0) {
-                    float vmin[4] = {CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, CUDART_INF_F};  // minima of the four groups of 8 columns
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float2 kc = kcol_s[c0 + j];
-                        vmin[j >> 3] = fminf(vmin[j >> 3], fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y);
-                    }
-                    if (group == 32) {
-                        insert_best(fminf(fminf(vmin[0], vmin[1]), fminf(vmin[2], vmin[3])));
-                    } else if (group == 16) {
-                        insert_best(fminf(vmin[0], vmin[1]));
-                        insert_best(fminf(vmin[2], vmin[3]));
-                    } else {
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) insert_best(vmin[g]);
-                    }
-                };
-                tcgen05_ld_32x32_issue(taddr + c_begin, buf0);
-                for (int c0 = c_begin; c0 < c_end; c0 += 64) {
-                    tcgen05_wait_ld(buf0);
-                    tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
-                    minima(buf0, c0);
-                    tcgen05_wait_ld(buf1);
-                    tcgen05_ld_32x32_issue(taddr + (c0 + 64 < c_end ? c0 + 64 : c_begin), buf0);  // wraps to the second sweep's first columns
-                    minima(buf1, c0 + 32);
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < NC; ++i) xbest[(ch * NC + i) * BM + my_row] = best[i];
-            bar_workers();
-            lap(4);
-            // the threshold: the n_cand-th smallest group minimum over BOTH halves (at least n_cand slots lie at or under it)
-            {
-                const int other = 1 - ch;
-#pragma unroll
-                for (int i = 0; i < NC; ++i) insert_best(xbest[(other * NC + i) * BM + my_row]);
-            }
-            float theta = CUDART_INF_F;
-#pragma unroll
-            for (int i = 0; i < NC; ++i)
-                if (i == n_cand - 1) theta = best[i];
-            // e_cap bounds the pre-filter error of EVERY slot of this row. Slots up to theta + 2.5 e_cap are listed, so an
-            // unlisted slot's true v is above theta + 1.5 e_cap; theta + e_cap (rounded) is the bound that goes on.
-            const float e_cap = fmaf(pn, __int_as_float(kmax_i[0]), kEpsSum * fmaf(qs, __int_as_float(kmax_i[1]), __int_as_float(kmax_i[2]))) * 1.000001f;
-            const float t2 = fmaf(2.5f, e_cap, theta);
-            if (ch == 0) stat_excl[my_row] = theta + e_cap;
-            lap(5);
-            int cnt = 0;
-            if (alive) {
-                uint2* const my_list = list_e + (size_t)ch * (kListHalf + 1) * BM + my_row;
-                uint2* const spare = my_list + kListHalf * BM;
-                uint2* wp = my_list;  // the list's end
-                // sweep 2: list the slots at or under the widened threshold: a predicated store at the list's end, which
-                // stops advancing at the spare row (a list that reaches it counts as overflowed)
-                auto listing = [&](const uint32_t (&acc)[32], int c0) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float2 kc = kcol_s[c0 + j];
-                        const float v = fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y;
-                        if (v <= t2) {
-                            *wp = make_uint2(__float_as_uint(v), (unsigned)(c0 + j));
-                            if (wp != spare) wp += BM;
+                        for (int j = 0; j < 32; ++j) {
+                            const float2 kc = kcol_s[c0 + j];
+                            vmin = fminf(vmin, fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y);
                         }
+                    };
+                    tcgen05_ld_32x32_issue(taddr + c_begin, buf0);
+                    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                        tcgen05_wait_ld(buf0);
+                        tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
+                        minimum(buf0, c0);
+                        tcgen05_wait_ld(buf1);
+                        tcgen05_ld_32x32_issue(taddr + (c0 + 64 < c_end ? c0 + 64 : c_begin), buf0);  // wraps to the second sweep's first columns
+                        minimum(buf1, c0 + 32);
                     }
-                };
-                for (int c0 = c_begin; c0 < c_end; c0 += 64) {
-                    tcgen05_wait_ld(buf0);
-                    tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
-                    listing(buf0, c0);
-                    tcgen05_wait_ld(buf1);
-                    if (c0 + 64 < c_end) tcgen05_ld_32x32_issue(taddr + c0 + 64, buf0);
-                    listing(buf1, c0 + 32);
                 }
-                cnt = (int)((wp - my_list) / BM);
-                if (cnt == kListHalf) cnt = kListHalf + 1;
-            }
-            tcgen05_fence_before();
-            stat_cnt[ch * BM + my_row] = alive ? cnt : kListHalf + 1;
-            bar_workers();
-            lap(6);
-            // ---- P4: one thread per row: the n_cand smallest of the two lists by (v, slot) and the lower bound of the true v
-            // of everything else
-            if (wtid < BM) {
-                const int r = wtid;
-                const float qs_r = stat_qs[r];
-                const float pn_r = sqrtf(qs_r) * 1.0000002f;
-                float excl_r = stat_excl[r];
-                const int cnt0 = stat_cnt[r], cnt1 = stat_cnt[BM + r];
-                const bool trusted = cnt0 <= kListHalf && cnt1 <= kListHalf;
-                // keys (v bits, slot): v >= -tiny; a value rounded below zero sorts by its magnitude, still among the smallest
-                unsigned long long top[NC];
+                row_min[ch * BM + my_row] = vmin;
+                bar_workers();
+                lap(4);
+                {
+                    // lg2(1 + z) of the row's nearest slot, times 1 / tau: the exponent every weight is measured against
+                    const float u = fmaxf(fminf(row_min[my_row], row_min[BM + my_row]), 0.0f) * inv1mq;
+                    float r, lg;
+                    const float t = fmaf(u, u, u);
+                    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+                    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(1.0f + fmaf(2.0f, r, 2.0f * u)));
+                    lg_min_t = lg * inv_tau;
+                }
+                lap(5);
+                if (alive) {
+                    __nv_bfloat16* my_park = park + (size_t)my_row * W_PITCH;
+                    auto weights = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
-                for (int i = 0; i < NC; ++i) top[i] = ~0ull;
-                for (int h = 0; h < 2; ++h) {
-                    const int n_list = min(h == 0 ? cnt0 : cnt1, kListHalf);
-                    for (int e = 0; e < n_list; ++e) {
-                        const uint2 le = list_e[(h * (kListHalf + 1) + e) * BM + r];
-                        unsigned long long x = ((unsigned long long)(le.x & 0x7fffffffu) << 32) | le.y;
+                        for (int j0 = 0; j0 < 32; j0 += 8) {
+                            float e[8];
 #pragma unroll
-                        for (int i = 0; i < NC; ++i) {
-                            if (i < n_cand) {  // entries past the candidates stay empty: what falls out of the first n_cand is excluded
-                                const unsigned long long lo = umin64(top[i], x), hi = umax64(top[i], x);
-                                top[i] = lo, x = hi;
+                            for (int j = 0; j < 8; ++j) {
+                                const float2 kc = kcol_s[c0 + j0 + j];
+                                // slots past the occupied ones carry v = 3e38: every step below keeps the infinity and the weight is 0
+                                const float u = fmaxf(fmaf(-2.0f, __uint_as_float(acc[j0 + j]), qs + kc.x) * kc.y, 0.0f) * inv1mq;
+                                float r, lg;
+                                const float t = fmaf(u, u, u);
+                                asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+                                asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(1.0f + fmaf(2.0f, r, 2.0f * u)));
+                                e[j] = ex2_fast(fmaf(-inv_tau, lg, lg_min_t));
+                                sum += e[j];
+                            }
+                            uint4 pk;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(e[4], e[5]), h3 = __floats2bfloat162_rn(e[6], e[7]);
+                            pk.x = *reinterpret_cast<uint32_t*>(&h0), pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&h2), pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(my_park + c0 + j0) = pk;
+                        }
+                    };
+                    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                        tcgen05_wait_ld(buf0);
+                        tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
+                        weights(buf0, c0);
+                        tcgen05_wait_ld(buf1);
+                        if (c0 + 64 < c_end) tcgen05_ld_32x32_issue(taddr + c0 + 64, buf0);
+                        weights(buf1, c0 + 32);
+                    }
+                }
+                tcgen05_fence_before();
+                row_sum[ch * BM + my_row] = sum;
+                bar_workers();
+                lap(6);
+                // the rows go out normalised, 16 bytes per thread and consecutive threads along a row: whole 128-byte lines;
+                // four rows per pass, their loads issued before the first is used
+                {
+                    const int c8n = cap >> 3;                    // 16-byte pieces per row: 16, 32 or 64
+                    const int c8 = wtid % c8n, r_first = wtid / c8n, r_step = (32 * kWorkWarps) / c8n;
+                    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.w_split);
+                    for (int r0 = r_first; r0 < BM; r0 += 4 * r_step) {
+                        uint4 pk[4];
+                        float inv[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int r = r0 + u * r_step;
+                            if (r < BM) {
+                                pk[u] = *reinterpret_cast<const uint4*>(park + (size_t)r * W_PITCH + c8 * 8);
+                                inv[u] = row_sum[r] + row_sum[BM + r];
                             }
                         }
-                        if (x != ~0ull) {  // a listed slot that is not (or no longer) a candidate: v minus its own error bound
-                            const unsigned slot = (unsigned)(x & 0xffffu);
-                            const float2 kc = kcol_s[slot];
-                            const float w = (qs_r + kc.x) * kc.y * 1.0000002f;
-                            excl_r = fminf(excl_r, fmaf(-pn_r, kerr_s[slot], fmaf(-kEpsSum, w, __uint_as_float((unsigned)(x >> 32)))));
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int r = r0 + u * r_step;
+                            if (r < BM && q0 + r < p.rows) {
+                                const float sc = __fdividef(1.0f, inv[u]);
+                                uint32_t* w4 = reinterpret_cast<uint32_t*>(&pk[u]);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[e]));
+                                    const __nv_bfloat162 o = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+                                    w4[e] = *reinterpret_cast<const uint32_t*>(&o);
+                                }
+                                *reinterpret_cast<uint4*>(out + (q0 + r) * (size_t)(3 * cap) + c8 * 8) = pk[u];
+                            }
                         }
                     }
                 }
-#pragma unroll
-                for (int i = 0; i < NC; ++i) cand_slot[r * kCandMax + i] = (unsigned short)(top[i] & 0xffffu);
-                stat_excl[BM + r] = excl_r;
-                // untrusted (a list overflowed), nothing to bound with, or past the end: no re-scoring; P5c hands the row over
-                stat_mark[r] = (trusted && excl_r > 0.0f && q0 + r < p.rows) ? 1u : 0u;
-            }
-            bar_workers();  // the lists are consumed: their memory becomes the exact stage's
-            if (wtid == 0) *flag_count = 0;  // (ordered before P5c's increments by the barriers in between)
-            lap(7);
-            // the next tile's queries towards the L2 while this tile is finished
-            {
-                const long long next = tile + gridDim.x;
-                if (next < n_tiles) {
-                    constexpr int LPR = DK * 4 / 128;  // 128-byte lines per row
-                    for (int idx = wtid; idx < BM * LPR; idx += 32 * kWorkWarps) {
-                        const size_t r = (size_t)next * BM + idx / LPR;
-                        if (r < p.rows) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q + r * ldq + (idx % LPR) * 32));
+                bar_workers();  // the parked rows are consumed: the next tile may overwrite the operand and the ring
+                lap(7);
+            } else {
+                const float qs = stat_qs[my_row];
+                const float pn = sqrtf(qs) * 1.0000002f;
+                const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+                float best[NC];
+    #pragma unroll
+                for (int i = 0; i < NC; ++i) best[i] = CUDART_INF_F;
+                auto insert_best = [&](float x) {  // keep the NC smallest, sorted; branch-free
+    #pragma unroll
+                    for (int i = 0; i < NC; ++i) {
+                        const float lo = fminf(best[i], x), hi = fmaxf(best[i], x);
+                        best[i] = lo, x = hi;
                     }
-                }
-            }
-            // ---- P5a: exact squared distances, L = DK/16 lanes per row: lane g of a row holds the coordinates 4 (L s + g) .. + 3
-            // (s = 0..3) of the projected point as f64 -- the sum of the three bf16 pieces is the fp32 point, exactly -- and walks
-            // the row's candidates with the next two candidates' keys in flight: f64 differences to the key, squared and summed in
-            // four partial sums that are combined in a fixed order within the lane and then across the L lanes. Like the
-            // separate f64 kernel's fused multiply-adds this differs from the reference's one sequential sum only in the last
-            // bits of an f64 that is then rounded to f32. Conversions to f64 are the slow instructions here: the point is
-            // converted once per row.
-            for (int item = wtid; item < BM * L; item += 32 * kWorkWarps) {
-                const int r = item / L, g = item % L;
-                const bool active = stat_mark[r] != 0u;  // uniform over the lanes of a row
-                double pd[4][4];
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const int c = 4 * (L * s + g);
-                    const uint32_t off = sw128_offset(r, c % BK);
-                    const int kb = c / BK;
-                    const uint2 x0 = *reinterpret_cast<const uint2*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off);
-                    const uint2 x1 = *reinterpret_cast<const uint2*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off);
-                    const uint2 x2 = *reinterpret_cast<const uint2*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off);
-                    // a bf16 is the upper half of its fp32
-                    pd[s][0] = (double)(__uint_as_float(x0.x << 16) + (__uint_as_float(x1.x << 16) + __uint_as_float(x2.x << 16)));
-                    pd[s][1] = (double)(__uint_as_float(x0.x & 0xffff0000u) + (__uint_as_float(x1.x & 0xffff0000u) + __uint_as_float(x2.x & 0xffff0000u)));
-                    pd[s][2] = (double)(__uint_as_float(x0.y << 16) + (__uint_as_float(x1.y << 16) + __uint_as_float(x2.y << 16)));
-                    pd[s][3] = (double)(__uint_as_float(x0.y & 0xffff0000u) + (__uint_as_float(x1.y & 0xffff0000u) + __uint_as_float(x2.y & 0xffff0000u)));
-                }
-                const unsigned short* cs = cand_slot + r * kCandMax;
-                float4 kv[3][4];  // a ring of three keys: two in flight ahead of the one in use
-                auto fetch = [&](int j, float4 (&dst)[4]) {
-                    const float4* krow = reinterpret_cast<const float4*>(p.keys + (size_t)cs[j] * dk) + g;
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) dst[s] = __ldg(krow + L * s);
                 };
-                double tot[NC];
-                if (active) {
-                    fetch(0, kv[0]);
-                    if (1 < n_cand) fetch(1, kv[1]);
-                }
-#pragma unroll
-                for (int j = 0; j < NC; ++j) {
-                    tot[j] = 0.0;
-                    if (active && j < n_cand) {
-                        if (j + 2 < n_cand) fetch(j + 2, kv[(j + 2) % 3]);
-                        double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
-#pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-                            const float4 kk = kv[j % 3][s];
-                            const double d0 = pd[s][0] - (double)kk.x, d1 = pd[s][1] - (double)kk.y;
-                            const double d2 = pd[s][2] - (double)kk.z, d3 = pd[s][3] - (double)kk.w;
-                            s0 = fma(d0, d0, s0), s1 = fma(d1, d1, s1), s2 = fma(d2, d2, s2), s3 = fma(d3, d3, s3);
+                // both sweeps read 32 columns per tcgen05.ld into one of two register buffers, the next load in flight while
+                // the current buffer is used
+                uint32_t buf0[32], buf1[32];
+                if (alive) {
+                    // sweep 1: group minima
+                    auto minima = [&](const uint32_t (&acc)[32], int c0) {
+                        float vmin[4] = {CUDART_INF_F, CUDART_INF_F, CUDART_INF_F, CUDART_INF_F};  // minima of the four groups of 8 columns
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float2 kc = kcol_s[c0 + j];
+                            vmin[j >> 3] = fminf(vmin[j >> 3], fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y);
                         }
-                        tot[j] = (s0 + s1) + (s2 + s3);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < NC; ++j) {
-                    if (j < n_cand) {  // uniform over the warp
-                        double t = tot[j];
-#pragma unroll
-                        for (int m = 1; m < L; m <<= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
-                        if (g == 0) sqbuf[r * NC + j] = t;
-                    }
-                }
-            }
-            bar_workers();
-            lap(8);
-            // ---- P5b: one thread per (row, candidate), three at a time (f64 latency): the distance from the squared distance as
-            // `poincare_distance` computes it (f64 log1p form of 2 asinh sqrt, rounded to f32). Item n_cand of a row is the
-            // bound: every non-candidate has a true v of at least excl (1 - 4e-7: the f32 rounding of v itself), so its
-            // distance is at least d(v_lb / (1 - |p|^2)); the selection is proven when its largest distance is strictly smaller.
-            {
-                const int per_row = n_cand + 1, n_items = BM * per_row;
-                auto item_distance = [&](int t) {
-                    const int r = t / per_row, j = t - r * per_row;
-                    const bool bound = j == n_cand;
-                    const double sq = bound ? (double)stat_excl[BM + r] * (1.0 - 4e-7) : sqbuf[r * NC + j];
-                    const float ns = bound ? 0.0f : __ldg(p.norm_sq + cand_slot[r * kCandMax + j]);
-                    return exact_distance(sq, 1.0 - (double)stat_qs[r], ns);
-                };
-                auto item_store = [&](int t, float d) {
-                    const int r = t / per_row, j = t - r * per_row;
-                    if (j == n_cand)
-                        stat_dlb[r] = __float_as_uint(d);
-                    else
-                        d32[r * (NC + 1) + j] = d;
-                };
-                for (int t = wtid; t < n_items; t += 3 * 32 * kWorkWarps) {
-                    // the last pass may compute an item twice (same value, same address)
-                    const int ta = t, tb = min(t + 32 * kWorkWarps, n_items - 1), tc = min(t + 2 * 32 * kWorkWarps, n_items - 1);
-                    const float da = item_distance(ta), db = item_distance(tb), dc = item_distance(tc);
-                    item_store(ta, da), item_store(tb, db), item_store(tc, dc);
-                }
-            }
-            bar_workers();
-            lap(9);
-            // ---- P5c: one thread per row: selection by (distance bits, slot), the proof, softmax over the selected slots
-            if (wtid < BM) {
-                const int r = wtid;
-                const size_t q = q0 + r;
-                int ok = 0;
-                if (q < p.rows) {
-                    bool decisive = false;
-                    if (stat_mark[r] != 0u) {
-                        unsigned long long key[NC];
-#pragma unroll
-                        for (int j = 0; j < NC; ++j)
-                            key[j] = j < n_cand ? (((unsigned long long)__float_as_uint(d32[r * (NC + 1) + j]) << 32) | cand_slot[r * kCandMax + j]) : ~0ull;
-                        unsigned kth = 0u, mn = 0xffffffffu;
-                        unsigned selected = 0;  // bit j: candidate j is among the k smallest (bits, slot)
-#pragma unroll
-                        for (int j = 0; j < NC; ++j) {
-                            int rank = 0;
-#pragma unroll
-                            for (int i = 0; i < NC; ++i) rank += key[i] < key[j] ? 1 : 0;
-                            const unsigned bits = (unsigned)(key[j] >> 32);
-                            if (j < n_cand && rank < k) selected |= 1u << j, kth = max(kth, bits);
-                            if (j < n_cand) mn = min(mn, bits);
+                        if (group == 32) {
+                            insert_best(fminf(fminf(vmin[0], vmin[1]), fminf(vmin[2], vmin[3])));
+                        } else if (group == 16) {
+                            insert_best(fminf(vmin[0], vmin[1]));
+                            insert_best(fminf(vmin[2], vmin[3]));
+                        } else {
+    #pragma unroll
+                            for (int g = 0; g < 4; ++g) insert_best(vmin[g]);
                         }
-                        decisive = kth < stat_dlb[r];
-                        if (p.selftest_every > 0 && q % (size_t)p.selftest_every == 0) decisive = false;
-                        if (decisive) {
-                            const float dmin = __uint_as_float(mn);
-                            // ascending slot order (memory.rs:389-390), weights exp((min - d) / tau), their sum in that order
-#pragma unroll
+                    };
+                    tcgen05_ld_32x32_issue(taddr + c_begin, buf0);
+                    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                        tcgen05_wait_ld(buf0);
+                        tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
+                        minima(buf0, c0);
+                        tcgen05_wait_ld(buf1);
+                        tcgen05_ld_32x32_issue(taddr + (c0 + 64 < c_end ? c0 + 64 : c_begin), buf0);  // wraps to the second sweep's first columns
+                        minima(buf1, c0 + 32);
+                    }
+                }
+    #pragma unroll
+                for (int i = 0; i < NC; ++i) xbest[(ch * NC + i) * BM + my_row] = best[i];
+                bar_workers();
+                lap(4);
+                // the threshold: the n_cand-th smallest group minimum over BOTH halves (at least n_cand slots lie at or under it)
+                {
+                    const int other = 1 - ch;
+    #pragma unroll
+                    for (int i = 0; i < NC; ++i) insert_best(xbest[(other * NC + i) * BM + my_row]);
+                }
+                float theta = CUDART_INF_F;
+    #pragma unroll
+                for (int i = 0; i < NC; ++i)
+                    if (i == n_cand - 1) theta = best[i];
+                // e_cap bounds the pre-filter error of EVERY slot of this row. Slots up to theta + 2.5 e_cap are listed, so an
+                // unlisted slot's true v is above theta + 1.5 e_cap; theta + e_cap (rounded) is the bound that goes on.
+                const float e_cap = fmaf(pn, __int_as_float(kmax_i[0]), kEpsSum * fmaf(qs, __int_as_float(kmax_i[1]), __int_as_float(kmax_i[2]))) * 1.000001f;
+                const float t2 = fmaf(2.5f, e_cap, theta);
+                if (ch == 0) stat_excl[my_row] = theta + e_cap;
+                lap(5);
+                int cnt = 0;
+                if (alive) {
+                    uint2* const my_list = list_e + (size_t)ch * (kListHalf + 1) * BM + my_row;
+                    uint2* const spare = my_list + kListHalf * BM;
+                    uint2* wp = my_list;  // the list's end
+                    // sweep 2: list the slots at or under the widened threshold: a predicated store at the list's end, which
+                    // stops advancing at the spare row (a list that reaches it counts as overflowed)
+                    auto listing = [&](const uint32_t (&acc)[32], int c0) {
+    #pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float2 kc = kcol_s[c0 + j];
+                            const float v = fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y;
+                            if (v <= t2) {
+                                *wp = make_uint2(__float_as_uint(v), (unsigned)(c0 + j));
+                                if (wp != spare) wp += BM;
+                            }
+                        }
+                    };
+                    for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+                        tcgen05_wait_ld(buf0);
+                        tcgen05_ld_32x32_issue(taddr + c0 + 32, buf1);
+                        listing(buf0, c0);
+                        tcgen05_wait_ld(buf1);
+                        if (c0 + 64 < c_end) tcgen05_ld_32x32_issue(taddr + c0 + 64, buf0);
+                        listing(buf1, c0 + 32);
+                    }
+                    cnt = (int)((wp - my_list) / BM);
+                    if (cnt == kListHalf) cnt = kListHalf + 1;
+                }
+                tcgen05_fence_before();
+                stat_cnt[ch * BM + my_row] = alive ? cnt : kListHalf + 1;
+                bar_workers();
+                lap(6);
+                // ---- P4: one thread per row: the n_cand smallest of the two lists by (v, slot) and the lower bound of the true v
+                // of everything else
+                if (wtid < BM) {
+                    const int r = wtid;
+                    const float qs_r = stat_qs[r];
+                    const float pn_r = sqrtf(qs_r) * 1.0000002f;
+                    float excl_r = stat_excl[r];
+                    const int cnt0 = stat_cnt[r], cnt1 = stat_cnt[BM + r];
+                    const bool trusted = cnt0 <= kListHalf && cnt1 <= kListHalf;
+                    // keys (v bits, slot): v >= -tiny; a value rounded below zero sorts by its magnitude, still among the smallest
+                    unsigned long long top[NC];
+    #pragma unroll
+                    for (int i = 0; i < NC; ++i) top[i] = ~0ull;
+                    for (int h = 0; h < 2; ++h) {
+                        const int n_list = min(h == 0 ? cnt0 : cnt1, kListHalf);
+                        for (int e = 0; e < n_list; ++e) {
+                            const uint2 le = list_e[(h * (kListHalf + 1) + e) * BM + r];
+                            unsigned long long x = ((unsigned long long)(le.x & 0x7fffffffu) << 32) | le.y;
+    #pragma unroll
+                            for (int i = 0; i < NC; ++i) {
+                                if (i < n_cand) {  // entries past the candidates stay empty: what falls out of the first n_cand is excluded
+                                    const unsigned long long lo = umin64(top[i], x), hi = umax64(top[i], x);
+                                    top[i] = lo, x = hi;
+                                }
+                            }
+                            if (x != ~0ull) {  // a listed slot that is not (or no longer) a candidate: v minus its own error bound
+                                const unsigned slot = (unsigned)(x & 0xffffu);
+                                const float2 kc = kcol_s[slot];
+                                const float w = (qs_r + kc.x) * kc.y * 1.0000002f;
+                                excl_r = fminf(excl_r, fmaf(-pn_r, kerr_s[slot], fmaf(-kEpsSum, w, __uint_as_float((unsigned)(x >> 32)))));
+                            }
+                        }
+                    }
+    #pragma unroll
+                    for (int i = 0; i < NC; ++i) cand_slot[r * kCandMax + i] = (unsigned short)(top[i] & 0xffffu);
+                    stat_excl[BM + r] = excl_r;
+                    // untrusted (a list overflowed), nothing to bound with, or past the end: no re-scoring; P5c hands the row over
+                    stat_mark[r] = (trusted && excl_r > 0.0f && q0 + r < p.rows) ? 1u : 0u;
+                }
+                bar_workers();  // the lists are consumed: their memory becomes the exact stage's
+                if (wtid == 0) *flag_count = 0;  // (ordered before P5c's increments by the barriers in between)
+                lap(7);
+                // the next tile's queries towards the L2 while this tile is finished
+                {
+                    const long long next = tile + gridDim.x;
+                    if (next < n_tiles) {
+                        constexpr int LPR = DK * 4 / 128;  // 128-byte lines per row
+                        for (int idx = wtid; idx < BM * LPR; idx += 32 * kWorkWarps) {
+                            const size_t r = (size_t)next * BM + idx / LPR;
+                            if (r < p.rows) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.q + r * ldq + (idx % LPR) * 32));
+                        }
+                    }
+                }
+                // ---- P5a: exact squared distances, L = DK/16 lanes per row: lane g of a row holds the coordinates 4 (L s + g) .. + 3
+                // (s = 0..3) of the projected point as f64 -- the sum of the three bf16 pieces is the fp32 point, exactly -- and walks
+                // the row's candidates with the next two candidates' keys in flight: f64 differences to the key, squared and summed in
+                // four partial sums that are combined in a fixed order within the lane and then across the L lanes. Like the
+                // separate f64 kernel's fused multiply-adds this differs from the reference's one sequential sum only in the last
+                // bits of an f64 that is then rounded to f32. Conversions to f64 are the slow instructions here: the point is
+                // converted once per row.
+                for (int item = wtid; item < BM * L; item += 32 * kWorkWarps) {
+                    const int r = item / L, g = item % L;
+                    const bool active = stat_mark[r] != 0u;  // uniform over the lanes of a row
+                    double pd[4][4];
+    #pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const int c = 4 * (L * s + g);
+                        const uint32_t off = sw128_offset(r, c % BK);
+                        const int kb = c / BK;
+                        const uint2 x0 = *reinterpret_cast<const uint2*>(smem_a + (0 * KB_PIECE + kb) * A_BLOCK + off);
+                        const uint2 x1 = *reinterpret_cast<const uint2*>(smem_a + (1 * KB_PIECE + kb) * A_BLOCK + off);
+                        const uint2 x2 = *reinterpret_cast<const uint2*>(smem_a + (2 * KB_PIECE + kb) * A_BLOCK + off);
+                        // a bf16 is the upper half of its fp32
+                        pd[s][0] = (double)(__uint_as_float(x0.x << 16) + (__uint_as_float(x1.x << 16) + __uint_as_float(x2.x << 16)));
+                        pd[s][1] = (double)(__uint_as_float(x0.x & 0xffff0000u) + (__uint_as_float(x1.x & 0xffff0000u) + __uint_as_float(x2.x & 0xffff0000u)));
+                        pd[s][2] = (double)(__uint_as_float(x0.y << 16) + (__uint_as_float(x1.y << 16) + __uint_as_float(x2.y << 16)));
+                        pd[s][3] = (double)(__uint_as_float(x0.y & 0xffff0000u) + (__uint_as_float(x1.y & 0xffff0000u) + __uint_as_float(x2.y & 0xffff0000u)));
+                    }
+                    const unsigned short* cs = cand_slot + r * kCandMax;
+                    float4 kv[3][4];  // a ring of three keys: two in flight ahead of the one in use
+                    auto fetch = [&](int j, float4 (&dst)[4]) {
+                        const float4* krow = reinterpret_cast<const float4*>(p.keys + (size_t)cs[j] * dk) + g;
+    #pragma unroll
+                        for (int s = 0; s < 4; ++s) dst[s] = __ldg(krow + L * s);
+                    };
+                    double tot[NC];
+                    if (active) {
+                        fetch(0, kv[0]);
+                        if (1 < n_cand) fetch(1, kv[1]);
+                    }
+    #pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        tot[j] = 0.0;
+                        if (active && j < n_cand) {
+                            if (j + 2 < n_cand) fetch(j + 2, kv[(j + 2) % 3]);
+                            double s0 = 0.0, s1 = 0.0, s2 = 0.0, s3 = 0.0;
+    #pragma unroll
+                            for (int s = 0; s < 4; ++s) {
+                                const float4 kk = kv[j % 3][s];
+                                const double d0 = pd[s][0] - (double)kk.x, d1 = pd[s][1] - (double)kk.y;
+                                const double d2 = pd[s][2] - (double)kk.z, d3 = pd[s][3] - (double)kk.w;
+                                s0 = fma(d0, d0, s0), s1 = fma(d1, d1, s1), s2 = fma(d2, d2, s2), s3 = fma(d3, d3, s3);
+                            }
+                            tot[j] = (s0 + s1) + (s2 + s3);
+                        }
+                    }
+    #pragma unroll
+                    for (int j = 0; j < NC; ++j) {
+                        if (j < n_cand) {  // uniform over the warp
+                            double t = tot[j];
+    #pragma unroll
+                            for (int m = 1; m < L; m <<= 1) t += __shfl_xor_sync(0xffffffffu, t, m);
+                            if (g == 0) sqbuf[r * NC + j] = t;
+                        }
+                    }
+                }
+                bar_workers();
+                lap(8);
+                // ---- P5b: one thread per (row, candidate), three at a time (f64 latency): the distance from the squared distance as
+                // `poincare_distance` computes it (f64 log1p form of 2 asinh sqrt, rounded to f32). Item n_cand of a row is the
+                // bound: every non-candidate has a true v of at least excl (1 - 4e-7: the f32 rounding of v itself), so its
+                // distance is at least d(v_lb / (1 - |p|^2)); the selection is proven when its largest distance is strictly smaller.
+                {
+                    const int per_row = n_cand + 1, n_items = BM * per_row;
+                    auto item_distance = [&](int t) {
+                        const int r = t / per_row, j = t - r * per_row;
+                        const bool bound = j == n_cand;
+                        const double sq = bound ? (double)stat_excl[BM + r] * (1.0 - 4e-7) : sqbuf[r * NC + j];
+                        const float ns = bound ? 0.0f : __ldg(p.norm_sq + cand_slot[r * kCandMax + j]);
+                        return exact_distance(sq, 1.0 - (double)stat_qs[r], ns);
+                    };
+                    auto item_store = [&](int t, float d) {
+                        const int r = t / per_row, j = t - r * per_row;
+                        if (j == n_cand)
+                            stat_dlb[r] = __float_as_uint(d);
+                        else
+                            d32[r * (NC + 1) + j] = d;
+                    };
+                    for (int t = wtid; t < n_items; t += 3 * 32 * kWorkWarps) {
+                        // the last pass may compute an item twice (same value, same address)
+                        const int ta = t, tb = min(t + 32 * kWorkWarps, n_items - 1), tc = min(t + 2 * 32 * kWorkWarps, n_items - 1);
+                        const float da = item_distance(ta), db = item_distance(tb), dc = item_distance(tc);
+                        item_store(ta, da), item_store(tb, db), item_store(tc, dc);
+                    }
+                }
+                bar_workers();
+                lap(9);
+                // ---- P5c: one thread per row: selection by (distance bits, slot), the proof, softmax over the selected slots
+                if (wtid < BM) {
+                    const int r = wtid;
+                    const size_t q = q0 + r;
+                    int ok = 0;
+                    if (q < p.rows) {
+                        bool decisive = false;
+                        if (stat_mark[r] != 0u) {
+                            unsigned long long key[NC];
+    #pragma unroll
+                            for (int j = 0; j < NC; ++j)
+                                key[j] = j < n_cand ? (((unsigned long long)__float_as_uint(d32[r * (NC + 1) + j]) << 32) | cand_slot[r * kCandMax + j]) : ~0ull;
+                            unsigned kth = 0u, mn = 0xffffffffu;
+                            unsigned selected = 0;  // bit j: candidate j is among the k smallest (bits, slot)
+    #pragma unroll
                             for (int j = 0; j < NC; ++j) {
-                                if (!(selected >> j & 1u)) continue;
-                                const unsigned slot = (unsigned)key[j] & 0xffffu;
-                                int srank = 0;
-#pragma unroll
-                                for (int i = 0; i < NC; ++i) srank += ((selected >> i & 1u) && ((unsigned)key[i] & 0xffffu) < slot) ? 1 : 0;
-                                sels[r * NC + srank] = slot;
-                                selw[r * NC + srank] = expf(__fdiv_rn(__fsub_rn(dmin, __uint_as_float((unsigned)(key[j] >> 32))), p.tau));
+                                int rank = 0;
+    #pragma unroll
+                                for (int i = 0; i < NC; ++i) rank += key[i] < key[j] ? 1 : 0;
+                                const unsigned bits = (unsigned)(key[j] >> 32);
+                                if (j < n_cand && rank < k) selected |= 1u << j, kth = max(kth, bits);
+                                if (j < n_cand) mn = min(mn, bits);
                             }
-                            float sum = 0.0f;
-                            for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, selw[r * NC + j]);
-                            for (int j = 0; j < k; ++j) {
-                                const float wn = __fdiv_rn(selw[r * NC + j], sum);
-                                selw[r * NC + j] = wn;
-                                if (p.topk_slots) p.topk_slots[q * k + j] = sels[r * NC + j];
-                                if (p.topk_weights) p.topk_weights[q * k + j] = wn;
+                            decisive = kth < stat_dlb[r];
+                            if (p.selftest_every > 0 && q % (size_t)p.selftest_every == 0) decisive = false;
+                            if (decisive) {
+                                const float dmin = __uint_as_float(mn);
+                                // ascending slot order (memory.rs:389-390), weights exp((min - d) / tau), their sum in that order
+    #pragma unroll
+                                for (int j = 0; j < NC; ++j) {
+                                    if (!(selected >> j & 1u)) continue;
+                                    const unsigned slot = (unsigned)key[j] & 0xffffu;
+                                    int srank = 0;
+    #pragma unroll
+                                    for (int i = 0; i < NC; ++i) srank += ((selected >> i & 1u) && ((unsigned)key[i] & 0xffffu) < slot) ? 1 : 0;
+                                    sels[r * NC + srank] = slot;
+                                    selw[r * NC + srank] = expf(__fdiv_rn(__fsub_rn(dmin, __uint_as_float((unsigned)(key[j] >> 32))), p.tau));
+                                }
+                                float sum = 0.0f;
+                                for (int j = 0; j < k; ++j) sum = __fadd_rn(sum, selw[r * NC + j]);
+                                for (int j = 0; j < k; ++j) {
+                                    const float wn = __fdiv_rn(selw[r * NC + j], sum);
+                                    selw[r * NC + j] = wn;
+                                    if (p.topk_slots) p.topk_slots[q * k + j] = sels[r * NC + j];
+                                    if (p.topk_weights) p.topk_weights[q * k + j] = wn;
+                                }
+                                if (p.min_dist) p.min_dist[q] = dmin;
+                                ok = 1;
                             }
-                            if (p.min_dist) p.min_dist[q] = dmin;
-                            ok = 1;
                         }
+                        if (!decisive) flag_rows[atomicAdd(flag_count, 1)] = r;  // the exact stage writes this row
                     }
-                    if (!decisive) flag_rows[atomicAdd(flag_count, 1)] = r;  // the exact stage writes this row
+                    row_ok[r] = ok;
                 }
-                row_ok[r] = ok;
+                bar_workers();
+                lap(10);
+                // ---- P5d: the value read of the proven rows
+                read_selected_values<NC>(p.values, p.dv, p.m_val, p.m_bf16, p.weights, cap, k, q0, sels, selw, row_ok, wtid);
+                // ---- P5e: the rows whose selection the candidates could not prove (or a list overflowed, or the test hook) are
+                // recomputed over every slot. Rare, and uniform over the CTA (the count is shared); kept out of line so that it
+                // costs the common path no registers.
+                bar_workers();
+                if (*flag_count > 0) {
+                    const RetrieveParams pc = p;  // a local copy for the out-of-line call: the common path keeps reading the parameter bank
+                    exact_rows<DK>(pc, q0, smem_a, stat_qs, flag_rows, *flag_count, fx_p, fx_dist, fx_slot, fx_w, wtid);
+                }
+                bar_workers();  // the lists and the operand are free for the next tile
+                lap(11);
             }
-            bar_workers();
-            lap(10);
-            // ---- P5d: the value read of the proven rows
-            read_selected_values<NC>(p.values, p.dv, p.m_val, p.m_bf16, p.weights, cap, k, q0, sels, selw, row_ok, wtid);
-            // ---- P5e: the rows whose selection the candidates could not prove (or a list overflowed, or the test hook) are
-            // recomputed over every slot. Rare, and uniform over the CTA (the count is shared); kept out of line so that it
-            // costs the common path no registers.
-            bar_workers();
-            if (*flag_count > 0) {
-                const RetrieveParams pc = p;  // a local copy for the out-of-line call: the common path keeps reading the parameter bank
-                exact_rows<DK>(pc, q0, smem_a, stat_qs, flag_rows, *flag_count, fx_p, fx_dist, fx_slot, fx_w, wtid);
-            }
-            bar_workers();  // the lists and the operand are free for the next tile
-            lap(11);
         }
         if (p.phase_cycles && wtid == 0)
             for (int i = 0; i < kPhases; ++i) atomicAdd(p.phase_cycles + i, (unsigned long long)phase_clk[i]);
@@ -892,6 +1054,40 @@ int32_t launch_retrieve_fused(pssa_b200_ctx* ctx, const RetrieveParams& p) {
         rc = few ? go(retrieve_topk_fused_kernel<128, 9>, 2) : go(retrieve_topk_fused_kernel<128, kCandMax>, 3);
     if (rc) return rc;
     return after_launch(ctx, "retrieve_topk_fused_kernel");
+}
+
+// The all-slots read of the fast modes as one kernel (projection, distances, softmax, bf16 weight rows): for callers
+// that keep only the leading bf16 piece of every weight and multiply it themselves (the model's bf16 precision).
+bool retrieve_all_fused_eligible(const RetrieveParams& p) {
+    const bool topk = p.top_k != 0 && p.top_k < p.count;
+    return !topk && !p.single_token && p.count > 0 && p.value_terms == 1 && p.skip_value_read && p.skip_weights && p.w_split && !p.min_dist &&
+           (p.cap == 128 || p.cap == 256 || p.cap == 512) && (p.dk == 64 || p.dk == 128) && p.k_split && p.k_stat && p.rows > 0 &&
+           p.rows <= 0xffffffffull && p.tau > 0.0f && (reinterpret_cast<uintptr_t>(p.w_split) & 15) == 0;
+}
+
+int32_t launch_retrieve_all_fused(pssa_b200_ctx* ctx, const RetrieveParams& p) {
+    if (!retrieve_all_fused_eligible(p)) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 fused all-slots read: shape not eligible");
+    RetrieveParams q = p;
+    q.status = ctx->status_dev;
+    CUtensorMap map_b;
+    int32_t rc;
+    const int nh = p.cap >= 256 ? 256 : p.cap;
+    if ((rc = make_map(ctx, &map_b, p.k_split, (size_t)p.cap, (size_t)3 * p.dk, nh))) return rc;
+    const size_t smem = fused_smem(p.dk);
+    const long long tiles = (long long)((p.rows + BM - 1) / BM);
+    const unsigned grid = (unsigned)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+    static PerDeviceOnce attr[2];
+    auto go = [&](auto kernel, int which) -> int32_t {
+        if (attr[which].need(ctx->device)) {
+            PSSA_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr[which].done(ctx->device);
+        }
+        PSSA_CUDA(ctx, launch_dependent(kernel, dim3(grid), dim3(kThreads), smem, ctx->stream, map_b, q));
+        return PSSA_B200_OK;
+    };
+    rc = p.dk == 64 ? go(retrieve_topk_fused_kernel<64, 9, true>, 0) : go(retrieve_topk_fused_kernel<128, 9, true>, 1);
+    if (rc) return rc;
+    return after_launch(ctx, "retrieve_all_fused_kernel");
 }
 
 int32_t launch_compact_topk(pssa_b200_ctx* ctx, const float* weights, int cap, int k, size_t rows, unsigned* slots, float* w_out) {

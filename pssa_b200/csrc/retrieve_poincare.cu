@@ -18,6 +18,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
+
 #include <algorithm>
 #include <cfloat>
 #include <math_constants.h>
@@ -993,6 +995,12 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     // top-k reads whose shape fits take the one-kernel path (tensor-core pre-filter, exact f64 decision): same results
     // as the f64 distance kernel below, without the [rows, capacity] matrix in HBM
     if (!p.no_fused && retrieve_fused_eligible(p)) return launch_retrieve_fused(ctx, p);
+    // all-slots reads of the bf16-grade consumers whose shape fits: projection, distances, softmax and the bf16 weight rows
+    // in one kernel (the caller multiplies the rows by its own operand)
+    // (PSSA_B200_NO_ALL_SLOTS_FUSED keeps the separate kernels: read at every call, a test compares the two)
+    const char* keep_separate = getenv("PSSA_B200_NO_ALL_SLOTS_FUSED");
+    if (!p.no_fused && !exact && !(keep_separate && *keep_separate && *keep_separate != '0') && retrieve_all_fused_eligible(p))
+        return launch_retrieve_all_fused(ctx, p);
     if (!p.weights) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: this shape needs the [rows, capacity] weight rows as scratch");
     // with an empty bank the launch still publishes the projection (gpu_batch.rs:682-698 projects first)
     static PerDeviceOnce attr_a;

@@ -485,3 +485,33 @@ def test_reserved_model_allocates_nothing_during_calls(gpu):
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] == free0
     gm.close()
+
+
+def test_one_kernel_all_slots_read_agrees_with_the_separate_kernels(gpu, monkeypatch):
+    """The bf16 mode's all-slots read runs projection, distances, softmax and the bf16 weight rows as one kernel when
+    the shape allows it (three bf16 piece products instead of six, hardware sqrt / lg2 / ex2, weights rounded to bf16
+    before and after normalisation). Against the separate kernels (same weights, same prompts): logits within 2e-3
+    max-abs of each other, and both within the bf16 mode's 2e-2 of the fp32 CPU reference; a partly filled bank gives
+    its empty slots weight zero in both."""
+    import pssa_b200
+    om = O.Model.new(2, 512, 192, 64, 64, 256, tau_mem=0.1, seed=17)
+    fill_synthetic(om, 17, 0.6)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(1, 512, n) for n in (300, 257, 128, 40)]
+    ref = np.stack([om_prefill(om, ids) for ids in prompts])
+    out = []
+    for keep in ("1", "0"):
+        monkeypatch.setenv("PSSA_B200_NO_ALL_SLOTS_FUSED", keep)
+        gm = pssa_b200.PSSAModel(gpu, 2, 512, 192, 64, 64, 256, tau_mem=0.1, streams=4, precision=0)
+        upload(om, gm)
+        logits, _ = gm.prefill_batch(prompts, want_greedy=True)
+        out.append(logits.copy())
+        gm.close()
+    assert float(np.max(np.abs(out[0] - out[1]))) <= 2e-3
+    assert float(np.max(np.abs(out[0] - ref))) <= 2e-2 and float(np.max(np.abs(out[1] - ref))) <= 2e-2
+
+
+def om_prefill(om, ids):
+    om.reset_recurrent_state()
+    _, _, logits = om.prefill_inference(ids)
+    return np.array(logits, copy=True)
