@@ -61,6 +61,8 @@ struct GemmEpilogue {
     size_t ld_add, ld_res;
     float res_scale;
     int add_is_bf16;       // EPI_RESIDUAL: add_in points at bf16 values (row pitch ld_add in elements)
+    const float* row_scale;  // EPI_GATE: optional [M] factor on the accumulator's rows (an operand whose rows are not yet
+                             // normalised: softmax weights before the division by their sum); null = 1
     // EPI_POINCARE: the accumulator is the inner product p.k of a point in the ball (row) and a bank key (column);
     // row_stat[row] = (|p|^2, 1/(1-|p|^2)), col_stat[col] = (|k|^2, 1/(1-|k|^2)); out = d(p, k)
     const float2* row_stat;
@@ -274,6 +276,14 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
             const int rbase = m0 + quad * 32;
             const bool rows_in = rbase + 32 <= e.M;  // whole 32-row band inside the matrix
             bool released = false;
+            // EPI_GATE with row factors: the eight rows a lane stores are the same for every chunk of the tile
+            // (kept in registers by the instantiation that carries only this family; the run-time one loads them where used)
+            constexpr bool kHoistRowFactors = MODE == EPI_GATE;
+            float row_f[kHoistRowFactors ? 8 : 1];
+            if constexpr (kHoistRowFactors) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) row_f[i] = e.row_scale ? __ldg(e.row_scale + min(rbase + rsub + i * 4, e.M - 1)) : 1.0f;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
                 const int col0 = n0 + c0;
@@ -397,7 +407,11 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                                     val.z = fmaf(e.res_scale, val.z, rv.z), val.w = fmaf(e.res_scale, val.w, rv.w);
                                 }
                             } else if (epi == EPI_GATE) {
-                                const float4 av = pre_add[i], gv = pre_res[i];
+                                const float4 av = pre_add[i];
+                                float4 gv = pre_res[i];
+                                const float rf = kHoistRowFactors ? row_f[kHoistRowFactors ? i : 0]
+                                                                  : (e.row_scale ? __ldg(e.row_scale + rbase + rsub + i * 4) : 1.0f);
+                                gv.x *= rf, gv.y *= rf, gv.z *= rf, gv.w *= rf;
                                 val.x = fmaf(gv.x, val.x, av.x * e.alpha), val.y = fmaf(gv.y, val.y, av.y * e.alpha);
                                 val.z = fmaf(gv.z, val.z, av.z * e.alpha), val.w = fmaf(gv.w, val.w, av.w * e.alpha);
                             }
@@ -435,7 +449,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) gemm_bf16_tcgen05_kernel(cons
                                 o[q] += e.add_is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.add_in)[ai]) : e.add_in[ai];
                                 if (e.res_in) o[q] = fmaf(e.res_scale, o[q], e.res_in[(size_t)grow * e.ld_res + gcol + q]);
                             } else if (epi == EPI_GATE) {
-                                o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q], o[q],
+                                const float rs = e.row_scale ? e.row_scale[grow] : 1.0f;
+                                o[q] = fmaf(e.res_in[(size_t)grow * e.ld_res + gcol + q] * rs, o[q],
                                             e.add_in[(size_t)grow * e.ld_add + gcol + q] * e.alpha);
                             }
                             if (out32) {
@@ -627,14 +642,15 @@ int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const voi
 // epilogue (src/pssa.rs:1189-1192 without the adapter term, which rides in the MLP products as extra K columns).
 // gate [M, ld_gate] and y [M, N] fp32; out fp32 [M, N] and out16 bf16 [M, ld16] are both written.
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
-                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K, bool split_k) {
+                              const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K, bool split_k,
+                              const float* row_scale) {
     if (split_k && K % BK != 0) return fail(ctx, PSSA_B200_ERR_UNSUPPORTED, "B200 split GEMM needs K %% 64 == 0; K = %zu", K);
     int32_t rc = check_shape(ctx, x16, w16, M, N, split_k ? 3 * K : K);
     if (rc) return rc;
     GemmEpilogue e{};
     e.out = out, e.out16 = (__nv_bfloat16*)out_bf16, e.ldo = N, e.ld16 = ld16;
     e.M = (int)M, e.N = (int)N, e.K = (int)(split_k ? 3 * K : K), e.epi = EPI_GATE, e.alpha = alpha;
-    e.add_in = y, e.res_in = gate, e.ld_add = N, e.ld_res = ld_gate, e.res_scale = 1.0f;
+    e.add_in = y, e.res_in = gate, e.ld_add = N, e.ld_res = ld_gate, e.res_scale = 1.0f, e.row_scale = row_scale;
     if (split_k) e.n_pairs = 1, e.seg_kb = (int)(K / BK);  // pair (0, 0): leading piece of each operand
     return dispatch(ctx, x16, w16, e);
 }

@@ -92,6 +92,8 @@ struct RetrieveParams {
                            // partial products (error near 2^-16), else all six (fp32-accurate)
     int f32_distance;      // fast mode: squared differences accumulated in fp32 instead of f64 (ignored when exact)
     int skip_weights;      // all-slots, non-exact, w_split set: do not write the fp32 weight rows back (only the pieces are read)
+    float* row_scale_out;  // one-kernel all-slots read only: when set, the weight rows are left as exp((d_min - d) / tau), not
+                           // divided by their sum, and 1 / sum goes here ([rows]) for the consumer's epilogue to apply
     int skip_value_read;   // all-slots, non-exact, w_split set: stop after the softmax; the caller multiplies the weight pieces itself
     // tensor-core distances (non-exact, dk % 64 == 0; used when all four are set): q_split [rows, 3*dk] bf16 and
     // q_stat [rows] are scratch written by the projection kernel; k_split [cap, 3*dk] bf16 and k_stat [cap] come from
@@ -119,6 +121,8 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
 // softmax and value read of a top-k read in one kernel; same results as the f64 path of launch_memory_read
 bool retrieve_fused_eligible(const RetrieveParams& p);
 bool retrieve_all_fused_eligible(const RetrieveParams& p);
+// what launch_memory_read decides for this call: true = the one-kernel all-slots read runs (and honours row_scale_out)
+bool retrieve_all_fused_runs(const RetrieveParams& p, bool exact);
 int32_t launch_retrieve_all_fused(pssa_b200_ctx* ctx, const RetrieveParams& p);
 int32_t launch_retrieve_fused(pssa_b200_ctx* ctx, const RetrieveParams& p);
 // dense weight rows [rows, cap] -> selected slots and weights [rows, k] in ascending slot order
@@ -184,7 +188,7 @@ int32_t launch_gemm_bf16(pssa_b200_ctx* ctx, const void* x16, const void* w16, f
 // splits (K % 64 == 0) and only the leading pieces are multiplied.
 int32_t launch_gemm_bf16_gate(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, void* out_bf16, size_t ld16,
                               const float* gate, size_t ld_gate, const float* y, float alpha, size_t M, size_t N, size_t K,
-                              bool split_k = false);
+                              bool split_k = false, const float* row_scale = nullptr);
 // MLP output with both residuals fused: out = res_in ? res_in + res_scale*(X W^T + add_in) : X W^T + add_in
 // add_in is fp32 [M, N], or bf16 [M, ld_add_bf16] when ld_add_bf16 != 0
 int32_t launch_gemm_bf16_residual(pssa_b200_ctx* ctx, const void* x16, const void* w16, float* out, const void* add_in,

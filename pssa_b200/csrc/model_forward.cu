@@ -405,6 +405,10 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
         // observer wants m itself and keeps the two-product schedule.
         const bool proj_in_read = !exact && !(observe && publish) && rp.w_split && !(rp.top_k != 0 && rp.top_k < rp.count) && rp.count > 0;
         rp.skip_value_read = proj_in_read;
+        // the one-kernel all-slots read leaves the division by the row sums to the epilogue of the product that follows
+        // (its per-row factors borrow the buffer of the separate path's query statistics, which it does not use)
+        if (proj_in_read) rp.row_scale_out = reinterpret_cast<float*>(v.q_stat);
+        const float* weight_row_scale = (proj_in_read && retrieve_all_fused_runs(rp, exact)) ? rp.row_scale_out : nullptr;
         if ((rc = launch_memory_read(ctx, rp, exact))) return rc;
         // stages 5-6: adapter up + aggregation, then the SiLU MLP with its residual (src/gpu_batch.rs:934-1072)
         if (exact) {
@@ -425,7 +429,7 @@ int32_t forward_rows(pssa_b200_model* m, size_t rows, size_t lanes, const uint32
             const size_t ldz = m->d + 64, lda = 2 * m->d + 64;
             if (proj_in_read) {
                 if ((rc = launch_gemm_bf16_gate(ctx, v.w_split, b.vpsplit_bf16, nullptr, v.z_bf16, ldz, v.proj + m->off_gate, nc, v.y, ssm_scale,
-                                                nr, m->d, m->cap, /*split_k=*/true)))
+                                                nr, m->d, m->cap, /*split_k=*/true, weight_row_scale)))
                     return rc;
             } else if ((rc = launch_gemm_bf16_gate(ctx, v.m_bf16, b.wproj_bf16, nullptr, v.z_bf16, ldz, v.proj + m->off_gate, nc, v.y, ssm_scale,
                                                    nr, m->d, m->d)))

@@ -580,8 +580,13 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                     lg_min_t = lg * inv_tau;
                 }
                 lap(5);
+                // with row_scale_out the rows leave as they are, straight from this sweep (16 bytes per row and instruction: the
+                // stores ride under the sweep's XU work), and the consumer multiplies by 1 / sum; otherwise they are parked
+                const bool defer = p.row_scale_out != nullptr;
                 if (alive) {
-                    __nv_bfloat16* my_park = park + (size_t)my_row * W_PITCH;
+                    __nv_bfloat16* my_park = defer ? reinterpret_cast<__nv_bfloat16*>(p.w_split) + (q0 + my_row) * (size_t)(3 * cap)
+                                                   : park + (size_t)my_row * W_PITCH;
+                    const bool row_in = !defer || q0 + my_row < p.rows;
                     auto weights = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
                         for (int j0 = 0; j0 < 32; j0 += 8) {
@@ -603,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                             __nv_bfloat162 h2 = __floats2bfloat162_rn(e[4], e[5]), h3 = __floats2bfloat162_rn(e[6], e[7]);
                             pk.x = *reinterpret_cast<uint32_t*>(&h0), pk.y = *reinterpret_cast<uint32_t*>(&h1);
                             pk.z = *reinterpret_cast<uint32_t*>(&h2), pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(my_park + c0 + j0) = pk;
+                            if (row_in) *reinterpret_cast<uint4*>(my_park + c0 + j0) = pk;
                         }
                     };
                     for (int c0 = c_begin; c0 < c_end; c0 += 64) {
@@ -619,9 +624,11 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                 row_sum[ch * BM + my_row] = sum;
                 bar_workers();
                 lap(6);
-                // the rows go out normalised, 16 bytes per thread and consecutive threads along a row: whole 128-byte lines;
-                // four rows per pass, their loads issued before the first is used
-                {
+                if (defer) {
+                    if (wtid < BM && q0 + wtid < p.rows) p.row_scale_out[q0 + wtid] = __fdividef(1.0f, row_sum[wtid] + row_sum[BM + wtid]);
+                } else {
+                    // the rows go out normalised, 16 bytes per thread and consecutive threads along a row: whole 128-byte
+                    // lines; four rows per pass, their loads issued before the first is used
                     const int c8n = cap >> 3;                    // 16-byte pieces per row: 16, 32 or 64
                     const int c8 = wtid % c8n, r_first = wtid / c8n, r_step = (32 * kWorkWarps) / c8n;
                     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.w_split);

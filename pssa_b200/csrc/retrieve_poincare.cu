@@ -997,10 +997,7 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
     if (!p.no_fused && retrieve_fused_eligible(p)) return launch_retrieve_fused(ctx, p);
     // all-slots reads of the bf16-grade consumers whose shape fits: projection, distances, softmax and the bf16 weight rows
     // in one kernel (the caller multiplies the rows by its own operand)
-    // (PSSA_B200_NO_ALL_SLOTS_FUSED keeps the separate kernels: read at every call, a test compares the two)
-    const char* keep_separate = getenv("PSSA_B200_NO_ALL_SLOTS_FUSED");
-    if (!p.no_fused && !exact && !(keep_separate && *keep_separate && *keep_separate != '0') && retrieve_all_fused_eligible(p))
-        return launch_retrieve_all_fused(ctx, p);
+    if (retrieve_all_fused_runs(p, exact)) return launch_retrieve_all_fused(ctx, p);
     if (!p.weights) return fail(ctx, PSSA_B200_ERR_INVALID_ARGUMENT, "B200 memory read: this shape needs the [rows, capacity] weight rows as scratch");
     // with an empty bank the launch still publishes the projection (gpu_batch.rs:682-698 projects first)
     static PerDeviceOnce attr_a;
@@ -1100,6 +1097,12 @@ int32_t launch_memory_read(pssa_b200_ctx* ctx, const RetrieveParams& p, bool exa
         if ((rc = after_launch(ctx, "value_mix_kernel")) != PSSA_B200_OK) return rc;
     }
     return PSSA_B200_OK;
+}
+
+// (PSSA_B200_NO_ALL_SLOTS_FUSED keeps the separate kernels: read at every call, a test compares the two)
+bool retrieve_all_fused_runs(const RetrieveParams& p, bool exact) {
+    const char* keep_separate = getenv("PSSA_B200_NO_ALL_SLOTS_FUSED");
+    return !p.no_fused && !exact && !(keep_separate && *keep_separate && *keep_separate != '0') && retrieve_all_fused_eligible(p);
 }
 
 int32_t launch_split_keys(pssa_b200_ctx* ctx, const float* keys, const float* norm_sq, void* k_split, float2* k_stat, int cap, int dk) {
