@@ -49,6 +49,31 @@ __device__ __forceinline__ float ex2_fast(float x) {
     return y;
 }
 
+// packed fp32 pairs: one instruction, two IEEE-rounded results (the all-slots sweeps are bound by instruction issue next
+// to their three hardware approximations per slot)
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 constexpr int kListHalf = 32;  // slots one column half of a row can list under its threshold (about 10 expected)
 constexpr int kCandMax = 13;   // candidates re-scored per row: top_k + kMargin, at most this many (the kernel is
                                // instantiated for 9 and for 13)
@@ -364,7 +389,13 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
             const float2 ks = p.k_stat[i];
             const float kn = sqrtf(ks.x) * 1.0000002f;  // rounded up: it scales an error bound
             const float e = kEpsDot * kn * ks.y * 1.0000002f;
-            kcol_s[i] = i < count ? ks : make_float2(3.0e38f, 1.0f);
+            const float2 kv = i < count ? ks : make_float2(3.0e38f, 1.0f);
+            if constexpr (ALL) {  // slot pairs as (n0, n1, s0, s1): one 16-byte load feeds packed arithmetic on two columns
+                float* pair = reinterpret_cast<float*>(kcol_s) + 4 * (i >> 1) + (i & 1);
+                pair[0] = kv.x, pair[2] = kv.y;
+            } else {
+                kcol_s[i] = kv;
+            }
             kerr_s[i] = i < count ? e : 0.0f;
             if (i < count) m_e = fmaxf(m_e, e), m_s = fmaxf(m_s, ks.y), m_ns = fmaxf(m_ns, ks.x * ks.y * 1.0000002f);
         }
@@ -550,11 +581,16 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                 uint32_t buf0[32], buf1[32];
                 float vmin = CUDART_INF_F, sum = 0.0f, lg_min_t = 0.0f;
                 if (alive) {
+                    const f32x2 qs2 = pack2(qs, qs), m2 = pack2(-2.0f, -2.0f);
+                    const float4* kpair = reinterpret_cast<const float4*>(kcol_s);
                     auto minimum = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float2 kc = kcol_s[c0 + j];
-                            vmin = fminf(vmin, fmaf(-2.0f, __uint_as_float(acc[j]), qs + kc.x) * kc.y);
+                        for (int j = 0; j < 32; j += 2) {
+                            const float4 kc = kpair[(c0 + j) >> 1];
+                            float v0, v1;
+                            unpack2(mul2(fma2(m2, pack2(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1])), add2(qs2, pack2(kc.x, kc.y))),
+                                         pack2(kc.z, kc.w)), v0, v1);
+                            vmin = fminf(vmin, fminf(v0, v1));
                         }
                     };
                     tcgen05_ld_32x32_issue(taddr + c_begin, buf0);
@@ -586,22 +622,36 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                 if (alive) {
                     __nv_bfloat16* my_park = defer ? reinterpret_cast<__nv_bfloat16*>(p.w_split) + (q0 + my_row) * (size_t)(3 * cap)
                                                    : park + (size_t)my_row * W_PITCH;
+                    const f32x2 qs2 = pack2(qs, qs), m2 = pack2(-2.0f, -2.0f), inv1mq2 = pack2(inv1mq, inv1mq), two2 = pack2(2.0f, 2.0f),
+                                one2 = pack2(1.0f, 1.0f), ninv_tau2 = pack2(-inv_tau, -inv_tau), lg_min_t2 = pack2(lg_min_t, lg_min_t);
+                    const float4* kpair = reinterpret_cast<const float4*>(kcol_s);
+                    f32x2 sum2 = pack2(0.0f, 0.0f);
                     const bool row_in = !defer || q0 + my_row < p.rows;
                     auto weights = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
                         for (int j0 = 0; j0 < 32; j0 += 8) {
                             float e[8];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                const float2 kc = kcol_s[c0 + j0 + j];
+                            for (int j = 0; j < 8; j += 2) {
+                                const float4 kc = kpair[(c0 + j0 + j) >> 1];
                                 // slots past the occupied ones carry v = 3e38: every step below keeps the infinity and the weight is 0
-                                const float u = fmaxf(fmaf(-2.0f, __uint_as_float(acc[j0 + j]), qs + kc.x) * kc.y, 0.0f) * inv1mq;
-                                float r, lg;
-                                const float t = fmaf(u, u, u);
-                                asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
-                                asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(lg) : "f"(1.0f + fmaf(2.0f, r, 2.0f * u)));
-                                e[j] = ex2_fast(fmaf(-inv_tau, lg, lg_min_t));
-                                sum += e[j];
+                                float u0, u1;
+                                unpack2(mul2(mul2(fma2(m2, pack2(__uint_as_float(acc[j0 + j]), __uint_as_float(acc[j0 + j + 1])),
+                                                       add2(qs2, pack2(kc.x, kc.y))),
+                                                  pack2(kc.z, kc.w)),
+                                             inv1mq2),
+                                        u0, u1);
+                                const f32x2 u2 = pack2(fmaxf(u0, 0.0f), fmaxf(u1, 0.0f));
+                                float t0, t1, r0, r1, w0, w1, l0, l1, x0, x1;
+                                unpack2(fma2(u2, u2, u2), t0, t1);
+                                asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(t0));
+                                asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r1) : "f"(t1));
+                                unpack2(fma2(two2, pack2(r0, r1), fma2(two2, u2, one2)), w0, w1);
+                                asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l0) : "f"(w0));
+                                asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(l1) : "f"(w1));
+                                unpack2(fma2(ninv_tau2, pack2(l0, l1), lg_min_t2), x0, x1);
+                                e[j] = ex2_fast(x0), e[j + 1] = ex2_fast(x1);
+                                sum2 = add2(sum2, pack2(e[j], e[j + 1]));
                             }
                             uint4 pk;
                             __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
@@ -619,6 +669,9 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                         if (c0 + 64 < c_end) tcgen05_ld_32x32_issue(taddr + c0 + 64, buf0);
                         weights(buf1, c0 + 32);
                     }
+                    float s_lo, s_hi;
+                    unpack2(sum2, s_lo, s_hi);
+                    sum = s_lo + s_hi;
                 }
                 tcgen05_fence_before();
                 row_sum[ch * BM + my_row] = sum;
