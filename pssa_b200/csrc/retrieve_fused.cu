@@ -629,10 +629,10 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                     const bool row_in = !defer || q0 + my_row < p.rows;
                     auto weights = [&](const uint32_t (&acc)[32], int c0) {
 #pragma unroll
-                        for (int j0 = 0; j0 < 32; j0 += 8) {
-                            float e[8];
+                        for (int j0 = 0; j0 < 32; j0 += 16) {
+                            float e[16];
 #pragma unroll
-                            for (int j = 0; j < 8; j += 2) {
+                            for (int j = 0; j < 16; j += 2) {
                                 const float4 kc = kpair[(c0 + j0 + j) >> 1];
                                 // slots past the occupied ones carry v = 3e38: every step below keeps the infinity and the weight is 0
                                 float u0, u1;
@@ -653,12 +653,22 @@ __global__ void __launch_bounds__(kThreads, 1) retrieve_topk_fused_kernel(const 
                                 e[j] = ex2_fast(x0), e[j + 1] = ex2_fast(x1);
                                 sum2 = add2(sum2, pack2(e[j], e[j + 1]));
                             }
-                            uint4 pk;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(e[0], e[1]), h1 = __floats2bfloat162_rn(e[2], e[3]);
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(e[4], e[5]), h3 = __floats2bfloat162_rn(e[6], e[7]);
-                            pk.x = *reinterpret_cast<uint32_t*>(&h0), pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                            pk.z = *reinterpret_cast<uint32_t*>(&h2), pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                            if (row_in) *reinterpret_cast<uint4*>(my_park + c0 + j0) = pk;
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const __nv_bfloat162 hq = __floats2bfloat162_rn(e[2 * q], e[2 * q + 1]);
+                                pk[q] = *reinterpret_cast<const uint32_t*>(&hq);
+                            }
+                            if (defer) {
+                                // 32 bytes per thread and instruction: a whole sector of the row at once
+                                if (row_in)
+                                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(my_park + c0 + j0), "r"(pk[0]),
+                                                 "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
+                                                 : "memory");
+                            } else {
+                                *reinterpret_cast<uint4*>(my_park + c0 + j0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                                *reinterpret_cast<uint4*>(my_park + c0 + j0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                            }
                         }
                     };
                     for (int c0 = c_begin; c0 < c_end; c0 += 64) {
