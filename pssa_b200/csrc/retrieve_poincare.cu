@@ -459,7 +459,6 @@ __device__ __forceinline__ float exp2f_approx(float x) {
     return y;
 }
 
-constexpr int kSoftmaxGroups = 8;  // 128-slot groups the register path of the all-slots softmax holds (capacity <= 1024)
 constexpr int kTopkRegs = 16;  // distances per lane the register path of the top-k selection holds (capacity <= 512)
 
 template <bool EXACT>
