@@ -161,7 +161,8 @@ __global__ void __launch_bounds__(256) multiply_kernel(const float* __restrict__
 // src_rows != 0: indices come from the caller's device memory and are checked here; an index outside the table reads row 0
 // and raises PSSA_B200_ERR_TOKEN in the status word (the rule of the embedding kernel)
 __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restrict__ src, const uint32_t* __restrict__ rows_idx,
-                                                          float* __restrict__ dst, size_t n_rows, int d, size_t src_rows, int* status) {
+                                                          float* __restrict__ dst, __nv_bfloat16* __restrict__ dst16, size_t n_rows, int d,
+                                                          size_t src_rows, int* status) {
     pdl_trigger();  // the next kernel in the stream may start its prologue now ...
     pdl_wait();     // ... and this one, if launched as a dependent, waits here for its own predecessor
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -172,7 +173,9 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const float* __restric
         if (status && idx % d == 0) atomicExch(status, PSSA_B200_ERR_TOKEN);
         row = 0;
     }
-    dst[idx] = src[row * d + idx % d];
+    const float v = src[row * d + idx % d];
+    if (dst) dst[idx] = v;
+    if (dst16) dst16[idx] = __float2bfloat16_rn(v);  // the tensor-core head reads the gathered rows as bf16 only
 }
 
 __global__ void __launch_bounds__(256) to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, size_t n) {
@@ -374,9 +377,10 @@ int32_t launch_multiply(pssa_b200_ctx* ctx, const float* a, const float* b, floa
     return after_launch(ctx, "multiply_kernel");
 }
 
-int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d, size_t src_rows) {
+int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d, size_t src_rows,
+                           void* dst_bf16) {
     PSSA_CUDA(ctx, launch_dependent(gather_rows_kernel, dim3(blocks_for(n_rows * (size_t)d, 256)), dim3(256), 0, ctx->stream, src, rows_idx, dst,
-                                    n_rows, d, src_rows, ctx->status_dev));
+                                    (__nv_bfloat16*)dst_bf16, n_rows, d, src_rows, ctx->status_dev));
     return after_launch(ctx, "gather_rows_kernel");
 }
 

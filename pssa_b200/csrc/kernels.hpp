@@ -215,7 +215,9 @@ int32_t launch_combine_zraw(pssa_b200_ctx* ctx, const float* y, const float* g, 
 int32_t launch_residual(pssa_b200_ctx* ctx, const float* prev, const float* z, float* out, size_t n, float scale);
 int32_t launch_multiply(pssa_b200_ctx* ctx, const float* a, const float* b, float* out, size_t n);
 // src_rows != 0: rows_idx is range checked on the device against a table of src_rows rows (row 0 + PSSA_B200_ERR_TOKEN otherwise)
-int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d, size_t src_rows = 0);
+// dst (fp32) and dst_bf16 are both optional
+int32_t launch_gather_rows(pssa_b200_ctx* ctx, const float* src, const uint32_t* rows_idx, float* dst, size_t n_rows, int d, size_t src_rows = 0,
+                           void* dst_bf16 = nullptr);
 int32_t launch_to_bf16(pssa_b200_ctx* ctx, const float* src, void* dst, size_t n);
 int32_t launch_observe_rows(pssa_b200_ctx* ctx, const uint32_t* last_rows, size_t lanes, const float* weights, int cap, const float* q_pnc,
                             int k, const float* m_val, const float* z_direct, const float* feat_out, const float* feat_in, float scale,

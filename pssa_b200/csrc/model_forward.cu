@@ -504,13 +504,14 @@ int32_t head_rows(pssa_b200_model* m, const float* feats, size_t n_heads, bool w
     pssa_b200_ctx* ctx = m->ctx;
     Workspace& ws = m->ws;
     int32_t rc;
-    if ((rc = launch_gather_rows(ctx, feats, ws.last_rows, ws.last_feat, n_heads, (int)m->d))) return rc;
+    const bool exact = m->precision == PSSA_B200_PRECISION_FP32_EXACT;
+    // the last rows of the lanes; the tensor-core head takes them as bf16 straight from the gather (in place of the z staging buffer)
+    if ((rc = launch_gather_rows(ctx, feats, ws.last_rows, exact ? ws.last_feat : nullptr, n_heads, (int)m->d, 0, exact ? nullptr : ws.z_bf16)))
+        return rc;
     const float scale = 1.0f / std::sqrt((float)m->d);
-    if (m->precision == PSSA_B200_PRECISION_FP32_EXACT) {
+    if (exact) {
         if ((rc = launch_gemm_exact(ctx, ws.last_feat, m->unembed, ws.logits, n_heads, m->v, m->d, m->v, EPI_SCALE, scale))) return rc;
     } else {
-        // the head input is a handful of rows: convert in place of the z staging buffer
-        if ((rc = launch_to_bf16(ctx, ws.last_feat, ws.z_bf16, n_heads * m->d))) return rc;
         if ((rc = launch_gemm_bf16(ctx, ws.z_bf16, m->unembed_bf16, ws.logits, nullptr, n_heads, m->v, m->d, m->v, EPI_SCALE, scale))) return rc;
     }
     if (want_greedy && (rc = launch_greedy(ctx, ws.logits, ws.greedy, n_heads, (int)m->v))) return rc;
